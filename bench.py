@@ -1,0 +1,390 @@
+#!/usr/bin/env python
+"""Benchmark of the fused-op hot path (softmax / RMSNorm / LayerNorm) on B200.
+
+Workload: the fused-op micro-bench configuration -- (a) fp32 softmax over the
+last axis of logits[32,16,1024,1024] ~ N(0,4) under a causal -inf mask, (b) bf16
+RMSNorm and LayerNorm over x[16384,4096] ~ N(0,1), gamma ~ N(1,0.02), beta = 0,
+eps = 1e-6.  One "step" is one pass of all three kernels over that batch.
+Algorithmic bytes per step = 2*2^29*4 + 2*(2*2^26*2) = 4,831,838,208.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+One process per GPU (torchrun sets RANK / LOCAL_RANK / WORLD_SIZE); every rank
+runs the full batch on its own data (weak scaling, no collective on the data
+path); rank 0 prints ONE JSON line.  `value` is device-resident throughput;
+`e2e` is the same metric through the reference-facing host-pointer call
+(b200_execute_host: H2D copy, run, D2H copy, wait) from pinned host memory.
+`--impl reference` times the CPU restatement of the same ops on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+SM_SHAPE = (32, 16, 1024, 1024)
+NORM_SHAPE = (16384, 4096)
+EPS = 1e-6
+SM_BYTES = 2 * int(np.prod(SM_SHAPE)) * 4
+NORM_BYTES = 2 * int(np.prod(NORM_SHAPE)) * 2
+STEP_BYTES = SM_BYTES + 2 * NORM_BYTES
+METRIC = "GB/s (softmax/norm)"
+WORKLOAD = ("fused-op micro-bench: fp32 causal softmax logits[32,16,1024,1024] + bf16 RMSNorm + bf16 LayerNorm x[16384,4096], "
+            "eps 1e-6")
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            return json.load(fh), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+# ----------------------------------------------------------------------------- inputs ---
+def make_inputs(seed: int, sm_shape=SM_SHAPE, norm_shape=NORM_SHAPE, logits_out=None):
+    """Seeded synthetic inputs (PCG64): logits ~ N(0, 4) fp32, x ~ N(0,1) bf16, gamma ~ N(1, 0.02) bf16, beta = 0."""
+    import ml_dtypes
+    rng = np.random.default_rng(seed)
+    n = int(np.prod(sm_shape))
+    logits = logits_out if logits_out is not None else np.empty(n, dtype=np.float32)
+    chunk = 1 << 24
+    for lo in range(0, n, chunk):
+        hi = min(n, lo + chunk)
+        rng.standard_normal(hi - lo, dtype=np.float32, out=logits[lo:hi])
+        logits[lo:hi] *= 2.0
+    x = rng.standard_normal(int(np.prod(norm_shape)), dtype=np.float32).astype(ml_dtypes.bfloat16).reshape(norm_shape)
+    gamma = (1.0 + 0.02 * rng.standard_normal(norm_shape[1], dtype=np.float32)).astype(ml_dtypes.bfloat16)
+    beta = np.zeros(norm_shape[1], dtype=ml_dtypes.bfloat16)
+    return logits.reshape(sm_shape), x, gamma, beta
+
+
+# ------------------------------------------------------------------------ clock sampler ---
+class ClockSampler:
+    """Samples SM clock, power and clock-event reasons of one GPU through NVML while a region runs (read-only)."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+               0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting", 0x100: "display_clock_setting", 0x10: "sync_boost"}
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz, self.power = [], set(), None, []
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = index
+            if visible:
+                ids = [v for v in visible.split(",") if v.strip()]
+                if index < len(ids) and ids[index].strip().isdigit():
+                    phys = int(ids[index])
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                self.power.append(nv.nvmlDeviceGetPowerUsage(self._h) / 1000.0)
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.01)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples), "power_w_max": max(self.power) if self.power else None}
+
+
+# --------------------------------------------------------------------------- CPU legs ---
+def cpu_pass(cport, logits, x, gamma, beta, out_sm, out_n):
+    cport.softmax_f32(logits, 1.0, True, logits.shape[-2], out=out_sm)
+    cport.norm(x, gamma, None, EPS, True, out=out_n)
+    cport.norm(x, gamma, beta, EPS, False, out=out_n)
+
+
+def cpu_sample_shapes(frac_rows: int):
+    """A bounded sample of the workload: the first `frac_rows`-th of the softmax batch and of the norm rows."""
+    return (SM_SHAPE[0] // frac_rows,) + SM_SHAPE[1:], (NORM_SHAPE[0] // frac_rows, NORM_SHAPE[1])
+
+
+def run_cpu_baseline(logits, x, gamma, beta, frac_rows=4, passes=3):
+    from oracle import cport
+    sm_shape, n_shape = cpu_sample_shapes(frac_rows)
+    lg = logits[:sm_shape[0]]
+    xs = x[:n_shape[0]]
+    out_sm, out_n = np.empty_like(lg), np.empty_like(xs)
+    cpu_pass(cport, lg, xs, gamma, beta, out_sm, out_n)  # warm-up (page faults, thread pool)
+    best = float("inf")
+    for _ in range(passes):
+        t0 = time.perf_counter()
+        cpu_pass(cport, lg, xs, gamma, beta, out_sm, out_n)
+        best = min(best, time.perf_counter() - t0)
+    nbytes = 2 * lg.size * 4 + 2 * (2 * xs.size * 2)
+    return {"value": nbytes / best / 1e9, "unit": "GB/s", "cores": cport.num_threads(), "kind": "port",
+            "sample": f"softmax on logits{list(sm_shape)} + RMSNorm + LayerNorm on x{list(n_shape)} (1/{frac_rows} of the batch), best of {passes} passes"}
+
+
+def run_reference_arm(args, rank, world):
+    """The CPU implementation of the path on the host cores.  The reference's own implementation is Apple-only
+    (MPSGraph), and GoMLX's pure-Go CPU backend needs a Go toolchain that is absent, so this times the C
+    restatement (oracle/oracle_c.c) with every host thread OpenMP gives it."""
+    if rank != 0:
+        return
+    from oracle import cport
+    frac = 4
+    sm_shape, n_shape = cpu_sample_shapes(frac)
+    logits, x, gamma, beta = make_inputs(0, sm_shape, n_shape)
+    out_sm, out_n = np.empty_like(logits), np.empty_like(x)
+    for _ in range(args.warmup):
+        cpu_pass(cport, logits, x, gamma, beta, out_sm, out_n)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_pass(cport, logits, x, gamma, beta, out_sm, out_n)
+    dt = time.perf_counter() - t0
+    nbytes = 2 * logits.size * 4 + 2 * (2 * x.size * 2)
+    value = nbytes * args.steps / dt / 1e9
+    sample = f"each step = softmax on logits{list(sm_shape)} + RMSNorm + LayerNorm on x{list(n_shape)} (1/{frac} of the batch)"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cport.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "reference's own MPSGraph path and GoMLX's Go CPU backend are unavailable on this box; C restatement timed instead",
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------- GPU arm ---
+def compile_graph(b200, backend, name, shapes_in, build):
+    builder = backend.Builder(name)
+    f = builder.Main()
+    params = [f.Parameter(f"p{i}", s) for i, s in enumerate(shapes_in)]
+    outs = build(f, *params)
+    f.Return(list(outs) if isinstance(outs, (list, tuple)) else [outs], None)
+    return builder, builder.Compile()
+
+
+def run_b200_arm(args, rank, local_rank, world):
+    import torch
+    import torch.distributed as dist
+
+    import go_darwinml_b200 as b200
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    backend = b200.New(f"device={local_rank}")
+    L = b200.lib()
+    from go_darwinml_b200 import _lib as libmod
+
+    def host_alloc(nbytes, dtype, shape):
+        err = libmod.B200Error()
+        p = L.b200_host_alloc(nbytes, ctypes.byref(err))
+        if err.code:
+            raise RuntimeError(L.take_string(err.message))
+        buf = (ctypes.c_char * nbytes).from_address(p)
+        return p, np.frombuffer(buf, dtype=dtype).reshape(shape)
+
+    # pinned host copies of the inputs and of the outputs (e2e leg)
+    import ml_dtypes
+    bf16 = np.dtype(ml_dtypes.bfloat16)
+    n_sm, n_norm = int(np.prod(SM_SHAPE)), int(np.prod(NORM_SHAPE))
+    p_logits, h_logits = host_alloc(n_sm * 4, np.float32, (n_sm,))
+    logits, x, gamma, beta = make_inputs(rank, logits_out=h_logits)
+    p_x, h_x = host_alloc(n_norm * 2, bf16, NORM_SHAPE)
+    h_x[...] = x
+    p_g, h_g = host_alloc(NORM_SHAPE[1] * 2, bf16, (NORM_SHAPE[1],))
+    h_g[...] = gamma
+    p_b, h_b = host_alloc(NORM_SHAPE[1] * 2, bf16, (NORM_SHAPE[1],))
+    h_b[...] = beta
+    p_osm, h_osm = host_alloc(n_sm * 4, np.float32, SM_SHAPE)
+    p_orms, h_orms = host_alloc(n_norm * 2, bf16, NORM_SHAPE)
+    p_oln, h_oln = host_alloc(n_norm * 2, bf16, NORM_SHAPE)
+
+    D = b200.dtypes
+    s_logits, s_x, s_g = b200.Shape(D.Float32, SM_SHAPE), b200.Shape(D.BFloat16, NORM_SHAPE), b200.Shape(D.BFloat16, (NORM_SHAPE[1],))
+    _, exe_sm = compile_graph(b200, backend, "softmax", [s_logits], lambda f, a: f.FusedSoftmaxMasked(a, 1.0, True, None))
+    _, exe_rms = compile_graph(b200, backend, "rms", [s_x, s_g], lambda f, a, g: f.FusedRMSNorm(a, [-1], EPS, g))
+    _, exe_ln = compile_graph(b200, backend, "ln", [s_x, s_g, s_g], lambda f, a, g, b: f.FusedLayerNorm(a, [-1], EPS, g, b))
+    _, exe_all = compile_graph(b200, backend, "all", [s_logits, s_x, s_g, s_g],
+                               lambda f, a, xx, g, b: (f.FusedSoftmaxMasked(a, 1.0, True, None), f.FusedRMSNorm(xx, [-1], EPS, g),
+                                                      f.FusedLayerNorm(xx, [-1], EPS, g, b)))
+    d_logits = backend.BufferFromFlatData(local_rank, h_logits, s_logits)
+    d_x = backend.BufferFromFlatData(local_rank, h_x.reshape(-1), s_x)
+    d_g = backend.BufferFromFlatData(local_rank, h_g, s_g)
+    d_b = backend.BufferFromFlatData(local_rank, h_b, s_g)
+    backend.Synchronize(local_rank)
+
+    err = libmod.B200Error()
+    stream = torch.cuda.ExternalStream(L.b200_device_stream(local_rank, ctypes.byref(err)), device=local_rank)
+
+    def step(ev=None):
+        """One pass of the hot path on device-resident inputs; optionally brackets the softmax launch with events."""
+        if ev:
+            ev[0].record(stream)
+        o1 = exe_sm.Execute([d_logits], None, local_rank)
+        if ev:
+            ev[1].record(stream)
+        o2 = exe_rms.Execute([d_x, d_g], None, local_rank)
+        if ev:
+            ev[2].record(stream)
+        o3 = exe_ln.Execute([d_x, d_g, d_b], None, local_rank)
+        if ev:
+            ev[3].record(stream)
+        for o in o1 + o2 + o3:
+            backend.BufferFinalize(o)
+
+    def barrier():
+        backend.Synchronize(local_rank)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local_rank)
+    with sampler:
+        t_start.record(stream)
+        for i in range(args.steps):
+            step(evs[i])
+        t_end.record(stream)
+        backend.Synchronize(local_rank)
+        torch.cuda.synchronize()
+    barrier()
+    elapsed_ms = t_start.elapsed_time(t_end)
+    sm_ms = float(np.mean([e[0].elapsed_time(e[1]) for e in evs]))
+    rms_ms = float(np.mean([e[1].elapsed_time(e[2]) for e in evs]))
+    ln_ms = float(np.mean([e[2].elapsed_time(e[3]) for e in evs]))
+
+    # ---- e2e: host pointers in, host pointers out, through b200_execute_host ----
+    in_ptrs = (ctypes.c_void_p * 4)(p_logits, p_x, p_g, p_b)
+    in_sizes = (ctypes.c_int64 * 4)(n_sm * 4, n_norm * 2, NORM_SHAPE[1] * 2, NORM_SHAPE[1] * 2)
+    in_dtypes = (ctypes.c_int * 4)(int(D.Float32), int(D.BFloat16), int(D.BFloat16), int(D.BFloat16))
+    shp = [(ctypes.c_int64 * 4)(*SM_SHAPE), (ctypes.c_int64 * 2)(*NORM_SHAPE), (ctypes.c_int64 * 1)(NORM_SHAPE[1]), (ctypes.c_int64 * 1)(NORM_SHAPE[1])]
+    in_shapes = (ctypes.POINTER(ctypes.c_int64) * 4)(*[ctypes.cast(s, ctypes.POINTER(ctypes.c_int64)) for s in shp])
+    in_ranks = (ctypes.c_int * 4)(4, 2, 1, 1)
+    out_ptrs = (ctypes.c_void_p * 3)(p_osm, p_orms, p_oln)
+    out_sizes = (ctypes.c_int64 * 3)(n_sm * 4, n_norm * 2, n_norm * 2)
+    out_dtypes = (ctypes.c_int * 3)(int(D.Float32), int(D.BFloat16), int(D.BFloat16))
+    oshp = [(ctypes.c_int64 * 4)(*SM_SHAPE), (ctypes.c_int64 * 2)(*NORM_SHAPE), (ctypes.c_int64 * 2)(*NORM_SHAPE)]
+    out_shapes = (ctypes.POINTER(ctypes.c_int64) * 3)(*[ctypes.cast(s, ctypes.POINTER(ctypes.c_int64)) for s in oshp])
+    out_ranks = (ctypes.c_int * 3)(4, 2, 2)
+
+    def e2e_step():
+        e = libmod.B200Error()
+        ok = L.b200_execute_host(exe_all.handle, in_ptrs, in_sizes, in_dtypes, in_shapes, in_ranks, 4, out_ptrs, out_sizes, out_dtypes,
+                                 out_shapes, out_ranks, 3, ctypes.byref(e))
+        if not ok:
+            raise RuntimeError(L.take_string(e.message))
+
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e_step()
+    barrier()
+    e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_start.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e_end.record(stream)
+    backend.Synchronize(local_rank)
+    torch.cuda.synchronize()
+    e2e_ms = e_start.elapsed_time(e_end)
+    h2d = n_sm * 4 + n_norm * 2 + 2 * NORM_SHAPE[1] * 2
+    d2h = n_sm * 4 + 2 * n_norm * 2
+
+    # max over ranks, on device-measured times
+    times = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=f"cuda:{local_rank}")
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_ms = float(times[0]), float(times[1])
+
+    if rank == 0:
+        peaks, peak_src = measured_peaks()
+        ms_per_step = elapsed_ms / args.steps
+        value = world * STEP_BYTES / (ms_per_step * 1e-3) / 1e9
+        e2e_value = world * STEP_BYTES / (e2e_ms / e2e_steps * 1e-3) / 1e9
+        achieved = SM_BYTES / (sm_ms * 1e-3) / 1e9
+        traffic_path = os.path.join(ROOT, "profiles", "softmax_traffic.json")
+        traffic = None
+        if os.path.exists(traffic_path):
+            with open(traffic_path) as fh:
+                traffic = json.load(fh).get("dram_bytes_per_launch_full_workload")
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "l2": "inputs larger than L2: every step streams 4.8 GB through a 126 MB L2",
+                       "per_gpu_batch": "full (weak scaling, no data-path collective)", "algorithmic_bytes_per_step": STEP_BYTES},
+            "clocks": sampler.summary(),
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                    "ms_per_step": e2e_ms / e2e_steps, "call": "b200_execute_host (pinned host buffers)"},
+            "gpu_launches": args.steps * (exe_sm.NumLaunches() + exe_rms.NumLaunches() + exe_ln.NumLaunches()),
+            "roofline": {"bound": "hbm", "kernel": "softmax_rows_kernel<float,8,32> (causal)", "achieved": achieved,
+                         "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peak_src,
+                         "traffic": traffic, "algorithmic_bytes_per_launch": SM_BYTES, "ms_per_launch": sm_ms,
+                         "note": "causal launch skips loading 16-byte vectors right of the diagonal, so DRAM traffic is below the algorithmic bytes"},
+            "kernels": {"softmax_causal_f32": {"ms": sm_ms, "GB/s": SM_BYTES / sm_ms / 1e6, "frac_of_peak": SM_BYTES / sm_ms / 1e6 / peaks["hbm_gbs"]},
+                        "rms_norm_bf16": {"ms": rms_ms, "GB/s": NORM_BYTES / rms_ms / 1e6, "frac_of_peak": NORM_BYTES / rms_ms / 1e6 / peaks["hbm_gbs"]},
+                        "layer_norm_bf16": {"ms": ln_ms, "GB/s": NORM_BYTES / ln_ms / 1e6, "frac_of_peak": NORM_BYTES / ln_ms / 1e6 / peaks["hbm_gbs"]}},
+        }
+        if world == 1:
+            line["cpu_baseline"] = run_cpu_baseline(h_logits.reshape(SM_SHAPE), h_x, h_g, h_b)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+    else:
+        run_b200_arm(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

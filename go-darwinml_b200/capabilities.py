@@ -1,0 +1,47 @@
+"""backends.Capabilities of this backend (ref mpsgraph/gomlx/capabilities.go:14-167).
+
+The reference declares 96 op types and 12 dtypes.  Listed here is what this
+backend lowers; op types of the reference that are outside the forward
+(inference) path -- convolution, pooling, scatter, dynamic slice/update, RNG,
+batch-norm training/gradient, While/If/Sort/Call -- are absent, so GoMLX reports
+them as not implemented instead of failing late.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict
+
+from .backend import dtypes
+
+OPERATIONS = [
+    "Parameter", "Constant", "Identity", "Iota",
+    "Abs", "Neg", "Sqrt", "Rsqrt", "Exp", "Expm1", "Log", "Log1p", "Sin", "Cos", "Tanh", "Logistic", "Erf", "Floor", "Ceil",
+    "Round", "Sign", "LogicalNot", "BitwiseNot", "IsFinite", "IsNaN",
+    "Add", "Sub", "Mul", "Div", "Rem", "Pow", "Max", "Min", "Atan2", "LogicalAnd", "LogicalOr", "LogicalXor", "BitwiseAnd",
+    "BitwiseOr", "BitwiseXor", "ShiftLeft", "ShiftRightArithmetic", "ShiftRightLogical",
+    "Equal", "NotEqual", "LessThan", "LessOrEqual", "GreaterThan", "GreaterOrEqual",
+    "EqualTotalOrder", "NotEqualTotalOrder", "LessThanTotalOrder", "LessOrEqualTotalOrder", "GreaterThanTotalOrder",
+    "GreaterOrEqualTotalOrder",
+    "Reshape", "Transpose", "ConvertDType", "BroadcastInDim", "Slice", "Concatenate", "Reverse", "Pad", "Where", "Clamp",
+    "DotGeneral", "ReduceSum", "ReduceProduct", "ReduceMax", "ReduceMin", "ReduceLogicalAnd", "ReduceLogicalOr", "ArgMinMax",
+    "Gather", "BatchNormForInference",
+    "FusedSoftmax", "FusedGelu", "FusedLayerNorm", "FusedDense", "FusedAttentionQKVProjection",
+    "FusedScaledDotProductAttention",
+]
+
+
+@dataclass
+class Capabilities:
+    Functions: bool = False  # no sub-functions (the reference sets true for While/If/Call closures)
+    Operations: Dict[str, bool] = field(default_factory=dict)
+    DTypes: Dict[int, bool] = field(default_factory=dict)
+
+
+def backend_capabilities() -> Capabilities:
+    return Capabilities(
+        Functions=False,
+        Operations={name: True for name in OPERATIONS},
+        DTypes={int(d): True for d in (dtypes.Bool, dtypes.Int8, dtypes.Int16, dtypes.Int32, dtypes.Int64, dtypes.Float16,
+                                      dtypes.BFloat16, dtypes.Float32, dtypes.Float64, dtypes.Uint8, dtypes.Uint16,
+                                      dtypes.Uint32, dtypes.Uint64)},
+    )

@@ -1,0 +1,198 @@
+// Shared internal declarations of libb200mlx: dtypes, errors, the device
+// runtime (stream + caching allocator), buffers, the graph IR and the kernel
+// launchers.  Nothing here is part of the C ABI; see include/b200mlx.h for that.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/b200mlx.h"
+
+#ifdef __CUDACC__
+#define B200_HD __host__ __device__
+#else
+#define B200_HD
+#endif
+
+namespace b200 {
+
+// ---------------------------------------------------------------- dtypes ---
+B200_HD inline int dtype_size(int dt) {
+  switch (dt) {
+    case B200_BOOL: case B200_INT8: case B200_UINT8: return 1;
+    case B200_INT16: case B200_UINT16: case B200_FLOAT16: case B200_BFLOAT16: return 2;
+    case B200_INT32: case B200_UINT32: case B200_FLOAT32: return 4;
+    case B200_INT64: case B200_UINT64: case B200_FLOAT64: return 8;
+  }
+  return 0;
+}
+B200_HD inline bool dtype_valid(int dt) { return dt >= 0 && dt <= 12; }
+B200_HD inline bool dtype_is_float(int dt) {
+  return dt == B200_FLOAT16 || dt == B200_BFLOAT16 || dt == B200_FLOAT32 || dt == B200_FLOAT64;
+}
+B200_HD inline bool dtype_is_int(int dt) { return dtype_valid(dt) && !dtype_is_float(dt) && dt != B200_BOOL; }
+B200_HD inline bool dtype_is_unsigned(int dt) {
+  return dt == B200_UINT8 || dt == B200_UINT16 || dt == B200_UINT32 || dt == B200_UINT64 || dt == B200_BOOL;
+}
+const char* dtype_name(int dt);
+
+// ---------------------------------------------------------------- errors ---
+struct Status {
+  int code = 0;
+  std::string msg;
+  bool ok() const { return code == 0; }
+  static Status OK() { return Status(); }
+  static Status Invalid(const std::string& m) { return Status{B200_ERR_INVALID, m}; }
+  static Status Cuda(const std::string& m) { return Status{B200_ERR_CUDA, m}; }
+  static Status Unsupported(const std::string& m) { return Status{B200_ERR_UNSUPPORTED, m}; }
+  static Status Oom(const std::string& m) { return Status{B200_ERR_OOM, m}; }
+};
+std::string strfmt(const char* fmt, ...);
+inline void clear_error(B200Error* e) {
+  if (e) { e->code = 0; e->message = nullptr; }
+}
+inline void set_error(B200Error* e, const Status& s) {
+  if (!e) return;
+  e->code = s.code;
+  e->message = s.ok() ? nullptr : strdup(s.msg.c_str());
+}
+#define B200_CUDA_TRY(expr)                                                                         \
+  do {                                                                                              \
+    cudaError_t _e = (expr);                                                                        \
+    if (_e != cudaSuccess)                                                                          \
+      return ::b200::Status::Cuda(::b200::strfmt("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), \
+                                                 __FILE__, __LINE__));                              \
+  } while (0)
+#define B200_TRY(expr)          \
+  do {                          \
+    ::b200::Status _s = (expr); \
+    if (!_s.ok()) return _s;    \
+  } while (0)
+
+// --------------------------------------------------------------- runtime ---
+// One Device object per CUDA ordinal, created on first use and kept until
+// process exit.  It owns the stream every launch of this library goes to and a
+// stream-ordered caching allocator (blocks are reused only on that stream, so
+// freeing needs no synchronisation).
+class Device {
+ public:
+  static Status Get(int ordinal, Device** out);
+  int ordinal() const { return ordinal_; }
+  cudaStream_t stream() const { return stream_; }
+  int sm_count() const { return sm_count_; }
+  Status Alloc(int64_t nbytes, void** out);
+  void Free(void* p);
+  int64_t BytesReserved();
+  void Trim();
+  Status MakeCurrent();
+  Status Synchronize();
+  // Launch status: any launch helper calls this after a kernel launch.
+  Status CheckLaunch(const char* what);
+  // A small pinned staging area used by synchronous host<->device copies.
+ private:
+  Device() = default;
+  int ordinal_ = 0;
+  int sm_count_ = 148;
+  cudaStream_t stream_ = nullptr;
+  std::mutex mu_;
+  std::multimap<int64_t, void*> free_blocks_;  // size -> ptr
+  std::map<void*, int64_t> live_blocks_;       // ptr -> size
+  int64_t reserved_ = 0;
+};
+
+struct Buffer {
+  int device = 0;
+  int dtype = B200_FLOAT32;
+  std::vector<int64_t> dims;
+  void* ptr = nullptr;
+  int64_t nbytes = 0;
+  bool owned = true;
+  int64_t num_elements() const {
+    int64_t n = 1;
+    for (auto d : dims) n *= d;
+    return n;
+  }
+};
+
+// ------------------------------------------------------------------- IR ----
+enum class Op : int {
+  // leaves
+  Parameter, Constant, Iota,
+  // unary
+  Abs, Neg, Sqrt, Rsqrt, Exp, Expm1, Log, Log1p, Sin, Cos, Tanh, Sigmoid, Erf, Floor, Ceil, Round, Sign,
+  LogicalNot, BitwiseNot, IsFinite, IsNaN, Identity,
+  GeluExact, GeluTanh, Relu, Silu,  // activations, produced by b200_gelu / b200_dense
+  // binary
+  Add, Sub, Mul, Div, Rem, Pow, Max, Min, Atan2, LogicalAnd, LogicalOr, LogicalXor, BitwiseAnd, BitwiseOr,
+  BitwiseXor, ShiftLeft, ShiftRight, ShiftRightLogical,
+  // compare
+  Equal, NotEqual, LessThan, LessOrEqual, GreaterThan, GreaterOrEqual,
+  // ternary
+  Where, Clamp,
+  // data movement
+  Cast, Reshape, Transpose, BroadcastInDim, Slice, Concatenate, Reverse, Pad,
+  // contraction / reduction / indexing
+  DotGeneral, Reduce, ArgMinMax, Gather,
+  // fused
+  Softmax, SoftmaxMasked, LayerNorm, RmsNorm,
+  kNumOps
+};
+const char* op_name(Op op);
+bool op_is_unary(Op op);
+bool op_is_binary(Op op);
+bool op_is_compare(Op op);
+// Ops the elementwise interpreter can evaluate inside a fused chain.
+bool op_is_elementwise(Op op);
+
+struct Graph;
+
+struct Node {
+  Graph* graph = nullptr;
+  int id = 0;
+  Op op = Op::Parameter;
+  int dtype = B200_FLOAT32;
+  std::vector<int64_t> dims;
+  std::vector<Node*> in;
+  // generic attributes; meaning depends on op (documented where each op is built)
+  std::vector<int64_t> ia;            // integer attributes
+  std::vector<double> fa;             // floating attributes
+  std::vector<uint8_t> data;          // constant payload (host copy)
+  int64_t num_elements() const {
+    int64_t n = 1;
+    for (auto d : dims) n *= d;
+    return n;
+  }
+  int rank() const { return (int)dims.size(); }
+};
+
+struct Graph {
+  int device = 0;
+  std::vector<std::unique_ptr<Node>> nodes;
+  Node* Add(Op op, int dtype, std::vector<int64_t> dims, std::vector<Node*> in) {
+    auto n = std::make_unique<Node>();
+    n->graph = this;
+    n->id = (int)nodes.size();
+    n->op = op;
+    n->dtype = dtype;
+    n->dims = std::move(dims);
+    n->in = std::move(in);
+    nodes.push_back(std::move(n));
+    return nodes.back().get();
+  }
+};
+
+// What a B200Context handle points to: one graph under construction and its device.
+struct Ctx {
+  Graph graph;
+  Device* dev = nullptr;
+};
+
+}  // namespace b200

@@ -1,0 +1,1042 @@
+// Graph construction: the b200_* op functions of the C ABI.  Each validates its
+// operands, infers the result shape and appends one node (fused ops that are
+// pure rewrites append several).  No device work happens here.
+//
+// Counterpart in the reference: the Go Function methods (mpsgraph
+// function.go:288-3075, dotgeneral.go, gather.go) together with the native
+// graph-op wrappers they call (bridge.m:197-1106).  Shape rules follow those
+// call sites; GoMLX's shapeinference package itself is not part of that tree.
+#include <algorithm>
+#include <cmath>
+#include <set>
+
+#include "common.h"
+
+namespace b200 {
+
+const char* op_name(Op op) {
+  static const char* names[] = {
+      "Parameter", "Constant", "Iota",
+      "Abs", "Neg", "Sqrt", "Rsqrt", "Exp", "Expm1", "Log", "Log1p", "Sin", "Cos", "Tanh", "Sigmoid", "Erf", "Floor",
+      "Ceil", "Round", "Sign", "LogicalNot", "BitwiseNot", "IsFinite", "IsNaN", "Identity",
+      "GeluExact", "GeluTanh", "Relu", "Silu",
+      "Add", "Sub", "Mul", "Div", "Rem", "Pow", "Max", "Min", "Atan2", "LogicalAnd", "LogicalOr", "LogicalXor",
+      "BitwiseAnd", "BitwiseOr", "BitwiseXor", "ShiftLeft", "ShiftRight", "ShiftRightLogical",
+      "Equal", "NotEqual", "LessThan", "LessOrEqual", "GreaterThan", "GreaterOrEqual",
+      "Where", "Clamp",
+      "Cast", "Reshape", "Transpose", "BroadcastInDim", "Slice", "Concatenate", "Reverse", "Pad",
+      "DotGeneral", "Reduce", "ArgMinMax", "Gather",
+      "Softmax", "SoftmaxMasked", "LayerNorm", "RmsNorm"};
+  static_assert(sizeof(names) / sizeof(names[0]) == (size_t)Op::kNumOps, "op_name table out of date");
+  return names[(int)op];
+}
+bool op_is_unary(Op op) { return op >= Op::Abs && op <= Op::Silu; }
+bool op_is_binary(Op op) { return op >= Op::Add && op <= Op::ShiftRightLogical; }
+bool op_is_compare(Op op) { return op >= Op::Equal && op <= Op::GreaterOrEqual; }
+bool op_is_elementwise(Op op) {
+  return op_is_unary(op) || op_is_binary(op) || op_is_compare(op) || op == Op::Where || op == Op::Clamp || op == Op::Cast;
+}
+
+namespace {
+
+std::string dims_str(const std::vector<int64_t>& d) {
+  std::string s = "[";
+  for (size_t i = 0; i < d.size(); ++i) s += (i ? "," : "") + std::to_string(d[i]);
+  return s + "]";
+}
+
+Status check_node(B200Context ctx, B200Value v, const char* what, Node** out) {
+  if (!ctx) return Status::Invalid(std::string(what) + ": null context");
+  if (!v) return Status::Invalid(std::string(what) + ": null value");
+  Node* n = reinterpret_cast<Node*>(v);
+  Ctx* c = reinterpret_cast<Ctx*>(ctx);
+  if (n->graph != &c->graph || n->id < 0 || n->id >= (int)c->graph.nodes.size() || c->graph.nodes[n->id].get() != n)
+    return Status::Invalid(std::string(what) + ": value does not belong to this context");
+  *out = n;
+  return Status::OK();
+}
+
+Status broadcast_shapes(const char* what, const std::vector<int64_t>& a, const std::vector<int64_t>& b,
+                        std::vector<int64_t>* out) {
+  const size_t r = std::max(a.size(), b.size());
+  out->assign(r, 1);
+  for (size_t i = 0; i < r; ++i) {
+    const int64_t da = i < r - a.size() ? 1 : a[i - (r - a.size())];
+    const int64_t db = i < r - b.size() ? 1 : b[i - (r - b.size())];
+    if (da != db && da != 1 && db != 1)
+      return Status::Invalid(strfmt("%s: shapes %s and %s do not broadcast", what, dims_str(a).c_str(), dims_str(b).c_str()));
+    (*out)[i] = (da == 1) ? db : da;
+  }
+  return Status::OK();
+}
+
+B200Value ret(B200Error* err, const Status& s, Node* n) {
+  set_error(err, s);
+  return s.ok() ? reinterpret_cast<B200Value>(n) : nullptr;
+}
+
+Status unary_impl(B200Context ctx, Op op, B200Value x, Node** out) {
+  Node* n;
+  const char* name = op_name(op);
+  B200_TRY(check_node(ctx, x, name, &n));
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  int out_dtype = n->dtype;
+  switch (op) {
+    case Op::Sqrt: case Op::Rsqrt: case Op::Exp: case Op::Expm1: case Op::Log: case Op::Log1p: case Op::Sin: case Op::Cos:
+    case Op::Tanh: case Op::Sigmoid: case Op::Erf: case Op::Floor: case Op::Ceil: case Op::Round: case Op::GeluExact:
+    case Op::GeluTanh: case Op::Silu:
+      if (!dtype_is_float(n->dtype)) return Status::Invalid(strfmt("%s: needs a float operand, got %s", name, dtype_name(n->dtype)));
+      break;
+    case Op::LogicalNot:
+      if (n->dtype != B200_BOOL) return Status::Invalid(strfmt("%s: needs a Bool operand, got %s", name, dtype_name(n->dtype)));
+      break;
+    case Op::BitwiseNot:
+      if (dtype_is_float(n->dtype)) return Status::Invalid(strfmt("%s: needs an integer or Bool operand", name));
+      break;
+    case Op::Abs: case Op::Neg: case Op::Sign: case Op::Relu:
+      if (n->dtype == B200_BOOL) return Status::Invalid(strfmt("%s: Bool operand", name));
+      break;
+    case Op::IsFinite: case Op::IsNaN:
+      out_dtype = B200_BOOL;
+      break;
+    default: break;
+  }
+  *out = g.Add(op, out_dtype, n->dims, {n});
+  return Status::OK();
+}
+
+Status binary_impl(B200Context ctx, Op op, B200Value lhs, B200Value rhs, Node** out) {
+  Node *a, *b;
+  const char* name = op_name(op);
+  B200_TRY(check_node(ctx, lhs, name, &a));
+  B200_TRY(check_node(ctx, rhs, name, &b));
+  if (a->dtype != b->dtype)
+    return Status::Invalid(strfmt("%s: operand dtypes differ (%s vs %s)", name, dtype_name(a->dtype), dtype_name(b->dtype)));
+  const int dt = a->dtype;
+  switch (op) {
+    case Op::LogicalAnd: case Op::LogicalOr: case Op::LogicalXor:
+      if (dt != B200_BOOL) return Status::Invalid(strfmt("%s: needs Bool operands, got %s", name, dtype_name(dt)));
+      break;
+    case Op::BitwiseAnd: case Op::BitwiseOr: case Op::BitwiseXor:
+      if (dtype_is_float(dt)) return Status::Invalid(strfmt("%s: needs integer or Bool operands", name));
+      break;
+    case Op::ShiftLeft: case Op::ShiftRight: case Op::ShiftRightLogical:
+      if (!dtype_is_int(dt)) return Status::Invalid(strfmt("%s: needs integer operands", name));
+      break;
+    case Op::Atan2:
+      if (!dtype_is_float(dt)) return Status::Invalid(strfmt("%s: needs float operands", name));
+      break;
+    default:
+      if (dt == B200_BOOL && !op_is_compare(op) && op != Op::Max && op != Op::Min)
+        return Status::Invalid(strfmt("%s: Bool operands", name));
+      break;
+  }
+  std::vector<int64_t> dims;
+  B200_TRY(broadcast_shapes(name, a->dims, b->dims, &dims));
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  *out = g.Add(op, op_is_compare(op) ? (int)B200_BOOL : dt, dims, {a, b});
+  return Status::OK();
+}
+
+Status normalize_axis(const char* what, int axis, int rank, int* out) {
+  int a = axis < 0 ? axis + rank : axis;
+  if (a < 0 || a >= rank) return Status::Invalid(strfmt("%s: axis %d out of range for rank %d", what, axis, rank));
+  *out = a;
+  return Status::OK();
+}
+
+Status check_shape(const char* what, const int64_t* shape, int rank) {
+  if (rank < 0 || rank > 16) return Status::Invalid(strfmt("%s: rank %d not supported", what, rank));
+  if (rank > 0 && !shape) return Status::Invalid(strfmt("%s: null shape", what));
+  for (int i = 0; i < rank; ++i)
+    if (shape[i] < 0) return Status::Invalid(strfmt("%s: negative dimension", what));
+  return Status::OK();
+}
+
+Node* make_scalar_const(Graph& g, int dtype, double v);
+
+}  // namespace
+
+// Scalar constant of `dtype` holding v.  The reference makes helper scalars as
+// Float32 and casts them (function.go:212-231); the value therefore passes
+// through float32 first, and so it does here.
+namespace {
+Node* make_scalar_const(Graph& g, int dtype, double v) {
+  const float f32 = (float)v;
+  Node* n = g.Add(Op::Constant, B200_FLOAT32, {}, {});
+  n->data.resize(4);
+  memcpy(n->data.data(), &f32, 4);
+  if (dtype != B200_FLOAT32) n = g.Add(Op::Cast, dtype, {}, {n});
+  return n;
+}
+}  // namespace
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+const char* b200_version(void) { return "b200mlx 0.1 (sm_100a)"; }
+
+int b200_device_count(B200Error* err) {
+  clear_error(err);
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    set_error(err, Status::Cuda(strfmt("cudaGetDeviceCount: %s", cudaGetErrorString(e))));
+    return -1;
+  }
+  return n;
+}
+
+B200Context b200_create_context(int device, B200Error* err) {
+  clear_error(err);
+  Device* dev = nullptr;
+  Status s = Device::Get(device, &dev);
+  if (!s.ok()) { set_error(err, s); return nullptr; }
+  Ctx* c = new Ctx();
+  c->graph.device = device;
+  c->dev = dev;
+  return c;
+}
+void b200_destroy_context(B200Context ctx) { delete reinterpret_cast<Ctx*>(ctx); }
+const char* b200_device_name(B200Context ctx) {
+  if (!ctx) return nullptr;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, reinterpret_cast<Ctx*>(ctx)->graph.device) != cudaSuccess) return strdup("unknown");
+  return strdup(prop.name);
+}
+int b200_context_device(B200Context ctx) { return ctx ? reinterpret_cast<Ctx*>(ctx)->graph.device : -1; }
+
+int b200_value_dtype(B200Value v) { return v ? reinterpret_cast<Node*>(v)->dtype : -1; }
+int b200_value_rank(B200Value v) { return v ? reinterpret_cast<Node*>(v)->rank() : -1; }
+int b200_value_shape(B200Value v, int64_t* dims, int cap) {
+  if (!v) return -1;
+  Node* n = reinterpret_cast<Node*>(v);
+  for (int i = 0; i < n->rank() && i < cap; ++i) dims[i] = n->dims[i];
+  return n->rank();
+}
+
+// ---- leaves -----------------------------------------------------------------
+B200Value b200_placeholder(B200Context ctx, int dtype, const int64_t* shape, int rank, B200Error* err) {
+  clear_error(err);
+  if (!ctx) return ret(err, Status::Invalid("placeholder: null context"), nullptr);
+  if (!dtype_valid(dtype)) return ret(err, Status::Invalid("placeholder: bad dtype"), nullptr);
+  Status s = check_shape("placeholder", shape, rank);
+  if (!s.ok()) return ret(err, s, nullptr);
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  return ret(err, Status::OK(), g.Add(Op::Parameter, dtype, std::vector<int64_t>(shape, shape + rank), {}));
+}
+
+B200Value b200_constant(B200Context ctx, const void* data, int64_t nbytes, int dtype, const int64_t* shape, int rank,
+                        B200Error* err) {
+  clear_error(err);
+  if (!ctx) return ret(err, Status::Invalid("constant: null context"), nullptr);
+  if (!dtype_valid(dtype)) return ret(err, Status::Invalid("constant: bad dtype"), nullptr);
+  Status s = check_shape("constant", shape, rank);
+  if (!s.ok()) return ret(err, s, nullptr);
+  int64_t n = 1;
+  for (int i = 0; i < rank; ++i) n *= shape[i];
+  if (nbytes != n * dtype_size(dtype))
+    return ret(err, Status::Invalid(strfmt("constant: %lld bytes given, shape needs %lld", (long long)nbytes, (long long)(n * dtype_size(dtype)))), nullptr);
+  if (nbytes > 0 && !data) return ret(err, Status::Invalid("constant: null data"), nullptr);
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  Node* node = g.Add(Op::Constant, dtype, std::vector<int64_t>(shape, shape + rank), {});
+  node->data.assign((const uint8_t*)data, (const uint8_t*)data + nbytes);
+  return ret(err, Status::OK(), node);
+}
+
+B200Value b200_iota(B200Context ctx, int dtype, const int64_t* shape, int rank, int axis, B200Error* err) {
+  clear_error(err);
+  if (!ctx) return ret(err, Status::Invalid("Iota: null context"), nullptr);
+  if (!dtype_valid(dtype) || dtype == B200_BOOL) return ret(err, Status::Invalid("Iota: bad dtype"), nullptr);
+  Status s = check_shape("Iota", shape, rank);
+  if (!s.ok()) return ret(err, s, nullptr);
+  int a;
+  s = normalize_axis("Iota", axis, rank, &a);
+  if (!s.ok()) return ret(err, s, nullptr);
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  Node* n = g.Add(Op::Iota, dtype, std::vector<int64_t>(shape, shape + rank), {});
+  n->ia = {a};
+  return ret(err, Status::OK(), n);
+}
+
+// ---- unary / binary / compare -------------------------------------------------
+#define B200_UNARY(fn, OP)                                           \
+  B200Value fn(B200Context ctx, B200Value x, B200Error* err) {       \
+    clear_error(err);                                                \
+    Node* n = nullptr;                                               \
+    Status s = unary_impl(ctx, Op::OP, x, &n);                       \
+    return ret(err, s, n);                                           \
+  }
+B200_UNARY(b200_abs, Abs) B200_UNARY(b200_neg, Neg) B200_UNARY(b200_sqrt, Sqrt) B200_UNARY(b200_rsqrt, Rsqrt)
+B200_UNARY(b200_exp, Exp) B200_UNARY(b200_expm1, Expm1) B200_UNARY(b200_log, Log) B200_UNARY(b200_log1p, Log1p)
+B200_UNARY(b200_sin, Sin) B200_UNARY(b200_cos, Cos) B200_UNARY(b200_tanh, Tanh) B200_UNARY(b200_sigmoid, Sigmoid)
+B200_UNARY(b200_erf, Erf) B200_UNARY(b200_floor, Floor) B200_UNARY(b200_ceil, Ceil) B200_UNARY(b200_round, Round)
+B200_UNARY(b200_sign, Sign) B200_UNARY(b200_logical_not, LogicalNot) B200_UNARY(b200_bitwise_not, BitwiseNot)
+B200_UNARY(b200_is_finite, IsFinite) B200_UNARY(b200_is_nan, IsNaN) B200_UNARY(b200_identity, Identity)
+#undef B200_UNARY
+
+#define B200_BINARY(fn, OP)                                                        \
+  B200Value fn(B200Context ctx, B200Value lhs, B200Value rhs, B200Error* err) {    \
+    clear_error(err);                                                              \
+    Node* n = nullptr;                                                             \
+    Status s = binary_impl(ctx, Op::OP, lhs, rhs, &n);                             \
+    return ret(err, s, n);                                                         \
+  }
+B200_BINARY(b200_add, Add) B200_BINARY(b200_sub, Sub) B200_BINARY(b200_mul, Mul) B200_BINARY(b200_div, Div)
+B200_BINARY(b200_rem, Rem) B200_BINARY(b200_pow, Pow) B200_BINARY(b200_max, Max) B200_BINARY(b200_min, Min)
+B200_BINARY(b200_atan2, Atan2) B200_BINARY(b200_logical_and, LogicalAnd) B200_BINARY(b200_logical_or, LogicalOr)
+B200_BINARY(b200_logical_xor, LogicalXor) B200_BINARY(b200_bitwise_and, BitwiseAnd) B200_BINARY(b200_bitwise_or, BitwiseOr)
+B200_BINARY(b200_bitwise_xor, BitwiseXor) B200_BINARY(b200_shift_left, ShiftLeft) B200_BINARY(b200_shift_right, ShiftRight)
+B200_BINARY(b200_shift_right_logical, ShiftRightLogical)
+B200_BINARY(b200_equal, Equal) B200_BINARY(b200_not_equal, NotEqual) B200_BINARY(b200_less_than, LessThan)
+B200_BINARY(b200_less_or_equal, LessOrEqual) B200_BINARY(b200_greater_than, GreaterThan)
+B200_BINARY(b200_greater_or_equal, GreaterOrEqual)
+#undef B200_BINARY
+
+// ---- shape ops ----------------------------------------------------------------
+B200Value b200_reshape(B200Context ctx, B200Value x, const int64_t* shape, int rank, B200Error* err) {
+  clear_error(err);
+  Node* n;
+  Status s = check_node(ctx, x, "Reshape", &n);
+  if (s.ok()) s = check_shape("Reshape", shape, rank);
+  if (!s.ok()) return ret(err, s, nullptr);
+  int64_t count = 1;
+  for (int i = 0; i < rank; ++i) count *= shape[i];
+  if (count != n->num_elements())
+    return ret(err, Status::Invalid(strfmt("Reshape: %s has %lld elements, target %s has %lld", dims_str(n->dims).c_str(),
+                                           (long long)n->num_elements(), dims_str(std::vector<int64_t>(shape, shape + rank)).c_str(),
+                                           (long long)count)), nullptr);
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  return ret(err, Status::OK(), g.Add(Op::Reshape, n->dtype, std::vector<int64_t>(shape, shape + rank), {n}));
+}
+
+B200Value b200_transpose(B200Context ctx, B200Value x, const int* permutation, int rank, B200Error* err) {
+  clear_error(err);
+  Node* n;
+  Status s = check_node(ctx, x, "Transpose", &n);
+  if (!s.ok()) return ret(err, s, nullptr);
+  if (rank != n->rank()) return ret(err, Status::Invalid(strfmt("Transpose: %d permutation entries for rank %d", rank, n->rank())), nullptr);
+  std::vector<bool> seen(rank, false);
+  std::vector<int64_t> dims(rank);
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  std::vector<int64_t> perm(rank);
+  for (int i = 0; i < rank; ++i) {
+    const int p = permutation[i];
+    if (p < 0 || p >= rank || seen[p]) return ret(err, Status::Invalid("Transpose: not a permutation"), nullptr);
+    seen[p] = true;
+    dims[i] = n->dims[p];
+    perm[i] = p;
+  }
+  Node* t = g.Add(Op::Transpose, n->dtype, dims, {n});
+  t->ia = perm;
+  return ret(err, Status::OK(), t);
+}
+
+B200Value b200_cast(B200Context ctx, B200Value x, int dtype, B200Error* err) {
+  clear_error(err);
+  Node* n;
+  Status s = check_node(ctx, x, "ConvertDType", &n);
+  if (!s.ok()) return ret(err, s, nullptr);
+  if (!dtype_valid(dtype)) return ret(err, Status::Invalid("ConvertDType: bad dtype"), nullptr);
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  if (dtype == n->dtype) return ret(err, Status::OK(), g.Add(Op::Identity, dtype, n->dims, {n}));
+  return ret(err, Status::OK(), g.Add(Op::Cast, dtype, n->dims, {n}));
+}
+
+B200Value b200_broadcast_in_dim(B200Context ctx, B200Value x, const int64_t* shape, int rank, const int* broadcast_axes,
+                                int num_axes, B200Error* err) {
+  clear_error(err);
+  Node* n;
+  Status s = check_node(ctx, x, "BroadcastInDim", &n);
+  if (s.ok()) s = check_shape("BroadcastInDim", shape, rank);
+  if (!s.ok()) return ret(err, s, nullptr);
+  if (num_axes != n->rank())
+    return ret(err, Status::Invalid(strfmt("BroadcastInDim: %d broadcast axes for operand rank %d", num_axes, n->rank())), nullptr);
+  std::vector<int64_t> axes(num_axes);
+  std::vector<bool> seen(rank, false);
+  for (int i = 0; i < num_axes; ++i) {
+    const int a = broadcast_axes[i];
+    if (a < 0 || a >= rank || seen[a]) return ret(err, Status::Invalid("BroadcastInDim: bad broadcast axis"), nullptr);
+    seen[a] = true;
+    if (n->dims[i] != 1 && n->dims[i] != shape[a])
+      return ret(err, Status::Invalid(strfmt("BroadcastInDim: operand dim %d (%lld) does not match output dim %d (%lld)", i,
+                                             (long long)n->dims[i], a, (long long)shape[a])), nullptr);
+    axes[i] = a;
+  }
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  Node* b = g.Add(Op::BroadcastInDim, n->dtype, std::vector<int64_t>(shape, shape + rank), {n});
+  b->ia = axes;
+  return ret(err, Status::OK(), b);
+}
+
+B200Value b200_broadcast_to(B200Context ctx, B200Value x, const int64_t* shape, int rank, B200Error* err) {
+  clear_error(err);
+  Node* n;
+  Status s = check_node(ctx, x, "BroadcastTo", &n);
+  if (!s.ok()) return ret(err, s, nullptr);
+  if (rank < n->rank()) return ret(err, Status::Invalid("BroadcastTo: target rank smaller than operand rank"), nullptr);
+  std::vector<int> axes(n->rank());
+  for (int i = 0; i < n->rank(); ++i) axes[i] = rank - n->rank() + i;
+  return b200_broadcast_in_dim(ctx, x, shape, rank, axes.data(), n->rank(), err);
+}
+
+B200Value b200_slice(B200Context ctx, B200Value x, const int64_t* starts, const int64_t* ends, const int64_t* strides,
+                     int rank, B200Error* err) {
+  clear_error(err);
+  Node* n;
+  Status s = check_node(ctx, x, "Slice", &n);
+  if (!s.ok()) return ret(err, s, nullptr);
+  if (rank != n->rank()) return ret(err, Status::Invalid(strfmt("Slice: %d bounds for rank %d", rank, n->rank())), nullptr);
+  std::vector<int64_t> dims(rank), attrs;
+  for (int i = 0; i < rank; ++i) {
+    const int64_t st = strides ? strides[i] : 1;
+    if (st < 1 || starts[i] < 0 || ends[i] > n->dims[i] || starts[i] > ends[i])
+      return ret(err, Status::Invalid(strfmt("Slice: axis %d bounds [%lld:%lld:%lld] invalid for dim %lld", i, (long long)starts[i],
+                                             (long long)ends[i], (long long)st, (long long)n->dims[i])), nullptr);
+    dims[i] = (ends[i] - starts[i] + st - 1) / st;
+    attrs.push_back(starts[i]);
+    attrs.push_back(st);
+  }
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  Node* o = g.Add(Op::Slice, n->dtype, dims, {n});
+  o->ia = attrs;  // (start, stride) per axis
+  return ret(err, Status::OK(), o);
+}
+
+B200Value b200_concatenate(B200Context ctx, const B200Value* tensors, int num_tensors, int axis, B200Error* err) {
+  clear_error(err);
+  if (num_tensors < 1 || !tensors) return ret(err, Status::Invalid("Concatenate: no operands"), nullptr);
+  std::vector<Node*> in(num_tensors);
+  for (int i = 0; i < num_tensors; ++i) {
+    Status s = check_node(ctx, tensors[i], "Concatenate", &in[i]);
+    if (!s.ok()) return ret(err, s, nullptr);
+  }
+  int a;
+  Status s = normalize_axis("Concatenate", axis, in[0]->rank(), &a);
+  if (!s.ok()) return ret(err, s, nullptr);
+  std::vector<int64_t> dims = in[0]->dims;
+  for (int i = 1; i < num_tensors; ++i) {
+    if (in[i]->dtype != in[0]->dtype || in[i]->rank() != in[0]->rank())
+      return ret(err, Status::Invalid("Concatenate: operands differ in dtype or rank"), nullptr);
+    for (int d = 0; d < in[0]->rank(); ++d)
+      if (d != a && in[i]->dims[d] != in[0]->dims[d]) return ret(err, Status::Invalid("Concatenate: operand shapes differ off the axis"), nullptr);
+    dims[a] += in[i]->dims[a];
+  }
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  Node* o = g.Add(Op::Concatenate, in[0]->dtype, dims, in);
+  o->ia = {a};
+  return ret(err, Status::OK(), o);
+}
+
+B200Value b200_reverse(B200Context ctx, B200Value x, const int* axes, int num_axes, B200Error* err) {
+  clear_error(err);
+  Node* n;
+  Status s = check_node(ctx, x, "Reverse", &n);
+  if (!s.ok()) return ret(err, s, nullptr);
+  std::vector<int64_t> ax;
+  for (int i = 0; i < num_axes; ++i) {
+    int a;
+    s = normalize_axis("Reverse", axes[i], n->rank(), &a);
+    if (!s.ok()) return ret(err, s, nullptr);
+    ax.push_back(a);
+  }
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  Node* o = g.Add(Op::Reverse, n->dtype, n->dims, {n});
+  o->ia = ax;
+  return ret(err, Status::OK(), o);
+}
+
+B200Value b200_pad(B200Context ctx, B200Value x, B200Value pad_value, const int64_t* pad_before, const int64_t* pad_after,
+                   int rank, B200Error* err) {
+  clear_error(err);
+  Node *n, *pv;
+  Status s = check_node(ctx, x, "Pad", &n);
+  if (s.ok()) s = check_node(ctx, pad_value, "Pad", &pv);
+  if (!s.ok()) return ret(err, s, nullptr);
+  if (rank != n->rank()) return ret(err, Status::Invalid("Pad: rank mismatch"), nullptr);
+  if (pv->num_elements() != 1 || pv->dtype != n->dtype) return ret(err, Status::Invalid("Pad: fill value must be one element of the operand dtype"), nullptr);
+  std::vector<int64_t> dims(rank), attrs;
+  for (int i = 0; i < rank; ++i) {
+    if (pad_before[i] < 0 || pad_after[i] < 0) return ret(err, Status::Unsupported("Pad: negative padding"), nullptr);
+    dims[i] = n->dims[i] + pad_before[i] + pad_after[i];
+    attrs.push_back(pad_before[i]);
+  }
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  Node* o = g.Add(Op::Pad, n->dtype, dims, {n, pv});
+  o->ia = attrs;
+  return ret(err, Status::OK(), o);
+}
+
+// ---- selection ----------------------------------------------------------------
+B200Value b200_where(B200Context ctx, B200Value cond, B200Value on_true, B200Value on_false, B200Error* err) {
+  clear_error(err);
+  Node *c, *t, *f;
+  Status s = check_node(ctx, cond, "Where", &c);
+  if (s.ok()) s = check_node(ctx, on_true, "Where", &t);
+  if (s.ok()) s = check_node(ctx, on_false, "Where", &f);
+  if (!s.ok()) return ret(err, s, nullptr);
+  if (c->dtype != B200_BOOL) return ret(err, Status::Invalid("Where: condition must be Bool"), nullptr);
+  if (t->dtype != f->dtype) return ret(err, Status::Invalid("Where: branch dtypes differ"), nullptr);
+  std::vector<int64_t> d1, d2;
+  s = broadcast_shapes("Where", t->dims, f->dims, &d1);
+  if (s.ok()) s = broadcast_shapes("Where", c->dims, d1, &d2);
+  if (!s.ok()) return ret(err, s, nullptr);
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  return ret(err, Status::OK(), g.Add(Op::Where, t->dtype, d2, {c, t, f}));
+}
+
+B200Value b200_clamp(B200Context ctx, B200Value min_val, B200Value x, B200Value max_val, B200Error* err) {
+  clear_error(err);
+  Node *lo, *n, *hi;
+  Status s = check_node(ctx, min_val, "Clamp", &lo);
+  if (s.ok()) s = check_node(ctx, x, "Clamp", &n);
+  if (s.ok()) s = check_node(ctx, max_val, "Clamp", &hi);
+  if (!s.ok()) return ret(err, s, nullptr);
+  if (lo->dtype != n->dtype || hi->dtype != n->dtype) return ret(err, Status::Invalid("Clamp: dtypes differ"), nullptr);
+  std::vector<int64_t> d1, d2;
+  s = broadcast_shapes("Clamp", lo->dims, n->dims, &d1);
+  if (s.ok()) s = broadcast_shapes("Clamp", d1, hi->dims, &d2);
+  if (!s.ok()) return ret(err, s, nullptr);
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  return ret(err, Status::OK(), g.Add(Op::Clamp, n->dtype, d2, {lo, n, hi}));
+}
+
+// ---- contraction ----------------------------------------------------------------
+B200Value b200_dot_general(B200Context ctx, B200Value lhs, const int* lhs_contracting, int num_lhs_contracting,
+                           const int* lhs_batch, int num_lhs_batch, B200Value rhs, const int* rhs_contracting,
+                           int num_rhs_contracting, const int* rhs_batch, int num_rhs_batch, B200Error* err) {
+  clear_error(err);
+  Node *a, *b;
+  Status s = check_node(ctx, lhs, "DotGeneral", &a);
+  if (s.ok()) s = check_node(ctx, rhs, "DotGeneral", &b);
+  if (!s.ok()) return ret(err, s, nullptr);
+  if (a->dtype != b->dtype)
+    return ret(err, Status::Invalid(strfmt("DotGeneral: operand dtypes differ (%s vs %s)", dtype_name(a->dtype), dtype_name(b->dtype))), nullptr);
+  if (a->dtype == B200_BOOL) return ret(err, Status::Invalid("DotGeneral: Bool operands"), nullptr);
+  if (num_lhs_contracting != num_rhs_contracting || num_lhs_batch != num_rhs_batch)
+    return ret(err, Status::Invalid("DotGeneral: lhs and rhs must name the same number of contracting and of batch axes"), nullptr);
+  auto norm = [&](const int* axes, int n, int rank, std::vector<int64_t>* out) -> Status {
+    for (int i = 0; i < n; ++i) {
+      int ax;
+      B200_TRY(normalize_axis("DotGeneral", axes[i], rank, &ax));
+      out->push_back(ax);
+    }
+    return Status::OK();
+  };
+  std::vector<int64_t> lc, lb, rc, rb;
+  s = norm(lhs_contracting, num_lhs_contracting, a->rank(), &lc);
+  if (s.ok()) s = norm(lhs_batch, num_lhs_batch, a->rank(), &lb);
+  if (s.ok()) s = norm(rhs_contracting, num_rhs_contracting, b->rank(), &rc);
+  if (s.ok()) s = norm(rhs_batch, num_rhs_batch, b->rank(), &rb);
+  if (!s.ok()) return ret(err, s, nullptr);
+  std::set<int64_t> lset(lc.begin(), lc.end()), rset(rc.begin(), rc.end());
+  lset.insert(lb.begin(), lb.end());
+  rset.insert(rb.begin(), rb.end());
+  if (lset.size() != lc.size() + lb.size() || rset.size() != rc.size() + rb.size())
+    return ret(err, Status::Invalid("DotGeneral: an axis is named twice"), nullptr);
+  for (size_t i = 0; i < lc.size(); ++i)
+    if (a->dims[lc[i]] != b->dims[rc[i]])
+      return ret(err, Status::Invalid(strfmt("DotGeneral: contracting dims differ (%lld vs %lld)", (long long)a->dims[lc[i]], (long long)b->dims[rc[i]])), nullptr);
+  for (size_t i = 0; i < lb.size(); ++i)
+    if (a->dims[lb[i]] != b->dims[rb[i]])
+      return ret(err, Status::Invalid(strfmt("DotGeneral: batch dims differ (%lld vs %lld)", (long long)a->dims[lb[i]], (long long)b->dims[rb[i]])), nullptr);
+  // Output dims: batch ++ lhs free ++ rhs free (ref dotgeneral.go:34-50).
+  std::vector<int64_t> dims;
+  for (auto ax : lb) dims.push_back(a->dims[ax]);
+  for (int i = 0; i < a->rank(); ++i)
+    if (!lset.count(i)) dims.push_back(a->dims[i]);
+  for (int i = 0; i < b->rank(); ++i)
+    if (!rset.count(i)) dims.push_back(b->dims[i]);
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  Node* o = g.Add(Op::DotGeneral, a->dtype, dims, {a, b});
+  // ia = [nc, nb, lc..., lb..., rc..., rb...]; optional bias is in[2]; fa[0] = activation
+  o->ia = {(int64_t)lc.size(), (int64_t)lb.size()};
+  o->ia.insert(o->ia.end(), lc.begin(), lc.end());
+  o->ia.insert(o->ia.end(), lb.begin(), lb.end());
+  o->ia.insert(o->ia.end(), rc.begin(), rc.end());
+  o->ia.insert(o->ia.end(), rb.begin(), rb.end());
+  o->fa = {(double)B200_ACT_NONE};
+  return ret(err, Status::OK(), o);
+}
+
+B200Value b200_matmul(B200Context ctx, B200Value lhs, B200Value rhs, B200Error* err) {
+  clear_error(err);
+  Node *a, *b;
+  Status s = check_node(ctx, lhs, "MatMul", &a);
+  if (s.ok()) s = check_node(ctx, rhs, "MatMul", &b);
+  if (!s.ok()) return ret(err, s, nullptr);
+  if (a->rank() < 2 || a->rank() != b->rank()) return ret(err, Status::Invalid("MatMul: operands need equal rank >= 2"), nullptr);
+  const int r = a->rank();
+  std::vector<int> batch(r - 2);
+  for (int i = 0; i < r - 2; ++i) batch[i] = i;
+  const int lc = r - 1, rc = r - 2;
+  return b200_dot_general(ctx, lhs, &lc, 1, batch.data(), r - 2, rhs, &rc, 1, batch.data(), r - 2, err);
+}
+
+// ---- reductions -----------------------------------------------------------------
+B200Value b200_reduce(B200Context ctx, B200Value x, int reduce_type, const int* axes, int num_axes, B200Error* err) {
+  clear_error(err);
+  Node* n;
+  Status s = check_node(ctx, x, "Reduce", &n);
+  if (!s.ok()) return ret(err, s, nullptr);
+  if (reduce_type < 0 || reduce_type > 3) return ret(err, Status::Invalid("Reduce: bad reduce type"), nullptr);
+  std::set<int64_t> ax;
+  if (num_axes == 0) {
+    for (int i = 0; i < n->rank(); ++i) ax.insert(i);  // empty = all (ref function.go:1153-1158)
+  } else {
+    for (int i = 0; i < num_axes; ++i) {
+      int a;
+      s = normalize_axis("Reduce", axes[i], n->rank(), &a);
+      if (!s.ok()) return ret(err, s, nullptr);
+      if (!ax.insert(a).second) return ret(err, Status::Invalid("Reduce: axis named twice"), nullptr);
+    }
+  }
+  std::vector<int64_t> dims;
+  for (int i = 0; i < n->rank(); ++i)
+    if (!ax.count(i)) dims.push_back(n->dims[i]);
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  Node* o = g.Add(Op::Reduce, n->dtype, dims, {n});
+  o->ia = {reduce_type};
+  o->ia.insert(o->ia.end(), ax.begin(), ax.end());
+  return ret(err, Status::OK(), o);
+}
+
+static B200Value argminmax(B200Context ctx, B200Value x, int axis, int output_dtype, bool is_min, B200Error* err) {
+  clear_error(err);
+  Node* n;
+  Status s = check_node(ctx, x, "ArgMinMax", &n);
+  if (!s.ok()) return ret(err, s, nullptr);
+  int a;
+  s = normalize_axis("ArgMinMax", axis, n->rank(), &a);
+  if (!s.ok()) return ret(err, s, nullptr);
+  if (!dtype_is_int(output_dtype)) return ret(err, Status::Invalid("ArgMinMax: output dtype must be an integer type"), nullptr);
+  if (n->dtype == B200_BOOL) return ret(err, Status::Invalid("ArgMinMax: Bool operand"), nullptr);
+  if (n->dims[a] == 0) return ret(err, Status::Invalid("ArgMinMax: reduced axis has size 0"), nullptr);
+  std::vector<int64_t> dims;
+  for (int i = 0; i < n->rank(); ++i)
+    if (i != a) dims.push_back(n->dims[i]);
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  Node* o = g.Add(Op::ArgMinMax, output_dtype, dims, {n});
+  o->ia = {a, is_min ? 1 : 0};
+  return ret(err, Status::OK(), o);
+}
+B200Value b200_argmin(B200Context ctx, B200Value x, int axis, int output_dtype, B200Error* err) {
+  return argminmax(ctx, x, axis, output_dtype, true, err);
+}
+B200Value b200_argmax(B200Context ctx, B200Value x, int axis, int output_dtype, B200Error* err) {
+  return argminmax(ctx, x, axis, output_dtype, false, err);
+}
+
+// ---- gather ---------------------------------------------------------------------
+B200Value b200_gather(B200Context ctx, B200Value operand, B200Value start_indices, int index_vector_axis,
+                      const int* offset_output_axes, int num_offset_output_axes, const int* collapsed_slice_axes,
+                      int num_collapsed_slice_axes, const int* start_index_map, int num_start_index_map,
+                      const int64_t* slice_sizes, int num_slice_sizes, bool indices_are_sorted, B200Error* err) {
+  (void)indices_are_sorted;
+  clear_error(err);
+  Node *op, *idx;
+  Status s = check_node(ctx, operand, "Gather", &op);
+  if (s.ok()) s = check_node(ctx, start_indices, "Gather", &idx);
+  if (!s.ok()) return ret(err, s, nullptr);
+  if (!dtype_is_int(idx->dtype)) return ret(err, Status::Invalid("Gather: start indices must be integers"), nullptr);
+  const int orank = op->rank(), irank = idx->rank();
+  if (num_slice_sizes != orank) return ret(err, Status::Invalid("Gather: sliceSizes must have one entry per operand axis"), nullptr);
+  if (index_vector_axis < 0 || index_vector_axis > irank) return ret(err, Status::Invalid("Gather: indexVectorAxis out of range"), nullptr);
+  // indexVectorAxis == rank means an implicit trailing axis of size 1.
+  const int64_t ncomp = index_vector_axis == irank ? 1 : idx->dims[index_vector_axis];
+  if (ncomp != num_start_index_map) return ret(err, Status::Invalid("Gather: startIndexMap length must equal the index vector size"), nullptr);
+  std::set<int> collapsed;
+  for (int i = 0; i < num_collapsed_slice_axes; ++i) {
+    const int a = collapsed_slice_axes[i];
+    if (a < 0 || a >= orank || !collapsed.insert(a).second) return ret(err, Status::Invalid("Gather: bad collapsedSliceAxes"), nullptr);
+    if (slice_sizes[a] != 1) return ret(err, Status::Invalid("Gather: a collapsed axis must have slice size 1"), nullptr);
+  }
+  for (int i = 0; i < orank; ++i)
+    if (slice_sizes[i] < 0 || slice_sizes[i] > op->dims[i]) return ret(err, Status::Invalid("Gather: slice size out of range"), nullptr);
+  for (int i = 0; i < num_start_index_map; ++i)
+    if (start_index_map[i] < 0 || start_index_map[i] >= orank) return ret(err, Status::Invalid("Gather: bad startIndexMap"), nullptr);
+  if (num_offset_output_axes != orank - num_collapsed_slice_axes)
+    return ret(err, Status::Invalid("Gather: offsetOutputAxes must have one entry per non-collapsed operand axis"), nullptr);
+  const int batch_rank = index_vector_axis == irank ? irank : irank - 1;
+  const int out_rank = batch_rank + num_offset_output_axes;
+  std::set<int> offset_axes;
+  for (int i = 0; i < num_offset_output_axes; ++i) {
+    const int a = offset_output_axes[i];
+    if (a < 0 || a >= out_rank || !offset_axes.insert(a).second) return ret(err, Status::Invalid("Gather: bad offsetOutputAxes"), nullptr);
+    if (i > 0 && offset_output_axes[i] <= offset_output_axes[i - 1]) return ret(err, Status::Invalid("Gather: offsetOutputAxes must ascend"), nullptr);
+  }
+  std::vector<int64_t> batch_dims, offset_dims, dims(out_rank);
+  for (int i = 0; i < irank; ++i)
+    if (i != index_vector_axis) batch_dims.push_back(idx->dims[i]);
+  for (int i = 0; i < orank; ++i)
+    if (!collapsed.count(i)) offset_dims.push_back(slice_sizes[i]);
+  size_t bi = 0, oi = 0;
+  for (int d = 0; d < out_rank; ++d) dims[d] = offset_axes.count(d) ? offset_dims[oi++] : batch_dims[bi++];
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  Node* o = g.Add(Op::Gather, op->dtype, dims, {op, idx});
+  // ia = [index_vector_axis, n_off, off..., n_col, col..., n_map, map..., n_ss, ss...]
+  o->ia = {index_vector_axis, num_offset_output_axes};
+  for (int i = 0; i < num_offset_output_axes; ++i) o->ia.push_back(offset_output_axes[i]);
+  o->ia.push_back(num_collapsed_slice_axes);
+  for (int i = 0; i < num_collapsed_slice_axes; ++i) o->ia.push_back(collapsed_slice_axes[i]);
+  o->ia.push_back(num_start_index_map);
+  for (int i = 0; i < num_start_index_map; ++i) o->ia.push_back(start_index_map[i]);
+  o->ia.push_back(num_slice_sizes);
+  for (int i = 0; i < num_slice_sizes; ++i) o->ia.push_back(slice_sizes[i]);
+  return ret(err, Status::OK(), o);
+}
+
+// out[..., i, ...] = x[..., indices[..., i, ...], ...] along `axis`; indices has x's rank.
+// Expressed as an XLA gather over flattened coordinates is awkward, so it is
+// lowered to: Iota coordinates for the other axes are implicit in the general
+// gather kernel through a full index tensor built here from primitives.
+B200Value b200_gather_along_axis(B200Context ctx, B200Value x, B200Value indices, int axis, B200Error* err) {
+  clear_error(err);
+  Node *n, *idx;
+  Status s = check_node(ctx, x, "GatherAlongAxis", &n);
+  if (s.ok()) s = check_node(ctx, indices, "GatherAlongAxis", &idx);
+  if (!s.ok()) return ret(err, s, nullptr);
+  int a;
+  s = normalize_axis("GatherAlongAxis", axis, n->rank(), &a);
+  if (!s.ok()) return ret(err, s, nullptr);
+  if (idx->rank() != n->rank() || !dtype_is_int(idx->dtype)) return ret(err, Status::Invalid("GatherAlongAxis: indices must be integers of the operand's rank"), nullptr);
+  for (int d = 0; d < n->rank(); ++d)
+    if (d != a && idx->dims[d] != n->dims[d]) return ret(err, Status::Invalid("GatherAlongAxis: index shape must match the operand off the axis"), nullptr);
+  // Build a [.., rank] coordinate tensor: coordinate d is Iota(d) except on `axis`, where it is the index.
+  const int r = n->rank();
+  std::vector<int64_t> ext = idx->dims;
+  ext.push_back(1);
+  std::vector<B200Value> parts;
+  for (int d = 0; d < r; ++d) {
+    B200Value c;
+    if (d == a) c = b200_reshape(ctx, indices, ext.data(), r + 1, err);
+    else c = b200_iota(ctx, idx->dtype, ext.data(), r + 1, d, err);
+    if (!c) return nullptr;
+    parts.push_back(c);
+  }
+  B200Value coords = b200_concatenate(ctx, parts.data(), r, r, err);
+  if (!coords) return nullptr;
+  std::vector<int> collapsed(r), map(r);
+  std::vector<int64_t> ss(r, 1);
+  for (int d = 0; d < r; ++d) collapsed[d] = map[d] = d;
+  return b200_gather(ctx, x, coords, r, nullptr, 0, collapsed.data(), r, map.data(), r, ss.data(), r, false, err);
+}
+
+// ---- fused ops ------------------------------------------------------------------
+B200Value b200_softmax(B200Context ctx, B200Value x, int axis, B200Error* err) {
+  clear_error(err);
+  Node* n;
+  Status s = check_node(ctx, x, "FusedSoftmax", &n);
+  if (!s.ok()) return ret(err, s, nullptr);
+  int a;
+  s = normalize_axis("FusedSoftmax", axis, n->rank(), &a);
+  if (!s.ok()) return ret(err, s, nullptr);
+  if (!dtype_is_float(n->dtype)) return ret(err, Status::Invalid("FusedSoftmax: needs a float operand"), nullptr);
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  Node* o = g.Add(Op::Softmax, n->dtype, n->dims, {n});
+  o->ia = {a};
+  return ret(err, Status::OK(), o);
+}
+
+B200Value b200_softmax_masked(B200Context ctx, B200Value x, double scale, int causal, B200Value mask, B200Error* err) {
+  clear_error(err);
+  Node *n, *m = nullptr;
+  Status s = check_node(ctx, x, "SoftmaxMasked", &n);
+  if (s.ok() && mask) s = check_node(ctx, mask, "SoftmaxMasked", &m);
+  if (!s.ok()) return ret(err, s, nullptr);
+  if (!dtype_is_float(n->dtype) || n->dtype == B200_FLOAT64) return ret(err, Status::Invalid("SoftmaxMasked: needs a 16/32-bit float operand"), nullptr);
+  if (n->rank() < 2) return ret(err, Status::Invalid("SoftmaxMasked: operand needs rank >= 2 ([..., Sq, Sk])"), nullptr);
+  if (m) {
+    if (m->dtype != B200_BOOL && m->dtype != n->dtype) return ret(err, Status::Invalid("SoftmaxMasked: mask must be Bool or of the operand dtype"), nullptr);
+    if (m->rank() > n->rank()) return ret(err, Status::Invalid("SoftmaxMasked: mask rank exceeds operand rank"), nullptr);
+    const int off = n->rank() - m->rank();
+    for (int i = 0; i < m->rank(); ++i)
+      if (m->dims[i] != 1 && m->dims[i] != n->dims[off + i]) return ret(err, Status::Invalid("SoftmaxMasked: mask does not broadcast to the scores"), nullptr);
+  }
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  std::vector<Node*> in = {n};
+  if (m) in.push_back(m);
+  Node* o = g.Add(Op::SoftmaxMasked, n->dtype, n->dims, in);
+  o->ia = {causal ? 1 : 0};
+  o->fa = {scale};
+  return ret(err, Status::OK(), o);
+}
+
+static Status norm_common(B200Context ctx, const char* what, B200Value x, const int* axes, int num_axes, Node** xn,
+                          std::vector<int64_t>* ax) {
+  B200_TRY(check_node(ctx, x, what, xn));
+  if (!dtype_is_float((*xn)->dtype)) return Status::Invalid(strfmt("%s: needs a float operand", what));
+  if (num_axes < 1) return Status::Invalid(strfmt("%s: no axes", what));
+  std::set<int64_t> seen;
+  for (int i = 0; i < num_axes; ++i) {
+    int a;
+    B200_TRY(normalize_axis(what, axes[i], (*xn)->rank(), &a));  // negative axes allowed (ref function.go:2417-2428)
+    if (!seen.insert(a).second) return Status::Invalid(strfmt("%s: axis named twice", what));
+  }
+  ax->assign(seen.begin(), seen.end());
+  return Status::OK();
+}
+
+// gamma / beta of lower rank are laid onto the normalised axes in order
+// (ref function.go:2499-2530); equal-rank ones broadcast as they are.
+static Status check_scale(const char* what, Node* x, Node* p, const std::vector<int64_t>& axes) {
+  if (p->dtype != x->dtype) return Status::Invalid(strfmt("%s: gamma/beta dtype differs from the operand", what));
+  if (p->rank() >= x->rank()) {
+    if (p->rank() > x->rank()) return Status::Invalid(strfmt("%s: gamma/beta rank exceeds operand rank", what));
+    for (int i = 0; i < x->rank(); ++i)
+      if (p->dims[i] != 1 && p->dims[i] != x->dims[i]) return Status::Invalid(strfmt("%s: gamma/beta does not broadcast", what));
+    return Status::OK();
+  }
+  if (p->rank() > (int)axes.size()) return Status::Invalid(strfmt("%s: gamma/beta rank exceeds the number of normalised axes", what));
+  for (int i = 0; i < p->rank(); ++i)
+    if (p->dims[i] != 1 && p->dims[i] != x->dims[axes[i]]) return Status::Invalid(strfmt("%s: gamma/beta does not match the normalised axes", what));
+  return Status::OK();
+}
+
+B200Value b200_layer_norm(B200Context ctx, B200Value x, const int* axes, int num_axes, double epsilon, B200Value gamma,
+                          B200Value beta, B200Error* err) {
+  clear_error(err);
+  Node *n, *g_ = nullptr, *b_ = nullptr;
+  std::vector<int64_t> ax;
+  Status s = norm_common(ctx, "FusedLayerNorm", x, axes, num_axes, &n, &ax);
+  if (s.ok() && gamma) s = check_node(ctx, gamma, "FusedLayerNorm: gamma", &g_);
+  if (s.ok() && beta) s = check_node(ctx, beta, "FusedLayerNorm: beta", &b_);
+  if (s.ok() && g_) s = check_scale("FusedLayerNorm", n, g_, ax);
+  if (s.ok() && b_) s = check_scale("FusedLayerNorm", n, b_, ax);
+  if (!s.ok()) return ret(err, s, nullptr);
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  // A full-rank gamma/beta that varies along a non-normalised axis cannot be a
+  // per-column vector: normalise first, then scale and shift as elementwise ops.
+  auto varies_off_axes = [&](Node* p) {
+    if (!p || p->rank() < n->rank()) return false;
+    for (int i = 0; i < n->rank(); ++i)
+      if (p->dims[i] != 1 && !std::count(ax.begin(), ax.end(), (int64_t)i)) return true;
+    return false;
+  };
+  const bool split = varies_off_axes(g_) || varies_off_axes(b_);
+  std::vector<Node*> in = {n};
+  // ia = [has_gamma, has_beta, axes...]
+  if (g_ && !split) in.push_back(g_);
+  if (b_ && !split) in.push_back(b_);
+  Node* o = g.Add(Op::LayerNorm, n->dtype, n->dims, in);
+  o->ia = {(g_ && !split) ? 1 : 0, (b_ && !split) ? 1 : 0};
+  o->ia.insert(o->ia.end(), ax.begin(), ax.end());
+  o->fa = {epsilon};
+  if (split) {
+    B200Value y = reinterpret_cast<B200Value>(o);
+    if (g_) { y = b200_mul(ctx, y, gamma, err); if (!y) return nullptr; }
+    if (b_) { y = b200_add(ctx, y, beta, err); if (!y) return nullptr; }
+    return y;
+  }
+  return ret(err, Status::OK(), o);
+}
+
+B200Value b200_rms_norm(B200Context ctx, B200Value x, const int* axes, int num_axes, double epsilon, B200Value gamma,
+                        B200Error* err) {
+  clear_error(err);
+  Node *n, *g_ = nullptr;
+  std::vector<int64_t> ax;
+  Status s = norm_common(ctx, "RMSNorm", x, axes, num_axes, &n, &ax);
+  if (s.ok() && gamma) s = check_node(ctx, gamma, "RMSNorm: gamma", &g_);
+  if (s.ok() && g_) s = check_scale("RMSNorm", n, g_, ax);
+  if (!s.ok()) return ret(err, s, nullptr);
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  std::vector<Node*> in = {n};
+  if (g_) in.push_back(g_);
+  Node* o = g.Add(Op::RmsNorm, n->dtype, n->dims, in);
+  o->ia = {g_ ? 1 : 0, 0};
+  o->ia.insert(o->ia.end(), ax.begin(), ax.end());
+  o->fa = {epsilon};
+  return ret(err, Status::OK(), o);
+}
+
+B200Value b200_gelu(B200Context ctx, B200Value x, int exact, B200Error* err) {
+  clear_error(err);
+  Node* n = nullptr;
+  Status s = unary_impl(ctx, exact ? Op::GeluExact : Op::GeluTanh, x, &n);
+  return ret(err, s, n);
+}
+
+B200Value b200_dense(B200Context ctx, B200Value x, B200Value weight, B200Value bias, int activation, B200Error* err) {
+  clear_error(err);
+  Node *xn, *wn, *bn = nullptr;
+  Status s = check_node(ctx, x, "FusedDense: x", &xn);
+  if (s.ok()) s = check_node(ctx, weight, "FusedDense: weight", &wn);
+  if (s.ok() && bias) s = check_node(ctx, bias, "FusedDense: bias", &bn);
+  if (!s.ok()) return ret(err, s, nullptr);
+  if (xn->rank() < 1 || wn->rank() < 2)
+    return ret(err, Status::Invalid(strfmt("FusedDense: x must have rank >= 1 (got %d), weight must have rank >= 2 (got %d)", xn->rank(), wn->rank())), nullptr);
+  if (xn->dims.back() != wn->dims[0])
+    return ret(err, Status::Invalid(strfmt("FusedDense: x's last dim (%lld) must match weight's first dim (%lld)", (long long)xn->dims.back(), (long long)wn->dims[0])), nullptr);
+  if (activation < B200_ACT_NONE || activation > B200_ACT_TANH)
+    return ret(err, Status::Invalid(strfmt("FusedDense: unsupported activation type %d", activation)), nullptr);
+  const int lc = xn->rank() - 1, rc = 0;
+  B200Value y = b200_dot_general(ctx, x, &lc, 1, nullptr, 0, weight, &rc, 1, nullptr, 0, err);
+  if (!y) return nullptr;
+  Node* yn = reinterpret_cast<Node*>(y);
+  const bool float_epilogue = yn->dtype == B200_FLOAT32 || yn->dtype == B200_BFLOAT16 || yn->dtype == B200_FLOAT16;
+  if (bn) {
+    if (bn->dtype != yn->dtype || bn->rank() > yn->rank()) return ret(err, Status::Invalid("FusedDense: bias dtype or rank"), nullptr);
+    // trailing-axis broadcast (ref function.go:2604-2612)
+    const int off = yn->rank() - bn->rank();
+    for (int i = 0; i < bn->rank(); ++i)
+      if (bn->dims[i] != yn->dims[off + i]) return ret(err, Status::Invalid("FusedDense: bias shape does not match the output's trailing dims"), nullptr);
+  }
+  // The GEMM epilogue takes a bias vector over the N axis and an activation.
+  const bool simple_bias = !bn || (bn->rank() == 1 && wn->rank() == 2);
+  if (float_epilogue && simple_bias) {
+    if (bn) yn->in.push_back(bn);
+    yn->fa[0] = (double)activation;
+    return y;
+  }
+  if (bn) {
+    std::vector<int> axes(bn->rank());
+    for (int i = 0; i < bn->rank(); ++i) axes[i] = yn->rank() - bn->rank() + i;
+    B200Value bb = b200_broadcast_in_dim(ctx, bias, yn->dims.data(), yn->rank(), axes.data(), bn->rank(), err);
+    if (!bb) return nullptr;
+    y = b200_add(ctx, y, bb, err);
+    if (!y) return nullptr;
+  }
+  Node* act = nullptr;
+  Status as = Status::OK();
+  switch (activation) {
+    case B200_ACT_GELU: as = unary_impl(ctx, Op::GeluTanh, y, &act); break;
+    case B200_ACT_RELU: as = unary_impl(ctx, Op::Relu, y, &act); break;
+    case B200_ACT_SILU: as = unary_impl(ctx, Op::Silu, y, &act); break;
+    case B200_ACT_TANH: as = unary_impl(ctx, Op::Tanh, y, &act); break;
+    default: return y;
+  }
+  return ret(err, as, act);
+}
+
+bool b200_attention_qkv_projection(B200Context ctx, B200Value x, B200Value w_qkv, B200Value bias_q, B200Value bias_k,
+                                   B200Value bias_v, int query_dim, int key_value_dim, B200Value* out_q, B200Value* out_k,
+                                   B200Value* out_v, B200Error* err) {
+  clear_error(err);
+  Node *xn, *wn;
+  Status s = check_node(ctx, x, "FusedAttentionQKVProjection: x", &xn);
+  if (s.ok()) s = check_node(ctx, w_qkv, "FusedAttentionQKVProjection: wQKV", &wn);
+  if (!s.ok()) { set_error(err, s); return false; }
+  if (xn->rank() < 1) { set_error(err, Status::Invalid("FusedAttentionQKVProjection: x must have rank >= 1")); return false; }
+  if (wn->rank() != 2 || wn->dims[1] != query_dim + 2 * (int64_t)key_value_dim) {
+    set_error(err, Status::Invalid("FusedAttentionQKVProjection: wQKV must be [in, queryDim + 2*keyValueDim]"));
+    return false;
+  }
+  const int lc = xn->rank() - 1, rc = 0;
+  B200Value combined = b200_dot_general(ctx, x, &lc, 1, nullptr, 0, w_qkv, &rc, 1, nullptr, 0, err);
+  if (!combined) return false;
+  Node* cn = reinterpret_cast<Node*>(combined);
+  const int r = cn->rank();
+  auto part = [&](int64_t lo, int64_t hi, B200Value bias, B200Value* out) -> bool {
+    std::vector<int64_t> st(r, 0), en(cn->dims), sd(r, 1);
+    st[r - 1] = lo;
+    en[r - 1] = hi;
+    B200Value v = b200_slice(ctx, combined, st.data(), en.data(), sd.data(), r, err);
+    if (!v) return false;
+    if (bias) {
+      Node* bn;
+      Status bs = check_node(ctx, bias, "FusedAttentionQKVProjection: bias", &bn);
+      if (!bs.ok()) { set_error(err, bs); return false; }
+      Node* vn = reinterpret_cast<Node*>(v);
+      std::vector<int> axes(bn->rank());
+      for (int i = 0; i < bn->rank(); ++i) axes[i] = r - bn->rank() + i;
+      B200Value bb = b200_broadcast_in_dim(ctx, bias, vn->dims.data(), r, axes.data(), bn->rank(), err);
+      if (!bb) return false;
+      v = b200_add(ctx, v, bb, err);
+      if (!v) return false;
+    }
+    *out = v;
+    return true;
+  };
+  return part(0, query_dim, bias_q, out_q) && part(query_dim, query_dim + key_value_dim, bias_k, out_k) &&
+         part(query_dim + key_value_dim, query_dim + 2 * (int64_t)key_value_dim, bias_v, out_v);
+}
+
+B200Value b200_scaled_dot_product_attention(B200Context ctx, B200Value query, B200Value key, B200Value value, B200Value mask,
+                                            int num_heads, int num_kv_heads, int axes_layout, double scale, int causal,
+                                            B200Error* err) {
+  clear_error(err);
+  Node *q, *k, *v, *m = nullptr;
+  Status s = check_node(ctx, query, "SDPA: query", &q);
+  if (s.ok()) s = check_node(ctx, key, "SDPA: key", &k);
+  if (s.ok()) s = check_node(ctx, value, "SDPA: value", &v);
+  if (s.ok() && mask) s = check_node(ctx, mask, "SDPA: mask", &m);
+  if (!s.ok()) return ret(err, s, nullptr);
+  if (q->rank() != 4) return ret(err, Status::Invalid(strfmt("SDPA: query must have rank 4, got %d", q->rank())), nullptr);
+  if (k->rank() != 4 || v->rank() != 4) return ret(err, Status::Invalid("SDPA: key and value must have rank 4"), nullptr);
+  if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
+    return ret(err, Status::Invalid(strfmt("SDPA: numHeads (%d) must be positive and divisible by numKVHeads (%d)", num_heads, num_kv_heads)), nullptr);
+  const bool bshd = axes_layout == B200_LAYOUT_BSHD;
+  // Work in BHSD like the reference (function.go:2697-2726).
+  const int perm[4] = {0, 2, 1, 3};
+  B200Value Q = query, K = key, V = value, M = mask;
+  if (bshd) {
+    Q = b200_transpose(ctx, Q, perm, 4, err); if (!Q) return nullptr;
+    K = b200_transpose(ctx, K, perm, 4, err); if (!K) return nullptr;
+    V = b200_transpose(ctx, V, perm, 4, err); if (!V) return nullptr;
+    if (m && m->rank() == 4) { M = b200_transpose(ctx, M, perm, 4, err); if (!M) return nullptr; }
+  }
+  Node* qn = reinterpret_cast<Node*>(Q);
+  Node* kn = reinterpret_cast<Node*>(K);
+  if (qn->dims[1] != num_heads || kn->dims[1] != num_kv_heads)
+    return ret(err, Status::Invalid("SDPA: head counts do not match the tensors"), nullptr);
+  // GQA: query head h reads KV head h / repeats (each KV head repeated `repeats`
+  // times consecutively, ref function.go:2910-2955).  Q is regrouped to
+  // [B, Hkv, repeats*Sq, D] so K and V are used as they are, never copied.
+  const int64_t B = qn->dims[0], H = num_heads, Hkv = num_kv_heads, Sq = qn->dims[2], D = qn->dims[3], Sk = kn->dims[2];
+  const int64_t rep = H / Hkv;
+  B200Value Qg = Q;
+  if (rep > 1) {
+    const int64_t g4[4] = {B, Hkv, rep * Sq, D};
+    Qg = b200_reshape(ctx, Q, g4, 4, err);
+    if (!Qg) return nullptr;
+  }
+  const int c3 = 3, bt[2] = {0, 1};
+  B200Value scores = b200_dot_general(ctx, Qg, &c3, 1, bt, 2, K, &c3, 1, bt, 2, err);  // [B, Hkv, rep*Sq, Sk]
+  if (!scores) return nullptr;
+  const int64_t s4[4] = {B, H, Sq, Sk};
+  if (rep > 1) { scores = b200_reshape(ctx, scores, s4, 4, err); if (!scores) return nullptr; }
+  B200Value probs = b200_softmax_masked(ctx, scores, scale, causal, M, err);
+  if (!probs) return nullptr;
+  if (rep > 1) {
+    const int64_t p4[4] = {B, Hkv, rep * Sq, Sk};
+    probs = b200_reshape(ctx, probs, p4, 4, err);
+    if (!probs) return nullptr;
+  }
+  const int c2 = 2;
+  B200Value out = b200_dot_general(ctx, probs, &c3, 1, bt, 2, V, &c2, 1, bt, 2, err);  // [B, Hkv, rep*Sq, D]
+  if (!out) return nullptr;
+  const int64_t o4[4] = {B, H, Sq, reinterpret_cast<Node*>(V)->dims[3]};
+  if (rep > 1) { out = b200_reshape(ctx, out, o4, 4, err); if (!out) return nullptr; }
+  if (bshd) out = b200_transpose(ctx, out, perm, 4, err);
+  return out;
+}
+
+B200Value b200_batch_norm_inference(B200Context ctx, B200Value input, B200Value mean, B200Value variance, B200Value gamma,
+                                    B200Value beta, float epsilon, int feature_axis, B200Error* err) {
+  clear_error(err);
+  Node* n;
+  Status s = check_node(ctx, input, "BatchNormForInference", &n);
+  if (!s.ok()) return ret(err, s, nullptr);
+  int a;
+  s = normalize_axis("BatchNormForInference", feature_axis, n->rank(), &a);
+  if (!s.ok()) return ret(err, s, nullptr);
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  auto bc = [&](B200Value p) -> B200Value { return b200_broadcast_in_dim(ctx, p, n->dims.data(), n->rank(), &a, 1, err); };
+  B200Value m = bc(mean); if (!m) return nullptr;
+  B200Value var = bc(variance); if (!var) return nullptr;
+  B200Value eps = reinterpret_cast<B200Value>(make_scalar_const(g, n->dtype, epsilon));
+  B200Value d = b200_sub(ctx, input, m, err); if (!d) return nullptr;
+  B200Value ve = b200_add(ctx, var, eps, err); if (!ve) return nullptr;
+  B200Value r = b200_rsqrt(ctx, ve, err); if (!r) return nullptr;
+  B200Value y = b200_mul(ctx, d, r, err); if (!y) return nullptr;
+  if (gamma) { B200Value gg = bc(gamma); if (!gg) return nullptr; y = b200_mul(ctx, y, gg, err); if (!y) return nullptr; }
+  if (beta) { B200Value bb = bc(beta); if (!bb) return nullptr; y = b200_add(ctx, y, bb, err); if (!y) return nullptr; }
+  return y;
+}
+
+}  // extern "C"

@@ -1,0 +1,159 @@
+// Launchers of the sm_100a kernels.  Each takes raw device pointers, enqueues on
+// the Device's stream and returns a Status; none allocates or synchronises.
+#pragma once
+
+#include "common.h"
+
+namespace b200 {
+namespace k {
+
+constexpr int kMaxDims = 8;
+
+// ------------------------------------------------------------- softmax -----
+struct SoftmaxParams {
+  const void* x = nullptr;
+  void* y = nullptr;
+  int64_t rows = 0, cols = 0;
+  int dtype = B200_FLOAT32;
+  double scale = 1.0;
+  bool causal = false;
+  int64_t seq_q = 0;  // rows = batch * heads * seq_q; 0 means rows
+  int64_t heads = 1;
+  const void* mask = nullptr;
+  int mask_kind = 0;                          // 1 bool, 2 float (dtype of x)
+  int64_t mask_strides[4] = {0, 0, 0, 0};     // batch, head, q, k (elements)
+};
+Status softmax_rows(Device* dev, const SoftmaxParams& p);
+Status softmax_strided(Device* dev, const void* x, void* y, int64_t outer, int64_t n, int64_t inner, int dtype);
+
+// ---------------------------------------------------------------- norms ----
+struct NormParams {
+  const void* x = nullptr;
+  const void* gamma = nullptr;  // [cols] of x's dtype, or null
+  const void* beta = nullptr;   // [cols] of x's dtype, or null (LayerNorm only)
+  void* y = nullptr;
+  int64_t rows = 0, cols = 0;
+  int dtype = B200_FLOAT32;
+  double epsilon = 1e-5;
+  bool rms = false;
+};
+Status norm_rows(Device* dev, const NormParams& p);
+
+// ---------------------------------------------- fused elementwise chains ---
+// A straight-line program over virtual registers, evaluated per output element
+// by one interpreter kernel.  Leaves are loads from dense tensors addressed
+// through broadcast strides of the OUTPUT index space, iotas, or immediates.
+constexpr int kEwMaxInstr = 48;
+constexpr int kEwMaxLeaves = 8;
+constexpr int kEwMaxRegs = 24;
+
+enum EwKind : uint8_t { EW_LOAD = 0, EW_IMM = 1, EW_IOTA = 2, EW_OP = 3, EW_CAST = 4 };
+
+struct EwInstr {
+  uint8_t kind;   // EwKind
+  uint8_t op;     // b200::Op value for EW_OP
+  uint8_t dtype;  // dtype of the RESULT (for EW_OP: compares produce Bool but compute in src dtype, see sdtype)
+  uint8_t sdtype; // dtype of the operands (EW_OP, EW_CAST)
+  uint8_t dst, a, b, c;  // register numbers; for EW_LOAD a = leaf index; for EW_IOTA a = output dim
+  uint64_t imm;   // EW_IMM: raw bits of the value already in register representation
+};
+
+struct EwLeaf {
+  const void* ptr;
+  int64_t strides[kMaxDims];  // per OUTPUT dim, in elements; 0 = broadcast
+  int dtype;
+};
+
+struct EwProgram {
+  int num_instr = 0;
+  int num_leaves = 0;
+  int num_regs = 0;
+  int rank = 0;                 // collapsed output rank (<= kMaxDims)
+  int64_t dims[kMaxDims] = {0};  // output dims
+  EwInstr instr[kEwMaxInstr];
+  EwLeaf leaves[kEwMaxLeaves];
+  int out_reg = 0;
+  int out_dtype = B200_FLOAT32;
+  void* out = nullptr;
+  bool wide = false;  // needs 64-bit registers (any I64/U64/F64 value)
+};
+Status ewise_run(Device* dev, const EwProgram& prog);
+
+// ---------------------------------------------------------- data movement --
+// y[idx] = x[offset + sum_d idx_d * strides_d] over a dense row-major output.
+// Covers Transpose, Slice, Reverse, BroadcastInDim (stride 0) and
+// Concatenate / Pad (through out_offset and out_strides).
+struct StridedCopyParams {
+  const void* x = nullptr;
+  void* y = nullptr;
+  int elt_size = 4;
+  int rank = 0;
+  int64_t dims[kMaxDims] = {0};
+  int64_t in_strides[kMaxDims] = {0};   // elements, may be 0 or negative
+  int64_t in_offset = 0;                // elements
+  int64_t out_strides[kMaxDims] = {0};  // elements
+  int64_t out_offset = 0;
+};
+Status strided_copy(Device* dev, const StridedCopyParams& p);
+// Batched 2-D transpose through shared memory: x[batch, rows, cols] -> y[batch, cols, rows].
+Status transpose_2d(Device* dev, const void* x, void* y, int64_t batch, int64_t rows, int64_t cols, int elt_size);
+Status fill(Device* dev, void* y, int64_t n, int elt_size, uint64_t pattern);
+Status iota(Device* dev, void* y, int dtype, int64_t outer, int64_t n, int64_t inner);
+Status cast(Device* dev, const void* x, int src_dtype, void* y, int dst_dtype, int64_t n);
+
+// ------------------------------------------------------------ reductions ---
+// x viewed as [outer, n, inner] -> y[outer, inner].  Floats accumulate in fp32
+// (f64 in f64), integers in their own width.
+Status reduce(Device* dev, const void* x, void* y, int dtype, int reduce_type, int64_t outer, int64_t n,
+              int64_t inner, void* scratch, int64_t scratch_bytes);
+int64_t reduce_scratch_bytes(int dtype, int64_t outer, int64_t n, int64_t inner);
+Status arg_min_max(Device* dev, const void* x, void* y, int dtype, int out_dtype, bool is_min, int64_t outer,
+                   int64_t n, int64_t inner);
+
+// ---------------------------------------------------------------- gather ---
+// Row gather (embedding lookup): y[i, :] = table[clamp(ids[i]), :], rows of row_bytes bytes.
+Status gather_rows(Device* dev, const void* table, const void* ids, int ids_dtype, void* y, int64_t num_ids,
+                   int64_t num_rows, int64_t row_bytes);
+// General XLA gather, one thread per output element.
+struct GatherParams {
+  const void* operand = nullptr;
+  const void* indices = nullptr;
+  void* y = nullptr;
+  int elt_size = 4;
+  int ids_dtype = B200_INT32;
+  int out_rank = 0;
+  int64_t out_dims[kMaxDims] = {0};
+  int operand_rank = 0;
+  int64_t operand_dims[kMaxDims] = {0};
+  int64_t operand_strides[kMaxDims] = {0};
+  int64_t slice_sizes[kMaxDims] = {0};
+  // For every output dim: if it is an offset dim, offset_operand_axis >= 0 names the operand axis it walks;
+  // else batch_pos names which batch (index) coordinate it is.
+  int out_offset_operand_axis[kMaxDims];
+  int out_batch_pos[kMaxDims];
+  int num_batch_dims = 0;
+  int64_t batch_index_strides[kMaxDims] = {0};  // strides of the indices tensor for each batch coordinate
+  int64_t index_vector_stride = 0;              // stride along index_vector_axis
+  int num_index_components = 0;
+  int start_index_map[kMaxDims];
+};
+Status gather_general(Device* dev, const GatherParams& p);
+
+// ------------------------------------------------------------------ GEMM ---
+struct GemmParams {
+  const void* a = nullptr;
+  const void* b = nullptr;
+  void* c = nullptr;
+  int64_t batch = 1, m = 0, n = 0, k = 0;
+  bool a_k_major = true;   // A is [batch, M, K] (true) or [batch, K, M]
+  bool b_k_major = false;  // B is [batch, N, K] (true) or [batch, K, N]
+  int dtype = B200_BFLOAT16;
+  const void* bias = nullptr;  // [N] of dtype, or null
+  int activation = B200_ACT_NONE;
+  // batch strides in elements; 0 on an operand broadcasts it over the batch
+  int64_t a_batch_stride = -1, b_batch_stride = -1;  // -1 = dense (m*k, k*n)
+};
+Status gemm(Device* dev, const GemmParams& p);
+
+}  // namespace k
+}  // namespace b200

@@ -1,0 +1,240 @@
+// Data-movement kernels: strided copy (Transpose / Slice / Reverse /
+// BroadcastInDim / Concatenate / Pad), tiled 2-D transpose, fill, iota, cast.
+//
+// The reference realises a permutation as a chain of pairwise axis swaps, each
+// a full pass over the tensor (mpsgraph bridge.m:425-465).  Here any
+// permutation, slice, reversal or broadcast is ONE pass: the output is walked
+// densely and the input address is computed from strides.  All HBM-bound:
+// bytes = input bytes touched + output bytes.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "../kernels.h"
+
+namespace b200 {
+namespace k {
+
+namespace {
+
+struct ScArgs {
+  const void* x;
+  void* y;
+  int rank;
+  int64_t dims[kMaxDims];
+  int64_t in_strides[kMaxDims];
+  int64_t out_strides[kMaxDims];
+  int64_t in_offset, out_offset;
+  int64_t total;
+};
+
+// One thread per output element; T is an unsigned integer of the element size.
+template <typename T>
+__global__ void __launch_bounds__(256) strided_copy_kernel(const __grid_constant__ ScArgs a) {
+  const T* x = reinterpret_cast<const T*>(a.x);
+  T* y = reinterpret_cast<T*>(a.y);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.total; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t rem = i, in = a.in_offset, out = a.out_offset;
+    for (int d = a.rank - 1; d >= 0; --d) {
+      const int64_t c = rem % a.dims[d];
+      rem /= a.dims[d];
+      in += c * a.in_strides[d];
+      out += c * a.out_strides[d];
+    }
+    y[out] = x[in];
+  }
+}
+
+// Same walk, but the innermost dim is contiguous on both sides and a multiple
+// of VEC elements: moves 16 bytes per thread.
+template <int ELT>
+__global__ void __launch_bounds__(256) strided_copy_vec_kernel(const __grid_constant__ ScArgs a) {
+  constexpr int VEC = 16 / ELT;
+  const char* x = reinterpret_cast<const char*>(a.x);
+  char* y = reinterpret_cast<char*>(a.y);
+  const int64_t inner_vecs = a.dims[a.rank - 1] / VEC;
+  const int64_t total_vecs = a.total / VEC;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_vecs; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t rem = i / inner_vecs;
+    const int64_t cv = i % inner_vecs;
+    int64_t in = a.in_offset + cv * VEC, out = a.out_offset + cv * VEC;
+    for (int d = a.rank - 2; d >= 0; --d) {
+      const int64_t c = rem % a.dims[d];
+      rem /= a.dims[d];
+      in += c * a.in_strides[d];
+      out += c * a.out_strides[d];
+    }
+    *reinterpret_cast<uint4*>(y + out * ELT) = *reinterpret_cast<const uint4*>(x + in * ELT);
+  }
+}
+
+// x[batch, rows, cols] -> y[batch, cols, rows] through a padded 32x32 tile.
+template <typename T>
+__global__ void __launch_bounds__(256) transpose_2d_kernel(const T* x, T* y, int64_t rows, int64_t cols) {
+  __shared__ T tile[32][33];
+  const int64_t b = blockIdx.z;
+  const T* xb = x + b * rows * cols;
+  T* yb = y + b * rows * cols;
+  const int64_t c0 = (int64_t)blockIdx.x * 32, r0 = (int64_t)blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+#pragma unroll
+  for (int i = 0; i < 32; i += 8) {
+    const int64_t r = r0 + ty + i, c = c0 + tx;
+    if (r < rows && c < cols) tile[ty + i][tx] = xb[r * cols + c];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 32; i += 8) {
+    const int64_t c = c0 + ty + i, r = r0 + tx;
+    if (r < rows && c < cols) yb[c * rows + r] = tile[tx][ty + i];
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) fill_kernel(T* y, int64_t n, T v) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) y[i] = v;
+}
+
+template <typename T> __device__ __forceinline__ T from_index(int64_t i) { return (T)i; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_index<__nv_bfloat16>(int64_t i) { return __float2bfloat16_rn((float)i); }
+template <> __device__ __forceinline__ __half from_index<__half>(int64_t i) { return __float2half_rn((float)i); }
+
+template <typename T>
+__global__ void __launch_bounds__(256) iota_kernel(T* y, int64_t total, int64_t n, int64_t inner) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x)
+    y[i] = from_index<T>((i / inner) % n);
+}
+
+unsigned grid_for(Device* dev, int64_t work_items) {
+  const int64_t blocks = (work_items + 255) / 256;
+  const int64_t cap = (int64_t)dev->sm_count() * 32;
+  return (unsigned)(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+}
+
+}  // namespace
+
+Status strided_copy(Device* dev, const StridedCopyParams& p) {
+  ScArgs a;
+  a.x = p.x; a.y = p.y; a.in_offset = p.in_offset; a.out_offset = p.out_offset;
+  // Collapse neighbouring dims that are contiguous on both sides; drop size-1 dims.
+  int r = 0;
+  int64_t total = 1;
+  for (int d = 0; d < p.rank; ++d) {
+    total *= p.dims[d];
+    if (p.dims[d] == 1) continue;
+    if (r > 0 && a.in_strides[r - 1] == p.in_strides[d] * p.dims[d] && a.out_strides[r - 1] == p.out_strides[d] * p.dims[d]) {
+      a.dims[r - 1] *= p.dims[d];
+      a.in_strides[r - 1] = p.in_strides[d];
+      a.out_strides[r - 1] = p.out_strides[d];
+    } else {
+      a.dims[r] = p.dims[d];
+      a.in_strides[r] = p.in_strides[d];
+      a.out_strides[r] = p.out_strides[d];
+      ++r;
+    }
+  }
+  if (total == 0) return Status::OK();
+  if (r == 0) { a.dims[0] = 1; a.in_strides[0] = 1; a.out_strides[0] = 1; r = 1; }
+  a.rank = r;
+  a.total = total;
+  B200_TRY(dev->MakeCurrent());
+  cudaStream_t s = dev->stream();
+  const int es = p.elt_size;
+  const int vec = 16 / es;
+  bool vec_ok = a.in_strides[r - 1] == 1 && a.out_strides[r - 1] == 1 && a.dims[r - 1] % vec == 0 &&
+                (a.in_offset % vec) == 0 && (a.out_offset % vec) == 0 &&
+                (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.y) & 15) == 0;
+  for (int d = 0; d + 1 < r && vec_ok; ++d) vec_ok = (a.in_strides[d] % vec == 0) && (a.out_strides[d] % vec == 0);
+  if (vec_ok) {
+    const unsigned grid = grid_for(dev, total / vec);
+    switch (es) {
+      case 1: strided_copy_vec_kernel<1><<<grid, 256, 0, s>>>(a); break;
+      case 2: strided_copy_vec_kernel<2><<<grid, 256, 0, s>>>(a); break;
+      case 4: strided_copy_vec_kernel<4><<<grid, 256, 0, s>>>(a); break;
+      case 8: strided_copy_vec_kernel<8><<<grid, 256, 0, s>>>(a); break;
+      default: return Status::Invalid("strided_copy: element size");
+    }
+  } else {
+    const unsigned grid = grid_for(dev, total);
+    switch (es) {
+      case 1: strided_copy_kernel<uint8_t><<<grid, 256, 0, s>>>(a); break;
+      case 2: strided_copy_kernel<uint16_t><<<grid, 256, 0, s>>>(a); break;
+      case 4: strided_copy_kernel<uint32_t><<<grid, 256, 0, s>>>(a); break;
+      case 8: strided_copy_kernel<uint64_t><<<grid, 256, 0, s>>>(a); break;
+      default: return Status::Invalid("strided_copy: element size");
+    }
+  }
+  return dev->CheckLaunch("strided_copy");
+}
+
+Status transpose_2d(Device* dev, const void* x, void* y, int64_t batch, int64_t rows, int64_t cols, int elt_size) {
+  if (batch * rows * cols == 0) return Status::OK();
+  if (batch > 65535 || (rows + 31) / 32 > 65535) return Status::Unsupported("transpose_2d: grid too large");
+  B200_TRY(dev->MakeCurrent());
+  dim3 grid((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32), (unsigned)batch);
+  cudaStream_t s = dev->stream();
+  switch (elt_size) {
+    case 1: transpose_2d_kernel<uint8_t><<<grid, 256, 0, s>>>((const uint8_t*)x, (uint8_t*)y, rows, cols); break;
+    case 2: transpose_2d_kernel<uint16_t><<<grid, 256, 0, s>>>((const uint16_t*)x, (uint16_t*)y, rows, cols); break;
+    case 4: transpose_2d_kernel<uint32_t><<<grid, 256, 0, s>>>((const uint32_t*)x, (uint32_t*)y, rows, cols); break;
+    case 8: transpose_2d_kernel<uint64_t><<<grid, 256, 0, s>>>((const uint64_t*)x, (uint64_t*)y, rows, cols); break;
+    default: return Status::Invalid("transpose_2d: element size");
+  }
+  return dev->CheckLaunch("transpose_2d");
+}
+
+Status fill(Device* dev, void* y, int64_t n, int elt_size, uint64_t pattern) {
+  if (n == 0) return Status::OK();
+  B200_TRY(dev->MakeCurrent());
+  const unsigned grid = grid_for(dev, n);
+  cudaStream_t s = dev->stream();
+  switch (elt_size) {
+    case 1: fill_kernel<uint8_t><<<grid, 256, 0, s>>>((uint8_t*)y, n, (uint8_t)pattern); break;
+    case 2: fill_kernel<uint16_t><<<grid, 256, 0, s>>>((uint16_t*)y, n, (uint16_t)pattern); break;
+    case 4: fill_kernel<uint32_t><<<grid, 256, 0, s>>>((uint32_t*)y, n, (uint32_t)pattern); break;
+    case 8: fill_kernel<uint64_t><<<grid, 256, 0, s>>>((uint64_t*)y, n, pattern); break;
+    default: return Status::Invalid("fill: element size");
+  }
+  return dev->CheckLaunch("fill");
+}
+
+Status iota(Device* dev, void* y, int dtype, int64_t outer, int64_t n, int64_t inner) {
+  const int64_t total = outer * n * inner;
+  if (total == 0) return Status::OK();
+  B200_TRY(dev->MakeCurrent());
+  const unsigned grid = grid_for(dev, total);
+  cudaStream_t s = dev->stream();
+#define IOTA_CASE(DT, T) case DT: iota_kernel<T><<<grid, 256, 0, s>>>((T*)y, total, n, inner); break;
+  switch (dtype) {
+    IOTA_CASE(B200_INT8, int8_t) IOTA_CASE(B200_INT16, int16_t) IOTA_CASE(B200_INT32, int32_t)
+    IOTA_CASE(B200_INT64, int64_t) IOTA_CASE(B200_UINT8, uint8_t) IOTA_CASE(B200_UINT16, uint16_t)
+    IOTA_CASE(B200_UINT32, uint32_t) IOTA_CASE(B200_UINT64, uint64_t) IOTA_CASE(B200_FLOAT32, float)
+    IOTA_CASE(B200_FLOAT64, double) IOTA_CASE(B200_BFLOAT16, __nv_bfloat16) IOTA_CASE(B200_FLOAT16, __half)
+    default: return Status::Unsupported(strfmt("iota: dtype %s", dtype_name(dtype)));
+  }
+#undef IOTA_CASE
+  return dev->CheckLaunch("iota");
+}
+
+Status cast(Device* dev, const void* x, int src_dtype, void* y, int dst_dtype, int64_t n) {
+  // A cast is a one-instruction elementwise program.
+  EwProgram p;
+  p.rank = 1;
+  p.dims[0] = n;
+  p.num_leaves = 1;
+  p.leaves[0].ptr = x;
+  p.leaves[0].dtype = src_dtype;
+  for (int d = 0; d < kMaxDims; ++d) p.leaves[0].strides[d] = 0;
+  p.leaves[0].strides[0] = 1;
+  p.num_instr = 2;
+  p.instr[0] = EwInstr{EW_LOAD, 0, (uint8_t)src_dtype, (uint8_t)src_dtype, 0, 0, 0, 0, 0};
+  p.instr[1] = EwInstr{EW_CAST, 0, (uint8_t)dst_dtype, (uint8_t)src_dtype, 1, 0, 0, 0, 0};
+  p.num_regs = 2;
+  p.out_reg = 1;
+  p.out_dtype = dst_dtype;
+  p.out = y;
+  p.wide = dtype_size(src_dtype) == 8 || dtype_size(dst_dtype) == 8;
+  return ewise_run(dev, p);
+}
+
+}  // namespace k
+}  // namespace b200

@@ -1,0 +1,1445 @@
+// The lowering pass: graph -> launch plan, and the executor that replays it.
+//
+// Counterpart in the reference: Builder.Compile / compileSimple (mpsgraph
+// builder.go:72-109) hands the graph to MPSGraph's compiler, and
+// Executable.Execute (executable.go:50-112) copies every input in, waits, and
+// copies every output out.  Here compile() walks the graph once and emits a
+// list of kernel launches with a static memory plan; execute() only binds
+// pointers and enqueues.
+//
+// What the pass does:
+//   * dead-code elimination from the targets;
+//   * Reshape / Identity become views (no launch);
+//   * chains of elementwise ops, broadcasts, transposes, slices, reversals,
+//     iotas and scalar constants are fused into ONE interpreter program per
+//     materialised result (kernels/ewise.cu);
+//   * DotGeneral picks the operand-major form the GEMM reads in place, so no
+//     transpose is materialised for the [B,M,K]x[B,K,N], [B,K,M]x[B,K,N],
+//     QK^T and PV forms; bias and activation ride in the GEMM epilogue;
+//   * Softmax / SoftmaxMasked / LayerNorm / RMSNorm / Reduce / ArgMinMax /
+//     Gather go to their dedicated kernels;
+//   * intermediates get offsets in one arena by a liveness scan (a value's
+//     bytes are reused after its last reader), outputs are fresh allocations.
+#include <algorithm>
+#include <array>
+#include <cmath>
+#include <functional>
+#include <sstream>
+#include <unordered_map>
+
+#include "common.h"
+#include "kernels.h"
+
+namespace b200 {
+
+namespace k {
+Status gemm_simt(Device* dev, const GemmParams& p);
+}
+
+namespace {
+
+enum class SlotKind { Input, Const, Arena, Output, Scratch };
+
+struct Slot {
+  SlotKind kind = SlotKind::Arena;
+  int index = 0;        // input / output ordinal, or constant ordinal
+  int64_t nbytes = 0;
+  int64_t offset = 0;   // arena offset (Arena / Scratch)
+  int first_step = -1, last_step = -1;
+};
+
+struct Step {
+  std::string desc;
+  std::vector<int> reads, writes;
+  int launches = 1;
+  std::function<Status(Device*, void* const*)> run;  // ptrs indexed by slot
+};
+
+struct OutputDesc {
+  int slot;
+  int dtype;
+  std::vector<int64_t> dims;
+  int64_t nbytes;
+};
+
+struct Exec {
+  Device* dev = nullptr;
+  std::vector<Slot> slots;
+  std::vector<Step> steps;
+  std::vector<OutputDesc> inputs;   // slot = the input's slot
+  std::vector<OutputDesc> outputs;
+  std::vector<void*> const_ptrs;
+  void* arena = nullptr;
+  int64_t arena_bytes = 0;
+  int num_launches = 0;
+  std::mutex mu;
+  ~Exec() {
+    if (dev) {
+      for (void* p : const_ptrs) dev->Free(p);
+      dev->Free(arena);
+    }
+  }
+};
+
+int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+std::vector<int64_t> dense_strides(const std::vector<int64_t>& dims) {
+  std::vector<int64_t> s(dims.size());
+  int64_t acc = 1;
+  for (int i = (int)dims.size() - 1; i >= 0; --i) {
+    s[i] = acc;
+    acc *= dims[i];
+  }
+  return s;
+}
+
+// Per-dimension affine map from a node's index space into the index space of
+// the fused kernel's output: node_idx[i] = a[i] * out_idx[m[i]] + b[i]
+// (m[i] == -1: the coordinate is the constant b[i]).
+struct IndexMap {
+  std::vector<int> m;
+  std::vector<int64_t> a, b;
+  std::string key() const {
+    std::string s;
+    for (size_t i = 0; i < m.size(); ++i) s += std::to_string(m[i]) + ":" + std::to_string(a[i]) + ":" + std::to_string(b[i]) + ",";
+    return s;
+  }
+  static IndexMap Identity(int rank) {
+    IndexMap im;
+    for (int i = 0; i < rank; ++i) { im.m.push_back(i); im.a.push_back(1); im.b.push_back(0); }
+    return im;
+  }
+};
+
+class Planner {
+ public:
+  Planner(Ctx* ctx, Exec* exec) : ctx_(ctx), ex_(exec), g_(ctx->graph) {}
+
+  Status Run(const std::vector<Node*>& feeds, const std::vector<Node*>& targets) {
+    const int n = (int)g_.nodes.size();
+    live_.assign(n, false);
+    uses_.assign(n, 0);
+    slot_of_.assign(n, -1);
+    // liveness + use counts
+    std::vector<Node*> stack(targets.begin(), targets.end());
+    while (!stack.empty()) {
+      Node* x = stack.back();
+      stack.pop_back();
+      if (live_[x->id]) continue;
+      live_[x->id] = true;
+      for (Node* i : x->in) stack.push_back(i);
+    }
+    for (int i = 0; i < n; ++i)
+      if (live_[i])
+        for (Node* in : g_.nodes[i]->in) uses_[in->id]++;
+    for (Node* t : targets) uses_[t->id]++;
+    // inputs
+    for (size_t i = 0; i < feeds.size(); ++i) {
+      Node* f = feeds[i];
+      if (f->op != Op::Parameter) return Status::Invalid("compile: feed is not a placeholder");
+      if (slot_of_[f->id] >= 0) return Status::Invalid("compile: placeholder listed twice");
+      const int s = NewSlot(SlotKind::Input, (int)i, f->num_elements() * dtype_size(f->dtype));
+      slot_of_[f->id] = s;
+      ex_->inputs.push_back(OutputDesc{s, f->dtype, f->dims, ex_->slots[s].nbytes});
+    }
+    for (int i = 0; i < n; ++i)
+      if (live_[i] && g_.nodes[i]->op == Op::Parameter && slot_of_[i] < 0)
+        return Status::Invalid("compile: a placeholder used by the targets is not among the feeds");
+    // Which node's storage becomes which output: the first target whose base
+    // (through views) is a computed node claims that node's slot.
+    target_of_base_.clear();
+    std::vector<int> target_base(targets.size(), -1);
+    for (size_t t = 0; t < targets.size(); ++t) {
+      Node* b = ViewBase(targets[t]);
+      if (b->op != Op::Parameter && !(b->op == Op::Constant) && !target_of_base_.count(b->id)) {
+        target_of_base_[b->id] = (int)t;
+        target_base[t] = b->id;
+      }
+    }
+    // Emit in creation order (operands always precede users), materialising
+    // what must exist in memory; fused producers are pulled in on demand.
+    for (int i = 0; i < n; ++i) {
+      if (!live_[i]) continue;
+      Node* x = g_.nodes[i].get();
+      if (MustMaterialize(x)) B200_TRY(EnsureMaterialized(x));
+    }
+    // Outputs.
+    for (size_t t = 0; t < targets.size(); ++t) {
+      Node* x = targets[t];
+      B200_TRY(EnsureMaterialized(x));
+      int s = slot_of_[ViewBase(x)->id];
+      const int64_t nbytes = x->num_elements() * dtype_size(x->dtype);
+      if (target_base[t] < 0) {
+        // target is (a view of) an input, a constant, or storage another output owns: copy
+        const int o = NewSlot(SlotKind::Output, (int)t, nbytes);
+        const int src = s;
+        Step st;
+        st.desc = "copy -> output " + std::to_string(t);
+        st.reads = {src};
+        st.writes = {o};
+        st.run = [src, o, nbytes](Device* dev, void* const* p) -> Status {
+          if (nbytes == 0) return Status::OK();
+          B200_CUDA_TRY(cudaMemcpyAsync(p[o], p[src], (size_t)nbytes, cudaMemcpyDeviceToDevice, dev->stream()));
+          return Status::OK();
+        };
+        st.launches = 0;
+        ex_->steps.push_back(std::move(st));
+        s = o;
+      }
+      ex_->outputs.push_back(OutputDesc{s, x->dtype, x->dims, nbytes});
+    }
+    PlanArena();
+    ex_->num_launches = 0;
+    for (auto& st : ex_->steps) ex_->num_launches += st.launches;
+    return Status::OK();
+  }
+
+ private:
+  Ctx* ctx_;
+  Exec* ex_;
+  Graph& g_;
+  std::vector<bool> live_;
+  std::vector<int> uses_;
+  std::vector<int> slot_of_;  // node id -> slot (materialised nodes; views resolve through ViewBase)
+  std::unordered_map<int, int> target_of_base_;
+
+  int NewSlot(SlotKind kind, int index, int64_t nbytes) {
+    Slot s;
+    s.kind = kind;
+    s.index = index;
+    s.nbytes = nbytes;
+    ex_->slots.push_back(s);
+    return (int)ex_->slots.size() - 1;
+  }
+  int NewValueSlot(Node* x) {
+    const int64_t nbytes = x->num_elements() * dtype_size(x->dtype);
+    auto it = target_of_base_.find(x->id);
+    const int s = (it != target_of_base_.end()) ? NewSlot(SlotKind::Output, it->second, nbytes) : NewSlot(SlotKind::Arena, 0, nbytes);
+    slot_of_[x->id] = s;
+    return s;
+  }
+  int NewTemp(int64_t nbytes) { return NewSlot(SlotKind::Arena, 0, nbytes); }
+
+  static bool IsView(Node* x) { return x->op == Op::Reshape || x->op == Op::Identity; }
+  static Node* ViewBase(Node* x) {
+    while (IsView(x)) x = x->in[0];
+    return x;
+  }
+  static bool IsScalarConst(Node* x) { return x->op == Op::Constant && x->num_elements() == 1; }
+  // A Reshape whose non-1 dims are the operand's non-1 dims in the same order.
+  static bool UnitReshape(Node* x) {
+    if (x->op != Op::Reshape) return false;
+    std::vector<int64_t> a, b;
+    for (auto d : x->dims) if (d != 1) a.push_back(d);
+    for (auto d : x->in[0]->dims) if (d != 1) b.push_back(d);
+    return a == b;
+  }
+  // Ops that can be evaluated inside an elementwise program.
+  static bool Fusible(Node* x) {
+    if (op_is_elementwise(x->op)) return true;
+    switch (x->op) {
+      case Op::BroadcastInDim: case Op::Transpose: case Op::Slice: case Op::Reverse: case Op::Iota: return true;
+      case Op::Constant: return IsScalarConst(x);
+      default: return false;
+    }
+  }
+  // Cheap enough to recompute in every consumer instead of storing.
+  bool Cheap(Node* x) const {
+    if (x->op == Op::Iota || IsScalarConst(x)) return true;
+    if ((x->op == Op::BroadcastInDim || x->op == Op::Cast || IsView(x)) && Cheap(x->in[0])) return true;
+    return false;
+  }
+  bool MustMaterialize(Node* x) const {
+    if (x->op == Op::Parameter) return false;       // already in memory
+    if (IsView(x)) return false;                    // resolved through its base
+    if (IsScalarConst(x)) return false;             // becomes an immediate (materialised on demand if a kernel needs memory)
+    if (!Fusible(x)) return true;
+    if (target_of_base_.count(x->id)) return true;
+    if (uses_[x->id] > 1 && !Cheap(x)) return true;
+    return false;                                   // inlined into its consumer, or pulled in on demand
+  }
+
+  Status EnsureMaterialized(Node* x) {
+    Node* b = ViewBase(x);
+    if (slot_of_[b->id] >= 0) return Status::OK();
+    return Materialize(b);
+  }
+  int SlotOf(Node* x) const { return slot_of_[ViewBase(x)->id]; }
+
+  // ------------------------------------------------------------ dispatch ---
+  Status Materialize(Node* x) {
+    switch (x->op) {
+      case Op::Parameter: return Status::Invalid("compile: unbound placeholder");
+      case Op::Constant: return EmitConstant(x);
+      case Op::DotGeneral: return EmitDotGeneral(x);
+      case Op::Reduce: return EmitReduce(x);
+      case Op::ArgMinMax: return EmitArgMinMax(x);
+      case Op::Gather: return EmitGather(x);
+      case Op::Softmax: return EmitSoftmax(x);
+      case Op::SoftmaxMasked: return EmitSoftmaxMasked(x);
+      case Op::LayerNorm: case Op::RmsNorm: return EmitNorm(x);
+      case Op::Concatenate: return EmitConcatenate(x);
+      case Op::Pad: return EmitPad(x);
+      case Op::Transpose: case Op::Slice: case Op::Reverse: case Op::BroadcastInDim:
+        if (ViewBase(x->in[0])->op == Op::Parameter || slot_of_[ViewBase(x->in[0])->id] >= 0 || !Fusible(ViewBase(x->in[0])) ||
+            IsView(x->in[0]))
+          return EmitMovement(x);
+        return EmitEwise(x);
+      default:
+        if (Fusible(x)) return EmitEwise(x);
+        return Status::Unsupported(strfmt("compile: no lowering for %s", op_name(x->op)));
+    }
+  }
+
+  Status EmitConstant(Node* x) {
+    void* p = nullptr;
+    const int64_t nbytes = (int64_t)x->data.size();
+    B200_TRY(ex_->dev->Alloc(nbytes > 0 ? nbytes : 1, &p));
+    if (nbytes > 0) {
+      B200_TRY(ex_->dev->MakeCurrent());
+      B200_CUDA_TRY(cudaMemcpyAsync(p, x->data.data(), (size_t)nbytes, cudaMemcpyHostToDevice, ex_->dev->stream()));
+      B200_CUDA_TRY(cudaStreamSynchronize(ex_->dev->stream()));
+    }
+    ex_->const_ptrs.push_back(p);
+    slot_of_[x->id] = NewSlot(SlotKind::Const, (int)ex_->const_ptrs.size() - 1, nbytes);
+    return Status::OK();
+  }
+
+  // ------------------------------------------------- elementwise programs ---
+  struct EwBuild {
+    k::EwProgram prog;
+    std::vector<int> leaf_slots;
+    std::unordered_map<std::string, int> memo;  // (node id, index map) -> virtual register
+    int next_vreg = 0;
+    int op_budget = 0;
+    bool overflow = false;
+    std::vector<bool> dim_used_by_iota;
+    std::vector<std::array<int, 3>> vreg_ops;  // per instruction (= virtual register): operand vregs, -1 = none
+    std::vector<int64_t> leaf_offsets;         // element offset added to each leaf's base pointer
+  };
+
+  static uint64_t ImmBits(int dtype, const uint8_t* data) {
+    // register representation of one element (see kernels/ewise.cu)
+    switch (dtype) {
+      case B200_FLOAT32: { uint32_t u; memcpy(&u, data, 4); return u; }
+      case B200_BFLOAT16: { uint16_t h; memcpy(&h, data, 2); return (uint32_t)h << 16; }
+      case B200_FLOAT16: {
+        uint16_t h; memcpy(&h, data, 2);
+        const uint32_t sign = (h >> 15) & 1, exp = (h >> 10) & 0x1f, man = h & 0x3ff;
+        float f;
+        if (exp == 0) f = ldexpf((float)man, -24);
+        else if (exp == 31) f = man ? NAN : INFINITY;
+        else f = ldexpf((float)(man | 0x400), (int)exp - 25);
+        if (sign) f = -f;
+        uint32_t u; memcpy(&u, &f, 4); return u;
+      }
+      case B200_FLOAT64: case B200_INT64: case B200_UINT64: { uint64_t u; memcpy(&u, data, 8); return u; }
+      case B200_INT32: case B200_UINT32: { uint32_t u; memcpy(&u, data, 4); return u; }
+      case B200_INT16: { int16_t v; memcpy(&v, data, 2); return (uint32_t)(int32_t)v; }
+      case B200_UINT16: { uint16_t v; memcpy(&v, data, 2); return v; }
+      case B200_INT8: return (uint32_t)(int32_t)(int8_t)data[0];
+      case B200_UINT8: return data[0];
+      case B200_BOOL: return data[0] ? 1 : 0;
+    }
+    return 0;
+  }
+
+  int PushInstr(EwBuild& b, k::EwInstr in) {
+    if (b.prog.num_instr >= k::kEwMaxInstr) { b.overflow = true; return 0; }
+    in.dst = 0;
+    const int v = b.next_vreg++;
+    b.prog.instr[b.prog.num_instr++] = in;
+    return v;
+  }
+
+  // Emits code computing node x under index map im; returns the virtual register.
+  Status BuildExpr(EwBuild& b, Node* x, const IndexMap& im, int* out_vreg) {
+    if (b.overflow) { *out_vreg = 0; return Status::OK(); }
+    const std::string key = std::to_string(x->id) + "|" + im.key();
+    auto it = b.memo.find(key);
+    if (it != b.memo.end()) { *out_vreg = it->second; return Status::OK(); }
+    int v = -1;
+    Node* base = ViewBase(x);
+    const bool in_memory = base->op == Op::Parameter || slot_of_[base->id] >= 0;
+    if (!in_memory && IsView(x) && Fusible(ViewBase(x->in[0])) && (x->op == Op::Identity || UnitReshape(x))) {
+      // A view that only adds or drops size-1 dims of a value that is not in
+      // memory: carry the index map through instead of forcing a store.
+      Node* src = x->in[0];
+      IndexMap sm;
+      int xi = 0;
+      for (int j = 0; j < src->rank(); ++j) {
+        if (src->dims[j] == 1 && x->op != Op::Identity) { sm.m.push_back(-1); sm.a.push_back(0); sm.b.push_back(0); continue; }
+        if (x->op != Op::Identity)
+          while (x->dims[xi] == 1) ++xi;
+        sm.m.push_back(im.m[xi]); sm.a.push_back(im.a[xi]); sm.b.push_back(im.b[xi]);
+        ++xi;
+      }
+      return BuildExprMemo(b, key, src, sm, out_vreg);
+    }
+    const bool inline_it = !in_memory && !IsView(x) && Fusible(x) && (b.op_budget > 0 || Cheap(x));
+    if (!inline_it) {
+      // leaf: load from memory through the index map
+      if (!in_memory) B200_TRY(Materialize(base));
+      if (b.prog.num_leaves >= k::kEwMaxLeaves) { b.overflow = true; *out_vreg = 0; return Status::OK(); }
+      const int slot = slot_of_[base->id];
+      k::EwLeaf& lf = b.prog.leaves[b.prog.num_leaves];
+      lf.ptr = nullptr;
+      lf.dtype = x->dtype;
+      for (int d = 0; d < k::kMaxDims; ++d) lf.strides[d] = 0;
+      const std::vector<int64_t> cs = dense_strides(x->dims);
+      int64_t base_off = 0;
+      for (int i = 0; i < x->rank(); ++i) {
+        base_off += cs[i] * im.b[i];
+        if (im.m[i] >= 0) lf.strides[im.m[i]] += cs[i] * im.a[i];
+      }
+      b.leaf_offsets.push_back(base_off);
+      b.leaf_slots.push_back(slot);
+      k::EwInstr in{};
+      in.kind = k::EW_LOAD;
+      in.dtype = in.sdtype = (uint8_t)x->dtype;
+      in.a = (uint8_t)b.prog.num_leaves;
+      b.prog.num_leaves++;
+      b.vreg_ops.push_back({-1, -1, -1});
+      v = PushInstr(b, in);
+    } else if (x->op == Op::Constant) {
+      k::EwInstr in{};
+      in.kind = k::EW_IMM;
+      in.dtype = in.sdtype = (uint8_t)x->dtype;
+      in.imm = ImmBits(x->dtype, x->data.data());
+      b.vreg_ops.push_back({-1, -1, -1});
+      v = PushInstr(b, in);
+    } else if (x->op == Op::Iota) {
+      const int ax = (int)x->ia[0];
+      k::EwInstr in{};
+      in.dtype = in.sdtype = (uint8_t)x->dtype;
+      if (im.m[ax] < 0 || b.prog.dims[im.m[ax]] == 1) {
+        // constant coordinate
+        in.kind = k::EW_IMM;
+        in.imm = IotaImm(x->dtype, im.b[ax]);
+      } else if (im.a[ax] == 1 && im.b[ax] == 0) {
+        in.kind = k::EW_IOTA;
+        in.a = (uint8_t)im.m[ax];
+        b.dim_used_by_iota[im.m[ax]] = true;
+      } else {
+        // strided / offset iota: not expressible as a plain coordinate; keep it in memory
+        B200_TRY(Materialize(x));
+        return BuildExpr(b, x, im, out_vreg);
+      }
+      b.vreg_ops.push_back({-1, -1, -1});
+      v = PushInstr(b, in);
+    } else if (x->op == Op::BroadcastInDim) {
+      Node* src = x->in[0];
+      IndexMap sm;
+      for (int i = 0; i < src->rank(); ++i) {
+        const int oa = (int)x->ia[i];
+        if (src->dims[i] == 1 && x->dims[oa] != 1) { sm.m.push_back(-1); sm.a.push_back(0); sm.b.push_back(0); }
+        else { sm.m.push_back(im.m[oa]); sm.a.push_back(im.a[oa]); sm.b.push_back(im.b[oa]); }
+      }
+      return BuildExprMemo(b, key, src, sm, out_vreg);
+    } else if (x->op == Op::Transpose) {
+      Node* src = x->in[0];
+      IndexMap sm;
+      sm.m.resize(src->rank()); sm.a.resize(src->rank()); sm.b.resize(src->rank());
+      for (int i = 0; i < x->rank(); ++i) {
+        const int p = (int)x->ia[i];
+        sm.m[p] = im.m[i]; sm.a[p] = im.a[i]; sm.b[p] = im.b[i];
+      }
+      return BuildExprMemo(b, key, src, sm, out_vreg);
+    } else if (x->op == Op::Slice) {
+      Node* src = x->in[0];
+      IndexMap sm = im;
+      for (int i = 0; i < x->rank(); ++i) {
+        const int64_t start = x->ia[2 * i], stride = x->ia[2 * i + 1];
+        sm.a[i] = im.a[i] * stride;
+        sm.b[i] = im.b[i] * stride + start;
+      }
+      return BuildExprMemo(b, key, src, sm, out_vreg);
+    } else if (x->op == Op::Reverse) {
+      Node* src = x->in[0];
+      IndexMap sm = im;
+      for (int64_t ax : x->ia) {
+        sm.a[ax] = -im.a[ax];
+        sm.b[ax] = x->dims[ax] - 1 - im.b[ax];
+      }
+      return BuildExprMemo(b, key, src, sm, out_vreg);
+    } else {
+      // unary / binary / compare / where / clamp / cast
+      b.op_budget--;
+      int r[3] = {-1, -1, -1};
+      for (size_t i = 0; i < x->in.size() && i < 3; ++i) {
+        Node* o = x->in[i];
+        // NumPy-style broadcast: operand dims right-aligned to the result's
+        IndexMap om;
+        const int off = x->rank() - o->rank();
+        for (int d = 0; d < o->rank(); ++d) {
+          if (o->dims[d] == 1 && x->dims[off + d] != 1) { om.m.push_back(-1); om.a.push_back(0); om.b.push_back(0); }
+          else { om.m.push_back(im.m[off + d]); om.a.push_back(im.a[off + d]); om.b.push_back(im.b[off + d]); }
+        }
+        B200_TRY(BuildExpr(b, o, om, &r[i]));
+        if (b.overflow) { *out_vreg = 0; return Status::OK(); }
+      }
+      k::EwInstr in{};
+      if (x->op == Op::Cast) {
+        in.kind = k::EW_CAST;
+        in.dtype = (uint8_t)x->dtype;
+        in.sdtype = (uint8_t)x->in[0]->dtype;
+      } else {
+        in.kind = k::EW_OP;
+        in.op = (uint8_t)x->op;
+        in.dtype = (uint8_t)x->dtype;
+        in.sdtype = (uint8_t)((x->op == Op::Where) ? x->in[1]->dtype : x->in[0]->dtype);
+      }
+      b.vreg_ops.push_back({r[0], r[1], r[2]});
+      v = PushInstr(b, in);
+    }
+    b.memo[key] = v;
+    *out_vreg = v;
+    return Status::OK();
+  }
+  Status BuildExprMemo(EwBuild& b, const std::string& key, Node* src, const IndexMap& sm, int* out_vreg) {
+    B200_TRY(BuildExpr(b, src, sm, out_vreg));
+    b.memo[key] = *out_vreg;
+    return Status::OK();
+  }
+  static uint64_t IotaImm(int dtype, int64_t v) {
+    switch (dtype) {
+      case B200_FLOAT32: case B200_BFLOAT16: case B200_FLOAT16: { float f = (float)v; uint32_t u; memcpy(&u, &f, 4); return u; }
+      case B200_FLOAT64: { double d = (double)v; uint64_t u; memcpy(&u, &d, 8); return u; }
+      case B200_INT64: case B200_UINT64: return (uint64_t)v;
+      case B200_INT8: return (uint32_t)(int32_t)(int8_t)v;
+      case B200_INT16: return (uint32_t)(int32_t)(int16_t)v;
+      case B200_UINT8: return (uint32_t)(uint8_t)v;
+      case B200_UINT16: return (uint32_t)(uint16_t)v;
+      default: return (uint32_t)v;
+    }
+  }
+
+  Status EmitEwise(Node* x) {
+    if (x->rank() > k::kMaxDims) return Status::Unsupported("compile: elementwise result with more than 8 dims");
+    // Try with a generous inlining budget; on overflow of the interpreter's
+    // limits retry with a smaller one (deeper operands then become kernels of their own).
+    for (int budget = 24; budget >= 1; budget /= 2) {
+      EwBuild b;
+      b.op_budget = budget;
+      b.dim_used_by_iota.assign(x->rank() + 1, false);
+      b.prog.rank = x->rank();
+      for (int d = 0; d < x->rank(); ++d) b.prog.dims[d] = x->dims[d];
+      int root = 0;
+      // The root itself must be computed here even when it has a slot pending.
+      B200_TRY(BuildRoot(b, x, &root));
+      if (b.overflow) continue;
+      if (!AssignRegisters(b, root)) continue;
+      return FinishEwise(b, x);
+    }
+    return Status::Unsupported(strfmt("compile: elementwise node %s does not fit the interpreter", op_name(x->op)));
+  }
+
+  Status BuildRoot(EwBuild& b, Node* x, int* root) {
+    // x has no slot yet, so BuildExpr would inline it if budget allows; force that.
+    if (b.op_budget < 1) b.op_budget = 1;
+    return BuildExpr(b, x, IndexMap::Identity(x->rank()), root);
+  }
+
+  // Linear-scan allocation of physical registers from virtual ones.
+  bool AssignRegisters(EwBuild& b, int root_vreg) {
+    const int ni = b.prog.num_instr;
+    std::vector<int> last_use(ni, -1), phys(ni, -1);
+    for (int i = 0; i < ni; ++i)
+      for (int o : b.vreg_ops[i])
+        if (o >= 0) last_use[o] = i;
+    last_use[root_vreg] = ni;  // live to the end
+    std::vector<int> free_regs;
+    int next = 0;
+    for (int i = 0; i < ni; ++i) {
+      // operands whose last use is this instruction free their register AFTER it reads them,
+      // but the destination may reuse such a register only if it is not also read here by
+      // another element of the vector -- each thread reads all operands before writing, so reuse is safe.
+      k::EwInstr& in = b.prog.instr[i];
+      const auto& ops = b.vreg_ops[i];
+      if (in.kind == k::EW_OP || in.kind == k::EW_CAST) {
+        in.a = (uint8_t)(ops[0] >= 0 ? phys[ops[0]] : 0);
+        in.b = (uint8_t)(ops[1] >= 0 ? phys[ops[1]] : 0);
+        in.c = (uint8_t)(ops[2] >= 0 ? phys[ops[2]] : 0);
+      }
+      int dst;
+      if (!free_regs.empty()) { dst = free_regs.back(); free_regs.pop_back(); }
+      else dst = next++;
+      if (dst >= k::kEwMaxRegs) return false;
+      phys[i] = dst;
+      in.dst = (uint8_t)dst;
+      for (int o : ops)
+        if (o >= 0 && last_use[o] == i) {
+          bool dup = false;
+          for (int f : free_regs) dup |= (f == phys[o]);
+          if (!dup) free_regs.push_back(phys[o]);
+        }
+      if (last_use[i] < 0) free_regs.push_back(dst);  // value never read
+    }
+    b.prog.num_regs = next;
+    b.prog.out_reg = phys[root_vreg];
+    return true;
+  }
+
+  Status FinishEwise(EwBuild& b, Node* x) {
+    k::EwProgram prog = b.prog;
+    prog.out_dtype = x->dtype;
+    prog.wide = dtype_size(x->dtype) == 8;
+    for (int i = 0; i < prog.num_instr; ++i)
+      if (dtype_size(prog.instr[i].dtype) == 8 || dtype_size(prog.instr[i].sdtype) == 8) prog.wide = true;
+    // Drop size-1 dims and collapse neighbouring output dims that every leaf walks contiguously.
+    {
+      int r = 0;
+      int remap[k::kMaxDims];
+      int64_t dims[k::kMaxDims];
+      int64_t strides[k::kEwMaxLeaves][k::kMaxDims];
+      bool kept_iota[k::kMaxDims];
+      for (int d = 0; d < prog.rank; ++d) {
+        remap[d] = 0;
+        if (prog.dims[d] == 1) continue;  // never an iota dim (BuildExpr turns those into immediates)
+        bool merge = r > 0 && !b.dim_used_by_iota[d] && !kept_iota[r - 1];
+        if (merge)
+          for (int l = 0; l < prog.num_leaves; ++l) merge &= (strides[l][r - 1] == prog.leaves[l].strides[d] * prog.dims[d]);
+        if (merge) {
+          dims[r - 1] *= prog.dims[d];
+          for (int l = 0; l < prog.num_leaves; ++l) strides[l][r - 1] = prog.leaves[l].strides[d];
+          remap[d] = r - 1;
+        } else {
+          dims[r] = prog.dims[d];
+          for (int l = 0; l < prog.num_leaves; ++l) strides[l][r] = prog.leaves[l].strides[d];
+          kept_iota[r] = b.dim_used_by_iota[d];
+          remap[d] = r;
+          ++r;
+        }
+      }
+      if (r == 0) {
+        dims[0] = 1;
+        for (int l = 0; l < prog.num_leaves; ++l) strides[l][0] = 0;
+        r = 1;
+      }
+      for (int i = 0; i < prog.num_instr; ++i)
+        if (prog.instr[i].kind == k::EW_IOTA) prog.instr[i].a = (uint8_t)remap[prog.instr[i].a];
+      prog.rank = r;
+      for (int d = 0; d < k::kMaxDims; ++d) {
+        prog.dims[d] = d < r ? dims[d] : 0;
+        for (int l = 0; l < prog.num_leaves; ++l) prog.leaves[l].strides[d] = d < r ? strides[l][d] : 0;
+      }
+    }
+    const int out_slot = NewValueSlot(x);
+    Step st;
+    std::ostringstream os;
+    os << "ewise[" << op_name(x->op) << " instr=" << prog.num_instr << " leaves=" << prog.num_leaves << " regs=" << prog.num_regs
+       << (prog.wide ? " wide" : "") << "]";
+    st.desc = os.str();
+    st.reads = b.leaf_slots;
+    st.writes = {out_slot};
+    std::vector<int> leaf_slots = b.leaf_slots;
+    std::vector<int64_t> leaf_offsets = b.leaf_offsets;
+    st.run = [prog, leaf_slots, leaf_offsets, out_slot](Device* dev, void* const* p) -> Status {
+      k::EwProgram q = prog;
+      for (int l = 0; l < q.num_leaves; ++l)
+        q.leaves[l].ptr = (const char*)p[leaf_slots[l]] + leaf_offsets[l] * dtype_size(q.leaves[l].dtype);
+      q.out = p[out_slot];
+      return k::ewise_run(dev, q);
+    };
+    ex_->steps.push_back(std::move(st));
+    return Status::OK();
+  }
+
+  // --------------------------------------------------------- data movement ---
+  // A lone Transpose / Slice / Reverse / BroadcastInDim of something already in memory.
+  Status EmitMovement(Node* x) {
+    Node* src = x->in[0];
+    B200_TRY(EnsureMaterialized(src));
+    if (x->rank() > k::kMaxDims) return Status::Unsupported("compile: more than 8 dims");
+    const int in_slot = SlotOf(src);
+    k::StridedCopyParams p;
+    p.elt_size = dtype_size(x->dtype);
+    p.rank = x->rank();
+    const std::vector<int64_t> cs = dense_strides(src->dims), os = dense_strides(x->dims);
+    for (int d = 0; d < x->rank(); ++d) { p.dims[d] = x->dims[d]; p.out_strides[d] = os[d]; p.in_strides[d] = 0; }
+    switch (x->op) {
+      case Op::Transpose:
+        for (int d = 0; d < x->rank(); ++d) p.in_strides[d] = cs[x->ia[d]];
+        break;
+      case Op::Slice:
+        for (int d = 0; d < x->rank(); ++d) { p.in_strides[d] = cs[d] * x->ia[2 * d + 1]; p.in_offset += cs[d] * x->ia[2 * d]; }
+        break;
+      case Op::Reverse:
+        for (int d = 0; d < x->rank(); ++d) p.in_strides[d] = cs[d];
+        for (int64_t ax : x->ia) { p.in_strides[ax] = -cs[ax]; p.in_offset += cs[ax] * (x->dims[ax] - 1); }
+        break;
+      default:  // BroadcastInDim
+        for (int i = 0; i < src->rank(); ++i) {
+          const int oa = (int)x->ia[i];
+          p.in_strides[oa] = (src->dims[i] == 1 && x->dims[oa] != 1) ? 0 : cs[i];
+        }
+        break;
+    }
+    // Batched swap of the two innermost dims goes through the tiled transpose.
+    bool tiled = false;
+    int64_t tb = 1, trows = 0, tcols = 0;
+    if (x->op == Op::Transpose && x->rank() >= 2) {
+      const int r = x->rank();
+      tiled = x->ia[r - 1] == r - 2 && x->ia[r - 2] == r - 1;
+      for (int d = 0; d < r - 2 && tiled; ++d) { tiled = x->ia[d] == d; tb *= x->dims[d]; }
+      trows = src->dims[r - 2];
+      tcols = src->dims[r - 1];
+      if (tb > 65535 || (trows + 31) / 32 > 65535) tiled = false;
+    }
+    const int out_slot = NewValueSlot(x);
+    Step st;
+    st.desc = std::string("move[") + op_name(x->op) + (tiled ? " tiled" : "") + "]";
+    st.reads = {in_slot};
+    st.writes = {out_slot};
+    const int es = p.elt_size;
+    if (tiled) {
+      st.run = [=](Device* dev, void* const* ptrs) -> Status { return k::transpose_2d(dev, ptrs[in_slot], ptrs[out_slot], tb, trows, tcols, es); };
+    } else {
+      st.run = [p, in_slot, out_slot](Device* dev, void* const* ptrs) -> Status {
+        k::StridedCopyParams q = p;
+        q.x = ptrs[in_slot];
+        q.y = ptrs[out_slot];
+        return k::strided_copy(dev, q);
+      };
+    }
+    ex_->steps.push_back(std::move(st));
+    return Status::OK();
+  }
+
+  // Copies `src` (any materialised node) into a sub-block of slot `out_slot`.
+  void EmitBlockCopy(Node* src, int out_slot, const std::vector<int64_t>& out_dims, const std::vector<int64_t>& out_start,
+                     const char* what) {
+    k::StridedCopyParams p;
+    p.elt_size = dtype_size(src->dtype);
+    p.rank = src->rank();
+    const std::vector<int64_t> cs = dense_strides(src->dims), os = dense_strides(out_dims);
+    for (int d = 0; d < src->rank(); ++d) {
+      p.dims[d] = src->dims[d];
+      p.in_strides[d] = cs[d];
+      p.out_strides[d] = os[d];
+      p.out_offset += os[d] * out_start[d];
+    }
+    const int in_slot = SlotOf(src);
+    Step st;
+    st.desc = std::string("move[") + what + "]";
+    st.reads = {in_slot};
+    st.writes = {out_slot};
+    st.run = [p, in_slot, out_slot](Device* dev, void* const* ptrs) -> Status {
+      k::StridedCopyParams q = p;
+      q.x = ptrs[in_slot];
+      q.y = ptrs[out_slot];
+      return k::strided_copy(dev, q);
+    };
+    ex_->steps.push_back(std::move(st));
+  }
+
+  Status EmitConcatenate(Node* x) {
+    if (x->rank() > k::kMaxDims) return Status::Unsupported("compile: more than 8 dims");
+    for (Node* in : x->in) B200_TRY(EnsureMaterialized(in));
+    const int out_slot = NewValueSlot(x);
+    const int ax = (int)x->ia[0];
+    int64_t pos = 0;
+    for (Node* in : x->in) {
+      std::vector<int64_t> start(x->rank(), 0);
+      start[ax] = pos;
+      EmitBlockCopy(in, out_slot, x->dims, start, "Concatenate");
+      pos += in->dims[ax];
+    }
+    return Status::OK();
+  }
+
+  Status EmitPad(Node* x) {
+    if (x->rank() > k::kMaxDims) return Status::Unsupported("compile: more than 8 dims");
+    Node* src = x->in[0];
+    Node* pv = x->in[1];
+    B200_TRY(EnsureMaterialized(src));
+    B200_TRY(EnsureMaterialized(pv));
+    const int out_slot = NewValueSlot(x);
+    const int pv_slot = SlotOf(pv);
+    {
+      // fill = broadcast of the one-element pad value
+      k::StridedCopyParams p;
+      p.elt_size = dtype_size(x->dtype);
+      p.rank = 1;
+      p.dims[0] = x->num_elements();
+      p.in_strides[0] = 0;
+      p.out_strides[0] = 1;
+      Step st;
+      st.desc = "move[Pad fill]";
+      st.reads = {pv_slot};
+      st.writes = {out_slot};
+      st.run = [p, pv_slot, out_slot](Device* dev, void* const* ptrs) -> Status {
+        k::StridedCopyParams q = p;
+        q.x = ptrs[pv_slot];
+        q.y = ptrs[out_slot];
+        return k::strided_copy(dev, q);
+      };
+      ex_->steps.push_back(std::move(st));
+    }
+    std::vector<int64_t> start(x->ia.begin(), x->ia.end());
+    EmitBlockCopy(src, out_slot, x->dims, start, "Pad body");
+    ex_->steps.back().reads.push_back(out_slot);  // ordered after the fill
+    return Status::OK();
+  }
+
+  // Makes a dense copy of `src` permuted by `perm` into a temp slot; returns the slot.
+  int EmitPermutedTemp(Node* src, const std::vector<int>& perm, const char* what) {
+    k::StridedCopyParams p;
+    p.elt_size = dtype_size(src->dtype);
+    p.rank = src->rank();
+    const std::vector<int64_t> cs = dense_strides(src->dims);
+    std::vector<int64_t> od(src->rank());
+    for (int d = 0; d < src->rank(); ++d) od[d] = src->dims[perm[d]];
+    const std::vector<int64_t> os = dense_strides(od);
+    for (int d = 0; d < src->rank(); ++d) { p.dims[d] = od[d]; p.in_strides[d] = cs[perm[d]]; p.out_strides[d] = os[d]; }
+    const int in_slot = SlotOf(src);
+    const int tmp = NewTemp(src->num_elements() * dtype_size(src->dtype));
+    Step st;
+    st.desc = std::string("move[") + what + "]";
+    st.reads = {in_slot};
+    st.writes = {tmp};
+    st.run = [p, in_slot, tmp](Device* dev, void* const* ptrs) -> Status {
+      k::StridedCopyParams q = p;
+      q.x = ptrs[in_slot];
+      q.y = ptrs[tmp];
+      return k::strided_copy(dev, q);
+    };
+    ex_->steps.push_back(std::move(st));
+    return tmp;
+  }
+
+  // ------------------------------------------------------------ DotGeneral ---
+  // Decides whether an operand, as it lies in memory, is [batch, free, contract]
+  // (K-major) or [batch, contract, free] (MN-major) with the batch and
+  // contracting axes in the required order.  Returns 1, 0, or -1 (needs a copy).
+  static int OperandMajor(Node* t, const std::vector<int64_t>& batch, const std::vector<int64_t>& contract) {
+    const int r = t->rank();
+    std::vector<int> role(r, 0);  // 0 free, 1 batch, 2 contracting
+    for (auto a : batch) role[a] = 1;
+    for (auto a : contract) role[a] = 2;
+    // size-1 axes can sit anywhere; ignore them when reading the order
+    std::vector<int> order;
+    for (int i = 0; i < r; ++i)
+      if (t->dims[i] != 1) {
+        if (order.empty() || order.back() != role[i]) order.push_back(role[i]);
+      }
+    auto ascending = [&](const std::vector<int64_t>& axes) {
+      int64_t prev = -1;
+      for (auto a : axes) {
+        if (t->dims[a] == 1) continue;
+        if (a < prev) return false;
+        prev = a;
+      }
+      return true;
+    };
+    if (!ascending(batch) || !ascending(contract)) return -1;
+    // strip a leading batch group
+    size_t i = 0;
+    if (i < order.size() && order[i] == 1) ++i;
+    std::vector<int> rest(order.begin() + i, order.end());
+    for (int v : rest)
+      if (v == 1) return -1;  // batch axes not leading
+    if (rest.empty()) return 1;
+    if (rest.size() == 1) return 1;  // only free or only contracting: either reading works; call it K-major
+    if (rest.size() == 2) return (rest[0] == 0 && rest[1] == 2) ? 1 : ((rest[0] == 2 && rest[1] == 0) ? 0 : -1);
+    return -1;
+  }
+
+  Status EmitDotGeneral(Node* x) {
+    Node* a = x->in[0];
+    Node* b = x->in[1];
+    Node* bias = x->in.size() > 2 ? x->in[2] : nullptr;
+    B200_TRY(EnsureMaterialized(a));
+    B200_TRY(EnsureMaterialized(b));
+    if (bias) B200_TRY(EnsureMaterialized(bias));
+    const int nc = (int)x->ia[0], nb = (int)x->ia[1];
+    std::vector<int64_t> lc(x->ia.begin() + 2, x->ia.begin() + 2 + nc);
+    std::vector<int64_t> lb(x->ia.begin() + 2 + nc, x->ia.begin() + 2 + nc + nb);
+    std::vector<int64_t> rc(x->ia.begin() + 2 + nc + nb, x->ia.begin() + 2 + 2 * nc + nb);
+    std::vector<int64_t> rb(x->ia.begin() + 2 + 2 * nc + nb, x->ia.begin() + 2 + 2 * nc + 2 * nb);
+    int64_t B = 1, K = 1;
+    for (auto ax : lb) B *= a->dims[ax];
+    for (auto ax : lc) K *= a->dims[ax];
+    const int64_t M = (B * K) ? a->num_elements() / (B * K) : 0;
+    const int64_t N = (B * K) ? b->num_elements() / (B * K) : 0;
+    int a_major = OperandMajor(a, lb, lc);
+    int b_major = OperandMajor(b, rb, rc);  // 1: [B,N,K]; 0: [B,K,N]
+    // With several contracting (or batch) axes both sides must walk them in the same order.
+    auto same_order = [](Node* t1, const std::vector<int64_t>& ax1, Node* t2, const std::vector<int64_t>& ax2) {
+      std::vector<size_t> idx;
+      for (size_t i = 0; i < ax1.size(); ++i)
+        if (t1->dims[ax1[i]] != 1) idx.push_back(i);
+      for (size_t i = 1; i < idx.size(); ++i)
+        if ((ax1[idx[i]] > ax1[idx[i - 1]]) != (ax2[idx[i]] > ax2[idx[i - 1]])) return false;
+      return true;
+    };
+    if (!same_order(a, lc, b, rc) || !same_order(a, lb, b, rb)) b_major = -1;
+    int a_slot = SlotOf(a), b_slot = SlotOf(b);
+    auto canonical = [&](Node* t, const std::vector<int64_t>& batch, const std::vector<int64_t>& contract) {
+      std::vector<int> perm;
+      std::vector<bool> used(t->rank(), false);
+      for (auto ax : batch) { perm.push_back((int)ax); used[ax] = true; }
+      for (auto ax : contract) used[ax] = true;
+      for (int i = 0; i < t->rank(); ++i)
+        if (!used[i]) perm.push_back(i);
+      for (auto ax : contract) perm.push_back((int)ax);
+      return perm;
+    };
+    if (a_major < 0) {
+      if (a->rank() > k::kMaxDims) return Status::Unsupported("DotGeneral: more than 8 dims");
+      a_slot = EmitPermutedTemp(a, canonical(a, lb, lc), "DotGeneral lhs -> [B,M,K]");
+      a_major = 1;
+    }
+    if (b_major < 0) {
+      if (b->rank() > k::kMaxDims) return Status::Unsupported("DotGeneral: more than 8 dims");
+      b_slot = EmitPermutedTemp(b, canonical(b, rb, rc), "DotGeneral rhs -> [B,N,K]");
+      b_major = 1;
+    }
+    const int out_slot = NewValueSlot(x);
+    k::GemmParams gp;
+    gp.batch = B; gp.m = M; gp.n = N; gp.k = K;
+    gp.a_k_major = a_major == 1;
+    gp.b_k_major = b_major == 1;
+    gp.dtype = x->dtype;
+    gp.activation = (int)x->fa[0];
+    const int bias_slot = bias ? SlotOf(bias) : -1;
+    Step st;
+    st.desc = strfmt("gemm[B=%lld M=%lld N=%lld K=%lld %s a:%s b:%s%s act=%d]", (long long)B, (long long)M, (long long)N, (long long)K,
+                     dtype_name(x->dtype), gp.a_k_major ? "MK" : "KM", gp.b_k_major ? "NK" : "KN", bias ? " bias" : "", gp.activation);
+    st.reads = {a_slot, b_slot};
+    if (bias) st.reads.push_back(bias_slot);
+    st.writes = {out_slot};
+    st.run = [gp, a_slot, b_slot, bias_slot, out_slot](Device* dev, void* const* p) -> Status {
+      k::GemmParams q = gp;
+      q.a = p[a_slot];
+      q.b = p[b_slot];
+      q.c = p[out_slot];
+      q.bias = bias_slot >= 0 ? p[bias_slot] : nullptr;
+      return k::gemm(dev, q);
+    };
+    ex_->steps.push_back(std::move(st));
+    return Status::OK();
+  }
+
+  // ------------------------------------------------------------ reductions ---
+  Status EmitReduce(Node* x) {
+    Node* src = x->in[0];
+    B200_TRY(EnsureMaterialized(src));
+    const int rt = (int)x->ia[0];
+    std::vector<int64_t> axes(x->ia.begin() + 1, x->ia.end());
+    std::sort(axes.begin(), axes.end());
+    // Runs of neighbouring reduced axes, folded from the innermost run outwards.
+    struct Run { int lo, hi; };
+    std::vector<Run> runs;
+    for (auto ax : axes) {
+      if (!runs.empty() && runs.back().hi + 1 == (int)ax) runs.back().hi = (int)ax;
+      else runs.push_back(Run{(int)ax, (int)ax});
+    }
+    std::vector<int64_t> cur = src->dims;
+    int cur_slot = SlotOf(src);
+    if (runs.empty()) {
+      // nothing to reduce (rank-0 operand): copy through
+      const int out_slot = NewValueSlot(x);
+      const int64_t nbytes = x->num_elements() * dtype_size(x->dtype);
+      Step st;
+      st.desc = "copy[Reduce of scalar]";
+      st.reads = {cur_slot};
+      st.writes = {out_slot};
+      st.launches = 0;
+      st.run = [=](Device* dev, void* const* p) -> Status {
+        B200_CUDA_TRY(cudaMemcpyAsync(p[out_slot], p[cur_slot], (size_t)nbytes, cudaMemcpyDeviceToDevice, dev->stream()));
+        return Status::OK();
+      };
+      ex_->steps.push_back(std::move(st));
+      return Status::OK();
+    }
+    for (int ri = (int)runs.size() - 1; ri >= 0; --ri) {
+      int64_t outer = 1, n = 1, inner = 1;
+      for (int d = 0; d < runs[ri].lo; ++d) outer *= cur[d];
+      for (int d = runs[ri].lo; d <= runs[ri].hi; ++d) n *= cur[d];
+      for (int d = runs[ri].hi + 1; d < (int)cur.size(); ++d) inner *= cur[d];
+      const bool last = ri == 0;
+      const int64_t out_bytes = outer * inner * dtype_size(x->dtype);
+      const int out_slot = last ? NewValueSlot(x) : NewTemp(out_bytes);
+      const int64_t sb = k::reduce_scratch_bytes(x->dtype, outer, n, inner);
+      const int scratch_slot = sb > 0 ? NewTemp(sb) : -1;
+      const int in_slot = cur_slot, dt = x->dtype;
+      Step st;
+      st.desc = strfmt("reduce[type=%d outer=%lld n=%lld inner=%lld %s%s]", rt, (long long)outer, (long long)n, (long long)inner,
+                       dtype_name(dt), sb > 0 ? " split" : "");
+      st.reads = {in_slot};
+      st.writes = {out_slot};
+      if (scratch_slot >= 0) st.writes.push_back(scratch_slot);
+      st.launches = sb > 0 ? 2 : 1;
+      st.run = [=](Device* dev, void* const* p) -> Status {
+        return k::reduce(dev, p[in_slot], p[out_slot], dt, rt, outer, n, inner, scratch_slot >= 0 ? p[scratch_slot] : nullptr, sb);
+      };
+      ex_->steps.push_back(std::move(st));
+      cur.erase(cur.begin() + runs[ri].lo, cur.begin() + runs[ri].hi + 1);
+      cur_slot = out_slot;
+    }
+    return Status::OK();
+  }
+
+  Status EmitArgMinMax(Node* x) {
+    Node* src = x->in[0];
+    B200_TRY(EnsureMaterialized(src));
+    const int ax = (int)x->ia[0];
+    const bool is_min = x->ia[1] != 0;
+    int64_t outer = 1, inner = 1;
+    for (int d = 0; d < ax; ++d) outer *= src->dims[d];
+    for (int d = ax + 1; d < src->rank(); ++d) inner *= src->dims[d];
+    const int64_t n = src->dims[ax];
+    const int in_slot = SlotOf(src), out_slot = NewValueSlot(x);
+    const int dt = src->dtype, odt = x->dtype;
+    Step st;
+    st.desc = strfmt("arg%s[outer=%lld n=%lld inner=%lld %s -> %s]", is_min ? "min" : "max", (long long)outer, (long long)n,
+                     (long long)inner, dtype_name(dt), dtype_name(odt));
+    st.reads = {in_slot};
+    st.writes = {out_slot};
+    st.run = [=](Device* dev, void* const* p) -> Status { return k::arg_min_max(dev, p[in_slot], p[out_slot], dt, odt, is_min, outer, n, inner); };
+    ex_->steps.push_back(std::move(st));
+    return Status::OK();
+  }
+
+  // ---------------------------------------------------------------- gather ---
+  Status EmitGather(Node* x) {
+    Node* op = x->in[0];
+    Node* idx = x->in[1];
+    B200_TRY(EnsureMaterialized(op));
+    B200_TRY(EnsureMaterialized(idx));
+    size_t pos = 0;
+    const int iva = (int)x->ia[pos++];
+    auto take = [&]() { const int n = (int)x->ia[pos++]; std::vector<int64_t> v(x->ia.begin() + pos, x->ia.begin() + pos + n); pos += n; return v; };
+    const std::vector<int64_t> off_axes = take(), collapsed = take(), sim = take(), ss = take();
+    const int orank = op->rank(), irank = idx->rank();
+    if (orank > k::kMaxDims || x->rank() > k::kMaxDims || irank > k::kMaxDims) return Status::Unsupported("Gather: more than 8 dims");
+    const int op_slot = SlotOf(op), idx_slot = SlotOf(idx), out_slot = NewValueSlot(x);
+    const int es = dtype_size(op->dtype), idt = idx->dtype;
+    // Fast path: whole rows of the leading axis (embedding lookup; ref gather.go:61-91).
+    bool rows = sim.size() == 1 && sim[0] == 0 && collapsed.size() == 1 && collapsed[0] == 0 && ss[0] == 1 &&
+                (iva == irank || iva == irank - 1);
+    for (int d = 1; d < orank && rows; ++d) rows = ss[d] == op->dims[d];
+    const int batch_rank = iva == irank ? irank : irank - 1;
+    for (size_t i = 0; i < off_axes.size() && rows; ++i) rows = off_axes[i] == (int64_t)(batch_rank + i);
+    int64_t row_bytes = es;
+    for (int d = 1; d < orank; ++d) row_bytes *= op->dims[d];
+    rows = rows && (row_bytes % 16 == 0) && orank >= 1;
+    if (rows) {
+      const int64_t num_ids = idx->num_elements(), num_rows = op->dims[0];
+      Step st;
+      st.desc = strfmt("gather_rows[ids=%lld rows=%lld row_bytes=%lld]", (long long)num_ids, (long long)num_rows, (long long)row_bytes);
+      st.reads = {op_slot, idx_slot};
+      st.writes = {out_slot};
+      st.run = [=](Device* dev, void* const* p) -> Status { return k::gather_rows(dev, p[op_slot], p[idx_slot], idt, p[out_slot], num_ids, num_rows, row_bytes); };
+      ex_->steps.push_back(std::move(st));
+      return Status::OK();
+    }
+    k::GatherParams gp;
+    gp.elt_size = es;
+    gp.ids_dtype = idt;
+    gp.out_rank = x->rank();
+    gp.operand_rank = orank;
+    const std::vector<int64_t> ostr = dense_strides(op->dims), istr = dense_strides(idx->dims);
+    for (int d = 0; d < orank; ++d) { gp.operand_dims[d] = op->dims[d]; gp.operand_strides[d] = ostr[d]; gp.slice_sizes[d] = ss[d]; }
+    std::vector<int> offset_operand_axes;  // non-collapsed operand axes in order
+    for (int d = 0; d < orank; ++d)
+      if (!std::count(collapsed.begin(), collapsed.end(), (int64_t)d)) offset_operand_axes.push_back(d);
+    int bpos = 0;
+    for (int d = 0; d < x->rank(); ++d) {
+      gp.out_dims[d] = x->dims[d];
+      auto it = std::find(off_axes.begin(), off_axes.end(), (int64_t)d);
+      if (it != off_axes.end()) { gp.out_offset_operand_axis[d] = offset_operand_axes[it - off_axes.begin()]; gp.out_batch_pos[d] = -1; }
+      else { gp.out_offset_operand_axis[d] = -1; gp.out_batch_pos[d] = bpos++; }
+    }
+    gp.num_batch_dims = bpos;
+    int bi = 0;
+    for (int d = 0; d < irank; ++d)
+      if (d != iva) gp.batch_index_strides[bi++] = istr[d];
+    gp.index_vector_stride = iva < irank ? istr[iva] : 0;
+    gp.num_index_components = (int)sim.size();
+    for (size_t i = 0; i < sim.size(); ++i) gp.start_index_map[i] = (int)sim[i];
+    Step st;
+    st.desc = "gather_general";
+    st.reads = {op_slot, idx_slot};
+    st.writes = {out_slot};
+    st.run = [gp, op_slot, idx_slot, out_slot](Device* dev, void* const* p) -> Status {
+      k::GatherParams q = gp;
+      q.operand = p[op_slot];
+      q.indices = p[idx_slot];
+      q.y = p[out_slot];
+      return k::gather_general(dev, q);
+    };
+    ex_->steps.push_back(std::move(st));
+    return Status::OK();
+  }
+
+  // ----------------------------------------------------------- softmax etc. ---
+  Status EmitSoftmax(Node* x) {
+    Node* src = x->in[0];
+    B200_TRY(EnsureMaterialized(src));
+    const int ax = (int)x->ia[0];
+    int64_t outer = 1, inner = 1;
+    for (int d = 0; d < ax; ++d) outer *= src->dims[d];
+    for (int d = ax + 1; d < src->rank(); ++d) inner *= src->dims[d];
+    const int64_t n = src->dims[ax];
+    const int in_slot = SlotOf(src), out_slot = NewValueSlot(x), dt = x->dtype;
+    Step st;
+    st.desc = strfmt("softmax[outer=%lld n=%lld inner=%lld %s]", (long long)outer, (long long)n, (long long)inner, dtype_name(dt));
+    st.reads = {in_slot};
+    st.writes = {out_slot};
+    if (inner == 1 && dt != B200_FLOAT64) {
+      st.run = [=](Device* dev, void* const* p) -> Status {
+        k::SoftmaxParams sp;
+        sp.x = p[in_slot]; sp.y = p[out_slot]; sp.rows = outer; sp.cols = n; sp.dtype = dt;
+        return k::softmax_rows(dev, sp);
+      };
+    } else {
+      if (dt == B200_FLOAT64) return Status::Unsupported("FusedSoftmax: Float64");
+      st.run = [=](Device* dev, void* const* p) -> Status { return k::softmax_strided(dev, p[in_slot], p[out_slot], outer, n, inner, dt); };
+    }
+    ex_->steps.push_back(std::move(st));
+    return Status::OK();
+  }
+
+  Status EmitSoftmaxMasked(Node* x) {
+    Node* src = x->in[0];
+    Node* mask = x->in.size() > 1 ? x->in[1] : nullptr;
+    B200_TRY(EnsureMaterialized(src));
+    if (mask) B200_TRY(EnsureMaterialized(mask));
+    const int r = src->rank();
+    const int64_t cols = src->dims[r - 1], seq_q = src->dims[r - 2];
+    const int64_t heads = r >= 3 ? src->dims[r - 3] : 1;
+    int64_t rows = 1;
+    for (int d = 0; d < r - 1; ++d) rows *= src->dims[d];
+    k::SoftmaxParams sp;
+    sp.rows = rows; sp.cols = cols; sp.dtype = x->dtype; sp.scale = x->fa[0]; sp.causal = x->ia[0] != 0;
+    sp.seq_q = seq_q; sp.heads = heads;
+    if (mask) {
+      sp.mask_kind = mask->dtype == B200_BOOL ? 1 : 2;
+      const std::vector<int64_t> ms = dense_strides(mask->dims);
+      const int off = r - mask->rank();
+      // positions: batch (everything left of heads, must be one dim or broadcast), head, q, k
+      auto stride_at = [&](int xdim) -> int64_t {
+        const int md = xdim - off;
+        if (md < 0 || mask->dims[md] == 1) return 0;
+        return ms[md];
+      };
+      sp.mask_strides[3] = stride_at(r - 1);
+      sp.mask_strides[2] = stride_at(r - 2);
+      sp.mask_strides[1] = r >= 3 ? stride_at(r - 3) : 0;
+      int64_t bstride = 0;
+      int nonbroadcast_batch_dims = 0;
+      for (int d = 0; d < r - 3; ++d)
+        if (stride_at(d) != 0) { nonbroadcast_batch_dims++; bstride = stride_at(d); }
+      if (nonbroadcast_batch_dims > 1 || (nonbroadcast_batch_dims == 1 && r - 3 > 1))
+        return Status::Unsupported("SoftmaxMasked: mask varies over more than one leading batch axis");
+      sp.mask_strides[0] = bstride;
+    }
+    const int in_slot = SlotOf(src), out_slot = NewValueSlot(x), mask_slot = mask ? SlotOf(mask) : -1;
+    Step st;
+    st.desc = strfmt("softmax_masked[rows=%lld cols=%lld %s scale=%g causal=%d mask=%d]", (long long)rows, (long long)cols,
+                     dtype_name(x->dtype), sp.scale, (int)sp.causal, sp.mask_kind);
+    st.reads = {in_slot};
+    if (mask) st.reads.push_back(mask_slot);
+    st.writes = {out_slot};
+    st.run = [sp, in_slot, out_slot, mask_slot](Device* dev, void* const* p) -> Status {
+      k::SoftmaxParams q = sp;
+      q.x = p[in_slot];
+      q.y = p[out_slot];
+      q.mask = mask_slot >= 0 ? p[mask_slot] : nullptr;
+      return k::softmax_rows(dev, q);
+    };
+    ex_->steps.push_back(std::move(st));
+    return Status::OK();
+  }
+
+  // A [cols] vector for gamma / beta: the parameter itself when it already is
+  // one, else a broadcast copy laid over the normalised axes.
+  Status NormParamSlot(Node* x, Node* p, const std::vector<int64_t>& axes, int64_t cols, int* slot) {
+    B200_TRY(EnsureMaterialized(p));
+    if (p->num_elements() == cols) {
+      // dims (ignoring 1s) must follow the normalised axes in order: true when counts match, because
+      // check_scale() aligned it either to the axes (lower rank) or to the full shape (equal rank).
+      *slot = SlotOf(p);
+      return Status::OK();
+    }
+    // broadcast inside the normalised axes
+    std::vector<int64_t> nd;
+    for (auto ax : axes) nd.push_back(x->dims[ax]);
+    k::StridedCopyParams sc;
+    sc.elt_size = dtype_size(p->dtype);
+    sc.rank = (int)nd.size();
+    if (sc.rank > k::kMaxDims) return Status::Unsupported("norm: more than 8 normalised axes");
+    const std::vector<int64_t> os = dense_strides(nd), ps = dense_strides(p->dims);
+    for (int d = 0; d < sc.rank; ++d) {
+      sc.dims[d] = nd[d];
+      sc.out_strides[d] = os[d];
+      int pd;
+      if (p->rank() >= x->rank()) pd = (int)axes[d];
+      else pd = d < p->rank() ? d : -1;
+      sc.in_strides[d] = (pd < 0 || p->dims[pd] == 1) ? 0 : ps[pd];
+    }
+    const int in_slot = SlotOf(p);
+    const int tmp = NewTemp(cols * dtype_size(p->dtype));
+    Step st;
+    st.desc = "move[norm parameter broadcast]";
+    st.reads = {in_slot};
+    st.writes = {tmp};
+    st.run = [sc, in_slot, tmp](Device* dev, void* const* ptrs) -> Status {
+      k::StridedCopyParams q = sc;
+      q.x = ptrs[in_slot];
+      q.y = ptrs[tmp];
+      return k::strided_copy(dev, q);
+    };
+    ex_->steps.push_back(std::move(st));
+    *slot = tmp;
+    return Status::OK();
+  }
+
+  Status EmitNorm(Node* x) {
+    Node* src = x->in[0];
+    B200_TRY(EnsureMaterialized(src));
+    if (x->dtype == B200_FLOAT64) return Status::Unsupported("norm: Float64");
+    const bool rms = x->op == Op::RmsNorm;
+    const bool has_gamma = x->ia[0] != 0, has_beta = x->ia[1] != 0;
+    std::vector<int64_t> axes(x->ia.begin() + 2, x->ia.end());
+    const int r = src->rank();
+    int64_t cols = 1;
+    for (auto ax : axes) cols *= src->dims[ax];
+    const int64_t rows = cols ? src->num_elements() / cols : 0;
+    // trailing block of axes?
+    bool trailing = true;
+    for (size_t i = 0; i < axes.size(); ++i) trailing &= axes[i] == (int64_t)(r - (int)axes.size() + (int)i);
+    int gamma_slot = -1, beta_slot = -1;
+    size_t pi = 1;
+    if (has_gamma) B200_TRY(NormParamSlot(src, x->in[pi++], axes, cols, &gamma_slot));
+    if (has_beta) B200_TRY(NormParamSlot(src, x->in[pi++], axes, cols, &beta_slot));
+    int in_slot = SlotOf(src);
+    std::vector<int> perm, inv;
+    if (!trailing) {
+      if (r > k::kMaxDims) return Status::Unsupported("norm: more than 8 dims");
+      std::vector<bool> is_norm(r, false);
+      for (auto ax : axes) is_norm[ax] = true;
+      for (int d = 0; d < r; ++d)
+        if (!is_norm[d]) perm.push_back(d);
+      for (auto ax : axes) perm.push_back((int)ax);
+      in_slot = EmitPermutedTemp(src, perm, "norm axes -> trailing");
+      inv.resize(r);
+      for (int d = 0; d < r; ++d) inv[perm[d]] = d;
+    }
+    const int64_t nbytes = x->num_elements() * dtype_size(x->dtype);
+    const int norm_out = trailing ? NewValueSlot(x) : NewTemp(nbytes);
+    k::NormParams np;
+    np.rows = rows; np.cols = cols; np.dtype = x->dtype; np.epsilon = x->fa[0]; np.rms = rms;
+    Step st;
+    st.desc = strfmt("%s[rows=%lld cols=%lld %s gamma=%d beta=%d]", rms ? "rms_norm" : "layer_norm", (long long)rows, (long long)cols,
+                     dtype_name(x->dtype), (int)has_gamma, (int)has_beta);
+    st.reads = {in_slot};
+    if (gamma_slot >= 0) st.reads.push_back(gamma_slot);
+    if (beta_slot >= 0) st.reads.push_back(beta_slot);
+    st.writes = {norm_out};
+    st.run = [np, in_slot, gamma_slot, beta_slot, norm_out](Device* dev, void* const* p) -> Status {
+      k::NormParams q = np;
+      q.x = p[in_slot];
+      q.y = p[norm_out];
+      q.gamma = gamma_slot >= 0 ? p[gamma_slot] : nullptr;
+      q.beta = beta_slot >= 0 ? p[beta_slot] : nullptr;
+      return k::norm_rows(dev, q);
+    };
+    ex_->steps.push_back(std::move(st));
+    if (!trailing) {
+      // permute back
+      std::vector<int64_t> pd(r);
+      for (int d = 0; d < r; ++d) pd[d] = src->dims[perm[d]];
+      k::StridedCopyParams sc;
+      sc.elt_size = dtype_size(x->dtype);
+      sc.rank = r;
+      const std::vector<int64_t> ps = dense_strides(pd), os = dense_strides(x->dims);
+      for (int d = 0; d < r; ++d) { sc.dims[d] = x->dims[d]; sc.out_strides[d] = os[d]; sc.in_strides[d] = ps[inv[d]]; }
+      const int out_slot = NewValueSlot(x);
+      Step back;
+      back.desc = "move[norm axes back]";
+      back.reads = {norm_out};
+      back.writes = {out_slot};
+      back.run = [sc, norm_out, out_slot](Device* dev, void* const* ptrs) -> Status {
+        k::StridedCopyParams q = sc;
+        q.x = ptrs[norm_out];
+        q.y = ptrs[out_slot];
+        return k::strided_copy(dev, q);
+      };
+      ex_->steps.push_back(std::move(back));
+    }
+    return Status::OK();
+  }
+
+  // ----------------------------------------------------------- memory plan ---
+  void PlanArena() {
+    auto& slots = ex_->slots;
+    for (int si = 0; si < (int)ex_->steps.size(); ++si) {
+      for (int s : ex_->steps[si].writes) {
+        if (slots[s].first_step < 0) slots[s].first_step = si;
+        slots[s].last_step = si;
+      }
+      for (int s : ex_->steps[si].reads) {
+        if (slots[s].first_step < 0) slots[s].first_step = si;
+        slots[s].last_step = si;
+      }
+    }
+    // Greedy first-fit over time: walk slots by first use, place each at the
+    // lowest offset that does not overlap a slot still alive.
+    std::vector<int> order;
+    for (int s = 0; s < (int)slots.size(); ++s)
+      if (slots[s].kind == SlotKind::Arena && slots[s].first_step >= 0) order.push_back(s);
+    std::sort(order.begin(), order.end(), [&](int a, int b) { return slots[a].first_step < slots[b].first_step; });
+    std::vector<int> placed;
+    int64_t top = 0;
+    for (int s : order) {
+      const int64_t size = align_up(std::max<int64_t>(slots[s].nbytes, 1), 256);
+      std::vector<std::pair<int64_t, int64_t>> busy;
+      for (int o : placed)
+        if (slots[o].last_step >= slots[s].first_step && slots[o].first_step <= slots[s].last_step)
+          busy.emplace_back(slots[o].offset, slots[o].offset + align_up(std::max<int64_t>(slots[o].nbytes, 1), 256));
+      std::sort(busy.begin(), busy.end());
+      int64_t off = 0;
+      for (auto& iv : busy) {
+        if (off + size <= iv.first) break;
+        off = std::max(off, iv.second);
+      }
+      slots[s].offset = off;
+      top = std::max(top, off + size);
+      placed.push_back(s);
+    }
+    ex_->arena_bytes = top;
+  }
+};
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+B200Exec b200_compile(B200Context ctx, const B200Value* feeds, int num_feeds, const B200Value* targets, int num_targets,
+                      B200Error* err) {
+  clear_error(err);
+  if (!ctx) { set_error(err, Status::Invalid("compile: null context")); return nullptr; }
+  Ctx* c = reinterpret_cast<Ctx*>(ctx);
+  if (num_targets < 1 || !targets) { set_error(err, Status::Invalid("compile: no outputs (Return was not called)")); return nullptr; }
+  std::vector<Node*> f, t;
+  auto own = [&](B200Value v) -> Node* {
+    Node* n = reinterpret_cast<Node*>(v);
+    if (!n || n->graph != &c->graph) return nullptr;
+    return n;
+  };
+  for (int i = 0; i < num_feeds; ++i) {
+    Node* n = own(feeds[i]);
+    if (!n) { set_error(err, Status::Invalid("compile: feed does not belong to this context")); return nullptr; }
+    f.push_back(n);
+  }
+  for (int i = 0; i < num_targets; ++i) {
+    Node* n = own(targets[i]);
+    if (!n) { set_error(err, Status::Invalid("compile: target does not belong to this context")); return nullptr; }
+    t.push_back(n);
+  }
+  std::unique_ptr<Exec> ex(new Exec());
+  ex->dev = c->dev;
+  Planner planner(c, ex.get());
+  Status s = planner.Run(f, t);
+  if (s.ok() && ex->arena_bytes > 0) s = ex->dev->Alloc(ex->arena_bytes, &ex->arena);
+  if (!s.ok()) { set_error(err, s); return nullptr; }
+  return ex.release();
+}
+
+void b200_destroy_exec(B200Exec exec) { delete reinterpret_cast<Exec*>(exec); }
+int b200_exec_device(B200Exec exec) { return exec ? reinterpret_cast<Exec*>(exec)->dev->ordinal() : -1; }
+int b200_exec_num_inputs(B200Exec exec) { return exec ? (int)reinterpret_cast<Exec*>(exec)->inputs.size() : -1; }
+int b200_exec_num_outputs(B200Exec exec) { return exec ? (int)reinterpret_cast<Exec*>(exec)->outputs.size() : -1; }
+static int desc_shape(const OutputDesc& d, int* dtype, int64_t* dims, int cap) {
+  if (dtype) *dtype = d.dtype;
+  for (int i = 0; i < (int)d.dims.size() && i < cap; ++i) dims[i] = d.dims[i];
+  return (int)d.dims.size();
+}
+int b200_exec_output_shape(B200Exec exec, int i, int* dtype, int64_t* dims, int cap) {
+  Exec* ex = reinterpret_cast<Exec*>(exec);
+  if (!ex || i < 0 || i >= (int)ex->outputs.size()) return -1;
+  return desc_shape(ex->outputs[i], dtype, dims, cap);
+}
+int b200_exec_input_shape(B200Exec exec, int i, int* dtype, int64_t* dims, int cap) {
+  Exec* ex = reinterpret_cast<Exec*>(exec);
+  if (!ex || i < 0 || i >= (int)ex->inputs.size()) return -1;
+  return desc_shape(ex->inputs[i], dtype, dims, cap);
+}
+int b200_exec_num_launches(B200Exec exec) { return exec ? reinterpret_cast<Exec*>(exec)->num_launches : -1; }
+int64_t b200_exec_arena_bytes(B200Exec exec) { return exec ? reinterpret_cast<Exec*>(exec)->arena_bytes : -1; }
+int64_t b200_exec_describe(B200Exec exec, char* buf, int64_t cap) {
+  Exec* ex = reinterpret_cast<Exec*>(exec);
+  if (!ex) return -1;
+  std::string s;
+  for (auto& st : ex->steps) s += st.desc + "\n";
+  if (buf && cap > 0) {
+    const int64_t n = std::min<int64_t>(cap - 1, (int64_t)s.size());
+    memcpy(buf, s.data(), (size_t)n);
+    buf[n] = 0;
+  }
+  return (int64_t)s.size();
+}
+
+bool b200_execute(B200Exec exec, const B200Buffer* inputs, int num_inputs, B200Buffer* outputs, int num_outputs, B200Error* err) {
+  clear_error(err);
+  Exec* ex = reinterpret_cast<Exec*>(exec);
+  if (!ex) { set_error(err, Status::Invalid("Execute: null executable")); return false; }
+  if (num_inputs != (int)ex->inputs.size()) {
+    set_error(err, Status::Invalid(strfmt("Execute: expected %d inputs, got %d", (int)ex->inputs.size(), num_inputs)));
+    return false;
+  }
+  if (num_outputs != (int)ex->outputs.size()) {
+    set_error(err, Status::Invalid(strfmt("Execute: expected %d outputs, got %d", (int)ex->outputs.size(), num_outputs)));
+    return false;
+  }
+  std::lock_guard<std::mutex> lock(ex->mu);  // executions of one executable are serialised (ref executable.go:25, 51)
+  std::vector<void*> ptrs(ex->slots.size(), nullptr);
+  for (int i = 0; i < num_inputs; ++i) {
+    Buffer* b = reinterpret_cast<Buffer*>(inputs[i]);
+    const OutputDesc& d = ex->inputs[i];
+    if (!b || !b->ptr) { set_error(err, Status::Invalid(strfmt("Execute: input %d is null or finalized", i))); return false; }
+    if (b->device != ex->dev->ordinal()) { set_error(err, Status::Invalid(strfmt("Execute: input %d lives on device %d, executable on %d", i, b->device, ex->dev->ordinal()))); return false; }
+    if (b->dtype != d.dtype || b->dims != d.dims) {
+      set_error(err, Status::Invalid(strfmt("Execute: input %d shape mismatch (buffer %s, expected %s)", i, dtype_name(b->dtype), dtype_name(d.dtype))));
+      return false;
+    }
+    ptrs[d.slot] = b->ptr;
+  }
+  std::vector<Buffer*> outs;
+  auto fail = [&](const Status& s) {
+    for (Buffer* b : outs) { ex->dev->Free(b->ptr); delete b; }
+    set_error(err, s);
+    return false;
+  };
+  for (int i = 0; i < num_outputs; ++i) {
+    const OutputDesc& d = ex->outputs[i];
+    Buffer* b = new Buffer();
+    b->device = ex->dev->ordinal();
+    b->dtype = d.dtype;
+    b->dims = d.dims;
+    b->nbytes = d.nbytes;
+    Status s = ex->dev->Alloc(d.nbytes > 0 ? d.nbytes : 1, &b->ptr);
+    outs.push_back(b);
+    if (!s.ok()) return fail(s);
+    ptrs[d.slot] = b->ptr;
+  }
+  for (size_t s = 0; s < ex->slots.size(); ++s) {
+    const Slot& sl = ex->slots[s];
+    if (sl.kind == SlotKind::Arena) ptrs[s] = (char*)ex->arena + sl.offset;
+    else if (sl.kind == SlotKind::Const) ptrs[s] = ex->const_ptrs[sl.index];
+  }
+  for (auto& st : ex->steps) {
+    Status s = st.run(ex->dev, ptrs.data());
+    if (!s.ok()) return fail(Status{s.code, st.desc + ": " + s.msg});
+  }
+  for (int i = 0; i < num_outputs; ++i) outputs[i] = outs[i];
+  return true;
+}
+
+}  // extern "C"

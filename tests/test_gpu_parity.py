@@ -1,0 +1,476 @@
+"""Parity of the CUDA path against the CPU oracle on seeded inputs, through the C ABI.
+
+Tolerances (stated by the target): bit-exact for integer, Bool and indexing results; rel 1e-5 for
+fp32; rel 2e-2 for bf16 contractions.  Float comparisons add a norm-relative term (atol_scale * rtol
+* rms(expected)) because the elementwise relative error of a zero-mean sum is unbounded.
+"""
+import ml_dtypes
+import numpy as np
+import pytest
+
+from tests.util import assert_parity, rng_array, run_backend
+
+pytestmark = pytest.mark.gpu
+
+BF16 = ml_dtypes.bfloat16
+F32_RTOL, BF16_RTOL = 1e-5, 2e-2
+
+
+# --------------------------------------------------------------------------- elementwise ---
+UNARY_F = ["Abs", "Neg", "Sqrt", "Rsqrt", "Exp", "Expm1", "Log", "Log1p", "Sin", "Cos", "Tanh", "Logistic", "Erf", "Floor", "Ceil",
+           "Round", "Sign", "Identity"]
+
+
+@pytest.mark.parametrize("op", UNARY_F)
+@pytest.mark.parametrize("dtype", [np.float32, BF16], ids=["f32", "bf16"])
+def test_unary_float(b200, backend, op, dtype):
+    rng = np.random.default_rng(1)
+    x = rng_array(rng, (37, 52), np.float32, 2.0)
+    if op in ("Sqrt", "Rsqrt", "Log"):
+        x = np.abs(x) + 0.1
+    if op == "Log1p":
+        x = np.abs(x)
+    x = x.astype(dtype)
+    rtol = 2e-5 if dtype == np.float32 else 8e-3   # bf16: half an ulp is 2^-9
+    assert_parity(b200, backend, lambda f, a: getattr(f, op)(a), [x], rtol=rtol, atol_scale=1.0 if op in ("Expm1", "Log1p", "Sin", "Cos") else 0.01, what=op)
+
+
+def test_round_ties_to_even(b200, backend):
+    x = np.array([0.5, 1.5, 2.5, -0.5, -1.5, 3.5000002, 2.4999998], dtype=np.float32)
+    got = run_backend(b200, backend, lambda f, a: f.Round(a), [x])[0]
+    np.testing.assert_array_equal(got, np.rint(x))
+
+
+BINARY_F = ["Add", "Sub", "Mul", "Div", "Max", "Min", "Pow", "Atan2", "Rem"]
+
+
+@pytest.mark.parametrize("op", BINARY_F)
+def test_binary_float_broadcast(b200, backend, op):
+    rng = np.random.default_rng(2)
+    a = rng_array(rng, (5, 1, 33), np.float32)
+    b = rng_array(rng, (7, 33), np.float32)
+    if op == "Pow":
+        a = np.abs(a) + 0.5
+    if op in ("Div", "Rem"):
+        b = np.where(np.abs(b) < 0.1, 0.5, b).astype(np.float32)
+    assert_parity(b200, backend, lambda f, x, y: getattr(f, op)(x, y), [a, b], rtol=3e-5 if op == "Pow" else F32_RTOL,
+                  atol_scale=1.0 if op == "Rem" else 0.0, what=op)
+
+
+@pytest.mark.parametrize("dtype", [np.int8, np.int16, np.int32, np.int64, np.uint8, np.uint16, np.uint32, np.uint64])
+@pytest.mark.parametrize("op", ["Add", "Sub", "Mul", "Div", "Rem", "Max", "Min", "BitwiseAnd", "BitwiseOr", "BitwiseXor"])
+def test_binary_integer_exact(b200, backend, dtype, op):
+    rng = np.random.default_rng(3)
+    a = rng_array(rng, (64,), dtype)
+    b = rng_array(rng, (64,), dtype)
+    b[::7] = 0  # division by zero is defined: quotient all-ones, remainder the dividend
+    assert_parity(b200, backend, lambda f, x, y: getattr(f, op)(x, y), [a, b], what=f"{op}/{np.dtype(dtype).name}")
+
+
+@pytest.mark.parametrize("dtype", [np.int32, np.uint8, np.int64])
+@pytest.mark.parametrize("op", ["ShiftLeft", "ShiftRightArithmetic", "ShiftRightLogical"])
+def test_shifts_exact(b200, backend, dtype, op):
+    rng = np.random.default_rng(4)
+    a = rng_array(rng, (40,), dtype)
+    s = rng.integers(0, np.dtype(dtype).itemsize * 8 + 3, size=40).astype(dtype)
+    assert_parity(b200, backend, lambda f, x, y: getattr(f, op)(x, y), [a, s], what=op)
+
+
+@pytest.mark.parametrize("op", ["Equal", "NotEqual", "LessThan", "LessOrEqual", "GreaterThan", "GreaterOrEqual"])
+@pytest.mark.parametrize("dtype", [np.float32, np.int32, BF16], ids=["f32", "i32", "bf16"])
+def test_compare_exact(b200, backend, op, dtype):
+    rng = np.random.default_rng(5)
+    a = rng.integers(-3, 4, size=(9, 31)).astype(np.float32).astype(dtype)
+    b = rng.integers(-3, 4, size=(31,)).astype(np.float32).astype(dtype)
+    assert_parity(b200, backend, lambda f, x, y: getattr(f, op)(x, y), [a, b], what=op)
+
+
+def test_logical_ops_exact(b200, backend):
+    rng = np.random.default_rng(6)
+    a, b = rng_array(rng, (50,), np.bool_), rng_array(rng, (50,), np.bool_)
+    for op in ("LogicalAnd", "LogicalOr", "LogicalXor"):
+        assert_parity(b200, backend, lambda f, x, y: getattr(f, op)(x, y), [a, b], what=op)
+    assert_parity(b200, backend, lambda f, x: f.LogicalNot(x), [a], what="LogicalNot")
+
+
+def test_isfinite_isnan(b200, backend):
+    x = np.array([0.0, np.inf, -np.inf, np.nan, 1.5, -2.0], dtype=np.float32)
+    assert_parity(b200, backend, lambda f, a: (f.IsFinite(a), f.IsNaN(a)), [x])
+
+
+def test_where_clamp(b200, backend):
+    rng = np.random.default_rng(7)
+    c = rng_array(rng, (6, 20), np.bool_)
+    a, b = rng_array(rng, (6, 20), np.float32), rng_array(rng, (20,), np.float32)
+    assert_parity(b200, backend, lambda f, cc, x, y: f.Where(cc, x, f.BroadcastInDim(y, _S(b200, np.float32, 6, 20), [1])), [c, a, b])
+    lo, hi = np.array(-0.5, dtype=np.float32), np.array(0.25, dtype=np.float32)
+    assert_parity(b200, backend, lambda f, l, x, h: f.Clamp(l, x, h), [lo, a, hi])
+
+
+def _S(b200, dtype, *dims):
+    return b200.Shape(b200.dtypes.from_numpy(np.dtype(dtype)), dims)
+
+
+@pytest.mark.parametrize("src,dst", [(np.float32, np.int32), (np.float32, np.int8), (np.float32, np.uint8), (np.float32, np.int64),
+                                     (np.int32, np.float32), (np.int64, np.float32), (np.float32, BF16), (BF16, np.float32),
+                                     (np.int32, np.int8), (np.uint8, np.int32), (np.float32, np.bool_), (np.int32, np.bool_),
+                                     (np.float32, np.float64), (np.float64, np.float32), (np.float32, np.float16)])
+def test_convert_dtype(b200, backend, src, dst):
+    rng = np.random.default_rng(8)
+    x = rng_array(rng, (300,), src, 100.0)
+    if np.dtype(src).kind == "f" or np.dtype(src) == np.dtype(BF16):
+        x[:4] = np.array([1e10, -1e10, 0.0, -0.0], dtype=np.float32).astype(src)
+    assert_parity(b200, backend, lambda f, a: f.ConvertDType(a, b200.dtypes.from_numpy(np.dtype(dst))), [x], rtol=0.0, what=f"{src}->{dst}")
+
+
+def test_fused_chain_is_one_launch(b200, backend):
+    rng = np.random.default_rng(9)
+    x, w, b = rng_array(rng, (64, 128), np.float32), rng_array(rng, (128,), np.float32), rng_array(rng, (128,), np.float32)
+
+    def build(f, xx, ww, bb):
+        s = _S(b200, np.float32, 64, 128)
+        return f.Tanh(f.Add(f.Mul(xx, f.BroadcastInDim(ww, s, [1])), f.BroadcastInDim(bb, s, [1])))
+
+    (got,), plan = run_backend(b200, backend, build, [x, w, b], describe=True)
+    assert plan.count("\n") == 1 and plan.startswith("ewise["), plan
+    want = np.tanh((x.astype(np.float64) * w + b).astype(np.float32).astype(np.float64)).astype(np.float32)
+    np.testing.assert_allclose(got, want, rtol=2e-5, atol=1e-6)
+
+
+def test_bf16_chain_rounds_after_every_op(b200, backend):
+    # a fused chain must equal the op-by-op result, so 16-bit intermediates are re-rounded
+    rng = np.random.default_rng(10)
+    a, b, c = (rng_array(rng, (1000,), BF16) for _ in range(3))
+    assert_parity(b200, backend, lambda f, x, y, z: f.Mul(f.Add(x, y), z), [a, b, c], rtol=0.0, what="bf16 chain")
+
+
+def test_iota_inside_chain_and_causal_mask_from_primitives(b200, backend):
+    # the reference's SDPA builds its causal mask from two Int32 iotas and GreaterOrEqual (function.go:2777-2794)
+    S = 19
+    x = rng_array(np.random.default_rng(11), (3, S, S), np.float32)
+
+    def build(f, s):
+        shp = _S(b200, np.int32, S, S)
+        keep = f.GreaterOrEqual(f.Iota(shp, 0), f.Iota(shp, 1))
+        keep3 = f.BroadcastInDim(keep, _S(b200, np.bool_, 3, S, S), [1, 2])
+        neg = f.BroadcastInDim(f.Constant(np.array([-np.inf], dtype=np.float32), 1), _S(b200, np.float32, 3, S, S), [2])
+        return f.FusedSoftmax(f.Where(keep3, s, neg), 2)
+
+    assert_parity(b200, backend, build, [x], rtol=F32_RTOL, atol_scale=0.01)
+
+
+# ------------------------------------------------------------------------ data movement ---
+@pytest.mark.parametrize("perm", [(1, 0), (0, 2, 1), (2, 0, 1), (0, 2, 1, 3), (3, 2, 1, 0)])
+@pytest.mark.parametrize("dtype", [np.float32, BF16, np.int8, np.int64], ids=["f32", "bf16", "i8", "i64"])
+def test_transpose_exact(b200, backend, perm, dtype):
+    dims = (6, 10, 7, 16)[:len(perm)]
+    x = rng_array(np.random.default_rng(12), dims, dtype)
+    assert_parity(b200, backend, lambda f, a: f.Transpose(a, *perm), [x], what=f"Transpose{perm}")
+
+
+def test_slice_reverse_concat_pad_broadcast_exact(b200, backend):
+    rng = np.random.default_rng(13)
+    x = rng_array(rng, (9, 12, 8), np.float32)
+    y = rng_array(rng, (9, 5, 8), np.float32)
+    assert_parity(b200, backend, lambda f, a: f.Slice(a, [1, 2, 0], [9, 11, 8], [2, 3, 1]), [x])
+    assert_parity(b200, backend, lambda f, a: f.Reverse(a, 0, 2), [x])
+    assert_parity(b200, backend, lambda f, a, b: f.Concatenate(1, a, b, a), [x, y])
+    assert_parity(b200, backend, lambda f, a: f.Pad(a, f.Constant(np.array([7.0], dtype=np.float32)), (1, 2), (0, 0), (3, 0)), [x])
+    assert_parity(b200, backend, lambda f, a: f.BroadcastInDim(a, _S(b200, np.float32, 4, 9, 5, 8), [1, 2, 3]), [y])
+    # movement feeding arithmetic is folded into the consumer
+    assert_parity(b200, backend, lambda f, a: f.Add(f.Transpose(a, 2, 1, 0), f.Transpose(a, 2, 1, 0)), [x], rtol=0.0)
+
+
+def test_empty_and_scalar_shapes(b200, backend):
+    s = np.array(3.5, dtype=np.float32)
+    assert_parity(b200, backend, lambda f, a: f.Mul(a, a), [s], rtol=0.0)
+    e = np.zeros((0, 4), dtype=np.float32)
+    got = run_backend(b200, backend, lambda f, a: f.Exp(a), [e])[0]
+    assert got.shape == (0, 4)
+    got = run_backend(b200, backend, lambda f, a: f.ReduceSum(a, 0), [e])[0]
+    np.testing.assert_array_equal(got, np.zeros(4, dtype=np.float32))
+
+
+# --------------------------------------------------------------------------- reductions ---
+@pytest.mark.parametrize("op", ["ReduceSum", "ReduceMax", "ReduceMin", "ReduceProduct"])
+@pytest.mark.parametrize("axes", [(), (0,), (1,), (2,), (0, 2), (1, 2), (0, 1, 2)])
+def test_reduce_float(b200, backend, op, axes):
+    x = rng_array(np.random.default_rng(14), (7, 33, 20), np.float32, 0.9 if op == "ReduceProduct" else 1.0)
+    if op == "ReduceProduct":
+        x = (1.0 + 0.01 * x).astype(np.float32)
+    assert_parity(b200, backend, lambda f, a: getattr(f, op)(a, *axes), [x], rtol=2e-5, atol_scale=1.0, what=f"{op}{axes}")
+
+
+def test_reduce_large_uses_split_path(b200, backend):
+    x = rng_array(np.random.default_rng(15), (3, 200_000), np.float32)
+    (got,), plan = run_backend(b200, backend, lambda f, a: f.ReduceSum(a, 1), [x], describe=True)
+    assert "split" in plan
+    np.testing.assert_allclose(got, x.astype(np.float64).sum(axis=1), rtol=1e-5, atol=1e-2)
+    x2 = rng_array(np.random.default_rng(16), (50_000, 6), np.float32)
+    assert_parity(b200, backend, lambda f, a: f.ReduceMax(a, 0), [x2], rtol=0.0)
+
+
+@pytest.mark.parametrize("dtype", [np.int32, np.int64, np.uint8, np.int8])
+def test_reduce_integer_exact(b200, backend, dtype):
+    x = rng_array(np.random.default_rng(17), (11, 300), dtype)
+    for op in ("ReduceSum", "ReduceMax", "ReduceMin"):
+        assert_parity(b200, backend, lambda f, a: getattr(f, op)(a, 1), [x], what=op)
+
+
+def test_reduce_logical(b200, backend):
+    x = rng_array(np.random.default_rng(18), (9, 40), np.bool_)
+    x[3] = True
+    x[5] = False
+    assert_parity(b200, backend, lambda f, a: (f.ReduceLogicalAnd(a, 1), f.ReduceLogicalOr(a, 1)), [x])
+
+
+@pytest.mark.parametrize("axis", [0, 1, 2])
+@pytest.mark.parametrize("is_min", [False, True])
+@pytest.mark.parametrize("dtype", [np.float32, BF16, np.int32], ids=["f32", "bf16", "i32"])
+def test_argminmax_exact(b200, backend, axis, is_min, dtype):
+    x = rng_array(np.random.default_rng(19), (6, 301, 5), dtype)
+    assert_parity(b200, backend, lambda f, a: f.ArgMinMax(a, axis, b200.dtypes.Int32, is_min), [x])
+
+
+def test_argmax_ties_and_nan(b200, backend):
+    x = np.array([[1, 7, 7, 3], [np.nan, 9, np.nan, 2], [5, 5, 5, 5]], dtype=np.float32)
+    got = run_backend(b200, backend, lambda f, a: f.ArgMinMax(a, 1, b200.dtypes.Int64, False), [x])[0]
+    np.testing.assert_array_equal(got, np.array([1, 0, 0], dtype=np.int64))  # lowest index on ties; first NaN wins
+
+
+def test_argmax_vocab_sized_rows(b200, backend):
+    x = rng_array(np.random.default_rng(20), (4, 50257), np.float32)
+    assert_parity(b200, backend, lambda f, a: f.ArgMinMax(a, -1 + 2, b200.dtypes.Int32, False), [x])
+
+
+# ------------------------------------------------------------------------------- gather ---
+def test_gather_embedding_rows_bf16(b200, backend):
+    rng = np.random.default_rng(21)
+    table = rng_array(rng, (1000, 768), BF16)
+    ids = rng.integers(0, 1000, size=(4, 33, 1)).astype(np.int32)
+    (got,), plan = run_backend(b200, backend, lambda f, t, i: f.Gather(t, i, 2, [2], [0], [0], [1, 768], False), [table, ids], describe=True)
+    assert "gather_rows" in plan
+    np.testing.assert_array_equal(got.view(np.uint16), table[ids[..., 0]].view(np.uint16))
+
+
+def test_gather_clamps_out_of_range(b200, backend):
+    table = np.arange(12, dtype=np.float32).reshape(4, 3)
+    ids = np.array([[-5], [99], [2]], dtype=np.int32)
+    assert_parity(b200, backend, lambda f, t, i: f.Gather(t, i, 1, [1], [0], [0], [1, 3], False), [table, ids])
+
+
+def test_gather_general_windows(b200, backend):
+    rng = np.random.default_rng(22)
+    op = rng_array(rng, (6, 7, 8), np.float32)
+    idx = rng.integers(0, 5, size=(5, 2)).astype(np.int32)
+    # windows of [2, 7, 3] starting at (i, *, j)
+    assert_parity(b200, backend, lambda f, t, i: f.Gather(t, i, 1, [1, 2, 3], [], [0, 2], [2, 7, 3], False), [op, idx])
+
+
+# ----------------------------------------------------------------------------- softmax ---
+@pytest.mark.parametrize("shape,axis", [((33, 1024), 1), ((5, 7, 96), 2), ((4, 50257), 1), ((6, 100, 12), 1), ((3, 4096), 1), ((2, 20000), 1),
+                                        ((8, 17), 1)])
+@pytest.mark.parametrize("dtype", [np.float32, BF16], ids=["f32", "bf16"])
+def test_softmax(b200, backend, shape, axis, dtype):
+    x = rng_array(np.random.default_rng(23), shape, dtype, 2.0)
+    rtol = F32_RTOL if dtype == np.float32 else 8e-3
+    assert_parity(b200, backend, lambda f, a: f.FusedSoftmax(a, axis), [x], rtol=rtol, atol_scale=0.01, what=f"softmax{shape}")
+
+
+@pytest.mark.parametrize("sq,sk", [(64, 64), (128, 1024), (100, 100), (1024, 1024)])
+def test_softmax_causal(b200, backend, sq, sk):
+    x = rng_array(np.random.default_rng(24), (2, 3, sq, sk), np.float32, 2.0)
+    got = assert_parity(b200, backend, lambda f, a: f.FusedSoftmaxMasked(a, 0.125, True, None), [x], rtol=F32_RTOL, atol_scale=0.01)[0]
+    # masked positions are exactly zero, rows sum to one
+    iu = np.triu_indices(sq, 1, sk)
+    assert (got[..., iu[0], iu[1]] == 0).all()
+    np.testing.assert_allclose(got.sum(-1), 1.0, rtol=1e-5)
+
+
+def test_softmax_masks(b200, backend):
+    rng = np.random.default_rng(25)
+    x = rng_array(rng, (2, 3, 40, 48), np.float32)
+    bm = rng.integers(0, 4, size=(2, 1, 40, 48)) > 0
+    bm[..., 0] = True
+    fm = rng_array(rng, (40, 48), np.float32)
+    assert_parity(b200, backend, lambda f, a, m: f.FusedSoftmaxMasked(a, 1.0, False, m), [x, bm], rtol=F32_RTOL, atol_scale=0.01)
+    assert_parity(b200, backend, lambda f, a, m: f.FusedSoftmaxMasked(a, 0.5, True, m), [x, fm], rtol=F32_RTOL, atol_scale=0.01)
+    # a fully masked row is NaN (IEEE), as the oracle defines
+    bm2 = bm.copy()
+    bm2[0, 0, 5, :] = False
+    assert_parity(b200, backend, lambda f, a, m: f.FusedSoftmaxMasked(a, 1.0, False, m), [x, bm2], rtol=F32_RTOL, atol_scale=0.01)
+
+
+# ------------------------------------------------------------------------------- norms ---
+@pytest.mark.parametrize("rows,cols", [(64, 4096), (33, 768), (17, 2048), (5, 100), (3, 16384), (2, 40000), (9, 8)])
+@pytest.mark.parametrize("dtype", [np.float32, BF16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("kind", ["layer", "rms"])
+def test_norms(b200, backend, rows, cols, dtype, kind):
+    rng = np.random.default_rng(26)
+    x = rng_array(rng, (rows, cols), dtype)
+    g = (1.0 + 0.02 * rng.standard_normal(cols)).astype(np.float32).astype(dtype)
+    b = (0.1 * rng.standard_normal(cols)).astype(np.float32).astype(dtype)
+    rtol = 2e-5 if dtype == np.float32 else 8e-3
+    if kind == "layer":
+        assert_parity(b200, backend, lambda f, a, gg, bb: f.FusedLayerNorm(a, [-1], 1e-6, gg, bb), [x, g, b], rtol=rtol, atol_scale=0.05)
+    else:
+        assert_parity(b200, backend, lambda f, a, gg: f.FusedRMSNorm(a, [-1], 1e-6, gg), [x, g], rtol=rtol, atol_scale=0.05)
+
+
+def test_layer_norm_axes_and_param_shapes(b200, backend):
+    rng = np.random.default_rng(27)
+    x = rng_array(rng, (4, 6, 10), np.float32)
+    g2 = rng_array(rng, (6, 10), np.float32)
+    assert_parity(b200, backend, lambda f, a, g: f.FusedLayerNorm(a, [1, 2], 1e-5, g, None), [x, g2], rtol=2e-5, atol_scale=0.05)
+    assert_parity(b200, backend, lambda f, a: f.FusedLayerNorm(a, [1], 1e-5, None, None), [x], rtol=2e-5, atol_scale=0.05)   # non-trailing axis
+    g_full = rng_array(rng, (1, 1, 10), np.float32)
+    assert_parity(b200, backend, lambda f, a, g: f.FusedLayerNorm(a, [-1], 1e-5, g, g), [x, g_full], rtol=2e-5, atol_scale=0.05)
+    g_rows = rng_array(rng, (4, 1, 10), np.float32)  # varies off the normalised axis -> split into norm + mul
+    assert_parity(b200, backend, lambda f, a, g: f.FusedLayerNorm(a, [-1], 1e-5, g, None), [x, g_rows], rtol=2e-5, atol_scale=0.05)
+
+
+def test_gelu_both_forms(b200, backend):
+    x = rng_array(np.random.default_rng(28), (1000,), np.float32, 2.0)
+    assert_parity(b200, backend, lambda f, a: f.FusedGelu(a, True), [x], rtol=2e-5, atol_scale=0.01)
+    assert_parity(b200, backend, lambda f, a: f.FusedGelu(a, False), [x], rtol=2e-5, atol_scale=0.01)
+
+
+# -------------------------------------------------------------------------- DotGeneral ---
+def _dot_tol(dtype):
+    return (F32_RTOL, 1.0) if dtype == np.float32 else (BF16_RTOL, 1.0)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, BF16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("form", ["BMK_BKN", "BKM_BKN", "BMK_BNK", "BKM_BNK"])
+@pytest.mark.parametrize("B,M,N,K", [(1, 2, 2, 3), (2, 64, 48, 40), (3, 130, 70, 257), (2, 256, 256, 128), (1, 512, 384, 1024)])
+def test_dot_general_forms(b200, backend, dtype, form, B, M, N, K):
+    rng = np.random.default_rng(29)
+    a = rng_array(rng, (B, M, K) if form.startswith("BMK") else (B, K, M), dtype)
+    b = rng_array(rng, (B, K, N) if form.endswith("BKN") else (B, N, K), dtype)
+    lc = [2] if form.startswith("BMK") else [1]
+    rc = [1] if form.endswith("BKN") else [2]
+    rtol, ascale = _dot_tol(dtype)
+    assert_parity(b200, backend, lambda f, x, y: f.DotGeneral(x, lc, [0], y, rc, [0]), [a, b], rtol=rtol, atol_scale=ascale, what=form)
+
+
+def test_dot_general_needs_operand_copy(b200, backend):
+    rng = np.random.default_rng(30)
+    a = rng_array(rng, (5, 3, 7, 4), np.float32)   # [m1, b, k, m2]
+    b = rng_array(rng, (7, 3, 6), np.float32)      # [k, b, n]
+    assert_parity(b200, backend, lambda f, x, y: f.DotGeneral(x, [2], [1], y, [0], [1]), [a, b], rtol=F32_RTOL, atol_scale=1.0)
+    c = rng_array(rng, (4, 5, 6), np.float32)
+    d = rng_array(rng, (6, 5, 3), np.float32)
+    assert_parity(b200, backend, lambda f, x, y: f.DotGeneral(x, [1, 2], [], y, [1, 0], []), [c, d], rtol=F32_RTOL, atol_scale=1.0)
+
+
+@pytest.mark.parametrize("dtype", [np.int32, np.int64, np.float64])
+def test_dot_general_other_dtypes(b200, backend, dtype):
+    rng = np.random.default_rng(31)
+    a, b = rng_array(rng, (9, 20), dtype), rng_array(rng, (20, 11), dtype)
+    assert_parity(b200, backend, lambda f, x, y: f.DotGeneral(x, [1], [], y, [0], []), [a, b], rtol=1e-12, atol_scale=1.0)
+
+
+@pytest.mark.parametrize("act", [0, 1, 2, 3, 4])
+@pytest.mark.parametrize("dtype", [np.float32, BF16], ids=["f32", "bf16"])
+def test_fused_dense(b200, backend, act, dtype):
+    rng = np.random.default_rng(32)
+    x, w, b = rng_array(rng, (4, 50, 96), dtype), rng_array(rng, (96, 160), dtype, 0.1), rng_array(rng, (160,), dtype)
+    rtol, ascale = _dot_tol(dtype)
+    assert_parity(b200, backend, lambda f, xx, ww, bb: f.FusedDense(xx, ww, bb, act), [x, w, b], rtol=rtol, atol_scale=ascale)
+
+
+@pytest.mark.parametrize("layout", [0, 1])
+@pytest.mark.parametrize("heads,kv_heads", [(4, 4), (8, 2)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_sdpa(b200, backend, layout, heads, kv_heads, causal):
+    rng = np.random.default_rng(33)
+    B, S, D = 2, 48, 16
+    shp = lambda h: (B, h, S, D) if layout == 0 else (B, S, h, D)
+    q, k, v = rng_array(rng, shp(heads), np.float32), rng_array(rng, shp(kv_heads), np.float32), rng_array(rng, shp(kv_heads), np.float32)
+    assert_parity(b200, backend,
+                  lambda f, qq, kk, vv: f.FusedScaledDotProductAttention(qq, kk, vv, None, heads, kv_heads, layout, 0.25, causal),
+                  [q, k, v], rtol=2e-5, atol_scale=1.0)
+
+
+def test_qkv_projection(b200, backend):
+    rng = np.random.default_rng(34)
+    x, w = rng_array(rng, (3, 10, 32), np.float32), rng_array(rng, (32, 64 + 2 * 16), np.float32, 0.2)
+    bq, bk, bv = rng_array(rng, (64,), np.float32), rng_array(rng, (16,), np.float32), rng_array(rng, (16,), np.float32)
+    assert_parity(b200, backend, lambda f, xx, ww, a, b, c: f.FusedAttentionQKVProjection(xx, ww, a, b, c, 64, 16), [x, w, bq, bk, bv],
+                  rtol=F32_RTOL, atol_scale=1.0)
+
+
+# ----------------------------------------------------------------- boundary behaviour ---
+def test_error_behaviour_matches_the_reference(b200, backend):
+    builder = backend.Builder("errors")
+    f = builder.Main()
+    x = f.Parameter("x", b200.shapes.Make(b200.dtypes.Float32, 2, 3))
+    w = f.Parameter("w", b200.shapes.Make(b200.dtypes.Float32, 4, 5))
+    with pytest.raises(b200.BackendError, match="must match weight's first dim"):   # ref function.go:2582-2585
+        f.FusedDense(x, w, None, 0)
+    with pytest.raises(b200.BackendError, match="unsupported activation"):          # ref function.go:2662
+        f.FusedDense(x, f.Parameter("w2", b200.shapes.Make(b200.dtypes.Float32, 3, 5)), None, 17)
+    with pytest.raises(b200.BackendError, match="out of range"):                      # ref function.go:2423-2425
+        f.FusedLayerNorm(x, [5], 1e-5, None, None)
+    with pytest.raises(b200.BackendError, match="rank 4"):                            # ref function.go:2690-2692
+        f.FusedScaledDotProductAttention(x, x, x, None, 1, 1, 0, 1.0, False)
+    with pytest.raises(b200.BackendError, match="no outputs"):                        # ref builder.go:79-81
+        builder.Compile()
+    other = backend.Builder("other").Main()
+    with pytest.raises(b200.BackendError, match="unrelated function scope"):          # ref function.go:194
+        f.Add(x, other.Parameter("y", b200.shapes.Make(b200.dtypes.Float32, 2, 3)))
+    f.Return([f.Add(x, x)], None)
+    exe = builder.Compile()
+    with pytest.raises(b200.BackendError, match="already been compiled"):             # ref builder.go:73-75
+        builder.Compile()
+    with pytest.raises(b200.BackendError, match="expected 2 inputs"):                 # ref executable.go:55-58
+        exe.Execute([], None, 0)
+    bad = backend.FromNumpy(np.zeros((3, 2), dtype=np.float32))
+    good = backend.FromNumpy(np.zeros((4, 5), dtype=np.float32))
+    with pytest.raises(b200.BackendError, match="shape mismatch"):                    # ref executable.go:66-72
+        exe.Execute([bad, good], None, 0)
+    backend.BufferFinalize(bad)
+    with pytest.raises(b200.BackendError, match="finalized"):
+        backend.BufferShape(bad)
+    assert backend.HasSharedBuffers() is False
+    with pytest.raises(b200.BackendError):
+        backend.NewSharedBuffer(0, b200.shapes.Make(b200.dtypes.Float32, 2))
+
+
+def test_execute_host_matches_device_path(b200, backend):
+    rng = np.random.default_rng(35)
+    x = rng_array(rng, (64, 256), np.float32)
+    builder = backend.Builder("host")
+    f = builder.Main()
+    p = f.Parameter("x", b200.shapes.Make(b200.dtypes.Float32, 64, 256))
+    f.Return([f.FusedSoftmax(p, 1), f.ReduceSum(p, 1)], None)
+    exe = builder.Compile()
+    host = exe.ExecuteHost([x])
+    buf = backend.FromNumpy(x)
+    dev = [backend.ToNumpy(b) for b in exe.Execute([buf], None, 0)]
+    for h, d in zip(host, dev):
+        np.testing.assert_array_equal(h, d)
+
+
+def test_buffer_round_trip_and_scalar(b200, backend):
+    for arr in (np.arange(24, dtype=np.int16).reshape(2, 3, 4), np.array(2.5, dtype=np.float64), np.zeros((0,), dtype=np.float32)):
+        buf = backend.FromNumpy(arr)
+        assert backend.BufferShape(buf).Dimensions == list(arr.shape)
+        assert backend.BufferDeviceNum(buf) == 0
+        np.testing.assert_array_equal(backend.ToNumpy(buf), arr)
+        backend.BufferFinalize(buf)
+
+
+def test_intermediates_share_arena_memory(b200, backend):
+    # a chain of unfusable ops must not grow memory linearly: dead intermediates are reused
+    builder = backend.Builder("arena")
+    f = builder.Main()
+    x = f.Parameter("x", b200.shapes.Make(b200.dtypes.Float32, 256, 256))
+    v = x
+    for _ in range(8):
+        v = f.FusedSoftmax(v, 1)
+    f.Return([v], None)
+    exe = builder.Compile()
+    one = 256 * 256 * 4
+    assert b200.lib().b200_exec_arena_bytes(exe.handle) <= 2 * one + 1024
+    assert exe.NumLaunches() == 8
