@@ -282,7 +282,9 @@ class Backend:
         _check(err, "Synchronize")
 
     def FromNumpy(self, array: np.ndarray, device_num: Optional[int] = None) -> Buffer:
-        array = np.ascontiguousarray(array)
+        array = np.asarray(array)  # (ascontiguousarray would turn a 0-d array into shape (1,))
+        if not array.flags["C_CONTIGUOUS"]:
+            array = array.copy()
         return self.BufferFromFlatData(self._device if device_num is None else device_num, array.reshape(-1),
                                        Shape(dtypes.from_numpy(array.dtype), array.shape))
 

@@ -409,7 +409,7 @@ def test_error_behaviour_matches_the_reference(b200, backend):
     with pytest.raises(b200.BackendError, match="must match weight's first dim"):   # ref function.go:2582-2585
         f.FusedDense(x, w, None, 0)
     with pytest.raises(b200.BackendError, match="unsupported activation"):          # ref function.go:2662
-        f.FusedDense(x, f.Parameter("w2", b200.shapes.Make(b200.dtypes.Float32, 3, 5)), None, 17)
+        f.FusedDense(x, f.Constant(np.zeros(15, dtype=np.float32), 3, 5), None, 17)
     with pytest.raises(b200.BackendError, match="out of range"):                      # ref function.go:2423-2425
         f.FusedLayerNorm(x, [5], 1e-5, None, None)
     with pytest.raises(b200.BackendError, match="rank 4"):                            # ref function.go:2690-2692
