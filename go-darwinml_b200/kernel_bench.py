@@ -1,0 +1,142 @@
+"""Times ONE kernel of libb200mlx.so through its direct C-ABI entry point.
+
+  python go-darwinml_b200/kernel_bench.py softmax  --rows 65536 --cols 1024 --dtype f32 [--causal] [--iters 20]
+  python go-darwinml_b200/kernel_bench.py rmsnorm  --rows 16384 --cols 4096 --dtype bf16
+  python go-darwinml_b200/kernel_bench.py layernorm --rows 16384 --cols 4096 --dtype bf16
+  python go-darwinml_b200/kernel_bench.py gemm --batch 8 --m 4096 --n 4096 --k 4096 --dtype bf16 [--a-km] [--b-nk]
+
+Inputs are seeded random tensors resident in HBM; timing is CUDA events on the
+library's stream after warm-up; between timed launches an L2-sized buffer is
+rewritten unless the operands exceed L2 anyway.  Prints one JSON line with the
+mean launch time, the achieved GB/s (algorithmic bytes) or TFLOP/s, and the
+fraction of the measured peak when MEASURED_PEAKS.json is present.  Small shapes
+of this tool are what the ncu captures under profiles/ were taken on.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+DT = {"f32": (7, 4), "bf16": (6, 2), "f16": (5, 2)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["softmax", "rmsnorm", "layernorm", "gemm"])
+    ap.add_argument("--rows", type=int, default=65536)
+    ap.add_argument("--cols", type=int, default=1024)
+    ap.add_argument("--seq-q", type=int, default=0)
+    ap.add_argument("--causal", action="store_true")
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--a-km", action="store_true", help="A stored [batch, K, M]")
+    ap.add_argument("--b-nk", action="store_true", help="B stored [batch, N, K]")
+    ap.add_argument("--dtype", default="f32", choices=list(DT))
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--device", type=int, default=0)
+    ap.add_argument("--no-flush", action="store_true")
+    args = ap.parse_args()
+
+    import torch
+
+    import go_darwinml_b200 as b200
+    from go_darwinml_b200 import _lib as libmod
+
+    backend = b200.New(f"device={args.device}")
+    L = b200.lib()
+    code, es = DT[args.dtype]
+    torch.cuda.set_device(args.device)
+    err = libmod.B200Error()
+    stream = torch.cuda.ExternalStream(L.b200_device_stream(args.device, ctypes.byref(err)), device=args.device)
+    tdt = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[args.dtype]
+    gen = torch.Generator(device=f"cuda:{args.device}").manual_seed(0)
+
+    def rand(*shape, scale=1.0):
+        return (torch.randn(*shape, generator=gen, device=f"cuda:{args.device}", dtype=torch.float32) * scale).to(tdt)
+
+    def check(ok, e):
+        if not ok:
+            raise RuntimeError(L.take_string(e.message))
+
+    if args.kernel == "softmax":
+        x, y = rand(args.rows, args.cols, scale=2.0), torch.empty(args.rows, args.cols, device=f"cuda:{args.device}", dtype=tdt)
+        seq_q = args.seq_q or min(args.rows, args.cols)
+        work, unit, kind = 2 * args.rows * args.cols * es, "GB/s", "hbm"
+        operand_bytes = work
+
+        def launch():
+            e = libmod.B200Error()
+            check(L.b200_k_softmax(args.device, x.data_ptr(), y.data_ptr(), args.rows, args.cols, code, 1.0, int(args.causal), seq_q,
+                                   ctypes.byref(e)), e)
+    elif args.kernel in ("rmsnorm", "layernorm"):
+        x, y = rand(args.rows, args.cols), torch.empty(args.rows, args.cols, device=f"cuda:{args.device}", dtype=tdt)
+        g, b = (1 + 0.02 * rand(args.cols).float()).to(tdt), torch.zeros(args.cols, device=f"cuda:{args.device}", dtype=tdt)
+        work, unit, kind = 2 * args.rows * args.cols * es, "GB/s", "hbm"
+        operand_bytes = work
+
+        def launch():
+            e = libmod.B200Error()
+            if args.kernel == "rmsnorm":
+                check(L.b200_k_rms_norm(args.device, x.data_ptr(), g.data_ptr(), y.data_ptr(), args.rows, args.cols, code, 1e-6, ctypes.byref(e)), e)
+            else:
+                check(L.b200_k_layer_norm(args.device, x.data_ptr(), g.data_ptr(), b.data_ptr(), y.data_ptr(), args.rows, args.cols, code, 1e-6,
+                                          ctypes.byref(e)), e)
+    else:
+        B, M, N, K = args.batch, args.m, args.n, args.k
+        a = rand(B, K, M) if args.a_km else rand(B, M, K)
+        bb = rand(B, N, K) if args.b_nk else rand(B, K, N)
+        c = torch.empty(B, M, N, device=f"cuda:{args.device}", dtype=tdt)
+        work, unit, kind = 2 * B * M * N * K, "TFLOP/s", "tensor"
+        operand_bytes = (a.numel() + bb.numel() + c.numel()) * es
+
+        def launch():
+            e = libmod.B200Error()
+            check(L.b200_k_gemm(args.device, a.data_ptr(), bb.data_ptr(), c.data_ptr(), B, M, N, K, int(not args.a_km), int(args.b_nk), code,
+                                None, 0, ctypes.byref(e)), e)
+
+    torch.cuda.synchronize()
+    flush = None
+    if not args.no_flush and operand_bytes < 512 << 20:
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=f"cuda:{args.device}")
+    for _ in range(args.warmup):
+        launch()
+    backend.Synchronize(args.device)
+    times = []
+    for _ in range(args.iters):
+        if flush is not None:
+            with torch.cuda.stream(stream):
+                flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        launch()
+        e1.record(stream)
+        backend.Synchronize(args.device)
+        times.append(e0.elapsed_time(e1))
+    ms = float(np.mean(times))
+    best = float(np.min(times))
+    achieved = work / (ms * 1e-3) / (1e9 if kind == "hbm" else 1e12)
+    out = {"kernel": args.kernel, "args": {k: v for k, v in vars(args).items() if k != "kernel"}, "ms_mean": ms, "ms_best": best,
+           "achieved": achieved, "unit": unit, "l2": "flushed between launches" if flush is not None else "operands exceed L2"}
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        with open(peaks_path) as fh:
+            peaks = json.load(fh)
+        peak = peaks["hbm_gbs"] if kind == "hbm" else peaks["bf16_tflops"]
+        out["peak"], out["frac_of_measured"] = peak, achieved / peak
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()
