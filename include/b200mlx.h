@@ -347,6 +347,15 @@ bool b200_k_gemm(int device, const void* a, const void* b, void* c, int64_t batc
 int64_t b200_k_reduce_sum_scratch_bytes(int64_t n);
 bool b200_k_reduce_sum_f32(int device, const float* x, float* out, int64_t n, void* scratch, int64_t scratch_bytes,
                            B200Error* err);
+/* The same reduction for callers that cannot allocate device memory (fixed
+ * memory budgets, latency-critical loops, threads without access to an
+ * allocator): the partial sums go to a 16 KiB array built into the library's
+ * device image, so no scratch pointer is passed and nothing is allocated.
+ * n must be <= 2^30; larger inputs are refused with B200_ERR_INVALID.  The
+ * first call on a device performs one-time set-up and should precede any stream
+ * capture.  All calls on a device share the array: overlapping calls would race.
+ * This entry point has no counterpart in the reference. */
+bool b200_k_reduce_sum_f32_noalloc(int device, const float* x, float* out, int64_t n, B200Error* err);
 
 #ifdef __cplusplus
 }
