@@ -7,10 +7,22 @@
 //   RMSNorm:   y = x * rsqrt(sum(x*x)/n + eps) [* gamma]   (no reference counterpart)
 //
 // Statistics are accumulated in fp32 whatever the storage type; the result is
-// rounded once.  One row group (32, 256 or 1024 threads) owns a row: the row is
-// loaded once with 128-bit streaming loads, stays in registers as packed 16-byte
-// vectors for all passes, reductions are warp shuffles, and it is stored once.
-// HBM-bound: algorithmic bytes = 2 * rows * cols * sizeof(T) (+ gamma, beta once).
+// rounded once.
+//
+// Design (HBM-bound; algorithmic bytes = 2 * rows * cols * sizeof(T), gamma and
+// beta are read once per CTA):
+//   * persistent grid: a multiple of the SM count of CTAs, each walking rows
+//     with a grid stride, so there is no wave-quantisation tail at 16k rows;
+//   * a row group of TPR threads (32..1024, chosen so that a thread owns at
+//     most 32 elements) cooperates on a row; groups of one CTA synchronise with
+//     their own named barrier, never with the whole CTA;
+//   * the row is loaded once with 128-bit streaming loads, unpacked ONCE to
+//     fp32 registers and reused by the mean / variance / output passes;
+//   * gamma (unpacked) and beta (packed) are loaded to registers once per CTA,
+//     outside the row loop: at 2 bytes per element the kernel is as close to
+//     the instruction-issue limit as to the HBM limit, so every per-element
+//     instruction counts;
+//   * the next row's loads are issued before the current row is reduced.
 #include "../kernels.h"
 #include "rowwise.cuh"
 
@@ -28,81 +40,118 @@ struct NArgs {
   float eps;
 };
 
-template <typename T, int ITERS, int TPR, bool RMS>
-__global__ void __launch_bounds__(TPR > 256 ? TPR : 256) norm_rows_kernel(const NArgs a) {
+// Sum over the TPR threads of a row group; all of them get the result.
+// `slot` is this group's private area of WPR floats; `bar` its barrier id.
+template <int TPR>
+__device__ __forceinline__ float group_sum(float v, float* slot, int bar) {
+  v = warp_reduce(v, SumOp());
+  if constexpr (TPR > 32) {
+    constexpr int WPR = TPR / 32;
+    const int lane = threadIdx.x & 31, w = (threadIdx.x % TPR) >> 5;
+    asm volatile("bar.sync %0, %1;" ::"r"(bar), "r"(TPR) : "memory");  // previous use of slot is over
+    if (lane == 0) slot[w] = v;
+    asm volatile("bar.sync %0, %1;" ::"r"(bar), "r"(TPR) : "memory");
+    float t = (lane < WPR) ? slot[lane] : 0.f;
+    v = warp_reduce(t, SumOp());
+  }
+  return v;
+}
+
+template <typename T, int ITERS, int TPR, bool RMS, bool HAS_G, bool HAS_B>
+__global__ void __launch_bounds__(TPR > 256 ? TPR : 256, TPR > 512 ? 1 : (TPR > 256 ? 1 : 2)) norm_rows_kernel(const NArgs a) {
   constexpr int V = Cvt<T>::N;
+  constexpr int BLOCK = TPR > 256 ? TPR : 256;
+  constexpr int GROUPS = BLOCK / TPR;
   __shared__ float red[32];
-  const int rows_per_cta = blockDim.x / TPR;
-  int64_t row = (int64_t)blockIdx.x * rows_per_cta + threadIdx.x / TPR;
+  const int group = threadIdx.x / TPR;
   const int t = threadIdx.x % TPR;
-  const bool active = row < a.rows;
-  if (!active) row = a.rows - 1;
-  const T* xr = reinterpret_cast<const T*>(a.x) + row * a.cols;
-  T* yr = reinterpret_cast<T*>(a.y) + row * a.cols;
+  float* slot = red + group * (TPR / 32);
+  const int bar = 1 + group;
   const float inv_n = 1.0f / (float)a.cols;
 
+  // per-thread column offsets and validity are the same for every row
+  bool valid[ITERS];
+  int64_t c0[ITERS];
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    c0[it] = (int64_t)(it * TPR + t) * V;
+    valid[it] = c0[it] < a.cols;
+  }
+  float g[ITERS][V];
+  Raw16 bq[ITERS];  // beta stays packed (16 bytes per vector): unpacking it per row is cheaper than 32 more registers
+  if constexpr (HAS_G) {
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it)
+      if (valid[it]) Cvt<T>::unpack(ld_cached16(reinterpret_cast<const T*>(a.gamma) + c0[it]), g[it]);
+  }
+  if constexpr (HAS_B && !RMS) {
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it)
+      if (valid[it]) bq[it] = ld_cached16(reinterpret_cast<const T*>(a.beta) + c0[it]);
+  }
+
+  const int64_t row_stride = (int64_t)gridDim.x * GROUPS;
+  int64_t row = (int64_t)blockIdx.x * GROUPS + group;
   Raw16 raw[ITERS];
+  if (row < a.rows) {
+    const T* xr = reinterpret_cast<const T*>(a.x) + row * a.cols;
 #pragma unroll
-  for (int it = 0; it < ITERS; ++it) {
-    const int64_t c0 = (int64_t)(it * TPR + t) * V;
-    if (c0 < a.cols) raw[it] = ld_stream16(xr + c0);
+    for (int it = 0; it < ITERS; ++it)
+      if (valid[it]) raw[it] = ld_stream16(xr + c0[it]);
   }
-  float mean = 0.f;
-  if constexpr (!RMS) {
-    float s = 0.f;
+  for (; row < a.rows; row += row_stride) {
+    float f[ITERS][V];
 #pragma unroll
-    for (int it = 0; it < ITERS; ++it) {
-      const int64_t c0 = (int64_t)(it * TPR + t) * V;
-      if (c0 < a.cols) {
-        float f[V];
-        Cvt<T>::unpack(raw[it], f);
+    for (int it = 0; it < ITERS; ++it)
+      if (valid[it]) Cvt<T>::unpack(raw[it], f[it]);
+    // prefetch the next row of this group while this one is reduced
+    const int64_t next = row + row_stride;
+    if (next < a.rows) {
+      const T* xn = reinterpret_cast<const T*>(a.x) + next * a.cols;
 #pragma unroll
-        for (int e = 0; e < V; ++e) s += f[e];
-      }
+      for (int it = 0; it < ITERS; ++it)
+        if (valid[it]) raw[it] = ld_stream16(xn + c0[it]);
     }
-    mean = group_reduce<TPR>(s, SumOp(), 0.f, red) * inv_n;
-  }
-  float sq = 0.f;
+    float mean = 0.f;
+    if constexpr (!RMS) {
+      float s = 0.f;
 #pragma unroll
-  for (int it = 0; it < ITERS; ++it) {
-    const int64_t c0 = (int64_t)(it * TPR + t) * V;
-    if (c0 < a.cols) {
-      float f[V];
-      Cvt<T>::unpack(raw[it], f);
+      for (int it = 0; it < ITERS; ++it)
+        if (valid[it]) {
 #pragma unroll
-      for (int e = 0; e < V; ++e) {
-        const float d = f[e] - mean;
-        sq += d * d;
-      }
+          for (int e = 0; e < V; ++e) s += f[it][e];
+        }
+      mean = group_sum<TPR>(s, slot, bar) * inv_n;
     }
-  }
-  sq = group_reduce<TPR>(sq, SumOp(), 0.f, red);
-  const float rstd = rsqrtf(sq * inv_n + a.eps);
-  if (!active) return;
+    float sq = 0.f;
 #pragma unroll
-  for (int it = 0; it < ITERS; ++it) {
-    const int64_t c0 = (int64_t)(it * TPR + t) * V;
-    if (c0 < a.cols) {
-      float f[V];
-      Cvt<T>::unpack(raw[it], f);
+    for (int it = 0; it < ITERS; ++it)
+      if (valid[it]) {
 #pragma unroll
-      for (int e = 0; e < V; ++e) f[e] = (f[e] - mean) * rstd;
-      if (a.gamma) {
-        float g[V];
-        Cvt<T>::unpack(ld_cached16(reinterpret_cast<const T*>(a.gamma) + c0), g);
-#pragma unroll
-        for (int e = 0; e < V; ++e) f[e] *= g[e];
+        for (int e = 0; e < V; ++e) {
+          if constexpr (!RMS) f[it][e] -= mean;
+          sq += f[it][e] * f[it][e];
+        }
       }
-      if (!RMS && a.beta) {
+    sq = group_sum<TPR>(sq, slot, bar);
+    const float rstd = rsqrtf(sq * inv_n + a.eps);
+    T* yr = reinterpret_cast<T*>(a.y) + row * a.cols;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it)
+      if (valid[it]) {
         float b[V];
-        Cvt<T>::unpack(ld_cached16(reinterpret_cast<const T*>(a.beta) + c0), b);
+        if constexpr (HAS_B && !RMS) Cvt<T>::unpack(bq[it], b);
 #pragma unroll
-        for (int e = 0; e < V; ++e) f[e] += b[e];
+        for (int e = 0; e < V; ++e) {
+          float v = f[it][e] * rstd;
+          if constexpr (HAS_G) v *= g[it][e];
+          if constexpr (HAS_B && !RMS) v += b[e];
+          f[it][e] = v;
+        }
+        Raw16 o;
+        Cvt<T>::pack(f[it], o);
+        st_stream16(yr + c0[it], o);
       }
-      Raw16 o;
-      Cvt<T>::pack(f, o);
-      st_stream16(yr + c0, o);
-    }
   }
 }
 
@@ -135,39 +184,55 @@ __global__ void __launch_bounds__(256) norm_generic_kernel(const NArgs a) {
   }
 }
 
+template <typename T, int ITERS, int TPR, bool RMS>
+void launch_params(const NArgs& a, unsigned grid, cudaStream_t s) {
+  constexpr int BLOCK = TPR > 256 ? TPR : 256;
+  const bool hg = a.gamma != nullptr, hb = a.beta != nullptr && !RMS;
+  if (hg && hb) norm_rows_kernel<T, ITERS, TPR, RMS, true, true><<<grid, BLOCK, 0, s>>>(a);
+  else if (hg) norm_rows_kernel<T, ITERS, TPR, RMS, true, false><<<grid, BLOCK, 0, s>>>(a);
+  else if (hb) norm_rows_kernel<T, ITERS, TPR, RMS, false, true><<<grid, BLOCK, 0, s>>>(a);
+  else norm_rows_kernel<T, ITERS, TPR, RMS, false, false><<<grid, BLOCK, 0, s>>>(a);
+}
+
 template <typename T, int TPR, bool RMS>
-void launch_tpr(const NArgs& a, int iters, cudaStream_t s) {
-  const int block = TPR > 256 ? TPR : 256;
-  const int rows_per_cta = block / TPR;
-  const unsigned grid = (unsigned)((a.rows + rows_per_cta - 1) / rows_per_cta);
+void launch_tpr(Device* dev, const NArgs& a, int iters, cudaStream_t s) {
+  constexpr int BLOCK = TPR > 256 ? TPR : 256;
+  constexpr int GROUPS = BLOCK / TPR;
+  const int64_t ctas_needed = (a.rows + GROUPS - 1) / GROUPS;
+  // persistent: a few CTAs per SM, never more than there are row slots
+  int64_t grid = (int64_t)dev->sm_count() * (BLOCK >= 1024 ? 1 : 2);
+  if (grid > ctas_needed) grid = ctas_needed;
   switch (iters) {
-    case 1: norm_rows_kernel<T, 1, TPR, RMS><<<grid, block, 0, s>>>(a); break;
-    case 2: norm_rows_kernel<T, 2, TPR, RMS><<<grid, block, 0, s>>>(a); break;
-    case 4: norm_rows_kernel<T, 4, TPR, RMS><<<grid, block, 0, s>>>(a); break;
-    case 8: norm_rows_kernel<T, 8, TPR, RMS><<<grid, block, 0, s>>>(a); break;
-    default: norm_rows_kernel<T, 16, TPR, RMS><<<grid, block, 0, s>>>(a); break;
+    case 1: launch_params<T, 1, TPR, RMS>(a, (unsigned)grid, s); break;
+    case 2: launch_params<T, 2, TPR, RMS>(a, (unsigned)grid, s); break;
+    default: launch_params<T, 4, TPR, RMS>(a, (unsigned)grid, s); break;
   }
 }
 
 template <typename T, bool RMS>
-void launch_typed(const NArgs& a, cudaStream_t s) {
+void launch_typed(Device* dev, const NArgs& a, cudaStream_t s) {
   constexpr int V = Cvt<T>::N;
+  constexpr int MAX_ITERS = 4;
   auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   const bool vec_ok = (a.cols % V == 0) && al16(a.x) && al16(a.y) && al16(a.gamma) && al16(a.beta) &&
-                      a.cols <= (int64_t)1024 * V * 16;
+                      a.cols <= (int64_t)1024 * V * MAX_ITERS;
   if (!vec_ok) {
     norm_generic_kernel<T, RMS><<<(unsigned)a.rows, 256, 0, s>>>(a);
     return;
   }
   const int64_t vecs = a.cols / V;
   int tpr = 32;
-  if (vecs > 32 * 16) tpr = 256;
-  if (vecs > 256 * 16) tpr = 1024;
+  while ((int64_t)tpr * MAX_ITERS < vecs) tpr *= 2;
   int iters = 1;
   while ((int64_t)iters * tpr < vecs) iters *= 2;
-  if (tpr == 32) launch_tpr<T, 32, RMS>(a, iters, s);
-  else if (tpr == 256) launch_tpr<T, 256, RMS>(a, iters, s);
-  else launch_tpr<T, 1024, RMS>(a, iters, s);
+  switch (tpr) {
+    case 32: launch_tpr<T, 32, RMS>(dev, a, iters, s); break;
+    case 64: launch_tpr<T, 64, RMS>(dev, a, iters, s); break;
+    case 128: launch_tpr<T, 128, RMS>(dev, a, iters, s); break;
+    case 256: launch_tpr<T, 256, RMS>(dev, a, iters, s); break;
+    case 512: launch_tpr<T, 512, RMS>(dev, a, iters, s); break;
+    default: launch_tpr<T, 1024, RMS>(dev, a, iters, s); break;
+  }
 }
 
 }  // namespace
@@ -179,9 +244,9 @@ Status norm_rows(Device* dev, const NormParams& p) {
   B200_TRY(dev->MakeCurrent());
   cudaStream_t s = dev->stream();
   switch (p.dtype) {
-    case B200_FLOAT32: p.rms ? launch_typed<float, true>(a, s) : launch_typed<float, false>(a, s); break;
-    case B200_BFLOAT16: p.rms ? launch_typed<__nv_bfloat16, true>(a, s) : launch_typed<__nv_bfloat16, false>(a, s); break;
-    case B200_FLOAT16: p.rms ? launch_typed<__half, true>(a, s) : launch_typed<__half, false>(a, s); break;
+    case B200_FLOAT32: p.rms ? launch_typed<float, true>(dev, a, s) : launch_typed<float, false>(dev, a, s); break;
+    case B200_BFLOAT16: p.rms ? launch_typed<__nv_bfloat16, true>(dev, a, s) : launch_typed<__nv_bfloat16, false>(dev, a, s); break;
+    case B200_FLOAT16: p.rms ? launch_typed<__half, true>(dev, a, s) : launch_typed<__half, false>(dev, a, s); break;
     default: return Status::Unsupported(strfmt("norm: dtype %s", dtype_name(p.dtype)));
   }
   return dev->CheckLaunch(p.rms ? "rms_norm" : "layer_norm");

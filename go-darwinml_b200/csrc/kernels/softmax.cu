@@ -101,7 +101,7 @@ __global__ void __launch_bounds__(TPR > 256 ? TPR : 256) softmax_rows_kernel(con
 #pragma unroll
     for (int e = 0; e < V; ++e) {
       // A fully masked row has mx = -inf: (-inf) - (-inf) = NaN, as IEEE gives.
-      v[it][e] = expf(v[it][e] - mx);
+      v[it][e] = __expf(v[it][e] - mx);
       sum += v[it][e];
     }
   }
