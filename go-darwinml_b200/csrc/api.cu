@@ -94,6 +94,7 @@ bool b200_buffer_to_host(B200Buffer buf, void* data, int64_t nbytes, B200Error* 
   if (s.ok()) {
     cudaError_t e = cudaStreamSynchronize(dev->stream());
     if (e != cudaSuccess) s = Status::Cuda(strfmt("stream synchronize failed: %s", cudaGetErrorString(e)));
+    else s = dev->CheckKernelErrors();
   }
   if (!s.ok()) { set_error(err, s); return false; }
   return true;

@@ -54,6 +54,7 @@ struct Status {
   static Status Cuda(const std::string& m) { return Status{B200_ERR_CUDA, m}; }
   static Status Unsupported(const std::string& m) { return Status{B200_ERR_UNSUPPORTED, m}; }
   static Status Oom(const std::string& m) { return Status{B200_ERR_OOM, m}; }
+  static Status Timeout(const std::string& m) { return Status{B200_ERR_TIMEOUT, m}; }
 };
 std::string strfmt(const char* fmt, ...);
 inline void clear_error(B200Error* e) {
@@ -96,12 +97,22 @@ class Device {
   Status Synchronize();
   // Launch status: any launch helper calls this after a kernel launch.
   Status CheckLaunch(const char* what);
+  // A word of device memory that kernels with bounded waits set when a wait
+  // gives up.  Read back (and cleared) at synchronisation points, and only when
+  // a kernel that can set it was launched since the last check.
+  int* kernel_error_flag() {
+    error_check_pending_ = true;
+    return error_flag_;
+  }
+  Status CheckKernelErrors();
   // A small pinned staging area used by synchronous host<->device copies.
  private:
   Device() = default;
   int ordinal_ = 0;
   int sm_count_ = 148;
   cudaStream_t stream_ = nullptr;
+  int* error_flag_ = nullptr;
+  bool error_check_pending_ = false;
   std::mutex mu_;
   std::multimap<int64_t, void*> free_blocks_;  // size -> ptr
   std::map<void*, int64_t> live_blocks_;       // ptr -> size

@@ -1,5 +1,591 @@
-// placeholder until the tcgen05 kernel lands
+// DotGeneral's dense contraction on the 5th-generation tensor cores.
+//
+//   C[b, m, n] = act( sum_k A(b, m, k) * B(b, k, n) + bias[n] )     fp32 accumulation,
+//   one rounding to the storage type in the epilogue (output dtype = input dtype,
+//   as the reference's matmul does: mpsgraph dotgeneral.go:52, bridge.m:684-700).
+//
+// Both operands are read IN PLACE in either storage order:
+//   A as [batch, M, K] ("K-major")  or [batch, K, M] ("MN-major"),
+//   B as [batch, N, K] ("K-major")  or [batch, K, N] ("MN-major"),
+// because the UMMA instruction descriptor carries a major bit per operand.  The
+// reference materialises up to three transposes per DotGeneral instead
+// (dotgeneral.go:110-142).
+//
+// Structure (one CTA per SM, persistent over output tiles of 128 x 256):
+//   warp 0     producer: one lane issues TMA tile loads (128-byte swizzle) into a
+//              4-stage shared-memory ring, signalling "full" mbarriers by byte count;
+//   warp 1     issuer: one lane issues tcgen05.mma (M=128, N=256, K=16 per instruction)
+//              from shared-memory descriptors into a TMEM accumulator; tcgen05.commit
+//              releases ring stages ("empty") and publishes finished accumulators;
+//   warps 2-5  epilogue: tcgen05.ld the accumulator (each warp its own 32 TMEM lanes),
+//              add bias, apply the activation, round, store 16-byte vectors.
+// TMEM holds two 256-column accumulators, so the epilogue of tile i overlaps the
+// main loop of tile i+1.  Tensor-core bound: flops = 2 * batch * M * N * K.
+//
+// fp32 operands use the same kernel through a 3-way bf16 split (see gemm_split3
+// below): a = a1 + a2 + a3 with 8 significant bits each, six partial products
+// accumulated in fp32 -- about fp32 accuracy at 1/6 of the bf16 rate.
+//
+// Every wait on an mbarrier is bounded (about two seconds of wall time); a wait
+// that gives up raises a flag in global memory, every role leaves its loop, the
+// TMEM allocation is released and the host reports B200_ERR_TIMEOUT.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <mutex>
+
 #include "../kernels.h"
-namespace b200 { namespace k {
-Status gemm_tcgen05(Device*, const GemmParams&, bool* taken) { *taken = false; return Status::OK(); }
-}}
+#include "gemm_common.cuh"
+
+namespace b200 {
+namespace k {
+
+namespace {
+
+constexpr int BM = 128;        // tile rows  (UMMA M)
+constexpr int BN = 256;        // tile cols  (UMMA N)
+constexpr int BK = 64;         // K elements per stage = one 128-byte swizzle row of 16-bit elements
+constexpr int UMMA_K = 16;     // K elements per tcgen05.mma for 16-bit types
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+
+// ------------------------------------------------------------------ PTX wrappers ---
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  Returns false (and raises *err_flag) when the limit passes or
+// another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* err_flag, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 0x3ff) == 0) {
+      if (*err_flag != 0) return false;
+      if (global_ns() - t0 > kWaitLimitNs) {
+        atomicCAS((int*)err_flag, 0, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// Arrives on the mbarrier once every tcgen05.mma issued so far by this thread has finished.
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// 32 lanes x 32 columns of 32-bit accumulators: thread i of the warp gets lane (base + i), columns [col, col + 32).
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor for a 128-byte-swizzled operand tile (see the
+// layout notes at the tile loader).  Addresses and offsets are in 16-byte units.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3fff);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;  // 128-byte swizzle
+  return d;
+}
+
+}  // namespace
+
+namespace {
+
+struct TcArgs {
+  void* c;
+  const void* bias;
+  int64_t M, N, K, ldc;
+  int batch;
+  int a_kmajor, b_kmajor;
+  int activation;
+  int in_f16;       // operands are F16 (else BF16)
+  int out_dtype;    // B200_BFLOAT16, B200_FLOAT16 or B200_FLOAT32
+  int tiles_m, tiles_n;
+  int64_t total_tiles;
+  int k_blocks;     // ceil(K / BK)
+  int segs;         // 1, or 6 partial products of the 3-way split
+  int vec_store;    // rows of C start 16-byte aligned and N is a multiple of the vector width
+  int* err_flag;
+};
+
+// plane of A / B used by each of the six partial products of the 3-way split,
+// smallest terms first: a1*b3, a3*b1, a2*b2, a1*b2, a2*b1, a1*b1
+__constant__ int kPlaneA[6] = {0, 2, 1, 0, 1, 0};
+__constant__ int kPlaneB[6] = {2, 0, 1, 1, 0, 0};
+
+__device__ __forceinline__ void tile_coords(const TcArgs& g, int64_t t, int* b, int* m_t, int* n_t) {
+  const int per_batch = g.tiles_m * g.tiles_n;
+  *b = (int)(t / per_batch);
+  const int r = (int)(t % per_batch);
+  constexpr int GROUP = 16;  // m-tiles per super-row: CTAs running together share A and B panels in L2
+  const int group_size = GROUP * g.tiles_n;
+  const int first_m = (r / group_size) * GROUP;
+  const int gm = (g.tiles_m - first_m) < GROUP ? (g.tiles_m - first_m) : GROUP;
+  const int in_group = r % group_size;
+  *m_t = first_m + in_group % gm;
+  *n_t = in_group / gm;
+}
+
+template <typename OutT> __device__ __forceinline__ void store_chunk(const TcArgs& g, OutT* crow, int64_t col0, const float* v);
+
+template <>
+__device__ __forceinline__ void store_chunk<float>(const TcArgs& g, float* crow, int64_t col0, const float* v) {
+  if (g.vec_store) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4)
+      if (col0 + j < g.N) *reinterpret_cast<float4*>(crow + col0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < g.N) crow[col0 + j] = v[j];
+  }
+}
+template <>
+__device__ __forceinline__ void store_chunk<__nv_bfloat16>(const TcArgs& g, __nv_bfloat16* crow, int64_t col0, const float* v) {
+  if (g.vec_store) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 8)
+      if (col0 + j < g.N) {
+        uint4 q;
+        __nv_bfloat162 h;
+        h = __floats2bfloat162_rn(v[j], v[j + 1]); q.x = *reinterpret_cast<uint32_t*>(&h);
+        h = __floats2bfloat162_rn(v[j + 2], v[j + 3]); q.y = *reinterpret_cast<uint32_t*>(&h);
+        h = __floats2bfloat162_rn(v[j + 4], v[j + 5]); q.z = *reinterpret_cast<uint32_t*>(&h);
+        h = __floats2bfloat162_rn(v[j + 6], v[j + 7]); q.w = *reinterpret_cast<uint32_t*>(&h);
+        *reinterpret_cast<uint4*>(crow + col0 + j) = q;
+      }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < g.N) crow[col0 + j] = __float2bfloat16_rn(v[j]);
+  }
+}
+template <>
+__device__ __forceinline__ void store_chunk<__half>(const TcArgs& g, __half* crow, int64_t col0, const float* v) {
+  if (g.vec_store) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 8)
+      if (col0 + j < g.N) {
+        uint4 q;
+        __half2 h;
+        h = __floats2half2_rn(v[j], v[j + 1]); q.x = *reinterpret_cast<uint32_t*>(&h);
+        h = __floats2half2_rn(v[j + 2], v[j + 3]); q.y = *reinterpret_cast<uint32_t*>(&h);
+        h = __floats2half2_rn(v[j + 4], v[j + 5]); q.z = *reinterpret_cast<uint32_t*>(&h);
+        h = __floats2half2_rn(v[j + 6], v[j + 7]); q.w = *reinterpret_cast<uint32_t*>(&h);
+        *reinterpret_cast<uint4*>(crow + col0 + j) = q;
+      }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < g.N) crow[col0 + j] = __float2half_rn(v[j]);
+  }
+}
+
+template <typename OutT> __device__ __forceinline__ float load_bias(const void* bias, int64_t col) {
+  return 0.f;
+}
+template <> __device__ __forceinline__ float load_bias<float>(const void* bias, int64_t col) { return reinterpret_cast<const float*>(bias)[col]; }
+template <> __device__ __forceinline__ float load_bias<__nv_bfloat16>(const void* bias, int64_t col) {
+  return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[col]);
+}
+template <> __device__ __forceinline__ float load_bias<__half>(const void* bias, int64_t col) {
+  return __half2float(reinterpret_cast<const __half*>(bias)[col]);
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const TcArgs g) {
+  extern __shared__ unsigned char smem_raw[];
+  // operand tiles need 1024-byte alignment for the 128-byte swizzle
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE_BYTES);
+  uint64_t* full = bars;                    // [STAGES]  TMA bytes landed
+  uint64_t* empty = bars + STAGES;          // [STAGES]  MMAs that read the stage are done
+  uint64_t* acc_full = bars + 2 * STAGES;   // [2]       accumulator complete
+  uint64_t* acc_empty = bars + 2 * STAGES + 2;  // [2]   accumulator drained by the epilogue
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* err = g.err_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int iters = g.k_blocks * g.segs;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer ---
+    if (lane == 0) {
+      int s = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int64_t t = blockIdx.x; t < g.total_tiles && ok; t += gridDim.x) {
+        int b, m_t, n_t;
+        tile_coords(g, t, &b, &m_t, &n_t);
+        const int m0 = m_t * BM, n0 = n_t * BN;
+        for (int it = 0; it < iters; ++it) {
+          if (!mbar_wait(&empty[s], phase ^ 1, err, 1)) { ok = false; break; }
+          const int seg = it / g.k_blocks, kb = it % g.k_blocks;
+          const int pa = g.segs > 1 ? kPlaneA[seg] : 0, pb = g.segs > 1 ? kPlaneB[seg] : 0;
+          unsigned char* sa = tiles + s * STAGE_BYTES;
+          unsigned char* sb = sa + A_STAGE_BYTES;
+          mbar_expect_tx(&full[s], STAGE_BYTES);
+          if (g.a_kmajor) {
+            // box {64 k, 128 m}: 128 rows of 128 bytes
+            tma_load_4d(sa, &tm_a, &full[s], kb * BK, m0, b, pa);
+          } else {
+            // two boxes {64 m, 64 k}: 64 k-rows of 128 bytes each, one box per 64-wide block of M
+            tma_load_4d(sa, &tm_a, &full[s], m0, kb * BK, b, pa);
+            tma_load_4d(sa + 8192, &tm_a, &full[s], m0 + 64, kb * BK, b, pa);
+          }
+          if (g.b_kmajor) {
+            tma_load_4d(sb, &tm_b, &full[s], kb * BK, n0, b, pb);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) tma_load_4d(sb + j * 8192, &tm_b, &full[s], n0 + j * 64, kb * BK, b, pb);
+          }
+          if (++s == STAGES) { s = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------------- issuer ---
+    if (lane == 0) {
+      // instruction descriptor: fp32 accumulate, operand format, majors, N and M
+      uint32_t idesc = 0;
+      idesc |= 1u << 4;                                  // D format: F32
+      idesc |= (g.in_f16 ? 0u : 1u) << 7;                // A format: F16 = 0, BF16 = 1
+      idesc |= (g.in_f16 ? 0u : 1u) << 10;               // B format
+      idesc |= (g.a_kmajor ? 0u : 1u) << 15;             // A major: 0 = K, 1 = MN
+      idesc |= (g.b_kmajor ? 0u : 1u) << 16;             // B major
+      idesc |= (uint32_t)(BN >> 3) << 17;
+      idesc |= (uint32_t)(BM >> 4) << 24;
+      // K-major tile: rows of 128 bytes, 8-row groups 1024 bytes apart; 16 k-elements = 32 bytes along the row.
+      // MN-major tile: 64-wide blocks 8192 bytes apart (LBO), 8-k-row groups 1024 bytes apart (SBO); 16 k = 2 groups.
+      const uint32_t a_lbo = g.a_kmajor ? 16u : 8192u, b_lbo = g.b_kmajor ? 16u : 8192u;
+      const uint32_t a_kstep = g.a_kmajor ? 32u : 2048u, b_kstep = g.b_kmajor ? 32u : 2048u;
+      int s = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int local_tile = 0;
+      for (int64_t t = blockIdx.x; t < g.total_tiles && ok; t += gridDim.x, ++local_tile) {
+        const int acc = local_tile & 1;
+        const uint32_t acc_phase = (local_tile >> 1) & 1;
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, err, 2)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int it = 0; it < iters; ++it) {
+          if (!mbar_wait(&full[s], phase, err, 3)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(tiles + s * STAGE_BYTES), sb = sa + A_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = make_smem_desc(sa + k * a_kstep, a_lbo, 1024);
+            const uint64_t db = make_smem_desc(sb + k * b_kstep, b_lbo, 1024);
+            umma_f16(d_tmem, da, db, idesc, (it | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(&empty[s]);  // frees the stage once these MMAs have read it
+          if (++s == STAGES) { s = 0; phase ^= 1; }
+        }
+        if (ok) tc_commit(&acc_full[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue ---
+    const int quarter = warp & 3;              // TMEM lanes [32*quarter, 32*quarter + 32) belong to this warp
+    const int row_in_tile = quarter * 32 + lane;
+    bool ok = true;
+    int local_tile = 0;
+    for (int64_t t = blockIdx.x; t < g.total_tiles && ok; t += gridDim.x, ++local_tile) {
+      int b, m_t, n_t;
+      tile_coords(g, t, &b, &m_t, &n_t);
+      const int acc = local_tile & 1;
+      const uint32_t acc_phase = (local_tile >> 1) & 1;
+      const bool landed = mbar_wait(&acc_full[acc], acc_phase, err, 4);
+      if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }  // the warp leaves together: tcgen05.ld is warp-collective
+      tc_fence_after();
+      const int64_t row = (int64_t)m_t * BM + row_in_tile;
+      const int64_t n0 = (int64_t)n_t * BN;
+      OutT* crow = reinterpret_cast<OutT*>(g.c) + ((int64_t)b * g.M + row) * g.ldc;
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int chunk = 0; chunk < BN / 32; ++chunk) {
+        const int64_t col0 = n0 + chunk * 32;
+        if (col0 >= g.N) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld32(taddr + chunk * 32, r);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (g.bias) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < g.N) v[j] += load_bias<OutT>(g.bias, col0 + j);
+        }
+        if (g.activation != B200_ACT_NONE) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = apply_activation(g.activation, v[j]);
+        }
+        if (row < g.M) store_chunk<OutT>(g, crow, col0, v);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown ---
+  tc_fence_before();
+  __shared__ int failed;
+  if (threadIdx.x == 0) failed = *err;
+  __syncthreads();
+  if (failed != 0) {
+    // a wait gave up: let copies and MMAs still in flight settle before the tiles and TMEM go away
+    const unsigned long long t0 = global_ns();
+    while (global_ns() - t0 < 200000ull) {}
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace
+
+namespace {
+
+// ---- fp32 -> three bf16 planes (hi, mid, lo): x = p0 + p1 + p2 up to 2^-24 relative ----
+__global__ void __launch_bounds__(256) split3_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ planes, int64_t n) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float v = x[i];
+    const __nv_bfloat16 h0 = __float2bfloat16_rn(v);
+    const float r1 = v - __bfloat162float(h0);
+    const __nv_bfloat16 h1 = __float2bfloat16_rn(r1);
+    const float r2 = r1 - __bfloat162float(h1);
+    planes[i] = h0;
+    planes[n + i] = h1;
+    planes[2 * n + i] = __float2bfloat16_rn(r2);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+Status get_encode_fn(EncodeTiledFn* out) {
+  static std::mutex mu;
+  static EncodeTiledFn fn = nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !p) {
+      cudaGetLastError();
+      return Status::Cuda("cuTensorMapEncodeTiled is not available from this driver");
+    }
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  *out = fn;
+  return Status::OK();
+}
+
+// 4-D map {inner, outer, batch, plane} over 16-bit elements with a {64, box_outer, 1, 1} box and 128-byte swizzle.
+Status make_operand_map(CUtensorMap* map, const void* base, bool f16, int64_t inner, int64_t outer, int64_t ld, int64_t batch,
+                        int64_t batch_stride, int64_t planes, int64_t plane_stride, int box_outer) {
+  EncodeTiledFn fn;
+  B200_TRY(get_encode_fn(&fn));
+  cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)batch, (cuuint64_t)planes};
+  cuuint64_t strides[3] = {(cuuint64_t)ld * 2, (cuuint64_t)batch_stride * 2, (cuuint64_t)plane_stride * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_outer, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return Status::Cuda(strfmt("cuTensorMapEncodeTiled failed with code %d", (int)r));
+  return Status::OK();
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
+  *taken = false;
+  const bool is16 = p.dtype == B200_BFLOAT16 || p.dtype == B200_FLOAT16;
+  const bool is32 = p.dtype == B200_FLOAT32;
+  if (!is16 && !is32) return Status::OK();
+  if (p.batch <= 0 || p.m <= 0 || p.n <= 0 || p.k <= 0) return Status::OK();
+  if (p.a_batch_stride >= 0 || p.b_batch_stride >= 0) return Status::OK();  // only dense batches here
+  // TMA needs 16-byte aligned bases and row pitches: the contiguous extent of each operand must be a multiple of 8 elements.
+  const int64_t a_inner = p.a_k_major ? p.k : p.m, b_inner = p.b_k_major ? p.k : p.n;
+  if (a_inner % 8 != 0 || b_inner % 8 != 0) return Status::OK();
+  if (!aligned16(p.a) || !aligned16(p.b)) return Status::OK();
+  if (p.m > 0x7fffffffLL || p.n > 0x7fffffffLL || p.k > 0x7fffffffLL || p.batch > 0x7fffffffLL) return Status::OK();
+  // tiny problems are latency-bound either way; leave them to the SIMT kernel
+  if ((double)p.batch * p.m * p.n * p.k < 64.0 * 64.0 * 64.0) return Status::OK();
+  *taken = true;
+
+  B200_TRY(dev->MakeCurrent());
+  cudaStream_t stream = dev->stream();
+  const void* a = p.a;
+  const void* b = p.b;
+  void* tmp_a = nullptr;
+  void* tmp_b = nullptr;
+  int64_t planes = 1, a_plane_stride = 0, b_plane_stride = 0;
+  const int64_t a_elems = p.batch * p.m * p.k, b_elems = p.batch * p.k * p.n;
+  if (is32) {
+    // three bf16 planes per operand
+    Status s = dev->Alloc(a_elems * 6, &tmp_a);
+    if (s.ok()) s = dev->Alloc(b_elems * 6, &tmp_b);
+    if (!s.ok()) { dev->Free(tmp_a); return s; }
+    auto grid_for = [&](int64_t n) { int64_t g = (n + 255) / 256, cap = (int64_t)dev->sm_count() * 16; return (unsigned)(g < cap ? g : cap); };
+    split3_kernel<<<grid_for(a_elems), 256, 0, stream>>>((const float*)p.a, (__nv_bfloat16*)tmp_a, a_elems);
+    split3_kernel<<<grid_for(b_elems), 256, 0, stream>>>((const float*)p.b, (__nv_bfloat16*)tmp_b, b_elems);
+    a = tmp_a; b = tmp_b;
+    planes = 3; a_plane_stride = a_elems; b_plane_stride = b_elems;
+  }
+  auto cleanup = [&]() { dev->Free(tmp_a); dev->Free(tmp_b); };
+
+  CUtensorMap tm_a, tm_b;
+  Status s;
+  const bool f16 = p.dtype == B200_FLOAT16;
+  if (p.a_k_major) s = make_operand_map(&tm_a, a, f16, p.k, p.m, p.k, p.batch, p.m * p.k, planes, planes > 1 ? a_plane_stride : p.m * p.k * p.batch, BM);
+  else s = make_operand_map(&tm_a, a, f16, p.m, p.k, p.m, p.batch, p.m * p.k, planes, planes > 1 ? a_plane_stride : p.m * p.k * p.batch, 64);
+  if (s.ok()) {
+    if (p.b_k_major) s = make_operand_map(&tm_b, b, f16, p.k, p.n, p.k, p.batch, p.n * p.k, planes, planes > 1 ? b_plane_stride : p.n * p.k * p.batch, BN);
+    else s = make_operand_map(&tm_b, b, f16, p.n, p.k, p.n, p.batch, p.n * p.k, planes, planes > 1 ? b_plane_stride : p.n * p.k * p.batch, 64);
+  }
+  if (!s.ok()) { cleanup(); return s; }
+
+  TcArgs g;
+  g.c = p.c; g.bias = p.bias;
+  g.M = p.m; g.N = p.n; g.K = p.k; g.ldc = p.n;
+  g.batch = (int)p.batch;
+  g.a_kmajor = p.a_k_major ? 1 : 0; g.b_kmajor = p.b_k_major ? 1 : 0;
+  g.activation = p.activation;
+  g.in_f16 = f16 ? 1 : 0;
+  g.out_dtype = p.dtype;
+  g.tiles_m = (int)((p.m + BM - 1) / BM);
+  g.tiles_n = (int)((p.n + BN - 1) / BN);
+  g.total_tiles = (int64_t)g.tiles_m * g.tiles_n * p.batch;
+  g.k_blocks = (int)((p.k + BK - 1) / BK);
+  g.segs = is32 ? 6 : 1;
+  const int out_vec = is32 ? 4 : 8;
+  g.vec_store = (p.n % out_vec == 0 && aligned16(p.c) && (!p.bias || true)) ? 1 : 0;
+  g.err_flag = dev->kernel_error_flag();
+
+  const int64_t grid = g.total_tiles < dev->sm_count() ? g.total_tiles : dev->sm_count();
+  cudaError_t e = cudaSuccess;
+  // the dynamic shared memory opt-in is per function and per device; do it once
+  static std::mutex attr_mu;
+  static bool attr_done[3][64] = {};
+#define LAUNCH_TC(OutT, SLOT)                                                                                               \
+  do {                                                                                                                      \
+    {                                                                                                                       \
+      std::lock_guard<std::mutex> lock(attr_mu);                                                                            \
+      if (!attr_done[SLOT][dev->ordinal()]) {                                                                               \
+        e = cudaFuncSetAttribute(gemm_tcgen05_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);       \
+        attr_done[SLOT][dev->ordinal()] = (e == cudaSuccess);                                                               \
+      }                                                                                                                     \
+    }                                                                                                                       \
+    if (e == cudaSuccess) gemm_tcgen05_kernel<OutT><<<(unsigned)grid, NUM_THREADS, SMEM_BYTES, stream>>>(tm_a, tm_b, g);     \
+  } while (0)
+  if (is32) LAUNCH_TC(float, 0);
+  else if (f16) LAUNCH_TC(__half, 1);
+  else LAUNCH_TC(__nv_bfloat16, 2);
+#undef LAUNCH_TC
+  cleanup();  // stream-ordered: the blocks are reused only by work enqueued after this kernel
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return Status::Cuda(strfmt("gemm_tcgen05: %s", cudaGetErrorString(e)));
+  }
+  return dev->CheckLaunch("gemm_tcgen05");
+}
+
+}  // namespace k
+}  // namespace b200

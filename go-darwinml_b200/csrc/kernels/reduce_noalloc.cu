@@ -14,9 +14,10 @@
 // image: kNoAllocScratchBytes bytes on every GPU that loads the library, held
 // until the process exits.  Consequences the caller must know:
 //   * n is limited to kNoAllocMaxElements; larger inputs are refused.
-//   * The FIRST call on a device looks up the array's device address and
-//     creates the library's stream for that device.  Make that first call
-//     before starting any stream capture.
+//   * The FIRST call on a device looks up the array's device address and, if
+//     nothing else has used that device through this library yet, performs the
+//     library's one-time device set-up (its stream and status word).  Make that
+//     first call before starting any stream capture.
 //   * Every call on a device uses the same array and leaves its partial sums
 //     behind.  Nothing needs clearing between calls: each launch overwrites
 //     every slot it later reads.  Calls issued through this library run one

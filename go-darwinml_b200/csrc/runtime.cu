@@ -57,6 +57,8 @@ Status Device::Get(int ordinal, Device** out) {
     int sms = 0;
     B200_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ordinal));
     d->sm_count_ = sms > 0 ? sms : 148;
+    B200_CUDA_TRY(cudaMalloc((void**)&d->error_flag_, 256));
+    B200_CUDA_TRY(cudaMemset(d->error_flag_, 0, 256));
     g_devices[ordinal] = d.release();
   }
   *out = g_devices[ordinal];
@@ -71,6 +73,22 @@ Status Device::MakeCurrent() {
 Status Device::Synchronize() {
   B200_TRY(MakeCurrent());
   B200_CUDA_TRY(cudaStreamSynchronize(stream_));
+  return CheckKernelErrors();
+}
+
+Status Device::CheckKernelErrors() {
+  if (!error_flag_ || !error_check_pending_) return Status::OK();
+  error_check_pending_ = false;
+  int code = 0;
+  B200_CUDA_TRY(cudaMemcpyAsync(&code, error_flag_, sizeof(int), cudaMemcpyDeviceToHost, stream_));
+  B200_CUDA_TRY(cudaStreamSynchronize(stream_));
+  if (code != 0) {
+    B200_CUDA_TRY(cudaMemsetAsync(error_flag_, 0, sizeof(int), stream_));
+    static const char* who[] = {"?", "the tile producer waiting for a free stage", "the MMA issuer waiting for a drained accumulator",
+                                "the MMA issuer waiting for operand tiles", "the epilogue waiting for a finished accumulator"};
+    return Status::Timeout(strfmt("a bounded wait inside a GEMM kernel gave up (%s); its results are invalid",
+                                  (code >= 1 && code <= 4) ? who[code] : who[0]));
+  }
   return Status::OK();
 }
 

@@ -1,0 +1,230 @@
+"""Graph builders for the benchmark configurations, written against the Function interface.
+
+Each builder takes a Function-like object (the backend's Function, or any object with the same
+methods, e.g. a CPU oracle in the tests) plus already-created parameter values, and returns the
+output value(s).  They use only the reference's op vocabulary: Gather, FusedLayerNorm, FusedDense,
+FusedAttentionQKVProjection, FusedScaledDotProductAttention, DotGeneral and elementwise ops
+(ref mpsgraph/gomlx/function.go), plus FusedRMSNorm for the Llama-style model.
+
+  mlp_forward          configuration "MLP forward, fp32"            x[64,784] -> softmax probabilities [64,10]
+  gpt2_forward         GPT-2-small-shaped decoder forward, bf16     ids[B,S] -> logits [B,S,V]
+  llama_forward        Llama-style decoder forward (GQA, SwiGLU, RMSNorm, RoPE), bf16
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List
+
+import numpy as np
+
+ACT_NONE, ACT_GELU, ACT_RELU, ACT_SILU, ACT_TANH = 0, 1, 2, 3, 4
+LAYOUT_BHSD, LAYOUT_BSHD = 0, 1
+C_I32, C_BF16, C_F32 = 3, 6, 7
+
+
+class _Shape:
+    def __init__(self, code, dims):
+        self.DType, self.Dimensions = code, list(dims)
+
+    def Rank(self):
+        return len(self.Dimensions)
+
+
+# ------------------------------------------------------------------------------------ MLP ---
+def mlp_param_shapes(batch=64, d_in=784, d_hidden=512, d_out=10):
+    return [("x", (batch, d_in)), ("w1", (d_in, d_hidden)), ("b1", (d_hidden,)), ("w2", (d_hidden, d_out)), ("b2", (d_out,))]
+
+
+def mlp_init(seed=0, batch=64, d_in=784, d_hidden=512, d_out=10) -> List[np.ndarray]:
+    """x ~ U(-1,1); W ~ N(0, 1/fan_in); biases zero."""
+    rng = np.random.default_rng(seed)
+    x = rng.uniform(-1, 1, size=(batch, d_in)).astype(np.float32)
+    w1 = (rng.standard_normal((d_in, d_hidden)) / math.sqrt(d_in)).astype(np.float32)
+    w2 = (rng.standard_normal((d_hidden, d_out)) / math.sqrt(d_hidden)).astype(np.float32)
+    return [x, w1, np.zeros(d_hidden, np.float32), w2, np.zeros(d_out, np.float32)]
+
+
+def mlp_forward(f, x, w1, b1, w2, b2):
+    h = f.FusedDense(x, w1, b1, ACT_RELU)
+    logits = f.FusedDense(h, w2, b2, ACT_NONE)
+    return f.FusedSoftmax(logits, 1)
+
+
+# ---------------------------------------------------------------------------------- GPT-2 ---
+@dataclass
+class GPT2Config:
+    layers: int = 12
+    d_model: int = 768
+    heads: int = 12
+    d_ff: int = 3072
+    seq: int = 1024
+    vocab: int = 50257
+    batch: int = 16
+    eps: float = 1e-5
+
+
+def gpt2_param_shapes(c: GPT2Config):
+    d = c.d_model
+    out = [("ids", (c.batch, c.seq, 1)), ("wte", (c.vocab, d)), ("wpe", (c.seq, d))]
+    for i in range(c.layers):
+        out += [(f"l{i}.ln1_g", (d,)), (f"l{i}.ln1_b", (d,)), (f"l{i}.wqkv", (d, 3 * d)), (f"l{i}.bq", (d,)), (f"l{i}.bk", (d,)),
+                (f"l{i}.bv", (d,)), (f"l{i}.wo", (d, d)), (f"l{i}.bo", (d,)), (f"l{i}.ln2_g", (d,)), (f"l{i}.ln2_b", (d,)),
+                (f"l{i}.wfc", (d, c.d_ff)), (f"l{i}.bfc", (c.d_ff,)), (f"l{i}.wproj", (c.d_ff, d)), (f"l{i}.bproj", (d,))]
+    out += [("lnf_g", (d,)), ("lnf_b", (d,))]
+    return out
+
+
+def _init_params(shapes, seed, float_dtype, vocab):
+    """weights ~ N(0, 0.02); norm gains 1, biases 0; token ids uniform in [0, vocab)."""
+    rng = np.random.default_rng(seed)
+    arrays = []
+    for name, shape in shapes:
+        if name == "ids":
+            arrays.append(rng.integers(0, vocab, size=shape, dtype=np.int64).astype(np.int32))
+        elif name.endswith("_g") or name.endswith(".g"):
+            arrays.append(np.ones(shape, np.float32).astype(float_dtype))
+        elif name.split(".")[-1].startswith("b") or name.endswith("_b"):
+            arrays.append(np.zeros(shape, np.float32).astype(float_dtype))
+        elif name in ("rope_cos", "rope_sin"):
+            arrays.append(None)  # filled by the caller
+        else:
+            arrays.append((0.02 * rng.standard_normal(shape, dtype=np.float32)).astype(float_dtype))
+    return arrays
+
+
+def gpt2_init(c: GPT2Config, seed=0, float_dtype=None):
+    import ml_dtypes
+    return _init_params(gpt2_param_shapes(c), seed, float_dtype or ml_dtypes.bfloat16, c.vocab)
+
+
+def gpt2_forward(f, c: GPT2Config, dtype_code, *params):
+    """Returns logits [B, S, V].  The LM head is tied to the token embedding (contract d with wte's axis 1)."""
+    it = iter(params)
+    ids, wte, wpe = next(it), next(it), next(it)
+    B, S, d, H = c.batch, c.seq, c.d_model, c.heads
+    D = d // H
+    x = f.Gather(wte, ids, 2, [2], [0], [0], [1, d], False)                       # [B, S, d]
+    x = f.Add(x, f.BroadcastInDim(wpe, _Shape(dtype_code, (B, S, d)), [1, 2]))
+    for _ in range(c.layers):
+        ln1_g, ln1_b, wqkv, bq, bk, bv, wo, bo, ln2_g, ln2_b, wfc, bfc, wproj, bproj = (next(it) for _ in range(14))
+        h = f.FusedLayerNorm(x, [-1], c.eps, ln1_g, ln1_b)
+        q, k, v = f.FusedAttentionQKVProjection(h, wqkv, bq, bk, bv, d, d)
+        q, k, v = (f.Reshape(t, B, S, H, D) for t in (q, k, v))
+        a = f.FusedScaledDotProductAttention(q, k, v, None, H, H, LAYOUT_BSHD, 1.0 / math.sqrt(D), True)
+        x = f.Add(x, f.FusedDense(f.Reshape(a, B, S, d), wo, bo, ACT_NONE))
+        h = f.FusedLayerNorm(x, [-1], c.eps, ln2_g, ln2_b)
+        m = f.FusedDense(h, wfc, bfc, ACT_GELU)
+        x = f.Add(x, f.FusedDense(m, wproj, bproj, ACT_NONE))
+    lnf_g, lnf_b = next(it), next(it)
+    x = f.FusedLayerNorm(x, [-1], c.eps, lnf_g, lnf_b)
+    return f.DotGeneral(x, [2], None, wte, [1], None)
+
+
+def gpt2_flops_per_token(c: GPT2Config) -> float:
+    d, S = c.d_model, c.seq
+    return c.layers * (2 * d * 3 * d + 2 * d * d + 4 * d * c.d_ff + 4 * S * d) + 2 * d * c.vocab  # full S x S attention counted
+
+
+# ---------------------------------------------------------------------------------- Llama ---
+@dataclass
+class LlamaConfig:
+    layers: int = 16
+    d_model: int = 2048
+    heads: int = 32
+    kv_heads: int = 8
+    d_ff: int = 8192
+    seq: int = 2048
+    vocab: int = 128256
+    batch: int = 64
+    eps: float = 1e-5
+    rope_theta: float = 500000.0
+
+
+def llama_param_shapes(c: LlamaConfig):
+    d, D = c.d_model, c.d_model // c.heads
+    kv = c.kv_heads * D
+    out = [("ids", (c.batch, c.seq, 1)), ("embed", (c.vocab, d)), ("rope_cos", (c.seq, D)), ("rope_sin", (c.seq, D))]
+    for i in range(c.layers):
+        out += [(f"l{i}.norm1_g", (d,)), (f"l{i}.wqkv", (d, d + 2 * kv)), (f"l{i}.wo", (d, d)), (f"l{i}.norm2_g", (d,)),
+                (f"l{i}.wgate", (d, c.d_ff)), (f"l{i}.wup", (d, c.d_ff)), (f"l{i}.wdown", (c.d_ff, d))]
+    out += [("normf_g", (d,)), ("lm_head", (d, c.vocab))]
+    return out
+
+
+def rope_tables(c: LlamaConfig):
+    """cos / sin of position * theta^(-2i/D), both halves of the head dim (rotate-half form)."""
+    D = c.d_model // c.heads
+    inv = c.rope_theta ** (-np.arange(0, D, 2, dtype=np.float64) / D)
+    ang = np.arange(c.seq, dtype=np.float64)[:, None] * inv[None, :]
+    ang = np.concatenate([ang, ang], axis=1)
+    return np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+
+
+def llama_init(c: LlamaConfig, seed=0, float_dtype=None):
+    import ml_dtypes
+    dt = float_dtype or ml_dtypes.bfloat16
+    shapes = llama_param_shapes(c)
+    arrays = _init_params(shapes, seed, dt, c.vocab)
+    cos, sin = rope_tables(c)
+    for i, (name, _) in enumerate(shapes):
+        if name == "rope_cos":
+            arrays[i] = cos.astype(dt)
+        elif name == "rope_sin":
+            arrays[i] = sin.astype(dt)
+    return arrays
+
+
+def _rope(f, x, cos_b, sin_b, dims, half):
+    """x * cos + rotate_half(x) * sin, rotate_half(x) = concat(-x[half:], x[:half]) on the last axis."""
+    r = len(dims)
+    lo = f.Slice(x, [0] * r, dims[:-1] + [half], [1] * r)
+    hi = f.Slice(x, [0] * (r - 1) + [half], dims, [1] * r)
+    rot = f.Concatenate(r - 1, f.Neg(hi), lo)
+    return f.Add(f.Mul(x, cos_b), f.Mul(rot, sin_b))
+
+
+def llama_forward(f, c: LlamaConfig, dtype_code, *params):
+    """Returns logits [B, S, V]."""
+    it = iter(params)
+    ids, embed, cos, sin = next(it), next(it), next(it), next(it)
+    B, S, d, H, Hkv = c.batch, c.seq, c.d_model, c.heads, c.kv_heads
+    D = d // H
+    kv = Hkv * D
+    x = f.Gather(embed, ids, 2, [2], [0], [0], [1, d], False)                     # [B, S, d]
+    cos_q = f.BroadcastInDim(cos, _Shape(dtype_code, (B, S, H, D)), [1, 3])
+    sin_q = f.BroadcastInDim(sin, _Shape(dtype_code, (B, S, H, D)), [1, 3])
+    cos_k = f.BroadcastInDim(cos, _Shape(dtype_code, (B, S, Hkv, D)), [1, 3])
+    sin_k = f.BroadcastInDim(sin, _Shape(dtype_code, (B, S, Hkv, D)), [1, 3])
+    for _ in range(c.layers):
+        norm1_g, wqkv, wo, norm2_g, wgate, wup, wdown = (next(it) for _ in range(7))
+        h = f.FusedRMSNorm(x, [-1], c.eps, norm1_g)
+        q, k, v = f.FusedAttentionQKVProjection(h, wqkv, None, None, None, d, kv)
+        q = _rope(f, f.Reshape(q, B, S, H, D), cos_q, sin_q, [B, S, H, D], D // 2)
+        k = _rope(f, f.Reshape(k, B, S, Hkv, D), cos_k, sin_k, [B, S, Hkv, D], D // 2)
+        v = f.Reshape(v, B, S, Hkv, D)
+        a = f.FusedScaledDotProductAttention(q, k, v, None, H, Hkv, LAYOUT_BSHD, 1.0 / math.sqrt(D), True)
+        x = f.Add(x, f.FusedDense(f.Reshape(a, B, S, d), wo, None, ACT_NONE))
+        h = f.FusedRMSNorm(x, [-1], c.eps, norm2_g)
+        gate = f.FusedDense(h, wgate, None, ACT_SILU)
+        up = f.FusedDense(h, wup, None, ACT_NONE)
+        x = f.Add(x, f.FusedDense(f.Mul(gate, up), wdown, None, ACT_NONE))
+    normf_g, lm_head = next(it), next(it)
+    x = f.FusedRMSNorm(x, [-1], c.eps, normf_g)
+    return f.FusedDense(x, lm_head, None, ACT_NONE)
+
+
+def llama_flops_per_token(c: LlamaConfig) -> float:
+    d, S = c.d_model, c.seq
+    kv = c.kv_heads * (d // c.heads)
+    return c.layers * (2 * d * d * 2 + 2 * d * kv * 2 + 6 * d * c.d_ff + 4 * S * d) + 2 * d * c.vocab  # full S x S attention counted
+
+
+def build_executable(pkg, backend, name, shapes_and_dtypes, forward):
+    """Compiles `forward(f, *params)` with one Parameter per (shape, numpy dtype); returns (builder, executable)."""
+    builder = backend.Builder(name)
+    f = builder.Main()
+    params = [f.Parameter(f"p{i}", pkg.Shape(pkg.dtypes.from_numpy(dt), shape)) for i, (shape, dt) in enumerate(shapes_and_dtypes)]
+    out = forward(f, *params)
+    f.Return(list(out) if isinstance(out, (list, tuple)) else [out], None)
+    return builder, builder.Compile()
