@@ -327,11 +327,24 @@ def run_b200_arm(args, rank, local_rank, world):
     h2d = n_sm * 4 + n_norm * 2 + 2 * NORM_SHAPE[1] * 2
     d2h = n_sm * 4 + 2 * n_norm * 2
 
+    # the other configurations (DotGeneral sweep, transformer forwards); never allowed to sink the headline line
+    extras, extras_error = None, None
+    if not args.no_extras:
+        for o in (d_logits, d_x, d_g, d_b):
+            backend.BufferFinalize(o)
+        L.b200_device_trim(local_rank)
+        try:
+            extras = run_extras(b200, backend, L, libmod, torch, stream, local_rank, world, measured_peaks()[0])
+        except Exception as ex:  # noqa: BLE001
+            extras_error = f"{type(ex).__name__}: {ex}"
+    gpt_ms = extras["gpt2_small_fwd_bf16"]["ms_per_forward"] if extras else 0.0
+    llama_ms = extras["llama_1b_fwd_bf16"]["ms_per_forward"] if extras else 0.0
+
     # max over ranks, on device-measured times
-    times = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=f"cuda:{local_rank}")
+    times = torch.tensor([elapsed_ms, e2e_ms, gpt_ms, llama_ms], dtype=torch.float64, device=f"cuda:{local_rank}")
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms = float(times[0]), float(times[1])
+    elapsed_ms, e2e_ms, gpt_ms, llama_ms = (float(t) for t in times)
 
     if rank == 0:
         peaks, peak_src = measured_peaks()
@@ -362,6 +375,12 @@ def run_b200_arm(args, rank, local_rank, world):
                         "rms_norm_bf16": {"ms": rms_ms, "GB/s": NORM_BYTES / rms_ms / 1e6, "frac_of_peak": NORM_BYTES / rms_ms / 1e6 / peaks["hbm_gbs"]},
                         "layer_norm_bf16": {"ms": ln_ms, "GB/s": NORM_BYTES / ln_ms / 1e6, "frac_of_peak": NORM_BYTES / ln_ms / 1e6 / peaks["hbm_gbs"]}},
         }
+        if extras:
+            extras["gpt2_small_fwd_bf16"]["tokens_per_s_all_gpus"] = world * 16 * 1024 / (gpt_ms * 1e-3)   # batch 16 per GPU (weak)
+            extras["llama_1b_fwd_bf16"]["tokens_per_s_all_gpus"] = 64 // world * world * 2048 / (llama_ms * 1e-3)  # batch 64 in total (strong)
+            line["extras"] = extras
+        if extras_error:
+            line["extras_error"] = extras_error
         if world == 1:
             line["cpu_baseline"] = run_cpu_baseline(h_logits.reshape(SM_SHAPE), h_x, h_g, h_b)
         print(json.dumps(line), flush=True)
@@ -370,12 +389,109 @@ def run_b200_arm(args, rank, local_rank, world):
         dist.destroy_process_group()
 
 
+# ----------------------------------------------------------- other configurations (extras) ---
+def run_extras(b200, backend, L, libmod, torch, stream, local_rank, world, peaks):
+    """DotGeneral sweep (TFLOP/s) and the two transformer forwards (tokens/s).  Reported next to the headline
+    metric; inputs and weights are seeded random tensors created on the device and wrapped as buffers."""
+    import go_darwinml_b200.workloads as W
+    dev = f"cuda:{local_rank}"
+    gen = torch.Generator(device=dev).manual_seed(1234 + local_rank)
+    out = {}
+
+    def timed(fn, iters, warmup=2):
+        for _ in range(warmup):
+            fn()
+        backend.Synchronize(local_rank)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(iters):
+            fn()
+        e1.record(stream)
+        backend.Synchronize(local_rank)
+        return e0.elapsed_time(e1) / iters
+
+    # --- DotGeneral sweep: [8,M,K]x[8,K,N] and [8,K,M]x[8,K,N], M=N=K in {1024,4096,8192}, bf16 and fp32 ---
+    sweep = {}
+    for dt_name, tdt, code in (("bf16", torch.bfloat16, 6), ("f32", torch.float32, 7)):
+        for n in (1024, 4096, 8192):
+            a = torch.randn(8, n, n, generator=gen, device=dev, dtype=torch.float32).to(tdt)
+            b = torch.randn(8, n, n, generator=gen, device=dev, dtype=torch.float32).to(tdt)
+            c = torch.empty(8, n, n, device=dev, dtype=tdt)
+            for form, a_kmajor in (("BMK_BKN", 1), ("BKM_BKN", 0)):
+                def launch():
+                    e = libmod.B200Error()
+                    if not L.b200_k_gemm(local_rank, a.data_ptr(), b.data_ptr(), c.data_ptr(), 8, n, n, n, a_kmajor, 0, code, None, 0,
+                                         ctypes.byref(e)):
+                        raise RuntimeError(L.take_string(e.message))
+                ms = timed(launch, 3 if n == 8192 else 10)
+                tf = 2 * 8 * n ** 3 / (ms * 1e-3) / 1e12
+                sweep[f"{dt_name}_{form}_{n}"] = {"ms": ms, "TFLOP/s": tf, "frac_of_bf16_peak": tf / peaks["bf16_tflops"]}
+            del a, b, c
+    out["dot_general_sweep"] = sweep
+
+    def model_tokens_per_s(name, cfg, shapes, forward, flops_per_token, iters):
+        bufs, keep = [], []
+        for pname, shape in shapes:
+            if pname == "ids":
+                t = torch.randint(0, cfg.vocab, shape, generator=gen, device=dev, dtype=torch.int32)
+                code = int(b200.dtypes.Int32)
+            elif pname in ("rope_cos", "rope_sin"):
+                cos, sin = W.rope_tables(cfg)
+                t = torch.from_numpy(cos if pname == "rope_cos" else sin).to(dev).to(torch.bfloat16)
+                code = int(b200.dtypes.BFloat16)
+            elif pname.endswith("_g"):
+                t = torch.ones(shape, device=dev, dtype=torch.bfloat16)
+                code = int(b200.dtypes.BFloat16)
+            elif pname.split(".")[-1].startswith("b") or pname.endswith("_b"):
+                t = torch.zeros(shape, device=dev, dtype=torch.bfloat16)
+                code = int(b200.dtypes.BFloat16)
+            else:
+                t = (0.02 * torch.randn(shape, generator=gen, device=dev, dtype=torch.float32)).to(torch.bfloat16)
+                code = int(b200.dtypes.BFloat16)
+            keep.append(t)
+            e = libmod.B200Error()
+            h = L.b200_buffer_wrap(local_rank, t.data_ptr(), code, (ctypes.c_int64 * max(len(shape), 1))(*shape), len(shape), ctypes.byref(e))
+            bufs.append(b200.Buffer(h))
+        dts = [np.dtype(np.int32) if n == "ids" else np.dtype(ml_dtypes_bf16()) for n, _ in shapes]
+        torch.cuda.synchronize()
+        builder, exe = W.build_executable(b200, backend, name, [(s, d) for (_, s), d in zip(shapes, dts)], forward)
+
+        def run():
+            for o in exe.Execute(bufs, None, local_rank):
+                backend.BufferFinalize(o)
+        ms = timed(run, iters, warmup=1)
+        tokens = cfg.batch * cfg.seq
+        res = {"ms_per_forward": ms, "tokens_per_s_this_gpu": tokens / (ms * 1e-3), "batch_this_gpu": cfg.batch,
+               "launches_per_forward": exe.NumLaunches(), "TFLOP/s": tokens * flops_per_token / (ms * 1e-3) / 1e12,
+               "arena_GiB": L.b200_exec_arena_bytes(exe.handle) / 2 ** 30}
+        exe.Finalize()
+        builder.Finalize()
+        L.b200_device_trim(local_rank)
+        return res
+
+    g = W.GPT2Config()
+    out["gpt2_small_fwd_bf16"] = model_tokens_per_s("gpt2", g, W.gpt2_param_shapes(g),
+                                                   lambda f, *p: W.gpt2_forward(f, g, int(b200.dtypes.BFloat16), *p),
+                                                   W.gpt2_flops_per_token(g), 3)
+    lc = W.LlamaConfig(batch=64 // world)  # batch 64 sharded by batch across the GPUs
+    out["llama_1b_fwd_bf16"] = model_tokens_per_s("llama", lc, W.llama_param_shapes(lc),
+                                                 lambda f, *p: W.llama_forward(f, lc, int(b200.dtypes.BFloat16), *p),
+                                                 W.llama_flops_per_token(lc), 2)
+    return out
+
+
+def ml_dtypes_bf16():
+    import ml_dtypes
+    return ml_dtypes.bfloat16
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the DotGeneral sweep and the transformer forwards")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
