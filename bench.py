@@ -341,10 +341,8 @@ def run_b200_arm(args, rank, local_rank, world):
     llama_ms = extras["llama_1b_fwd_bf16"]["ms_per_forward"] if extras else 0.0
 
     # max over ranks, on device-measured times
-    times = torch.tensor([elapsed_ms, e2e_ms, gpt_ms, llama_ms], dtype=torch.float64, device=f"cuda:{local_rank}")
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms, gpt_ms, llama_ms = (float(t) for t in times)
+    from go_darwinml_b200.sharding import max_over_ranks
+    elapsed_ms, e2e_ms, gpt_ms, llama_ms = max_over_ranks([elapsed_ms, e2e_ms, gpt_ms, llama_ms], device=f"cuda:{local_rank}")
 
     if rank == 0:
         peaks, peak_src = measured_peaks()

@@ -51,7 +51,8 @@ constexpr int STAGES = 4;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
 constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int EPI_STAGE_FLOATS = 32 * 33;     // per epilogue warp: a 32 x 32 fp32 block, rows padded to 33 words
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + 4 * EPI_STAGE_FLOATS * 4;
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
@@ -252,6 +253,11 @@ __device__ __forceinline__ void store_chunk<__half>(const TcArgs& g, __half* cro
   }
 }
 
+template <typename OutT> __device__ __forceinline__ void store_one(OutT* p, float v);
+template <> __device__ __forceinline__ void store_one<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store_one<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ void store_one<__half>(__half* p, float v) { *p = __float2half_rn(v); }
+
 template <typename OutT> __device__ __forceinline__ float load_bias(const void* bias, int64_t col) {
   return 0.f;
 }
@@ -275,6 +281,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   uint64_t* acc_full = bars + 2 * STAGES;   // [2]       accumulator complete
   uint64_t* acc_empty = bars + 2 * STAGES + 2;  // [2]   accumulator drained by the epilogue
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  float* epi_stage = reinterpret_cast<float*>(tiles + STAGES * STAGE_BYTES + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* err = g.err_flag;
@@ -409,7 +416,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = apply_activation(g.activation, v[j]);
         }
-        if (row < g.M) store_chunk<OutT>(g, crow, col0, v);
+        if (g.vec_store) {
+          if (row < g.M) store_chunk<OutT>(g, crow, col0, v);
+        } else {
+          // Rows of C do not start 16-byte aligned (N is not a multiple of the vector width): transpose the
+          // 32 x 32 block through shared memory so that a warp writes 32 CONSECUTIVE columns of one row per store.
+          float* st = epi_stage + (warp - 2) * EPI_STAGE_FLOATS;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) st[lane * 33 + j] = v[j];
+          __syncwarp();
+          const int64_t row_base = (int64_t)m_t * BM + quarter * 32;
+          const int64_t col = col0 + lane;
+          OutT* cb = reinterpret_cast<OutT*>(g.c) + ((int64_t)b * g.M + row_base) * g.ldc + col;
+          for (int r = 0; r < 32; ++r)
+            if (row_base + r < g.M && col < g.N) store_one<OutT>(cb + (int64_t)r * g.ldc, st[r * 33 + lane]);
+          __syncwarp();
+        }
       }
       tc_fence_before();
       __syncwarp();

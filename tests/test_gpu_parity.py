@@ -474,3 +474,29 @@ def test_intermediates_share_arena_memory(b200, backend):
     one = 256 * 256 * 4
     assert b200.lib().b200_exec_arena_bytes(exe.handle) <= 2 * one + 1024
     assert exe.NumLaunches() == 8
+
+
+def test_dot_general_unaligned_n_uses_tensor_cores(b200, backend):
+    # N = 1003 is not a multiple of 8: rows of C are not 16-byte aligned; B is [N, K] so its rows still are
+    rng = np.random.default_rng(36)
+    a, b = rng_array(rng, (300, 128), BF16), rng_array(rng, (1003, 128), BF16)
+    assert_parity(b200, backend, lambda f, x, y: f.DotGeneral(x, [1], [], y, [1], []), [a, b], rtol=BF16_RTOL, atol_scale=1.0)
+    a32, b32 = a.astype(np.float32), b.astype(np.float32)
+    assert_parity(b200, backend, lambda f, x, y: f.DotGeneral(x, [1], [], y, [1], []), [a32, b32], rtol=F32_RTOL, atol_scale=1.0)
+
+
+def test_batch_sharded_runner_matches_single_device(b200, backend):
+    from go_darwinml_b200.sharding import BatchShardedRunner
+    import ctypes
+    from go_darwinml_b200 import _lib
+    err = _lib.B200Error()
+    ndev = b200.lib().b200_device_count(ctypes.byref(err))
+    rng = np.random.default_rng(37)
+    x, w = rng_array(rng, (6, 40, 64), np.float32), rng_array(rng, (64, 48), np.float32)
+    build = lambda f, xx, ww: f.FusedSoftmax(f.FusedDense(xx, ww, None, 0), 2)
+    single = run_backend(b200, backend, build, [x, w])[0]
+    devices = [0, 1] if ndev >= 2 else [0, 0]   # two replicas; on a one-GPU box both live on device 0
+    runner = BatchShardedRunner(b200, devices, build, [(x.shape, x.dtype), (w.shape, w.dtype)], [True, False])
+    got = runner([x, w])[0]
+    runner.close()
+    np.testing.assert_array_equal(got, single)   # replicas run the same kernels: bit-identical
