@@ -350,11 +350,10 @@ def run_b200_arm(args, rank, local_rank, world):
         value = world * STEP_BYTES / (ms_per_step * 1e-3) / 1e9
         e2e_value = world * STEP_BYTES / (e2e_ms / e2e_steps * 1e-3) / 1e9
         achieved = SM_BYTES / (sm_ms * 1e-3) / 1e9
-        traffic_path = os.path.join(ROOT, "profiles", "softmax_traffic.json")
-        traffic = None
-        if os.path.exists(traffic_path):
-            with open(traffic_path) as fh:
-                traffic = json.load(fh).get("dram_bytes_per_launch_full_workload")
+        # dram__bytes_read.sum + dram__bytes_write.sum of the causal softmax kernel, captured with ncu on 131072 rows
+        # (276.9 MB + 479.1 MB per launch) and scaled x4 to the 524288-row launch; rows are independent, so traffic is
+        # proportional to the row count (profiles/softmax_causal_f32_rows131072x1024.md)
+        traffic = 4 * (276888064 + 479067648)
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
