@@ -427,30 +427,7 @@ def run_extras(b200, backend, L, libmod, torch, stream, local_rank, world, peaks
     out["dot_general_sweep"] = sweep
 
     def model_tokens_per_s(name, cfg, shapes, forward, flops_per_token, iters):
-        bufs, keep = [], []
-        for pname, shape in shapes:
-            if pname == "ids":
-                t = torch.randint(0, cfg.vocab, shape, generator=gen, device=dev, dtype=torch.int32)
-                code = int(b200.dtypes.Int32)
-            elif pname in ("rope_cos", "rope_sin"):
-                cos, sin = W.rope_tables(cfg)
-                t = torch.from_numpy(cos if pname == "rope_cos" else sin).to(dev).to(torch.bfloat16)
-                code = int(b200.dtypes.BFloat16)
-            elif pname.endswith("_g"):
-                t = torch.ones(shape, device=dev, dtype=torch.bfloat16)
-                code = int(b200.dtypes.BFloat16)
-            elif pname.split(".")[-1].startswith("b") or pname.endswith("_b"):
-                t = torch.zeros(shape, device=dev, dtype=torch.bfloat16)
-                code = int(b200.dtypes.BFloat16)
-            else:
-                t = (0.02 * torch.randn(shape, generator=gen, device=dev, dtype=torch.float32)).to(torch.bfloat16)
-                code = int(b200.dtypes.BFloat16)
-            keep.append(t)
-            e = libmod.B200Error()
-            h = L.b200_buffer_wrap(local_rank, t.data_ptr(), code, (ctypes.c_int64 * max(len(shape), 1))(*shape), len(shape), ctypes.byref(e))
-            bufs.append(b200.Buffer(h))
-        dts = [np.dtype(np.int32) if n == "ids" else np.dtype(ml_dtypes_bf16()) for n, _ in shapes]
-        torch.cuda.synchronize()
+        bufs, dts, keep = W.make_device_params(b200, torch, shapes, cfg, local_rank)
         builder, exe = W.build_executable(b200, backend, name, [(s, d) for (_, s), d in zip(shapes, dts)], forward)
 
         def run():

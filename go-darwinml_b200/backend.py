@@ -681,6 +681,20 @@ class Executable:
         _check(err, "Execute")
         return [Buffer(outs[i]) for i in range(len(self.output_shapes))]
 
+    def ExecuteProfiled(self, inputs: Sequence[Buffer]):
+        """Execute with every step of the launch plan timed by CUDA events; returns (outputs, report text)."""
+        hs = [b._h() for b in inputs]
+        ins = (ctypes.c_void_p * max(len(hs), 1))(*hs)
+        outs = (ctypes.c_void_p * max(len(self.output_shapes), 1))()
+        cap = 1 << 20
+        buf = ctypes.create_string_buffer(cap)
+        err = _lib.B200Error()
+        with self._mu:
+            self._L.b200_execute_profiled(self.handle, ins, len(hs), outs, len(self.output_shapes), ctypes.cast(buf, ctypes.c_void_p), cap,
+                                          ctypes.byref(err))
+        _check(err, "ExecuteProfiled")
+        return [Buffer(outs[i]) for i in range(len(self.output_shapes))], buf.value.decode()
+
     def ExecuteHost(self, inputs: Sequence[np.ndarray]) -> List[np.ndarray]:
         """Host arrays in, host arrays out, through b200_execute_host: the calling shape of the
         reference's native execute (ref bridge.h:167-172), copies and wait included."""

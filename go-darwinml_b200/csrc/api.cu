@@ -290,6 +290,22 @@ bool b200_k_gemm(int device, const void* a, const void* b, void* c, int64_t batc
   return true;
 }
 
+bool b200_k_attention(int device, const void* q, const void* k_, const void* v, void* o, int64_t batch, int64_t heads, int64_t kv_heads,
+                      int64_t seq_q, int64_t seq_k, int64_t head_dim, int bshd, int causal, double scale, int dtype, B200Error* err) {
+  clear_error(err);
+  Device* dev;
+  Status s = Device::Get(device, &dev);
+  if (s.ok()) {
+    k::AttentionParams p;
+    p.q = q; p.k = k_; p.v = v; p.o = o;
+    p.B = batch; p.H = heads; p.Hkv = kv_heads; p.Sq = seq_q; p.Sk = seq_k; p.head_dim = head_dim;
+    p.bshd = bshd != 0; p.causal = causal != 0; p.scale = scale; p.dtype = dtype;
+    s = k::attention(dev, p);
+  }
+  if (!s.ok()) { set_error(err, s); return false; }
+  return true;
+}
+
 int64_t b200_k_reduce_sum_scratch_bytes(int64_t n) { return k::reduce_scratch_bytes(B200_FLOAT32, 1, n, 1); }
 
 bool b200_k_reduce_sum_f32(int device, const float* x, float* out, int64_t n, void* scratch, int64_t scratch_bytes, B200Error* err) {

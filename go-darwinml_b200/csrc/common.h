@@ -153,7 +153,7 @@ enum class Op : int {
   // contraction / reduction / indexing
   DotGeneral, Reduce, ArgMinMax, Gather,
   // fused
-  Softmax, SoftmaxMasked, LayerNorm, RmsNorm,
+  Softmax, SoftmaxMasked, LayerNorm, RmsNorm, Attention,
   kNumOps
 };
 const char* op_name(Op op);

@@ -26,7 +26,7 @@ const char* op_name(Op op) {
       "Where", "Clamp",
       "Cast", "Reshape", "Transpose", "BroadcastInDim", "Slice", "Concatenate", "Reverse", "Pad",
       "DotGeneral", "Reduce", "ArgMinMax", "Gather",
-      "Softmax", "SoftmaxMasked", "LayerNorm", "RmsNorm"};
+      "Softmax", "SoftmaxMasked", "LayerNorm", "RmsNorm", "Attention"};
   static_assert(sizeof(names) / sizeof(names[0]) == (size_t)Op::kNumOps, "op_name table out of date");
   return names[(int)op];
 }
@@ -931,6 +931,32 @@ bool b200_attention_qkv_projection(B200Context ctx, B200Value x, B200Value w_qkv
   if (!combined) return false;
   Node* cn = reinterpret_cast<Node*>(combined);
   const int r = cn->rank();
+  // When every bias present is a plain vector of the right length, the three biases become ONE vector added in the
+  // GEMM epilogue (absent ones are zeros), instead of three separate elementwise adds after the slices.
+  bool fold = (bias_q || bias_k || bias_v) && (cn->dtype == B200_FLOAT32 || cn->dtype == B200_BFLOAT16 || cn->dtype == B200_FLOAT16);
+  const int64_t want[3] = {query_dim, key_value_dim, key_value_dim};
+  B200Value biases[3] = {bias_q, bias_k, bias_v};
+  for (int i = 0; i < 3 && fold; ++i) {
+    if (!biases[i]) continue;
+    Node* bn;
+    Status bs = check_node(ctx, biases[i], "FusedAttentionQKVProjection: bias", &bn);
+    if (!bs.ok()) { set_error(err, bs); return false; }
+    fold = bn->rank() == 1 && bn->dims[0] == want[i] && bn->dtype == cn->dtype;
+  }
+  if (fold) {
+    Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+    B200Value parts[3];
+    for (int i = 0; i < 3; ++i) {
+      if (biases[i]) { parts[i] = biases[i]; continue; }
+      Node* z = g.Add(Op::Constant, cn->dtype, {want[i]}, {});
+      z->data.assign((size_t)want[i] * dtype_size(cn->dtype), 0);
+      parts[i] = reinterpret_cast<B200Value>(z);
+    }
+    B200Value all = b200_concatenate(ctx, parts, 3, 0, err);
+    if (!all) return false;
+    cn->in.push_back(reinterpret_cast<Node*>(all));
+    bias_q = bias_k = bias_v = nullptr;
+  }
   auto part = [&](int64_t lo, int64_t hi, B200Value bias, B200Value* out) -> bool {
     std::vector<int64_t> st(r, 0), en(cn->dims), sd(r, 1);
     st[r - 1] = lo;
@@ -971,6 +997,21 @@ B200Value b200_scaled_dot_product_attention(B200Context ctx, B200Value query, B2
   if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
     return ret(err, Status::Invalid(strfmt("SDPA: numHeads (%d) must be positive and divisible by numKVHeads (%d)", num_heads, num_kv_heads)), nullptr);
   const bool bshd = axes_layout == B200_LAYOUT_BSHD;
+  // Fused path: no mask tensor, head dim 64, 16-bit floats.  One kernel reads Q, K and V in the layout they come
+  // in; neither the scores, nor a mask, nor repeated K/V heads, nor a transposed copy is ever written.
+  {
+    const int s_ax = bshd ? 1 : 2, h_ax = bshd ? 2 : 1;
+    const bool shapes_ok = k->dims == v->dims && q->dims[0] == k->dims[0] && q->dims[3] == k->dims[3] &&
+                           q->dims[h_ax] == num_heads && k->dims[h_ax] == num_kv_heads && q->dtype == k->dtype && q->dtype == v->dtype;
+    if (!shapes_ok) return ret(err, Status::Invalid("SDPA: query / key / value shapes, dtypes or head counts do not agree"), nullptr);
+    if (!m && q->dims[3] == 64 && (q->dtype == B200_BFLOAT16 || q->dtype == B200_FLOAT16) && q->dims[s_ax] > 0 && k->dims[s_ax] > 0) {
+      Graph& gr = reinterpret_cast<Ctx*>(ctx)->graph;
+      Node* o = gr.Add(Op::Attention, q->dtype, q->dims, {q, k, v});
+      o->ia = {num_heads, num_kv_heads, bshd ? 1 : 0, causal ? 1 : 0};
+      o->fa = {scale};
+      return ret(err, Status::OK(), o);
+    }
+  }
   // Work in BHSD like the reference (function.go:2697-2726).
   const int perm[4] = {0, 2, 1, 3};
   B200Value Q = query, K = key, V = value, M = mask;

@@ -155,5 +155,25 @@ struct GemmParams {
 };
 Status gemm(Device* dev, const GemmParams& p);
 
+// ------------------------------------------------------------- attention ---
+// softmax(scale * Q K^T [+ causal mask]) V for Q [B, Sq, H, D] / K, V [B, Sk, Hkv, D] (bshd) or [B, H, Sq, D] (bhsd);
+// O has Q's layout.  Query head h reads KV head h / (H / Hkv).
+struct AttentionParams {
+  const void* q = nullptr;
+  const void* k = nullptr;
+  const void* v = nullptr;
+  void* o = nullptr;
+  int64_t B = 0, H = 0, Hkv = 0, Sq = 0, Sk = 0, head_dim = 0;
+  bool bshd = true;
+  bool causal = false;
+  double scale = 1.0;
+  int dtype = B200_BFLOAT16;
+  // Optional element strides (batch, head, sequence) per input; 0 = dense in the stated layout.  Lets Q, K and V be
+  // read straight out of a wider buffer, e.g. the three column blocks of a fused QKV projection.
+  int64_t q_strides[3] = {0, 0, 0}, k_strides[3] = {0, 0, 0}, v_strides[3] = {0, 0, 0};
+};
+bool attention_supported(const AttentionParams& p);
+Status attention(Device* dev, const AttentionParams& p);
+
 }  // namespace k
 }  // namespace b200

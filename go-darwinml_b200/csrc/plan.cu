@@ -278,6 +278,7 @@ class Planner {
       case Op::Softmax: return EmitSoftmax(x);
       case Op::SoftmaxMasked: return EmitSoftmaxMasked(x);
       case Op::LayerNorm: case Op::RmsNorm: return EmitNorm(x);
+      case Op::Attention: return EmitAttention(x);
       case Op::Concatenate: return EmitConcatenate(x);
       case Op::Pad: return EmitPad(x);
       case Op::Transpose: case Op::Slice: case Op::Reverse: case Op::BroadcastInDim:
@@ -735,14 +736,45 @@ class Planner {
 
   Status EmitConcatenate(Node* x) {
     if (x->rank() > k::kMaxDims) return Status::Unsupported("compile: more than 8 dims");
-    for (Node* in : x->in) B200_TRY(EnsureMaterialized(in));
+    // An operand that is a not-yet-stored Slice of something in memory is copied straight from its source.
+    auto direct_slice = [&](Node* in) {
+      return in->op == Op::Slice && slot_of_[in->id] < 0 && uses_[in->id] == 1;
+    };
+    for (Node* in : x->in) B200_TRY(EnsureMaterialized(direct_slice(in) ? in->in[0] : in));
     const int out_slot = NewValueSlot(x);
     const int ax = (int)x->ia[0];
     int64_t pos = 0;
     for (Node* in : x->in) {
       std::vector<int64_t> start(x->rank(), 0);
       start[ax] = pos;
-      EmitBlockCopy(in, out_slot, x->dims, start, "Concatenate");
+      if (direct_slice(in)) {
+        Node* src = in->in[0];
+        k::StridedCopyParams p;
+        p.elt_size = dtype_size(in->dtype);
+        p.rank = in->rank();
+        const std::vector<int64_t> cs = dense_strides(src->dims), os = dense_strides(x->dims);
+        for (int d = 0; d < in->rank(); ++d) {
+          p.dims[d] = in->dims[d];
+          p.in_strides[d] = cs[d] * in->ia[2 * d + 1];
+          p.in_offset += cs[d] * in->ia[2 * d];
+          p.out_strides[d] = os[d];
+          p.out_offset += os[d] * start[d];
+        }
+        const int in_slot = SlotOf(src);
+        Step st;
+        st.desc = "move[Concatenate of Slice]";
+        st.reads = {in_slot};
+        st.writes = {out_slot};
+        st.run = [p, in_slot, out_slot](Device* dev, void* const* ptrs) -> Status {
+          k::StridedCopyParams q = p;
+          q.x = ptrs[in_slot];
+          q.y = ptrs[out_slot];
+          return k::strided_copy(dev, q);
+        };
+        ex_->steps.push_back(std::move(st));
+      } else {
+        EmitBlockCopy(in, out_slot, x->dims, start, "Concatenate");
+      }
       pos += in->dims[ax];
     }
     return Status::OK();
@@ -1154,6 +1186,87 @@ class Planner {
     return Status::OK();
   }
 
+  // Recognises t = Reshape[B,S,H,D](Slice(X[B,S,W], last axis [lo, lo + H*D))) with X in (or going to) memory:
+  // the attention kernel can then read t in place inside X.  Fills the source node, the element offset and the
+  // (batch, head, sequence) strides.
+  bool StridedProjectionView(Node* t, bool bshd, Node** src, int64_t* offset, int64_t strides[3]) {
+    if (!bshd || t->op != Op::Reshape || t->rank() != 4) return false;
+    Node* sl = t->in[0];
+    if (sl->op != Op::Slice || sl->rank() != 3) return false;
+    Node* X = sl->in[0];
+    if (X->rank() != 3 || slot_of_[ViewBase(sl)->id] >= 0) return false;  // already copied: nothing to gain
+    for (int d = 0; d < 3; ++d)
+      if (sl->ia[2 * d + 1] != 1) return false;
+    if (sl->ia[0] != 0 || sl->ia[2] != 0 || sl->dims[0] != X->dims[0] || sl->dims[1] != X->dims[1]) return false;
+    const int64_t B = t->dims[0], S = t->dims[1], H = t->dims[2], D = t->dims[3], W = X->dims[2];
+    if (sl->dims[0] != B || sl->dims[1] != S || sl->dims[2] != H * D) return false;
+    const int64_t lo = sl->ia[4];
+    if (lo % 8 != 0 || W % 8 != 0) return false;  // TMA: 16-byte aligned base and pitches
+    Node* base = ViewBase(X);
+    if (!(base->op == Op::Parameter || slot_of_[base->id] >= 0 || MustMaterialize(base))) return false;
+    *src = X;
+    *offset = lo;
+    strides[0] = S * W;
+    strides[1] = D;
+    strides[2] = W;
+    return true;
+  }
+
+  Status EmitAttention(Node* x) {
+    Node* q = x->in[0];
+    Node* kk = x->in[1];
+    Node* v = x->in[2];
+    const bool bshd = x->ia[2] != 0;
+    Node* srcs[3] = {q, kk, v};
+    int64_t offs[3] = {0, 0, 0};
+    int64_t strd[3][3] = {{0, 0, 0}, {0, 0, 0}, {0, 0, 0}};
+    if (x->dtype == B200_BFLOAT16 || x->dtype == B200_FLOAT16) {
+      for (int i = 0; i < 3; ++i) {
+        Node* src;
+        int64_t off, st3[3];
+        if (StridedProjectionView(srcs[i], bshd, &src, &off, st3)) {
+          srcs[i] = src;
+          offs[i] = off;
+          for (int j = 0; j < 3; ++j) strd[i][j] = st3[j];
+        }
+      }
+    }
+    B200_TRY(EnsureMaterialized(srcs[0]));
+    B200_TRY(EnsureMaterialized(srcs[1]));
+    B200_TRY(EnsureMaterialized(srcs[2]));
+    k::AttentionParams ap;
+    ap.B = q->dims[0];
+    ap.H = x->ia[0];
+    ap.Hkv = x->ia[1];
+    ap.Sq = q->dims[bshd ? 1 : 2];
+    ap.Sk = kk->dims[bshd ? 1 : 2];
+    ap.head_dim = q->dims[3];
+    ap.bshd = bshd;
+    ap.causal = x->ia[3] != 0;
+    ap.scale = x->fa[0];
+    ap.dtype = x->dtype;
+    for (int j = 0; j < 3; ++j) { ap.q_strides[j] = strd[0][j]; ap.k_strides[j] = strd[1][j]; ap.v_strides[j] = strd[2][j]; }
+    const int qs = SlotOf(srcs[0]), ks = SlotOf(srcs[1]), vs = SlotOf(srcs[2]), os = NewValueSlot(x);
+    const int64_t es = dtype_size(x->dtype);
+    const int64_t qo = offs[0] * es, ko = offs[1] * es, vo = offs[2] * es;
+    Step st;
+    st.desc = strfmt("attention[B=%lld H=%lld Hkv=%lld Sq=%lld Sk=%lld D=%lld %s %s causal=%d]", (long long)ap.B, (long long)ap.H,
+                     (long long)ap.Hkv, (long long)ap.Sq, (long long)ap.Sk, (long long)ap.head_dim, dtype_name(ap.dtype),
+                     bshd ? "BSHD" : "BHSD", (int)ap.causal);
+    st.reads = {qs, ks, vs};
+    st.writes = {os};
+    st.run = [ap, qs, ks, vs, os, qo, ko, vo](Device* dev, void* const* p) -> Status {
+      k::AttentionParams a = ap;
+      a.q = (const char*)p[qs] + qo;
+      a.k = (const char*)p[ks] + ko;
+      a.v = (const char*)p[vs] + vo;
+      a.o = p[os];
+      return k::attention(dev, a);
+    };
+    ex_->steps.push_back(std::move(st));
+    return Status::OK();
+  }
+
   // A [cols] vector for gamma / beta: the parameter itself when it already is
   // one, else a broadcast copy laid over the normalised axes.
   Status NormParamSlot(Node* x, Node* p, const std::vector<int64_t>& axes, int64_t cols, int* slot) {
@@ -1386,7 +1499,33 @@ int64_t b200_exec_describe(B200Exec exec, char* buf, int64_t cap) {
   return (int64_t)s.size();
 }
 
+static bool execute_impl(B200Exec exec, const B200Buffer* inputs, int num_inputs, B200Buffer* outputs, int num_outputs,
+                         std::vector<float>* step_ms, B200Error* err);
+
 bool b200_execute(B200Exec exec, const B200Buffer* inputs, int num_inputs, B200Buffer* outputs, int num_outputs, B200Error* err) {
+  return execute_impl(exec, inputs, num_inputs, outputs, num_outputs, nullptr, err);
+}
+
+int64_t b200_execute_profiled(B200Exec exec, const B200Buffer* inputs, int num_inputs, B200Buffer* outputs, int num_outputs, char* report,
+                              int64_t cap, B200Error* err) {
+  std::vector<float> ms;
+  if (!execute_impl(exec, inputs, num_inputs, outputs, num_outputs, &ms, err)) return -1;
+  Exec* ex = reinterpret_cast<Exec*>(exec);
+  std::string s;
+  double total = 0;
+  for (float v : ms) total += v;
+  for (size_t i = 0; i < ms.size(); ++i) s += strfmt("%9.4f ms  %5.1f%%  ", ms[i], total > 0 ? 100.0 * ms[i] / total : 0.0) + ex->steps[i].desc + "\n";
+  s += strfmt("%9.4f ms  total of %d steps\n", total, (int)ms.size());
+  if (report && cap > 0) {
+    const int64_t n = std::min<int64_t>(cap - 1, (int64_t)s.size());
+    memcpy(report, s.data(), (size_t)n);
+    report[n] = 0;
+  }
+  return (int64_t)s.size();
+}
+
+static bool execute_impl(B200Exec exec, const B200Buffer* inputs, int num_inputs, B200Buffer* outputs, int num_outputs,
+                         std::vector<float>* step_ms, B200Error* err) {
   clear_error(err);
   Exec* ex = reinterpret_cast<Exec*>(exec);
   if (!ex) { set_error(err, Status::Invalid("Execute: null executable")); return false; }
@@ -1434,9 +1573,26 @@ bool b200_execute(B200Exec exec, const B200Buffer* inputs, int num_inputs, B200B
     if (sl.kind == SlotKind::Arena) ptrs[s] = (char*)ex->arena + sl.offset;
     else if (sl.kind == SlotKind::Const) ptrs[s] = ex->const_ptrs[sl.index];
   }
+  std::vector<cudaEvent_t> events;
+  if (step_ms) {
+    events.resize(ex->steps.size() + 1);
+    for (auto& e : events) cudaEventCreate(&e);
+    cudaEventRecord(events[0], ex->dev->stream());
+  }
+  size_t si = 0;
   for (auto& st : ex->steps) {
     Status s = st.run(ex->dev, ptrs.data());
-    if (!s.ok()) return fail(Status{s.code, st.desc + ": " + s.msg});
+    if (!s.ok()) {
+      for (auto& e : events) cudaEventDestroy(e);
+      return fail(Status{s.code, st.desc + ": " + s.msg});
+    }
+    if (step_ms) cudaEventRecord(events[++si], ex->dev->stream());
+  }
+  if (step_ms) {
+    cudaStreamSynchronize(ex->dev->stream());
+    step_ms->resize(ex->steps.size());
+    for (size_t i = 0; i < ex->steps.size(); ++i) cudaEventElapsedTime(&(*step_ms)[i], events[i], events[i + 1]);
+    for (auto& e : events) cudaEventDestroy(e);
   }
   for (int i = 0; i < num_outputs; ++i) outputs[i] = outs[i];
   return true;

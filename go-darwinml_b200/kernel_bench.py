@@ -31,7 +31,7 @@ DT = {"f32": (7, 4), "bf16": (6, 2), "f16": (5, 2)}
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["softmax", "rmsnorm", "layernorm", "gemm"])
+    ap.add_argument("kernel", choices=["softmax", "rmsnorm", "layernorm", "gemm", "attention", "ewise"])
     ap.add_argument("--rows", type=int, default=65536)
     ap.add_argument("--cols", type=int, default=1024)
     ap.add_argument("--seq-q", type=int, default=0)
@@ -42,6 +42,11 @@ def main():
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--a-km", action="store_true", help="A stored [batch, K, M]")
     ap.add_argument("--b-nk", action="store_true", help="B stored [batch, N, K]")
+    ap.add_argument("--expr", default="add", choices=["add", "bias", "rope", "chain"], help="ewise: which fused chain to time")
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--bhsd", action="store_true")
     ap.add_argument("--dtype", default="f32", choices=list(DT))
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
@@ -93,6 +98,60 @@ def main():
             else:
                 check(L.b200_k_layer_norm(args.device, x.data_ptr(), g.data_ptr(), b.data_ptr(), y.data_ptr(), args.rows, args.cols, code, 1e-6,
                                           ctypes.byref(e)), e)
+    elif args.kernel == "ewise":
+        # a fused elementwise chain compiled through the graph layer (one launch); bytes = distinct inputs + output
+        npdt = {"f32": np.float32, "bf16": __import__("ml_dtypes").bfloat16, "f16": np.float16}[args.dtype]
+        S = lambda *d: b200.Shape(b200.dtypes.from_numpy(np.dtype(npdt)), d)
+        R, C = args.rows, args.cols
+        builder = backend.Builder("ewise")
+        f = builder.Main()
+        if args.expr == "add":
+            shapes = [(R, C), (R, C)]
+            ps = [f.Parameter(f"p{i}", S(*sh)) for i, sh in enumerate(shapes)]
+            y = f.Add(ps[0], ps[1])
+        elif args.expr == "bias":
+            shapes = [(R, C), (C,)]
+            ps = [f.Parameter(f"p{i}", S(*sh)) for i, sh in enumerate(shapes)]
+            y = f.Add(ps[0], f.BroadcastInDim(ps[1], S(R, C), [1]))
+        elif args.expr == "rope":
+            H, Dh = C // 64, 64
+            shapes = [(R, H, Dh), (R, H, Dh), (R, Dh), (R, Dh)]
+            ps = [f.Parameter(f"p{i}", S(*sh)) for i, sh in enumerate(shapes)]
+            cb = f.BroadcastInDim(ps[2], S(R, H, Dh), [0, 2])
+            sb = f.BroadcastInDim(ps[3], S(R, H, Dh), [0, 2])
+            y = f.Add(f.Mul(ps[0], cb), f.Mul(ps[1], sb))
+        else:
+            shapes = [(R, C), (C,), (C,)]
+            ps = [f.Parameter(f"p{i}", S(*sh)) for i, sh in enumerate(shapes)]
+            y = f.Tanh(f.Add(f.Mul(ps[0], f.BroadcastInDim(ps[1], S(R, C), [1])), f.BroadcastInDim(ps[2], S(R, C), [1])))
+        f.Return([y], None)
+        exe = builder.Compile()
+        tens = [rand(*sh) for sh in shapes]
+        bufs = []
+        for t, sh in zip(tens, shapes):
+            e = libmod.B200Error()
+            bufs.append(b200.Buffer(L.b200_buffer_wrap(args.device, t.data_ptr(), code, (ctypes.c_int64 * len(sh))(*sh), len(sh), ctypes.byref(e))))
+        work = (sum(t.numel() for t in tens) + R * C) * es
+        unit, kind = "GB/s", "hbm"
+        operand_bytes = work
+        print(exe.Describe().strip(), file=sys.stderr)
+
+        def launch():
+            for o in exe.Execute(bufs, None, args.device):
+                backend.BufferFinalize(o)
+    elif args.kernel == "attention":
+        B, H, Hkv, S = args.batch, args.heads, args.kv_heads, args.seq
+        shp = (lambda h: (B, h, S, 64)) if args.bhsd else (lambda h: (B, S, h, 64))
+        q, kk, v = rand(*shp(H)), rand(*shp(Hkv)), rand(*shp(Hkv))
+        o = torch.empty_like(q)
+        work = 4 * B * H * S * S * 64 * (0.5 if args.causal else 1.0)
+        unit, kind = "TFLOP/s", "tensor"
+        operand_bytes = (q.numel() * 2 + kk.numel() * 2) * es
+
+        def launch():
+            e = libmod.B200Error()
+            check(L.b200_k_attention(args.device, q.data_ptr(), kk.data_ptr(), v.data_ptr(), o.data_ptr(), B, H, Hkv, S, S, 64,
+                                     int(not args.bhsd), int(args.causal), 0.125, code, ctypes.byref(e)), e)
     else:
         B, M, N, K = args.batch, args.m, args.n, args.k
         a = rand(B, K, M) if args.a_km else rand(B, M, K)

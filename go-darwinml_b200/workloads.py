@@ -153,12 +153,15 @@ def llama_param_shapes(c: LlamaConfig):
 
 
 def rope_tables(c: LlamaConfig):
-    """cos / sin of position * theta^(-2i/D), both halves of the head dim (rotate-half form)."""
+    """cos and SIGNED sin of position * theta^(-2i/D) over both halves of the head dim (rotate-half form):
+    rope(x) = x * cos + swap_halves(x) * sin_signed, with sin_signed = concat(-sin, sin), which equals the usual
+    x * cos + concat(-x2, x1) * sin exactly (the sign moves from the activations into the table)."""
     D = c.d_model // c.heads
     inv = c.rope_theta ** (-np.arange(0, D, 2, dtype=np.float64) / D)
     ang = np.arange(c.seq, dtype=np.float64)[:, None] * inv[None, :]
-    ang = np.concatenate([ang, ang], axis=1)
-    return np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+    cos = np.concatenate([np.cos(ang), np.cos(ang)], axis=1)
+    sin_signed = np.concatenate([-np.sin(ang), np.sin(ang)], axis=1)
+    return cos.astype(np.float32), sin_signed.astype(np.float32)
 
 
 def llama_init(c: LlamaConfig, seed=0, float_dtype=None):
@@ -176,12 +179,12 @@ def llama_init(c: LlamaConfig, seed=0, float_dtype=None):
 
 
 def _rope(f, x, cos_b, sin_b, dims, half):
-    """x * cos + rotate_half(x) * sin, rotate_half(x) = concat(-x[half:], x[:half]) on the last axis."""
+    """x * cos + swap_halves(x) * sin_signed on the last axis (see rope_tables)."""
     r = len(dims)
     lo = f.Slice(x, [0] * r, dims[:-1] + [half], [1] * r)
     hi = f.Slice(x, [0] * (r - 1) + [half], dims, [1] * r)
-    rot = f.Concatenate(r - 1, f.Neg(hi), lo)
-    return f.Add(f.Mul(x, cos_b), f.Mul(rot, sin_b))
+    swapped = f.Concatenate(r - 1, hi, lo)
+    return f.Add(f.Mul(x, cos_b), f.Mul(swapped, sin_b))
 
 
 def llama_forward(f, c: LlamaConfig, dtype_code, *params):
@@ -192,10 +195,11 @@ def llama_forward(f, c: LlamaConfig, dtype_code, *params):
     D = d // H
     kv = Hkv * D
     x = f.Gather(embed, ids, 2, [2], [0], [0], [1, d], False)                     # [B, S, d]
-    cos_q = f.BroadcastInDim(cos, _Shape(dtype_code, (B, S, H, D)), [1, 3])
-    sin_q = f.BroadcastInDim(sin, _Shape(dtype_code, (B, S, H, D)), [1, 3])
-    cos_k = f.BroadcastInDim(cos, _Shape(dtype_code, (B, S, Hkv, D)), [1, 3])
-    sin_k = f.BroadcastInDim(sin, _Shape(dtype_code, (B, S, Hkv, D)), [1, 3])
+    # tables spread over the heads once ([S, Hx, D], a few MB), then broadcast over the batch inside each fused chain
+    def table(t, hx):
+        per_head = f.BroadcastInDim(t, _Shape(dtype_code, (S, hx, D)), [0, 2])
+        return f.BroadcastInDim(per_head, _Shape(dtype_code, (B, S, hx, D)), [1, 2, 3])
+    cos_q, sin_q, cos_k, sin_k = table(cos, H), table(sin, H), table(cos, Hkv), table(sin, Hkv)
     for _ in range(c.layers):
         norm1_g, wqkv, wo, norm2_g, wgate, wup, wdown = (next(it) for _ in range(7))
         h = f.FusedRMSNorm(x, [-1], c.eps, norm1_g)
@@ -228,3 +232,41 @@ def build_executable(pkg, backend, name, shapes_and_dtypes, forward):
     out = forward(f, *params)
     f.Return(list(out) if isinstance(out, (list, tuple)) else [out], None)
     return builder, builder.Compile()
+
+
+def make_device_params(pkg, torch, shapes, cfg, device: int, seed: int = 1234):
+    """Seeded random parameters created directly in device memory (torch is only the random source and the owner
+    of the allocations) and wrapped as backend buffers.  Returns (buffers, numpy dtypes, keep-alive list)."""
+    import ctypes
+
+    import ml_dtypes
+
+    from . import _lib
+    L = pkg.lib()
+    dev = f"cuda:{device}"
+    gen = torch.Generator(device=dev).manual_seed(seed + device)
+    bufs, dts, keep = [], [], []
+    for pname, shape in shapes:
+        if pname == "ids":
+            t = torch.randint(0, cfg.vocab, shape, generator=gen, device=dev, dtype=torch.int32)
+            code, npdt = int(pkg.dtypes.Int32), np.dtype(np.int32)
+        else:
+            code, npdt = int(pkg.dtypes.BFloat16), np.dtype(ml_dtypes.bfloat16)
+            if pname in ("rope_cos", "rope_sin"):
+                cos, sin = rope_tables(cfg)
+                t = torch.from_numpy(cos if pname == "rope_cos" else sin).to(dev).to(torch.bfloat16)
+            elif pname.endswith("_g"):
+                t = torch.ones(shape, device=dev, dtype=torch.bfloat16)
+            elif pname.split(".")[-1].startswith("b") or pname.endswith("_b"):
+                t = torch.zeros(shape, device=dev, dtype=torch.bfloat16)
+            else:
+                t = (0.02 * torch.randn(shape, generator=gen, device=dev, dtype=torch.float32)).to(torch.bfloat16)
+        keep.append(t)
+        err = _lib.B200Error()
+        h = L.b200_buffer_wrap(device, t.data_ptr(), code, (ctypes.c_int64 * max(len(shape), 1))(*shape), len(shape), ctypes.byref(err))
+        if err.code:
+            raise RuntimeError(L.take_string(err.message))
+        bufs.append(pkg.Buffer(h))
+        dts.append(npdt)
+    torch.cuda.synchronize()
+    return bufs, dts, keep

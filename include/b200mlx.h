@@ -277,6 +277,12 @@ int64_t b200_exec_describe(B200Exec exec, char* buf, int64_t cap);
  * Inputs are not consumed.  Executions of one B200Exec are serialised. */
 bool b200_execute(B200Exec exec, const B200Buffer* inputs, int num_inputs, B200Buffer* outputs, int num_outputs,
                   B200Error* err);
+/* Like b200_execute, but brackets every step of the launch plan with CUDA events, waits, and writes a
+ * NUL-terminated report (one line per step: milliseconds, share, description) into report (truncated to cap).
+ * Returns the full report length, or -1 with error.  The reference has no profiling hook (only DEBUG
+ * fprintf, ref bridge.m:1218-1236). */
+int64_t b200_execute_profiled(B200Exec exec, const B200Buffer* inputs, int num_inputs, B200Buffer* outputs, int num_outputs,
+                              char* report, int64_t cap, B200Error* err);
 /* Host pointers in, host pointers out: the exact calling shape of
  * mpsgraph_execute (ref bridge.h:167-172; bridge.m:1251-1403).  Copies inputs
  * host->device, runs, copies outputs device->host, and waits. */
@@ -342,6 +348,13 @@ bool b200_k_rms_norm(int device, const void* x, const void* gamma, void* y, int6
  * dtype in {BF16, F16, F32}.  bias [N] (may be NULL) and activation are applied in the epilogue. */
 bool b200_k_gemm(int device, const void* a, const void* b, void* c, int64_t batch, int64_t m, int64_t n, int64_t k,
                  int a_k_major, int b_k_major, int dtype, const void* bias, int activation, B200Error* err);
+/* Fused attention softmax(scale * Q K^T [+ causal mask]) V, the kernel behind
+ * b200_scaled_dot_product_attention when no mask tensor is given (ref function.go:2669-2907).
+ * Q is [batch, seq_q, heads, 64] (bshd != 0) or [batch, heads, seq_q, 64]; K and V likewise with kv_heads and
+ * seq_k; O has Q's layout.  head_dim must be 64, dtype BF16 or F16. */
+bool b200_k_attention(int device, const void* q, const void* k, const void* v, void* o, int64_t batch, int64_t heads,
+                      int64_t kv_heads, int64_t seq_q, int64_t seq_k, int64_t head_dim, int bshd, int causal, double scale,
+                      int dtype, B200Error* err);
 /* Sum of all n elements of x (F32) into out[0] (F32).  scratch must hold
  * b200_k_reduce_sum_scratch_bytes(n) bytes of device memory. */
 int64_t b200_k_reduce_sum_scratch_bytes(int64_t n);

@@ -500,3 +500,29 @@ def test_batch_sharded_runner_matches_single_device(b200, backend):
     got = runner([x, w])[0]
     runner.close()
     np.testing.assert_array_equal(got, single)   # replicas run the same kernels: bit-identical
+
+
+@pytest.mark.parametrize("layout", [0, 1], ids=["BHSD", "BSHD"])
+@pytest.mark.parametrize("heads,kv_heads", [(2, 2), (8, 2)])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("sq,sk", [(64, 64), (128, 128), (200, 200), (300, 300), (1, 77), (130, 333)])
+@pytest.mark.parametrize("dtype", [BF16, np.float16], ids=["bf16", "f16"])
+def test_fused_attention_head_dim_64(b200, backend, layout, heads, kv_heads, causal, sq, sk, dtype):
+    # the single-kernel path: 16-bit floats, head dim 64, no mask tensor
+    if dtype == np.float16 and (heads, kv_heads, layout) != (8, 2, 1):
+        pytest.skip("f16 covered on one head/layout combination")
+    rng = np.random.default_rng(38)
+    B, D = 2, 64
+    shp = lambda h, s: (B, h, s, D) if layout == 0 else (B, s, h, D)
+    q, k, v = rng_array(rng, shp(heads, sq), dtype), rng_array(rng, shp(kv_heads, sk), dtype), rng_array(rng, shp(kv_heads, sk), dtype)
+    (got,), plan = run_backend(b200, backend,
+                               lambda f, qq, kk, vv: f.FusedScaledDotProductAttention(qq, kk, vv, None, heads, kv_heads, layout, 0.125, causal),
+                               [q, k, v], describe=True)
+    assert plan.startswith("attention[") and plan.count("\n") == 1, plan
+    # The fused kernel keeps the scores in fp32 (the unfused lowering rounds them to the storage type before the
+    # softmax), so the yardstick is the oracle evaluated on the same inputs in fp32, rounded once at the end.
+    from oracle.oracle import OracleFunction, compare
+    want = OracleFunction().FusedScaledDotProductAttention(q.astype(np.float32), k.astype(np.float32), v.astype(np.float32), None, heads,
+                                                           kv_heads, layout, 0.125, causal).astype(dtype)
+    ok, viol = compare(got, want, BF16_RTOL, 1.0)
+    assert ok, viol
