@@ -721,3 +721,38 @@ class Executable:
                                       out_shapes, out_ranks, n_out, ctypes.byref(err))
         _check(err, "Execute")
         return [o.reshape(s.Dimensions) for o, s in zip(outs, self.output_shapes)]
+
+    def ExecuteHostSliced(self, inputs: Sequence[np.ndarray], sliced: Sequence[bool], num_slices: int,
+                          outputs: Optional[Sequence[np.ndarray]] = None) -> List[np.ndarray]:
+        """Runs this executable (compiled for ONE slice) over `num_slices` leading-axis slices of host arrays through
+        b200_execute_host_sliced: uploads, kernels and downloads of neighbouring slices overlap.  inputs[i] with
+        sliced[i] has shape [num_slices * d0, d1, ...] for an executable input [d0, d1, ...]; the others are passed
+        whole to every slice.  Returns (or fills `outputs` with) arrays of shape [num_slices * o0, o1, ...]."""
+        n_in, n_out = len(self.input_shapes), len(self.output_shapes)
+        if len(inputs) != n_in or len(sliced) != n_in:
+            raise BackendError(1, f"ExecuteSliced: expected {n_in} inputs and flags, got {len(inputs)} and {len(sliced)}")
+        if num_slices < 0:
+            raise BackendError(1, "ExecuteSliced: negative slice count")
+        arrs = [np.ascontiguousarray(a) for a in inputs]
+        for i, (a, s, fl) in enumerate(zip(arrs, self.input_shapes, sliced)):
+            want = s.Size() * s.DType.np.itemsize * (num_slices if fl else 1)
+            if a.nbytes != want or a.dtype != s.DType.np:
+                raise BackendError(1, f"ExecuteSliced: input {i} has {a.nbytes} bytes of {a.dtype}, expected {want} of {s.DType.np}")
+            if fl and s.Rank() == 0:
+                raise BackendError(1, f"ExecuteSliced: input {i} is a scalar and cannot be sliced")
+        if outputs is None:
+            outs = [np.empty((num_slices * s.Dimensions[0],) + tuple(s.Dimensions[1:]) if s.Rank() > 0 else (num_slices,), dtype=s.DType.np)
+                    for s in self.output_shapes]
+        else:
+            outs = list(outputs)
+            for j, (o, s) in enumerate(zip(outs, self.output_shapes)):
+                if o.nbytes != num_slices * s.Size() * s.DType.np.itemsize or not o.flags.c_contiguous:
+                    raise BackendError(1, f"ExecuteSliced: output {j} must be a contiguous array of {num_slices} slices")
+        in_ptrs = (ctypes.c_void_p * max(n_in, 1))(*[a.ctypes.data for a in arrs])
+        flags = _i32([1 if f else 0 for f in sliced])
+        out_ptrs = (ctypes.c_void_p * max(n_out, 1))(*[a.ctypes.data for a in outs])
+        err = _lib.B200Error()
+        with self._mu:
+            self._L.b200_execute_host_sliced(self.handle, in_ptrs, flags, n_in, out_ptrs, n_out, num_slices, ctypes.byref(err))
+        _check(err, "ExecuteSliced")
+        return outs

@@ -88,6 +88,8 @@ class Device {
   static Status Get(int ordinal, Device** out);
   int ordinal() const { return ordinal_; }
   cudaStream_t stream() const { return stream_; }
+  // Two extra streams for host<->device copies that overlap the compute stream (created on first use).
+  Status CopyStreams(cudaStream_t* in, cudaStream_t* out);
   int sm_count() const { return sm_count_; }
   Status Alloc(int64_t nbytes, void** out);
   void Free(void* p);
@@ -111,6 +113,7 @@ class Device {
   int ordinal_ = 0;
   int sm_count_ = 148;
   cudaStream_t stream_ = nullptr;
+  cudaStream_t copy_in_ = nullptr, copy_out_ = nullptr;
   int* error_flag_ = nullptr;
   bool error_check_pending_ = false;
   std::mutex mu_;
@@ -199,6 +202,10 @@ struct Graph {
     return nodes.back().get();
   }
 };
+
+// Compile-time rewrite: turns RMSNorm spelled in primitives (x * rsqrt(mean(x^2, last) + eps) [* gamma]) into one
+// RmsNorm node.  Returns the number of patterns rewritten.  Defined in rewrite.cpp.
+int RewriteRmsNorm(Graph& graph, const std::vector<Node*>& targets);
 
 // What a B200Context handle points to: one graph under construction and its device.
 struct Ctx {

@@ -1456,6 +1456,7 @@ B200Exec b200_compile(B200Context ctx, const B200Value* feeds, int num_feeds, co
     if (!n) { set_error(err, Status::Invalid("compile: target does not belong to this context")); return nullptr; }
     t.push_back(n);
   }
+  RewriteRmsNorm(c->graph, t);
   std::unique_ptr<Exec> ex(new Exec());
   ex->dev = c->dev;
   Planner planner(c, ex.get());
@@ -1595,6 +1596,142 @@ static bool execute_impl(B200Exec exec, const B200Buffer* inputs, int num_inputs
     for (auto& e : events) cudaEventDestroy(e);
   }
   for (int i = 0; i < num_outputs; ++i) outputs[i] = outs[i];
+  return true;
+}
+
+// Host arrays in, host arrays out, over `num_slices` consecutive leading-axis slices.  The executable is compiled for ONE slice.
+// Three streams: the upload of slice s+1, the kernels of slice s and the download of slice s-1 run at the same time, each
+// pair ordered by events; two sets of device buffers alternate.
+bool b200_execute_host_sliced(B200Exec exec, void** input_data, const int* input_sliced, int num_inputs, void** output_data,
+                              int num_outputs, int64_t num_slices, B200Error* err) {
+  clear_error(err);
+  Exec* ex = reinterpret_cast<Exec*>(exec);
+  if (!ex) { set_error(err, Status::Invalid("ExecuteSliced: null executable")); return false; }
+  if (num_inputs != (int)ex->inputs.size() || num_outputs != (int)ex->outputs.size()) {
+    set_error(err, Status::Invalid(strfmt("ExecuteSliced: expected %d inputs and %d outputs, got %d and %d", (int)ex->inputs.size(),
+                                          (int)ex->outputs.size(), num_inputs, num_outputs)));
+    return false;
+  }
+  if (num_slices < 0) { set_error(err, Status::Invalid("ExecuteSliced: negative slice count")); return false; }
+  for (int i = 0; i < num_inputs; ++i)
+    if (!input_data[i] && ex->inputs[i].nbytes > 0) { set_error(err, Status::Invalid(strfmt("ExecuteSliced: input %d is null", i))); return false; }
+  for (int i = 0; i < num_outputs; ++i)
+    if (!output_data[i] && ex->outputs[i].nbytes > 0 && num_slices > 0) { set_error(err, Status::Invalid(strfmt("ExecuteSliced: output %d is null", i))); return false; }
+  if (num_slices == 0) return true;
+  std::lock_guard<std::mutex> lock(ex->mu);
+  Device* dev = ex->dev;
+  Status st = dev->MakeCurrent();
+  cudaStream_t s_in = nullptr, s_out = nullptr;
+  if (st.ok()) st = dev->CopyStreams(&s_in, &s_out);
+  if (!st.ok()) { set_error(err, st); return false; }
+  const cudaStream_t s_main = dev->stream();
+
+  constexpr int kSets = 2;
+  std::vector<void*> owned;  // every device block of this call
+  std::vector<void*> in_ptr[kSets], out_ptr[kSets];
+  cudaEvent_t ev_in[kSets] = {}, ev_done[kSets] = {}, ev_out[kSets] = {}, ev_start = nullptr;
+  auto release = [&]() {
+    for (void* p : owned) dev->Free(p);
+    for (int k = 0; k < kSets; ++k) {
+      if (ev_in[k]) cudaEventDestroy(ev_in[k]);
+      if (ev_done[k]) cudaEventDestroy(ev_done[k]);
+      if (ev_out[k]) cudaEventDestroy(ev_out[k]);
+    }
+    if (ev_start) cudaEventDestroy(ev_start);
+  };
+  auto fail = [&](const Status& s) {
+    cudaStreamSynchronize(s_in);
+    cudaStreamSynchronize(s_main);
+    cudaStreamSynchronize(s_out);
+    release();
+    set_error(err, s);
+    return false;
+  };
+#define B200_SLICED_TRY(expr)                                                                  \
+  do {                                                                                         \
+    cudaError_t e_ = (expr);                                                                   \
+    if (e_ != cudaSuccess) return fail(Status::Cuda(strfmt("%s: %s", #expr, cudaGetErrorString(e_)))); \
+  } while (0)
+
+  const int sets = (int)std::min<int64_t>(kSets, num_slices);
+  for (int k = 0; k < kSets; ++k) { in_ptr[k].assign(num_inputs, nullptr); out_ptr[k].assign(num_outputs, nullptr); }
+  for (int i = 0; i < num_inputs; ++i) {
+    const int copies = input_sliced && input_sliced[i] ? sets : 1;
+    for (int k = 0; k < copies; ++k) {
+      void* p = nullptr;
+      st = dev->Alloc(std::max<int64_t>(ex->inputs[i].nbytes, 1), &p);
+      if (!st.ok()) return fail(st);
+      owned.push_back(p);
+      in_ptr[k][i] = p;
+    }
+    for (int k = copies; k < kSets; ++k) in_ptr[k][i] = in_ptr[0][i];
+  }
+  for (int i = 0; i < num_outputs; ++i)
+    for (int k = 0; k < sets; ++k) {
+      void* p = nullptr;
+      st = dev->Alloc(std::max<int64_t>(ex->outputs[i].nbytes, 1), &p);
+      if (!st.ok()) return fail(st);
+      owned.push_back(p);
+      out_ptr[k][i] = p;
+    }
+  for (int k = 0; k < kSets; ++k) {
+    B200_SLICED_TRY(cudaEventCreateWithFlags(&ev_in[k], cudaEventDisableTiming));
+    B200_SLICED_TRY(cudaEventCreateWithFlags(&ev_done[k], cudaEventDisableTiming));
+    B200_SLICED_TRY(cudaEventCreateWithFlags(&ev_out[k], cudaEventDisableTiming));
+  }
+  B200_SLICED_TRY(cudaEventCreateWithFlags(&ev_start, cudaEventDisableTiming));
+  // The blocks above may have been freed by earlier work on the compute stream: the copy streams start after it.
+  B200_SLICED_TRY(cudaEventRecord(ev_start, s_main));
+  B200_SLICED_TRY(cudaStreamWaitEvent(s_in, ev_start, 0));
+  B200_SLICED_TRY(cudaStreamWaitEvent(s_out, ev_start, 0));
+  // Inputs shared by every slice (weights, tables) go up once, ahead of slice 0.
+  for (int i = 0; i < num_inputs; ++i)
+    if (!(input_sliced && input_sliced[i]) && ex->inputs[i].nbytes > 0)
+      B200_SLICED_TRY(cudaMemcpyAsync(in_ptr[0][i], input_data[i], (size_t)ex->inputs[i].nbytes, cudaMemcpyHostToDevice, s_in));
+
+  std::vector<void*> ptrs(ex->slots.size(), nullptr);
+  for (size_t s = 0; s < ex->slots.size(); ++s) {
+    const Slot& sl = ex->slots[s];
+    if (sl.kind == SlotKind::Arena) ptrs[s] = (char*)ex->arena + sl.offset;
+    else if (sl.kind == SlotKind::Const) ptrs[s] = ex->const_ptrs[sl.index];
+  }
+  for (int64_t sl = 0; sl < num_slices; ++sl) {
+    const int k = (int)(sl % kSets);
+    // upload: the set's previous kernels (slice sl - 2) must have finished reading it
+    if (sl >= kSets) B200_SLICED_TRY(cudaStreamWaitEvent(s_in, ev_done[k], 0));
+    for (int i = 0; i < num_inputs; ++i)
+      if (input_sliced && input_sliced[i] && ex->inputs[i].nbytes > 0)
+        B200_SLICED_TRY(cudaMemcpyAsync(in_ptr[k][i], (const char*)input_data[i] + sl * ex->inputs[i].nbytes, (size_t)ex->inputs[i].nbytes,
+                                        cudaMemcpyHostToDevice, s_in));
+    B200_SLICED_TRY(cudaEventRecord(ev_in[k], s_in));
+    // kernels: after the upload, and after the download of slice sl - 2 has drained the set's outputs
+    B200_SLICED_TRY(cudaStreamWaitEvent(s_main, ev_in[k], 0));
+    if (sl >= kSets) B200_SLICED_TRY(cudaStreamWaitEvent(s_main, ev_out[k], 0));
+    for (int i = 0; i < num_inputs; ++i) ptrs[ex->inputs[i].slot] = in_ptr[k][i];
+    for (int i = 0; i < num_outputs; ++i) ptrs[ex->outputs[i].slot] = out_ptr[k][i];
+    for (auto& step : ex->steps) {
+      Status s = step.run(dev, ptrs.data());
+      if (!s.ok()) return fail(Status{s.code, step.desc + ": " + s.msg});
+    }
+    B200_SLICED_TRY(cudaEventRecord(ev_done[k], s_main));
+    // download
+    B200_SLICED_TRY(cudaStreamWaitEvent(s_out, ev_done[k], 0));
+    for (int i = 0; i < num_outputs; ++i)
+      if (ex->outputs[i].nbytes > 0)
+        B200_SLICED_TRY(cudaMemcpyAsync((char*)output_data[i] + sl * ex->outputs[i].nbytes, out_ptr[k][i], (size_t)ex->outputs[i].nbytes,
+                                        cudaMemcpyDeviceToHost, s_out));
+    B200_SLICED_TRY(cudaEventRecord(ev_out[k], s_out));
+  }
+  // Join: the compute stream waits for both copy streams so that the blocks can go back to the stream-ordered allocator.
+  for (int k = 0; k < sets; ++k) {
+    B200_SLICED_TRY(cudaStreamWaitEvent(s_main, ev_in[k], 0));
+    B200_SLICED_TRY(cudaStreamWaitEvent(s_main, ev_out[k], 0));
+  }
+  B200_SLICED_TRY(cudaStreamSynchronize(s_out));
+  st = dev->Synchronize();
+  if (!st.ok()) return fail(st);
+#undef B200_SLICED_TRY
+  release();
   return true;
 }
 

@@ -65,6 +65,18 @@ Status Device::Get(int ordinal, Device** out) {
   return Status::OK();
 }
 
+Status Device::CopyStreams(cudaStream_t* in, cudaStream_t* out) {
+  std::lock_guard<std::mutex> lock(mu_);
+  if (!copy_in_) {
+    B200_CUDA_TRY(cudaSetDevice(ordinal_));
+    B200_CUDA_TRY(cudaStreamCreateWithFlags(&copy_in_, cudaStreamNonBlocking));
+    B200_CUDA_TRY(cudaStreamCreateWithFlags(&copy_out_, cudaStreamNonBlocking));
+  }
+  *in = copy_in_;
+  *out = copy_out_;
+  return Status::OK();
+}
+
 Status Device::MakeCurrent() {
   B200_CUDA_TRY(cudaSetDevice(ordinal_));
   return Status::OK();

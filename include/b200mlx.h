@@ -290,6 +290,15 @@ bool b200_execute_host(B200Exec exec, void** input_data, const int64_t* input_si
                        int64_t** input_shapes, const int* input_ranks, int num_inputs, void** output_data,
                        const int64_t* output_sizes, const int* output_dtypes, int64_t** output_shapes,
                        const int* output_ranks, int num_outputs, B200Error* err);
+/* The same over num_slices consecutive leading-axis slices of the host arrays, for an executable compiled for ONE
+ * slice.  Input i with input_sliced[i] != 0 holds num_slices x (executable input i) back to back and slice s is fed
+ * to run s; other inputs (weights, tables) are uploaded once and fed to every run.  Output j receives num_slices x
+ * (executable output j) back to back.  The result equals num_slices calls of b200_execute_host, but the upload of
+ * slice s+1, the kernels of slice s and the download of slice s-1 run concurrently on three streams (pass pinned
+ * memory from b200_host_alloc for the copies to overlap).  Blocks until every output is in host memory.  The
+ * reference's execute (ref bridge.m:1293-1391) uploads, runs and downloads strictly in sequence. */
+bool b200_execute_host_sliced(B200Exec exec, void** input_data, const int* input_sliced, int num_inputs, void** output_data,
+                              int num_outputs, int64_t num_slices, B200Error* err);
 
 /* ---- device buffers (ref bridge.h:175-178; backend.go:103-167) ---------- */
 B200Buffer b200_buffer_alloc(int device, int dtype, const int64_t* shape, int rank, B200Error* err);

@@ -8,7 +8,8 @@ import ml_dtypes
 import numpy as np
 import pytest
 
-from tests.util import assert_parity, rng_array, run_backend
+from oracle.oracle import compare
+from tests.util import assert_parity, rng_array, run_backend, run_oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -452,6 +453,47 @@ def test_execute_host_matches_device_path(b200, backend):
         np.testing.assert_array_equal(h, d)
 
 
+@pytest.mark.parametrize("num_slices", [1, 2, 5])
+def test_execute_host_sliced_equals_slice_by_slice(b200, backend, num_slices):
+    # one executable compiled for a [4, 8, 256] slice; weights are shared by every slice
+    rng = np.random.default_rng(36 + num_slices)
+    D = b200.dtypes
+    builder = backend.Builder("sliced")
+    f = builder.Main()
+    p = f.Parameter("x", b200.shapes.Make(D.Float32, 4, 8, 256))
+    w = f.Parameter("w", b200.shapes.Make(D.Float32, 256, 32))
+    g = f.Parameter("g", b200.shapes.Make(D.Float32, 256))
+    sm = f.FusedSoftmaxMasked(p, 0.5, True, None)
+    y = f.DotGeneral(f.FusedRMSNorm(p, [-1], 1e-6, g), [2], [], w, [0], [])
+    f.Return([sm, y, f.ArgMinMax(p, 2, D.Int32, False)], None)
+    exe = builder.Compile()
+    x = rng_array(rng, (4 * num_slices, 8, 256), np.float32)
+    wv, gv = rng_array(rng, (256, 32), np.float32), rng_array(rng, (256,), np.float32)
+    got = exe.ExecuteHostSliced([x, wv, gv], [True, False, False], num_slices)
+    assert got[0].shape == (4 * num_slices, 8, 256) and got[1].shape == (4 * num_slices, 8, 32) and got[2].shape == (4 * num_slices, 8)
+    for s in range(num_slices):
+        want = exe.ExecuteHost([x[4 * s:4 * s + 4], wv, gv])
+        for o, wnt in zip(got, want):
+            np.testing.assert_array_equal(o[4 * s:4 * s + 4], wnt)
+    # repeated calls reuse the device blocks and streams
+    again = exe.ExecuteHostSliced([x, wv, gv], [True, False, False], num_slices)
+    for a, b_ in zip(got, again):
+        np.testing.assert_array_equal(a, b_)
+
+
+def test_execute_host_sliced_argument_checks(b200, backend):
+    builder = backend.Builder("sliced_err")
+    f = builder.Main()
+    p = f.Parameter("x", b200.shapes.Make(b200.dtypes.Float32, 2, 8))
+    f.Return([f.Neg(p)], None)
+    exe = builder.Compile()
+    assert exe.ExecuteHostSliced([np.zeros((0, 8), np.float32)], [True], 0)[0].shape == (0, 8)
+    with pytest.raises(b200.BackendError, match="expected 1 inputs"):
+        exe.ExecuteHostSliced([], [], 1)
+    with pytest.raises(b200.BackendError, match="bytes"):
+        exe.ExecuteHostSliced([np.zeros((3, 8), np.float32)], [True], 2)
+
+
 def test_buffer_round_trip_and_scalar(b200, backend):
     for arr in (np.arange(24, dtype=np.int16).reshape(2, 3, 4), np.array(2.5, dtype=np.float64), np.zeros((0,), dtype=np.float32)):
         buf = backend.FromNumpy(arr)
@@ -526,3 +568,117 @@ def test_fused_attention_head_dim_64(b200, backend, layout, heads, kv_heads, cau
                                                            kv_heads, layout, 0.125, causal).astype(dtype)
     ok, viol = compare(got, want, BF16_RTOL, 1.0)
     assert ok, viol
+
+
+# ---- RMSNorm spelled in primitives is recognised and runs as the one row kernel --------------------------------
+def _rms_from_primitives(b200, spelling, dt, shape, eps=1e-6, with_gamma=True):
+    """GoMLX has no fused RMSNorm: a model emits Mul, ReduceSum, Div/Mul, Add, Rsqrt, Mul(, Mul).  Several spellings."""
+    C = shape[-1]
+    full = _S(b200, dt, *shape)
+    keep = shape[:-1] + (1,)
+    lead = list(range(len(shape) - 1))
+
+    def scalar(f, v, like_shape, axes_shape):
+        c = f.Constant(np.array([v], dtype=np.float32), 1)
+        c = f.ConvertDType(c, b200.dtypes.from_numpy(np.dtype(dt))) if np.dtype(dt) != np.float32 else c
+        return f.BroadcastInDim(c, _S(b200, dt, *axes_shape), [len(axes_shape) - 1] if len(axes_shape) else [])
+
+    def build(f, x, g):
+        ss = f.ReduceSum(f.Mul(x, x), len(shape) - 1)                               # [lead]
+        if spelling == "keepdims":      # reshape to [.., 1], mean by Div, broadcast last
+            st = f.Reshape(ss, *keep)
+            st = f.Div(st, scalar(f, float(C), keep, keep))
+            st = f.Rsqrt(f.Add(st, scalar(f, eps, keep, keep)))
+            y = f.Mul(x, f.BroadcastInDim(st, full, list(range(len(shape)))))
+        elif spelling == "early_broadcast":  # statistic broadcast to the full shape first, mean by Mul(1/C)
+            st = f.BroadcastInDim(ss, full, lead)
+            st = f.Mul(scalar(f, 1.0 / C, shape, shape), st)
+            y = f.Mul(f.Rsqrt(f.Add(scalar(f, eps, shape, shape), st)), x)
+        else:                            # x / sqrt(mean + eps)
+            st = f.Div(ss, scalar(f, float(C), shape[:-1], shape[:-1]))
+            st = f.Sqrt(f.Add(st, scalar(f, eps, shape[:-1], shape[:-1])))
+            y = f.Div(x, f.BroadcastInDim(st, full, lead))
+        if with_gamma:
+            y = f.Mul(y, f.BroadcastInDim(g, full, [len(shape) - 1]))
+        return y
+    return build
+
+
+@pytest.mark.parametrize("spelling", ["keepdims", "early_broadcast", "div_sqrt"])
+@pytest.mark.parametrize("dt", ["float32", "bfloat16"])
+def test_rmsnorm_from_primitives_is_one_kernel(b200, backend, spelling, dt):
+    import ml_dtypes
+    npdt = np.dtype(np.float32) if dt == "float32" else np.dtype(ml_dtypes.bfloat16)
+    rng = np.random.default_rng(91)
+    shape = (3, 7, 256)
+    x = rng_array(rng, shape, npdt)
+    g = (1 + 0.1 * rng.standard_normal(256)).astype(np.float32).astype(npdt)
+    build = _rms_from_primitives(b200, spelling, npdt, shape)
+    (got,), plan = run_backend(b200, backend, build, [x, g], describe=True)
+    assert "rms_norm[" in plan and "gamma=1" in plan, plan
+    assert len([l for l in plan.strip().splitlines() if l.strip()]) == 1, plan
+    (want,) = run_oracle(build, [x, g])
+    # fp32: the fused kernel and the op-by-op chain agree to rounding; 16-bit: the chain rounds every step to 8 bits
+    ok, viol = compare(got, want, 1e-5 if dt == "float32" else 2e-2, 0.0)
+    assert ok, viol
+    # and it equals the fused op the backend offers directly
+    (fused,) = run_backend(b200, backend, lambda f, a, gg: f.FusedRMSNorm(a, [-1], 1e-6, gg), [x, g])
+    np.testing.assert_array_equal(got, fused)
+
+
+def test_rmsnorm_lookalikes_are_left_alone(b200, backend):
+    rng = np.random.default_rng(92)
+    x = rng_array(rng, (4, 4, 4), np.float32)
+    full = _S(b200, np.float32, 4, 4, 4)
+
+    def c(f, v, *dims):
+        return f.BroadcastInDim(f.Constant(np.array([v], dtype=np.float32), 1), _S(b200, np.float32, *dims), [len(dims) - 1])
+
+    def not_last_axis(f, a):       # statistic over axis 1, not the last
+        ss = f.ReduceSum(f.Mul(a, a), 1)
+        st = f.Rsqrt(f.Add(f.Div(ss, c(f, 4.0, 4, 4)), c(f, 1e-6, 4, 4)))
+        return f.Mul(a, f.BroadcastInDim(st, full, [0, 2]))
+
+    def wrong_rows(f, a):          # sum over the last axis, but broadcast back along axis 0: rows are permuted
+        ss = f.ReduceSum(f.Mul(a, a), 2)
+        st = f.Rsqrt(f.Add(f.Div(ss, c(f, 4.0, 4, 4)), c(f, 1e-6, 4, 4)))
+        return f.Mul(a, f.BroadcastInDim(st, full, [1, 2]))
+
+    def not_a_mean(f, a):          # divides by 3, not by the row length
+        ss = f.ReduceSum(f.Mul(a, a), 2)
+        st = f.Rsqrt(f.Add(f.Div(ss, c(f, 3.0, 4, 4)), c(f, 1e-6, 4, 4)))
+        return f.Mul(a, f.BroadcastInDim(st, full, [0, 1]))
+
+    def other_tensor(f, a):        # normalises a DIFFERENT tensor by x's statistic
+        ss = f.ReduceSum(f.Mul(a, a), 2)
+        st = f.Rsqrt(f.Add(f.Div(ss, c(f, 4.0, 4, 4)), c(f, 1e-6, 4, 4)))
+        return f.Mul(f.Neg(a), f.BroadcastInDim(st, full, [0, 1]))
+
+    for build in (not_last_axis, wrong_rows, not_a_mean, other_tensor):
+        (got,), plan = run_backend(b200, backend, build, [x], describe=True)
+        assert "rms_norm[" not in plan, (build.__name__, plan)
+        (want,) = run_oracle(build, [x])
+        ok, viol = compare(got, want, 1e-5, 0.0)
+        assert ok, (build.__name__, viol)
+
+
+def test_rmsnorm_rewrite_keeps_shared_intermediates(b200, backend):
+    # the statistic is also an output, and the normalised value feeds two users: only the root is rewritten
+    rng = np.random.default_rng(93)
+    x = rng_array(rng, (5, 128), np.float32)
+    g = rng_array(rng, (128,), np.float32)
+    full = _S(b200, np.float32, 5, 128)
+
+    def build(f, a, gg):
+        ss = f.ReduceSum(f.Mul(a, a), 1)
+        mean = f.Div(ss, f.BroadcastInDim(f.Constant(np.array([128.0], dtype=np.float32), 1), _S(b200, np.float32, 5), [0]))
+        inv = f.Rsqrt(f.Add(mean, f.BroadcastInDim(f.Constant(np.array([1e-5], dtype=np.float32), 1), _S(b200, np.float32, 5), [0])))
+        n = f.Mul(a, f.BroadcastInDim(inv, full, [0]))
+        return [f.Mul(n, f.BroadcastInDim(gg, full, [1])), f.Neg(n), mean]
+
+    got, plan = run_backend(b200, backend, build, [x, g], describe=True)
+    assert "rms_norm[" in plan and "gamma=0" in plan, plan
+    want = run_oracle(build, [x, g])
+    for a, w in zip(got, want):
+        ok, viol = compare(a, w, 1e-5, 0.0)
+        assert ok, viol
