@@ -33,6 +33,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "../kernels.h"
@@ -170,6 +171,51 @@ template <> __device__ __forceinline__ float load_bias<__half>(const void* bias,
   return __half2float(reinterpret_cast<const __half*>(bias)[col]);
 }
 
+// One epilogue warp drains its 32 TMEM lanes of a finished 128 x 256 accumulator: bias, activation, rounding, stores.
+// row0 is the first row of C held by lane 0 of this CTA's accumulator; `stage` is the warp's 32 x 33 fp32 scratch.
+template <typename OutT>
+__device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem_acc, int64_t row0, int64_t n0, int b, int quarter, int lane,
+                                                  float* stage) {
+  const int64_t row = row0 + quarter * 32 + lane;
+  OutT* crow = reinterpret_cast<OutT*>(g.c) + ((int64_t)b * g.M + row) * g.ldc;
+  const uint32_t taddr = tmem_acc + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+  for (int chunk = 0; chunk < BN / 32; ++chunk) {
+    const int64_t col0 = n0 + chunk * 32;
+    if (col0 >= g.N) break;  // uniform across the warp
+    uint32_t r[32];
+    tmem_ld32(taddr + chunk * 32, r);
+    tmem_ld_wait();
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+    if (g.bias) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < g.N) v[j] += load_bias<OutT>(g.bias, col0 + j);
+    }
+    if (g.activation != B200_ACT_NONE) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = apply_activation(g.activation, v[j]);
+    }
+    if (g.vec_store) {
+      if (row < g.M) store_chunk<OutT>(g, crow, col0, v);
+    } else {
+      // Rows of C do not start 16-byte aligned (N is not a multiple of the vector width): transpose the
+      // 32 x 32 block through shared memory so that a warp writes 32 CONSECUTIVE columns of one row per store.
+#pragma unroll
+      for (int j = 0; j < 32; ++j) stage[lane * 33 + j] = v[j];
+      __syncwarp();
+      const int64_t row_base = row0 + quarter * 32;
+      const int64_t col = col0 + lane;
+      OutT* cb = reinterpret_cast<OutT*>(g.c) + ((int64_t)b * g.M + row_base) * g.ldc + col;
+      for (int rr = 0; rr < 32; ++rr)
+        if (row_base + rr < g.M && col < g.N) store_one<OutT>(cb + (int64_t)rr * g.ldc, stage[rr * 33 + lane]);
+      __syncwarp();
+    }
+  }
+}
+
 template <typename OutT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const TcArgs g) {
@@ -283,7 +329,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   } else {
     // ------------------------------------------------------------------ epilogue ---
     const int quarter = warp & 3;              // TMEM lanes [32*quarter, 32*quarter + 32) belong to this warp
-    const int row_in_tile = quarter * 32 + lane;
     bool ok = true;
     int local_tile = 0;
     for (int64_t t = blockIdx.x; t < g.total_tiles && ok; t += gridDim.x, ++local_tile) {
@@ -294,46 +339,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const bool landed = mbar_wait(&acc_full[acc], acc_phase, err, 4);
       if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }  // the warp leaves together: tcgen05.ld is warp-collective
       tc_fence_after();
-      const int64_t row = (int64_t)m_t * BM + row_in_tile;
-      const int64_t n0 = (int64_t)n_t * BN;
-      OutT* crow = reinterpret_cast<OutT*>(g.c) + ((int64_t)b * g.M + row) * g.ldc;
-      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
-#pragma unroll 1
-      for (int chunk = 0; chunk < BN / 32; ++chunk) {
-        const int64_t col0 = n0 + chunk * 32;
-        if (col0 >= g.N) break;  // uniform across the warp
-        uint32_t r[32];
-        tmem_ld32(taddr + chunk * 32, r);
-        tmem_ld_wait();
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        if (g.bias) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (col0 + j < g.N) v[j] += load_bias<OutT>(g.bias, col0 + j);
-        }
-        if (g.activation != B200_ACT_NONE) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = apply_activation(g.activation, v[j]);
-        }
-        if (g.vec_store) {
-          if (row < g.M) store_chunk<OutT>(g, crow, col0, v);
-        } else {
-          // Rows of C do not start 16-byte aligned (N is not a multiple of the vector width): transpose the
-          // 32 x 32 block through shared memory so that a warp writes 32 CONSECUTIVE columns of one row per store.
-          float* st = epi_stage + (warp - 2) * EPI_STAGE_FLOATS;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) st[lane * 33 + j] = v[j];
-          __syncwarp();
-          const int64_t row_base = (int64_t)m_t * BM + quarter * 32;
-          const int64_t col = col0 + lane;
-          OutT* cb = reinterpret_cast<OutT*>(g.c) + ((int64_t)b * g.M + row_base) * g.ldc + col;
-          for (int r = 0; r < 32; ++r)
-            if (row_base + r < g.M && col < g.N) store_one<OutT>(cb + (int64_t)r * g.ldc, st[r * 33 + lane]);
-          __syncwarp();
-        }
-      }
+      drain_accumulator<OutT>(g, tmem_base + acc * BN, (int64_t)m_t * BM, (int64_t)n_t * BN, b, quarter, lane, epi_stage + (warp - 2) * EPI_STAGE_FLOATS);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
@@ -354,6 +360,181 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// CTA-pair variant: two CTAs of a cluster (neighbouring SMs) compute one 256 x 256 tile with tcgen05.mma
+// cta_group::2.  Each CTA loads its 128 rows of A and HALF of the tile's B columns (128), so a CTA pulls 32 KiB per
+// 64-deep K block from L2 instead of 48 KiB; its TMEM holds the 128 x 256 accumulator of its own rows.  The CTA of
+// even rank (the leader) issues every MMA.  Barriers:
+//   full[s]      leader only; counts the bytes of BOTH CTAs' tile loads (the peer's loads name it by cluster address)
+//   empty[s]     one per CTA; the leader commits to both once the MMAs that read stage s are done
+//   acc_full[a]  one per CTA; the leader commits to both when a tile's accumulator is complete
+//   acc_empty[a] leader only; the 4 + 4 epilogue warps of both CTAs arrive when they have drained it
+// The pair joins at a cluster barrier before either releases TMEM or exits, so no CTA's shared memory or barriers
+// are touched after it has gone.
+constexpr int P_STAGES = 6;
+constexpr int P_BN_HALF = BN / 2;                         // B columns held per CTA
+constexpr int P_B_STAGE_BYTES = P_BN_HALF * BK * 2;       // 16 KiB
+constexpr int P_STAGE_BYTES = A_STAGE_BYTES + P_B_STAGE_BYTES;  // 32 KiB
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256 + 4 * EPI_STAGE_FLOATS * 4;
+
+__device__ __forceinline__ void pair_tile_coords(const TcArgs& g, int64_t t, int* b, int* m_t, int* n_t) {
+  // same grouping as tile_coords over tiles of 256 rows: g.tiles_m counts 256-row tiles here
+  tile_coords(g, t, b, m_t, n_t);
+}
+
+template <typename OutT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const TcArgs g) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + P_STAGES * P_STAGE_BYTES);
+  uint64_t* full = bars;                          // [P_STAGES]
+  uint64_t* empty = bars + P_STAGES;              // [P_STAGES]
+  uint64_t* acc_full = bars + 2 * P_STAGES;       // [2]
+  uint64_t* acc_empty = bars + 2 * P_STAGES + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * P_STAGES + 4);
+  float* epi_stage = reinterpret_cast<float*>(tiles + P_STAGES * P_STAGE_BYTES + 256);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int64_t pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  volatile int* err = g.err_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before either signals the other's
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int iters = g.k_blocks * g.segs;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer ---
+    if (lane == 0) {
+      int s = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int64_t t = pair; t < g.total_tiles && ok; t += num_pairs) {
+        int b, m_t, n_t;
+        pair_tile_coords(g, t, &b, &m_t, &n_t);
+        const int m0 = m_t * 2 * BM + (int)rank * BM;          // this CTA's 128 rows of A
+        const int n0 = n_t * BN + (int)rank * P_BN_HALF;       // this CTA's 128 columns of B
+        for (int it = 0; it < iters; ++it) {
+          if (!mbar_wait_cluster(&empty[s], phase ^ 1, err, 1)) { ok = false; break; }
+          const int seg = it / g.k_blocks, kb = it % g.k_blocks;
+          const int pa = g.segs > 1 ? kPlaneA[seg] : 0, pb = g.segs > 1 ? kPlaneB[seg] : 0;
+          unsigned char* sa = tiles + s * P_STAGE_BYTES;
+          unsigned char* sb = sa + A_STAGE_BYTES;
+          if (leader) mbar_expect_tx(&full[s], 2 * P_STAGE_BYTES);
+          const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
+          if (g.a_kmajor) {
+            tma_load_4d_pair(sa, &tm_a, bar, kb * BK, m0, b, pa);
+          } else {
+            tma_load_4d_pair(sa, &tm_a, bar, m0, kb * BK, b, pa);
+            tma_load_4d_pair(sa + 8192, &tm_a, bar, m0 + 64, kb * BK, b, pa);
+          }
+          if (g.b_kmajor) {
+            tma_load_4d_pair(sb, &tm_b, bar, kb * BK, n0, b, pb);
+          } else {
+            tma_load_4d_pair(sb, &tm_b, bar, n0, kb * BK, b, pb);
+            tma_load_4d_pair(sb + 8192, &tm_b, bar, n0 + 64, kb * BK, b, pb);
+          }
+          if (++s == P_STAGES) { s = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------------- issuer ---
+    if (lane == 0 && leader) {
+      uint32_t idesc = 0;
+      idesc |= 1u << 4;
+      idesc |= (g.in_f16 ? 0u : 1u) << 7;
+      idesc |= (g.in_f16 ? 0u : 1u) << 10;
+      idesc |= (g.a_kmajor ? 0u : 1u) << 15;
+      idesc |= (g.b_kmajor ? 0u : 1u) << 16;
+      idesc |= (uint32_t)(BN >> 3) << 17;
+      idesc |= (uint32_t)((2 * BM) >> 4) << 24;   // M = 256 across the pair
+      const uint32_t a_lbo = g.a_kmajor ? 16u : 8192u, b_lbo = g.b_kmajor ? 16u : 8192u;
+      const uint32_t a_kstep = g.a_kmajor ? 32u : 2048u, b_kstep = g.b_kmajor ? 32u : 2048u;
+      int s = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int local_tile = 0;
+      for (int64_t t = pair; t < g.total_tiles && ok; t += num_pairs, ++local_tile) {
+        const int acc = local_tile & 1;
+        const uint32_t acc_phase = (local_tile >> 1) & 1;
+        if (!mbar_wait_cluster(&acc_empty[acc], acc_phase ^ 1, err, 2)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int it = 0; it < iters; ++it) {
+          if (!mbar_wait_cluster(&full[s], phase, err, 3)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(tiles + s * P_STAGE_BYTES), sb = sa + A_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = make_smem_desc(sa + k * a_kstep, a_lbo, 1024);
+            const uint64_t db = make_smem_desc(sb + k * b_kstep, b_lbo, 1024);
+            umma_f16_pair(d_tmem, da, db, idesc, (it | k) != 0 ? 1u : 0u);
+          }
+          // the stage is free in BOTH CTAs once these MMAs have read it
+          tc_commit_pair(map_to_cta(smem_u32(&empty[s]), 0));
+          tc_commit_pair(map_to_cta(smem_u32(&empty[s]), 1));
+          if (++s == P_STAGES) { s = 0; phase ^= 1; }
+        }
+        if (ok) {
+          tc_commit_pair(map_to_cta(smem_u32(&acc_full[acc]), 0));
+          tc_commit_pair(map_to_cta(smem_u32(&acc_full[acc]), 1));
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue ---
+    const int quarter = warp & 3;
+    bool ok = true;
+    int local_tile = 0;
+    for (int64_t t = pair; t < g.total_tiles && ok; t += num_pairs, ++local_tile) {
+      int b, m_t, n_t;
+      pair_tile_coords(g, t, &b, &m_t, &n_t);
+      const int acc = local_tile & 1;
+      const uint32_t acc_phase = (local_tile >> 1) & 1;
+      const bool landed = mbar_wait_cluster(&acc_full[acc], acc_phase, err, 4);
+      if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }
+      tc_fence_after();
+      drain_accumulator<OutT>(g, tmem_base + acc * BN, (int64_t)m_t * 2 * BM + (int64_t)rank * BM, (int64_t)n_t * BN, b, quarter, lane,
+                              epi_stage + (warp - 2) * EPI_STAGE_FLOATS);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown ---
+  tc_fence_before();
+  __shared__ int failed;
+  if (threadIdx.x == 0) failed = *err;
+  __syncthreads();
+  if (failed != 0) {
+    const unsigned long long t0 = global_ns();
+    while (global_ns() - t0 < 200000ull) {}
+    __syncthreads();
+  }
+  cluster_sync_all();  // the peer has issued its last load, MMA and remote arrive
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
 }
 
@@ -425,13 +606,18 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
   }
   auto cleanup = [&]() { dev->Free(tmp_a); dev->Free(tmp_b); };
 
+  // CTA pairs (256-row tiles) whenever there is more than one 128-row tile of M to share B with
+  static const bool pair_allowed = []() { const char* v = getenv("B200MLX_GEMM_PAIR"); return !(v && v[0] == '0'); }();
+  const bool use_pair = pair_allowed && p.m > BM;
+
   CUtensorMap tm_a, tm_b;
   Status s;
   const bool f16 = p.dtype == B200_FLOAT16;
+  const int b_box = use_pair ? P_BN_HALF : BN;
   if (p.a_k_major) s = make_operand_map(&tm_a, a, f16, p.k, p.m, p.k, p.batch, p.m * p.k, planes, planes > 1 ? a_plane_stride : p.m * p.k * p.batch, BM);
   else s = make_operand_map(&tm_a, a, f16, p.m, p.k, p.m, p.batch, p.m * p.k, planes, planes > 1 ? a_plane_stride : p.m * p.k * p.batch, 64);
   if (s.ok()) {
-    if (p.b_k_major) s = make_operand_map(&tm_b, b, f16, p.k, p.n, p.k, p.batch, p.n * p.k, planes, planes > 1 ? b_plane_stride : p.n * p.k * p.batch, BN);
+    if (p.b_k_major) s = make_operand_map(&tm_b, b, f16, p.k, p.n, p.k, p.batch, p.n * p.k, planes, planes > 1 ? b_plane_stride : p.n * p.k * p.batch, b_box);
     else s = make_operand_map(&tm_b, b, f16, p.n, p.k, p.n, p.batch, p.n * p.k, planes, planes > 1 ? b_plane_stride : p.n * p.k * p.batch, 64);
   }
   if (!s.ok()) { cleanup(); return s; }
@@ -444,20 +630,21 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
   g.activation = p.activation;
   g.in_f16 = f16 ? 1 : 0;
   g.out_dtype = p.dtype;
-  g.tiles_m = (int)((p.m + BM - 1) / BM);
+  const int tile_rows = use_pair ? 2 * BM : BM;
+  g.tiles_m = (int)((p.m + tile_rows - 1) / tile_rows);
   g.tiles_n = (int)((p.n + BN - 1) / BN);
   g.total_tiles = (int64_t)g.tiles_m * g.tiles_n * p.batch;
   g.k_blocks = (int)((p.k + BK - 1) / BK);
   g.segs = is32 ? 6 : 1;
   const int out_vec = is32 ? 4 : 8;
-  g.vec_store = (p.n % out_vec == 0 && aligned16(p.c) && (!p.bias || true)) ? 1 : 0;
+  g.vec_store = (p.n % out_vec == 0 && aligned16(p.c)) ? 1 : 0;
   g.err_flag = dev->kernel_error_flag();
 
-  const int64_t grid = g.total_tiles < dev->sm_count() ? g.total_tiles : dev->sm_count();
   cudaError_t e = cudaSuccess;
   // the dynamic shared memory opt-in is per function and per device; do it once
   static std::mutex attr_mu;
-  static bool attr_done[3][64] = {};
+  static bool attr_done[6][64] = {};
+  static int max_pairs[6][64] = {};
 #define LAUNCH_TC(OutT, SLOT)                                                                                               \
   do {                                                                                                                      \
     {                                                                                                                       \
@@ -467,12 +654,50 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
         attr_done[SLOT][dev->ordinal()] = (e == cudaSuccess);                                                               \
       }                                                                                                                     \
     }                                                                                                                       \
+    const int64_t grid = g.total_tiles < dev->sm_count() ? g.total_tiles : dev->sm_count();                                 \
     if (e == cudaSuccess) gemm_tcgen05_kernel<OutT><<<(unsigned)grid, NUM_THREADS, SMEM_BYTES, stream>>>(tm_a, tm_b, g);     \
   } while (0)
-  if (is32) LAUNCH_TC(float, 0);
-  else if (f16) LAUNCH_TC(__half, 1);
-  else LAUNCH_TC(__nv_bfloat16, 2);
+#define LAUNCH_TC_PAIR(OutT, SLOT)                                                                                          \
+  do {                                                                                                                      \
+    {                                                                                                                       \
+      std::lock_guard<std::mutex> lock(attr_mu);                                                                            \
+      if (!attr_done[SLOT][dev->ordinal()]) {                                                                               \
+        e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES); \
+        attr_done[SLOT][dev->ordinal()] = (e == cudaSuccess);                                                               \
+        /* how many pairs can be resident at once: the persistent grid is that many clusters */                             \
+        int clusters = 0;                                                                                                   \
+        cudaLaunchConfig_t cfg = {};                                                                                        \
+        cfg.gridDim = dim3((unsigned)(dev->sm_count() & ~1));                                                               \
+        cfg.blockDim = dim3(NUM_THREADS);                                                                                   \
+        cfg.dynamicSmemBytes = P_SMEM_BYTES;                                                                                \
+        cudaLaunchAttribute attr[1];                                                                                        \
+        attr[0].id = cudaLaunchAttributeClusterDimension;                                                                   \
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;                           \
+        cfg.attrs = attr; cfg.numAttrs = 1;                                                                                 \
+        if (e == cudaSuccess && cudaOccupancyMaxActiveClusters(&clusters, gemm_tcgen05_pair_kernel<OutT>, &cfg) != cudaSuccess) { \
+          cudaGetLastError();                                                                                               \
+          clusters = 0;                                                                                                     \
+        }                                                                                                                   \
+        if (clusters <= 0 || clusters > dev->sm_count() / 2) clusters = dev->sm_count() / 2;                                \
+        max_pairs[SLOT][dev->ordinal()] = clusters;                                                                         \
+      }                                                                                                                     \
+    }                                                                                                                       \
+    const int64_t cap = max_pairs[SLOT][dev->ordinal()];                                                                    \
+    const int64_t pairs = g.total_tiles < cap ? g.total_tiles : cap;                                                        \
+    if (e == cudaSuccess)                                                                                                   \
+      gemm_tcgen05_pair_kernel<OutT><<<(unsigned)(2 * pairs), NUM_THREADS, P_SMEM_BYTES, stream>>>(tm_a, tm_b, g);           \
+  } while (0)
+  if (use_pair) {
+    if (is32) LAUNCH_TC_PAIR(float, 3);
+    else if (f16) LAUNCH_TC_PAIR(__half, 4);
+    else LAUNCH_TC_PAIR(__nv_bfloat16, 5);
+  } else {
+    if (is32) LAUNCH_TC(float, 0);
+    else if (f16) LAUNCH_TC(__half, 1);
+    else LAUNCH_TC(__nv_bfloat16, 2);
+  }
 #undef LAUNCH_TC
+#undef LAUNCH_TC_PAIR
   cleanup();  // stream-ordered: the blocks are reused only by work enqueued after this kernel
   if (e != cudaSuccess) {
     cudaGetLastError();
