@@ -252,6 +252,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   if (warp == 0) {
     // ------------------------------------------------------------------ producer ---
     if (lane == 0) {
+      // one thread, about 500 cycles per stage: no divisions in the loop, (seg, kb) advance by increments
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -259,28 +260,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         int b, m_t, n_t;
         tile_coords(g, t, &b, &m_t, &n_t);
         const int m0 = m_t * BM, n0 = n_t * BN;
-        for (int it = 0; it < iters; ++it) {
-          if (!mbar_wait(&empty[s], phase ^ 1, err, 1)) { ok = false; break; }
-          const int seg = it / g.k_blocks, kb = it % g.k_blocks;
+        for (int seg = 0; seg < g.segs && ok; ++seg) {
           const int pa = g.segs > 1 ? kPlaneA[seg] : 0, pb = g.segs > 1 ? kPlaneB[seg] : 0;
-          unsigned char* sa = tiles + s * STAGE_BYTES;
-          unsigned char* sb = sa + A_STAGE_BYTES;
-          mbar_expect_tx(&full[s], STAGE_BYTES);
-          if (g.a_kmajor) {
-            // box {64 k, 128 m}: 128 rows of 128 bytes
-            tma_load_4d(sa, &tm_a, &full[s], kb * BK, m0, b, pa);
-          } else {
-            // two boxes {64 m, 64 k}: 64 k-rows of 128 bytes each, one box per 64-wide block of M
-            tma_load_4d(sa, &tm_a, &full[s], m0, kb * BK, b, pa);
-            tma_load_4d(sa + 8192, &tm_a, &full[s], m0 + 64, kb * BK, b, pa);
-          }
-          if (g.b_kmajor) {
-            tma_load_4d(sb, &tm_b, &full[s], kb * BK, n0, b, pb);
-          } else {
+          for (int kb = 0; kb < g.k_blocks; ++kb) {
+            if (!mbar_wait(&empty[s], phase ^ 1, err, 1)) { ok = false; break; }
+            unsigned char* sa = tiles + s * STAGE_BYTES;
+            unsigned char* sb = sa + A_STAGE_BYTES;
+            const int k0 = kb * BK;
+            mbar_expect_tx(&full[s], STAGE_BYTES);
+            if (g.a_kmajor) {
+              // box {64 k, 128 m}: 128 rows of 128 bytes
+              tma_load_4d(sa, &tm_a, &full[s], k0, m0, b, pa);
+            } else {
+              // two boxes {64 m, 64 k}: 64 k-rows of 128 bytes each, one box per 64-wide block of M
+              tma_load_4d(sa, &tm_a, &full[s], m0, k0, b, pa);
+              tma_load_4d(sa + 8192, &tm_a, &full[s], m0 + 64, k0, b, pa);
+            }
+            if (g.b_kmajor) {
+              tma_load_4d(sb, &tm_b, &full[s], k0, n0, b, pb);
+            } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) tma_load_4d(sb + j * 8192, &tm_b, &full[s], n0 + j * 64, kb * BK, b, pb);
+              for (int j = 0; j < 4; ++j) tma_load_4d(sb + j * 8192, &tm_b, &full[s], n0 + j * 64, k0, b, pb);
+            }
+            if (++s == STAGES) { s = 0; phase ^= 1; }
           }
-          if (++s == STAGES) { s = 0; phase ^= 1; }
         }
       }
     }
@@ -300,6 +303,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       // MN-major tile: 64-wide blocks 8192 bytes apart (LBO), 8-k-row groups 1024 bytes apart (SBO); 16 k = 2 groups.
       const uint32_t a_lbo = g.a_kmajor ? 16u : 8192u, b_lbo = g.b_kmajor ? 16u : 8192u;
       const uint32_t a_kstep = g.a_kmajor ? 32u : 2048u, b_kstep = g.b_kmajor ? 32u : 2048u;
+      // per stage the descriptors differ only in the 14-bit address field (shared memory is below 256 KiB: no carry)
+      const uint64_t da0 = make_smem_desc(smem_u32(tiles), a_lbo, 1024), db0 = make_smem_desc(smem_u32(tiles) + A_STAGE_BYTES, b_lbo, 1024);
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -313,13 +318,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         for (int it = 0; it < iters; ++it) {
           if (!mbar_wait(&full[s], phase, err, 3)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sa = smem_u32(tiles + s * STAGE_BYTES), sb = sa + A_STAGE_BYTES;
+          const uint64_t da_s = da0 + (uint64_t)((s * STAGE_BYTES) >> 4), db_s = db0 + (uint64_t)((s * STAGE_BYTES) >> 4);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t da = make_smem_desc(sa + k * a_kstep, a_lbo, 1024);
-            const uint64_t db = make_smem_desc(sb + k * b_kstep, b_lbo, 1024);
-            umma_f16(d_tmem, da, db, idesc, (it | k) != 0 ? 1u : 0u);
-          }
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_f16(d_tmem, da_s + (uint64_t)((k * a_kstep) >> 4), db_s + (uint64_t)((k * b_kstep) >> 4), idesc, (it | k) != 0 ? 1u : 0u);
           tc_commit(&empty[s]);  // frees the stage once these MMAs have read it
           if (++s == STAGES) { s = 0; phase ^= 1; }
         }
@@ -424,35 +426,62 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   if (warp == 0) {
     // ------------------------------------------------------------------ producer ---
     if (lane == 0) {
-      int s = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int64_t t = pair; t < g.total_tiles && ok; t += num_pairs) {
-        int b, m_t, n_t;
-        pair_tile_coords(g, t, &b, &m_t, &n_t);
-        const int m0 = m_t * 2 * BM + (int)rank * BM;          // this CTA's 128 rows of A
-        const int n0 = n_t * BN + (int)rank * P_BN_HALF;       // this CTA's 128 columns of B
-        for (int it = 0; it < iters; ++it) {
-          if (!mbar_wait_cluster(&empty[s], phase ^ 1, err, 1)) { ok = false; break; }
-          const int seg = it / g.k_blocks, kb = it % g.k_blocks;
-          const int pa = g.segs > 1 ? kPlaneA[seg] : 0, pb = g.segs > 1 ? kPlaneB[seg] : 0;
-          unsigned char* sa = tiles + s * P_STAGE_BYTES;
-          unsigned char* sb = sa + A_STAGE_BYTES;
+      // A single thread runs this loop and every stage has about 500 cycles, so it carries no divisions: the cursor
+      // (tile, seg, kb) advances by increments.  (Measured: with a division per k-block the loop itself cost 10 % of
+      // the kernel's throughput; asking L2 to prefetch tiles ahead of the ring halved it, the requests compete with the loads.)
+      struct Cursor {
+        int64_t t;        // global tile index
+        int b, m0, n0;    // this CTA's rows of A / columns of B in that tile
+        int seg, kb;
+      };
+      auto place = [&](Cursor& c) {
+        int m_t, n_t;
+        pair_tile_coords(g, c.t, &c.b, &m_t, &n_t);
+        c.m0 = m_t * 2 * BM + (int)rank * BM;
+        c.n0 = n_t * BN + (int)rank * P_BN_HALF;
+      };
+      auto advance = [&](Cursor& c) {  // returns false past the last item
+        if (++c.kb == g.k_blocks) {
+          c.kb = 0;
+          if (++c.seg == g.segs) {
+            c.seg = 0;
+            c.t += num_pairs;
+            if (c.t >= g.total_tiles) return false;
+            place(c);
+          }
+        }
+        return true;
+      };
+      auto issue = [&](unsigned char* sa, uint32_t bar, const Cursor& c) {
+        const int pa = g.segs > 1 ? kPlaneA[c.seg] : 0, pb = g.segs > 1 ? kPlaneB[c.seg] : 0;
+        const int k0 = c.kb * BK;
+        unsigned char* sb = sa + A_STAGE_BYTES;
+        if (g.a_kmajor) {
+          tma_load_4d_pair(sa, &tm_a, bar, k0, c.m0, c.b, pa);
+        } else {
+          tma_load_4d_pair(sa, &tm_a, bar, c.m0, k0, c.b, pa);
+          tma_load_4d_pair(sa + 8192, &tm_a, bar, c.m0 + 64, k0, c.b, pa);
+        }
+        if (g.b_kmajor) {
+          tma_load_4d_pair(sb, &tm_b, bar, k0, c.n0, c.b, pb);
+        } else {
+          tma_load_4d_pair(sb, &tm_b, bar, c.n0, k0, c.b, pb);
+          tma_load_4d_pair(sb + 8192, &tm_b, bar, c.n0 + 64, k0, c.b, pb);
+        }
+      };
+      if (pair < g.total_tiles) {
+        Cursor ld{pair, 0, 0, 0, 0, 0};
+        place(ld);
+        // full[s] of the leader, as a cluster address: the same offset for every stage
+        const uint32_t full0 = map_to_cta(smem_u32(&full[0]), 0);
+        int s = 0;
+        uint32_t phase = 0;
+        for (;;) {
+          if (!mbar_wait_cluster(&empty[s], phase ^ 1, err, 1)) break;
           if (leader) mbar_expect_tx(&full[s], 2 * P_STAGE_BYTES);
-          const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
-          if (g.a_kmajor) {
-            tma_load_4d_pair(sa, &tm_a, bar, kb * BK, m0, b, pa);
-          } else {
-            tma_load_4d_pair(sa, &tm_a, bar, m0, kb * BK, b, pa);
-            tma_load_4d_pair(sa + 8192, &tm_a, bar, m0 + 64, kb * BK, b, pa);
-          }
-          if (g.b_kmajor) {
-            tma_load_4d_pair(sb, &tm_b, bar, kb * BK, n0, b, pb);
-          } else {
-            tma_load_4d_pair(sb, &tm_b, bar, n0, kb * BK, b, pb);
-            tma_load_4d_pair(sb + 8192, &tm_b, bar, n0 + 64, kb * BK, b, pb);
-          }
+          issue(tiles + s * P_STAGE_BYTES, full0 + s * 8, ld);
           if (++s == P_STAGES) { s = 0; phase ^= 1; }
+          if (!advance(ld)) break;
         }
       }
     }
@@ -469,6 +498,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
       idesc |= (uint32_t)((2 * BM) >> 4) << 24;   // M = 256 across the pair
       const uint32_t a_lbo = g.a_kmajor ? 16u : 8192u, b_lbo = g.b_kmajor ? 16u : 8192u;
       const uint32_t a_kstep = g.a_kmajor ? 32u : 2048u, b_kstep = g.b_kmajor ? 32u : 2048u;
+      const uint32_t empty_own = map_to_cta(smem_u32(&empty[0]), 0), empty_peer = map_to_cta(smem_u32(&empty[0]), 1);
+      const uint64_t da0 = make_smem_desc(smem_u32(tiles), a_lbo, 1024), db0 = make_smem_desc(smem_u32(tiles) + A_STAGE_BYTES, b_lbo, 1024);
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -482,16 +513,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         for (int it = 0; it < iters; ++it) {
           if (!mbar_wait_cluster(&full[s], phase, err, 3)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sa = smem_u32(tiles + s * P_STAGE_BYTES), sb = sa + A_STAGE_BYTES;
+          // the descriptors differ from stage 0's only in the 14-bit address field (shared memory is below 256 KiB: no carry)
+          const uint64_t da_s = da0 + (uint64_t)((s * P_STAGE_BYTES) >> 4), db_s = db0 + (uint64_t)((s * P_STAGE_BYTES) >> 4);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t da = make_smem_desc(sa + k * a_kstep, a_lbo, 1024);
-            const uint64_t db = make_smem_desc(sb + k * b_kstep, b_lbo, 1024);
-            umma_f16_pair(d_tmem, da, db, idesc, (it | k) != 0 ? 1u : 0u);
-          }
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_f16_pair(d_tmem, da_s + (uint64_t)((k * a_kstep) >> 4), db_s + (uint64_t)((k * b_kstep) >> 4), idesc, (it | k) != 0 ? 1u : 0u);
           // the stage is free in BOTH CTAs once these MMAs have read it
-          tc_commit_pair(map_to_cta(smem_u32(&empty[s]), 0));
-          tc_commit_pair(map_to_cta(smem_u32(&empty[s]), 1));
+          tc_commit_pair(empty_own + s * 8);
+          tc_commit_pair(empty_peer + s * 8);
           if (++s == P_STAGES) { s = 0; phase ^= 1; }
         }
         if (ok) {
@@ -608,7 +637,11 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
 
   // CTA pairs (256-row tiles) whenever there is more than one 128-row tile of M to share B with
   static const bool pair_allowed = []() { const char* v = getenv("B200MLX_GEMM_PAIR"); return !(v && v[0] == '0'); }();
-  const bool use_pair = pair_allowed && p.m > BM;
+  // Pairs pay off once a tile's main loop is long enough to hide the cross-CTA hand-offs (measured: K = 512 is 8 % slower on
+  // pairs, K >= 4096 is 5 - 10 % faster) and there are enough tiles to fill the GPU either way.
+  const int64_t k_iters = (p.k + BK - 1) / BK * (is32 ? 6 : 1);
+  const int64_t pair_tiles = ((p.m + 2 * BM - 1) / (2 * BM)) * ((p.n + BN - 1) / BN) * p.batch;
+  const bool use_pair = pair_allowed && p.m > BM && k_iters >= 16 && pair_tiles >= 32;
 
   CUtensorMap tm_a, tm_b;
   Status s;
