@@ -8,20 +8,23 @@
 // around a softmax and materialises the [B, H, Sq, Sk] score tensor, a causal
 // mask built from two iotas, repeated K/V heads for GQA and up to four layout
 // transposes (mpsgraph function.go:2697-2907).  Here none of those tensors
-// exists: one CTA owns 128 query rows of one head and walks the keys in blocks of
-// 64 with an online softmax, reading Q, K and V in place through TMA.
+// exists: one CTA owns 256 query rows of one head (two tiles of 128) and walks
+// the keys in blocks of 64 with an online softmax, reading Q, K and V in place
+// through TMA.
 //
-// Per key block:  S = Q K_j^T   (tcgen05.mma 128 x 64 x 16, four per block, fp32 in TMEM)
-//                 each of the 128 threads owns one query row: tcgen05.ld its 64 scores,
-//                 mask, running max / sum in base 2, P = exp2(...) rounded to the input
-//                 type and written to shared memory in the 128-byte-swizzled K-major layout
-//                 O_j = P V_j   (tcgen05.mma 128 x 64 x 16, four per block; V is read as an
-//                 MN-major operand, so it needs no transpose)
-//                 O = O * alpha + O_j in registers.
-// K/V blocks are double-buffered; three CTAs fit on an SM, so one CTA's softmax
-// overlaps another's MMAs.  Causal launches skip key blocks right of the diagonal.
-// Tensor-bound in flops (4 * Sq * Sk * 64 per head, half that when causal), with
-// the exponentials (one MUFU op per score) as the co-limiter.
+// Warp roles (320 threads, two CTAs per SM):
+//   warp 0      loader: Q once, then K_j / V_j blocks into a 3-stage ring;
+//   warp 1      issuer: S_t = Q_t K_j^T (tcgen05.mma 128 x 64 x 16, fp32 in TMEM) and O_t += P_t V_j for both tiles
+//               (V read as an MN-major operand, so it needs no transpose); the two tiles alternate, so one tile's
+//               MMAs run under the other tile's softmax;
+//   warps 2-5   softmax of tile 0, warps 6-9 of tile 1: each thread owns one query row: tcgen05.ld its 64 scores,
+//               running max / sum in base 2 with the scale folded into the exponent's FMA, P = exp2(...) rounded to
+//               the input type and written to shared memory in the 128-byte-swizzled K-major layout.
+// The output accumulates in TMEM across key blocks.  Its reference maximum is only moved when a row's maximum grew by
+// more than 2^8 since the last move (then the row of O is rescaled in TMEM); P stays below 2^8 and the final division
+// by the row sum cancels the common factor, so nothing is lost and most blocks skip the rescale.
+// Causal launches skip key blocks right of the diagonal.  Tensor-bound in flops (4 * Sq * Sk * 64 per head, half that
+// when causal) with the exponentials (one MUFU op per score, 16 per clock per SM) as the real limiter at head dim 64.
 // Every mbarrier wait is bounded; a wait that gives up sets the device's error word.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -40,14 +43,18 @@ namespace {
 using namespace sm100;
 
 constexpr int HD = 64;           // head dim
-constexpr int BQ = 128;          // query rows per CTA (UMMA M)
+constexpr int BQ = 128;          // query rows per tile (UMMA M)
+constexpr int QT = 2;            // query tiles per CTA
 constexpr int BKV = 64;          // keys per step (UMMA N of the score MMA, K of the PV MMA)
-constexpr int Q_BYTES = BQ * HD * 2;     // 16 KiB
-constexpr int KV_BYTES = BKV * HD * 2;   // 8 KiB
-constexpr int P_BYTES = BQ * BKV * 2;    // 16 KiB
-constexpr int ATT_SMEM = Q_BYTES + 4 * KV_BYTES + P_BYTES + 1024 + 128;
-constexpr int ATT_THREADS = 128;
-constexpr int ATT_TMEM_COLS = 128;       // 64 score columns + 64 output columns
+constexpr int KV_STAGES = 3;
+constexpr int Q_BYTES = BQ * HD * 2;     // 16 KiB per tile
+constexpr int KV_BYTES = BKV * HD * 2;   // 8 KiB (K or V)
+constexpr int P_BYTES = BQ * BKV * 2;    // 16 KiB per tile
+constexpr int ATT_TILE_BYTES = QT * Q_BYTES + KV_STAGES * 2 * KV_BYTES + QT * P_BYTES;  // 112 KiB
+constexpr int ATT_SMEM = ATT_TILE_BYTES + 256;   // + barriers; the dynamic window itself is 1024-byte aligned (checked)
+constexpr int ATT_THREADS = 320;
+constexpr int ATT_TMEM_COLS = 256;       // S0, S1, O0, O1: 64 columns each
+constexpr float kRescaleThreshold = 8.f; // log2 units
 
 struct AttArgs {
   void* o;
@@ -55,7 +62,7 @@ struct AttArgs {
   int B, H, Hkv, Sq, Sk;
   int causal;
   int is_f16;
-  float scale_log2e;          // scale * log2(e)
+  float scale_log2e;          // scale * log2(e), > 0
   int* err_flag;
 };
 
@@ -75,46 +82,53 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 template <typename T>
-__global__ void __launch_bounds__(ATT_THREADS, 3)
+__global__ void __launch_bounds__(ATT_THREADS, 2)
 attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const AttArgs g) {
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  unsigned char* sQ = base;
-  unsigned char* sK = sQ + Q_BYTES;            // two buffers
-  unsigned char* sV = sK + 2 * KV_BYTES;       // two buffers
-  unsigned char* sP = sV + 2 * KV_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
-  uint64_t* q_full = bars;          // [1]
-  uint64_t* kv_full = bars + 1;     // [2]
-  uint64_t* s_done = bars + 3;      // [1] score MMAs finished
-  uint64_t* pv_done = bars + 4;     // [1] PV MMAs finished
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* sQ = smem_raw;                          // [QT] tiles
+  unsigned char* sKV = sQ + QT * Q_BYTES;                // [KV_STAGES] x (K, V)
+  unsigned char* sP = sKV + KV_STAGES * 2 * KV_BYTES;    // [QT] tiles
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + QT * P_BYTES);
+  uint64_t* q_full = bars;                       // [1]
+  uint64_t* kv_full = bars + 1;                  // [KV_STAGES] bytes of K_j and V_j landed
+  uint64_t* kv_empty = kv_full + KV_STAGES;      // [KV_STAGES] every MMA that reads the stage is done
+  uint64_t* s_full = kv_empty + KV_STAGES;       // [QT] scores of the current block are in TMEM
+  uint64_t* p_ready = s_full + QT;               // [QT] P is in shared memory (and S has been read): 4 warp arrivals
+  uint64_t* o_done = p_ready + QT;               // [QT] the PV MMAs of the current block are done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + QT);
+  int* failed = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* err = g.err_flag;
 
   // work item: heavy (late) query blocks first so the causal tail is short
-  const int nq = (g.Sq + BQ - 1) / BQ;
+  const int nq = (g.Sq + QT * BQ - 1) / (QT * BQ);
   const int64_t item = blockIdx.x;
   const int qb = nq - 1 - (int)(item % nq);
   const int h = (int)((item / nq) % g.H);
   const int b = (int)(item / ((int64_t)nq * g.H));
   const int hkv = h / (g.H / g.Hkv);
-  const int q0 = qb * BQ;
-  int kv_end = g.Sk;
-  if (g.causal) kv_end = (q0 + BQ < g.Sk) ? q0 + BQ : g.Sk;   // keys beyond the block's last row are masked for every row
-  const int nkv = (kv_end + BKV - 1) / BKV;
+  const int q0 = qb * QT * BQ;
+  // key blocks each tile walks: under a causal mask keys beyond the tile's last row are masked for every row
+  auto blocks_of = [&](int t) {
+    const int first = q0 + t * BQ;
+    int kv_end = g.Sk;
+    if (g.causal && first + BQ < kv_end) kv_end = first + BQ;
+    return first < g.Sq ? (kv_end + BKV - 1) / BKV : 0;   // a tile wholly past the last query row does nothing
+  };
+  const int nkv0 = blocks_of(0), nkv1 = blocks_of(1);
+  const int nkv_max = nkv0 > nkv1 ? nkv0 : nkv1;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    mbar_init(&kv_full[0], 1);
-    mbar_init(&kv_full[1], 1);
-    mbar_init(s_done, 1);
-    mbar_init(pv_done, 1);
+    for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    for (int t = 0; t < QT; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_ready[t], 4); mbar_init(&o_done[t], 1); }
+    *failed = 0;
+    if ((smem_u32(smem_raw) & 1023u) != 0) { atomicCAS((int*)g.err_flag, 0, 5); *failed = 1; }  // swizzled tiles need the alignment
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 0) {
+  if (warp == 1) {
     tmem_alloc(tmem_slot, ATT_TMEM_COLS);
     tmem_relinquish();
   }
@@ -122,152 +136,225 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 64;
-  const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;   // this warp's 32 TMEM lanes
+  const bool misaligned = *failed != 0;
 
-  // instruction descriptors: fp32 accumulate, M = 128, N = 64
-  const uint32_t fmt = g.is_f16 ? 0u : 1u;
-  const uint32_t idesc_common = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
-  const uint32_t idesc_s = idesc_common;                 // Q (K-major) x K_j (K-major)
-  const uint32_t idesc_pv = idesc_common | (1u << 16);   // P (K-major) x V_j (MN-major)
-
-  bool ok = true;
-  bool issued = true;   // thread 0: false once one of its own waits gave up
-  if (threadIdx.x == 0) {
-    mbar_expect_tx(q_full, Q_BYTES);
-    tma_load_4d(sQ, &tm_q, q_full, 0, q0, h, b);
-    mbar_expect_tx(&kv_full[0], 2 * KV_BYTES);
-    tma_load_4d(sK, &tm_k, &kv_full[0], 0, 0, hkv, b);
-    tma_load_4d(sV, &tm_v, &kv_full[0], 0, 0, hkv, b);
-  }
-
-  const int row = warp * 32 + lane;      // query row inside the block
-  const int q_row = q0 + row;
-  float o_acc[HD];
+  if (misaligned) {
+    // nothing was issued; fall through to the teardown
+  } else if (warp == 0) {
+    // -------------------------------------------------------------------- loader ---
+    if (lane == 0) {
+      mbar_expect_tx(q_full, QT * Q_BYTES);
 #pragma unroll
-  for (int d = 0; d < HD; ++d) o_acc[d] = 0.f;
-  float m_run = -INFINITY, l_run = 0.f;
-
-  for (int j = 0; j < nkv; ++j) {
-    const int buf = j & 1;
-    const uint32_t par = (uint32_t)(j & 1);
-    if (threadIdx.x == 0) {
-      // prefetch the next key/value block into the other buffer (its last readers, the PV MMAs of step j-1, are done)
-      if (j + 1 < nkv) {
-        mbar_expect_tx(&kv_full[buf ^ 1], 2 * KV_BYTES);
-        tma_load_4d(sK + (buf ^ 1) * KV_BYTES, &tm_k, &kv_full[buf ^ 1], 0, (j + 1) * BKV, hkv, b);
-        tma_load_4d(sV + (buf ^ 1) * KV_BYTES, &tm_v, &kv_full[buf ^ 1], 0, (j + 1) * BKV, hkv, b);
+      for (int t = 0; t < QT; ++t) tma_load_4d(sQ + t * Q_BYTES, &tm_q, q_full, 0, q0 + t * BQ, h, b);
+      int s = 0;
+      uint32_t phase = 0;
+      for (int j = 0; j < nkv_max; ++j) {
+        if (!mbar_wait(&kv_empty[s], phase ^ 1, err, 1)) break;
+        unsigned char* dst = sKV + s * 2 * KV_BYTES;
+        mbar_expect_tx(&kv_full[s], 2 * KV_BYTES);
+        tma_load_4d(dst, &tm_k, &kv_full[s], 0, j * BKV, hkv, b);
+        tma_load_4d(dst + KV_BYTES, &tm_v, &kv_full[s], 0, j * BKV, hkv, b);
+        if (++s == KV_STAGES) { s = 0; phase ^= 1; }
       }
-      bool landed = (j > 0) || mbar_wait(q_full, 0, err, 1);
-      landed = landed && mbar_wait(&kv_full[buf], (uint32_t)((j >> 1) & 1), err, 3);
-      issued = landed;
-      if (landed) {
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------------- issuer ---
+    if (lane == 0) {
+      // instruction descriptors: fp32 accumulate, M = 128, N = 64
+      const uint32_t fmt = g.is_f16 ? 0u : 1u;
+      const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
+      const uint32_t idesc_pv = idesc_s | (1u << 16);   // P (K-major) x V_j (MN-major)
+      const uint64_t dq0 = make_smem_desc(smem_u32(sQ), 16, 1024);
+      const uint64_t dk0 = make_smem_desc(smem_u32(sKV), 16, 1024);
+      const uint64_t dv0 = make_smem_desc(smem_u32(sKV) + KV_BYTES, 8192, 1024);
+      const uint64_t dp0 = make_smem_desc(smem_u32(sP), 16, 1024);
+      auto issue_scores = [&](int t, int stage) {   // S_t = Q_t K^T
+        const uint64_t dq = dq0 + (uint64_t)((t * Q_BYTES) >> 4), dk = dk0 + (uint64_t)((stage * 2 * KV_BYTES) >> 4);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) umma_f16(tmem_base + t * 64, dq + (uint64_t)((k * 32) >> 4), dk + (uint64_t)((k * 32) >> 4), idesc_s, k != 0 ? 1u : 0u);
+        tc_commit(&s_full[t]);
+      };
+      bool ok = mbar_wait(q_full, 0, err, 2);
+      int s = 0;
+      uint32_t phase = 0;
+      if (ok) ok = mbar_wait(&kv_full[0], 0, err, 3);
+      if (ok) {
         tc_fence_after();
-        const uint32_t a0 = smem_u32(sQ), b0 = smem_u32(sK + buf * KV_BYTES);
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k)
-          umma_f16(tmem_s, make_smem_desc(a0 + k * 32, 16, 1024), make_smem_desc(b0 + k * 32, 16, 1024), idesc_s, k != 0 ? 1u : 0u);
+        for (int t = 0; t < QT; ++t)
+          if ((t ? nkv1 : nkv0) > 0) issue_scores(t, 0);
       }
-      tc_commit(s_done);   // also arrives when nothing was issued, so the other threads never wait on a dead step
-    }
-    // ---- scores -> probabilities ----
-    {
-      const bool landed = mbar_wait(s_done, par, err, 4);
-      if (!__syncthreads_and((landed && issued) ? 1 : 0)) { ok = false; break; }
-    }
-    tc_fence_after();
-    uint32_t sr[64];
-    tmem_ld32(tmem_s + lane_addr, sr);
-    tmem_ld32(tmem_s + lane_addr + 32, sr + 32);
-    tmem_ld_wait();
-    const int kv0 = j * BKV;
-    int limit = g.Sk - kv0;                               // columns >= limit are masked
-    if (g.causal && q_row + 1 - kv0 < limit) limit = q_row + 1 - kv0;
-    float mx = m_run;
+      for (int j = 0; j < nkv_max && ok; ++j) {
+        const int s_next = (s + 1 == KV_STAGES) ? 0 : s + 1;
+        const uint32_t phase_next = (s + 1 == KV_STAGES) ? (phase ^ 1) : phase;
+        bool next_landed = false;
 #pragma unroll
-    for (int c = 0; c < 64; ++c) {
-      float t = __uint_as_float(sr[c]) * g.scale_log2e;
-      t = (c < limit) ? t : -INFINITY;
-      sr[c] = __float_as_uint(t);
-      mx = fmaxf(mx, t);
-    }
-    // a row with nothing visible yet keeps m = -inf; use 0 as the reference point so exp2 sees -inf, not NaN
-    const float m_ref = (mx == -INFINITY) ? 0.f : mx;
-    const float alpha = fast_exp2(m_run - m_ref);
-    float psum = 0.f;
-    uint32_t packed[32];
+        for (int t = 0; t < QT; ++t) {
+          const int nt = t ? nkv1 : nkv0;
+          if (j >= nt) continue;
+          if (!mbar_wait(&p_ready[t], (uint32_t)(j & 1), err, 4)) { ok = false; break; }
+          tc_fence_after();
+          // O_t (+)= P_t V_j
+          const uint64_t dp = dp0 + (uint64_t)((t * P_BYTES) >> 4), dv = dv0 + (uint64_t)((s * 2 * KV_BYTES) >> 4);
 #pragma unroll
-    for (int c = 0; c < 64; c += 2) {
-      const float p0 = fast_exp2(__uint_as_float(sr[c]) - m_ref);
-      const float p1 = fast_exp2(__uint_as_float(sr[c + 1]) - m_ref);
-      psum += p0 + p1;
-      packed[c >> 1] = pack2<T>(p0, p1);
-    }
-    l_run = l_run * alpha + psum;
-    m_run = mx;
-    // P row -> shared memory, K-major with 128-byte swizzle: 16-byte chunk c of row r lives at chunk (c ^ (r & 7))
-    {
-      unsigned char* prow = sP + row * 128;
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        uint4 q = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-        *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = q;
+          for (int k = 0; k < BKV / 16; ++k)
+            umma_f16(tmem_base + 128 + t * 64, dp + (uint64_t)((k * 32) >> 4), dv + (uint64_t)((k * 2048) >> 4), idesc_pv, (j | k) != 0 ? 1u : 0u);
+          tc_commit(&o_done[t]);
+          // the tile's next scores go out at once: its softmax warps have read S_t (they said so with p_ready)
+          if (j + 1 < nt) {
+            if (!next_landed) {
+              if (!mbar_wait(&kv_full[s_next], phase_next, err, 3)) { ok = false; break; }
+              tc_fence_after();
+              next_landed = true;
+            }
+            issue_scores(t, s_next);
+          }
+        }
+        if (!ok) break;
+        tc_commit(&kv_empty[s]);   // every MMA that reads stage s has been issued before this point
+        s = s_next;
+        phase = phase_next;
       }
     }
-    fence_proxy_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    if (threadIdx.x == 0) {
+  } else {
+    // ------------------------------------------------------------------- softmax ---
+    const int t = (warp - 2) >> 2;          // query tile
+    const int quarter = warp & 3;           // TMEM lanes [32 * quarter, +32) are this warp's
+    const int row = quarter * 32 + lane;    // row inside the tile
+    const int q_row = q0 + t * BQ + row;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tmem_s = tmem_base + t * 64 + lane_addr, tmem_o = tmem_base + 128 + t * 64 + lane_addr;
+    unsigned char* prow = sP + t * P_BYTES + row * 128;
+    const float c = g.scale_log2e;
+    float m_ref = 0.f, l_run = 0.f;         // p = exp2(c * s - m_ref)
+    bool ok = true;
+    const int n = t ? nkv1 : nkv0;
+    for (int j = 0; j < n; ++j) {
+      {
+        const bool landed = mbar_wait(&s_full[t], (uint32_t)(j & 1), err, 6);
+        if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }   // tcgen05.ld is warp-collective: leave together
+      }
       tc_fence_after();
-      const uint32_t a0 = smem_u32(sP), b0 = smem_u32(sV + buf * KV_BYTES);
+      const int kv0 = j * BKV;
+      int limit = g.Sk - kv0;                               // columns >= limit are masked
+      if (g.causal && q_row + 1 - kv0 < limit) limit = q_row + 1 - kv0;
+      // Pass 1: the row maximum.  The scores are read from TMEM in halves of 32 columns, and again in pass 2, which
+      // keeps 32 values live instead of 64 (TMEM reads are cheap; registers are what limits two CTAs per SM).
+      float mx = -INFINITY;
 #pragma unroll
-      for (int k = 0; k < BKV / 16; ++k)
-        umma_f16(tmem_o, make_smem_desc(a0 + k * 32, 16, 1024), make_smem_desc(b0 + k * 2048, 8192, 1024), idesc_pv, k != 0 ? 1u : 0u);
-      tc_commit(pv_done);
+      for (int half = 0; half < 2; ++half) {
+        uint32_t sr[32];
+        tmem_ld32(tmem_s + half * 32, sr);
+        tmem_ld_wait();
+        if (limit < 64) {
+#pragma unroll
+          for (int cidx = 0; cidx < 32; ++cidx)
+            if (half * 32 + cidx >= limit) sr[cidx] = 0xff800000u;   // -inf
+        }
+#pragma unroll
+        for (int cidx = 0; cidx < 32; ++cidx) mx = fmaxf(mx, __uint_as_float(sr[cidx]));
+      }
+      const float m_new = mx * c;                           // c > 0: the maximum commutes with the scale
+      // Move the reference only when some row of the warp needs it (tcgen05.ld / st are warp-collective).
+      const bool grow = (j == 0) ? true : (m_new > m_ref + kRescaleThreshold);
+      bool waited_o = false;
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_next = grow ? (m_new == -INFINITY ? 0.f : m_new) : m_ref;
+        if (j > 0) {
+          // the PV MMAs of block j-1 must have landed before O is touched
+          const bool landed = mbar_wait(&o_done[t], (uint32_t)((j - 1) & 1), err, 7);
+          if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }
+          waited_o = true;
+          tc_fence_after();
+          const float alpha = fast_exp2(m_ref - m_next);    // 1 for rows that keep their reference
+          l_run *= alpha;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            uint32_t orow[32];
+            tmem_ld32(tmem_o + half * 32, orow);
+            tmem_ld_wait();
+#pragma unroll
+            for (int d = 0; d < 32; ++d) orow[d] = __float_as_uint(__uint_as_float(orow[d]) * alpha);
+            tmem_st32(tmem_o + half * 32, orow);
+          }
+          tmem_st_wait();
+        }
+        m_ref = m_next;
+      }
+      if (j > 0 && !waited_o) {
+        // sP_t is still being read by the PV MMAs of block j-1 until o_done says otherwise
+        const bool landed = mbar_wait(&o_done[t], (uint32_t)((j - 1) & 1), err, 7);
+        if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }
+      }
+      // Pass 2: P = exp2(c * s - m_ref), rounded, into shared memory: K-major with 128-byte swizzle, 16-byte chunk q
+      // of row r lives at chunk (q ^ (r & 7)).
+      float psum = 0.f;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t sr[32];
+        tmem_ld32(tmem_s + half * 32, sr);
+        tmem_ld_wait();
+        if (limit < 64) {
+#pragma unroll
+          for (int cidx = 0; cidx < 32; ++cidx)
+            if (half * 32 + cidx >= limit) sr[cidx] = 0xff800000u;
+        }
+#pragma unroll
+        for (int cidx = 0; cidx < 32; cidx += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[cidx]), c, -m_ref));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[cidx + 1]), c, -m_ref));
+          psum += p0 + p1;
+          sr[cidx >> 1] = pack2<T>(p0, p1);   // in place: entry cidx / 2 has been consumed
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          *reinterpret_cast<uint4*>(prow + (((half * 4 + q) ^ (row & 7)) << 4)) = make_uint4(sr[4 * q], sr[4 * q + 1], sr[4 * q + 2], sr[4 * q + 3]);
+      }
+      l_run += psum;
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_ready[t]);
     }
-    // rescale the running output while the PV MMAs run
+    if (ok && n > 0) {
+      const bool landed = mbar_wait(&o_done[t], (uint32_t)((n - 1) & 1), err, 7);
+      if (__all_sync(0xffffffffu, landed)) {
+        tc_fence_after();
+        const float inv = 1.0f / l_run;   // a fully masked row (l = 0) yields NaN, as the unfused path does
+        T* orow_g = reinterpret_cast<T*>(g.o) + (int64_t)b * g.o_sb + (int64_t)h * g.o_sh + (int64_t)q_row * g.o_ss;
 #pragma unroll
-    for (int d = 0; d < HD; ++d) o_acc[d] *= alpha;
-    {
-      const bool landed = mbar_wait(pv_done, par, err, 2);
-      if (!__syncthreads_and(landed ? 1 : 0)) { ok = false; break; }
+        for (int half = 0; half < 2; ++half) {
+          uint32_t orow[32];
+          tmem_ld32(tmem_o + half * 32, orow);
+          tmem_ld_wait();
+          if (q_row < g.Sq) {
+#pragma unroll
+            for (int d = 0; d < 32; d += 8) {
+              uint4 q;
+              q.x = pack2<T>(__uint_as_float(orow[d]) * inv, __uint_as_float(orow[d + 1]) * inv);
+              q.y = pack2<T>(__uint_as_float(orow[d + 2]) * inv, __uint_as_float(orow[d + 3]) * inv);
+              q.z = pack2<T>(__uint_as_float(orow[d + 4]) * inv, __uint_as_float(orow[d + 5]) * inv);
+              q.w = pack2<T>(__uint_as_float(orow[d + 6]) * inv, __uint_as_float(orow[d + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow_g + half * 32 + d) = q;
+            }
+          }
+        }
+      }
     }
-    tc_fence_after();
-    uint32_t pr[64];
-    tmem_ld32(tmem_o + lane_addr, pr);
-    tmem_ld32(tmem_o + lane_addr + 32, pr + 32);
-    tmem_ld_wait();
-#pragma unroll
-    for (int d = 0; d < HD; ++d) o_acc[d] += __uint_as_float(pr[d]);
-    tc_fence_before();
-    // the next step's score MMA overwrites tmem_s and its PV MMA overwrites tmem_o and sP: every thread has finished
-    // reading them once it passes the __syncthreads_and at the top of the next step (score) / the one above (PV).
   }
 
-  if (ok && q_row < g.Sq) {
-    const float inv = 1.0f / l_run;   // a fully masked row (l = 0) yields NaN, as the unfused path does
-    T* orow = reinterpret_cast<T*>(g.o) + (int64_t)b * g.o_sb + (int64_t)h * g.o_sh + (int64_t)q_row * g.o_ss;
-#pragma unroll
-    for (int d = 0; d < HD; d += 8) {
-      uint4 q;
-      q.x = pack2<T>(o_acc[d] * inv, o_acc[d + 1] * inv);
-      q.y = pack2<T>(o_acc[d + 2] * inv, o_acc[d + 3] * inv);
-      q.z = pack2<T>(o_acc[d + 4] * inv, o_acc[d + 5] * inv);
-      q.w = pack2<T>(o_acc[d + 6] * inv, o_acc[d + 7] * inv);
-      *reinterpret_cast<uint4*>(orow + d) = q;
-    }
-  }
-
+  // ---------------------------------------------------------------------- teardown ---
   tc_fence_before();
-  __shared__ int failed;
-  if (threadIdx.x == 0) failed = ok ? 0 : 1;
   __syncthreads();
-  if (failed != 0) {
+  if (threadIdx.x == 0 && *err != 0) *failed = 1;
+  __syncthreads();
+  if (*failed != 0) {
+    // a wait gave up: let copies and MMAs still in flight settle before the tiles and TMEM go away
     const unsigned long long t0 = global_ns();
     while (global_ns() - t0 < 200000ull) {}
     __syncthreads();
   }
-  if (warp == 0) {
+  if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, ATT_TMEM_COLS);
   }
@@ -279,6 +366,7 @@ bool attention_supported(const AttentionParams& p) {
   const bool is16 = p.dtype == B200_BFLOAT16 || p.dtype == B200_FLOAT16;
   if (!is16 || p.head_dim != HD) return false;
   if (p.B <= 0 || p.H <= 0 || p.Hkv <= 0 || p.Sq <= 0 || p.Sk <= 0 || p.H % p.Hkv != 0) return false;
+  if (!(p.scale > 0) || !(p.scale < 1e30)) return false;   // the kernel takes the row maximum before scaling
   auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
   return al(p.q) && al(p.k) && al(p.v) && al(p.o);
 }
@@ -314,7 +402,7 @@ Status attention(Device* dev, const AttentionParams& p) {
   g.is_f16 = f16 ? 1 : 0;
   g.scale_log2e = (float)(p.scale * 1.4426950408889634);
   g.err_flag = dev->kernel_error_flag();
-  const int64_t nq = (p.Sq + BQ - 1) / BQ;
+  const int64_t nq = (p.Sq + QT * BQ - 1) / (QT * BQ);
   const int64_t grid = nq * p.H * p.B;
   if (grid > 0x7fffffffLL) return Status::Unsupported("attention: too many work items");
   static std::mutex attr_mu;

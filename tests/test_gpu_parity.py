@@ -343,10 +343,10 @@ def _dot_tol(dtype):
 
 @pytest.mark.parametrize("dtype", [np.float32, BF16], ids=["f32", "bf16"])
 @pytest.mark.parametrize("form", ["BMK_BKN", "BKM_BKN", "BMK_BNK", "BKM_BNK"])
-# the last three run on CTA pairs (256-row tiles): a ragged second CTA, ragged N across two column tiles, and more tiles than
-# resident pairs (several tiles per pair: both accumulators and every ring phase are reused)
+# the last two run on CTA pairs (256-row tiles; chosen for K >= 1024 and >= 32 tiles): a ragged last pair (its second CTA has
+# no rows) with a ragged last column tile, and more tiles than resident pairs (both accumulators and every ring phase reused)
 @pytest.mark.parametrize("B,M,N,K", [(1, 2, 2, 3), (2, 64, 48, 40), (3, 130, 70, 257), (2, 256, 256, 128), (1, 512, 384, 1024),
-                                     (2, 392, 520, 192), (1, 136, 264, 64), (4, 1280, 1024, 448)])
+                                     (2, 392, 520, 192), (2, 1096, 1032, 1024), (4, 1280, 1024, 1024)])
 def test_dot_general_forms(b200, backend, dtype, form, B, M, N, K):
     rng = np.random.default_rng(29)
     a = rng_array(rng, (B, M, K) if form.startswith("BMK") else (B, K, M), dtype)
