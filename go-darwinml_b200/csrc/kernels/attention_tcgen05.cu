@@ -238,22 +238,28 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const int kv0 = j * BKV;
       int limit = g.Sk - kv0;                               // columns >= limit are masked
       if (g.causal && q_row + 1 - kv0 < limit) limit = q_row + 1 - kv0;
-      // Pass 1: the row maximum.  The scores are read from TMEM in halves of 32 columns, and again in pass 2, which
-      // keeps 32 values live instead of 64 (TMEM reads are cheap; registers are what limits two CTAs per SM).
-      float mx = -INFINITY;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t sr[32];
-        tmem_ld32(tmem_s + half * 32, sr);
+      // Pass 1: the row maximum.  The scores are read from TMEM here and again in pass 2 instead of being held across
+      // the rescale in between (TMEM reads are cheap; registers are what limits two CTAs per SM).
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;   // four chains: the reduction is latency-bound otherwise
+      {
+        uint32_t sr[64];
+        tmem_ld32(tmem_s, sr);
+        tmem_ld32(tmem_s + 32, sr + 32);
         tmem_ld_wait();
         if (limit < 64) {
 #pragma unroll
-          for (int cidx = 0; cidx < 32; ++cidx)
-            if (half * 32 + cidx >= limit) sr[cidx] = 0xff800000u;   // -inf
+          for (int cidx = 0; cidx < 64; ++cidx)
+            if (cidx >= limit) sr[cidx] = 0xff800000u;   // -inf
         }
 #pragma unroll
-        for (int cidx = 0; cidx < 32; ++cidx) mx = fmaxf(mx, __uint_as_float(sr[cidx]));
+        for (int cidx = 0; cidx < 64; cidx += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(sr[cidx]));
+          mx1 = fmaxf(mx1, __uint_as_float(sr[cidx + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(sr[cidx + 2]));
+          mx3 = fmaxf(mx3, __uint_as_float(sr[cidx + 3]));
+        }
       }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       const float m_new = mx * c;                           // c > 0: the maximum commutes with the scale
       // Move the reference only when some row of the warp needs it (tcgen05.ld / st are warp-collective).
       const bool grow = (j == 0) ? true : (m_new > m_ref + kRescaleThreshold);
@@ -288,29 +294,32 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
       // Pass 2: P = exp2(c * s - m_ref), rounded, into shared memory: K-major with 128-byte swizzle, 16-byte chunk q
       // of row r lives at chunk (q ^ (r & 7)).
-      float psum = 0.f;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t sr[32];
-        tmem_ld32(tmem_s + half * 32, sr);
+      float psum0 = 0.f, psum1 = 0.f;
+      {
+        uint32_t sr[64];
+        tmem_ld32(tmem_s, sr);
+        tmem_ld32(tmem_s + 32, sr + 32);
         tmem_ld_wait();
         if (limit < 64) {
 #pragma unroll
-          for (int cidx = 0; cidx < 32; ++cidx)
-            if (half * 32 + cidx >= limit) sr[cidx] = 0xff800000u;
+          for (int cidx = 0; cidx < 64; ++cidx)
+            if (cidx >= limit) sr[cidx] = 0xff800000u;
         }
 #pragma unroll
-        for (int cidx = 0; cidx < 32; cidx += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[cidx]), c, -m_ref));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[cidx + 1]), c, -m_ref));
-          psum += p0 + p1;
-          sr[cidx >> 1] = pack2<T>(p0, p1);   // in place: entry cidx / 2 has been consumed
-        }
+        for (int q = 0; q < 8; ++q) {
+          uint32_t w[4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
-          *reinterpret_cast<uint4*>(prow + (((half * 4 + q) ^ (row & 7)) << 4)) = make_uint4(sr[4 * q], sr[4 * q + 1], sr[4 * q + 2], sr[4 * q + 3]);
+          for (int e = 0; e < 4; ++e) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[8 * q + 2 * e]), c, -m_ref));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[8 * q + 2 * e + 1]), c, -m_ref));
+            psum0 += p0;
+            psum1 += p1;
+            w[e] = pack2<T>(p0, p1);
+          }
+          *reinterpret_cast<uint4*>(prow + ((q ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
       }
-      l_run += psum;
+      l_run += psum0 + psum1;
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
