@@ -100,66 +100,6 @@ __device__ __forceinline__ void tile_coords(const TcArgs& g, int64_t t, int* b, 
   *n_t = in_group / gm;
 }
 
-template <typename OutT> __device__ __forceinline__ void store_chunk(const TcArgs& g, OutT* crow, int64_t col0, const float* v);
-
-template <>
-__device__ __forceinline__ void store_chunk<float>(const TcArgs& g, float* crow, int64_t col0, const float* v) {
-  if (g.vec_store) {
-#pragma unroll
-    for (int j = 0; j < 32; j += 4)
-      if (col0 + j < g.N) *reinterpret_cast<float4*>(crow + col0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (col0 + j < g.N) crow[col0 + j] = v[j];
-  }
-}
-template <>
-__device__ __forceinline__ void store_chunk<__nv_bfloat16>(const TcArgs& g, __nv_bfloat16* crow, int64_t col0, const float* v) {
-  if (g.vec_store) {
-#pragma unroll
-    for (int j = 0; j < 32; j += 8)
-      if (col0 + j < g.N) {
-        uint4 q;
-        __nv_bfloat162 h;
-        h = __floats2bfloat162_rn(v[j], v[j + 1]); q.x = *reinterpret_cast<uint32_t*>(&h);
-        h = __floats2bfloat162_rn(v[j + 2], v[j + 3]); q.y = *reinterpret_cast<uint32_t*>(&h);
-        h = __floats2bfloat162_rn(v[j + 4], v[j + 5]); q.z = *reinterpret_cast<uint32_t*>(&h);
-        h = __floats2bfloat162_rn(v[j + 6], v[j + 7]); q.w = *reinterpret_cast<uint32_t*>(&h);
-        *reinterpret_cast<uint4*>(crow + col0 + j) = q;
-      }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (col0 + j < g.N) crow[col0 + j] = __float2bfloat16_rn(v[j]);
-  }
-}
-template <>
-__device__ __forceinline__ void store_chunk<__half>(const TcArgs& g, __half* crow, int64_t col0, const float* v) {
-  if (g.vec_store) {
-#pragma unroll
-    for (int j = 0; j < 32; j += 8)
-      if (col0 + j < g.N) {
-        uint4 q;
-        __half2 h;
-        h = __floats2half2_rn(v[j], v[j + 1]); q.x = *reinterpret_cast<uint32_t*>(&h);
-        h = __floats2half2_rn(v[j + 2], v[j + 3]); q.y = *reinterpret_cast<uint32_t*>(&h);
-        h = __floats2half2_rn(v[j + 4], v[j + 5]); q.z = *reinterpret_cast<uint32_t*>(&h);
-        h = __floats2half2_rn(v[j + 6], v[j + 7]); q.w = *reinterpret_cast<uint32_t*>(&h);
-        *reinterpret_cast<uint4*>(crow + col0 + j) = q;
-      }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (col0 + j < g.N) crow[col0 + j] = __float2half_rn(v[j]);
-  }
-}
-
-template <typename OutT> __device__ __forceinline__ void store_one(OutT* p, float v);
-template <> __device__ __forceinline__ void store_one<float>(float* p, float v) { *p = v; }
-template <> __device__ __forceinline__ void store_one<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
-template <> __device__ __forceinline__ void store_one<__half>(__half* p, float v) { *p = __float2half_rn(v); }
-
 template <typename OutT> __device__ __forceinline__ float load_bias(const void* bias, int64_t col) {
   return 0.f;
 }
@@ -171,46 +111,122 @@ template <> __device__ __forceinline__ float load_bias<__half>(const void* bias,
   return __half2float(reinterpret_cast<const __half*>(bias)[col]);
 }
 
+template <typename OutT> struct OutTraits;
+template <> struct OutTraits<float> { static constexpr int kColsPerWord = 1; static constexpr bool kFast = false; };
+template <> struct OutTraits<__nv_bfloat16> { static constexpr int kColsPerWord = 2; static constexpr bool kFast = true; };
+template <> struct OutTraits<__half> { static constexpr int kColsPerWord = 2; static constexpr bool kFast = true; };
+
+template <typename OutT> __device__ __forceinline__ uint32_t pack_word(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack_word<float>(float a, float) { return __float_as_uint(a); }
+template <> __device__ __forceinline__ uint32_t pack_word<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack_word<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// 32 consecutive bias values starting at col (col is a multiple of 32 and col + 32 <= N is NOT assumed: tail guarded).
+template <typename OutT>
+__device__ __forceinline__ void add_bias32(const TcArgs& g, int64_t col, float* v) {
+  if (g.vec_store && col + 32 <= g.N) {
+    // 16-byte loads; every lane reads the same addresses (one broadcast transaction each)
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const OutT*>(g.bias) + col);
+    constexpr int kPerVec = 16 / (int)sizeof(OutT);
+#pragma unroll
+    for (int q = 0; q < 32 / kPerVec; ++q) {
+      const uint4 w = __ldg(src + q);
+      const OutT* e = reinterpret_cast<const OutT*>(&w);
+#pragma unroll
+      for (int i = 0; i < kPerVec; ++i) v[q * kPerVec + i] += (float)e[i];
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col + j < g.N) v[j] += load_bias<OutT>(g.bias, col + j);
+  }
+}
+
 // One epilogue warp drains its 32 TMEM lanes of a finished 128 x 256 accumulator: bias, activation, rounding, stores.
-// row0 is the first row of C held by lane 0 of this CTA's accumulator; `stage` is the warp's 32 x 33 fp32 scratch.
+// row0 is the first row of C held by lane 0 of this CTA's accumulator; `stage` is the warp's 32 x 33 word scratch.
+// A thread holds one ROW of the accumulator, so storing from registers would scatter every store instruction over 32
+// rows (32 cache lines).  Instead the rounded values go through the scratch, 32 words per row at a time (32 fp32 or 64
+// 16-bit columns), and are written back transposed: a store instruction covers 4 rows x 128 contiguous bytes.  With
+// short K (a GELU layer at K = 768) the epilogue, not the main loop, was the kernel's critical path before this.
 template <typename OutT>
 __device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem_acc, int64_t row0, int64_t n0, int b, int quarter, int lane,
-                                                  float* stage) {
-  const int64_t row = row0 + quarter * 32 + lane;
-  OutT* crow = reinterpret_cast<OutT*>(g.c) + ((int64_t)b * g.M + row) * g.ldc;
+                                                  float* stage_f) {
+  using Tr = OutTraits<OutT>;
+  constexpr int CPW = Tr::kColsPerWord;
+  constexpr int STEP_COLS = 32 * CPW;          // columns per step: 32 words per row
+  uint32_t* stage = reinterpret_cast<uint32_t*>(stage_f);
   const uint32_t taddr = tmem_acc + ((uint32_t)(quarter * 32) << 16);
+  const int64_t row_base = row0 + quarter * 32;
+  OutT* cbase = reinterpret_cast<OutT*>(g.c) + ((int64_t)b * g.M + row_base) * g.ldc;
 #pragma unroll 1
-  for (int chunk = 0; chunk < BN / 32; ++chunk) {
-    const int64_t col0 = n0 + chunk * 32;
+  for (int step = 0; step < BN / STEP_COLS; ++step) {
+    const int64_t col0 = n0 + step * STEP_COLS;
     if (col0 >= g.N) break;  // uniform across the warp
-    uint32_t r[32];
-    tmem_ld32(taddr + chunk * 32, r);
-    tmem_ld_wait();
-    float v[32];
+    uint32_t words[32];
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-    if (g.bias) {
+    for (int part = 0; part < CPW; ++part) {
+      uint32_t r[32];
+      tmem_ld32(taddr + step * STEP_COLS + part * 32, r);
+      tmem_ld_wait();
+      float v[32];
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (col0 + j < g.N) v[j] += load_bias<OutT>(g.bias, col0 + j);
-    }
-    if (g.activation != B200_ACT_NONE) {
+      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+      if (g.bias) add_bias32<OutT>(g, col0 + part * 32, v);
+      apply_activation_n<32, Tr::kFast>(g.activation, v);
+      if (CPW == 1) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = apply_activation(g.activation, v[j]);
+        for (int j = 0; j < 32; ++j) words[j] = pack_word<OutT>(v[j], 0.f);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) words[part * 16 + j] = pack_word<OutT>(v[2 * j], v[2 * j + 1]);
+      }
     }
     if (g.vec_store) {
-      if (row < g.M) store_chunk<OutT>(g, crow, col0, v);
-    } else {
-      // Rows of C do not start 16-byte aligned (N is not a multiple of the vector width): transpose the
-      // 32 x 32 block through shared memory so that a warp writes 32 CONSECUTIVE columns of one row per store.
+      // this thread's row -> scratch (rows padded to 33 words: conflict-free both ways)
 #pragma unroll
-      for (int j = 0; j < 32; ++j) stage[lane * 33 + j] = v[j];
+      for (int j = 0; j < 32; ++j) stage[lane * 33 + j] = words[j];
       __syncwarp();
-      const int64_t row_base = row0 + quarter * 32;
-      const int64_t col = col0 + lane;
-      OutT* cb = reinterpret_cast<OutT*>(g.c) + ((int64_t)b * g.M + row_base) * g.ldc + col;
-      for (int rr = 0; rr < 32; ++rr)
-        if (row_base + rr < g.M && col < g.N) store_one<OutT>(cb + (int64_t)rr * g.ldc, stage[rr * 33 + lane]);
+      // transposed write-out: lane handles 4 words (16 bytes) of row (pass * 4 + lane / 8)
+      const int wg = (lane & 7) * 4;
+      const int64_t col = col0 + (int64_t)wg * CPW;
+#pragma unroll
+      for (int pass = 0; pass < 8; ++pass) {
+        const int rr = pass * 4 + (lane >> 3);
+        const uint32_t* src = stage + rr * 33 + wg;
+        const uint4 q = make_uint4(src[0], src[1], src[2], src[3]);
+        if (row_base + rr < g.M && col < g.N) *reinterpret_cast<uint4*>(cbase + (int64_t)rr * g.ldc + col) = q;
+      }
+      __syncwarp();
+    } else {
+      // Rows of C do not start 16-byte aligned (N is not a multiple of the vector width): a warp writes the CONSECUTIVE
+      // columns of one row per store instruction, element by element.
+#pragma unroll
+      for (int j = 0; j < 32; ++j) stage[lane * 33 + j] = words[j];
+      __syncwarp();
+      for (int rr = 0; rr < 32; ++rr) {
+        if (row_base + rr >= g.M) break;
+        OutT* crow = cbase + (int64_t)rr * g.ldc;
+        if (CPW == 1) {
+          const int64_t col = col0 + lane;
+          if (col < g.N) crow[col] = *reinterpret_cast<const OutT*>(&stage[rr * 33 + lane]);
+        } else {
+          // 64 columns: lane writes columns lane and lane + 32 (each a half of a packed word)
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const int cidx = hh * 32 + lane;
+            const int64_t col = col0 + cidx;
+            const uint32_t w = stage[rr * 33 + (cidx >> 1)];
+            const uint16_t bits = (cidx & 1) ? (uint16_t)(w >> 16) : (uint16_t)(w & 0xffffu);
+            if (col < g.N) reinterpret_cast<uint16_t*>(crow)[col] = bits;
+          }
+        }
+      }
       __syncwarp();
     }
   }
