@@ -150,6 +150,9 @@ struct GemmParams {
   int dtype = B200_BFLOAT16;
   const void* bias = nullptr;  // [N] of dtype, or null
   int activation = B200_ACT_NONE;
+  // [batch, M, N] of dtype or null: C = round(act(A B + bias)) + residual, rounded again (the op-by-op result of a
+  // DotGeneral followed by Add, without the extra pass over C)
+  const void* residual = nullptr;
   // batch strides in elements; 0 on an operand broadcasts it over the batch
   int64_t a_batch_stride = -1, b_batch_stride = -1;  // -1 = dense (m*k, k*n)
 };

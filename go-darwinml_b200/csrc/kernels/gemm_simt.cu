@@ -37,6 +37,7 @@ struct SimtArgs {
   const void* b;
   void* c;
   const void* bias;
+  const void* residual;
   int64_t m, n, k;
   int64_t a_sm, a_sk, a_sb;  // element strides of A along m, k, batch
   int64_t b_sk, b_sn, b_sb;
@@ -105,6 +106,12 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtArgs g) {
       } else {
         if (g.bias) v += g_load<T, A>(reinterpret_cast<const T*>(g.bias) + gn);
       }
+      if (g.residual) {
+        // the sum is rounded to the storage type first, as a separate DotGeneral would have left it
+        T t;
+        g_store<A, T>(&t, v);
+        v = g_load<T, A>(&t) + g_load<T, A>(reinterpret_cast<const T*>(g.residual) + (c - reinterpret_cast<T*>(g.c)) + gm * g.n + gn);
+      }
       g_store<A, T>(c + gm * g.n + gn, v);
     }
   }
@@ -115,7 +122,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtArgs g) {
 Status gemm_simt(Device* dev, const GemmParams& p) {
   if (p.batch * p.m * p.n == 0) return Status::OK();
   SimtArgs g;
-  g.a = p.a; g.b = p.b; g.c = p.c; g.bias = p.bias;
+  g.a = p.a; g.b = p.b; g.c = p.c; g.bias = p.bias; g.residual = p.residual;
   g.m = p.m; g.n = p.n; g.k = p.k;
   g.a_sm = p.a_k_major ? p.k : 1;
   g.a_sk = p.a_k_major ? 1 : p.m;

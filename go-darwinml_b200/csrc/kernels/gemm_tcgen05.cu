@@ -17,7 +17,7 @@
 //   warp 1     issuer: one lane issues tcgen05.mma (M=128, N=256, K=16 per instruction)
 //              from shared-memory descriptors into a TMEM accumulator; tcgen05.commit
 //              releases ring stages ("empty") and publishes finished accumulators;
-//   warps 2-5  epilogue: tcgen05.ld the accumulator (each warp its own 32 TMEM lanes),
+//   warps 2-9  epilogue: tcgen05.ld the accumulator (each warp 32 TMEM lanes x 128 columns),
 //              add bias, apply the activation, round, store 16-byte vectors.
 // TMEM holds two 256-column accumulators, so the epilogue of tile i overlaps the
 // main loop of tile i+1.  Tensor-core bound: flops = 2 * batch * M * N * K.
@@ -56,9 +56,11 @@ constexpr int STAGES = 4;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
 constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr int EPI_STAGE_FLOATS = 32 * 33;     // per epilogue warp: a 32 x 32 fp32 block, rows padded to 33 words
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + 4 * EPI_STAGE_FLOATS * 4;
-constexpr int NUM_THREADS = 192;
+constexpr int EPI_PITCH = 36;                 // words per scratch row: 32 + 4, so 16-byte accesses are aligned and conflict-free
+constexpr int EPI_WARPS = 8;                  // two per TMEM lane quarter: one per half of the tile's columns
+constexpr int EPI_STAGE_FLOATS = 16 * EPI_PITCH;  // per epilogue warp: 16 rows x 32 words (a warp stages its rows in two rounds)
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + EPI_WARPS * EPI_STAGE_FLOATS * 4;
+constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;   // producer warp, issuer warp, epilogue warps
 constexpr int TMEM_COLS = 512;
 
 }  // namespace
@@ -68,6 +70,7 @@ namespace {
 struct TcArgs {
   void* c;
   const void* bias;
+  const void* residual;   // same shape as C, or null
   int64_t M, N, K, ldc;
   int batch;
   int a_kmajor, b_kmajor;
@@ -127,6 +130,22 @@ template <> __device__ __forceinline__ uint32_t pack_word<__half>(float a, float
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// word (one fp32 or two 16-bit values, already rounded) + residual word, rounded again
+template <typename OutT> __device__ __forceinline__ uint32_t add_residual_word(uint32_t w, uint32_t r);
+template <> __device__ __forceinline__ uint32_t add_residual_word<float>(uint32_t w, uint32_t r) {
+  return __float_as_uint(__uint_as_float(w) + __uint_as_float(r));
+}
+template <> __device__ __forceinline__ uint32_t add_residual_word<__nv_bfloat16>(uint32_t w, uint32_t r) {
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r));
+  return pack_word<__nv_bfloat16>(a.x + b.x, a.y + b.y);
+}
+template <> __device__ __forceinline__ uint32_t add_residual_word<__half>(uint32_t w, uint32_t r) {
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&r));
+  return pack_word<__half>(a.x + b.x, a.y + b.y);
+}
+
 // 32 consecutive bias values starting at col (col is a multiple of 32 and col + 32 <= N is NOT assumed: tail guarded).
 template <typename OutT>
 __device__ __forceinline__ void add_bias32(const TcArgs& g, int64_t col, float* v) {
@@ -148,15 +167,17 @@ __device__ __forceinline__ void add_bias32(const TcArgs& g, int64_t col, float* 
   }
 }
 
-// One epilogue warp drains its 32 TMEM lanes of a finished 128 x 256 accumulator: bias, activation, rounding, stores.
-// row0 is the first row of C held by lane 0 of this CTA's accumulator; `stage` is the warp's 32 x 33 word scratch.
+// One epilogue warp drains its 32 TMEM lanes x 128 columns (half `chalf`) of a finished 128 x 256 accumulator: bias,
+// activation, rounding, stores.  row0 is the first row of C held by lane 0 of this CTA's accumulator; `stage` is the
+// warp's 16 x 36 word scratch.
 // A thread holds one ROW of the accumulator, so storing from registers would scatter every store instruction over 32
 // rows (32 cache lines).  Instead the rounded values go through the scratch, 32 words per row at a time (32 fp32 or 64
-// 16-bit columns), and are written back transposed: a store instruction covers 4 rows x 128 contiguous bytes.  With
-// short K (a GELU layer at K = 768) the epilogue, not the main loop, was the kernel's critical path before this.
+// 16-bit columns), 16 rows per round, and are written back transposed: a store instruction covers 4 rows x 128
+// contiguous bytes.  With short K (a GELU layer at K = 768) the epilogue, not the main loop, is the kernel's critical
+// path, which is why eight warps share it.
 template <typename OutT>
-__device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem_acc, int64_t row0, int64_t n0, int b, int quarter, int lane,
-                                                  float* stage_f) {
+__device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem_acc, int64_t row0, int64_t n0, int b, int quarter, int chalf,
+                                                  int lane, float* stage_f) {
   using Tr = OutTraits<OutT>;
   constexpr int CPW = Tr::kColsPerWord;
   constexpr int STEP_COLS = 32 * CPW;          // columns per step: 32 words per row
@@ -164,10 +185,25 @@ __device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem
   const uint32_t taddr = tmem_acc + ((uint32_t)(quarter * 32) << 16);
   const int64_t row_base = row0 + quarter * 32;
   OutT* cbase = reinterpret_cast<OutT*>(g.c) + ((int64_t)b * g.M + row_base) * g.ldc;
+  const OutT* rbase = g.residual ? reinterpret_cast<const OutT*>(g.residual) + ((int64_t)b * g.M + row_base) * g.ldc : nullptr;
+  const int wg = (lane & 7) * 4;               // write-out: this lane's 4 words of a row
 #pragma unroll 1
-  for (int step = 0; step < BN / STEP_COLS; ++step) {
+  for (int step = chalf * (BN / 2 / STEP_COLS); step < (chalf + 1) * (BN / 2 / STEP_COLS); ++step) {
     const int64_t col0 = n0 + step * STEP_COLS;
     if (col0 >= g.N) break;  // uniform across the warp
+    const int64_t col = col0 + (int64_t)wg * CPW;
+    // The residual block of this step is fetched first, in the write-out layout, so that its latency hides under the
+    // TMEM reads and the activation arithmetic (loads issued after the stores below could not be hoisted: the
+    // compiler has to assume C and the residual alias).
+    uint4 rv[8];
+    if (rbase && g.vec_store) {
+#pragma unroll
+      for (int pass = 0; pass < 8; ++pass) {
+        const int rr = pass * 4 + (lane >> 3);
+        rv[pass] = (row_base + rr < g.M && col < g.N) ? __ldg(reinterpret_cast<const uint4*>(rbase + (int64_t)rr * g.ldc + col))
+                                                       : make_uint4(0, 0, 0, 0);
+      }
+    }
     uint32_t words[32];
 #pragma unroll
     for (int part = 0; part < CPW; ++part) {
@@ -187,43 +223,63 @@ __device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem
         for (int j = 0; j < 16; ++j) words[part * 16 + j] = pack_word<OutT>(v[2 * j], v[2 * j + 1]);
       }
     }
-    if (g.vec_store) {
-      // this thread's row -> scratch (rows padded to 33 words: conflict-free both ways)
 #pragma unroll
-      for (int j = 0; j < 32; ++j) stage[lane * 33 + j] = words[j];
-      __syncwarp();
-      // transposed write-out: lane handles 4 words (16 bytes) of row (pass * 4 + lane / 8)
-      const int wg = (lane & 7) * 4;
-      const int64_t col = col0 + (int64_t)wg * CPW;
+    for (int round = 0; round < 2; ++round) {
+      // rows [16 * round, +16) of the warp -> scratch, as 16-byte stores (row pitch 36 words: a quarter-warp covers all 32 banks)
+      if ((lane >> 4) == round) {
 #pragma unroll
-      for (int pass = 0; pass < 8; ++pass) {
-        const int rr = pass * 4 + (lane >> 3);
-        const uint32_t* src = stage + rr * 33 + wg;
-        const uint4 q = make_uint4(src[0], src[1], src[2], src[3]);
-        if (row_base + rr < g.M && col < g.N) *reinterpret_cast<uint4*>(cbase + (int64_t)rr * g.ldc + col) = q;
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<uint4*>(stage + (lane & 15) * EPI_PITCH + j) = make_uint4(words[j], words[j + 1], words[j + 2], words[j + 3]);
       }
       __syncwarp();
-    } else {
-      // Rows of C do not start 16-byte aligned (N is not a multiple of the vector width): a warp writes the CONSECUTIVE
-      // columns of one row per store instruction, element by element.
+      if (g.vec_store) {
+        // transposed write-out: lane handles 4 words (16 bytes) of row (16 * round + 4 * pass + lane / 8)
 #pragma unroll
-      for (int j = 0; j < 32; ++j) stage[lane * 33 + j] = words[j];
-      __syncwarp();
-      for (int rr = 0; rr < 32; ++rr) {
-        if (row_base + rr >= g.M) break;
-        OutT* crow = cbase + (int64_t)rr * g.ldc;
-        if (CPW == 1) {
-          const int64_t col = col0 + lane;
-          if (col < g.N) crow[col] = *reinterpret_cast<const OutT*>(&stage[rr * 33 + lane]);
-        } else {
-          // 64 columns: lane writes columns lane and lane + 32 (each a half of a packed word)
+        for (int pass = 0; pass < 4; ++pass) {
+          const int rl = pass * 4 + (lane >> 3);
+          const int rr = round * 16 + rl;
+          uint4 q = *reinterpret_cast<const uint4*>(stage + rl * EPI_PITCH + wg);
+          if (row_base + rr < g.M && col < g.N) {
+            if (rbase) {
+              const uint4 rq = rv[round * 4 + pass];
+              q.x = add_residual_word<OutT>(q.x, rq.x);
+              q.y = add_residual_word<OutT>(q.y, rq.y);
+              q.z = add_residual_word<OutT>(q.z, rq.z);
+              q.w = add_residual_word<OutT>(q.w, rq.w);
+            }
+            *reinterpret_cast<uint4*>(cbase + (int64_t)rr * g.ldc + col) = q;
+          }
+        }
+      } else {
+        // Rows of C do not start 16-byte aligned (N is not a multiple of the vector width): a warp writes the CONSECUTIVE
+        // columns of one row per store instruction, element by element.
+        for (int rl = 0; rl < 16; ++rl) {
+          const int rr = round * 16 + rl;
+          if (row_base + rr >= g.M) break;
+          OutT* crow = cbase + (int64_t)rr * g.ldc;
+          if (CPW == 1) {
+            const int64_t c1 = col0 + lane;
+            if (c1 < g.N) {
+              uint32_t w = stage[rl * EPI_PITCH + lane];
+              if (rbase) w = add_residual_word<OutT>(w, reinterpret_cast<const uint32_t*>(rbase + (int64_t)rr * g.ldc)[c1]);
+              reinterpret_cast<uint32_t*>(crow)[c1] = w;
+            }
+          } else {
+            // 64 columns: lane writes columns lane and lane + 32 (each a half of a packed word)
 #pragma unroll
-          for (int hh = 0; hh < 2; ++hh) {
-            const int cidx = hh * 32 + lane;
-            const int64_t col = col0 + cidx;
-            const uint32_t w = stage[rr * 33 + (cidx >> 1)];
-            const uint16_t bits = (cidx & 1) ? (uint16_t)(w >> 16) : (uint16_t)(w & 0xffffu);
-            if (col < g.N) reinterpret_cast<uint16_t*>(crow)[col] = bits;
+            for (int hh = 0; hh < 2; ++hh) {
+              const int cidx = hh * 32 + lane;
+              const int64_t c1 = col0 + cidx;
+              const uint32_t w = stage[rl * EPI_PITCH + (cidx >> 1)];
+              uint16_t bits = (cidx & 1) ? (uint16_t)(w >> 16) : (uint16_t)(w & 0xffffu);
+              if (c1 < g.N) {
+                if (rbase) {
+                  const uint32_t rbits = reinterpret_cast<const uint16_t*>(rbase + (int64_t)rr * g.ldc)[c1];
+                  bits = (uint16_t)(add_residual_word<OutT>(bits, rbits) & 0xffffu);   // low halves; the high halves are zero
+                }
+                reinterpret_cast<uint16_t*>(crow)[c1] = bits;
+              }
+            }
           }
         }
       }
@@ -251,7 +307,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], EPI_WARPS); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -357,7 +413,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const bool landed = mbar_wait(&acc_full[acc], acc_phase, err, 4);
       if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }  // the warp leaves together: tcgen05.ld is warp-collective
       tc_fence_after();
-      drain_accumulator<OutT>(g, tmem_base + acc * BN, (int64_t)m_t * BM, (int64_t)n_t * BN, b, quarter, lane, epi_stage + (warp - 2) * EPI_STAGE_FLOATS);
+      drain_accumulator<OutT>(g, tmem_base + acc * BN, (int64_t)m_t * BM, (int64_t)n_t * BN, b, quarter, (warp - 2) >> 2, lane,
+                              epi_stage + (warp - 2) * EPI_STAGE_FLOATS);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
@@ -389,14 +446,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 //   full[s]      leader only; counts the bytes of BOTH CTAs' tile loads (the peer's loads name it by cluster address)
 //   empty[s]     one per CTA; the leader commits to both once the MMAs that read stage s are done
 //   acc_full[a]  one per CTA; the leader commits to both when a tile's accumulator is complete
-//   acc_empty[a] leader only; the 4 + 4 epilogue warps of both CTAs arrive when they have drained it
+//   acc_empty[a] leader only; the 8 + 8 epilogue warps of both CTAs arrive when they have drained it
 // The pair joins at a cluster barrier before either releases TMEM or exits, so no CTA's shared memory or barriers
 // are touched after it has gone.
 constexpr int P_STAGES = 6;
 constexpr int P_BN_HALF = BN / 2;                         // B columns held per CTA
 constexpr int P_B_STAGE_BYTES = P_BN_HALF * BK * 2;       // 16 KiB
 constexpr int P_STAGE_BYTES = A_STAGE_BYTES + P_B_STAGE_BYTES;  // 32 KiB
-constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256 + 4 * EPI_STAGE_FLOATS * 4;
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256 + EPI_WARPS * EPI_STAGE_FLOATS * 4;
 
 __device__ __forceinline__ void pair_tile_coords(const TcArgs& g, int64_t t, int* b, int* m_t, int* n_t) {
   // same grouping as tile_coords over tiles of 256 rows: g.tiles_m counts 256-row tiles here
@@ -424,7 +481,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 2 * EPI_WARPS); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -558,8 +615,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
       const bool landed = mbar_wait_cluster(&acc_full[acc], acc_phase, err, 4);
       if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }
       tc_fence_after();
-      drain_accumulator<OutT>(g, tmem_base + acc * BN, (int64_t)m_t * 2 * BM + (int64_t)rank * BM, (int64_t)n_t * BN, b, quarter, lane,
-                              epi_stage + (warp - 2) * EPI_STAGE_FLOATS);
+      drain_accumulator<OutT>(g, tmem_base + acc * BN, (int64_t)m_t * 2 * BM + (int64_t)rank * BM, (int64_t)n_t * BN, b, quarter,
+                              (warp - 2) >> 2, lane, epi_stage + (warp - 2) * EPI_STAGE_FLOATS);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
@@ -652,12 +709,13 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
   auto cleanup = [&]() { dev->Free(tmp_a); dev->Free(tmp_b); };
 
   // CTA pairs (256-row tiles) whenever there is more than one 128-row tile of M to share B with
-  static const bool pair_allowed = []() { const char* v = getenv("B200MLX_GEMM_PAIR"); return !(v && v[0] == '0'); }();
+  static const int pair_mode = []() { const char* v = getenv("B200MLX_GEMM_PAIR"); return v ? atoi(v) : 1; }();   // 0 never, 1 by shape, 2 always
+  const bool pair_allowed = pair_mode != 0;
   // Pairs pay off once a tile's main loop is long enough to hide the cross-CTA hand-offs (measured: K = 512 is 8 % slower on
   // pairs, K >= 4096 is 5 - 10 % faster) and there are enough tiles to fill the GPU either way.
   const int64_t k_iters = (p.k + BK - 1) / BK * (is32 ? 6 : 1);
   const int64_t pair_tiles = ((p.m + 2 * BM - 1) / (2 * BM)) * ((p.n + BN - 1) / BN) * p.batch;
-  const bool use_pair = pair_allowed && p.m > BM && k_iters >= 16 && pair_tiles >= 32;
+  const bool use_pair = pair_allowed && p.m > BM && (pair_mode == 2 || (k_iters >= 16 && pair_tiles >= 32));
 
   CUtensorMap tm_a, tm_b;
   Status s;
@@ -672,7 +730,7 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
   if (!s.ok()) { cleanup(); return s; }
 
   TcArgs g;
-  g.c = p.c; g.bias = p.bias;
+  g.c = p.c; g.bias = p.bias; g.residual = p.residual;
   g.M = p.m; g.N = p.n; g.K = p.k; g.ldc = p.n;
   g.batch = (int)p.batch;
   g.a_kmajor = p.a_k_major ? 1 : 0; g.b_kmajor = p.b_k_major ? 1 : 0;
@@ -686,7 +744,7 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
   g.k_blocks = (int)((p.k + BK - 1) / BK);
   g.segs = is32 ? 6 : 1;
   const int out_vec = is32 ? 4 : 8;
-  g.vec_store = (p.n % out_vec == 0 && aligned16(p.c)) ? 1 : 0;
+  g.vec_store = (p.n % out_vec == 0 && aligned16(p.c) && aligned16(p.residual)) ? 1 : 0;
   g.err_flag = dev->kernel_error_flag();
 
   cudaError_t e = cudaSuccess;

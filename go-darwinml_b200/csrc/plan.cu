@@ -880,10 +880,14 @@ class Planner {
   Status EmitDotGeneral(Node* x) {
     Node* a = x->in[0];
     Node* b = x->in[1];
-    Node* bias = x->in.size() > 2 ? x->in[2] : nullptr;
+    // inputs: lhs, rhs, [bias], [residual]; fa = {activation, has_residual (set by the compile-time rewrite)}
+    const bool has_residual = x->fa.size() > 1 && x->fa[1] != 0;
+    Node* residual = has_residual ? x->in.back() : nullptr;
+    Node* bias = (int)x->in.size() - (has_residual ? 1 : 0) > 2 ? x->in[2] : nullptr;
     B200_TRY(EnsureMaterialized(a));
     B200_TRY(EnsureMaterialized(b));
     if (bias) B200_TRY(EnsureMaterialized(bias));
+    if (residual) B200_TRY(EnsureMaterialized(residual));
     const int nc = (int)x->ia[0], nb = (int)x->ia[1];
     std::vector<int64_t> lc(x->ia.begin() + 2, x->ia.begin() + 2 + nc);
     std::vector<int64_t> lb(x->ia.begin() + 2 + nc, x->ia.begin() + 2 + nc + nb);
@@ -935,18 +939,22 @@ class Planner {
     gp.dtype = x->dtype;
     gp.activation = (int)x->fa[0];
     const int bias_slot = bias ? SlotOf(bias) : -1;
+    const int res_slot = residual ? SlotOf(residual) : -1;
     Step st;
-    st.desc = strfmt("gemm[B=%lld M=%lld N=%lld K=%lld %s a:%s b:%s%s act=%d]", (long long)B, (long long)M, (long long)N, (long long)K,
-                     dtype_name(x->dtype), gp.a_k_major ? "MK" : "KM", gp.b_k_major ? "NK" : "KN", bias ? " bias" : "", gp.activation);
+    st.desc = strfmt("gemm[B=%lld M=%lld N=%lld K=%lld %s a:%s b:%s%s%s act=%d]", (long long)B, (long long)M, (long long)N, (long long)K,
+                     dtype_name(x->dtype), gp.a_k_major ? "MK" : "KM", gp.b_k_major ? "NK" : "KN", bias ? " bias" : "",
+                     residual ? " +residual" : "", gp.activation);
     st.reads = {a_slot, b_slot};
     if (bias) st.reads.push_back(bias_slot);
+    if (residual) st.reads.push_back(res_slot);
     st.writes = {out_slot};
-    st.run = [gp, a_slot, b_slot, bias_slot, out_slot](Device* dev, void* const* p) -> Status {
+    st.run = [gp, a_slot, b_slot, bias_slot, res_slot, out_slot](Device* dev, void* const* p) -> Status {
       k::GemmParams q = gp;
       q.a = p[a_slot];
       q.b = p[b_slot];
       q.c = p[out_slot];
       q.bias = bias_slot >= 0 ? p[bias_slot] : nullptr;
+      q.residual = res_slot >= 0 ? p[res_slot] : nullptr;
       return k::gemm(dev, q);
     };
     ex_->steps.push_back(std::move(st));
@@ -1457,6 +1465,7 @@ B200Exec b200_compile(B200Context ctx, const B200Value* feeds, int num_feeds, co
     t.push_back(n);
   }
   RewriteRmsNorm(c->graph, t);
+  RewriteGemmResidual(c->graph, t);
   std::unique_ptr<Exec> ex(new Exec());
   ex->dev = c->dev;
   Planner planner(c, ex.get());

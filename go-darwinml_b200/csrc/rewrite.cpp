@@ -227,6 +227,64 @@ Node* MatchGamma(Node* G, const Node* x) {
 
 }  // namespace
 
+namespace {
+// nodes reachable from the targets, and their users among those
+void LiveAndUsers(Graph& graph, const std::vector<Node*>& targets, std::unordered_set<Node*>* live,
+                  std::unordered_map<Node*, std::vector<Node*>>* users) {
+  std::vector<Node*> stack(targets.begin(), targets.end());
+  while (!stack.empty()) {
+    Node* n = stack.back();
+    stack.pop_back();
+    if (!live->insert(n).second) continue;
+    for (Node* i : n->in) stack.push_back(i);
+  }
+  for (auto& up : graph.nodes)
+    if (live->count(up.get()))
+      for (Node* i : up->in) (*users)[i].push_back(up.get());
+}
+}  // namespace
+
+// A transformer block ends its attention and MLP halves with "x + Dense(...)".  Run op by op the sum costs a read of
+// both operands and a write of the result (three passes over the activations) right after the GEMM wrote one of them;
+// in the GEMM's epilogue it costs one extra read.  The product is still rounded to the storage type before the
+// addition, so the fused value is bit-identical to the two-op one.
+int RewriteGemmResidual(Graph& graph, const std::vector<Node*>& targets) {
+  std::unordered_set<Node*> live;
+  std::unordered_map<Node*, std::vector<Node*>> users;
+  LiveAndUsers(graph, targets, &live, &users);
+  std::unordered_set<Node*> is_target(targets.begin(), targets.end());
+  int rewritten = 0;
+  for (auto& up : graph.nodes) {
+    Node* m = up.get();
+    if (!live.count(m) || m->op != Op::Add) continue;
+    if (!(m->dtype == B200_FLOAT32 || m->dtype == B200_BFLOAT16 || m->dtype == B200_FLOAT16)) continue;
+    for (int side = 0; side < 2; ++side) {
+      Node* x = m->in[side];
+      Node* r = m->in[1 - side];
+      if (x == r || r->dims != m->dims || r->dtype != m->dtype) continue;
+      // the product, seen through views that keep the element order, each with this chain as its only user
+      bool chain_ok = true;
+      Node* d = x;
+      while (d->op == Op::Reshape || d->op == Op::Identity) {
+        if (is_target.count(d) || users[d].size() != 1) { chain_ok = false; break; }
+        d = d->in[0];
+      }
+      if (!chain_ok || d->op != Op::DotGeneral || is_target.count(d) || users[d].size() != 1) continue;
+      if (d->dtype != m->dtype || d->num_elements() != m->num_elements()) continue;
+      if (d->fa.size() > 1 && d->fa[1] != 0) continue;   // already carries a residual
+      // r must exist independently of d (it cannot use d: d has a single user, the chain)
+      m->op = Op::DotGeneral;
+      m->in = d->in;
+      m->in.push_back(r);
+      m->ia = d->ia;
+      m->fa = {d->fa.empty() ? 0.0 : d->fa[0], 1.0};
+      ++rewritten;
+      break;
+    }
+  }
+  return rewritten;
+}
+
 int RewriteRmsNorm(Graph& graph, const std::vector<Node*>& targets) {
   // nodes reachable from the targets, and their users
   std::unordered_set<Node*> live;

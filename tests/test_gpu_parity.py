@@ -685,3 +685,31 @@ def test_rmsnorm_rewrite_keeps_shared_intermediates(b200, backend):
     for a, w in zip(got, want):
         ok, viol = compare(a, w, 1e-5, 0.0)
         assert ok, viol
+
+
+# ---- Add(DotGeneral, r) runs in the GEMM epilogue and equals the two-op result bit for bit -----------------------
+@pytest.mark.parametrize("dtype,shape", [(BF16, (2, 300, 256, 192)), (np.float32, (1, 130, 96, 64)), (BF16, (1, 9, 7, 5)),
+                                         (BF16, (2, 520, 1030, 1024))], ids=["bf16", "f32", "bf16_tiny_simt", "bf16_pairs_ragged_n"])
+def test_dense_plus_residual_is_one_gemm(b200, backend, dtype, shape):
+    B, M, N, K = shape
+    rng = np.random.default_rng(95)
+    x, w = rng_array(rng, (B, M, K), dtype), rng_array(rng, (K, N), dtype, 0.1)
+    bias, r = rng_array(rng, (N,), dtype), rng_array(rng, (B * M, N), dtype)
+
+    def fused(f, xx, ww, bb, rr):
+        y = f.FusedDense(xx, ww, bb, 1)                   # GELU in the epilogue too
+        return f.Add(rr, f.Reshape(y, B * M, N))           # seen through the reshape; residual on the left
+
+    def two_ops(f, xx, ww, bb, rr):
+        y = f.FusedDense(xx, ww, bb, 1)
+        return [f.Add(rr, f.Reshape(y, B * M, N)), y]      # y has a second user: the sum stays a separate kernel
+
+    (got,), plan = run_backend(b200, backend, fused, [x, w, bias, r], describe=True)
+    assert "+residual" in plan and len(plan.strip().splitlines()) == 1, plan
+    (want, _), plan2 = run_backend(b200, backend, two_ops, [x, w, bias, r], describe=True)
+    assert "+residual" not in plan2, plan2
+    np.testing.assert_array_equal(got.view(np.uint16 if dtype is BF16 else np.uint32), want.view(np.uint16 if dtype is BF16 else np.uint32))
+    rtol, ascale = _dot_tol(dtype)
+    (oracle,) = run_oracle(fused, [x, w, bias, r])
+    ok, viol = compare(got, oracle, rtol, ascale)
+    assert ok, viol
