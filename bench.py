@@ -144,6 +144,7 @@ def cpu_sample_shapes(frac_rows: int):
 
 def run_cpu_baseline(logits, x, gamma, beta, frac_rows=4, passes=3):
     from oracle import cport
+    cport.use_all_cores()   # torchrun exports OMP_NUM_THREADS=1
     sm_shape, n_shape = cpu_sample_shapes(frac_rows)
     lg = logits[:sm_shape[0]]
     xs = x[:n_shape[0]]
@@ -166,6 +167,7 @@ def run_reference_arm(args, rank, world):
     if rank != 0:
         return
     from oracle import cport
+    cport.use_all_cores()   # torchrun exports OMP_NUM_THREADS=1
     frac = 4
     sm_shape, n_shape = cpu_sample_shapes(frac)
     logits, x, gamma, beta = make_inputs(0, sm_shape, n_shape)

@@ -25,6 +25,8 @@ def lib():
         L.oracle_gemm_f32.argtypes = [p, p, p, i64, i64, i64, i64, i, i]
         L.oracle_gemm_bf16.argtypes = [p, p, p, i64, i64, i64, i64, i, i]
         L.oracle_num_threads.restype = i
+        L.oracle_set_num_threads.argtypes = [i]
+        L.oracle_set_num_threads.restype = None
         _lib = L
     return _lib
 
@@ -65,3 +67,11 @@ def gemm(a: np.ndarray, b: np.ndarray, a_k_major: bool, b_k_major: bool) -> np.n
 
 def num_threads() -> int:
     return lib().oracle_num_threads()
+
+
+def use_all_cores() -> int:
+    """One OpenMP thread per core this process may run on, whatever OMP_NUM_THREADS says; returns the count."""
+    import os
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().oracle_set_num_threads(n)
+    return num_threads()

@@ -172,6 +172,15 @@ void oracle_gemm_bf16(const uint16_t* a, const uint16_t* b, uint16_t* c, int64_t
   }
 }
 
+/* Sets the OpenMP team size for the calls that follow (launchers such as torchrun export OMP_NUM_THREADS=1). */
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int oracle_num_threads(void) {
   int n = 1;
 #ifdef _OPENMP
