@@ -206,8 +206,8 @@ struct Graph {
 // Compile-time rewrite: turns RMSNorm spelled in primitives (x * rsqrt(mean(x^2, last) + eps) [* gamma]) into one
 // RmsNorm node.  Returns the number of patterns rewritten.  Defined in rewrite.cpp.
 int RewriteRmsNorm(Graph& graph, const std::vector<Node*>& targets);
-// Compile-time rewrite: Add(DotGeneral(...), r) where the product has no other user becomes one DotGeneral node that adds
-// r in its epilogue (rounding the product first, so the value is the op-by-op one).  Returns the number of rewrites.
+// Compile-time rewrite: Add(DotGeneral(...), r) or Mul(DotGeneral(...), r) where the product has no other user becomes one
+// DotGeneral node that combines with r in its epilogue (rounding the product first, so the value is the op-by-op one).  Returns the number of rewrites.
 int RewriteGemmResidual(Graph& graph, const std::vector<Node*>& targets);
 
 // What a B200Context handle points to: one graph under construction and its device.

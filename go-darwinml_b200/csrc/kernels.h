@@ -153,6 +153,7 @@ struct GemmParams {
   // [batch, M, N] of dtype or null: C = round(act(A B + bias)) + residual, rounded again (the op-by-op result of a
   // DotGeneral followed by Add, without the extra pass over C)
   const void* residual = nullptr;
+  int residual_op = 0;   // 0: + residual, 1: * residual (a gated MLP's act(x W1) * (x W2))
   // batch strides in elements; 0 on an operand broadcasts it over the batch
   int64_t a_batch_stride = -1, b_batch_stride = -1;  // -1 = dense (m*k, k*n)
 };

@@ -38,6 +38,7 @@ struct SimtArgs {
   void* c;
   const void* bias;
   const void* residual;
+  int residual_op;
   int64_t m, n, k;
   int64_t a_sm, a_sk, a_sb;  // element strides of A along m, k, batch
   int64_t b_sk, b_sn, b_sb;
@@ -110,7 +111,8 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtArgs g) {
         // the sum is rounded to the storage type first, as a separate DotGeneral would have left it
         T t;
         g_store<A, T>(&t, v);
-        v = g_load<T, A>(&t) + g_load<T, A>(reinterpret_cast<const T*>(g.residual) + (c - reinterpret_cast<T*>(g.c)) + gm * g.n + gn);
+        const A rv = g_load<T, A>(reinterpret_cast<const T*>(g.residual) + (c - reinterpret_cast<T*>(g.c)) + gm * g.n + gn);
+        v = g.residual_op ? g_load<T, A>(&t) * rv : g_load<T, A>(&t) + rv;
       }
       g_store<A, T>(c + gm * g.n + gn, v);
     }
@@ -122,7 +124,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtArgs g) {
 Status gemm_simt(Device* dev, const GemmParams& p) {
   if (p.batch * p.m * p.n == 0) return Status::OK();
   SimtArgs g;
-  g.a = p.a; g.b = p.b; g.c = p.c; g.bias = p.bias; g.residual = p.residual;
+  g.a = p.a; g.b = p.b; g.c = p.c; g.bias = p.bias; g.residual = p.residual; g.residual_op = p.residual_op;
   g.m = p.m; g.n = p.n; g.k = p.k;
   g.a_sm = p.a_k_major ? p.k : 1;
   g.a_sk = p.a_k_major ? 1 : p.m;

@@ -71,6 +71,7 @@ struct TcArgs {
   void* c;
   const void* bias;
   const void* residual;   // same shape as C, or null
+  int residual_mul;       // combine by * instead of +
   int64_t M, N, K, ldc;
   int batch;
   int a_kmajor, b_kmajor;
@@ -130,20 +131,20 @@ template <> __device__ __forceinline__ uint32_t pack_word<__half>(float a, float
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// word (one fp32 or two 16-bit values, already rounded) + residual word, rounded again
-template <typename OutT> __device__ __forceinline__ uint32_t add_residual_word(uint32_t w, uint32_t r);
-template <> __device__ __forceinline__ uint32_t add_residual_word<float>(uint32_t w, uint32_t r) {
-  return __float_as_uint(__uint_as_float(w) + __uint_as_float(r));
+// word (one fp32 or two 16-bit values, already rounded) combined with the residual word (+ or *), rounded again
+template <typename OutT> __device__ __forceinline__ uint32_t add_residual_word(uint32_t w, uint32_t r, int mul);
+template <> __device__ __forceinline__ uint32_t add_residual_word<float>(uint32_t w, uint32_t r, int mul) {
+  return __float_as_uint(mul ? __uint_as_float(w) * __uint_as_float(r) : __uint_as_float(w) + __uint_as_float(r));
 }
-template <> __device__ __forceinline__ uint32_t add_residual_word<__nv_bfloat16>(uint32_t w, uint32_t r) {
+template <> __device__ __forceinline__ uint32_t add_residual_word<__nv_bfloat16>(uint32_t w, uint32_t r, int mul) {
   const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
   const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r));
-  return pack_word<__nv_bfloat16>(a.x + b.x, a.y + b.y);
+  return mul ? pack_word<__nv_bfloat16>(a.x * b.x, a.y * b.y) : pack_word<__nv_bfloat16>(a.x + b.x, a.y + b.y);
 }
-template <> __device__ __forceinline__ uint32_t add_residual_word<__half>(uint32_t w, uint32_t r) {
+template <> __device__ __forceinline__ uint32_t add_residual_word<__half>(uint32_t w, uint32_t r, int mul) {
   const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w));
   const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&r));
-  return pack_word<__half>(a.x + b.x, a.y + b.y);
+  return mul ? pack_word<__half>(a.x * b.x, a.y * b.y) : pack_word<__half>(a.x + b.x, a.y + b.y);
 }
 
 // 32 consecutive bias values starting at col (col is a multiple of 32 and col + 32 <= N is NOT assumed: tail guarded).
@@ -242,10 +243,10 @@ __device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem
           if (row_base + rr < g.M && col < g.N) {
             if (rbase) {
               const uint4 rq = rv[round * 4 + pass];
-              q.x = add_residual_word<OutT>(q.x, rq.x);
-              q.y = add_residual_word<OutT>(q.y, rq.y);
-              q.z = add_residual_word<OutT>(q.z, rq.z);
-              q.w = add_residual_word<OutT>(q.w, rq.w);
+              q.x = add_residual_word<OutT>(q.x, rq.x, g.residual_mul);
+              q.y = add_residual_word<OutT>(q.y, rq.y, g.residual_mul);
+              q.z = add_residual_word<OutT>(q.z, rq.z, g.residual_mul);
+              q.w = add_residual_word<OutT>(q.w, rq.w, g.residual_mul);
             }
             *reinterpret_cast<uint4*>(cbase + (int64_t)rr * g.ldc + col) = q;
           }
@@ -261,7 +262,7 @@ __device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem
             const int64_t c1 = col0 + lane;
             if (c1 < g.N) {
               uint32_t w = stage[rl * EPI_PITCH + lane];
-              if (rbase) w = add_residual_word<OutT>(w, reinterpret_cast<const uint32_t*>(rbase + (int64_t)rr * g.ldc)[c1]);
+              if (rbase) w = add_residual_word<OutT>(w, reinterpret_cast<const uint32_t*>(rbase + (int64_t)rr * g.ldc)[c1], g.residual_mul);
               reinterpret_cast<uint32_t*>(crow)[c1] = w;
             }
           } else {
@@ -275,7 +276,7 @@ __device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem
               if (c1 < g.N) {
                 if (rbase) {
                   const uint32_t rbits = reinterpret_cast<const uint16_t*>(rbase + (int64_t)rr * g.ldc)[c1];
-                  bits = (uint16_t)(add_residual_word<OutT>(bits, rbits) & 0xffffu);   // low halves; the high halves are zero
+                  bits = (uint16_t)(add_residual_word<OutT>(bits, rbits, g.residual_mul) & 0xffffu);   // low halves; the high halves are zero
                 }
                 reinterpret_cast<uint16_t*>(crow)[c1] = bits;
               }
@@ -730,7 +731,7 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
   if (!s.ok()) { cleanup(); return s; }
 
   TcArgs g;
-  g.c = p.c; g.bias = p.bias; g.residual = p.residual;
+  g.c = p.c; g.bias = p.bias; g.residual = p.residual; g.residual_mul = p.residual_op;
   g.M = p.m; g.N = p.n; g.K = p.k; g.ldc = p.n;
   g.batch = (int)p.batch;
   g.a_kmajor = p.a_k_major ? 1 : 0; g.b_kmajor = p.b_k_major ? 1 : 0;

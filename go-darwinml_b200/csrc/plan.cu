@@ -938,12 +938,13 @@ class Planner {
     gp.b_k_major = b_major == 1;
     gp.dtype = x->dtype;
     gp.activation = (int)x->fa[0];
+    gp.residual_op = (has_residual && x->fa[1] == 2.0) ? 1 : 0;
     const int bias_slot = bias ? SlotOf(bias) : -1;
     const int res_slot = residual ? SlotOf(residual) : -1;
     Step st;
     st.desc = strfmt("gemm[B=%lld M=%lld N=%lld K=%lld %s a:%s b:%s%s%s act=%d]", (long long)B, (long long)M, (long long)N, (long long)K,
                      dtype_name(x->dtype), gp.a_k_major ? "MK" : "KM", gp.b_k_major ? "NK" : "KN", bias ? " bias" : "",
-                     residual ? " +residual" : "", gp.activation);
+                     residual ? (gp.residual_op ? " *residual" : " +residual") : "", gp.activation);
     st.reads = {a_slot, b_slot};
     if (bias) st.reads.push_back(bias_slot);
     if (residual) st.reads.push_back(res_slot);

@@ -244,7 +244,8 @@ void LiveAndUsers(Graph& graph, const std::vector<Node*>& targets, std::unordere
 }
 }  // namespace
 
-// A transformer block ends its attention and MLP halves with "x + Dense(...)".  Run op by op the sum costs a read of
+// A transformer block ends its attention and MLP halves with "x + Dense(...)" (and a gated MLP multiplies two Dense
+// results: the same rewrite with * in place of +).  Run op by op the sum costs a read of
 // both operands and a write of the result (three passes over the activations) right after the GEMM wrote one of them;
 // in the GEMM's epilogue it costs one extra read.  The product is still rounded to the storage type before the
 // addition, so the fused value is bit-identical to the two-op one.
@@ -256,12 +257,18 @@ int RewriteGemmResidual(Graph& graph, const std::vector<Node*>& targets) {
   int rewritten = 0;
   for (auto& up : graph.nodes) {
     Node* m = up.get();
-    if (!live.count(m) || m->op != Op::Add) continue;
+    if (!live.count(m) || (m->op != Op::Add && m->op != Op::Mul)) continue;
     if (!(m->dtype == B200_FLOAT32 || m->dtype == B200_BFLOAT16 || m->dtype == B200_FLOAT16)) continue;
     for (int side = 0; side < 2; ++side) {
       Node* x = m->in[side];
       Node* r = m->in[1 - side];
       if (x == r || r->dims != m->dims || r->dtype != m->dtype) continue;
+      {
+        // a broadcast or generated operand is cheaper inside an elementwise kernel (stride 0, no tensor in memory)
+        const Node* rs = r;
+        while (rs->op == Op::Reshape || rs->op == Op::Identity || rs->op == Op::Cast) rs = rs->in[0];
+        if (rs->op == Op::BroadcastInDim || rs->op == Op::Constant || rs->op == Op::Iota) continue;
+      }
       // the product, seen through views that keep the element order, each with this chain as its only user
       bool chain_ok = true;
       Node* d = x;
@@ -273,11 +280,11 @@ int RewriteGemmResidual(Graph& graph, const std::vector<Node*>& targets) {
       if (d->dtype != m->dtype || d->num_elements() != m->num_elements()) continue;
       if (d->fa.size() > 1 && d->fa[1] != 0) continue;   // already carries a residual
       // r must exist independently of d (it cannot use d: d has a single user, the chain)
-      m->op = Op::DotGeneral;
       m->in = d->in;
       m->in.push_back(r);
       m->ia = d->ia;
-      m->fa = {d->fa.empty() ? 0.0 : d->fa[0], 1.0};
+      m->fa = {d->fa.empty() ? 0.0 : d->fa[0], m->op == Op::Mul ? 2.0 : 1.0};   // before m->op changes below
+      m->op = Op::DotGeneral;
       ++rewritten;
       break;
     }

@@ -713,3 +713,29 @@ def test_dense_plus_residual_is_one_gemm(b200, backend, dtype, shape):
     (oracle,) = run_oracle(fused, [x, w, bias, r])
     ok, viol = compare(got, oracle, rtol, ascale)
     assert ok, viol
+
+
+def test_gated_mlp_product_is_fused_into_one_gemm(b200, backend):
+    # act(x W1) * (x W2): the product runs in the epilogue of one of the two GEMMs; a scalar scale stays elementwise
+    rng = np.random.default_rng(96)
+    x, w1, w2 = rng_array(rng, (4, 70, 128), BF16), rng_array(rng, (128, 264), BF16, 0.1), rng_array(rng, (128, 264), BF16, 0.1)
+
+    def gated(f, xx, a, b_):
+        return f.Mul(f.FusedDense(xx, a, None, 3), f.FusedDense(xx, b_, None, 0))
+
+    def unfused(f, xx, a, b_):
+        g, u = f.FusedDense(xx, a, None, 3), f.FusedDense(xx, b_, None, 0)
+        return [f.Mul(g, u), g, u]
+
+    (got,), plan = run_backend(b200, backend, gated, [x, w1, w2], describe=True)
+    assert plan.count("gemm[") == 2 and "*residual" in plan and "ewise" not in plan, plan
+    (want, _, _), plan2 = run_backend(b200, backend, unfused, [x, w1, w2], describe=True)
+    assert "*residual" not in plan2
+    np.testing.assert_array_equal(got.view(np.uint16), want.view(np.uint16))
+
+    def scaled(f, xx, a, b_):
+        c = f.BroadcastInDim(f.Constant(np.array([0.5], dtype=BF16), 1), _S(b200, BF16, 4, 70, 264), [2])
+        return f.Mul(f.FusedDense(xx, a, None, 0), c)
+
+    (_,), plan3 = run_backend(b200, backend, scaled, [x, w1, w2], describe=True)
+    assert "residual" not in plan3, plan3
