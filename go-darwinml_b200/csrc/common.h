@@ -157,6 +157,8 @@ enum class Op : int {
   DotGeneral, Reduce, ArgMinMax, Gather,
   // fused
   Softmax, SoftmaxMasked, LayerNorm, RmsNorm, Attention,
+  // produced only by the compile-time rewrites: x * c + swap_halves(x) * s on the last axis (rotary embedding)
+  Rope,
   kNumOps
 };
 const char* op_name(Op op);
@@ -209,6 +211,9 @@ int RewriteRmsNorm(Graph& graph, const std::vector<Node*>& targets);
 // Compile-time rewrite: Add(DotGeneral(...), r) or Mul(DotGeneral(...), r) where the product has no other user becomes one
 // DotGeneral node that combines with r in its epilogue (rounding the product first, so the value is the op-by-op one).  Returns the number of rewrites.
 int RewriteGemmResidual(Graph& graph, const std::vector<Node*>& targets);
+// Compile-time rewrite: Add(Mul(x, c), Mul(Concatenate(upper half of x, lower half of x), s)) on the last axis becomes one
+// Rope node (inputs x, c, s): one pass over x instead of two slices, a concatenation and a three-op chain.
+int RewriteRope(Graph& graph, const std::vector<Node*>& targets);
 
 // What a B200Context handle points to: one graph under construction and its device.
 struct Ctx {

@@ -26,7 +26,7 @@ const char* op_name(Op op) {
       "Where", "Clamp",
       "Cast", "Reshape", "Transpose", "BroadcastInDim", "Slice", "Concatenate", "Reverse", "Pad",
       "DotGeneral", "Reduce", "ArgMinMax", "Gather",
-      "Softmax", "SoftmaxMasked", "LayerNorm", "RmsNorm", "Attention"};
+      "Softmax", "SoftmaxMasked", "LayerNorm", "RmsNorm", "Attention", "Rope"};
   static_assert(sizeof(names) / sizeof(names[0]) == (size_t)Op::kNumOps, "op_name table out of date");
   return names[(int)op];
 }

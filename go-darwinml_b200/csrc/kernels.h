@@ -159,6 +159,22 @@ struct GemmParams {
 };
 Status gemm(Device* dev, const GemmParams& p);
 
+// ------------------------------------------------------------------ rope ---
+// y[r, j] = round(round(x[r, j] * c[r, j]) + round(x[r, j ^ half] * s[r, j])) over rows of `cols` elements made of heads of
+// `head_dim`: j ^ half swaps the halves of each head.  x may live inside a wider buffer (row pitch x_pitch elements);
+// c and s repeat with a period of c_period / s_period elements (a table shared by every batch entry); y is dense.
+struct RopeParams {
+  const void* x = nullptr;
+  const void* c = nullptr;
+  const void* s = nullptr;
+  void* y = nullptr;
+  int64_t rows = 0, cols = 0, head_dim = 0;
+  int64_t x_pitch = 0;
+  int64_t c_period = 0, s_period = 0;
+  int dtype = B200_BFLOAT16;
+};
+Status rope(Device* dev, const RopeParams& p);
+
 // ------------------------------------------------------------- attention ---
 // softmax(scale * Q K^T [+ causal mask]) V for Q [B, Sq, H, D] / K, V [B, Sk, Hkv, D] (bshd) or [B, H, Sq, D] (bhsd);
 // O has Q's layout.  Query head h reads KV head h / (H / Hkv).

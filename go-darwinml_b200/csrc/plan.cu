@@ -279,6 +279,7 @@ class Planner {
       case Op::SoftmaxMasked: return EmitSoftmaxMasked(x);
       case Op::LayerNorm: case Op::RmsNorm: return EmitNorm(x);
       case Op::Attention: return EmitAttention(x);
+      case Op::Rope: return EmitRope(x);
       case Op::Concatenate: return EmitConcatenate(x);
       case Op::Pad: return EmitPad(x);
       case Op::Transpose: case Op::Slice: case Op::Reverse: case Op::BroadcastInDim:
@@ -1276,6 +1277,71 @@ class Planner {
     return Status::OK();
   }
 
+  // A table operand of Rope: when it is a broadcast of a smaller tensor over LEADING axes only (the same table for every
+  // batch entry), the kernel reads the small tensor with a period instead of a materialised copy.
+  Status PeriodicOperand(Node* t, int* slot, int64_t* period) {
+    Node* b = t;
+    while (b->op == Op::Identity) b = b->in[0];
+    if (b->op == Op::BroadcastInDim) {
+      Node* src = b->in[0];
+      const int r = b->rank(), k = src->rank();
+      bool trailing = k <= r && k > 0;
+      for (int i = 0; i < k && trailing; ++i) trailing = b->ia[i] == r - k + i && src->dims[i] == b->dims[r - k + i];
+      if (trailing && src->num_elements() > 0) {
+        B200_TRY(EnsureMaterialized(src));
+        *slot = SlotOf(src);
+        *period = src->num_elements();
+        return Status::OK();
+      }
+    }
+    B200_TRY(EnsureMaterialized(t));
+    *slot = SlotOf(t);
+    *period = t->num_elements();
+    return Status::OK();
+  }
+
+  Status EmitRope(Node* x) {
+    Node* src = x->in[0];
+    k::RopeParams rp;
+    rp.dtype = x->dtype;
+    rp.head_dim = x->dims.back();
+    Node* base = src;
+    int64_t offset = 0, st3[3];
+    const int64_t vec = 16 / dtype_size(x->dtype);
+    if (src->rank() == 4 && StridedProjectionView(src, true, &base, &offset, st3) && offset % vec == 0 && st3[2] % vec == 0) {
+      rp.rows = src->dims[0] * src->dims[1];
+      rp.cols = src->dims[2] * src->dims[3];
+      rp.x_pitch = st3[2];
+    } else {
+      base = src;
+      offset = 0;
+      rp.cols = src->dims.back();
+      rp.rows = src->num_elements() / rp.cols;
+      rp.x_pitch = rp.cols;
+    }
+    B200_TRY(EnsureMaterialized(base));
+    int c_slot, s_slot;
+    B200_TRY(PeriodicOperand(x->in[1], &c_slot, &rp.c_period));
+    B200_TRY(PeriodicOperand(x->in[2], &s_slot, &rp.s_period));
+    const int x_slot = SlotOf(base), out_slot = NewValueSlot(x);
+    const int64_t x_off = offset * dtype_size(x->dtype);
+    Step st;
+    st.desc = strfmt("rope[rows=%lld cols=%lld head=%lld %s pitch=%lld table_period=%lld]", (long long)rp.rows, (long long)rp.cols,
+                     (long long)rp.head_dim, dtype_name(x->dtype), (long long)rp.x_pitch, (long long)rp.c_period);
+    st.reads = {x_slot, c_slot, s_slot};
+    st.writes = {out_slot};
+    st.run = [rp, x_slot, c_slot, s_slot, out_slot, x_off](Device* dev, void* const* p) -> Status {
+      k::RopeParams q = rp;
+      q.x = (const char*)p[x_slot] + x_off;
+      q.c = p[c_slot];
+      q.s = p[s_slot];
+      q.y = p[out_slot];
+      return k::rope(dev, q);
+    };
+    ex_->steps.push_back(std::move(st));
+    return Status::OK();
+  }
+
   // A [cols] vector for gamma / beta: the parameter itself when it already is
   // one, else a broadcast copy laid over the normalised axes.
   Status NormParamSlot(Node* x, Node* p, const std::vector<int64_t>& axes, int64_t cols, int* slot) {
@@ -1467,6 +1533,7 @@ B200Exec b200_compile(B200Context ctx, const B200Value* feeds, int num_feeds, co
   }
   RewriteRmsNorm(c->graph, t);
   RewriteGemmResidual(c->graph, t);
+  RewriteRope(c->graph, t);
   std::unique_ptr<Exec> ex(new Exec());
   ex->dev = c->dev;
   Planner planner(c, ex.get());

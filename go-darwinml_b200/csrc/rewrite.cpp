@@ -292,6 +292,71 @@ int RewriteGemmResidual(Graph& graph, const std::vector<Node*>& targets) {
   return rewritten;
 }
 
+// Rotary position embedding in its rotate-half form reaches a backend as
+//   Add(Mul(x, cos), Mul(Concatenate(Slice(x, upper half), Slice(x, lower half)), sin))        (last axis, even size)
+// with the sign of the rotation folded into the sin table (or into a Neg that this matcher does not look through).
+// Op by op that is two slice copies, a concatenation and a three-op elementwise pass over every query and key of
+// every layer; as one Rope node the kernel reads x once (in place inside the QKV projection when it can) and writes
+// the result once.  Each product and the sum are rounded to the storage type, so the value is the op-by-op one.
+int RewriteRope(Graph& graph, const std::vector<Node*>& targets) {
+  std::unordered_set<Node*> live;
+  std::unordered_map<Node*, std::vector<Node*>> users;
+  LiveAndUsers(graph, targets, &live, &users);
+  auto half_slice = [](Node* s, Node* x, bool upper) {
+    if (s->op != Op::Slice || s->in[0] != x) return false;
+    const int r = x->rank();
+    const int64_t D = x->dims[r - 1], h = D / 2;
+    for (int d = 0; d < r; ++d) {
+      const int64_t start = s->ia[2 * d], stride = s->ia[2 * d + 1];
+      if (stride != 1) return false;
+      if (d < r - 1) {
+        if (start != 0 || s->dims[d] != x->dims[d]) return false;
+      } else if (start != (upper ? h : 0) || s->dims[d] != h) {
+        return false;
+      }
+    }
+    return true;
+  };
+  int rewritten = 0;
+  for (auto& up : graph.nodes) {
+    Node* m = up.get();
+    if (!live.count(m) || m->op != Op::Add) continue;
+    if (!(m->dtype == B200_FLOAT32 || m->dtype == B200_BFLOAT16 || m->dtype == B200_FLOAT16)) continue;
+    const int r = m->rank();
+    if (r < 1 || m->dims[r - 1] % 16 != 0) continue;   // half a head is a whole number of 16-byte vectors for every float type
+    Node* p = m->in[0];
+    Node* q = m->in[1];
+    if (p->op != Op::Mul || q->op != Op::Mul) continue;
+    Node *x = nullptr, *c = nullptr, *s = nullptr;
+    // one product has the Concatenate of x's halves as an operand, the other has x itself
+    for (int which = 0; which < 2 && !x; ++which) {
+      Node* rot_mul = which ? p : q;
+      Node* dir_mul = which ? q : p;
+      for (int rs = 0; rs < 2 && !x; ++rs) {
+        Node* w = rot_mul->in[rs];
+        if (w->op != Op::Concatenate || w->in.size() != 2 || w->ia.empty() || w->ia[0] != r - 1) continue;
+        Node* src = w->in[0]->op == Op::Slice ? w->in[0]->in[0] : nullptr;
+        if (!src || src->dims != m->dims || src->dtype != m->dtype) continue;
+        if (!half_slice(w->in[0], src, true) || !half_slice(w->in[1], src, false)) continue;
+        for (int ds = 0; ds < 2; ++ds) {
+          if (dir_mul->in[ds] != src) continue;
+          x = src;
+          c = dir_mul->in[1 - ds];
+          s = rot_mul->in[1 - rs];
+          break;
+        }
+      }
+    }
+    if (!x || c->dims != m->dims || s->dims != m->dims || c->dtype != m->dtype || s->dtype != m->dtype) continue;
+    m->op = Op::Rope;
+    m->in = {x, c, s};
+    m->ia.clear();
+    m->fa.clear();
+    ++rewritten;
+  }
+  return rewritten;
+}
+
 int RewriteRmsNorm(Graph& graph, const std::vector<Node*>& targets) {
   // nodes reachable from the targets, and their users
   std::unordered_set<Node*> live;

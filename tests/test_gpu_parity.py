@@ -739,3 +739,57 @@ def test_gated_mlp_product_is_fused_into_one_gemm(b200, backend):
 
     (_,), plan3 = run_backend(b200, backend, scaled, [x, w1, w2], describe=True)
     assert "residual" not in plan3, plan3
+
+
+# ---- rotary embedding spelled with Slice / Concatenate / Mul / Add runs as one pass --------------------------------
+def _rope_graph(b200, dt, B, S, H, D, hide=False):
+    full = _S(b200, dt, B, S, H, D)
+
+    def build(f, x, cos, sin):
+        r = 4
+        lo = f.Slice(x, [0, 0, 0, 0], [B, S, H, D // 2], [1] * r)
+        hi = f.Slice(x, [0, 0, 0, D // 2], [B, S, H, D], [1] * r)
+        swapped = f.Concatenate(3, hi, lo)
+        c = f.BroadcastInDim(cos, full, [1, 2, 3])     # table [S, H, D] shared by every batch entry
+        s = f.BroadcastInDim(sin, full, [1, 2, 3])
+        xd = f.Identity(x) if hide else x              # a different node for the direct product: the matcher must not fire
+        return f.Add(f.Mul(xd, c), f.Mul(swapped, s))
+    return build
+
+
+@pytest.mark.parametrize("dt", [BF16, np.float32], ids=["bf16", "f32"])
+def test_rope_from_primitives_is_one_kernel(b200, backend, dt):
+    B, S, H, D = 3, 17, 4, 64
+    rng = np.random.default_rng(97)
+    x = rng_array(rng, (B, S, H, D), dt)
+    ang = rng.uniform(0, 6.28, size=(S, H, D))
+    cos, sin = np.cos(ang).astype(np.float32).astype(dt), np.sin(ang).astype(np.float32).astype(dt)
+    (got,), plan = run_backend(b200, backend, _rope_graph(b200, dt, B, S, H, D), [x, cos, sin], describe=True)
+    assert plan.count("\n") == 1 and plan.startswith("rope["), plan
+    assert f"table_period={S * H * D}" in plan, plan           # the batch broadcast is never materialised
+    (plain,), plan2 = run_backend(b200, backend, _rope_graph(b200, dt, B, S, H, D, hide=True), [x, cos, sin], describe=True)
+    assert "rope[" not in plan2, plan2
+    word = np.uint16 if dt is BF16 else np.uint32
+    np.testing.assert_array_equal(got.view(word), plain.view(word))     # the op-by-op value, bit for bit
+    (want,) = run_oracle(_rope_graph(b200, dt, B, S, H, D), [x, cos, sin])
+    ok, viol = compare(got, want, 8e-3 if dt is BF16 else 1e-6, 1.0)
+    assert ok, viol
+
+
+def test_rope_reads_queries_inside_the_projection_buffer(b200, backend):
+    # q = Reshape(Slice(QKV)) feeds the rotary kernel in place: no Slice copy in the plan
+    B, S, H, D, W = 2, 24, 4, 64, 4 * 64 + 2 * 64
+    rng = np.random.default_rng(98)
+    qkv = rng_array(rng, (B, S, W), BF16)
+    ang = rng.uniform(0, 6.28, size=(S, H, D))
+    cos, sin = np.cos(ang).astype(np.float32).astype(BF16), np.sin(ang).astype(np.float32).astype(BF16)
+
+    def build(f, t, c_, s_):
+        q = f.Reshape(f.Slice(t, [0, 0, 64], [B, S, 64 + H * D], [1, 1, 1]), B, S, H, D)
+        return [_rope_graph(b200, BF16, B, S, H, D)(f, q, c_, s_), f.Neg(t)]
+
+    got, plan = run_backend(b200, backend, build, [qkv, cos, sin], describe=True)
+    assert "rope[" in plan and f"pitch={W}" in plan and "move[" not in plan, plan
+    want = run_oracle(build, [qkv, cos, sin])
+    ok, viol = compare(got[0], want[0], 8e-3, 1.0)
+    assert ok, viol
