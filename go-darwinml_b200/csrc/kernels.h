@@ -97,7 +97,14 @@ struct StridedCopyParams {
 Status strided_copy(Device* dev, const StridedCopyParams& p);
 // Batched 2-D transpose through shared memory: x[batch, rows, cols] -> y[batch, cols, rows].
 Status transpose_2d(Device* dev, const void* x, void* y, int64_t batch, int64_t rows, int64_t cols, int elt_size);
+// Up to 8 contiguous arrays laid end to end into y with ONE launch (small concatenations are launch-bound: a fused QKV
+// projection joins three bias vectors per layer).  counts are in elements.
+constexpr int kMaxConcatFlat = 8;
+Status concat_flat(Device* dev, const void* const* src, const int64_t* counts, int n, void* y, int elt_size);
 Status fill(Device* dev, void* y, int64_t n, int elt_size, uint64_t pattern);
+// Packs rows of `cols` elements stored with a pitch of `src_pitch` elements into a dense [rows, cols] array, writing
+// whole 16-byte vectors of the destination whatever the alignment of its rows.
+Status unpad_rows(Device* dev, const void* src, void* dst, int64_t rows, int64_t cols, int64_t src_pitch, int elt_size);
 Status iota(Device* dev, void* y, int dtype, int64_t outer, int64_t n, int64_t inner);
 Status cast(Device* dev, const void* x, int src_dtype, void* y, int dst_dtype, int64_t n);
 
@@ -154,6 +161,9 @@ struct GemmParams {
   // DotGeneral followed by Add, without the extra pass over C)
   const void* residual = nullptr;
   int residual_op = 0;   // 0: + residual, 1: * residual (a gated MLP's act(x W1) * (x W2))
+  // Row pitch of C (and of the residual) in elements; 0 = n.  A pitch rounded up to 16 bytes lets a ragged N use the
+  // vector epilogue: the columns between n and the pitch are written with don't-care values.
+  int64_t ldc = 0;
   // batch strides in elements; 0 on an operand broadcasts it over the batch
   int64_t a_batch_stride = -1, b_batch_stride = -1;  // -1 = dense (m*k, k*n)
 };

@@ -39,7 +39,7 @@ struct SimtArgs {
   const void* bias;
   const void* residual;
   int residual_op;
-  int64_t m, n, k;
+  int64_t m, n, k, ldc;
   int64_t a_sm, a_sk, a_sb;  // element strides of A along m, k, batch
   int64_t b_sk, b_sn, b_sb;
   int activation;
@@ -54,7 +54,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtArgs g) {
   const int64_t batch = blockIdx.z;
   const T* a = reinterpret_cast<const T*>(g.a) + batch * g.a_sb;
   const T* b = reinterpret_cast<const T*>(g.b) + batch * g.b_sb;
-  T* c = reinterpret_cast<T*>(g.c) + batch * g.m * g.n;
+  T* c = reinterpret_cast<T*>(g.c) + batch * g.m * g.ldc;
   const int64_t m0 = (int64_t)blockIdx.y * BM, n0 = (int64_t)blockIdx.x * BN;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   A acc[4][4];
@@ -111,10 +111,10 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtArgs g) {
         // the sum is rounded to the storage type first, as a separate DotGeneral would have left it
         T t;
         g_store<A, T>(&t, v);
-        const A rv = g_load<T, A>(reinterpret_cast<const T*>(g.residual) + (c - reinterpret_cast<T*>(g.c)) + gm * g.n + gn);
+        const A rv = g_load<T, A>(reinterpret_cast<const T*>(g.residual) + (c - reinterpret_cast<T*>(g.c)) + gm * g.ldc + gn);
         v = g.residual_op ? g_load<T, A>(&t) * rv : g_load<T, A>(&t) + rv;
       }
-      g_store<A, T>(c + gm * g.n + gn, v);
+      g_store<A, T>(c + gm * g.ldc + gn, v);
     }
   }
 }
@@ -125,7 +125,7 @@ Status gemm_simt(Device* dev, const GemmParams& p) {
   if (p.batch * p.m * p.n == 0) return Status::OK();
   SimtArgs g;
   g.a = p.a; g.b = p.b; g.c = p.c; g.bias = p.bias; g.residual = p.residual; g.residual_op = p.residual_op;
-  g.m = p.m; g.n = p.n; g.k = p.k;
+  g.m = p.m; g.n = p.n; g.k = p.k; g.ldc = p.ldc > 0 ? p.ldc : p.n;
   g.a_sm = p.a_k_major ? p.k : 1;
   g.a_sk = p.a_k_major ? 1 : p.m;
   g.b_sk = p.b_k_major ? 1 : p.n;

@@ -252,34 +252,46 @@ __device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem
           }
         }
       } else {
-        // Rows of C do not start 16-byte aligned (N is not a multiple of the vector width): a warp writes the CONSECUTIVE
-        // columns of one row per store instruction, element by element.
-        for (int rl = 0; rl < 16; ++rl) {
-          const int rr = round * 16 + rl;
-          if (row_base + rr >= g.M) break;
-          OutT* crow = cbase + (int64_t)rr * g.ldc;
+        // Rows of C do not start 16-byte aligned (N is not a multiple of the vector width): a warp writes one row's 32
+        // words per store instruction, 4 bytes per lane.  A 16-bit row that starts on an odd element is 2 bytes off the
+        // word grid: its words are re-cut from neighbouring staged words (funnel shift) and the two end elements go out
+        // as 2-byte stores.  Fully unrolled and predicated: the loads of all 16 rows are independent.
+        // parity of the element index of (row, col0): col0 and ldc * 16 * round contribute nothing when they are even
+        const uint32_t n_odd = (uint32_t)(g.ldc & 1);
+        const uint32_t base_odd = (uint32_t)((((int64_t)b * g.M + row_base + round * 16) * g.ldc + col0) & 1);
+        OutT* crow = cbase + (int64_t)(round * 16) * g.ldc;
+        const OutT* rrow = rbase ? rbase + (int64_t)(round * 16) * g.ldc : nullptr;
+#pragma unroll 4
+        for (int rl = 0; rl < 16; ++rl, crow += g.ldc, rrow += (rbase ? g.ldc : 0)) {
+          if (row_base + round * 16 + rl >= g.M) break;
           if (CPW == 1) {
             const int64_t c1 = col0 + lane;
             if (c1 < g.N) {
               uint32_t w = stage[rl * EPI_PITCH + lane];
-              if (rbase) w = add_residual_word<OutT>(w, reinterpret_cast<const uint32_t*>(rbase + (int64_t)rr * g.ldc)[c1], g.residual_mul);
+              if (rbase) w = add_residual_word<OutT>(w, reinterpret_cast<const uint32_t*>(rrow)[c1], g.residual_mul);
               reinterpret_cast<uint32_t*>(crow)[c1] = w;
             }
           } else {
-            // 64 columns: lane writes columns lane and lane + 32 (each a half of a packed word)
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-              const int cidx = hh * 32 + lane;
-              const int64_t c1 = col0 + cidx;
-              const uint32_t w = stage[rl * EPI_PITCH + (cidx >> 1)];
-              uint16_t bits = (cidx & 1) ? (uint16_t)(w >> 16) : (uint16_t)(w & 0xffffu);
-              if (c1 < g.N) {
-                if (rbase) {
-                  const uint32_t rbits = reinterpret_cast<const uint16_t*>(rbase + (int64_t)rr * g.ldc)[c1];
-                  bits = (uint16_t)(add_residual_word<OutT>(bits, rbits, g.residual_mul) & 0xffffu);   // low halves; the high halves are zero
-                }
-                reinterpret_cast<uint16_t*>(crow)[c1] = bits;
-              }
+            const uint32_t odd = base_odd ^ ((uint32_t)rl & n_odd);
+            const uint32_t w0 = stage[rl * EPI_PITCH + lane];
+            const uint32_t w1 = stage[rl * EPI_PITCH + lane + 1];   // lane 31 reads the pad word: unused
+            uint32_t w = odd ? __funnelshift_r(w0, w1, 16) : w0;     // elements (2 lane + odd, 2 lane + odd + 1)
+            const int64_t c1 = col0 + 2 * lane + odd;
+            uint16_t* c16 = reinterpret_cast<uint16_t*>(crow);
+            const uint16_t* r16 = reinterpret_cast<const uint16_t*>(rrow);
+            const bool pair_ok = c1 + 1 < g.N && !(odd && lane == 31);
+            if (pair_ok) {
+              if (rbase) w = add_residual_word<OutT>(w, (uint32_t)r16[c1] | ((uint32_t)r16[c1 + 1] << 16), g.residual_mul);
+              *reinterpret_cast<uint32_t*>(c16 + c1) = w;     // (row start + 2 lane + odd) is even: 4-byte aligned
+            } else if (c1 < g.N) {
+              uint32_t lo = w & 0xffffu;                      // the last column of the row, or element 63 of an odd row
+              if (rbase) lo = add_residual_word<OutT>(lo, r16[c1], g.residual_mul) & 0xffffu;
+              c16[c1] = (uint16_t)lo;
+            }
+            if (odd && lane == 0 && col0 < g.N) {             // element 0 of an odd row
+              uint32_t lo = w0 & 0xffffu;
+              if (rbase) lo = add_residual_word<OutT>(lo, r16[col0], g.residual_mul) & 0xffffu;
+              c16[col0] = (uint16_t)lo;
             }
           }
         }
@@ -732,7 +744,7 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
 
   TcArgs g;
   g.c = p.c; g.bias = p.bias; g.residual = p.residual; g.residual_mul = p.residual_op;
-  g.M = p.m; g.N = p.n; g.K = p.k; g.ldc = p.n;
+  g.M = p.m; g.N = p.n; g.K = p.k; g.ldc = p.ldc > 0 ? p.ldc : p.n;
   g.batch = (int)p.batch;
   g.a_kmajor = p.a_k_major ? 1 : 0; g.b_kmajor = p.b_k_major ? 1 : 0;
   g.activation = p.activation;
@@ -745,7 +757,7 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
   g.k_blocks = (int)((p.k + BK - 1) / BK);
   g.segs = is32 ? 6 : 1;
   const int out_vec = is32 ? 4 : 8;
-  g.vec_store = (p.n % out_vec == 0 && aligned16(p.c) && aligned16(p.residual)) ? 1 : 0;
+  g.vec_store = (g.ldc % out_vec == 0 && g.ldc >= (p.n + out_vec - 1) / out_vec * out_vec && aligned16(p.c) && aligned16(p.residual)) ? 1 : 0;
   g.err_flag = dev->kernel_error_flag();
 
   cudaError_t e = cudaSuccess;

@@ -104,6 +104,64 @@ __global__ void __launch_bounds__(256) iota_kernel(T* y, int64_t total, int64_t 
     y[i] = from_index<T>((i / inner) % n);
 }
 
+// Dense [rows, cols] from rows stored with a pitch: every thread produces one ALIGNED 16-byte vector of the destination
+// (the destination as a whole is one contiguous array, so its vectors never straddle anything but a row seam).  The
+// source bytes of a vector lie at an arbitrary even offset: two aligned 16-byte loads and a funnel shift.  Vectors
+// that straddle a row seam, and the tail, go element by element.
+template <typename E>
+__global__ void __launch_bounds__(256) unpad_rows_kernel(const E* __restrict__ src, E* __restrict__ dst, int64_t total, int64_t cols,
+                                                         int64_t pitch) {
+  constexpr int V = 16 / (int)sizeof(E);
+  const int64_t nvec = (total + V - 1) / V;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < nvec; t += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t i0 = t * V;
+    const int64_t r = i0 / cols;
+    const int64_t c = i0 - r * cols;
+    if (c + V <= cols && i0 + V <= total) {
+      const uintptr_t addr = reinterpret_cast<uintptr_t>(src + r * pitch + c);
+      const uint4* a = reinterpret_cast<const uint4*>(addr & ~uintptr_t(15));
+      const uint32_t sh = (uint32_t)(addr & 15);
+      const uint4 v0 = __ldg(a);
+      uint4 out = v0;
+      if (sh != 0) {
+        const uint4 v1 = __ldg(a + 1);
+        const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        const uint32_t bits = (sh & 3) * 8;
+        switch (sh >> 2) {
+          case 0: out = make_uint4(__funnelshift_r(w[0], w[1], bits), __funnelshift_r(w[1], w[2], bits), __funnelshift_r(w[2], w[3], bits), __funnelshift_r(w[3], w[4], bits)); break;
+          case 1: out = make_uint4(__funnelshift_r(w[1], w[2], bits), __funnelshift_r(w[2], w[3], bits), __funnelshift_r(w[3], w[4], bits), __funnelshift_r(w[4], w[5], bits)); break;
+          case 2: out = make_uint4(__funnelshift_r(w[2], w[3], bits), __funnelshift_r(w[3], w[4], bits), __funnelshift_r(w[4], w[5], bits), __funnelshift_r(w[5], w[6], bits)); break;
+          default: out = make_uint4(__funnelshift_r(w[3], w[4], bits), __funnelshift_r(w[4], w[5], bits), __funnelshift_r(w[5], w[6], bits), __funnelshift_r(w[6], w[7], bits)); break;
+        }
+      }
+      *reinterpret_cast<uint4*>(dst + i0) = out;
+    } else {
+      int64_t rr = r, cc = c;
+      for (int e = 0; e < V && i0 + e < total; ++e) {
+        dst[i0 + e] = src[rr * pitch + cc];
+        if (++cc == cols) { cc = 0; ++rr; }
+      }
+    }
+  }
+}
+
+struct ConcatFlatArgs {
+  const void* src[kMaxConcatFlat];
+  int64_t end[kMaxConcatFlat];   // running element count after each operand
+  int n;
+  void* dst;
+};
+template <typename E>
+__global__ void __launch_bounds__(256) concat_flat_kernel(const ConcatFlatArgs a) {
+  const int64_t total = a.end[a.n - 1];
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    int k = 0;
+    while (i >= a.end[k]) ++k;
+    const int64_t start = k ? a.end[k - 1] : 0;
+    reinterpret_cast<E*>(a.dst)[i] = reinterpret_cast<const E*>(a.src[k])[i - start];
+  }
+}
+
 unsigned grid_for(Device* dev, int64_t work_items) {
   const int64_t blocks = (work_items + 255) / 256;
   const int64_t cap = (int64_t)dev->sm_count() * 32;
@@ -164,6 +222,42 @@ Status strided_copy(Device* dev, const StridedCopyParams& p) {
     }
   }
   return dev->CheckLaunch("strided_copy");
+}
+
+Status concat_flat(Device* dev, const void* const* src, const int64_t* counts, int n, void* y, int elt_size) {
+  if (n < 1 || n > kMaxConcatFlat) return Status::Invalid("concat_flat: 1 to 8 operands");
+  ConcatFlatArgs a;
+  int64_t run = 0;
+  for (int i = 0; i < n; ++i) { a.src[i] = src[i]; run += counts[i]; a.end[i] = run; }
+  for (int i = n; i < kMaxConcatFlat; ++i) { a.src[i] = nullptr; a.end[i] = run; }
+  a.n = n;
+  a.dst = y;
+  if (run == 0) return Status::OK();
+  B200_TRY(dev->MakeCurrent());
+  const unsigned grid = grid_for(dev, run);
+  cudaStream_t s = dev->stream();
+  switch (elt_size) {
+    case 1: concat_flat_kernel<uint8_t><<<grid, 256, 0, s>>>(a); break;
+    case 2: concat_flat_kernel<uint16_t><<<grid, 256, 0, s>>>(a); break;
+    case 4: concat_flat_kernel<uint32_t><<<grid, 256, 0, s>>>(a); break;
+    case 8: concat_flat_kernel<uint64_t><<<grid, 256, 0, s>>>(a); break;
+    default: return Status::Invalid("concat_flat: element size");
+  }
+  return dev->CheckLaunch("concat_flat");
+}
+
+// The source must be readable for 16 bytes past its last element (the second aligned load of the last vector).
+Status unpad_rows(Device* dev, const void* src, void* dst, int64_t rows, int64_t cols, int64_t src_pitch, int elt_size) {
+  const int64_t total = rows * cols;
+  if (total == 0) return Status::OK();
+  if (!(elt_size == 2 || elt_size == 4) || src_pitch < cols) return Status::Invalid("unpad_rows: 2- or 4-byte elements, pitch >= cols");
+  if ((reinterpret_cast<uintptr_t>(dst) & 15) != 0 || (reinterpret_cast<uintptr_t>(src) & (uintptr_t)(elt_size - 1)) != 0)
+    return Status::Invalid("unpad_rows: destination must be 16-byte aligned");
+  B200_TRY(dev->MakeCurrent());
+  const unsigned grid = grid_for(dev, (total + 16 / elt_size - 1) / (16 / elt_size));
+  if (elt_size == 2) unpad_rows_kernel<uint16_t><<<grid, 256, 0, dev->stream()>>>((const uint16_t*)src, (uint16_t*)dst, total, cols, src_pitch);
+  else unpad_rows_kernel<uint32_t><<<grid, 256, 0, dev->stream()>>>((const uint32_t*)src, (uint32_t*)dst, total, cols, src_pitch);
+  return dev->CheckLaunch("unpad_rows");
 }
 
 Status transpose_2d(Device* dev, const void* x, void* y, int64_t batch, int64_t rows, int64_t cols, int elt_size) {

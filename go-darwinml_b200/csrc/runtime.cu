@@ -96,10 +96,12 @@ Status Device::CheckKernelErrors() {
   B200_CUDA_TRY(cudaStreamSynchronize(stream_));
   if (code != 0) {
     B200_CUDA_TRY(cudaMemsetAsync(error_flag_, 0, sizeof(int), stream_));
-    static const char* who[] = {"?", "the tile producer waiting for a free stage", "the MMA issuer waiting for a drained accumulator",
-                                "the MMA issuer waiting for operand tiles", "the epilogue waiting for a finished accumulator"};
-    return Status::Timeout(strfmt("a bounded wait inside a GEMM kernel gave up (%s); its results are invalid",
-                                  (code >= 1 && code <= 4) ? who[code] : who[0]));
+    static const char* who[] = {"?", "a tile loader waiting for a free stage", "an MMA issuer waiting for a drained accumulator or for Q",
+                                "an MMA issuer waiting for operand tiles", "an epilogue or MMA issuer waiting for its producer",
+                                "a kernel whose shared-memory window is not 1024-byte aligned", "a softmax warp waiting for scores",
+                                "a softmax warp waiting for the output MMAs"};
+    return Status::Timeout(strfmt("a bounded wait inside a tensor-core kernel gave up (%s); its results are invalid",
+                                  (code >= 1 && code <= 7) ? who[code] : who[0]));
   }
   return Status::OK();
 }

@@ -793,3 +793,26 @@ def test_rope_reads_queries_inside_the_projection_buffer(b200, backend):
     want = run_oracle(build, [qkv, cos, sin])
     ok, viol = compare(got[0], want[0], 8e-3, 1.0)
     assert ok, viol
+
+
+@pytest.mark.parametrize("dtype,M,N", [(BF16, 2048, 2051), (np.float32, 1040, 2050), (BF16, 4100, 1030)], ids=["bf16_odd", "f32_even", "bf16_even"])
+def test_large_ragged_result_goes_through_a_padded_pitch(b200, backend, dtype, M, N):
+    # rows that are not a whole number of 16-byte vectors: GEMM into a padded pitch, then one packing pass
+    rng = np.random.default_rng(99)
+    a, w = rng_array(rng, (M, 64), dtype), rng_array(rng, (N, 64), dtype, 0.2)
+    (got,), plan = run_backend(b200, backend, lambda f, x, y: f.DotGeneral(x, [1], [], y, [1], []), [a, w], describe=True)
+    assert "move[pack" in plan, plan
+    (want,) = run_oracle(lambda f, x, y: f.DotGeneral(x, [1], [], y, [1], []), [a, w])
+    rtol, ascale = _dot_tol(dtype)
+    ok, viol = compare(got, want, rtol, ascale)
+    assert ok, viol
+
+
+def test_small_concatenation_is_one_launch(b200, backend):
+    rng = np.random.default_rng(100)
+    parts = [rng_array(rng, (n,), BF16) for n in (768, 768, 768, 5)]
+    (got,), plan = run_backend(b200, backend, lambda f, *p: f.Concatenate(0, *p), parts, describe=True)
+    assert plan.count("\n") == 1 and "flat" in plan, plan
+    np.testing.assert_array_equal(got.view(np.uint16), np.concatenate(parts).view(np.uint16))
+    ints = [rng_array(rng, (1, 3, 7), np.int64), rng_array(rng, (1, 2, 7), np.int64)]
+    assert_parity(b200, backend, lambda f, a, b: f.Concatenate(1, a, b), ints)
