@@ -1,7 +1,11 @@
 // LayerNorm and RMSNorm row kernels.
 //
-//   LayerNorm: mu = sum(x)/n; d = x - mu; var = sum(d*d)/n (biased, two-pass);
-//              y = d * rsqrt(var + eps) [* gamma] [+ beta]
+//   LayerNorm: one pass over the row: d = x - K; m = sum(d)/n; var = sum(d*d)/n - m*m (biased);
+//              y = (d - m) * rsqrt(var + eps) [* gamma] [+ beta]          -- equal to the two-pass textbook form.
+//              K is the row's first element for fp32 and f16 rows (any value near the data removes the cancellation
+//              of the one-pass formula).  bf16 rows use K = 0: with fp32 sums the cancellation error of the variance
+//              is about 1e-6 * (mean/sigma)^2 relative, and a bf16 row whose mean/sigma exceeds 100 has lost its
+//              variance to its own 8-bit quantisation already, so the error stays below the input's noise;
 //              (the formula of the reference's FusedLayerNorm lowering,
 //              mpsgraph function.go:2430-2558, which spends ~12 graph ops on it)
 //   RMSNorm:   y = x * rsqrt(sum(x*x)/n + eps) [* gamma]   (no reference counterpart)
@@ -22,7 +26,12 @@
 //     outside the row loop: at 2 bytes per element the kernel is as close to
 //     the instruction-issue limit as to the HBM limit, so every per-element
 //     instruction counts;
-//   * the next row's loads are issued before the current row is reduced.
+//   * the next row's loads are issued before the current row is reduced;
+//   * one reduction round per row: sum and sum of squares travel together (LayerNorm's shifted one-pass variance),
+//     the per-warp partials are double-buffered in shared memory so a round costs ONE named barrier, and the
+//     cross-warp step is a few broadcast reads instead of a second shuffle tree.
+#include <type_traits>
+
 #include "../kernels.h"
 #include "rowwise.cuh"
 
@@ -40,21 +49,32 @@ struct NArgs {
   float eps;
 };
 
-// Sum over the TPR threads of a row group; all of them get the result.
-// `slot` is this group's private area of WPR floats; `bar` its barrier id.
-template <int TPR>
-__device__ __forceinline__ float group_sum(float v, float* slot, int bar) {
-  v = warp_reduce(v, SumOp());
+// Sums of NV values over the TPR threads of a row group; all of them get the results.  `slots` is this group's private
+// area of 2 x NV x WPR floats, used alternately by successive calls (`phase`), which is what lets one barrier per call
+// suffice: a warp can only reach the call after next, which reuses a buffer, once every warp has passed this call's
+// barrier and therefore finished reading the call before.
+template <int TPR, int NV>
+__device__ __forceinline__ void group_sum_n(float (&v)[NV], float* slots, int bar, int& phase) {
+#pragma unroll
+  for (int i = 0; i < NV; ++i) v[i] = warp_reduce(v[i], SumOp());
   if constexpr (TPR > 32) {
     constexpr int WPR = TPR / 32;
     const int lane = threadIdx.x & 31, w = (threadIdx.x % TPR) >> 5;
-    asm volatile("bar.sync %0, %1;" ::"r"(bar), "r"(TPR) : "memory");  // previous use of slot is over
-    if (lane == 0) slot[w] = v;
+    float* buf = slots + phase * (NV * WPR);
+    phase ^= 1;
+    if (lane == 0) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) buf[i * WPR + w] = v[i];
+    }
     asm volatile("bar.sync %0, %1;" ::"r"(bar), "r"(TPR) : "memory");
-    float t = (lane < WPR) ? slot[lane] : 0.f;
-    v = warp_reduce(t, SumOp());
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      float t = 0.f;
+#pragma unroll
+      for (int k = 0; k < WPR; ++k) t += buf[i * WPR + k];   // same address for every lane: broadcast reads
+      v[i] = t;
+    }
   }
-  return v;
 }
 
 template <typename T, int ITERS, int TPR, bool RMS, bool HAS_G, bool HAS_B>
@@ -62,10 +82,11 @@ __global__ void __launch_bounds__(TPR > 256 ? TPR : 256, TPR > 512 ? 1 : (TPR > 
   constexpr int V = Cvt<T>::N;
   constexpr int BLOCK = TPR > 256 ? TPR : 256;
   constexpr int GROUPS = BLOCK / TPR;
-  __shared__ float red[32];
+  __shared__ float red[2 * 2 * 32];   // per group: 2 phases x up to 2 values x warps per row
   const int group = threadIdx.x / TPR;
   const int t = threadIdx.x % TPR;
-  float* slot = red + group * (TPR / 32);
+  float* slot = red + group * (4 * (TPR / 32));
+  int phase = 0;
   const int bar = 1 + group;
   const float inv_n = 1.0f / (float)a.cols;
 
@@ -93,17 +114,21 @@ __global__ void __launch_bounds__(TPR > 256 ? TPR : 256, TPR > 512 ? 1 : (TPR > 
   const int64_t row_stride = (int64_t)gridDim.x * GROUPS;
   int64_t row = (int64_t)blockIdx.x * GROUPS + group;
   Raw16 raw[ITERS];
+  constexpr bool SHIFT = !RMS && !std::is_same<T, __nv_bfloat16>::value;
+  float shift = 0.f;   // LayerNorm on fp32 / f16 rows: the row's first element
   if (row < a.rows) {
     const T* xr = reinterpret_cast<const T*>(a.x) + row * a.cols;
 #pragma unroll
     for (int it = 0; it < ITERS; ++it)
       if (valid[it]) raw[it] = ld_stream16(xr + c0[it]);
+    if constexpr (SHIFT) shift = Cvt<T>::load1(xr);
   }
   for (; row < a.rows; row += row_stride) {
     float f[ITERS][V];
 #pragma unroll
     for (int it = 0; it < ITERS; ++it)
       if (valid[it]) Cvt<T>::unpack(raw[it], f[it]);
+    const float K = shift;
     // prefetch the next row of this group while this one is reduced
     const int64_t next = row + row_stride;
     if (next < a.rows) {
@@ -111,30 +136,37 @@ __global__ void __launch_bounds__(TPR > 256 ? TPR : 256, TPR > 512 ? 1 : (TPR > 
 #pragma unroll
       for (int it = 0; it < ITERS; ++it)
         if (valid[it]) raw[it] = ld_stream16(xn + c0[it]);
+      if constexpr (SHIFT) shift = Cvt<T>::load1(xn);
     }
-    float mean = 0.f;
-    if constexpr (!RMS) {
-      float s = 0.f;
+    float rstd, offset = 0.f;   // y = f * rstd + offset
+    if constexpr (RMS) {
+      float acc[1] = {0.f};
 #pragma unroll
       for (int it = 0; it < ITERS; ++it)
         if (valid[it]) {
 #pragma unroll
-          for (int e = 0; e < V; ++e) s += f[it][e];
+          for (int e = 0; e < V; ++e) acc[0] += f[it][e] * f[it][e];
         }
-      mean = group_sum<TPR>(s, slot, bar) * inv_n;
+      group_sum_n<TPR, 1>(acc, slot, bar, phase);
+      rstd = rsqrtf(acc[0] * inv_n + a.eps);
+    } else {
+      float acc[2] = {0.f, 0.f};
+#pragma unroll
+      for (int it = 0; it < ITERS; ++it)
+        if (valid[it]) {
+#pragma unroll
+          for (int e = 0; e < V; ++e) {
+            if constexpr (SHIFT) f[it][e] -= K;
+            acc[0] += f[it][e];
+            acc[1] += f[it][e] * f[it][e];
+          }
+        }
+      group_sum_n<TPR, 2>(acc, slot, bar, phase);
+      const float center = acc[0] * inv_n;                      // mean - K
+      const float var = fmaxf(acc[1] * inv_n - center * center, 0.f);
+      rstd = rsqrtf(var + a.eps);
+      offset = -center * rstd;
     }
-    float sq = 0.f;
-#pragma unroll
-    for (int it = 0; it < ITERS; ++it)
-      if (valid[it]) {
-#pragma unroll
-        for (int e = 0; e < V; ++e) {
-          if constexpr (!RMS) f[it][e] -= mean;
-          sq += f[it][e] * f[it][e];
-        }
-      }
-    sq = group_sum<TPR>(sq, slot, bar);
-    const float rstd = rsqrtf(sq * inv_n + a.eps);
     T* yr = reinterpret_cast<T*>(a.y) + row * a.cols;
 #pragma unroll
     for (int it = 0; it < ITERS; ++it)
@@ -143,7 +175,7 @@ __global__ void __launch_bounds__(TPR > 256 ? TPR : 256, TPR > 512 ? 1 : (TPR > 
         if constexpr (HAS_B && !RMS) Cvt<T>::unpack(bq[it], b);
 #pragma unroll
         for (int e = 0; e < V; ++e) {
-          float v = f[it][e] * rstd;
+          float v = RMS ? f[it][e] * rstd : fmaf(f[it][e], rstd, offset);
           if constexpr (HAS_G) v *= g[it][e];
           if constexpr (HAS_B && !RMS) v += b[e];
           f[it][e] = v;
