@@ -523,6 +523,23 @@ class Function:
         return self._wrap(self._L.b200_pad(self.builder.ctx, self._h(x, "Pad"), self._h(fill_value, "Pad"), _i64(before), _i64(after),
                                            len(axes_config), ctypes.byref(err)), err, "Pad")
 
+    def DynamicSlice(self, operand, start_indices: Sequence[Value], slice_sizes: Sequence[int]) -> Value:
+        """Slice at start indices given as scalar integer Values, one per axis (ref function.go:1571-1594)."""
+        err = _lib.B200Error()
+        hs = [self._h(v, "DynamicSlice: start index") for v in start_indices]
+        arr = (ctypes.c_void_p * max(len(hs), 1))(*hs)
+        return self._wrap(self._L.b200_dynamic_slice(self.builder.ctx, self._h(operand, "DynamicSlice"), arr, len(hs), _i64(slice_sizes),
+                                                     len(slice_sizes), ctypes.byref(err)), err, "DynamicSlice")
+
+    def DynamicUpdateSlice(self, operand, update, start_indices: Sequence[Value]) -> Value:
+        """operand with `update` written at the start indices (ref function.go:1596-1621)."""
+        err = _lib.B200Error()
+        hs = [self._h(v, "DynamicUpdateSlice: start index") for v in start_indices]
+        arr = (ctypes.c_void_p * max(len(hs), 1))(*hs)
+        return self._wrap(self._L.b200_dynamic_update_slice(self.builder.ctx, self._h(operand, "DynamicUpdateSlice"),
+                                                            self._h(update, "DynamicUpdateSlice"), arr, len(hs), ctypes.byref(err)),
+                          err, "DynamicUpdateSlice")
+
     def Where(self, condition, on_true, on_false) -> Value:
         err = _lib.B200Error()
         return self._wrap(self._L.b200_where(self.builder.ctx, self._h(condition, "Where"), self._h(on_true, "Where"), self._h(on_false, "Where"),

@@ -22,7 +22,7 @@ OPERATIONS = [
     "Equal", "NotEqual", "LessThan", "LessOrEqual", "GreaterThan", "GreaterOrEqual",
     "EqualTotalOrder", "NotEqualTotalOrder", "LessThanTotalOrder", "LessOrEqualTotalOrder", "GreaterThanTotalOrder",
     "GreaterOrEqualTotalOrder",
-    "Reshape", "Transpose", "ConvertDType", "BroadcastInDim", "Slice", "Concatenate", "Reverse", "Pad", "Where", "Clamp",
+    "Reshape", "Transpose", "ConvertDType", "BroadcastInDim", "Slice", "Concatenate", "Reverse", "Pad", "DynamicSlice", "DynamicUpdateSlice", "Where", "Clamp",
     "DotGeneral", "ReduceSum", "ReduceProduct", "ReduceMax", "ReduceMin", "ReduceLogicalAnd", "ReduceLogicalOr", "ArgMinMax",
     "Gather", "BatchNormForInference",
     "FusedSoftmax", "FusedGelu", "FusedLayerNorm", "FusedDense", "FusedAttentionQKVProjection",

@@ -152,7 +152,7 @@ enum class Op : int {
   // ternary
   Where, Clamp,
   // data movement
-  Cast, Reshape, Transpose, BroadcastInDim, Slice, Concatenate, Reverse, Pad,
+  Cast, Reshape, Transpose, BroadcastInDim, Slice, Concatenate, Reverse, Pad, DynamicSlice, DynamicUpdateSlice,
   // contraction / reduction / indexing
   DotGeneral, Reduce, ArgMinMax, Gather,
   // fused

@@ -24,7 +24,7 @@ const char* op_name(Op op) {
       "BitwiseAnd", "BitwiseOr", "BitwiseXor", "ShiftLeft", "ShiftRight", "ShiftRightLogical",
       "Equal", "NotEqual", "LessThan", "LessOrEqual", "GreaterThan", "GreaterOrEqual",
       "Where", "Clamp",
-      "Cast", "Reshape", "Transpose", "BroadcastInDim", "Slice", "Concatenate", "Reverse", "Pad",
+      "Cast", "Reshape", "Transpose", "BroadcastInDim", "Slice", "Concatenate", "Reverse", "Pad", "DynamicSlice", "DynamicUpdateSlice",
       "DotGeneral", "Reduce", "ArgMinMax", "Gather",
       "Softmax", "SoftmaxMasked", "LayerNorm", "RmsNorm", "Attention", "Rope"};
   static_assert(sizeof(names) / sizeof(names[0]) == (size_t)Op::kNumOps, "op_name table out of date");
@@ -430,6 +430,61 @@ B200Value b200_concatenate(B200Context ctx, const B200Value* tensors, int num_te
   Node* o = g.Add(Op::Concatenate, in[0]->dtype, dims, in);
   o->ia = {a};
   return ret(err, Status::OK(), o);
+}
+
+// ---- dynamic slices (ref function.go:1571-1621) ------------------------------------------------
+static Status dynamic_starts(B200Context ctx, const char* what, Node* operand, const B200Value* start_indices, int num_indices,
+                             std::vector<Node*>* starts) {
+  if (num_indices != operand->rank()) return Status::Invalid(strfmt("%s: %d start indices for an operand of rank %d", what, num_indices, operand->rank()));
+  if (operand->rank() > 8) return Status::Unsupported(strfmt("%s: more than 8 dims", what));
+  for (int i = 0; i < num_indices; ++i) {
+    Node* n;
+    B200_TRY(check_node(ctx, start_indices[i], what, &n));
+    if (n->num_elements() != 1 || !dtype_is_int(n->dtype)) return Status::Invalid(strfmt("%s: start index %d must be one integer value", what, i));
+    starts->push_back(n);
+  }
+  return Status::OK();
+}
+
+B200Value b200_dynamic_slice(B200Context ctx, B200Value operand, const B200Value* start_indices, int num_indices,
+                             const int64_t* slice_sizes, int rank, B200Error* err) {
+  clear_error(err);
+  Node* n;
+  Status s = check_node(ctx, operand, "DynamicSlice", &n);
+  if (!s.ok()) return ret(err, s, nullptr);
+  if (rank != n->rank() || (rank > 0 && !slice_sizes)) return ret(err, Status::Invalid("DynamicSlice: one slice size per axis"), nullptr);
+  std::vector<Node*> starts;
+  s = dynamic_starts(ctx, "DynamicSlice", n, start_indices, num_indices, &starts);
+  if (!s.ok()) return ret(err, s, nullptr);
+  std::vector<int64_t> dims(rank);
+  for (int i = 0; i < rank; ++i) {
+    if (slice_sizes[i] < 0 || slice_sizes[i] > n->dims[i])
+      return ret(err, Status::Invalid(strfmt("DynamicSlice: slice size %lld on axis %d exceeds dim %lld", (long long)slice_sizes[i], i, (long long)n->dims[i])), nullptr);
+    dims[i] = slice_sizes[i];
+  }
+  std::vector<Node*> in = {n};
+  in.insert(in.end(), starts.begin(), starts.end());
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  return ret(err, Status::OK(), g.Add(Op::DynamicSlice, n->dtype, dims, in));
+}
+
+B200Value b200_dynamic_update_slice(B200Context ctx, B200Value operand, B200Value update, const B200Value* start_indices,
+                                    int num_indices, B200Error* err) {
+  clear_error(err);
+  Node *n, *u;
+  Status s = check_node(ctx, operand, "DynamicUpdateSlice: operand", &n);
+  if (s.ok()) s = check_node(ctx, update, "DynamicUpdateSlice: update", &u);
+  if (!s.ok()) return ret(err, s, nullptr);
+  if (u->dtype != n->dtype || u->rank() != n->rank()) return ret(err, Status::Invalid("DynamicUpdateSlice: update differs from the operand in dtype or rank"), nullptr);
+  for (int i = 0; i < n->rank(); ++i)
+    if (u->dims[i] > n->dims[i]) return ret(err, Status::Invalid(strfmt("DynamicUpdateSlice: update dim %d (%lld) exceeds operand dim %lld", i, (long long)u->dims[i], (long long)n->dims[i])), nullptr);
+  std::vector<Node*> starts;
+  s = dynamic_starts(ctx, "DynamicUpdateSlice", n, start_indices, num_indices, &starts);
+  if (!s.ok()) return ret(err, s, nullptr);
+  std::vector<Node*> in = {n, u};
+  in.insert(in.end(), starts.begin(), starts.end());
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  return ret(err, Status::OK(), g.Add(Op::DynamicUpdateSlice, n->dtype, n->dims, in));
 }
 
 B200Value b200_reverse(B200Context ctx, B200Value x, const int* axes, int num_axes, B200Error* err) {

@@ -97,6 +97,23 @@ struct StridedCopyParams {
 Status strided_copy(Device* dev, const StridedCopyParams& p);
 // Batched 2-D transpose through shared memory: x[batch, rows, cols] -> y[batch, cols, rows].
 Status transpose_2d(Device* dev, const void* x, void* y, int64_t batch, int64_t rows, int64_t cols, int elt_size);
+// Slices whose start indices live in device memory (one integer scalar per axis, any integer dtype), clamped so the
+// block fits.  dynamic_slice: y[block dims] = x[start + idx].  dynamic_update_slice: y = x with the block `u` written at
+// start (one pass: every element of y comes from u or from x).
+struct DynSliceParams {
+  const void* x = nullptr;       // operand [x_dims]
+  const void* u = nullptr;       // update block [b_dims] (update only)
+  void* y = nullptr;
+  int elt_size = 4;
+  int rank = 0;
+  int64_t x_dims[kMaxDims] = {0};
+  int64_t b_dims[kMaxDims] = {0};  // slice sizes / update dims
+  const void* starts[kMaxDims] = {nullptr};
+  int start_dtypes[kMaxDims] = {0};
+};
+Status dynamic_slice(Device* dev, const DynSliceParams& p);
+Status dynamic_update_slice(Device* dev, const DynSliceParams& p);
+
 // Up to 8 contiguous arrays laid end to end into y with ONE launch (small concatenations are launch-bound: a fused QKV
 // projection joins three bias vectors per layer).  counts are in elements.
 constexpr int kMaxConcatFlat = 8;

@@ -145,6 +145,75 @@ __global__ void __launch_bounds__(256) unpad_rows_kernel(const E* __restrict__ s
   }
 }
 
+struct DynArgs {
+  const void* x;
+  const void* u;
+  void* y;
+  int rank;
+  int64_t x_dims[kMaxDims], b_dims[kMaxDims];
+  const void* starts[kMaxDims];
+  int start_dtypes[kMaxDims];
+};
+__device__ __forceinline__ int64_t load_index(const void* p, int dtype) {
+  switch (dtype) {
+    case B200_INT8: return *reinterpret_cast<const int8_t*>(p);
+    case B200_INT16: return *reinterpret_cast<const int16_t*>(p);
+    case B200_INT32: return *reinterpret_cast<const int32_t*>(p);
+    case B200_INT64: return *reinterpret_cast<const int64_t*>(p);
+    case B200_UINT8: return *reinterpret_cast<const uint8_t*>(p);
+    case B200_UINT16: return *reinterpret_cast<const uint16_t*>(p);
+    case B200_UINT32: return *reinterpret_cast<const uint32_t*>(p);
+    default: {
+      const uint64_t v = *reinterpret_cast<const uint64_t*>(p);
+      return v > (uint64_t)INT64_MAX ? INT64_MAX : (int64_t)v;
+    }
+  }
+}
+// Clamped start of the block on every axis, computed once per CTA.
+__device__ __forceinline__ void block_starts(const DynArgs& a, int64_t* start_sh) {
+  if (threadIdx.x < a.rank) {
+    const int d = threadIdx.x;
+    int64_t v = load_index(a.starts[d], a.start_dtypes[d]);
+    const int64_t hi = a.x_dims[d] - a.b_dims[d];
+    v = v < 0 ? 0 : (v > hi ? hi : v);
+    start_sh[d] = v;
+  }
+  __syncthreads();
+}
+template <typename E>
+__global__ void __launch_bounds__(256) dynamic_slice_kernel(const DynArgs a, int64_t total) {
+  __shared__ int64_t start[kMaxDims];
+  block_starts(a, start);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t rem = i, src = 0, stride = 1;
+    for (int d = a.rank - 1; d >= 0; --d) {
+      const int64_t c = rem % a.b_dims[d];
+      rem /= a.b_dims[d];
+      src += (c + start[d]) * stride;
+      stride *= a.x_dims[d];
+    }
+    reinterpret_cast<E*>(a.y)[i] = reinterpret_cast<const E*>(a.x)[src];
+  }
+}
+template <typename E>
+__global__ void __launch_bounds__(256) dynamic_update_slice_kernel(const DynArgs a, int64_t total) {
+  __shared__ int64_t start[kMaxDims];
+  block_starts(a, start);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t rem = i, usrc = 0, ustride = 1;
+    bool inside = true;
+    for (int d = a.rank - 1; d >= 0; --d) {
+      const int64_t c = rem % a.x_dims[d];
+      rem /= a.x_dims[d];
+      const int64_t r = c - start[d];
+      inside = inside && r >= 0 && r < a.b_dims[d];
+      usrc += r * ustride;
+      ustride *= a.b_dims[d];
+    }
+    reinterpret_cast<E*>(a.y)[i] = inside ? reinterpret_cast<const E*>(a.u)[usrc] : reinterpret_cast<const E*>(a.x)[i];
+  }
+}
+
 struct ConcatFlatArgs {
   const void* src[kMaxConcatFlat];
   int64_t end[kMaxConcatFlat];   // running element count after each operand
@@ -223,6 +292,40 @@ Status strided_copy(Device* dev, const StridedCopyParams& p) {
   }
   return dev->CheckLaunch("strided_copy");
 }
+
+static Status dyn_launch(Device* dev, const DynSliceParams& p, bool update) {
+  if (p.rank < 0 || p.rank > kMaxDims) return Status::Invalid("dynamic slice: rank");
+  DynArgs a;
+  a.x = p.x; a.u = p.u; a.y = p.y; a.rank = p.rank;
+  int64_t total = 1;
+  for (int d = 0; d < kMaxDims; ++d) {
+    a.x_dims[d] = d < p.rank ? p.x_dims[d] : 1;
+    a.b_dims[d] = d < p.rank ? p.b_dims[d] : 1;
+    a.starts[d] = d < p.rank ? p.starts[d] : nullptr;
+    a.start_dtypes[d] = d < p.rank ? p.start_dtypes[d] : B200_INT32;
+    if (d < p.rank) total *= update ? p.x_dims[d] : p.b_dims[d];
+  }
+  if (total == 0) return Status::OK();
+  B200_TRY(dev->MakeCurrent());
+  const unsigned grid = grid_for(dev, total);
+  cudaStream_t s = dev->stream();
+#define B200_DYN(E)                                                              \
+  do {                                                                           \
+    if (update) dynamic_update_slice_kernel<E><<<grid, 256, 0, s>>>(a, total);   \
+    else dynamic_slice_kernel<E><<<grid, 256, 0, s>>>(a, total);                 \
+  } while (0)
+  switch (p.elt_size) {
+    case 1: B200_DYN(uint8_t); break;
+    case 2: B200_DYN(uint16_t); break;
+    case 4: B200_DYN(uint32_t); break;
+    case 8: B200_DYN(uint64_t); break;
+    default: return Status::Invalid("dynamic slice: element size");
+  }
+#undef B200_DYN
+  return dev->CheckLaunch(update ? "dynamic_update_slice" : "dynamic_slice");
+}
+Status dynamic_slice(Device* dev, const DynSliceParams& p) { return dyn_launch(dev, p, false); }
+Status dynamic_update_slice(Device* dev, const DynSliceParams& p) { return dyn_launch(dev, p, true); }
 
 Status concat_flat(Device* dev, const void* const* src, const int64_t* counts, int n, void* y, int elt_size) {
   if (n < 1 || n > kMaxConcatFlat) return Status::Invalid("concat_flat: 1 to 8 operands");

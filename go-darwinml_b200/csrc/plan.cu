@@ -282,6 +282,7 @@ class Planner {
       case Op::Rope: return EmitRope(x);
       case Op::Concatenate: return EmitConcatenate(x);
       case Op::Pad: return EmitPad(x);
+      case Op::DynamicSlice: case Op::DynamicUpdateSlice: return EmitDynamicSlice(x);
       case Op::Transpose: case Op::Slice: case Op::Reverse: case Op::BroadcastInDim:
         if (ViewBase(x->in[0])->op == Op::Parameter || slot_of_[ViewBase(x->in[0])->id] >= 0 || !Fusible(ViewBase(x->in[0])) ||
             IsView(x->in[0]))
@@ -801,6 +802,45 @@ class Planner {
       }
       pos += in->dims[ax];
     }
+    return Status::OK();
+  }
+
+  // DynamicSlice (inputs: operand, starts...) and DynamicUpdateSlice (operand, update, starts...): the start scalars are
+  // read on the device, so the launch plan stays static.
+  Status EmitDynamicSlice(Node* x) {
+    const bool update = x->op == Op::DynamicUpdateSlice;
+    Node* operand = x->in[0];
+    Node* upd = update ? x->in[1] : nullptr;
+    const size_t first = update ? 2 : 1;
+    B200_TRY(EnsureMaterialized(operand));
+    if (upd) B200_TRY(EnsureMaterialized(upd));
+    for (size_t i = first; i < x->in.size(); ++i) B200_TRY(EnsureMaterialized(x->in[i]));
+    k::DynSliceParams dp;
+    dp.elt_size = dtype_size(x->dtype);
+    dp.rank = operand->rank();
+    for (int d = 0; d < dp.rank; ++d) {
+      dp.x_dims[d] = operand->dims[d];
+      dp.b_dims[d] = update ? upd->dims[d] : x->dims[d];
+      dp.start_dtypes[d] = x->in[first + d]->dtype;
+    }
+    std::vector<int> start_slots;
+    for (size_t i = first; i < x->in.size(); ++i) start_slots.push_back(SlotOf(x->in[i]));
+    const int x_slot = SlotOf(operand), u_slot = upd ? SlotOf(upd) : -1, out_slot = NewValueSlot(x);
+    Step st;
+    st.desc = strfmt("move[%s rank=%d]", update ? "DynamicUpdateSlice" : "DynamicSlice", dp.rank);
+    st.reads = start_slots;
+    st.reads.push_back(x_slot);
+    if (upd) st.reads.push_back(u_slot);
+    st.writes = {out_slot};
+    st.run = [dp, start_slots, x_slot, u_slot, out_slot, update](Device* dev, void* const* p) -> Status {
+      k::DynSliceParams q = dp;
+      q.x = p[x_slot];
+      q.u = u_slot >= 0 ? p[u_slot] : nullptr;
+      q.y = p[out_slot];
+      for (size_t i = 0; i < start_slots.size(); ++i) q.starts[i] = p[start_slots[i]];
+      return update ? k::dynamic_update_slice(dev, q) : k::dynamic_slice(dev, q);
+    };
+    ex_->steps.push_back(std::move(st));
     return Status::OK();
   }
 

@@ -187,6 +187,16 @@ B200Value b200_concatenate(B200Context ctx, const B200Value* tensors, int num_te
 B200Value b200_reverse(B200Context ctx, B200Value x, const int* axes, int num_axes, B200Error* err);
 B200Value b200_pad(B200Context ctx, B200Value x, B200Value pad_value, const int64_t* pad_before,
                    const int64_t* pad_after, int rank, B200Error* err);
+/* Slice whose start indices are scalar integer VALUES of the graph, one per axis (ref function.go:1571-1594;
+ * bridge.m:918-984 builds it from per-axis gathers).  Out-of-range starts are clamped so that the slice fits, as
+ * GoMLX documents for DynamicSlice; the reference bridge does not clamp (its gather reads whatever MPSGraph returns
+ * for an out-of-range index), so parity is defined for in-range starts. */
+B200Value b200_dynamic_slice(B200Context ctx, B200Value operand, const B200Value* start_indices, int num_indices,
+                             const int64_t* slice_sizes, int rank, B200Error* err);
+/* operand with the block `update` written at the (clamped) start indices (ref function.go:1596-1621;
+ * bridge.m:986-1108 builds it from a mask, per-axis gathers and a select: three passes over the operand). */
+B200Value b200_dynamic_update_slice(B200Context ctx, B200Value operand, B200Value update, const B200Value* start_indices,
+                                    int num_indices, B200Error* err);
 
 /* ---- selection (ref bridge.h:133-136) ---------------------------------- */
 B200Value b200_where(B200Context ctx, B200Value cond, B200Value on_true, B200Value on_false, B200Error* err);

@@ -282,6 +282,34 @@ class OracleFunction:
         pads = [(c[0], c[1]) for c in axes_config]
         return np.pad(x, pads, mode="constant", constant_values=np.asarray(fill_value).reshape(-1)[0])
 
+    @staticmethod
+    def _clamped_starts(what, operand, starts, sizes):
+        if len(starts) != operand.ndim:
+            raise OracleError(f"{what}: one start index per axis")
+        out = []
+        for d, (s, n) in enumerate(zip(starts, sizes)):
+            s = np.asarray(s)
+            if s.size != 1 or s.dtype.kind not in "iu":
+                raise OracleError(f"{what}: start index {d} must be one integer value")
+            out.append(int(min(max(int(s.reshape(-1)[0]), 0), operand.shape[d] - n)))
+        return out
+
+    def DynamicSlice(self, operand, start_indices, slice_sizes):
+        # ref function.go:1571-1594; starts clamped so the slice fits (GoMLX's documented DynamicSlice)
+        if len(slice_sizes) != operand.ndim or any(n < 0 or n > d for n, d in zip(slice_sizes, operand.shape)):
+            raise OracleError("DynamicSlice: slice sizes")
+        st = self._clamped_starts("DynamicSlice", operand, start_indices, slice_sizes)
+        return np.ascontiguousarray(operand[tuple(slice(s, s + n) for s, n in zip(st, slice_sizes))])
+
+    def DynamicUpdateSlice(self, operand, update, start_indices):
+        # ref function.go:1596-1621
+        if update.dtype != operand.dtype or update.ndim != operand.ndim or any(u > d for u, d in zip(update.shape, operand.shape)):
+            raise OracleError("DynamicUpdateSlice: update shape or dtype")
+        st = self._clamped_starts("DynamicUpdateSlice", operand, start_indices, update.shape)
+        out = operand.copy()
+        out[tuple(slice(s, s + n) for s, n in zip(st, update.shape))] = update
+        return out
+
     def Where(self, cond, on_true, on_false):
         if cond.dtype != np.bool_ or on_true.dtype != on_false.dtype:
             raise OracleError("Where: dtypes")

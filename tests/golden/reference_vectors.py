@@ -135,6 +135,13 @@ CASES = [
     Case("Pad", "mpsgraph/gomlx/mpsgraph_test.go:877-938", [_a([1, 2, 3, 4], shape=(2, 2))],
          lambda f, x: f.Pad(x, f.Reshape(f.Constant(np.array([0], dtype=np.float32), 1)), (1, 0), (0, 1)),
          _a([0, 0, 0, 1, 2, 0, 3, 4, 0], shape=(3, 3)), tol=0),
+    Case("DynamicSlice [2,2] at (1,1)", "mpsgraph/gomlx/mpsgraph_test.go:993-1061",
+         [_a(range(1, 13), shape=(3, 4)), _a([1], I32, ()), _a([1], I32, ())],
+         lambda f, x, s0, s1: f.DynamicSlice(x, [s0, s1], [2, 2]), _a([6, 7, 10, 11], shape=(2, 2)), tol=0),
+    Case("DynamicUpdateSlice [2,2] at (1,1)", "mpsgraph/gomlx/mpsgraph_test.go:1064-1130",
+         [_a(range(1, 13), shape=(3, 4)), _a([100, 200, 300, 400], shape=(2, 2)), _a([1], I32, ()), _a([1], I32, ())],
+         lambda f, x, u, s0, s1: f.DynamicUpdateSlice(x, u, [s0, s1]),
+         _a([1, 2, 3, 4, 5, 100, 200, 8, 9, 300, 400, 12], shape=(3, 4)), tol=0),
     Case("ArgMax axis 1 Int32", "mpsgraph/gomlx/mpsgraph_test.go:941-991", [_a([1, 5, 3, 8, 2, 6], shape=(2, 3))],
          lambda f, x: f.ArgMinMax(x, 1, C_I32, False), _a([1, 0], I32), tol=0),
     Case("FusedSoftmax axis 1", "mpsgraph/gomlx/mpsgraph_test.go:1133-1190", [_a([1, 2, 3, 1, 1, 1], shape=(2, 3))],

@@ -816,3 +816,63 @@ def test_small_concatenation_is_one_launch(b200, backend):
     np.testing.assert_array_equal(got.view(np.uint16), np.concatenate(parts).view(np.uint16))
     ints = [rng_array(rng, (1, 3, 7), np.int64), rng_array(rng, (1, 2, 7), np.int64)]
     assert_parity(b200, backend, lambda f, a, b: f.Concatenate(1, a, b), ints)
+
+
+# ---- DynamicSlice / DynamicUpdateSlice (ref function.go:1571-1621): start indices are values of the graph ----------
+@pytest.mark.parametrize("dtype", [np.float32, BF16, np.int64, np.uint8], ids=["f32", "bf16", "i64", "u8"])
+def test_dynamic_slice_and_update_exact(b200, backend, dtype):
+    rng = np.random.default_rng(101)
+    x = rng_array(rng, (5, 7, 33), dtype)
+    u = rng_array(rng, (2, 7, 9), dtype)
+    for starts in ([1, 0, 5], [3, 0, 24], [0, 0, 0]):
+        s = [np.array(v, dtype=np.int32) for v in starts]
+        assert_parity(b200, backend, lambda f, a, s0, s1, s2: f.DynamicSlice(a, [s0, s1, s2], [2, 7, 9]), [x] + s, rtol=0.0)
+        assert_parity(b200, backend, lambda f, a, b, s0, s1, s2: f.DynamicUpdateSlice(a, b, [s0, s1, s2]), [x, u] + s, rtol=0.0)
+
+
+def test_dynamic_slice_clamps_and_takes_computed_indices(b200, backend):
+    # out-of-range starts are clamped so the block fits; an index may be any integer dtype and the result of other ops
+    rng = np.random.default_rng(102)
+    x = rng_array(rng, (6, 10), np.float32)
+    u = rng_array(rng, (4, 3), np.float32)
+    s0, s1 = np.array(-3, dtype=np.int64), np.array(200, dtype=np.uint8)
+
+    def build(f, a, b, i, j):
+        jj = f.Add(j, f.Constant(np.array([1], dtype=np.uint8)))           # 201: far past the end
+        return [f.DynamicSlice(a, [i, jj], [4, 3]), f.DynamicUpdateSlice(a, b, [i, jj])]
+
+    got = assert_parity(b200, backend, build, [x, u, s0, s1], rtol=0.0)
+    np.testing.assert_array_equal(got[0], x[0:4, 7:10])
+    want = x.copy()
+    want[0:4, 7:10] = u
+    np.testing.assert_array_equal(got[1], want)
+
+
+def test_dynamic_slice_kv_cache_step(b200, backend):
+    # the use the op exists for: write one position of a [B, S, H, D] cache and read a window back
+    rng = np.random.default_rng(103)
+    cache, new = rng_array(rng, (2, 64, 4, 16), BF16), rng_array(rng, (2, 1, 4, 16), BF16)
+    pos, zero = np.array(37, dtype=np.int32), np.array(0, dtype=np.int32)
+
+    def build(f, c, n, p, z):
+        c2 = f.DynamicUpdateSlice(c, n, [z, p, z, z])
+        return [c2, f.DynamicSlice(c2, [z, p, z, z], [2, 1, 4, 16])]
+
+    got = assert_parity(b200, backend, build, [cache, new, pos, zero], rtol=0.0)
+    np.testing.assert_array_equal(got[1].view(np.uint16), new.view(np.uint16))
+
+
+def test_dynamic_slice_argument_checks(b200, backend):
+    builder = backend.Builder("dyn_err")
+    f = builder.Main()
+    x = f.Parameter("x", b200.shapes.Make(b200.dtypes.Float32, 3, 4))
+    i = f.Parameter("i", b200.shapes.Make(b200.dtypes.Int32))
+    fl = f.Parameter("fl", b200.shapes.Make(b200.dtypes.Float32))
+    with pytest.raises(b200.BackendError, match="start indices"):
+        f.DynamicSlice(x, [i], [2, 2])
+    with pytest.raises(b200.BackendError, match="integer"):
+        f.DynamicSlice(x, [i, fl], [2, 2])
+    with pytest.raises(b200.BackendError, match="exceeds"):
+        f.DynamicSlice(x, [i, i], [2, 5])
+    with pytest.raises(b200.BackendError, match="exceeds"):
+        f.DynamicUpdateSlice(x, f.Parameter("u", b200.shapes.Make(b200.dtypes.Float32, 4, 4)), [i, i])
