@@ -23,6 +23,7 @@
 #include <algorithm>
 #include <array>
 #include <cmath>
+#include <cstdlib>
 #include <functional>
 #include <sstream>
 #include <unordered_map>
@@ -52,7 +53,15 @@ struct Step {
   std::string desc;
   std::vector<int> reads, writes;
   int launches = 1;
+  bool capturable = true;   // false when run() allocates or frees device memory (its pointers would be stale in a replay)
   std::function<Status(Device*, void* const*)> run;  // ptrs indexed by slot
+};
+
+// One instantiated CUDA graph of a whole launch plan, valid for one set of input / output addresses.
+struct PlanGraph {
+  std::vector<void*> key;
+  cudaGraphExec_t exec = nullptr;
+  uint64_t last_used = 0;
 };
 
 struct OutputDesc {
@@ -73,7 +82,16 @@ struct Exec {
   int64_t arena_bytes = 0;
   int num_launches = 0;
   std::mutex mu;
+  // Launch-bound plans replay as one CUDA graph: the second time a plan runs on the same input and output addresses
+  // (a serving loop that frees its outputs gets the same blocks back from the caching allocator) its steps are
+  // captured from the stream instead of launched, and later calls with those addresses are one cudaGraphLaunch.
+  bool capturable = false;
+  std::vector<PlanGraph> graphs;
+  std::vector<void*> last_key;
+  uint64_t tick = 0;
   ~Exec() {
+    for (auto& g : graphs)
+      if (g.exec) cudaGraphExecDestroy(g.exec);
     if (dev) {
       for (void* p : const_ptrs) dev->Free(p);
       dev->Free(arena);
@@ -1024,6 +1042,7 @@ class Planner {
     if (bias) st.reads.push_back(bias_slot);
     if (residual) st.reads.push_back(res_slot);
     st.writes = {gemm_out};
+    st.capturable = x->dtype != B200_FLOAT32;   // the fp32 path allocates its bf16 planes per launch
     st.run = [gp, a_slot, b_slot, bias_slot, res_slot, gemm_out](Device* dev, void* const* p) -> Status {
       k::GemmParams q = gp;
       q.a = p[a_slot];
@@ -1625,6 +1644,12 @@ B200Exec b200_compile(B200Context ctx, const B200Value* feeds, int num_feeds, co
   Planner planner(c, ex.get());
   Status s = planner.Run(f, t);
   if (s.ok() && ex->arena_bytes > 0) s = ex->dev->Alloc(ex->arena_bytes, &ex->arena);
+  {
+    static const bool graphs_on = []() { const char* v = getenv("B200MLX_GRAPHS"); return !(v && v[0] == '0'); }();
+    bool all = graphs_on && ex->steps.size() >= 4;
+    for (const Step& st : ex->steps) all = all && st.capturable;
+    ex->capturable = all;
+  }
   if (!s.ok()) { set_error(err, s); return nullptr; }
   return ex.release();
 }
@@ -1736,6 +1761,62 @@ static bool execute_impl(B200Exec exec, const B200Buffer* inputs, int num_inputs
     const Slot& sl = ex->slots[s];
     if (sl.kind == SlotKind::Arena) ptrs[s] = (char*)ex->arena + sl.offset;
     else if (sl.kind == SlotKind::Const) ptrs[s] = ex->const_ptrs[sl.index];
+  }
+  if (!step_ms && ex->capturable) {
+    std::vector<void*> key;
+    for (int i = 0; i < num_inputs; ++i) key.push_back(reinterpret_cast<Buffer*>(inputs[i])->ptr);
+    for (Buffer* b : outs) key.push_back(b->ptr);
+    cudaStream_t stream = ex->dev->stream();
+    PlanGraph* hit = nullptr;
+    for (auto& g : ex->graphs)
+      if (g.key == key) hit = &g;
+    Status gs = ex->dev->MakeCurrent();
+    if (!gs.ok()) return fail(gs);
+    if (!hit && key == ex->last_key) {
+      // second run on these addresses: record the plan instead of launching it
+      cudaGraph_t graph = nullptr;
+      cudaError_t ce = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal);
+      if (ce == cudaSuccess) {
+        Status rs = Status::OK();
+        for (auto& st : ex->steps) {
+          rs = st.run(ex->dev, ptrs.data());
+          if (!rs.ok()) { rs = Status{rs.code, st.desc + ": " + rs.msg}; break; }
+        }
+        ce = cudaStreamEndCapture(stream, &graph);
+        if (!rs.ok() && ce == cudaSuccess) ce = cudaErrorStreamCaptureInvalidated;   // a step refused to record: plain path below
+        cudaGraphExec_t gexec = nullptr;
+        if (ce == cudaSuccess) ce = cudaGraphInstantiate(&gexec, graph, 0);
+        if (graph) cudaGraphDestroy(graph);
+        if (ce == cudaSuccess) {
+          if (ex->graphs.size() >= 4) {   // keep the four most recently used address sets
+            size_t lru = 0;
+            for (size_t i = 1; i < ex->graphs.size(); ++i)
+              if (ex->graphs[i].last_used < ex->graphs[lru].last_used) lru = i;
+            cudaGraphExecDestroy(ex->graphs[lru].exec);
+            ex->graphs.erase(ex->graphs.begin() + (long)lru);
+          }
+          ex->graphs.push_back(PlanGraph{key, gexec, 0});
+          hit = &ex->graphs.back();
+        }
+      }
+      if (!hit) {
+        cudaGetLastError();
+        ex->capturable = false;   // this plan does not record cleanly; nothing was launched: the plain path below runs it
+                                  // now (and reports a real error if there is one) and on every later call
+      }
+    }
+    if (hit) {
+      hit->last_used = ++ex->tick;
+      ex->dev->kernel_error_flag();   // a replayed kernel can raise the error word too: have the next sync point read it
+      cudaError_t ce = cudaGraphLaunch(hit->exec, stream);
+      if (ce != cudaSuccess) {
+        cudaGetLastError();
+        return fail(Status::Cuda(strfmt("Execute: graph launch failed: %s", cudaGetErrorString(ce))));
+      }
+      for (int i = 0; i < num_outputs; ++i) outputs[i] = outs[i];
+      return true;
+    }
+    ex->last_key = key;
   }
   std::vector<cudaEvent_t> events;
   if (step_ms) {

@@ -876,3 +876,43 @@ def test_dynamic_slice_argument_checks(b200, backend):
         f.DynamicSlice(x, [i, i], [2, 5])
     with pytest.raises(b200.BackendError, match="exceeds"):
         f.DynamicUpdateSlice(x, f.Parameter("u", b200.shapes.Make(b200.dtypes.Float32, 4, 4)), [i, i])
+
+
+def test_repeated_execution_replays_a_cuda_graph(b200, backend):
+    # a plan run again on the same addresses is recorded once and replayed; results must not change, and new input
+    # CONTENT at the same address must be picked up
+    rng = np.random.default_rng(104)
+    x, w, g = rng_array(rng, (64, 256), BF16), rng_array(rng, (256, 128), BF16, 0.1), rng_array(rng, (256,), BF16)
+    builder = backend.Builder("graph_replay")
+    f = builder.Main()
+    px = f.Parameter("x", _S(b200, BF16, 64, 256))
+    pw = f.Parameter("w", _S(b200, BF16, 256, 128))
+    pg = f.Parameter("g", _S(b200, BF16, 256))
+    h = f.FusedRMSNorm(px, [-1], 1e-6, pg)
+    y = f.FusedSoftmax(f.FusedDense(h, pw, None, 1), 1)
+    z = f.ReduceSum(f.Tanh(y), 1)
+    f.Return([y, z, f.ArgMinMax(y, 1, b200.dtypes.Int32, False)], None)
+    exe = builder.Compile()
+    assert exe.NumLaunches() >= 4
+    bx, bw, bg = backend.FromNumpy(x), backend.FromNumpy(w), backend.FromNumpy(g)
+    first = None
+    for it in range(6):
+        outs = exe.Execute([bx, bw, bg], None, 0)
+        vals = [backend.ToNumpy(o) for o in outs]
+        for o in outs:
+            backend.BufferFinalize(o)           # the allocator hands the same blocks back: same addresses next time
+        if first is None:
+            first = vals
+        for a, b_ in zip(vals, first):
+            np.testing.assert_array_equal(a, b_)
+    # same addresses, new content
+    x2 = rng_array(rng, (64, 256), BF16)
+    backend.BufferFinalize(bx)
+    bx = backend.FromNumpy(x2)
+    outs = exe.Execute([bx, bw, bg], None, 0)
+    got = [backend.ToNumpy(o) for o in outs]
+    want = run_oracle(lambda ff, a, b_, c: (lambda hh: (lambda yy: [yy, ff.ReduceSum(ff.Tanh(yy), 1), ff.ArgMinMax(yy, 1, b200.dtypes.Int32, False)])(
+        ff.FusedSoftmax(ff.FusedDense(hh, b_, None, 1), 1)))(ff.FusedRMSNorm(a, [-1], 1e-6, c)), [x2, w, g])
+    ok, viol = compare(got[0], want[0], BF16_RTOL, 1.0)
+    assert ok, viol
+    assert not np.array_equal(got[0], first[0])
