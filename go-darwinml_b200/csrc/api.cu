@@ -129,11 +129,64 @@ B200Buffer b200_buffer_copy_to_device(B200Buffer buf, int device, B200Error* err
 void b200_buffer_free(B200Buffer buf) {
   Buffer* b = reinterpret_cast<Buffer*>(buf);
   if (!b) return;
-  if (b->owned && b->ptr) {
+  if (b->ipc && b->ptr) {
+    Device* dev;
+    if (Device::Get(b->device, &dev).ok() && dev->MakeCurrent().ok()) cudaIpcCloseMemHandle(b->ptr);
+  } else if (b->owned && b->ptr) {
     Device* dev;
     if (Device::Get(b->device, &dev).ok()) dev->Free(b->ptr);
   }
   delete b;
+}
+
+static_assert(sizeof(cudaIpcMemHandle_t) == B200_IPC_HANDLE_BYTES, "IPC handle size");
+
+bool b200_buffer_ipc_export(B200Buffer buf, void* handle_out, B200Error* err) {
+  clear_error(err);
+  Buffer* b = reinterpret_cast<Buffer*>(buf);
+  if (!b || !b->ptr || !handle_out) { set_error(err, Status::Invalid("ipc_export: null buffer or handle")); return false; }
+  if (!b->owned || b->ipc) { set_error(err, Status::Invalid("ipc_export: only a buffer this process allocated can be exported")); return false; }
+  Device* dev;
+  Status s = Device::Get(b->device, &dev);
+  if (s.ok()) s = dev->MakeCurrent();
+  if (!s.ok()) { set_error(err, s); return false; }
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, b->ptr);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    set_error(err, Status::Cuda(strfmt("cudaIpcGetMemHandle: %s", cudaGetErrorString(e))));
+    return false;
+  }
+  memcpy(handle_out, &h, sizeof(h));
+  return true;
+}
+
+B200Buffer b200_buffer_ipc_import(int device, const void* handle, int dtype, const int64_t* shape, int rank, B200Error* err) {
+  clear_error(err);
+  if (!handle || !dtype_valid(dtype) || rank < 0 || rank > 16 || (rank > 0 && !shape)) { set_error(err, Status::Invalid("ipc_import: bad handle, dtype or shape")); return nullptr; }
+  Device* dev;
+  Status s = Device::Get(device, &dev);
+  if (s.ok()) s = dev->MakeCurrent();
+  if (!s.ok()) { set_error(err, s); return nullptr; }
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    set_error(err, Status::Cuda(strfmt("cudaIpcOpenMemHandle: %s", cudaGetErrorString(e))));
+    return nullptr;
+  }
+  Buffer* b = new Buffer();
+  b->device = device;
+  b->dtype = dtype;
+  int64_t n = 1;
+  for (int i = 0; i < rank; ++i) { b->dims.push_back(shape[i]); n *= shape[i]; }
+  b->nbytes = n * dtype_size(dtype);
+  b->ptr = p;
+  b->owned = false;
+  b->ipc = true;
+  return b;
 }
 
 int b200_buffer_dtype(B200Buffer buf) { return buf ? reinterpret_cast<Buffer*>(buf)->dtype : -1; }
@@ -285,6 +338,39 @@ bool b200_k_gemm(int device, const void* a, const void* b, void* c, int64_t batc
     p.a = a; p.b = b; p.c = c; p.batch = batch; p.m = m; p.n = n; p.k = k_;
     p.a_k_major = a_k_major != 0; p.b_k_major = b_k_major != 0; p.dtype = dtype; p.bias = bias; p.activation = activation;
     s = k::gemm(dev, p);
+  }
+  if (!s.ok()) { set_error(err, s); return false; }
+  return true;
+}
+
+bool b200_k_gemm_allgather(int device, const void* a, const void* b, void* const* c_all, int num_ranks, int rank, int64_t m,
+                           int64_t n_local, int64_t k_, int a_k_major, int b_k_major, int dtype, B200Error* err) {
+  clear_error(err);
+  Device* dev;
+  Status s = Device::Get(device, &dev);
+  if (s.ok() && (num_ranks < 1 || num_ranks > 1 + k::GemmParams::kMaxExtraC || rank < 0 || rank >= num_ranks || !c_all))
+    s = Status::Invalid("gemm_allgather: 1 to 8 ranks, rank inside");
+  if (s.ok() && !(dtype == B200_BFLOAT16 || dtype == B200_FLOAT16)) s = Status::Unsupported("gemm_allgather: BF16 or F16");
+  if (s.ok() && (n_local % 8 != 0 || m <= 0 || n_local <= 0 || k_ <= 0)) s = Status::Invalid("gemm_allgather: n_local must be a positive multiple of 8");
+  if (s.ok()) {
+    const int64_t es = dtype_size(dtype);
+    k::GemmParams p;
+    p.a = a; p.b = b;
+    p.batch = 1; p.m = m; p.n = n_local; p.k = k_;
+    p.a_k_major = a_k_major != 0; p.b_k_major = b_k_major != 0;
+    p.dtype = dtype;
+    p.ldc = n_local * num_ranks;
+    const int64_t col_bytes = (int64_t)rank * n_local * es;
+    for (int r = 0; r < num_ranks && s.ok(); ++r)
+      if (!c_all[r]) s = Status::Invalid("gemm_allgather: null destination");
+    if (s.ok()) {
+      p.c = (char*)c_all[rank] + col_bytes;
+      for (int r = 0; r < num_ranks; ++r)
+        if (r != rank) p.c_extra[p.num_c_extra++] = (char*)c_all[r] + col_bytes;
+      bool taken = false;
+      s = k::gemm_tcgen05(dev, p, &taken);
+      if (s.ok() && !taken) s = Status::Unsupported("gemm_allgather: shape or alignment outside the tensor-core kernel (K and the operands' contiguous extents must be multiples of 8, 16-byte aligned)");
+    }
   }
   if (!s.ok()) { set_error(err, s); return false; }
   return true;

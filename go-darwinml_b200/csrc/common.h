@@ -129,6 +129,7 @@ struct Buffer {
   void* ptr = nullptr;
   int64_t nbytes = 0;
   bool owned = true;
+  bool ipc = false;   // mapped from another process: unmapped, not freed
   int64_t num_elements() const {
     int64_t n = 1;
     for (auto d : dims) n *= d;

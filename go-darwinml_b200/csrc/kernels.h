@@ -181,10 +181,17 @@ struct GemmParams {
   // Row pitch of C (and of the residual) in elements; 0 = n.  A pitch rounded up to 16 bytes lets a ragged N use the
   // vector epilogue: the columns between n and the pitch are written with don't-care values.
   int64_t ldc = 0;
+  // Further copies of C (same pitch and shape): the epilogue stores every tile to each of them as well.  They may be
+  // peer-device memory; only the tensor-core kernels honour them and only with vector stores (gemm_tcgen05 refuses otherwise).
+  static constexpr int kMaxExtraC = 7;
+  void* c_extra[kMaxExtraC] = {nullptr};
+  int num_c_extra = 0;
   // batch strides in elements; 0 on an operand broadcasts it over the batch
   int64_t a_batch_stride = -1, b_batch_stride = -1;  // -1 = dense (m*k, k*n)
 };
 Status gemm(Device* dev, const GemmParams& p);
+// The tensor-core path alone: *taken is false (and nothing is launched) when the problem is outside its rules.
+Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken);
 
 // ------------------------------------------------------------------ rope ---
 // y[r, j] = round(round(x[r, j] * c[r, j]) + round(x[r, j ^ half] * s[r, j])) over rows of `cols` elements made of heads of

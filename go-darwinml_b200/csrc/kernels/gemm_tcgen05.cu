@@ -71,6 +71,8 @@ struct TcArgs {
   void* c;
   const void* bias;
   const void* residual;   // same shape as C, or null
+  void* c_extra[GemmParams::kMaxExtraC];   // further copies of C (other ranks' buffers), same pitch
+  int num_c_extra;
   int residual_mul;       // combine by * instead of +
   int64_t M, N, K, ldc;
   int batch;
@@ -248,7 +250,11 @@ __device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem
               q.z = add_residual_word<OutT>(q.z, rq.z, g.residual_mul);
               q.w = add_residual_word<OutT>(q.w, rq.w, g.residual_mul);
             }
-            *reinterpret_cast<uint4*>(cbase + (int64_t)rr * g.ldc + col) = q;
+            const int64_t off = (int64_t)rr * g.ldc + col;
+            *reinterpret_cast<uint4*>(cbase + off) = q;
+            // the same vector to every other rank's copy: plain stores to peer-mapped memory (NVLink)
+            for (int x = 0; x < g.num_c_extra; ++x)
+              *reinterpret_cast<uint4*>(reinterpret_cast<OutT*>(g.c_extra[x]) + ((int64_t)b * g.M + row_base) * g.ldc + off) = q;
           }
         }
       } else {
@@ -744,6 +750,8 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
 
   TcArgs g;
   g.c = p.c; g.bias = p.bias; g.residual = p.residual; g.residual_mul = p.residual_op;
+  g.num_c_extra = p.num_c_extra;
+  for (int x = 0; x < GemmParams::kMaxExtraC; ++x) g.c_extra[x] = x < p.num_c_extra ? p.c_extra[x] : nullptr;
   g.M = p.m; g.N = p.n; g.K = p.k; g.ldc = p.ldc > 0 ? p.ldc : p.n;
   g.batch = (int)p.batch;
   g.a_kmajor = p.a_k_major ? 1 : 0; g.b_kmajor = p.b_k_major ? 1 : 0;
@@ -758,6 +766,11 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
   g.segs = is32 ? 6 : 1;
   const int out_vec = is32 ? 4 : 8;
   g.vec_store = (g.ldc % out_vec == 0 && g.ldc >= (p.n + out_vec - 1) / out_vec * out_vec && aligned16(p.c) && aligned16(p.residual)) ? 1 : 0;
+  if (p.num_c_extra > 0) {
+    bool ok = g.vec_store != 0 && !is32;
+    for (int x = 0; x < p.num_c_extra; ++x) ok = ok && aligned16(p.c_extra[x]);
+    if (!ok) { cleanup(); return Status::Unsupported("gemm: extra destinations need 16-byte aligned rows and a 16-bit type"); }
+  }
   g.err_flag = dev->kernel_error_flag();
 
   cudaError_t e = cudaSuccess;

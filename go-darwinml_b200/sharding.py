@@ -104,3 +104,100 @@ class BatchShardedRunner:
         for backend, builder, exe in self.replicas:
             exe.Finalize()
             builder.Finalize()
+
+
+class ColumnShardedMatmul:
+    """The one exchange step this path may have: a weight too wide for one GPU is split by columns, every rank
+    multiplies the (replicated) activations by its column block, and every rank needs the full result.
+
+    The usual form is GEMM then all-gather.  Here the all-gather is inside the GEMM: each rank's result buffer
+    C [m, world * n_local] is exported once to the other ranks of the host (`b200_buffer_ipc_export` / `_import`),
+    and `b200_k_gemm_allgather`'s epilogue stores every tile of the local [m, n_local] slab into ALL ranks' buffers,
+    its own and the peers' (plain stores over NVLink), while later tiles are still being multiplied.  After the
+    kernel each rank synchronises its stream and the ranks meet at a host barrier; nothing else is exchanged.
+
+    `exchange(obj) -> list` must return every rank's `obj` in rank order (torch.distributed.all_gather_object does);
+    `barrier()` must return once all ranks have called it.  One process per GPU.
+    """
+
+    def __init__(self, backend, device: int, rank: int, world: int, m: int, n_local: int, k: int, np_dtype,
+                 exchange: Callable[[bytes], List[bytes]], barrier: Callable[[], None], b_k_major: bool = False):
+        import ctypes
+
+        from . import _lib, dtypes
+        from .backend import Buffer, _check, _i64
+
+        if world < 1 or world > 8 or not (0 <= rank < world):
+            raise ValueError(f"bad rank {rank} of {world}")
+        if n_local % 8 != 0:
+            raise ValueError("n_local must be a multiple of 8 (16-byte stores)")
+        self.backend, self.device, self.rank, self.world = backend, device, rank, world
+        self.m, self.n_local, self.k, self.b_k_major = m, n_local, k, bool(b_k_major)
+        self._L = _lib.lib()
+        self._barrier = barrier
+        self.dtype = dtypes.from_numpy(np.dtype(np_dtype))
+        shape = (m, n_local * world)
+        err = _lib.B200Error()
+        handle = self._L.b200_buffer_alloc(device, int(self.dtype), _i64(shape), 2, ctypes.byref(err))
+        _check(err, "ColumnShardedMatmul: alloc")
+        self.c = Buffer(handle)
+        raw = ctypes.create_string_buffer(64)
+        self._L.b200_buffer_ipc_export(self.c.handle, raw, ctypes.byref(err))
+        _check(err, "ColumnShardedMatmul: export")
+        handles = exchange(bytes(raw.raw))
+        if len(handles) != world:
+            raise ValueError(f"exchange returned {len(handles)} handles for {world} ranks")
+        self._imported = []
+        self._views = []
+        for r in range(world):
+            if r == rank:
+                self._views.append(self.c)
+                continue
+            err = _lib.B200Error()
+            h = self._L.b200_buffer_ipc_import(device, handles[r], int(self.dtype), _i64(shape), 2, ctypes.byref(err))
+            _check(err, f"ColumnShardedMatmul: import from rank {r}")
+            buf = Buffer(h)
+            self._imported.append(buf)
+            self._views.append(buf)
+        ptrs = [self._L.b200_buffer_device_ptr(v.handle) for v in self._views]
+        self._c_all = (ctypes.c_void_p * world)(*ptrs)
+        barrier()   # nobody launches before every rank has mapped every buffer
+
+    def run(self, a, b_local) -> "object":
+        """a: Buffer [m, k]; b_local: Buffer [k, n_local] (or [n_local, k] with b_k_major).  Enqueues the kernel, waits
+        for this rank's stream and for the other ranks, and returns this rank's full C [m, world * n_local]."""
+        import ctypes
+
+        from . import _lib
+        from .backend import _check
+
+        err = _lib.B200Error()
+        self._L.b200_k_gemm_allgather(self.device, self._L.b200_buffer_device_ptr(a.handle), self._L.b200_buffer_device_ptr(b_local.handle),
+                                      self._c_all, self.world, self.rank, self.m, self.n_local, self.k, 1, int(self.b_k_major),
+                                      int(self.dtype), ctypes.byref(err))
+        _check(err, "ColumnShardedMatmul: gemm_allgather")
+        self.backend.Synchronize(self.device)
+        self._barrier()
+        return self.c
+
+    def launch(self, a, b_local) -> None:
+        """Only enqueues the kernel (for timing with device events); the caller synchronises and calls the barrier."""
+        import ctypes
+
+        from . import _lib
+        from .backend import _check
+
+        err = _lib.B200Error()
+        self._L.b200_k_gemm_allgather(self.device, self._L.b200_buffer_device_ptr(a.handle), self._L.b200_buffer_device_ptr(b_local.handle),
+                                      self._c_all, self.world, self.rank, self.m, self.n_local, self.k, 1, int(self.b_k_major),
+                                      int(self.dtype), ctypes.byref(err))
+        _check(err, "ColumnShardedMatmul: gemm_allgather")
+
+    def close(self) -> None:
+        """Unmaps the peers' buffers, waits for everybody to have done so, then frees this rank's."""
+        self.backend.Synchronize(self.device)
+        for buf in self._imported:
+            self.backend.BufferFinalize(buf)
+        self._imported = []
+        self._barrier()
+        self.backend.BufferFinalize(self.c)

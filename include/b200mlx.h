@@ -329,6 +329,13 @@ int b200_buffer_shape(B200Buffer buf, int64_t* dims, int cap);
 int64_t b200_buffer_nbytes(B200Buffer buf);
 int b200_buffer_device(B200Buffer buf); /* BufferDeviceNum (ref backend.go:126-129) */
 void* b200_buffer_device_ptr(B200Buffer buf);
+/* Sharing a buffer with the other processes of one host (one process per GPU): export writes a 64-byte handle that
+ * another process passes to import, which maps the same device memory (peer access over NVLink is enabled by the
+ * mapping).  The imported buffer is unmapped, not freed, by b200_buffer_free; the exporter must outlive every
+ * importer's use.  The reference is single-device (ref backend.go:144-167) and has no counterpart. */
+#define B200_IPC_HANDLE_BYTES 64
+bool b200_buffer_ipc_export(B200Buffer buf, void* handle_out, B200Error* err);
+B200Buffer b200_buffer_ipc_import(int device, const void* handle, int dtype, const int64_t* shape, int rank, B200Error* err);
 /* Wraps device memory owned by someone else (not freed by b200_buffer_free). */
 B200Buffer b200_buffer_wrap(int device, void* device_ptr, int dtype, const int64_t* shape, int rank, B200Error* err);
 
@@ -367,6 +374,15 @@ bool b200_k_rms_norm(int device, const void* x, const void* gamma, void* y, int6
  * dtype in {BF16, F16, F32}.  bias [N] (may be NULL) and activation are applied in the epilogue. */
 bool b200_k_gemm(int device, const void* a, const void* b, void* c, int64_t batch, int64_t m, int64_t n, int64_t k,
                  int a_k_major, int b_k_major, int dtype, const void* bias, int activation, B200Error* err);
+/* Column-sharded matmul with the all-gather fused into the GEMM: this rank multiplies A [M, K] by ITS column block of
+ * the weight (B stored [K, n_local] when b_k_major == 0, [n_local, K] otherwise) and the epilogue stores the [M, n_local]
+ * slab straight into columns [rank * n_local, +n_local) of EVERY rank's full result C_r [M, num_ranks * n_local]:
+ * c_all[r] is rank r's C as seen from this device (its own for r == rank, b200_buffer_ipc_import'ed peers otherwise),
+ * so the slab crosses NVLink as plain stores while the next tiles are still being multiplied.  No collective call
+ * follows; the ranks only have to agree (a host barrier after each has synchronised its stream) that every slab has
+ * landed before C is read.  n_local must be a multiple of 8 (16-byte stores).  dtype in {BF16, F16}. */
+bool b200_k_gemm_allgather(int device, const void* a, const void* b, void* const* c_all, int num_ranks, int rank, int64_t m,
+                           int64_t n_local, int64_t k, int a_k_major, int b_k_major, int dtype, B200Error* err);
 /* Fused attention softmax(scale * Q K^T [+ causal mask]) V, the kernel behind
  * b200_scaled_dot_product_attention when no mask tensor is given (ref function.go:2669-2907).
  * Q is [batch, seq_q, heads, 64] (bshd != 0) or [batch, heads, seq_q, 64]; K and V likewise with kv_heads and
