@@ -110,7 +110,7 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
-            self._stop.wait(0.01)
+            self._stop.wait(0.002)
 
     def __enter__(self):
         if self._nv is not None:
@@ -346,7 +346,9 @@ def run_b200_arm(args, rank, local_rank, world):
 
     e2e_steps = max(3, min(args.steps, 10))
     e2e_whole_ms = time_host_calls(e2e_step, 3) / 3
-    e2e_ms = time_host_calls(e2e_sliced_step, e2e_steps)
+    e2e_sampler = ClockSampler(local_rank)
+    with e2e_sampler:
+        e2e_ms = time_host_calls(e2e_sliced_step, e2e_steps)
     h2d = n_sm * 4 + n_norm * 2 + 2 * NORM_SHAPE[1] * 2
     d2h = n_sm * 4 + 2 * n_norm * 2
 
@@ -387,7 +389,7 @@ def run_b200_arm(args, rank, local_rank, world):
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "ms_per_step": e2e_ms / e2e_steps,
                     "call": f"b200_execute_host_sliced, {E2E_SLICES} batch slices, pinned host buffers, copies overlapped with kernels",
-                    "unsliced_ms_per_step": e2e_whole_ms, "unsliced_call": "b200_execute_host"},
+                    "unsliced_ms_per_step": e2e_whole_ms, "unsliced_call": "b200_execute_host", "clocks": e2e_sampler.summary()},
             "gpu_launches": args.steps * (exe_sm.NumLaunches() + exe_rms.NumLaunches() + exe_ln.NumLaunches()),
             "roofline": {"bound": "hbm", "kernel": "softmax_rows_kernel<float,8,32> (causal)", "achieved": achieved,
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peak_src,

@@ -26,6 +26,7 @@ _CTYPES = {
     "float": ctypes.c_float,
     "double": ctypes.c_double,
     "int64_t": ctypes.c_int64,
+    "unsigned": ctypes.c_ubyte,   # only "unsigned char" occurs
     "B200Context": ctypes.c_void_p,
     "B200Value": ctypes.c_void_p,
     "B200Exec": ctypes.c_void_p,

@@ -680,7 +680,8 @@ class Executable:
         return buf.value.decode()
 
     def Execute(self, inputs: Sequence[Buffer], donate=None, default_device: int = 0) -> List[Buffer]:
-        """Device buffers in, fresh device buffers out; enqueues and returns (no wait)."""
+        """Device buffers in, fresh device buffers out; enqueues and returns (no wait).  donate[i] hands input i to the
+        call: it is finalized, and an output that is DynamicUpdateSlice of it is updated in place."""
         if self.handle is None:
             raise BackendError(1, "Execute: executable has been finalized")
         if len(inputs) != len(self.input_shapes):
@@ -693,9 +694,22 @@ class Executable:
         ins = (ctypes.c_void_p * max(len(hs), 1))(*hs)
         outs = (ctypes.c_void_p * max(len(self.output_shapes), 1))()
         err = _lib.B200Error()
+        flags = None
+        if donate is not None and any(donate):
+            if len(donate) != len(inputs):
+                raise BackendError(1, f"Execute: {len(donate)} donate flags for {len(inputs)} inputs")
+            flags = (ctypes.c_ubyte * max(len(hs), 1))(*[1 if d else 0 for d in donate])
         with self._mu:
-            self._L.b200_execute(self.handle, ins, len(hs), outs, len(self.output_shapes), ctypes.byref(err))
+            if flags is None:
+                self._L.b200_execute(self.handle, ins, len(hs), outs, len(self.output_shapes), ctypes.byref(err))
+            else:
+                self._L.b200_execute_donating(self.handle, ins, flags, len(hs), outs, len(self.output_shapes), ctypes.byref(err))
         _check(err, "Execute")
+        if flags is not None:
+            for b, d in zip(inputs, donate):   # donated buffers were finalized by the call (ref backends.Executable.Execute's contract)
+                if d and b.valid:
+                    b.valid = False
+                    b.handle = None
         return [Buffer(outs[i]) for i in range(len(self.output_shapes))]
 
     def ExecuteProfiled(self, inputs: Sequence[Buffer]):

@@ -113,6 +113,8 @@ struct DynSliceParams {
 };
 Status dynamic_slice(Device* dev, const DynSliceParams& p);
 Status dynamic_update_slice(Device* dev, const DynSliceParams& p);
+// The same when y already holds x (y == x): only the block is written.
+Status dynamic_update_slice_inplace(Device* dev, const DynSliceParams& p);
 
 // Up to 8 contiguous arrays laid end to end into y with ONE launch (small concatenations are launch-bound: a fused QKV
 // projection joins three bias vectors per layer).  counts are in elements.

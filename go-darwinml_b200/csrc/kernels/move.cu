@@ -293,6 +293,48 @@ Status strided_copy(Device* dev, const StridedCopyParams& p) {
   return dev->CheckLaunch("strided_copy");
 }
 
+template <typename E>
+__global__ void __launch_bounds__(256) dynamic_update_inplace_kernel(const DynArgs a, int64_t total) {
+  __shared__ int64_t start[kMaxDims];
+  block_starts(a, start);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t rem = i, dst = 0, stride = 1;
+    for (int d = a.rank - 1; d >= 0; --d) {
+      const int64_t c = rem % a.b_dims[d];
+      rem /= a.b_dims[d];
+      dst += (c + start[d]) * stride;
+      stride *= a.x_dims[d];
+    }
+    reinterpret_cast<E*>(a.y)[dst] = reinterpret_cast<const E*>(a.u)[i];
+  }
+}
+
+Status dynamic_update_slice_inplace(Device* dev, const DynSliceParams& p) {
+  if (p.rank < 0 || p.rank > kMaxDims) return Status::Invalid("dynamic slice: rank");
+  DynArgs a;
+  a.x = p.y; a.u = p.u; a.y = p.y; a.rank = p.rank;
+  int64_t total = 1;
+  for (int d = 0; d < kMaxDims; ++d) {
+    a.x_dims[d] = d < p.rank ? p.x_dims[d] : 1;
+    a.b_dims[d] = d < p.rank ? p.b_dims[d] : 1;
+    a.starts[d] = d < p.rank ? p.starts[d] : nullptr;
+    a.start_dtypes[d] = d < p.rank ? p.start_dtypes[d] : B200_INT32;
+    if (d < p.rank) total *= p.b_dims[d];
+  }
+  if (total == 0) return Status::OK();
+  B200_TRY(dev->MakeCurrent());
+  const unsigned grid = grid_for(dev, total);
+  cudaStream_t s = dev->stream();
+  switch (p.elt_size) {
+    case 1: dynamic_update_inplace_kernel<uint8_t><<<grid, 256, 0, s>>>(a, total); break;
+    case 2: dynamic_update_inplace_kernel<uint16_t><<<grid, 256, 0, s>>>(a, total); break;
+    case 4: dynamic_update_inplace_kernel<uint32_t><<<grid, 256, 0, s>>>(a, total); break;
+    case 8: dynamic_update_inplace_kernel<uint64_t><<<grid, 256, 0, s>>>(a, total); break;
+    default: return Status::Invalid("dynamic slice: element size");
+  }
+  return dev->CheckLaunch("dynamic_update_slice_inplace");
+}
+
 static Status dyn_launch(Device* dev, const DynSliceParams& p, bool update) {
   if (p.rank < 0 || p.rank > kMaxDims) return Status::Invalid("dynamic slice: rank");
   DynArgs a;

@@ -85,6 +85,8 @@ struct Exec {
   // Launch-bound plans replay as one CUDA graph: the second time a plan runs on the same input and output addresses
   // (a serving loop that frees its outputs gets the same blocks back from the caching allocator) its steps are
   // captured from the stream instead of launched, and later calls with those addresses are one cudaGraphLaunch.
+  // output j may take over the memory of donated input donate_alias[j] (-1: never): see EmitDynamicSlice
+  std::vector<int> donate_alias;
   bool capturable = false;
   std::vector<PlanGraph> graphs;
   std::vector<void*> last_key;
@@ -850,12 +852,20 @@ class Planner {
     st.reads.push_back(x_slot);
     if (upd) st.reads.push_back(u_slot);
     st.writes = {out_slot};
+    // DynamicUpdateSlice straight from a placeholder into an output, the placeholder feeding nothing else: when the caller
+    // donates that input, execute binds the output to the input's memory and this step only writes the block.
+    if (update && operand->op == Op::Parameter && uses_[operand->id] == 1 && ex_->slots[out_slot].kind == SlotKind::Output &&
+        ex_->slots[x_slot].kind == SlotKind::Input) {
+      if (ex_->donate_alias.size() <= (size_t)ex_->slots[out_slot].index) ex_->donate_alias.resize(ex_->slots[out_slot].index + 1, -1);
+      ex_->donate_alias[ex_->slots[out_slot].index] = ex_->slots[x_slot].index;
+    }
     st.run = [dp, start_slots, x_slot, u_slot, out_slot, update](Device* dev, void* const* p) -> Status {
       k::DynSliceParams q = dp;
       q.x = p[x_slot];
       q.u = u_slot >= 0 ? p[u_slot] : nullptr;
       q.y = p[out_slot];
       for (size_t i = 0; i < start_slots.size(); ++i) q.starts[i] = p[start_slots[i]];
+      if (update && q.x == q.y) return k::dynamic_update_slice_inplace(dev, q);
       return update ? k::dynamic_update_slice(dev, q) : k::dynamic_slice(dev, q);
     };
     ex_->steps.push_back(std::move(st));
@@ -1689,16 +1699,21 @@ int64_t b200_exec_describe(B200Exec exec, char* buf, int64_t cap) {
 }
 
 static bool execute_impl(B200Exec exec, const B200Buffer* inputs, int num_inputs, B200Buffer* outputs, int num_outputs,
-                         std::vector<float>* step_ms, B200Error* err);
+                         std::vector<float>* step_ms, const unsigned char* donate, B200Error* err);
 
 bool b200_execute(B200Exec exec, const B200Buffer* inputs, int num_inputs, B200Buffer* outputs, int num_outputs, B200Error* err) {
-  return execute_impl(exec, inputs, num_inputs, outputs, num_outputs, nullptr, err);
+  return execute_impl(exec, inputs, num_inputs, outputs, num_outputs, nullptr, nullptr, err);
+}
+
+bool b200_execute_donating(B200Exec exec, const B200Buffer* inputs, const unsigned char* donate, int num_inputs, B200Buffer* outputs,
+                           int num_outputs, B200Error* err) {
+  return execute_impl(exec, inputs, num_inputs, outputs, num_outputs, nullptr, donate, err);
 }
 
 int64_t b200_execute_profiled(B200Exec exec, const B200Buffer* inputs, int num_inputs, B200Buffer* outputs, int num_outputs, char* report,
                               int64_t cap, B200Error* err) {
   std::vector<float> ms;
-  if (!execute_impl(exec, inputs, num_inputs, outputs, num_outputs, &ms, err)) return -1;
+  if (!execute_impl(exec, inputs, num_inputs, outputs, num_outputs, &ms, nullptr, err)) return -1;
   Exec* ex = reinterpret_cast<Exec*>(exec);
   std::string s;
   double total = 0;
@@ -1714,7 +1729,7 @@ int64_t b200_execute_profiled(B200Exec exec, const B200Buffer* inputs, int num_i
 }
 
 static bool execute_impl(B200Exec exec, const B200Buffer* inputs, int num_inputs, B200Buffer* outputs, int num_outputs,
-                         std::vector<float>* step_ms, B200Error* err) {
+                         std::vector<float>* step_ms, const unsigned char* donate, B200Error* err) {
   clear_error(err);
   Exec* ex = reinterpret_cast<Exec*>(exec);
   if (!ex) { set_error(err, Status::Invalid("Execute: null executable")); return false; }
@@ -1740,10 +1755,29 @@ static bool execute_impl(B200Exec exec, const B200Buffer* inputs, int num_inputs
     ptrs[d.slot] = b->ptr;
   }
   std::vector<Buffer*> outs;
+  std::vector<int> taken_from(num_outputs, -1);   // output j holds the block of donated input taken_from[j]
   auto fail = [&](const Status& s) {
-    for (Buffer* b : outs) { ex->dev->Free(b->ptr); delete b; }
+    for (size_t j = 0; j < outs.size(); ++j) {
+      if (taken_from[j] < 0) ex->dev->Free(outs[j]->ptr);   // a block taken from an input stays the input's on failure
+      delete outs[j];
+    }
     set_error(err, s);
     return false;
+  };
+  // On success donated inputs are finalized: the one an output took over loses its block to it, the others free theirs.
+  auto consume_donated = [&]() {
+    if (!donate) return;
+    for (int i = 0; i < num_inputs; ++i) {
+      if (!donate[i]) continue;
+      bool dup = false;
+      for (int k = 0; k < i; ++k) dup = dup || inputs[k] == inputs[i];
+      if (dup) continue;
+      Buffer* b = reinterpret_cast<Buffer*>(inputs[i]);
+      bool taken = false;
+      for (int j = 0; j < num_outputs; ++j) taken = taken || taken_from[j] == i;
+      if (taken) b->ptr = nullptr;
+      b200_buffer_free(inputs[i]);
+    }
   };
   for (int i = 0; i < num_outputs; ++i) {
     const OutputDesc& d = ex->outputs[i];
@@ -1752,6 +1786,16 @@ static bool execute_impl(B200Exec exec, const B200Buffer* inputs, int num_inputs
     b->dtype = d.dtype;
     b->dims = d.dims;
     b->nbytes = d.nbytes;
+    // a donated input this output may update in place: the output takes over the input's block
+    const int alias = (donate && (size_t)i < ex->donate_alias.size()) ? ex->donate_alias[i] : -1;
+    Buffer* src = alias >= 0 && donate[alias] ? reinterpret_cast<Buffer*>(inputs[alias]) : nullptr;
+    if (src && src->owned && !src->ipc && src->nbytes == d.nbytes) {
+      b->ptr = src->ptr;
+      taken_from[i] = alias;
+      outs.push_back(b);
+      ptrs[d.slot] = b->ptr;
+      continue;
+    }
     Status s = ex->dev->Alloc(d.nbytes > 0 ? d.nbytes : 1, &b->ptr);
     outs.push_back(b);
     if (!s.ok()) return fail(s);
@@ -1814,6 +1858,7 @@ static bool execute_impl(B200Exec exec, const B200Buffer* inputs, int num_inputs
         return fail(Status::Cuda(strfmt("Execute: graph launch failed: %s", cudaGetErrorString(ce))));
       }
       for (int i = 0; i < num_outputs; ++i) outputs[i] = outs[i];
+      consume_donated();
       return true;
     }
     ex->last_key = key;
@@ -1840,6 +1885,7 @@ static bool execute_impl(B200Exec exec, const B200Buffer* inputs, int num_inputs
     for (auto& e : events) cudaEventDestroy(e);
   }
   for (int i = 0; i < num_outputs; ++i) outputs[i] = outs[i];
+  consume_donated();
   return true;
 }
 

@@ -287,6 +287,13 @@ int64_t b200_exec_describe(B200Exec exec, char* buf, int64_t cap);
  * Inputs are not consumed.  Executions of one B200Exec are serialised. */
 bool b200_execute(B200Exec exec, const B200Buffer* inputs, int num_inputs, B200Buffer* outputs, int num_outputs,
                   B200Error* err);
+/* b200_execute with GoMLX's `donate` flags (ref executable.go:50-60 accepts and ignores them): donate[i] != 0 hands
+ * input i to the call: its handle is finalized by the call (do not free it again) and its memory may become an output.
+ * Today one case reuses it: an output that is DynamicUpdateSlice(input i, ...), with input i used by nothing else,
+ * is updated IN PLACE -- only the update block is written, which is what makes a KV-cache append cost the size of the
+ * new entry instead of a copy of the whole cache.  Other donated inputs are simply released. */
+bool b200_execute_donating(B200Exec exec, const B200Buffer* inputs, const unsigned char* donate, int num_inputs, B200Buffer* outputs,
+                           int num_outputs, B200Error* err);
 /* Like b200_execute, but brackets every step of the launch plan with CUDA events, waits, and writes a
  * NUL-terminated report (one line per step: milliseconds, share, description) into report (truncated to cap).
  * Returns the full report length, or -1 with error.  The reference has no profiling hook (only DEBUG

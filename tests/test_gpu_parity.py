@@ -916,3 +916,39 @@ def test_repeated_execution_replays_a_cuda_graph(b200, backend):
     ok, viol = compare(got[0], want[0], BF16_RTOL, 1.0)
     assert ok, viol
     assert not np.array_equal(got[0], first[0])
+
+
+def test_donated_cache_is_updated_in_place(b200, backend):
+    # Execute's donate flag (ref executable.go:50-60): a donated input that an output is DynamicUpdateSlice of is updated
+    # where it lies; without the flag the output is a fresh copy and the input stays valid and unchanged
+    rng = np.random.default_rng(105)
+    cache, new = rng_array(rng, (2, 64, 4, 16), BF16), rng_array(rng, (2, 1, 4, 16), BF16)
+    L = b200.lib()
+    builder = backend.Builder("donate")
+    f = builder.Main()
+    pc = f.Parameter("cache", _S(b200, BF16, 2, 64, 4, 16))
+    pn = f.Parameter("new", _S(b200, BF16, 2, 1, 4, 16))
+    pp = f.Parameter("pos", b200.shapes.Make(b200.dtypes.Int32))
+    z = f.Constant(np.array([0], dtype=np.int32))
+    z = f.Reshape(z)
+    f.Return([f.DynamicUpdateSlice(pc, pn, [z, pp, z, z])], None)
+    exe = builder.Compile()
+    want = cache.copy()
+    want[:, 37:38] = new
+    bn, bp = backend.FromNumpy(new), backend.FromNumpy(np.array(37, dtype=np.int32))
+
+    bc = backend.FromNumpy(cache)
+    addr = L.b200_buffer_device_ptr(bc.handle)
+    (out,) = exe.Execute([bc, bn, bp], [False, False, False], 0)
+    assert L.b200_buffer_device_ptr(out.handle) != addr and bc.valid
+    np.testing.assert_array_equal(backend.ToNumpy(out).view(np.uint16), want.view(np.uint16))
+    np.testing.assert_array_equal(backend.ToNumpy(bc).view(np.uint16), cache.view(np.uint16))
+    backend.BufferFinalize(out)
+
+    for _ in range(3):   # repeated steps: each output becomes the next donated cache (and the plan may be replayed)
+        (out,) = exe.Execute([bc, bn, bp], [True, False, False], 0)
+        assert L.b200_buffer_device_ptr(out.handle) == addr and not bc.valid
+        np.testing.assert_array_equal(backend.ToNumpy(out).view(np.uint16), want.view(np.uint16))
+        bc = out
+    with pytest.raises(b200.BackendError):
+        exe.Execute([bc, bn, bp], [True, False], 0)
