@@ -19,7 +19,8 @@
 //               MMAs run under the other tile's softmax;
 //   warps 2-5   softmax of tile 0, warps 6-9 of tile 1: each thread owns one query row: tcgen05.ld its 64 scores,
 //               running max / sum in base 2 with the scale folded into the exponent's FMA, P = exp2(...) rounded to
-//               the input type and written to shared memory in the 128-byte-swizzled K-major layout.
+//               the input type and written back over S in TENSOR MEMORY (tcgen05.st), where the PV MMA reads it as its
+//               A operand: P never touches shared memory.
 // The output accumulates in TMEM across key blocks.  Its reference maximum is only moved when a row's maximum grew by
 // more than 2^8 since the last move (then the row of O is rescaled in TMEM); P stays below 2^8 and the final division
 // by the row sum cancels the common factor, so nothing is lost and most blocks skip the rescale.
@@ -49,8 +50,7 @@ constexpr int BKV = 64;          // keys per step (UMMA N of the score MMA, K of
 constexpr int KV_STAGES = 3;
 constexpr int Q_BYTES = BQ * HD * 2;     // 16 KiB per tile
 constexpr int KV_BYTES = BKV * HD * 2;   // 8 KiB (K or V)
-constexpr int P_BYTES = BQ * BKV * 2;    // 16 KiB per tile
-constexpr int ATT_TILE_BYTES = QT * Q_BYTES + KV_STAGES * 2 * KV_BYTES + QT * P_BYTES;  // 112 KiB
+constexpr int ATT_TILE_BYTES = QT * Q_BYTES + KV_STAGES * 2 * KV_BYTES;  // 80 KiB: P never touches shared memory
 constexpr int ATT_SMEM = ATT_TILE_BYTES + 256;   // + barriers; the dynamic window itself is 1024-byte aligned (checked)
 constexpr int ATT_THREADS = 320;
 constexpr int ATT_TMEM_COLS = 256;       // S0, S1, O0, O1: 64 columns each
@@ -88,8 +88,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* sQ = smem_raw;                          // [QT] tiles
   unsigned char* sKV = sQ + QT * Q_BYTES;                // [KV_STAGES] x (K, V)
-  unsigned char* sP = sKV + KV_STAGES * 2 * KV_BYTES;    // [QT] tiles
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + QT * P_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + KV_STAGES * 2 * KV_BYTES);
   uint64_t* q_full = bars;                       // [1]
   uint64_t* kv_full = bars + 1;                  // [KV_STAGES] bytes of K_j and V_j landed
   uint64_t* kv_empty = kv_full + KV_STAGES;      // [KV_STAGES] every MMA that reads the stage is done
@@ -167,7 +166,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const uint64_t dq0 = make_smem_desc(smem_u32(sQ), 16, 1024);
       const uint64_t dk0 = make_smem_desc(smem_u32(sKV), 16, 1024);
       const uint64_t dv0 = make_smem_desc(smem_u32(sKV) + KV_BYTES, 8192, 1024);
-      const uint64_t dp0 = make_smem_desc(smem_u32(sP), 16, 1024);
       auto issue_scores = [&](int t, int stage) {   // S_t = Q_t K^T
         const uint64_t dq = dq0 + (uint64_t)((t * Q_BYTES) >> 4), dk = dk0 + (uint64_t)((stage * 2 * KV_BYTES) >> 4);
 #pragma unroll
@@ -195,10 +193,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           if (!mbar_wait(&p_ready[t], (uint32_t)(j & 1), err, 4)) { ok = false; break; }
           tc_fence_after();
           // O_t (+)= P_t V_j
-          const uint64_t dp = dp0 + (uint64_t)((t * P_BYTES) >> 4), dv = dv0 + (uint64_t)((s * 2 * KV_BYTES) >> 4);
+          // P_t lies in the first 32 columns of S_t (two 16-bit values per column): 16 keys per MMA = 8 columns
+          const uint64_t dv = dv0 + (uint64_t)((s * 2 * KV_BYTES) >> 4);
 #pragma unroll
           for (int k = 0; k < BKV / 16; ++k)
-            umma_f16(tmem_base + 128 + t * 64, dp + (uint64_t)((k * 32) >> 4), dv + (uint64_t)((k * 2048) >> 4), idesc_pv, (j | k) != 0 ? 1u : 0u);
+            umma_f16_ts(tmem_base + 128 + t * 64, tmem_base + t * 64 + k * 8, dv + (uint64_t)((k * 2048) >> 4), idesc_pv, (j | k) != 0 ? 1u : 0u);
           tc_commit(&o_done[t]);
           // the tile's next scores go out at once: its softmax warps have read S_t (they said so with p_ready)
           if (j + 1 < nt) {
@@ -224,7 +223,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int q_row = q0 + t * BQ + row;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const uint32_t tmem_s = tmem_base + t * 64 + lane_addr, tmem_o = tmem_base + 128 + t * 64 + lane_addr;
-    unsigned char* prow = sP + t * P_BYTES + row * 128;
     const float c = g.scale_log2e;
     float m_ref = 0.f, l_run = 0.f;         // p = exp2(c * s - m_ref)
     bool ok = true;
@@ -263,14 +261,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const float m_new = mx * c;                           // c > 0: the maximum commutes with the scale
       // Move the reference only when some row of the warp needs it (tcgen05.ld / st are warp-collective).
       const bool grow = (j == 0) ? true : (m_new > m_ref + kRescaleThreshold);
-      bool waited_o = false;
       if (__any_sync(0xffffffffu, grow)) {
         const float m_next = grow ? (m_new == -INFINITY ? 0.f : m_new) : m_ref;
         if (j > 0) {
           // the PV MMAs of block j-1 must have landed before O is touched
           const bool landed = mbar_wait(&o_done[t], (uint32_t)((j - 1) & 1), err, 7);
           if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }
-          waited_o = true;
           tc_fence_after();
           const float alpha = fast_exp2(m_ref - m_next);    // 1 for rows that keep their reference
           l_run *= alpha;
@@ -287,13 +283,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
         m_ref = m_next;
       }
-      if (j > 0 && !waited_o) {
-        // sP_t is still being read by the PV MMAs of block j-1 until o_done says otherwise
-        const bool landed = mbar_wait(&o_done[t], (uint32_t)((j - 1) & 1), err, 7);
-        if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }
-      }
-      // Pass 2: P = exp2(c * s - m_ref), rounded, into shared memory: K-major with 128-byte swizzle, 16-byte chunk q
-      // of row r lives at chunk (q ^ (r & 7)).
+      // Pass 2: P = exp2(c * s - m_ref), rounded to the input type, written over the first 32 columns of S_t, where the
+      // PV MMA reads it as its A operand (the PV MMAs of block j-1 read the previous P there, but they were issued
+      // before the score MMAs that produced this S, and MMAs run in issue order: they are done).
       float psum0 = 0.f, psum1 = 0.f;
       {
         uint32_t sr[64];
@@ -306,21 +298,17 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             if (cidx >= limit) sr[cidx] = 0xff800000u;
         }
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[8 * q + 2 * e]), c, -m_ref));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[8 * q + 2 * e + 1]), c, -m_ref));
-            psum0 += p0;
-            psum1 += p1;
-            w[e] = pack2<T>(p0, p1);
-          }
-          *reinterpret_cast<uint4*>(prow + ((q ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        for (int cidx = 0; cidx < 64; cidx += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[cidx]), c, -m_ref));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[cidx + 1]), c, -m_ref));
+          psum0 += p0;
+          psum1 += p1;
+          sr[cidx >> 1] = pack2<T>(p0, p1);   // in place: entry cidx / 2 has been consumed
         }
+        tmem_st32(tmem_s, sr);
+        tmem_st_wait();
       }
       l_run += psum0 + psum1;
-      fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[t]);
