@@ -12,7 +12,7 @@ namespace b200 {
 namespace k {
 namespace sm100 {
 
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // a bounded wait gives up after about two seconds
+
 
 // ------------------------------------------------------------------ PTX wrappers ---
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -42,16 +42,26 @@ __device__ __forceinline__ unsigned long long global_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait.  Returns false (and raises *err_flag) when the limit passes or
-// another role already gave up.
+// Bounded wait.  Returns false (and raises *err_flag) when the limit passes or another role already gave up.
+// The bound is kept on the SM's own cycle counter and only looked at every 256 polls: %globaltimer is a long-latency
+// read (it sat on the critical path of every wait that did not succeed at once, three per key block in the attention
+// kernel), %clock64 costs a few cycles.
+constexpr long long kWaitLimitCycles = 4000000000ll;   // about two seconds at 2 GHz
+__device__ __forceinline__ long long sm_cycles() {
+  long long t;
+  asm volatile("mov.u64 %0, %%clock64;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* err_flag, int code) {
   if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = global_ns();
   uint32_t spins = 0;
+  long long t0 = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0x3ff) == 0) {
+    if ((++spins & 0xff) == 0) {
       if (*err_flag != 0) return false;
-      if (global_ns() - t0 > kWaitLimitNs) {
+      if (t0 == 0) {
+        t0 = sm_cycles() | 1;
+      } else if (sm_cycles() - t0 > kWaitLimitCycles) {
         atomicCAS((int*)err_flag, 0, code);
         return false;
       }
@@ -128,6 +138,14 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
         "r"(r[30]), "r"(r[31])
       : "memory");
 }
+// 16-column store: thread i writes 16 columns of lane (base + i).
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
@@ -179,12 +197,14 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
 // Bounded wait on a barrier that the peer CTA (or an instruction issued by it) signals.
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* err_flag, int code) {
   if (mbar_try_wait_cluster(bar, parity)) return true;
-  const unsigned long long t0 = global_ns();
   uint32_t spins = 0;
+  long long t0 = 0;
   while (!mbar_try_wait_cluster(bar, parity)) {
-    if ((++spins & 0x3ff) == 0) {
+    if ((++spins & 0xff) == 0) {
       if (*err_flag != 0) return false;
-      if (global_ns() - t0 > kWaitLimitNs) {
+      if (t0 == 0) {
+        t0 = sm_cycles() | 1;
+      } else if (sm_cycles() - t0 > kWaitLimitCycles) {
         atomicCAS((int*)err_flag, 0, code);
         return false;
       }
