@@ -12,7 +12,8 @@
 // the keys in blocks of 64 with an online softmax, reading Q, K and V in place
 // through TMA.
 //
-// Warp roles (320 threads, two CTAs per SM):
+// Persistent CTAs (two per SM) walk the work items; the next item's queries are loaded while this one is computed.
+// Warp roles (320 threads):
 //   warp 0      loader: Q once, then K_j / V_j blocks into a 3-stage ring;
 //   warp 1      issuer: S_t = Q_t K_j^T (tcgen05.mma 128 x 64 x 16, fp32 in TMEM) and O_t += P_t V_j for both tiles
 //               (V read as an MN-major operand, so it needs no transpose); the two tiles alternate, so one tile's
@@ -50,7 +51,8 @@ constexpr int BKV = 64;          // keys per step (UMMA N of the score MMA, K of
 constexpr int KV_STAGES = 3;
 constexpr int Q_BYTES = BQ * HD * 2;     // 16 KiB per tile
 constexpr int KV_BYTES = BKV * HD * 2;   // 8 KiB (K or V)
-constexpr int ATT_TILE_BYTES = QT * Q_BYTES + KV_STAGES * 2 * KV_BYTES;  // 80 KiB: P never touches shared memory
+constexpr int Q_BUFS = 2;             // the next work item's queries are loaded while this one is computed
+constexpr int ATT_TILE_BYTES = Q_BUFS * QT * Q_BYTES + KV_STAGES * 2 * KV_BYTES;  // 112 KiB: P never touches shared memory
 constexpr int ATT_SMEM = ATT_TILE_BYTES + 256;   // + barriers; the dynamic window itself is 1024-byte aligned (checked)
 constexpr int ATT_THREADS = 320;
 constexpr int ATT_TMEM_COLS = 256;       // S0, S1, O0, O1: 64 columns each
@@ -86,14 +88,15 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)
 attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const AttArgs g) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  unsigned char* sQ = smem_raw;                          // [QT] tiles
-  unsigned char* sKV = sQ + QT * Q_BYTES;                // [KV_STAGES] x (K, V)
+  unsigned char* sQ = smem_raw;                          // [Q_BUFS][QT] tiles
+  unsigned char* sKV = sQ + Q_BUFS * QT * Q_BYTES;       // [KV_STAGES] x (K, V)
   uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + KV_STAGES * 2 * KV_BYTES);
-  uint64_t* q_full = bars;                       // [1]
-  uint64_t* kv_full = bars + 1;                  // [KV_STAGES] bytes of K_j and V_j landed
+  uint64_t* q_full = bars;                       // [Q_BUFS] the item's queries landed
+  uint64_t* q_empty = q_full + Q_BUFS;           // [Q_BUFS] every score MMA of the item that used the buffer is done
+  uint64_t* kv_full = q_empty + Q_BUFS;          // [KV_STAGES] bytes of K_j and V_j landed
   uint64_t* kv_empty = kv_full + KV_STAGES;      // [KV_STAGES] every MMA that reads the stage is done
   uint64_t* s_full = kv_empty + KV_STAGES;       // [QT] scores of the current block are in TMEM
-  uint64_t* p_ready = s_full + QT;               // [QT] P is in shared memory (and S has been read): 4 warp arrivals
+  uint64_t* p_ready = s_full + QT;               // [QT] P is in tensor memory (and S has been read): 4 warp arrivals
   uint64_t* o_done = p_ready + QT;               // [QT] the PV MMAs of the current block are done
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + QT);
   int* failed = reinterpret_cast<int*>(tmem_slot + 1);
@@ -101,26 +104,39 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* err = g.err_flag;
 
-  // work item: heavy (late) query blocks first so the causal tail is short
+  // Persistent CTAs: work items (256 query rows of one head) are dealt round-robin, heaviest (latest query block
+  // under a causal mask) first, so every CTA gets a similar mix and the fixed cost of a CTA -- launch, TMEM allocation,
+  // the first loads, the drain -- is paid once per CTA instead of once per item (it measured 7.5 us per item against
+  // 1.5 us per key block).  Barrier phases simply keep counting across items.
   const int nq = (g.Sq + QT * BQ - 1) / (QT * BQ);
-  const int64_t item = blockIdx.x;
-  const int qb = nq - 1 - (int)(item % nq);
-  const int h = (int)((item / nq) % g.H);
-  const int b = (int)(item / ((int64_t)nq * g.H));
-  const int hkv = h / (g.H / g.Hkv);
-  const int q0 = qb * QT * BQ;
-  // key blocks each tile walks: under a causal mask keys beyond the tile's last row are masked for every row
-  auto blocks_of = [&](int t) {
-    const int first = q0 + t * BQ;
-    int kv_end = g.Sk;
-    if (g.causal && first + BQ < kv_end) kv_end = first + BQ;
-    return first < g.Sq ? (kv_end + BKV - 1) / BKV : 0;   // a tile wholly past the last query row does nothing
+  const int64_t heads_total = (int64_t)g.H * g.B;
+  const int64_t num_items = (int64_t)nq * heads_total;
+  struct Item {
+    int h, b, hkv, q0, nkv0, nkv1, nkv_max;
   };
-  const int nkv0 = blocks_of(0), nkv1 = blocks_of(1);
-  const int nkv_max = nkv0 > nkv1 ? nkv0 : nkv1;
+  auto decode = [&](int64_t item) {
+    Item it;
+    const int qb = nq - 1 - (int)(item / heads_total);
+    const int64_t hb = item % heads_total;
+    it.h = (int)(hb % g.H);
+    it.b = (int)(hb / g.H);
+    it.hkv = it.h / (g.H / g.Hkv);
+    it.q0 = qb * QT * BQ;
+    // key blocks each tile walks: under a causal mask keys beyond the tile's last row are masked for every row
+    auto blocks_of = [&](int t) {
+      const int first = it.q0 + t * BQ;
+      int kv_end = g.Sk;
+      if (g.causal && first + BQ < kv_end) kv_end = first + BQ;
+      return first < g.Sq ? (kv_end + BKV - 1) / BKV : 0;   // a tile wholly past the last query row does nothing
+    };
+    it.nkv0 = blocks_of(0);
+    it.nkv1 = blocks_of(1);
+    it.nkv_max = it.nkv0 > it.nkv1 ? it.nkv0 : it.nkv1;
+    return it;
+  };
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
+    for (int q = 0; q < Q_BUFS; ++q) { mbar_init(&q_full[q], 1); mbar_init(&q_empty[q], 1); }
     for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
     for (int t = 0; t < QT; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_ready[t], 4); mbar_init(&o_done[t], 1); }
     *failed = 0;
@@ -142,18 +158,24 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   } else if (warp == 0) {
     // -------------------------------------------------------------------- loader ---
     if (lane == 0) {
-      mbar_expect_tx(q_full, QT * Q_BYTES);
-#pragma unroll
-      for (int t = 0; t < QT; ++t) tma_load_4d(sQ + t * Q_BYTES, &tm_q, q_full, 0, q0 + t * BQ, h, b);
       int s = 0;
-      uint32_t phase = 0;
-      for (int j = 0; j < nkv_max; ++j) {
-        if (!mbar_wait(&kv_empty[s], phase ^ 1, err, 1)) break;
-        unsigned char* dst = sKV + s * 2 * KV_BYTES;
-        mbar_expect_tx(&kv_full[s], 2 * KV_BYTES);
-        tma_load_4d(dst, &tm_k, &kv_full[s], 0, j * BKV, hkv, b);
-        tma_load_4d(dst + KV_BYTES, &tm_v, &kv_full[s], 0, j * BKV, hkv, b);
-        if (++s == KV_STAGES) { s = 0; phase ^= 1; }
+      uint32_t phase = 0, n_item = 0;
+      bool ok = true;
+      for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++n_item) {
+        const Item it = decode(item);
+        const int qbuf = (int)(n_item & 1);
+        if (!mbar_wait(&q_empty[qbuf], ((n_item >> 1) & 1) ^ 1, err, 1)) break;
+        mbar_expect_tx(&q_full[qbuf], QT * Q_BYTES);
+#pragma unroll
+        for (int t = 0; t < QT; ++t) tma_load_4d(sQ + (qbuf * QT + t) * Q_BYTES, &tm_q, &q_full[qbuf], 0, it.q0 + t * BQ, it.h, it.b);
+        for (int j = 0; j < it.nkv_max; ++j) {
+          if (!mbar_wait(&kv_empty[s], phase ^ 1, err, 1)) { ok = false; break; }
+          unsigned char* dst = sKV + s * 2 * KV_BYTES;
+          mbar_expect_tx(&kv_full[s], 2 * KV_BYTES);
+          tma_load_4d(dst, &tm_k, &kv_full[s], 0, j * BKV, it.hkv, it.b);
+          tma_load_4d(dst + KV_BYTES, &tm_v, &kv_full[s], 0, j * BKV, it.hkv, it.b);
+          if (++s == KV_STAGES) { s = 0; phase ^= 1; }
+        }
       }
     }
   } else if (warp == 1) {
@@ -166,53 +188,61 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const uint64_t dq0 = make_smem_desc(smem_u32(sQ), 16, 1024);
       const uint64_t dk0 = make_smem_desc(smem_u32(sKV), 16, 1024);
       const uint64_t dv0 = make_smem_desc(smem_u32(sKV) + KV_BYTES, 8192, 1024);
+      int qbuf = 0;
       auto issue_scores = [&](int t, int stage) {   // S_t = Q_t K^T
-        const uint64_t dq = dq0 + (uint64_t)((t * Q_BYTES) >> 4), dk = dk0 + (uint64_t)((stage * 2 * KV_BYTES) >> 4);
+        const uint64_t dq = dq0 + (uint64_t)(((qbuf * QT + t) * Q_BYTES) >> 4), dk = dk0 + (uint64_t)((stage * 2 * KV_BYTES) >> 4);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) umma_f16(tmem_base + t * 64, dq + (uint64_t)((k * 32) >> 4), dk + (uint64_t)((k * 32) >> 4), idesc_s, k != 0 ? 1u : 0u);
         tc_commit(&s_full[t]);
       };
-      bool ok = mbar_wait(q_full, 0, err, 2);
       int s = 0;
-      uint32_t phase = 0;
-      if (ok) ok = mbar_wait(&kv_full[0], 0, err, 3);
-      if (ok) {
+      uint32_t phase = 0, n_item = 0;
+      uint32_t done[QT] = {0, 0};   // key blocks each tile has finished so far, over all items: the phase of its barriers
+      bool ok = true;
+      for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++n_item) {
+        const Item it = decode(item);
+        qbuf = (int)(n_item & 1);
+        if (it.nkv_max == 0) { tc_commit(&q_empty[qbuf]); continue; }   // the loader loaded Q anyway: hand the buffer back
+        ok = mbar_wait(&q_full[qbuf], (n_item >> 1) & 1, err, 2);
+        if (ok) ok = mbar_wait(&kv_full[s], phase, err, 3);
+        if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int t = 0; t < QT; ++t)
-          if ((t ? nkv1 : nkv0) > 0) issue_scores(t, 0);
-      }
-      for (int j = 0; j < nkv_max && ok; ++j) {
-        const int s_next = (s + 1 == KV_STAGES) ? 0 : s + 1;
-        const uint32_t phase_next = (s + 1 == KV_STAGES) ? (phase ^ 1) : phase;
-        bool next_landed = false;
+          if ((t ? it.nkv1 : it.nkv0) > 0) issue_scores(t, s);
+        for (int j = 0; j < it.nkv_max && ok; ++j) {
+          const int s_next = (s + 1 == KV_STAGES) ? 0 : s + 1;
+          const uint32_t phase_next = (s + 1 == KV_STAGES) ? (phase ^ 1) : phase;
+          bool next_landed = false;
 #pragma unroll
-        for (int t = 0; t < QT; ++t) {
-          const int nt = t ? nkv1 : nkv0;
-          if (j >= nt) continue;
-          if (!mbar_wait(&p_ready[t], (uint32_t)(j & 1), err, 4)) { ok = false; break; }
-          tc_fence_after();
-          // O_t (+)= P_t V_j
-          // P_t lies in the first 32 columns of S_t (two 16-bit values per column): 16 keys per MMA = 8 columns
-          const uint64_t dv = dv0 + (uint64_t)((s * 2 * KV_BYTES) >> 4);
+          for (int t = 0; t < QT; ++t) {
+            const int nt = t ? it.nkv1 : it.nkv0;
+            if (j >= nt) continue;
+            if (!mbar_wait(&p_ready[t], done[t] & 1, err, 4)) { ok = false; break; }
+            tc_fence_after();
+            // O_t (+)= P_t V_j.  P_t lies in the first 32 columns of S_t (two 16-bit values per column): 16 keys per MMA = 8 columns
+            const uint64_t dv = dv0 + (uint64_t)((s * 2 * KV_BYTES) >> 4);
 #pragma unroll
-          for (int k = 0; k < BKV / 16; ++k)
-            umma_f16_ts(tmem_base + 128 + t * 64, tmem_base + t * 64 + k * 8, dv + (uint64_t)((k * 2048) >> 4), idesc_pv, (j | k) != 0 ? 1u : 0u);
-          tc_commit(&o_done[t]);
-          // the tile's next scores go out at once: its softmax warps have read S_t (they said so with p_ready)
-          if (j + 1 < nt) {
-            if (!next_landed) {
-              if (!mbar_wait(&kv_full[s_next], phase_next, err, 3)) { ok = false; break; }
-              tc_fence_after();
-              next_landed = true;
+            for (int k = 0; k < BKV / 16; ++k)
+              umma_f16_ts(tmem_base + 128 + t * 64, tmem_base + t * 64 + k * 8, dv + (uint64_t)((k * 2048) >> 4), idesc_pv, (j | k) != 0 ? 1u : 0u);
+            tc_commit(&o_done[t]);
+            ++done[t];
+            // the tile's next scores go out at once: its softmax warps have read S_t (they said so with p_ready)
+            if (j + 1 < nt) {
+              if (!next_landed) {
+                if (!mbar_wait(&kv_full[s_next], phase_next, err, 3)) { ok = false; break; }
+                tc_fence_after();
+                next_landed = true;
+              }
+              issue_scores(t, s_next);
             }
-            issue_scores(t, s_next);
           }
+          if (!ok) break;
+          tc_commit(&kv_empty[s]);   // every MMA that reads stage s has been issued before this point
+          s = s_next;
+          phase = phase_next;
         }
-        if (!ok) break;
-        tc_commit(&kv_empty[s]);   // every MMA that reads stage s has been issued before this point
-        s = s_next;
-        phase = phase_next;
+        if (ok) tc_commit(&q_empty[qbuf]);   // every score MMA of this item has been issued: Q may be replaced when they are done
       }
     }
   } else {
@@ -220,16 +250,20 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int t = (warp - 2) >> 2;          // query tile
     const int quarter = warp & 3;           // TMEM lanes [32 * quarter, +32) are this warp's
     const int row = quarter * 32 + lane;    // row inside the tile
-    const int q_row = q0 + t * BQ + row;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const uint32_t tmem_s = tmem_base + t * 64 + lane_addr, tmem_o = tmem_base + 128 + t * 64 + lane_addr;
     const float c = g.scale_log2e;
-    float m_ref = 0.f, l_run = 0.f;         // p = exp2(c * s - m_ref)
+    uint32_t done = 0;                      // key blocks this tile has finished so far, over all items: the barriers' phase
     bool ok = true;
-    const int n = t ? nkv1 : nkv0;
+    for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+    const Item it = decode(item);
+    const int h = it.h, b = it.b;
+    const int q_row = it.q0 + t * BQ + row;
+    float m_ref = 0.f, l_run = 0.f;         // p = exp2(c * s - m_ref)
+    const int n = t ? it.nkv1 : it.nkv0;
     for (int j = 0; j < n; ++j) {
       {
-        const bool landed = mbar_wait(&s_full[t], (uint32_t)(j & 1), err, 6);
+        const bool landed = mbar_wait(&s_full[t], done & 1, err, 6);
         if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }   // tcgen05.ld is warp-collective: leave together
       }
       tc_fence_after();
@@ -265,7 +299,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const float m_next = grow ? (m_new == -INFINITY ? 0.f : m_new) : m_ref;
         if (j > 0) {
           // the PV MMAs of block j-1 must have landed before O is touched
-          const bool landed = mbar_wait(&o_done[t], (uint32_t)((j - 1) & 1), err, 7);
+          const bool landed = mbar_wait(&o_done[t], (done - 1) & 1, err, 7);
           if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }
           tc_fence_after();
           const float alpha = fast_exp2(m_ref - m_next);    // 1 for rows that keep their reference
@@ -312,10 +346,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[t]);
+      ++done;
     }
     if (ok && n > 0) {
-      const bool landed = mbar_wait(&o_done[t], (uint32_t)((n - 1) & 1), err, 7);
-      if (__all_sync(0xffffffffu, landed)) {
+      const bool landed = mbar_wait(&o_done[t], (done - 1) & 1, err, 7);
+      if (!__all_sync(0xffffffffu, landed)) {
+        ok = false;
+      } else {
         tc_fence_after();
         const float inv = 1.0f / l_run;   // a fully masked row (l = 0) yields NaN, as the unfused path does
         T* orow_g = reinterpret_cast<T*>(g.o) + (int64_t)b * g.o_sb + (int64_t)h * g.o_sh + (int64_t)q_row * g.o_ss;
@@ -338,6 +375,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
       }
     }
+    if (!ok) break;
+    }   // items
   }
 
   // ---------------------------------------------------------------------- teardown ---
@@ -400,8 +439,9 @@ Status attention(Device* dev, const AttentionParams& p) {
   g.scale_log2e = (float)(p.scale * 1.4426950408889634);
   g.err_flag = dev->kernel_error_flag();
   const int64_t nq = (p.Sq + QT * BQ - 1) / (QT * BQ);
-  const int64_t grid = nq * p.H * p.B;
-  if (grid > 0x7fffffffLL) return Status::Unsupported("attention: too many work items");
+  const int64_t items = nq * p.H * p.B;
+  const int64_t resident = (int64_t)dev->sm_count() * 2;   // persistent: two CTAs per SM walk the work items
+  const int64_t grid = items < resident ? items : resident;
   static std::mutex attr_mu;
   static bool attr_done[2][64] = {};
   cudaError_t e = cudaSuccess;
