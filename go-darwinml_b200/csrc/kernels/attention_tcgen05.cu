@@ -64,6 +64,7 @@ struct AttArgs {
   int B, H, Hkv, Sq, Sk;
   int causal;
   int is_f16;
+  int o_wide;                 // rows of O start on 32-byte boundaries: 256-bit stores
   float scale_log2e;          // scale * log2(e), > 0
   int* err_flag;
 };
@@ -362,14 +363,21 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           tmem_ld32(tmem_o + half * 32, orow);
           tmem_ld_wait();
           if (q_row < g.Sq) {
+            // A thread owns a whole output row, so a warp's store touches 32 rows: write whole 32-byte sectors
+            // (256-bit stores), two per half, rather than 16-byte pieces that the L2 has to merge.
 #pragma unroll
-            for (int d = 0; d < 32; d += 8) {
-              uint4 q;
-              q.x = pack2<T>(__uint_as_float(orow[d]) * inv, __uint_as_float(orow[d + 1]) * inv);
-              q.y = pack2<T>(__uint_as_float(orow[d + 2]) * inv, __uint_as_float(orow[d + 3]) * inv);
-              q.z = pack2<T>(__uint_as_float(orow[d + 4]) * inv, __uint_as_float(orow[d + 5]) * inv);
-              q.w = pack2<T>(__uint_as_float(orow[d + 6]) * inv, __uint_as_float(orow[d + 7]) * inv);
-              *reinterpret_cast<uint4*>(orow_g + half * 32 + d) = q;
+            for (int d = 0; d < 32; d += 16) {
+              uint32_t w[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) w[e] = pack2<T>(__uint_as_float(orow[d + 2 * e]) * inv, __uint_as_float(orow[d + 2 * e + 1]) * inv);
+              if (g.o_wide) {
+                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(orow_g + half * 32 + d), "r"(w[0]), "r"(w[1]),
+                             "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                             : "memory");
+              } else {
+                *reinterpret_cast<uint4*>(orow_g + half * 32 + d) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(orow_g + half * 32 + d + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+              }
             }
           }
         }
@@ -436,6 +444,7 @@ Status attention(Device* dev, const AttentionParams& p) {
   g.B = (int)p.B; g.H = (int)p.H; g.Hkv = (int)p.Hkv; g.Sq = (int)p.Sq; g.Sk = (int)p.Sk;
   g.causal = p.causal ? 1 : 0;
   g.is_f16 = f16 ? 1 : 0;
+  g.o_wide = ((reinterpret_cast<uintptr_t>(p.o) & 31) == 0 && (g.o_sb % 16) == 0 && (g.o_sh % 16) == 0 && (g.o_ss % 16) == 0) ? 1 : 0;
   g.scale_log2e = (float)(p.scale * 1.4426950408889634);
   g.err_flag = dev->kernel_error_flag();
   const int64_t nq = (p.Sq + QT * BQ - 1) / (QT * BQ);
