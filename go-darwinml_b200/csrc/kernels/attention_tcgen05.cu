@@ -64,7 +64,6 @@ struct AttArgs {
   int B, H, Hkv, Sq, Sk;
   int causal;
   int is_f16;
-  int o_wide;                 // rows of O start on 32-byte boundaries: 256-bit stores
   float scale_log2e;          // scale * log2(e), > 0
   int* err_flag;
 };
@@ -93,7 +92,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   unsigned char* sKV = sQ + Q_BUFS * QT * Q_BYTES;       // [KV_STAGES] x (K, V)
   uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + KV_STAGES * 2 * KV_BYTES);
   uint64_t* q_full = bars;                       // [Q_BUFS] the item's queries landed
-  uint64_t* q_empty = q_full + Q_BUFS;           // [Q_BUFS] every score MMA of the item that used the buffer is done
+  uint64_t* q_empty = q_full + Q_BUFS;           // [Q_BUFS] the item's score MMAs are done AND its 8 softmax warps have staged O through the buffer
   uint64_t* kv_full = q_empty + Q_BUFS;          // [KV_STAGES] bytes of K_j and V_j landed
   uint64_t* kv_empty = kv_full + KV_STAGES;      // [KV_STAGES] every MMA that reads the stage is done
   uint64_t* s_full = kv_empty + KV_STAGES;       // [QT] scores of the current block are in TMEM
@@ -137,7 +136,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   };
 
   if (threadIdx.x == 0) {
-    for (int q = 0; q < Q_BUFS; ++q) { mbar_init(&q_full[q], 1); mbar_init(&q_empty[q], 1); }
+    for (int q = 0; q < Q_BUFS; ++q) { mbar_init(&q_full[q], 1); mbar_init(&q_empty[q], 1 + QT * 4); }
     for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
     for (int t = 0; t < QT; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_ready[t], 4); mbar_init(&o_done[t], 1); }
     *failed = 0;
@@ -255,11 +254,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const uint32_t tmem_s = tmem_base + t * 64 + lane_addr, tmem_o = tmem_base + 128 + t * 64 + lane_addr;
     const float c = g.scale_log2e;
     uint32_t done = 0;                      // key blocks this tile has finished so far, over all items: the barriers' phase
+    uint32_t n_item = 0;
     bool ok = true;
-    for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+    for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++n_item) {
     const Item it = decode(item);
     const int h = it.h, b = it.b;
-    const int q_row = it.q0 + t * BQ + row;
+    const int q_row = it.q0 + t * BQ + row;   // the row this thread's softmax works on
     float m_ref = 0.f, l_run = 0.f;         // p = exp2(c * s - m_ref)
     const int n = t ? it.nkv1 : it.nkv0;
     for (int j = 0; j < n; ++j) {
@@ -349,6 +349,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (lane == 0) mbar_arrive(&p_ready[t]);
       ++done;
     }
+    // Epilogue.  A thread owns a whole output row, so storing from registers would scatter every store instruction over
+    // 32 rows.  The item's query tile in shared memory is dead by now (every score MMA has finished), so the warp
+    // stages its 32 normalised rows there (16-byte chunks XOR-swizzled by row: conflict-free) and writes them back
+    // transposed, 4 rows x 128 contiguous bytes per instruction.  The buffer goes back to the loader only when the
+    // issuer AND all eight softmax warps have released it (q_empty counts nine arrivals).
+    const int qbuf = (int)(n_item & 1);
     if (ok && n > 0) {
       const bool landed = mbar_wait(&o_done[t], (done - 1) & 1, err, 7);
       if (!__all_sync(0xffffffffu, landed)) {
@@ -356,33 +362,37 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       } else {
         tc_fence_after();
         const float inv = 1.0f / l_run;   // a fully masked row (l = 0) yields NaN, as the unfused path does
-        T* orow_g = reinterpret_cast<T*>(g.o) + (int64_t)b * g.o_sb + (int64_t)h * g.o_sh + (int64_t)q_row * g.o_ss;
+        unsigned char* stage = sQ + (qbuf * QT + t) * Q_BYTES + quarter * 32 * 128;   // this warp's 32 rows x 128 bytes
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           uint32_t orow[32];
           tmem_ld32(tmem_o + half * 32, orow);
           tmem_ld_wait();
-          if (q_row < g.Sq) {
-            // A thread owns a whole output row, so a warp's store touches 32 rows: write whole 32-byte sectors
-            // (256-bit stores), two per half, rather than 16-byte pieces that the L2 has to merge.
 #pragma unroll
-            for (int d = 0; d < 32; d += 16) {
-              uint32_t w[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) w[e] = pack2<T>(__uint_as_float(orow[d + 2 * e]) * inv, __uint_as_float(orow[d + 2 * e + 1]) * inv);
-              if (g.o_wide) {
-                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(orow_g + half * 32 + d), "r"(w[0]), "r"(w[1]),
-                             "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
-                             : "memory");
-              } else {
-                *reinterpret_cast<uint4*>(orow_g + half * 32 + d) = make_uint4(w[0], w[1], w[2], w[3]);
-                *reinterpret_cast<uint4*>(orow_g + half * 32 + d + 8) = make_uint4(w[4], w[5], w[6], w[7]);
-              }
-            }
+          for (int q = 0; q < 4; ++q) {
+            uint4 v;
+            v.x = pack2<T>(__uint_as_float(orow[8 * q]) * inv, __uint_as_float(orow[8 * q + 1]) * inv);
+            v.y = pack2<T>(__uint_as_float(orow[8 * q + 2]) * inv, __uint_as_float(orow[8 * q + 3]) * inv);
+            v.z = pack2<T>(__uint_as_float(orow[8 * q + 4]) * inv, __uint_as_float(orow[8 * q + 5]) * inv);
+            v.w = pack2<T>(__uint_as_float(orow[8 * q + 6]) * inv, __uint_as_float(orow[8 * q + 7]) * inv);
+            *reinterpret_cast<uint4*>(stage + lane * 128 + (((half * 4 + q) ^ (lane & 7)) << 4)) = v;
           }
         }
+        __syncwarp();
+        const int chunk = lane & 7;
+#pragma unroll
+        for (int pass = 0; pass < 8; ++pass) {
+          const int rl = pass * 4 + (lane >> 3);              // row inside the warp's 32
+          const int64_t qr = (int64_t)it.q0 + t * BQ + quarter * 32 + rl;
+          const uint4 v = *reinterpret_cast<const uint4*>(stage + rl * 128 + ((chunk ^ (rl & 7)) << 4));
+          if (qr < g.Sq)
+            *reinterpret_cast<uint4*>(reinterpret_cast<T*>(g.o) + (int64_t)b * g.o_sb + (int64_t)h * g.o_sh + qr * g.o_ss + chunk * 8) = v;
+        }
+        fence_proxy_async_smem();   // the next writer of this buffer is a TMA load
       }
     }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&q_empty[qbuf]);   // also for an idle tile and after a failed wait: the loader counts nine
     if (!ok) break;
     }   // items
   }
@@ -444,7 +454,6 @@ Status attention(Device* dev, const AttentionParams& p) {
   g.B = (int)p.B; g.H = (int)p.H; g.Hkv = (int)p.Hkv; g.Sq = (int)p.Sq; g.Sk = (int)p.Sk;
   g.causal = p.causal ? 1 : 0;
   g.is_f16 = f16 ? 1 : 0;
-  g.o_wide = ((reinterpret_cast<uintptr_t>(p.o) & 31) == 0 && (g.o_sb % 16) == 0 && (g.o_sh % 16) == 0 && (g.o_ss % 16) == 0) ? 1 : 0;
   g.scale_log2e = (float)(p.scale * 1.4426950408889634);
   g.err_flag = dev->kernel_error_flag();
   const int64_t nq = (p.Sq + QT * BQ - 1) / (QT * BQ);
