@@ -71,3 +71,21 @@ def test_two_gloo_ranks_shard_and_aggregate(tmp_path):
     value, worst, m0, m1 = np.load(tmp_path / "agg.npy")
     assert worst == 20.0 and m0 == 20.0 and m1 == 1.0                     # max over ranks
     assert value == pytest.approx(logits.size / 20e-3)                    # all ranks' units / slowest rank's time
+
+
+def test_column_sharded_matmul_rejects_bad_arguments_before_touching_a_gpu():
+    # the constructor validates the layout first; these never reach the device
+    import numpy as np
+    import pytest
+
+    from go_darwinml_b200.sharding import ColumnShardedMatmul
+
+    def never(*_a, **_k):
+        raise AssertionError("exchange / barrier must not be called for a rejected layout")
+
+    with pytest.raises(ValueError, match="multiple of 8"):
+        ColumnShardedMatmul(None, 0, 0, 2, 128, 12, 64, np.float16, never, never)
+    with pytest.raises(ValueError, match="bad rank"):
+        ColumnShardedMatmul(None, 0, 2, 2, 128, 16, 64, np.float16, never, never)
+    with pytest.raises(ValueError, match="bad rank"):
+        ColumnShardedMatmul(None, 0, 0, 9, 128, 16, 64, np.float16, never, never)
