@@ -87,7 +87,12 @@ class Device {
  public:
   static Status Get(int ordinal, Device** out);
   int ordinal() const { return ordinal_; }
-  cudaStream_t stream() const { return stream_; }
+  // The stream work is enqueued on: the device's one compute stream, except inside a StreamOverride of the calling
+  // thread (used to record a launch plan into a CUDA graph on a private stream, so that work other threads enqueue on
+  // the compute stream meanwhile is not swept into the recording).
+  cudaStream_t stream() const;
+  cudaStream_t compute_stream() const { return stream_; }
+  Status CaptureStream(cudaStream_t* out);
   // Two extra streams for host<->device copies that overlap the compute stream (created on first use).
   Status CopyStreams(cudaStream_t* in, cudaStream_t* out);
   int sm_count() const { return sm_count_; }
@@ -113,13 +118,22 @@ class Device {
   int ordinal_ = 0;
   int sm_count_ = 148;
   cudaStream_t stream_ = nullptr;
-  cudaStream_t copy_in_ = nullptr, copy_out_ = nullptr;
+  cudaStream_t copy_in_ = nullptr, copy_out_ = nullptr, capture_ = nullptr;
   int* error_flag_ = nullptr;
   bool error_check_pending_ = false;
   std::mutex mu_;
   std::multimap<int64_t, void*> free_blocks_;  // size -> ptr
   std::map<void*, int64_t> live_blocks_;       // ptr -> size
   int64_t reserved_ = 0;
+};
+
+// While alive, Device::stream() of `dev` returns `s` on this thread only.
+class StreamOverride {
+ public:
+  StreamOverride(const Device* dev, cudaStream_t s);
+  ~StreamOverride();
+  StreamOverride(const StreamOverride&) = delete;
+  StreamOverride& operator=(const StreamOverride&) = delete;
 };
 
 struct Buffer {

@@ -1817,16 +1817,23 @@ static bool execute_impl(B200Exec exec, const B200Buffer* inputs, int num_inputs
     Status gs = ex->dev->MakeCurrent();
     if (!gs.ok()) return fail(gs);
     if (!hit && key == ex->last_key) {
-      // second run on these addresses: record the plan instead of launching it
+      // second run on these addresses: record the plan instead of launching it.  The recording happens on a private
+      // stream that only this thread sees as the device's stream, so work other threads enqueue on the compute stream
+      // meanwhile stays out of it.
       cudaGraph_t graph = nullptr;
-      cudaError_t ce = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal);
+      cudaStream_t cs = nullptr;
+      cudaError_t ce = ex->dev->CaptureStream(&cs).ok() ? cudaSuccess : cudaErrorUnknown;
+      if (ce == cudaSuccess) ce = cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal);
       if (ce == cudaSuccess) {
         Status rs = Status::OK();
-        for (auto& st : ex->steps) {
-          rs = st.run(ex->dev, ptrs.data());
-          if (!rs.ok()) { rs = Status{rs.code, st.desc + ": " + rs.msg}; break; }
+        {
+          StreamOverride record_on(ex->dev, cs);
+          for (auto& st : ex->steps) {
+            rs = st.run(ex->dev, ptrs.data());
+            if (!rs.ok()) { rs = Status{rs.code, st.desc + ": " + rs.msg}; break; }
+          }
         }
-        ce = cudaStreamEndCapture(stream, &graph);
+        ce = cudaStreamEndCapture(cs, &graph);
         if (!rs.ok() && ce == cudaSuccess) ce = cudaErrorStreamCaptureInvalidated;   // a step refused to record: plain path below
         cudaGraphExec_t gexec = nullptr;
         if (ce == cudaSuccess) ce = cudaGraphInstantiate(&gexec, graph, 0);

@@ -65,6 +65,32 @@ Status Device::Get(int ordinal, Device** out) {
   return Status::OK();
 }
 
+namespace {
+thread_local const Device* tls_override_dev = nullptr;
+thread_local cudaStream_t tls_override_stream = nullptr;
+}  // namespace
+
+cudaStream_t Device::stream() const { return (tls_override_dev == this && tls_override_stream) ? tls_override_stream : stream_; }
+
+StreamOverride::StreamOverride(const Device* dev, cudaStream_t s) {
+  tls_override_dev = dev;
+  tls_override_stream = s;
+}
+StreamOverride::~StreamOverride() {
+  tls_override_dev = nullptr;
+  tls_override_stream = nullptr;
+}
+
+Status Device::CaptureStream(cudaStream_t* out) {
+  std::lock_guard<std::mutex> lock(mu_);
+  if (!capture_) {
+    B200_CUDA_TRY(cudaSetDevice(ordinal_));
+    B200_CUDA_TRY(cudaStreamCreateWithFlags(&capture_, cudaStreamNonBlocking));
+  }
+  *out = capture_;
+  return Status::OK();
+}
+
 Status Device::CopyStreams(cudaStream_t* in, cudaStream_t* out) {
   std::lock_guard<std::mutex> lock(mu_);
   if (!copy_in_) {

@@ -952,3 +952,51 @@ def test_donated_cache_is_updated_in_place(b200, backend):
         bc = out
     with pytest.raises(b200.BackendError):
         exe.Execute([bc, bn, bp], [True, False], 0)
+
+
+def test_concurrent_executes_do_not_leak_into_each_others_graph_recording(b200, backend):
+    # two host threads drive two executables on the same device while each plan gets recorded into a CUDA graph: the
+    # recording runs on a private stream, so the other thread's launches must neither be swallowed nor replayed
+    import threading
+    rng = np.random.default_rng(106)
+
+    def make(tag, scale):
+        builder = backend.Builder(tag)
+        f = builder.Main()
+        p = f.Parameter("x", _S(b200, np.float32, 256, 128))
+        y = f.FusedSoftmax(p, 1)
+        y = f.ReduceSum(f.Mul(y, f.BroadcastInDim(f.Constant(np.array([scale], dtype=np.float32), 1), _S(b200, np.float32, 256, 128), [1])), 1)
+        z = f.FusedLayerNorm(f.Tanh(p), [-1], 1e-5, None, None)
+        w = f.ArgMinMax(z, 1, b200.dtypes.Int32, True)
+        f.Return([y, z, w], None)
+        return builder.Compile()
+
+    exes = [make("conc_a", 2.0), make("conc_b", 3.0)]
+    xs = [rng_array(rng, (256, 128), np.float32) for _ in exes]
+    bufs = [backend.FromNumpy(x) for x in xs]
+    ref = []
+    for exe, buf in zip(exes, bufs):
+        outs = exe.Execute([buf], None, 0)
+        ref.append([backend.ToNumpy(o) for o in outs])
+        for o in outs:
+            backend.BufferFinalize(o)
+    errors = []
+
+    def worker(i):
+        try:
+            for _ in range(25):
+                outs = exes[i].Execute([bufs[i]], None, 0)
+                vals = [backend.ToNumpy(o) for o in outs]
+                for o in outs:
+                    backend.BufferFinalize(o)
+                for a, b_ in zip(vals, ref[i]):
+                    np.testing.assert_array_equal(a, b_)
+        except Exception as e:  # noqa: BLE001
+            errors.append((i, repr(e)))
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
