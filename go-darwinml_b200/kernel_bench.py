@@ -4,6 +4,7 @@
   python go-darwinml_b200/kernel_bench.py rmsnorm  --rows 16384 --cols 4096 --dtype bf16
   python go-darwinml_b200/kernel_bench.py layernorm --rows 16384 --cols 4096 --dtype bf16
   python go-darwinml_b200/kernel_bench.py gemm --batch 8 --m 4096 --n 4096 --k 4096 --dtype bf16 [--a-km] [--b-nk]
+  python go-darwinml_b200/kernel_bench.py copy --rows 16384 --cols 4096 --dtype bf16    # yardstick, not a kernel of this library
 
 Inputs are seeded random tensors resident in HBM; timing is CUDA events on the
 library's stream after warm-up; between timed launches an L2-sized buffer is
@@ -31,7 +32,7 @@ DT = {"f32": (7, 4), "bf16": (6, 2), "f16": (5, 2)}
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["softmax", "rmsnorm", "layernorm", "gemm", "attention", "ewise"])
+    ap.add_argument("kernel", choices=["softmax", "rmsnorm", "layernorm", "gemm", "attention", "ewise", "copy"])
     ap.add_argument("--rows", type=int, default=65536)
     ap.add_argument("--cols", type=int, default=1024)
     ap.add_argument("--seq-q", type=int, default=0)
@@ -98,6 +99,16 @@ def main():
             else:
                 check(L.b200_k_layer_norm(args.device, x.data_ptr(), g.data_ptr(), b.data_ptr(), y.data_ptr(), args.rows, args.cols, code, 1e-6,
                                           ctypes.byref(e)), e)
+    elif args.kernel == "copy":
+        # Yardstick only: the CUDA runtime's device-to-device copy of a [rows, cols] tensor, timed like the kernels above.
+        # It shows what fraction of the measured peak (taken on a far larger copy) a plain copy of THIS size reaches.
+        x, y = rand(args.rows, args.cols), torch.empty(args.rows, args.cols, device=f"cuda:{args.device}", dtype=tdt)
+        work, unit, kind = 2 * args.rows * args.cols * es, "GB/s", "hbm"
+        operand_bytes = work
+
+        def launch():
+            with torch.cuda.stream(stream):
+                y.copy_(x, non_blocking=True)
     elif args.kernel == "ewise":
         # a fused elementwise chain compiled through the graph layer (one launch); bytes = distinct inputs + output
         npdt = {"f32": np.float32, "bf16": __import__("ml_dtypes").bfloat16, "f16": np.float16}[args.dtype]
