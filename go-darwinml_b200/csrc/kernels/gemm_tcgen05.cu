@@ -17,8 +17,9 @@
 //   warp 1     issuer: one lane issues tcgen05.mma (M=128, N=256, K=16 per instruction)
 //              from shared-memory descriptors into a TMEM accumulator; tcgen05.commit
 //              releases ring stages ("empty") and publishes finished accumulators;
-//   warps 2-9  epilogue: tcgen05.ld the accumulator (each warp 32 TMEM lanes x 128 columns),
-//              add bias, apply the activation, round, store 16-byte vectors.
+//   warps 2-   epilogue: tcgen05.ld the accumulator (a warp reaches the 32 TMEM lanes of its quarter), add bias,
+//              apply the activation, round, store 16-byte vectors.  Sixteen warps of 64 columns in this kernel
+//              (short K: the epilogue is the critical path), eight of 128 columns in the CTA-pair kernel below.
 // TMEM holds two 256-column accumulators, so the epilogue of tile i overlaps the
 // main loop of tile i+1.  Tensor-core bound: flops = 2 * batch * M * N * K.
 //
@@ -62,6 +63,12 @@ constexpr int EPI_STAGE_FLOATS = 16 * EPI_PITCH;  // per epilogue warp: 16 rows 
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + EPI_WARPS * EPI_STAGE_FLOATS * 4;
 constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;   // producer warp, issuer warp, epilogue warps
 constexpr int TMEM_COLS = 512;
+// the single-CTA kernel: sixteen epilogue warps, four per TMEM lane quarter (64 columns each)
+constexpr int S_EPI_WARPS = 16;
+constexpr int S_EPI_PITCH = 20;                      // words per scratch row: 16 + 4
+constexpr int S_EPI_STAGE_WORDS = 16 * S_EPI_PITCH;  // per warp: 16 rows x 16 words
+constexpr int S_SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + S_EPI_WARPS * S_EPI_STAGE_WORDS * 4;
+constexpr int S_NUM_THREADS = 64 + 32 * S_EPI_WARPS;
 
 }  // namespace
 
@@ -93,17 +100,25 @@ struct TcArgs {
 __constant__ int kPlaneA[6] = {0, 2, 1, 0, 1, 0};
 __constant__ int kPlaneB[6] = {2, 0, 1, 1, 0, 0};
 
-__device__ __forceinline__ void tile_coords(const TcArgs& g, int64_t t, int* b, int* m_t, int* n_t) {
-  const int per_batch = g.tiles_m * g.tiles_n;
-  *b = (int)(t / per_batch);
-  const int r = (int)(t % per_batch);
-  constexpr int GROUP = 16;  // m-tiles per super-row: CTAs running together share A and B panels in L2
-  const int group_size = GROUP * g.tiles_n;
-  const int first_m = (r / group_size) * GROUP;
-  const int gm = (g.tiles_m - first_m) < GROUP ? (g.tiles_m - first_m) : GROUP;
-  const int in_group = r % group_size;
-  *m_t = first_m + in_group % gm;
-  *n_t = in_group / gm;
+// Runs once per tile in the producer thread and in every epilogue warp (a few hundred dependent instructions with
+// 64-bit divisions): 32-bit unsigned arithmetic, three divisions, the remainders by multiply-subtract.  The launcher
+// refuses tile counts of 2^31 and more.
+__device__ __forceinline__ void tile_coords(const TcArgs& g, int64_t t64, int* b, int* m_t, int* n_t) {
+  constexpr uint32_t GROUP = 16;  // m-tiles per super-row: CTAs running together share A and B panels in L2
+  const uint32_t t = (uint32_t)t64;
+  const uint32_t tiles_m = (uint32_t)g.tiles_m, tiles_n = (uint32_t)g.tiles_n;
+  const uint32_t per_batch = tiles_m * tiles_n;
+  const uint32_t bi = t / per_batch;
+  const uint32_t r = t - bi * per_batch;
+  const uint32_t group_size = GROUP * tiles_n;
+  const uint32_t gidx = r / group_size;
+  const uint32_t in_group = r - gidx * group_size;
+  const uint32_t first_m = gidx * GROUP;
+  const uint32_t gm = (tiles_m - first_m) < GROUP ? (tiles_m - first_m) : GROUP;
+  const uint32_t ni = in_group / gm;
+  *b = (int)bi;
+  *m_t = (int)(first_m + in_group - ni * gm);
+  *n_t = (int)ni;
 }
 
 template <typename OutT> __device__ __forceinline__ float load_bias(const void* bias, int64_t col) {
@@ -149,15 +164,15 @@ template <> __device__ __forceinline__ uint32_t add_residual_word<__half>(uint32
   return mul ? pack_word<__half>(a.x * b.x, a.y * b.y) : pack_word<__half>(a.x + b.x, a.y + b.y);
 }
 
-// 32 consecutive bias values starting at col (col is a multiple of 32 and col + 32 <= N is NOT assumed: tail guarded).
-template <typename OutT>
-__device__ __forceinline__ void add_bias32(const TcArgs& g, int64_t col, float* v) {
-  if (g.vec_store && col + 32 <= g.N) {
+// NC consecutive bias values starting at col (col is a multiple of NC; col + NC <= N is NOT assumed: tail guarded).
+template <typename OutT, int NC>
+__device__ __forceinline__ void add_bias_n(const TcArgs& g, int64_t col, float* v) {
+  if (g.vec_store && col + NC <= g.N) {
     // 16-byte loads; every lane reads the same addresses (one broadcast transaction each)
     const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const OutT*>(g.bias) + col);
     constexpr int kPerVec = 16 / (int)sizeof(OutT);
 #pragma unroll
-    for (int q = 0; q < 32 / kPerVec; ++q) {
+    for (int q = 0; q < NC / kPerVec; ++q) {
       const uint4 w = __ldg(src + q);
       const OutT* e = reinterpret_cast<const OutT*>(&w);
 #pragma unroll
@@ -165,10 +180,12 @@ __device__ __forceinline__ void add_bias32(const TcArgs& g, int64_t col, float* 
     }
   } else {
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
+    for (int j = 0; j < NC; ++j)
       if (col + j < g.N) v[j] += load_bias<OutT>(g.bias, col + j);
   }
 }
+template <typename OutT>
+__device__ __forceinline__ void add_bias32(const TcArgs& g, int64_t col, float* v) { add_bias_n<OutT, 32>(g, col, v); }
 
 // One epilogue warp drains its 32 TMEM lanes x 128 columns (half `chalf`) of a finished 128 x 256 accumulator: bias,
 // activation, rounding, stores.  row0 is the first row of C held by lane 0 of this CTA's accumulator; `stage` is the
@@ -307,8 +324,143 @@ __device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem
   }
 }
 
+// The single-CTA kernel's epilogue.  That kernel runs the short-K shapes, where a tile's main loop is no longer than
+// its epilogue and the epilogue is a chain of dependent instructions (TMEM read, rounding, staging, write-out) that a
+// scheduler with two warps cannot keep issuing: SIXTEEN warps share a tile, four per TMEM lane quarter, 64 columns each,
+// in sub-steps of 16 words per row (32 16-bit columns or 16 fp32 columns) so that a thread stays under 112 registers.
+// Same data path as above with narrower rows: 16 rows x 16 words per staging round (20-word pitch: conflict-free 16-byte
+// accesses), written back 8 rows x 64 contiguous bytes per store instruction.
 template <typename OutT>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__device__ __forceinline__ void drain_accumulator_narrow(const TcArgs& g, uint32_t tmem_acc, int64_t row0, int64_t n0, int b, int quarter,
+                                                         int cq, int lane, uint32_t* stage) {
+  using Tr = OutTraits<OutT>;
+  constexpr int CPW = Tr::kColsPerWord;
+  constexpr int SUB_COLS = 16 * CPW;            // columns per sub-step: 16 words per row
+  constexpr int WARP_COLS = BN / 4;             // columns per warp
+  constexpr int SUBS = WARP_COLS / SUB_COLS;
+  const uint32_t taddr = tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(cq * WARP_COLS);
+  const int64_t row_base = row0 + quarter * 32;
+  OutT* cbase = reinterpret_cast<OutT*>(g.c) + ((int64_t)b * g.M + row_base) * g.ldc;
+  const OutT* rbase = g.residual ? reinterpret_cast<const OutT*>(g.residual) + ((int64_t)b * g.M + row_base) * g.ldc : nullptr;
+  const int wg = (lane & 3) * 4;                // write-out: this lane's 4 words of a 16-word row
+  const int rsub = lane >> 2;                   // write-out: row within a pass of 8 rows
+  // per-store work is kept to a pointer increment and a 32-bit compare: the epilogue is bound by instruction issue
+  const int rows_left = (int)((g.M - row_base) < 32 ? (g.M - row_base) : 32);
+  const int64_t pass_stride = 8 * g.ldc;
+#pragma unroll 1
+  for (int sub = 0; sub < SUBS; ++sub) {
+    const int64_t col0 = n0 + cq * WARP_COLS + sub * SUB_COLS;
+    if (col0 >= g.N) break;  // uniform across the warp
+    const int64_t col = col0 + (int64_t)wg * CPW;
+    // the residual block of this sub-step, fetched first in the write-out layout (latency hides under the TMEM read)
+    const bool col_ok = col < g.N;
+    const int64_t first = (int64_t)rsub * g.ldc + col;   // element offset of this lane's vector in pass 0
+    uint4 rv[4];
+    if (rbase && g.vec_store) {
+#pragma unroll
+      for (int pass = 0; pass < 4; ++pass)
+        rv[pass] = (col_ok && pass * 8 + rsub < rows_left) ? __ldg(reinterpret_cast<const uint4*>(rbase + first + pass * pass_stride))
+                                                           : make_uint4(0, 0, 0, 0);
+    }
+    uint32_t words[16];
+    {
+      uint32_t r[SUB_COLS];
+      if constexpr (CPW == 2) tmem_ld32(taddr + sub * SUB_COLS, r);
+      else tmem_ld16(taddr + sub * SUB_COLS, r);
+      tmem_ld_wait();
+      float v[SUB_COLS];
+#pragma unroll
+      for (int j = 0; j < SUB_COLS; ++j) v[j] = __uint_as_float(r[j]);
+      if (g.bias) add_bias_n<OutT, SUB_COLS>(g, col0, v);
+      apply_activation_n<SUB_COLS, Tr::kFast>(g.activation, v);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if constexpr (CPW == 2) words[j] = pack_word<OutT>(v[2 * j], v[2 * j + 1]);
+        else words[j] = pack_word<OutT>(v[j], 0.f);
+      }
+    }
+#pragma unroll
+    for (int round = 0; round < 2; ++round) {
+      if ((lane >> 4) == round) {
+#pragma unroll
+        for (int j = 0; j < 16; j += 4)
+          *reinterpret_cast<uint4*>(stage + (lane & 15) * S_EPI_PITCH + j) = make_uint4(words[j], words[j + 1], words[j + 2], words[j + 3]);
+      }
+      __syncwarp();
+      if (g.vec_store) {
+#pragma unroll
+        for (int pass = 0; pass < 2; ++pass) {
+          const int rl = pass * 8 + rsub;
+          const int rr = round * 16 + rl;
+          uint4 q = *reinterpret_cast<const uint4*>(stage + rl * S_EPI_PITCH + wg);
+          if (col_ok && rr < rows_left) {
+            if (rbase) {
+              const uint4 rq = rv[round * 2 + pass];
+              q.x = add_residual_word<OutT>(q.x, rq.x, g.residual_mul);
+              q.y = add_residual_word<OutT>(q.y, rq.y, g.residual_mul);
+              q.z = add_residual_word<OutT>(q.z, rq.z, g.residual_mul);
+              q.w = add_residual_word<OutT>(q.w, rq.w, g.residual_mul);
+            }
+            const int64_t off = first + (round * 2 + pass) * pass_stride;
+            *reinterpret_cast<uint4*>(cbase + off) = q;
+            if (g.num_c_extra > 0) {
+              // the same vector to every other rank's copy: plain stores to peer-mapped memory (NVLink)
+              for (int x = 0; x < g.num_c_extra; ++x)
+                *reinterpret_cast<uint4*>(reinterpret_cast<OutT*>(g.c_extra[x]) + ((int64_t)b * g.M + row_base) * g.ldc + off) = q;
+            }
+          }
+        }
+      } else {
+        // Rows of C do not start 16-byte aligned: 4 bytes per lane, two rows per store instruction (lanes 0-15 one row,
+        // lanes 16-31 the next).  A 16-bit row that starts on an odd element is 2 bytes off the word grid: its words are
+        // re-cut from neighbouring staged words (funnel shift) and the two end elements go out as 2-byte stores.
+        const int l16 = lane & 15;
+#pragma unroll 2
+        for (int it = 0; it < 8; ++it) {
+          const int rl = it * 2 + (lane >> 4);
+          const int rr = round * 16 + rl;
+          if (row_base + rr >= g.M) continue;
+          OutT* crow = cbase + (int64_t)rr * g.ldc;
+          const OutT* rrow = rbase ? rbase + (int64_t)rr * g.ldc : nullptr;
+          if constexpr (CPW == 1) {
+            const int64_t c1 = col0 + l16;
+            if (c1 < g.N) {
+              uint32_t w = stage[rl * S_EPI_PITCH + l16];
+              if (rbase) w = add_residual_word<OutT>(w, reinterpret_cast<const uint32_t*>(rrow)[c1], g.residual_mul);
+              reinterpret_cast<uint32_t*>(crow)[c1] = w;
+            }
+          } else {
+            const uint32_t odd = (uint32_t)((((int64_t)b * g.M + row_base + rr) * g.ldc + col0) & 1);
+            const uint32_t w0 = stage[rl * S_EPI_PITCH + l16];
+            const uint32_t w1 = stage[rl * S_EPI_PITCH + l16 + 1];  // lane 15 reads a pad word: unused
+            uint32_t w = odd ? __funnelshift_r(w0, w1, 16) : w0;    // elements (2 l16 + odd, 2 l16 + odd + 1)
+            const int64_t c1 = col0 + 2 * l16 + odd;
+            uint16_t* c16 = reinterpret_cast<uint16_t*>(crow);
+            const uint16_t* r16 = reinterpret_cast<const uint16_t*>(rrow);
+            const bool pair_ok = c1 + 1 < g.N && !(odd && l16 == 15);
+            if (pair_ok) {
+              if (rbase) w = add_residual_word<OutT>(w, (uint32_t)r16[c1] | ((uint32_t)r16[c1 + 1] << 16), g.residual_mul);
+              *reinterpret_cast<uint32_t*>(c16 + c1) = w;   // (row start + 2 l16 + odd) is even: 4-byte aligned
+            } else if (c1 < g.N) {
+              uint32_t lo = w & 0xffffu;                    // the last column of the row, or element 31 of an odd row
+              if (rbase) lo = add_residual_word<OutT>(lo, r16[c1], g.residual_mul) & 0xffffu;
+              c16[c1] = (uint16_t)lo;
+            }
+            if (odd && l16 == 0 && col0 < g.N) {           // element 0 of an odd row
+              uint32_t lo = w0 & 0xffffu;
+              if (rbase) lo = add_residual_word<OutT>(lo, r16[col0], g.residual_mul) & 0xffffu;
+              c16[col0] = (uint16_t)lo;
+            }
+          }
+        }
+      }
+      __syncwarp();
+    }
+  }
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(S_NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const TcArgs g) {
   extern __shared__ unsigned char smem_raw[];
   // operand tiles need 1024-byte alignment for the 128-byte swizzle
@@ -319,14 +471,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   uint64_t* acc_full = bars + 2 * STAGES;   // [2]       accumulator complete
   uint64_t* acc_empty = bars + 2 * STAGES + 2;  // [2]   accumulator drained by the epilogue
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
-  float* epi_stage = reinterpret_cast<float*>(tiles + STAGES * STAGE_BYTES + 256);
+  uint32_t* epi_stage = reinterpret_cast<uint32_t*>(tiles + STAGES * STAGE_BYTES + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* err = g.err_flag;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], EPI_WARPS); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], S_EPI_WARPS); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -432,8 +584,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const bool landed = mbar_wait(&acc_full[acc], acc_phase, err, 4);
       if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }  // the warp leaves together: tcgen05.ld is warp-collective
       tc_fence_after();
-      drain_accumulator<OutT>(g, tmem_base + acc * BN, (int64_t)m_t * BM, (int64_t)n_t * BN, b, quarter, (warp - 2) >> 2, lane,
-                              epi_stage + (warp - 2) * EPI_STAGE_FLOATS);
+      drain_accumulator_narrow<OutT>(g, tmem_base + acc * BN, (int64_t)m_t * BM, (int64_t)n_t * BN, b, quarter, (warp - 2) >> 2, lane,
+                                     epi_stage + (warp - 2) * S_EPI_STAGE_WORDS);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
@@ -704,6 +856,8 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
   if (p.m > 0x7fffffffLL || p.n > 0x7fffffffLL || p.k > 0x7fffffffLL || p.batch > 0x7fffffffLL) return Status::OK();
   // tiny problems are latency-bound either way; leave them to the SIMT kernel
   if ((double)p.batch * p.m * p.n * p.k < 64.0 * 64.0 * 64.0) return Status::OK();
+  // tile coordinates are computed in 32-bit arithmetic on the device
+  if ((double)p.batch * (double)((p.m + BM - 1) / BM) * (double)((p.n + BN - 1) / BN) >= 2147483648.0) return Status::OK();
   *taken = true;
 
   B200_TRY(dev->MakeCurrent());
@@ -783,12 +937,12 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
     {                                                                                                                       \
       std::lock_guard<std::mutex> lock(attr_mu);                                                                            \
       if (!attr_done[SLOT][dev->ordinal()]) {                                                                               \
-        e = cudaFuncSetAttribute(gemm_tcgen05_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);       \
+        e = cudaFuncSetAttribute(gemm_tcgen05_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, S_SMEM_BYTES);       \
         attr_done[SLOT][dev->ordinal()] = (e == cudaSuccess);                                                               \
       }                                                                                                                     \
     }                                                                                                                       \
     const int64_t grid = g.total_tiles < dev->sm_count() ? g.total_tiles : dev->sm_count();                                 \
-    if (e == cudaSuccess) gemm_tcgen05_kernel<OutT><<<(unsigned)grid, NUM_THREADS, SMEM_BYTES, stream>>>(tm_a, tm_b, g);     \
+    if (e == cudaSuccess) gemm_tcgen05_kernel<OutT><<<(unsigned)grid, S_NUM_THREADS, S_SMEM_BYTES, stream>>>(tm_a, tm_b, g); \
   } while (0)
 #define LAUNCH_TC_PAIR(OutT, SLOT)                                                                                          \
   do {                                                                                                                      \

@@ -43,6 +43,8 @@ def main():
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--a-km", action="store_true", help="A stored [batch, K, M]")
     ap.add_argument("--b-nk", action="store_true", help="B stored [batch, N, K]")
+    ap.add_argument("--act", default="none", choices=["none", "gelu", "relu", "silu", "tanh"],
+                    help="gemm: add a bias [N] and this activation in the epilogue (a dense layer)")
     ap.add_argument("--expr", default="add", choices=["add", "bias", "rope", "chain"], help="ewise: which fused chain to time")
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
@@ -171,10 +173,13 @@ def main():
         work, unit, kind = 2 * B * M * N * K, "TFLOP/s", "tensor"
         operand_bytes = (a.numel() + bb.numel() + c.numel()) * es
 
+        act = ["none", "gelu", "relu", "silu", "tanh"].index(args.act)
+        bias = rand(N) if act else None
+
         def launch():
             e = libmod.B200Error()
             check(L.b200_k_gemm(args.device, a.data_ptr(), bb.data_ptr(), c.data_ptr(), B, M, N, K, int(not args.a_km), int(args.b_nk), code,
-                                None, 0, ctypes.byref(e)), e)
+                                bias.data_ptr() if act else None, act, ctypes.byref(e)), e)
 
     torch.cuda.synchronize()
     flush = None
