@@ -62,6 +62,7 @@ struct AttArgs {
   void* o;
   int64_t o_sb, o_sh, o_ss;   // element strides of O along batch, head, sequence (head dim contiguous)
   int B, H, Hkv, Sq, Sk;
+  int group;                  // query heads per KV head: H / Hkv
   int causal;
   int is_f16;
   float scale_log2e;          // scale * log2(e), > 0
@@ -116,11 +117,16 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   };
   auto decode = [&](int64_t item) {
     Item it;
-    const int qb = nq - 1 - (int)(item / heads_total);
-    const int64_t hb = item % heads_total;
-    it.h = (int)(hb % g.H);
-    it.b = (int)(hb / g.H);
-    it.hkv = it.h / (g.H / g.Hkv);
+    // 32-bit unsigned arithmetic (the launcher refuses 2^31 items and more): this runs once per item in the
+    // single-thread loader and issuer, where a 64-bit division is some hundred dependent instructions
+    const uint32_t item32 = (uint32_t)item, ht32 = (uint32_t)heads_total, H32 = (uint32_t)g.H;
+    const uint32_t qi = item32 / ht32;
+    const uint32_t hb = item32 - qi * ht32;
+    const uint32_t bi = hb / H32;
+    const int qb = nq - 1 - (int)qi;
+    it.h = (int)(hb - bi * H32);
+    it.b = (int)bi;
+    it.hkv = (int)((uint32_t)it.h / (uint32_t)g.group);
     it.q0 = qb * QT * BQ;
     // key blocks each tile walks: under a causal mask keys beyond the tile's last row are masked for every row
     auto blocks_of = [&](int t) {
@@ -452,12 +458,14 @@ Status attention(Device* dev, const AttentionParams& p) {
   g.o = p.o;
   strides(p.Sq, p.H, &g.o_sb, &g.o_sh, &g.o_ss);
   g.B = (int)p.B; g.H = (int)p.H; g.Hkv = (int)p.Hkv; g.Sq = (int)p.Sq; g.Sk = (int)p.Sk;
+  g.group = (int)(p.H / p.Hkv);
   g.causal = p.causal ? 1 : 0;
   g.is_f16 = f16 ? 1 : 0;
   g.scale_log2e = (float)(p.scale * 1.4426950408889634);
   g.err_flag = dev->kernel_error_flag();
   const int64_t nq = (p.Sq + QT * BQ - 1) / (QT * BQ);
   const int64_t items = nq * p.H * p.B;
+  if (items >= 2147483648LL) return Status::Unsupported("attention: more than 2^31 work items");
   const int64_t resident = (int64_t)dev->sm_count() * 2;   // persistent: two CTAs per SM walk the work items
   const int64_t grid = items < resident ? items : resident;
   static std::mutex attr_mu;
