@@ -98,12 +98,19 @@ __global__ void __launch_bounds__(TPR > 256 ? TPR : 256, TPR > 512 ? 1 : (TPR > 
     c0[it] = (int64_t)(it * TPR + t) * V;
     valid[it] = c0[it] < a.cols;
   }
-  float g[ITERS][V];
+  // LayerNorm with both gamma and beta keeps BOTH packed (16 bytes per vector) and unpacks them per row: with gamma
+  // unpacked as well the kernel sat at its 128-register cap and spilled inside the row loop.
+  constexpr bool PACKED_G = HAS_G && HAS_B && !RMS && sizeof(T) == 2;
+  float g[PACKED_G ? 1 : ITERS][V];
+  Raw16 gq[PACKED_G ? ITERS : 1];
   Raw16 bq[ITERS];  // beta stays packed (16 bytes per vector): unpacking it per row is cheaper than 32 more registers
   if constexpr (HAS_G) {
 #pragma unroll
     for (int it = 0; it < ITERS; ++it)
-      if (valid[it]) Cvt<T>::unpack(ld_cached16(reinterpret_cast<const T*>(a.gamma) + c0[it]), g[it]);
+      if (valid[it]) {
+        if constexpr (PACKED_G) gq[it] = ld_cached16(reinterpret_cast<const T*>(a.gamma) + c0[it]);
+        else Cvt<T>::unpack(ld_cached16(reinterpret_cast<const T*>(a.gamma) + c0[it]), g[it]);
+      }
   }
   if constexpr (HAS_B && !RMS) {
 #pragma unroll
@@ -171,12 +178,23 @@ __global__ void __launch_bounds__(TPR > 256 ? TPR : 256, TPR > 512 ? 1 : (TPR > 
 #pragma unroll
     for (int it = 0; it < ITERS; ++it)
       if (valid[it]) {
+        // the empty asm makes the packed words opaque per row: otherwise the compiler hoists the (row-invariant)
+        // unpacking out of the row loop and keeps the 32-bit copies in registers after all
         float b[V];
-        if constexpr (HAS_B && !RMS) Cvt<T>::unpack(bq[it], b);
+        if constexpr (HAS_B && !RMS) {
+          asm volatile("" : "+r"(bq[it].w[0]), "+r"(bq[it].w[1]), "+r"(bq[it].w[2]), "+r"(bq[it].w[3]));
+          Cvt<T>::unpack(bq[it], b);
+        }
+        float gu[V];
+        if constexpr (PACKED_G) {
+          asm volatile("" : "+r"(gq[it].w[0]), "+r"(gq[it].w[1]), "+r"(gq[it].w[2]), "+r"(gq[it].w[3]));
+          Cvt<T>::unpack(gq[it], gu);
+        }
 #pragma unroll
         for (int e = 0; e < V; ++e) {
           float v = RMS ? f[it][e] * rstd : fmaf(f[it][e], rstd, offset);
-          if constexpr (HAS_G) v *= g[it][e];
+          if constexpr (PACKED_G) v *= gu[e];
+          else if constexpr (HAS_G) v *= g[it][e];
           if constexpr (HAS_B && !RMS) v += b[e];
           f[it][e] = v;
         }

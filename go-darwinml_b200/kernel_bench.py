@@ -3,7 +3,7 @@
   python go-darwinml_b200/kernel_bench.py softmax  --rows 65536 --cols 1024 --dtype f32 [--causal] [--iters 20]
   python go-darwinml_b200/kernel_bench.py rmsnorm  --rows 16384 --cols 4096 --dtype bf16
   python go-darwinml_b200/kernel_bench.py layernorm --rows 16384 --cols 4096 --dtype bf16
-  python go-darwinml_b200/kernel_bench.py gemm --batch 8 --m 4096 --n 4096 --k 4096 --dtype bf16 [--a-km] [--b-nk]
+  python go-darwinml_b200/kernel_bench.py gemm --batch 8 --m 4096 --n 4096 --k 4096 --dtype bf16 [--a-km] [--b-nk] [--act gelu]
   python go-darwinml_b200/kernel_bench.py copy --rows 16384 --cols 4096 --dtype bf16    # yardstick, not a kernel of this library
 
 Inputs are seeded random tensors resident in HBM; timing is CUDA events on the
