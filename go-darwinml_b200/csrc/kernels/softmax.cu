@@ -54,7 +54,7 @@ __device__ __forceinline__ float masked_score(const SmArgs& a, float xv, int64_t
 }
 
 template <typename T, int ITERS, int TPR>
-__global__ void __launch_bounds__(TPR > 256 ? TPR : 256) softmax_rows_kernel(const SmArgs a) {
+__global__ void __launch_bounds__(TPR > 256 ? TPR : 256, TPR > 256 ? 1 : ((sizeof(T) == 4 || ITERS <= 4) ? 4 : 2)) softmax_rows_kernel(const SmArgs a) {
   constexpr int V = Cvt<T>::N;
   __shared__ float red[32];
   const int rows_per_cta = blockDim.x / TPR;

@@ -5,6 +5,7 @@
   python go-darwinml_b200/kernel_bench.py layernorm --rows 16384 --cols 4096 --dtype bf16
   python go-darwinml_b200/kernel_bench.py gemm --batch 8 --m 4096 --n 4096 --k 4096 --dtype bf16 [--a-km] [--b-nk] [--act gelu]
   python go-darwinml_b200/kernel_bench.py copy --rows 16384 --cols 4096 --dtype bf16    # yardstick, not a kernel of this library
+  python go-darwinml_b200/kernel_bench.py fill --rows 524288 --cols 1024 --dtype f32    # yardstick: write-only stream
 
 Inputs are seeded random tensors resident in HBM; timing is CUDA events on the
 library's stream after warm-up; between timed launches an L2-sized buffer is
@@ -32,7 +33,7 @@ DT = {"f32": (7, 4), "bf16": (6, 2), "f16": (5, 2)}
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["softmax", "rmsnorm", "layernorm", "gemm", "attention", "ewise", "copy"])
+    ap.add_argument("kernel", choices=["softmax", "rmsnorm", "layernorm", "gemm", "attention", "ewise", "copy", "fill"])
     ap.add_argument("--rows", type=int, default=65536)
     ap.add_argument("--cols", type=int, default=1024)
     ap.add_argument("--seq-q", type=int, default=0)
@@ -111,6 +112,15 @@ def main():
         def launch():
             with torch.cuda.stream(stream):
                 y.copy_(x, non_blocking=True)
+    elif args.kernel == "fill":
+        # Yardstick only: the CUDA runtime's memset of a [rows, cols] tensor -- what a write-only stream of this size reaches.
+        y = torch.empty(args.rows, args.cols, device=f"cuda:{args.device}", dtype=tdt)
+        work, unit, kind = args.rows * args.cols * es, "GB/s", "hbm"
+        operand_bytes = 2 * work
+
+        def launch():
+            with torch.cuda.stream(stream):
+                y.zero_()
     elif args.kernel == "ewise":
         # a fused elementwise chain compiled through the graph layer (one launch); bytes = distinct inputs + output
         npdt = {"f32": np.float32, "bf16": __import__("ml_dtypes").bfloat16, "f16": np.float16}[args.dtype]
