@@ -35,6 +35,14 @@ struct SmArgs {
   int64_t m_b, m_h, m_q, m_k;  // mask strides in elements (0 = broadcast)
 };
 
+// exp(x) as one multiply and one MUFU op.  The flush-to-zero form: without it the compiler wraps the instruction in a
+// range test and two rescaling multiplies for results below 2^-126, which no tolerance of a softmax can see.
+__device__ __forceinline__ float exp_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f));
+  return y;
+}
+
 // scale and the explicit mask, without the causal limit
 template <typename T>
 __device__ __forceinline__ float scaled_score(const SmArgs& a, float xv, int64_t row, int64_t j) {
@@ -120,7 +128,7 @@ __global__ void __launch_bounds__(TPR > 256 ? TPR : 256, TPR > 256 ? 1 : ((sizeo
 #pragma unroll
       for (int e = 0; e < V; ++e) {
         // A fully masked row has mx = -inf: (-inf) - (-inf) = NaN, as IEEE gives.
-        v[it][e] = __expf(v[it][e] - mx);
+        v[it][e] = exp_fast(v[it][e] - mx);
         sum += v[it][e];
       }
     }
