@@ -207,6 +207,10 @@ struct RopeParams {
   int64_t rows = 0, cols = 0, head_dim = 0;
   int64_t x_pitch = 0;
   int64_t c_period = 0, s_period = 0;
+  // A table shared by every head: it holds [period / head_dim, head_dim] and element (row, col) of x reads
+  // table[(row mod (period / head_dim)) * head_dim + col mod head_dim].  Otherwise the table is indexed by the flat element
+  // number of x modulo its period.
+  bool c_per_head = false, s_per_head = false;
   int dtype = B200_BFLOAT16;
 };
 Status rope(Device* dev, const RopeParams& p);

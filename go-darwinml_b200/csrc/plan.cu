@@ -150,8 +150,13 @@ class Planner {
       for (Node* i : x->in) stack.push_back(i);
     }
     for (int i = 0; i < n; ++i)
-      if (live_[i])
-        for (Node* in : g_.nodes[i]->in) uses_[in->id]++;
+      if (live_[i]) {
+        // A Rope node's table operands do not count as uses: EmitRope reads the table underneath their broadcasts
+        // (PeriodicOperand) and materialises only what it really reads, so a table broadcast over the batch that feeds
+        // every layer's Rope must not be written out just because it has many users.
+        const size_t counted = g_.nodes[i]->op == Op::Rope ? 1 : g_.nodes[i]->in.size();
+        for (size_t k = 0; k < counted; ++k) uses_[g_.nodes[i]->in[k]->id]++;
+      }
     for (Node* t : targets) uses_[t->id]++;
     // inputs
     for (size_t i = 0; i < feeds.size(); ++i) {
@@ -1394,14 +1399,33 @@ class Planner {
 
   // A table operand of Rope: when it is a broadcast of a smaller tensor over LEADING axes only (the same table for every
   // batch entry), the kernel reads the small tensor with a period instead of a materialised copy.
-  Status PeriodicOperand(Node* t, int* slot, int64_t* period) {
+  // *per_head (when asked for): the table is [positions, head_dim], spread over the heads by a broadcast
+  // [S, D] -> [S, heads, D] and over the batch by a second one; the kernel then indexes it by (row mod S, column mod D)
+  // and neither broadcast is materialised.
+  Status PeriodicOperand(Node* t, int* slot, int64_t* period, int64_t head_dim = 0, bool* per_head = nullptr) {
     Node* b = t;
     while (b->op == Op::Identity) b = b->in[0];
+    if (per_head) *per_head = false;
     if (b->op == Op::BroadcastInDim) {
       Node* src = b->in[0];
       const int r = b->rank(), k = src->rank();
       bool trailing = k <= r && k > 0;
       for (int i = 0; i < k && trailing; ++i) trailing = b->ia[i] == r - k + i && src->dims[i] == b->dims[r - k + i];
+      if (trailing && per_head && head_dim > 0) {
+        // [S, D] -> [S, heads, D] underneath?  (x is [.., S, heads, D] with rows = (.., S): the row number mod S is the position)
+        Node* inner = src;
+        while (inner->op == Op::Identity) inner = inner->in[0];
+        if (inner->op == Op::BroadcastInDim && inner->rank() == 3 && inner->in[0]->rank() == 2 && inner->ia.size() == 2 &&
+            inner->ia[0] == 0 && inner->ia[1] == 2 && inner->in[0]->dims[0] == inner->dims[0] &&
+            inner->in[0]->dims[1] == inner->dims[2] && inner->dims[2] == head_dim && k == 3 && src->dims == inner->dims) {
+          Node* table = inner->in[0];
+          B200_TRY(EnsureMaterialized(table));
+          *slot = SlotOf(table);
+          *period = table->num_elements();
+          *per_head = true;
+          return Status::OK();
+        }
+      }
       if (trailing && src->num_elements() > 0) {
         B200_TRY(EnsureMaterialized(src));
         *slot = SlotOf(src);
@@ -1430,19 +1454,24 @@ class Planner {
     } else {
       base = src;
       offset = 0;
-      rp.cols = src->dims.back();
+      // rows of (heads x head_dim) when there is a head axis, so that a row number is a position (per-head tables below)
+      rp.cols = src->rank() >= 3 ? src->dims[src->rank() - 2] * src->dims.back() : src->dims.back();
       rp.rows = src->num_elements() / rp.cols;
       rp.x_pitch = rp.cols;
     }
     B200_TRY(EnsureMaterialized(base));
     int c_slot, s_slot;
-    B200_TRY(PeriodicOperand(x->in[1], &c_slot, &rp.c_period));
-    B200_TRY(PeriodicOperand(x->in[2], &s_slot, &rp.s_period));
+    // a per-head table needs x's rows to be (batch.., position) and its columns (head, head_dim): rank >= 3 with the
+    // position on axis rank - 3
+    const bool rows_are_positions = src->rank() >= 3 && rp.cols == src->dims[src->rank() - 2] * src->dims[src->rank() - 1];
+    B200_TRY(PeriodicOperand(x->in[1], &c_slot, &rp.c_period, rows_are_positions ? rp.head_dim : 0, &rp.c_per_head));
+    B200_TRY(PeriodicOperand(x->in[2], &s_slot, &rp.s_period, rows_are_positions ? rp.head_dim : 0, &rp.s_per_head));
     const int x_slot = SlotOf(base), out_slot = NewValueSlot(x);
     const int64_t x_off = offset * dtype_size(x->dtype);
     Step st;
-    st.desc = strfmt("rope[rows=%lld cols=%lld head=%lld %s pitch=%lld table_period=%lld]", (long long)rp.rows, (long long)rp.cols,
-                     (long long)rp.head_dim, dtype_name(x->dtype), (long long)rp.x_pitch, (long long)rp.c_period);
+    st.desc = strfmt("rope[rows=%lld cols=%lld head=%lld %s pitch=%lld table_period=%lld%s]", (long long)rp.rows, (long long)rp.cols,
+                     (long long)rp.head_dim, dtype_name(x->dtype), (long long)rp.x_pitch, (long long)rp.c_period,
+                     rp.c_per_head ? " per-head" : "");
     st.reads = {x_slot, c_slot, s_slot};
     st.writes = {out_slot};
     st.run = [rp, x_slot, c_slot, s_slot, out_slot, x_off](Device* dev, void* const* p) -> Status {

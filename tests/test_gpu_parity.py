@@ -776,6 +776,32 @@ def test_rope_from_primitives_is_one_kernel(b200, backend, dt):
     assert ok, viol
 
 
+@pytest.mark.parametrize("dt", [BF16, np.float32], ids=["bf16", "f32"])
+def test_rope_table_shared_by_the_heads_is_never_spread(b200, backend, dt):
+    # tables [S, D] -> BroadcastInDim [S, H, D] -> BroadcastInDim [B, S, H, D]: the kernel indexes the [S, D] table itself
+    B, S, H, D = 3, 19, 5, 64
+    rng = np.random.default_rng(99)
+    x = rng_array(rng, (B, S, H, D), dt)
+    ang = rng.uniform(0, 6.28, size=(S, D))
+    cos, sin = np.cos(ang).astype(np.float32).astype(dt), np.sin(ang).astype(np.float32).astype(dt)
+
+    def build(f, xx, c_, s_):
+        per_head = _S(b200, dt, S, H, D)
+        c3, s3 = f.BroadcastInDim(c_, per_head, [0, 2]), f.BroadcastInDim(s_, per_head, [0, 2])
+        return _rope_graph(b200, dt, B, S, H, D)(f, xx, c3, s3)
+
+    (got,), plan = run_backend(b200, backend, build, [x, cos, sin], describe=True)
+    assert plan.count("\n") == 1 and plan.startswith("rope[") and f"table_period={S * D} per-head" in plan, plan
+    (want,) = run_oracle(build, [x, cos, sin])
+    ok, viol = compare(got, want, 8e-3 if dt is BF16 else 1e-6, 1.0)
+    assert ok, viol
+    # the same tables spread by hand give the same bits
+    cos3, sin3 = np.ascontiguousarray(np.broadcast_to(cos[:, None, :], (S, H, D))), np.ascontiguousarray(np.broadcast_to(sin[:, None, :], (S, H, D)))
+    (spread,), _ = run_backend(b200, backend, _rope_graph(b200, dt, B, S, H, D), [x, cos3, sin3], describe=True)
+    word = np.uint16 if dt is BF16 else np.uint32
+    np.testing.assert_array_equal(got.view(word), spread.view(word))
+
+
 def test_rope_reads_queries_inside_the_projection_buffer(b200, backend):
     # q = Reshape(Slice(QKV)) feeds the rotary kernel in place: no Slice copy in the plan
     B, S, H, D, W = 2, 24, 4, 64, 4 * 64 + 2 * 64
