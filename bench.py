@@ -5,7 +5,13 @@ Workload: the fused-op micro-bench configuration -- (a) fp32 softmax over the
 last axis of logits[32,16,1024,1024] ~ N(0,4) under a causal -inf mask, (b) bf16
 RMSNorm and LayerNorm over x[16384,4096] ~ N(0,1), gamma ~ N(1,0.02), beta = 0,
 eps = 1e-6.  One "step" is one pass of all three kernels over that batch.
-Algorithmic bytes per step = 2*2^29*4 + 2*(2*2^26*2) = 4,831,838,208.
+
+Bytes.  GB/s figures count the bytes a pass MUST move: every output byte written once and every input byte that can
+influence an output read once.  Under the causal mask the inputs right of the diagonal influence nothing (their
+outputs are exactly 0), so the softmax counts 2^31 output bytes + the lower triangle of the logits at the 16-byte
+granularity the kernel loads at (1,077,936,128 B) = 3,225,419,776 B; each norm counts 2*2^26*2 = 268,435,456 B.
+A step is 3,762,290,688 B.  The dense count the configuration table quotes (read everything once + write once =
+4,294,967,296 B for the softmax, 4,831,838,208 B per step) is reported beside it under keys named "dense".
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
 
@@ -38,10 +44,38 @@ SM_SHAPE = (32, 16, 1024, 1024)
 NORM_SHAPE = (16384, 4096)
 EPS = 1e-6
 E2E_SLICES = 16  # leading-axis slices of the end-to-end leg (32 / 16 softmax batches, 16384 / 16 norm rows per slice)
-SM_BYTES = 2 * int(np.prod(SM_SHAPE)) * 4
+
+
+def causal_softmax_bytes(shape, elt=4, vec_bytes=16):
+    """Bytes a causal softmax over the last axis must move: the whole output, plus for row q of each [Sq, Sk] plane
+    the first q+1 inputs rounded up to whole 16-byte vectors (what lies right of the diagonal cannot change any output)."""
+    sq, sk = shape[-2], shape[-1]
+    planes = int(np.prod(shape[:-2]))
+    per_vec = vec_bytes // elt
+    q = np.arange(sq, dtype=np.int64)
+    read = int((np.minimum(-(-(q + 1) // per_vec) * per_vec, sk) * elt).sum()) * planes
+    return read + int(np.prod(shape)) * elt
+
+
+SM_DENSE_BYTES = 2 * int(np.prod(SM_SHAPE)) * 4          # read everything once + write once
+SM_BYTES = causal_softmax_bytes(SM_SHAPE)                  # what the causal pass must move
 NORM_BYTES = 2 * int(np.prod(NORM_SHAPE)) * 2
 STEP_BYTES = SM_BYTES + 2 * NORM_BYTES
+STEP_DENSE_BYTES = SM_DENSE_BYTES + 2 * NORM_BYTES
+# DRAM traffic of one causal softmax launch at the configuration's size, from an ncu capture of exactly that launch
+# (dram__bytes_read.sum, dram__bytes_write.sum; the capture and its command are in
+# profiles/softmax_causal_f32_rows524288x1024.md).  bench.py checks it against SM_BYTES and says so in the line.
+SM_NCU_DRAM_READ, SM_NCU_DRAM_WRITE = 1_107_461_888, 2_092_402_176   # 55 MB of the 2^31 output bytes were still dirty in L2 when the kernel ended
 METRIC = "GB/s (softmax/norm)"
+def config_dict():
+    """The workload description both arms print (identical, so the two lines are comparable key by key)."""
+    return {"workload": WORKLOAD, "l2": "inputs larger than L2: every step streams 3.8 GB through a 126 MB L2",
+            "per_gpu_batch": "full (weak scaling, no data-path collective)", "bytes_per_step": STEP_BYTES,
+            "dense_bytes_per_step": STEP_DENSE_BYTES, "bytes": BYTES_NOTE}
+
+
+BYTES_NOTE = ("bytes that must move: all outputs + the inputs that can influence them (causal softmax: lower triangle at 16-byte "
+              "granularity); the dense read-all + write-all count is reported under 'dense' keys")
 WORKLOAD = ("fused-op micro-bench: fp32 causal softmax logits[32,16,1024,1024] + bf16 RMSNorm + bf16 LayerNorm x[16384,4096], "
             "eps 1e-6")
 
@@ -137,54 +171,66 @@ def cpu_pass(cport, logits, x, gamma, beta, out_sm, out_n):
     cport.norm(x, gamma, beta, EPS, False, out=out_n)
 
 
-def cpu_sample_shapes(frac_rows: int):
-    """A bounded sample of the workload: the first `frac_rows`-th of the softmax batch and of the norm rows."""
-    return (SM_SHAPE[0] // frac_rows,) + SM_SHAPE[1:], (NORM_SHAPE[0] // frac_rows, NORM_SHAPE[1])
+def verify_against_oracle(cport, logits, x, gamma, beta, out_sm, out_rms, out_ln, samples=64, seed=7):
+    """Compares sampled rows of the three outputs with the CPU restatement (oracle/oracle_c.c, itself pinned to the
+    float64 oracle by the tests).  Softmax rows are taken as whole [Sq, Sk] planes' rows: a row's mask depends on its
+    position inside its plane.  Returns (ok, worst violation of |got-want| <= rtol*|want| + atol)."""
+    rng = np.random.default_rng(seed)
+    worst = -np.inf
+    planes = logits.reshape(-1, logits.shape[-2], logits.shape[-1])
+    got_planes = out_sm.reshape(planes.shape)
+    for pi in rng.choice(planes.shape[0], size=4, replace=False):   # 4 planes x 16 rows
+        want = cport.softmax_f32(planes[pi], 1.0, True, planes.shape[1])
+        rows = rng.choice(planes.shape[1], size=samples // 4, replace=False)
+        g, w = got_planes[pi][rows].astype(np.float64), want[rows].astype(np.float64)
+        worst = max(worst, float((np.abs(g - w) - (1e-5 * np.abs(w) + 1e-7)).max()))
+    rows = np.sort(rng.choice(x.shape[0], size=samples, replace=False))
+    xs = np.ascontiguousarray(x[rows])
+    for got, want in ((out_rms[rows], cport.norm(xs, gamma, None, EPS, True)), (out_ln[rows], cport.norm(xs, gamma, beta, EPS, False))):
+        g, w = got.astype(np.float64), want.astype(np.float64)
+        worst = max(worst, float((np.abs(g - w) - (8e-3 * np.abs(w) + 4e-4)).max()))   # bf16: one ulp is 2^-8 relative
+    return bool(worst <= 0), worst
 
 
-def run_cpu_baseline(logits, x, gamma, beta, frac_rows=4, passes=3):
+def run_cpu_baseline(logits, x, gamma, beta, passes=3):
+    """The CPU restatement on the whole configuration (the same batch the GPU arm runs), best of `passes`."""
     from oracle import cport
     cport.use_all_cores()   # torchrun exports OMP_NUM_THREADS=1
-    sm_shape, n_shape = cpu_sample_shapes(frac_rows)
-    lg = logits[:sm_shape[0]]
-    xs = x[:n_shape[0]]
-    out_sm, out_n = np.empty_like(lg), np.empty_like(xs)
-    cpu_pass(cport, lg, xs, gamma, beta, out_sm, out_n)  # warm-up (page faults, thread pool)
+    out_sm, out_n = np.empty_like(logits), np.empty_like(x)
+    cpu_pass(cport, logits, x, gamma, beta, out_sm, out_n)  # warm-up (page faults, thread pool)
     best = float("inf")
     for _ in range(passes):
         t0 = time.perf_counter()
-        cpu_pass(cport, lg, xs, gamma, beta, out_sm, out_n)
+        cpu_pass(cport, logits, x, gamma, beta, out_sm, out_n)
         best = min(best, time.perf_counter() - t0)
-    nbytes = 2 * lg.size * 4 + 2 * (2 * xs.size * 2)
-    return {"value": nbytes / best / 1e9, "unit": "GB/s", "cores": cport.num_threads(), "kind": "port",
-            "sample": f"softmax on logits{list(sm_shape)} + RMSNorm + LayerNorm on x{list(n_shape)} (1/{frac_rows} of the batch), best of {passes} passes"}
+    return {"value": STEP_BYTES / best / 1e9, "unit": "GB/s", "cores": cport.num_threads(), "kind": "port", "ms_per_step": best * 1e3,
+            "sample": f"the whole configuration: softmax on logits{list(logits.shape)} + RMSNorm + LayerNorm on x{list(x.shape)}, "
+                      f"best of {passes} passes after one warm-up; bytes counted as in the GPU arm ({STEP_BYTES} per step)"}
 
 
 def run_reference_arm(args, rank, world):
     """The CPU implementation of the path on the host cores.  The reference's own implementation is Apple-only
     (MPSGraph), and GoMLX's pure-Go CPU backend needs a Go toolchain that is absent, so this times the C
-    restatement (oracle/oracle_c.c) with every host thread OpenMP gives it."""
+    restatement (oracle/oracle_c.c) with every host thread OpenMP gives it, on the whole configuration."""
     if rank != 0:
         return
     from oracle import cport
     cport.use_all_cores()   # torchrun exports OMP_NUM_THREADS=1
-    frac = 4
-    sm_shape, n_shape = cpu_sample_shapes(frac)
-    logits, x, gamma, beta = make_inputs(0, sm_shape, n_shape)
+    logits, x, gamma, beta = make_inputs(0)
     out_sm, out_n = np.empty_like(logits), np.empty_like(x)
-    for _ in range(args.warmup):
+    for _ in range(max(1, min(args.warmup, 3))):
         cpu_pass(cport, logits, x, gamma, beta, out_sm, out_n)
     t0 = time.perf_counter()
     for _ in range(args.steps):
         cpu_pass(cport, logits, x, gamma, beta, out_sm, out_n)
     dt = time.perf_counter() - t0
-    nbytes = 2 * logits.size * 4 + 2 * (2 * x.size * 2)
-    value = nbytes * args.steps / dt / 1e9
-    sample = f"each step = softmax on logits{list(sm_shape)} + RMSNorm + LayerNorm on x{list(n_shape)} (1/{frac} of the batch)"
+    value = STEP_BYTES * args.steps / dt / 1e9
+    sample = f"each step = the whole configuration: softmax on logits{list(SM_SHAPE)} + RMSNorm + LayerNorm on x{list(NORM_SHAPE)}"
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic", "config": {"workload": WORKLOAD, "sample": sample},
+        "dtype": "f32", "data": "synthetic",
+        "config": config_dict(),
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cport.num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "reference's own MPSGraph path and GoMLX's Go CPU backend are unavailable on this box; C restatement timed instead",
@@ -193,6 +239,38 @@ def run_reference_arm(args, rank, world):
 
 
 # ---------------------------------------------------------------------------- GPU arm ---
+def time_bare_copies(torch, device, uploads, downloads, barrier, reps=3):
+    """ms per repetition of cudaMemcpyAsync over the given pinned (pointer, nbytes) lists, H2D and D2H concurrently."""
+    rt = ctypes.CDLL("libcudart.so.12")
+    rt.cudaMemcpyAsync.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
+    rt.cudaMemcpyAsync.restype = ctypes.c_int
+    H2D, D2H = 1, 2
+    dev = f"cuda:{device}"
+    d_up = [torch.empty(n, dtype=torch.uint8, device=dev) for _, n in uploads]
+    d_down = [torch.empty(n, dtype=torch.uint8, device=dev) for _, n in downloads]
+    s_up, s_down = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+
+    def once():
+        for (hp, n), d in zip(uploads, d_up):
+            if rt.cudaMemcpyAsync(d.data_ptr(), hp, n, H2D, s_up.cuda_stream) != 0:
+                raise RuntimeError("cudaMemcpyAsync H2D failed")
+        for (hp, n), d in zip(downloads, d_down):
+            if rt.cudaMemcpyAsync(hp, d.data_ptr(), n, D2H, s_down.cuda_stream) != 0:
+                raise RuntimeError("cudaMemcpyAsync D2H failed")
+    once()
+    torch.cuda.synchronize()
+    barrier()
+    e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    e0.record(s_up)
+    s_down.wait_event(e0)
+    for _ in range(reps):
+        once()
+    e1.record(s_up)
+    e2.record(s_down)
+    torch.cuda.synchronize()
+    return max(e0.elapsed_time(e1), e0.elapsed_time(e2)) / reps
+
+
 def compile_graph(b200, backend, name, shapes_in, build):
     builder = backend.Builder(name)
     f = builder.Main()
@@ -242,6 +320,7 @@ def run_b200_arm(args, rank, local_rank, world):
     D = b200.dtypes
     s_logits, s_x, s_g = b200.Shape(D.Float32, SM_SHAPE), b200.Shape(D.BFloat16, NORM_SHAPE), b200.Shape(D.BFloat16, (NORM_SHAPE[1],))
     _, exe_sm = compile_graph(b200, backend, "softmax", [s_logits], lambda f, a: f.FusedSoftmaxMasked(a, 1.0, True, None))
+    _, exe_sm_plain = compile_graph(b200, backend, "softmax_plain", [s_logits], lambda f, a: f.FusedSoftmaxMasked(a, 1.0, False, None))
     _, exe_rms = compile_graph(b200, backend, "rms", [s_x, s_g], lambda f, a, g: f.FusedRMSNorm(a, [-1], EPS, g))
     _, exe_ln = compile_graph(b200, backend, "ln", [s_x, s_g, s_g], lambda f, a, g, b: f.FusedLayerNorm(a, [-1], EPS, g, b))
     _, exe_all = compile_graph(b200, backend, "all", [s_logits, s_x, s_g, s_g],
@@ -296,6 +375,21 @@ def run_b200_arm(args, rank, local_rank, world):
     sm_ms = float(np.mean([e[0].elapsed_time(e[1]) for e in evs]))
     rms_ms = float(np.mean([e[1].elapsed_time(e[2]) for e in evs]))
     ln_ms = float(np.mean([e[2].elapsed_time(e[3]) for e in evs]))
+
+    # the unmasked softmax on the same logits: every byte is read and written, so its GB/s is a plain bandwidth figure
+    def plain_step():
+        for o in exe_sm_plain.Execute([d_logits], None, local_rank):
+            backend.BufferFinalize(o)
+    for _ in range(3):
+        plain_step()
+    backend.Synchronize(local_rank)
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    p0.record(stream)
+    for _ in range(10):
+        plain_step()
+    p1.record(stream)
+    backend.Synchronize(local_rank)
+    plain_ms = p0.elapsed_time(p1) / 10
 
     # ---- e2e: host pointers in, host pointers out, through b200_execute_host ----
     in_ptrs = (ctypes.c_void_p * 4)(p_logits, p_x, p_g, p_b)
@@ -352,6 +446,22 @@ def run_b200_arm(args, rank, local_rank, world):
     h2d = n_sm * 4 + n_norm * 2 + 2 * NORM_SHAPE[1] * 2
     d2h = n_sm * 4 + 2 * n_norm * 2
 
+    # The outputs of the last end-to-end step are in host memory: check sampled rows against the CPU restatement
+    # (outside every timed region).
+    from oracle import cport
+    cport.use_all_cores()
+    verified, verify_worst = verify_against_oracle(cport, h_logits.reshape(SM_SHAPE), h_x, h_g, h_b, h_osm, h_orms, h_oln)
+
+    # Yardstick for the end-to-end figure: the same pinned buffers moved by bare cudaMemcpyAsync calls, uploads on one
+    # stream and downloads on another at the same time, no kernels.  It shows what the box's host<->device path
+    # gives this process, i.e. how much of the end-to-end time is the copies themselves.
+    copy_floor_ms = None
+    try:
+        copy_floor_ms = time_bare_copies(torch, local_rank, [(p_logits, n_sm * 4), (p_x, n_norm * 2)],
+                                         [(p_osm, n_sm * 4), (p_orms, n_norm * 2), (p_oln, n_norm * 2)], barrier)
+    except Exception as ex:  # noqa: BLE001  (a yardstick must never sink the line)
+        copy_floor_ms = f"unavailable: {type(ex).__name__}: {ex}"
+
     # the other configurations (DotGeneral sweep, transformer forwards); never allowed to sink the headline line
     extras, extras_error = None, None
     if not args.no_extras:
@@ -367,38 +477,59 @@ def run_b200_arm(args, rank, local_rank, world):
 
     # max over ranks, on device-measured times
     from go_darwinml_b200.sharding import max_over_ranks
+    own = {"rank": rank, "ms_per_step": elapsed_ms / args.steps, "e2e_ms_per_step": e2e_ms / e2e_steps, "gpt2_ms_per_forward": gpt_ms,
+           "llama_ms_per_forward": llama_ms, "verified": verified}
+    per_rank = [own]
+    if world > 1:
+        per_rank = [None] * world
+        dist.all_gather_object(per_rank, own)
     elapsed_ms, e2e_ms, gpt_ms, llama_ms = max_over_ranks([elapsed_ms, e2e_ms, gpt_ms, llama_ms], device=f"cuda:{local_rank}")
 
     if rank == 0:
         peaks, peak_src = measured_peaks()
+        hbm = peaks["hbm_gbs"]
         ms_per_step = elapsed_ms / args.steps
         value = world * STEP_BYTES / (ms_per_step * 1e-3) / 1e9
         e2e_value = world * STEP_BYTES / (e2e_ms / e2e_steps * 1e-3) / 1e9
         achieved = SM_BYTES / (sm_ms * 1e-3) / 1e9
-        # dram__bytes_read.sum + dram__bytes_write.sum of the causal softmax kernel, captured with ncu on 131072 rows
-        # (276.9 MB + 479.1 MB per launch) and scaled x4 to the 524288-row launch; rows are independent, so traffic is
-        # proportional to the row count (profiles/softmax_causal_f32_rows131072x1024.md)
-        traffic = 4 * (276888064 + 479067648)
+        traffic = SM_NCU_DRAM_READ + SM_NCU_DRAM_WRITE
+
+        def kern(ms, nbytes, **more):
+            d = {"ms": ms, "GB/s": nbytes / ms / 1e6, "frac_of_peak": nbytes / ms / 1e6 / hbm, "bytes": nbytes}
+            d.update(more)
+            return d
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic",
-            "config": {"workload": WORKLOAD, "l2": "inputs larger than L2: every step streams 4.8 GB through a 126 MB L2",
-                       "per_gpu_batch": "full (weak scaling, no data-path collective)", "algorithmic_bytes_per_step": STEP_BYTES},
+            "data": "synthetic", "config": config_dict(),
+            "dense": {"value": world * STEP_DENSE_BYTES / (ms_per_step * 1e-3) / 1e9, "unit": "GB/s",
+                      "note": "the same time over the read-all + write-all byte count; under the causal mask the kernel never loads what "
+                              "lies right of the diagonal, so this is an effective rate, not a bandwidth"},
+            "verified": bool(all(r["verified"] for r in per_rank)),
+            "verified_how": "64 sampled rows of each of the three outputs of the last end-to-end step on every rank against the CPU restatement "
+                            f"(fp32 rel 1e-5, bf16 rel 8e-3); worst violation on rank 0 {verify_worst:.2e} (<= 0 passes)",
             "clocks": sampler.summary(),
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "ms_per_step": e2e_ms / e2e_steps,
                     "call": f"b200_execute_host_sliced, {E2E_SLICES} batch slices, pinned host buffers, copies overlapped with kernels",
-                    "unsliced_ms_per_step": e2e_whole_ms, "unsliced_call": "b200_execute_host", "clocks": e2e_sampler.summary()},
+                    "unsliced_ms_per_step": e2e_whole_ms, "unsliced_call": "b200_execute_host", "clocks": e2e_sampler.summary(),
+                    "bare_copy_ms_per_step_rank0": copy_floor_ms,
+                    "bare_copy_note": "the same pinned buffers through plain cudaMemcpyAsync, uploads and downloads on two streams at once, "
+                                      "no kernels: the floor the host<->device path of this box sets for one step"},
             "gpu_launches": args.steps * (exe_sm.NumLaunches() + exe_rms.NumLaunches() + exe_ln.NumLaunches()),
             "roofline": {"bound": "hbm", "kernel": "softmax_rows_kernel<float,8,32> (causal)", "achieved": achieved,
-                         "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peak_src,
-                         "traffic": traffic, "algorithmic_bytes_per_launch": SM_BYTES, "ms_per_launch": sm_ms,
-                         "note": "causal launch skips loading 16-byte vectors right of the diagonal, so DRAM traffic is below the algorithmic bytes"},
-            "kernels": {"softmax_causal_f32": {"ms": sm_ms, "GB/s": SM_BYTES / sm_ms / 1e6, "frac_of_peak": SM_BYTES / sm_ms / 1e6 / peaks["hbm_gbs"]},
-                        "rms_norm_bf16": {"ms": rms_ms, "GB/s": NORM_BYTES / rms_ms / 1e6, "frac_of_peak": NORM_BYTES / rms_ms / 1e6 / peaks["hbm_gbs"]},
-                        "layer_norm_bf16": {"ms": ln_ms, "GB/s": NORM_BYTES / ln_ms / 1e6, "frac_of_peak": NORM_BYTES / ln_ms / 1e6 / peaks["hbm_gbs"]}},
+                         "peak": hbm, "unit": "GB/s", "frac": achieved / hbm, "peak_source": peak_src,
+                         "traffic": traffic, "bytes_per_launch": SM_BYTES, "dense_bytes_per_launch": SM_DENSE_BYTES,
+                         "dense_GB/s": SM_DENSE_BYTES / sm_ms / 1e6, "ms_per_launch": sm_ms,
+                         "traffic_vs_bytes": traffic / SM_BYTES,
+                         "note": "achieved = bytes the causal pass must move (all outputs + lower-triangle inputs in 16-byte vectors) / launch "
+                                 "time; traffic = ncu dram read + write of this very launch size"},
+            "kernels": {"softmax_causal_f32": kern(sm_ms, SM_BYTES, dense_GBps=SM_DENSE_BYTES / sm_ms / 1e6),
+                        "softmax_plain_f32": kern(plain_ms, SM_DENSE_BYTES, note="same logits, no mask: read all + write all; timed apart from the step"),
+                        "rms_norm_bf16": kern(rms_ms, NORM_BYTES), "layer_norm_bf16": kern(ln_ms, NORM_BYTES)},
         }
+        if world > 1:
+            line["per_rank"] = per_rank
         if extras:
             extras["gpt2_small_fwd_bf16"]["tokens_per_s_all_gpus"] = world * 16 * 1024 / (gpt_ms * 1e-3)   # batch 16 per GPU (weak)
             extras["llama_1b_fwd_bf16"]["tokens_per_s_all_gpus"] = 64 // world * world * 2048 / (llama_ms * 1e-3)  # batch 64 in total (strong)
@@ -473,11 +604,11 @@ def run_extras(b200, backend, L, libmod, torch, stream, local_rank, world, peaks
     g = W.GPT2Config()
     out["gpt2_small_fwd_bf16"] = model_tokens_per_s("gpt2", g, W.gpt2_param_shapes(g),
                                                    lambda f, *p: W.gpt2_forward(f, g, int(b200.dtypes.BFloat16), *p),
-                                                   W.gpt2_flops_per_token(g), 3)
+                                                   W.gpt2_flops_per_token(g), 20)
     lc = W.LlamaConfig(batch=64 // world)  # batch 64 sharded by batch across the GPUs
     out["llama_1b_fwd_bf16"] = model_tokens_per_s("llama", lc, W.llama_param_shapes(lc),
                                                  lambda f, *p: W.llama_forward(f, lc, int(b200.dtypes.BFloat16), *p),
-                                                 W.llama_flops_per_token(lc), 2)
+                                                 W.llama_flops_per_token(lc), 20)
     return out
 
 

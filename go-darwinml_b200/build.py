@@ -42,7 +42,7 @@ def headers_mtime():
 
 
 def compile_one(src, obj, verbose):
-    cmd = ["nvcc", *NVCC_FLAGS, "-x", "cu", "-c", src, "-o", obj]
+    cmd = ["nvcc", *NVCC_FLAGS, "-I", OBJ, "-x", "cu", "-c", src, "-o", obj]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
@@ -50,8 +50,20 @@ def compile_one(src, obj, verbose):
     return src, r.returncode, r.stdout + r.stderr
 
 
+def embed_sources():
+    """csrc/kernels/ewise_ops.cuh as a C++ raw string literal (build/ewise_ops_src.inc): the run-time compiler of
+    ewise_jit.cu hands that text to NVRTC in front of every generated kernel."""
+    src = os.path.join(CSRC, "kernels", "ewise_ops.cuh")
+    dst = os.path.join(OBJ, "ewise_ops_src.inc")
+    text = 'R"EWOPS(' + open(src).read() + ')EWOPS"\n'
+    if not os.path.exists(dst) or open(dst).read() != text:
+        with open(dst, "w") as fh:
+            fh.write(text)
+
+
 def build(force=False, verbose=False):
     os.makedirs(OBJ, exist_ok=True)
+    embed_sources()
     hm = headers_mtime()
     jobs = []
     objs = []

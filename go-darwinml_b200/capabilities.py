@@ -33,6 +33,10 @@ OPERATIONS = [
 @dataclass
 class Capabilities:
     Functions: bool = False  # no sub-functions (the reference sets true for While/If/Call closures)
+    # Weights handed over as graph constants are uploaded to the device once, at compile, and stay resident; as
+    # parameters they would be passed (and shape-checked) on every Execute.  Same field as the reference's second
+    # backend sets (ref coreml/gomlx/capabilities.go:18-23).
+    PreferConstantsForVariables: bool = True
     Operations: Dict[str, bool] = field(default_factory=dict)
     DTypes: Dict[int, bool] = field(default_factory=dict)
 
@@ -40,6 +44,7 @@ class Capabilities:
 def backend_capabilities() -> Capabilities:
     return Capabilities(
         Functions=False,
+        PreferConstantsForVariables=True,
         Operations={name: True for name in OPERATIONS},
         DTypes={int(d): True for d in (dtypes.Bool, dtypes.Int8, dtypes.Int16, dtypes.Int32, dtypes.Int64, dtypes.Float16,
                                       dtypes.BFloat16, dtypes.Float32, dtypes.Float64, dtypes.Uint8, dtypes.Uint16,

@@ -111,15 +111,25 @@ B200Buffer b200_buffer_copy_to_device(B200Buffer buf, int device, B200Error* err
   s = Device::Get(b->device, &src);
   if (s.ok()) s = Device::Get(device, &dst);
   if (s.ok() && b->nbytes > 0) {
-    // Order the copy after the producer's stream, run it on the consumer's stream.
-    cudaEvent_t ev = nullptr;
+    // Order the copy after the producer's stream and run it on the consumer's stream; then make the producer's
+    // stream wait for the copy.  The source device's allocator hands a freed block out again at once on the
+    // grounds that every use of it was enqueued on that device's own stream: without the second wait a caller
+    // that finalizes the source right after this call could see its block overwritten while the copy still reads it.
+    cudaEvent_t ev = nullptr, done = nullptr;
     cudaError_t e = cudaSetDevice(b->device);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventRecord(ev, src->stream());
     if (e == cudaSuccess) e = cudaSetDevice(device);
     if (e == cudaSuccess) e = cudaStreamWaitEvent(dst->stream(), ev, 0);
     if (e == cudaSuccess) e = cudaMemcpyPeerAsync(o->ptr, device, b->ptr, b->device, (size_t)b->nbytes, dst->stream());
+    if (e == cudaSuccess && src != dst) {
+      e = cudaEventCreateWithFlags(&done, cudaEventDisableTiming);
+      if (e == cudaSuccess) e = cudaEventRecord(done, dst->stream());
+      if (e == cudaSuccess) e = cudaSetDevice(b->device);
+      if (e == cudaSuccess) e = cudaStreamWaitEvent(src->stream(), done, 0);
+    }
     if (ev) cudaEventDestroy(ev);
+    if (done) cudaEventDestroy(done);
     if (e != cudaSuccess) s = Status::Cuda(strfmt("peer copy failed: %s", cudaGetErrorString(e)));
   }
   if (!s.ok()) { set_error(err, s); b200_buffer_free(o); return nullptr; }

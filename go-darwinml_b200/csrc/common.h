@@ -8,6 +8,7 @@
 #include <cstdint>
 #include <cstdlib>
 #include <cstring>
+#include <atomic>
 #include <map>
 #include <memory>
 #include <mutex>
@@ -93,6 +94,10 @@ class Device {
   cudaStream_t stream() const;
   cudaStream_t compute_stream() const { return stream_; }
   Status CaptureStream(cudaStream_t* out);
+  // Held from cudaStreamBeginCapture to cudaStreamEndCapture on the capture stream: the device has one such stream,
+  // and two executables reaching their recording run at the same time would otherwise begin a capture on a stream
+  // that is already capturing.
+  std::mutex& capture_mutex() { return capture_mu_; }
   // Two extra streams for host<->device copies that overlap the compute stream (created on first use).
   Status CopyStreams(cudaStream_t* in, cudaStream_t* out);
   int sm_count() const { return sm_count_; }
@@ -120,8 +125,8 @@ class Device {
   cudaStream_t stream_ = nullptr;
   cudaStream_t copy_in_ = nullptr, copy_out_ = nullptr, capture_ = nullptr;
   int* error_flag_ = nullptr;
-  bool error_check_pending_ = false;
-  std::mutex mu_;
+  std::atomic<bool> error_check_pending_{false};   // set by launching threads, read at synchronisation points
+  std::mutex mu_, capture_mu_;
   std::multimap<int64_t, void*> free_blocks_;  // size -> ptr
   std::map<void*, int64_t> live_blocks_;       // ptr -> size
   int64_t reserved_ = 0;
@@ -222,7 +227,9 @@ struct Graph {
 
 // Compile-time rewrite: turns RMSNorm spelled in primitives (x * rsqrt(mean(x^2, last) + eps) [* gamma]) into one
 // RmsNorm node.  Returns the number of patterns rewritten.  Defined in rewrite.cpp.
-int RewriteRmsNorm(Graph& graph, const std::vector<Node*>& targets);
+int RewriteRmsNorm(Graph& graph, const std::vector<Node*>& targets);   // also LayerNorm: the same chain around x - mean(x)
+// Compile-time rewrite: Div(Exp(x - rowmax(x)), rowsum(Exp(x - rowmax(x)))) over the last axis becomes one Softmax node.
+int RewriteSoftmax(Graph& graph, const std::vector<Node*>& targets);
 // Compile-time rewrite: Add(DotGeneral(...), r) or Mul(DotGeneral(...), r) where the product has no other user becomes one
 // DotGeneral node that combines with r in its epilogue (rounding the product first, so the value is the op-by-op one).  Returns the number of rewrites.
 int RewriteGemmResidual(Graph& graph, const std::vector<Node*>& targets);

@@ -78,6 +78,26 @@ struct EwProgram {
   bool wide = false;  // needs 64-bit registers (any I64/U64/F64 value)
 };
 Status ewise_run(Device* dev, const EwProgram& prog);
+// The two templated fast shapes of ewise_run alone (x op y; small trees): *taken says whether one of them was launched.
+Status ewise_run_fast(Device* dev, const EwProgram& prog, bool* taken);
+
+// Run-time compiled form of a program (ewise_jit.cu): one straight-line kernel per distinct program text, built with
+// NVRTC at plan time and cached for the life of the process.  ewise_jit_prepare fails with B200_ERR_UNSUPPORTED when
+// NVRTC is not installed (the interpreter kernel of ewise_run then does the work).  The handle is never freed.
+struct EwJit;
+Status ewise_jit_prepare(Device* dev, const EwProgram& prog, EwJit** out);
+Status ewise_jit_run(Device* dev, EwJit* jit, const EwProgram& prog);   // prog: the same program with its pointers filled in
+bool ewise_jit_available(std::string* why);
+// The same for a reduction (B200ReduceType) whose operand is the program: the program's index space is viewed as
+// [outer, n, inner] (its dims must refine that split) and folded over n in one pass, so the chain's value is never
+// written to memory.  prog.out_dtype is the dtype of the chain's value and of the result; prog.out receives
+// [outer, inner].  Fails with B200_ERR_UNSUPPORTED when the shape would need a split across CTAs (ewise_jit_reduce_fits).
+bool ewise_jit_reduce_fits(int64_t outer, int64_t n, int64_t inner, int sm_count);
+Status ewise_jit_reduce_prepare(Device* dev, const EwProgram& prog, int reduce_type, int64_t outer, int64_t n, int64_t inner, EwJit** out);
+std::string ewise_jit_reduce_source(const EwProgram& prog, int reduce_type, int64_t outer, int64_t n, int64_t inner, bool allow_vector);
+// The generated CUDA C text and its compilation, separately (tests and tools).
+std::string ewise_jit_source(const EwProgram& prog, int sm_count, bool allow_vector);
+Status ewise_jit_nvrtc(const std::string& source, std::vector<char>* cubin);
 
 // ---------------------------------------------------------- data movement --
 // y[idx] = x[offset + sum_d idx_d * strides_d] over a dense row-major output.

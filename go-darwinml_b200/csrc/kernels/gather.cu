@@ -23,7 +23,10 @@ __device__ __forceinline__ int64_t load_index_dt(const void* ids, int dt, int64_
     case B200_INT32: return load_index<int32_t>(ids, i);
     case B200_INT64: return load_index<int64_t>(ids, i);
     case B200_UINT32: return load_index<uint32_t>(ids, i);
-    case B200_UINT64: return (int64_t)load_index<uint64_t>(ids, i);
+    case B200_UINT64: {   // saturate: an index above INT64_MAX clamps to the last row, not to row 0
+      const uint64_t v = reinterpret_cast<const uint64_t*>(ids)[i];
+      return v > (uint64_t)INT64_MAX ? INT64_MAX : (int64_t)v;
+    }
     case B200_INT16: return load_index<int16_t>(ids, i);
     case B200_UINT16: return load_index<uint16_t>(ids, i);
     case B200_INT8: return load_index<int8_t>(ids, i);

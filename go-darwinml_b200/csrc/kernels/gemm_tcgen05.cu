@@ -91,6 +91,13 @@ struct TcArgs {
   int64_t total_tiles;
   int k_blocks;     // ceil(K / BK)
   int segs;         // 1, or 6 partial products of the 3-way split
+  // fp32 operands only: a tile's K range is cut into num_chunks chunks of chunk_blocks k-blocks.  Each chunk is accumulated
+  // from zero in TMEM and the epilogue adds it to C in fp32 (round to nearest), so no TMEM accumulator ever holds more
+  // than a short partial sum.  The tensor core's fp32 accumulate TRUNCATES (measured: on all-positive data the error of a
+  // K = 8192 product is one-sided and 35 times the tolerance of 1e-5 of the result's RMS; on N(0,1) data 4.8 times),
+  // and that bias grows with the number of accumulations times the magnitude of the running sum; chunks of 512 keep it
+  // below 0.3 of the tolerance at every K (better than a plain fp32 FFMA GEMM, which is at 1.8 at K = 8192).
+  int num_chunks, chunk_blocks;
   int vec_store;    // rows of C start 16-byte aligned and N is a multiple of the vector width
   int* err_flag;
 };
@@ -195,9 +202,32 @@ __device__ __forceinline__ void add_bias32(const TcArgs& g, int64_t col, float* 
 // 16-bit columns), 16 rows per round, and are written back transposed: a store instruction covers 4 rows x 128
 // contiguous bytes.  With short K (a GELU layer at K = 768) the epilogue, not the main loop, is the kernel's critical
 // path, which is why eight warps share it.
+// 16 bytes of C read back through the coherent path (never ld.global.nc: the line was written by this kernel)
+__device__ __forceinline__ uint4 ld_c16(const void* p) {
+  uint4 q;
+  asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "l"(p) : "memory");
+  return q;
+}
+
+// fp32 chunked accumulation, applied to one word of the write-out: adds the value C already holds (chunks after the
+// first), and on a tile's last chunk does what the plain epilogue did before staging: bias, activation, residual.
+__device__ __forceinline__ uint32_t combine_chunk_word(const TcArgs& g, uint32_t acc, uint32_t c_old, bool first, bool last, int64_t col,
+                                                       const float* residual_elem) {
+  float v = __uint_as_float(acc);
+  if (!first) v += __uint_as_float(c_old);
+  if (last) {
+    if (g.bias) v += reinterpret_cast<const float*>(g.bias)[col];
+    float one[1] = {v};
+    apply_activation_n<1, false>(g.activation, one);
+    v = one[0];
+    if (residual_elem) v = g.residual_mul ? v * *residual_elem : v + *residual_elem;
+  }
+  return __float_as_uint(v);
+}
+
 template <typename OutT>
 __device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem_acc, int64_t row0, int64_t n0, int b, int quarter, int chalf,
-                                                  int lane, float* stage_f) {
+                                                  int lane, float* stage_f, int chunk) {
   using Tr = OutTraits<OutT>;
   constexpr int CPW = Tr::kColsPerWord;
   constexpr int STEP_COLS = 32 * CPW;          // columns per step: 32 words per row
@@ -206,6 +236,10 @@ __device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem
   const int64_t row_base = row0 + quarter * 32;
   OutT* cbase = reinterpret_cast<OutT*>(g.c) + ((int64_t)b * g.M + row_base) * g.ldc;
   const OutT* rbase = g.residual ? reinterpret_cast<const OutT*>(g.residual) + ((int64_t)b * g.M + row_base) * g.ldc : nullptr;
+  // chunked fp32 accumulation (see TcArgs::num_chunks): this drain adds its chunk to what C holds; only the last chunk
+  // applies bias, activation and residual, and it does so in the write-out loop, after the sum is complete
+  const bool chunked = CPW == 1 && g.num_chunks > 1;
+  const bool first_chunk = chunk == 0, last_chunk = chunk == g.num_chunks - 1;
   const int wg = (lane & 7) * 4;               // write-out: this lane's 4 words of a row
 #pragma unroll 1
   for (int step = chalf * (BN / 2 / STEP_COLS); step < (chalf + 1) * (BN / 2 / STEP_COLS); ++step) {
@@ -216,7 +250,18 @@ __device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem
     // TMEM reads and the activation arithmetic (loads issued after the stores below could not be hoisted: the
     // compiler has to assume C and the residual alias).
     uint4 rv[8];
-    if (rbase && g.vec_store) {
+    if (chunked) {
+      // what C holds so far, written by this very thread while draining the previous chunk (plain loads: the
+      // non-coherent path could return what the line held before that store)
+      if (!first_chunk && g.vec_store) {
+#pragma unroll
+        for (int pass = 0; pass < 8; ++pass) {
+          const int rr = pass * 4 + (lane >> 3);
+          rv[pass] = (row_base + rr < g.M && col < g.N) ? ld_c16(cbase + (int64_t)rr * g.ldc + col)
+                                                         : make_uint4(0, 0, 0, 0);
+        }
+      }
+    } else if (rbase && g.vec_store) {
 #pragma unroll
       for (int pass = 0; pass < 8; ++pass) {
         const int rr = pass * 4 + (lane >> 3);
@@ -233,8 +278,10 @@ __device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem
       float v[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-      if (g.bias) add_bias32<OutT>(g, col0 + part * 32, v);
-      apply_activation_n<32, Tr::kFast>(g.activation, v);
+      if (!chunked) {
+        if (g.bias) add_bias32<OutT>(g, col0 + part * 32, v);
+        apply_activation_n<32, Tr::kFast>(g.activation, v);
+      }
       if (CPW == 1) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) words[j] = pack_word<OutT>(v[j], 0.f);
@@ -260,7 +307,14 @@ __device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem
           const int rr = round * 16 + rl;
           uint4 q = *reinterpret_cast<const uint4*>(stage + rl * EPI_PITCH + wg);
           if (row_base + rr < g.M && col < g.N) {
-            if (rbase) {
+            if (chunked) {
+              const uint4 rq = first_chunk ? make_uint4(0, 0, 0, 0) : rv[round * 4 + pass];
+              const float* re = (last_chunk && rbase) ? reinterpret_cast<const float*>(rbase) + (int64_t)rr * g.ldc + col : nullptr;
+              q.x = combine_chunk_word(g, q.x, rq.x, first_chunk, last_chunk, col, re);
+              q.y = combine_chunk_word(g, q.y, rq.y, first_chunk, last_chunk, col + 1, re ? re + 1 : nullptr);
+              q.z = combine_chunk_word(g, q.z, rq.z, first_chunk, last_chunk, col + 2, re ? re + 2 : nullptr);
+              q.w = combine_chunk_word(g, q.w, rq.w, first_chunk, last_chunk, col + 3, re ? re + 3 : nullptr);
+            } else if (rbase) {
               const uint4 rq = rv[round * 4 + pass];
               q.x = add_residual_word<OutT>(q.x, rq.x, g.residual_mul);
               q.y = add_residual_word<OutT>(q.y, rq.y, g.residual_mul);
@@ -291,7 +345,10 @@ __device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem
             const int64_t c1 = col0 + lane;
             if (c1 < g.N) {
               uint32_t w = stage[rl * EPI_PITCH + lane];
-              if (rbase) w = add_residual_word<OutT>(w, reinterpret_cast<const uint32_t*>(rrow)[c1], g.residual_mul);
+              if (chunked) {
+                const uint32_t c_old = first_chunk ? 0u : reinterpret_cast<const volatile uint32_t*>(crow)[c1];
+                w = combine_chunk_word(g, w, c_old, first_chunk, last_chunk, c1, (last_chunk && rbase) ? reinterpret_cast<const float*>(rrow) + c1 : nullptr);
+              } else if (rbase) w = add_residual_word<OutT>(w, reinterpret_cast<const uint32_t*>(rrow)[c1], g.residual_mul);
               reinterpret_cast<uint32_t*>(crow)[c1] = w;
             }
           } else {
@@ -332,7 +389,7 @@ __device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem
 // accesses), written back 8 rows x 64 contiguous bytes per store instruction.
 template <typename OutT>
 __device__ __forceinline__ void drain_accumulator_narrow(const TcArgs& g, uint32_t tmem_acc, int64_t row0, int64_t n0, int b, int quarter,
-                                                         int cq, int lane, uint32_t* stage) {
+                                                         int cq, int lane, uint32_t* stage, int chunk) {
   using Tr = OutTraits<OutT>;
   constexpr int CPW = Tr::kColsPerWord;
   constexpr int SUB_COLS = 16 * CPW;            // columns per sub-step: 16 words per row
@@ -342,6 +399,8 @@ __device__ __forceinline__ void drain_accumulator_narrow(const TcArgs& g, uint32
   const int64_t row_base = row0 + quarter * 32;
   OutT* cbase = reinterpret_cast<OutT*>(g.c) + ((int64_t)b * g.M + row_base) * g.ldc;
   const OutT* rbase = g.residual ? reinterpret_cast<const OutT*>(g.residual) + ((int64_t)b * g.M + row_base) * g.ldc : nullptr;
+  const bool chunked = CPW == 1 && g.num_chunks > 1;   // fp32 chunked accumulation, as in drain_accumulator
+  const bool first_chunk = chunk == 0, last_chunk = chunk == g.num_chunks - 1;
   const int wg = (lane & 3) * 4;                // write-out: this lane's 4 words of a 16-word row
   const int rsub = lane >> 2;                   // write-out: row within a pass of 8 rows
   // per-store work is kept to a pointer increment and a 32-bit compare: the epilogue is bound by instruction issue
@@ -356,7 +415,14 @@ __device__ __forceinline__ void drain_accumulator_narrow(const TcArgs& g, uint32
     const bool col_ok = col < g.N;
     const int64_t first = (int64_t)rsub * g.ldc + col;   // element offset of this lane's vector in pass 0
     uint4 rv[4];
-    if (rbase && g.vec_store) {
+    if (chunked) {
+      if (!first_chunk && g.vec_store) {
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass)
+          rv[pass] = (col_ok && pass * 8 + rsub < rows_left) ? ld_c16(cbase + first + pass * pass_stride)
+                                                             : make_uint4(0, 0, 0, 0);
+      }
+    } else if (rbase && g.vec_store) {
 #pragma unroll
       for (int pass = 0; pass < 4; ++pass)
         rv[pass] = (col_ok && pass * 8 + rsub < rows_left) ? __ldg(reinterpret_cast<const uint4*>(rbase + first + pass * pass_stride))
@@ -371,8 +437,10 @@ __device__ __forceinline__ void drain_accumulator_narrow(const TcArgs& g, uint32
       float v[SUB_COLS];
 #pragma unroll
       for (int j = 0; j < SUB_COLS; ++j) v[j] = __uint_as_float(r[j]);
-      if (g.bias) add_bias_n<OutT, SUB_COLS>(g, col0, v);
-      apply_activation_n<SUB_COLS, Tr::kFast>(g.activation, v);
+      if (!chunked) {
+        if (g.bias) add_bias_n<OutT, SUB_COLS>(g, col0, v);
+        apply_activation_n<SUB_COLS, Tr::kFast>(g.activation, v);
+      }
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         if constexpr (CPW == 2) words[j] = pack_word<OutT>(v[2 * j], v[2 * j + 1]);
@@ -394,7 +462,14 @@ __device__ __forceinline__ void drain_accumulator_narrow(const TcArgs& g, uint32
           const int rr = round * 16 + rl;
           uint4 q = *reinterpret_cast<const uint4*>(stage + rl * S_EPI_PITCH + wg);
           if (col_ok && rr < rows_left) {
-            if (rbase) {
+            if (chunked) {
+              const uint4 rq = first_chunk ? make_uint4(0, 0, 0, 0) : rv[round * 2 + pass];
+              const float* re = (last_chunk && rbase) ? reinterpret_cast<const float*>(rbase) + first + (round * 2 + pass) * pass_stride : nullptr;
+              q.x = combine_chunk_word(g, q.x, rq.x, first_chunk, last_chunk, col, re);
+              q.y = combine_chunk_word(g, q.y, rq.y, first_chunk, last_chunk, col + 1, re ? re + 1 : nullptr);
+              q.z = combine_chunk_word(g, q.z, rq.z, first_chunk, last_chunk, col + 2, re ? re + 2 : nullptr);
+              q.w = combine_chunk_word(g, q.w, rq.w, first_chunk, last_chunk, col + 3, re ? re + 3 : nullptr);
+            } else if (rbase) {
               const uint4 rq = rv[round * 2 + pass];
               q.x = add_residual_word<OutT>(q.x, rq.x, g.residual_mul);
               q.y = add_residual_word<OutT>(q.y, rq.y, g.residual_mul);
@@ -426,7 +501,10 @@ __device__ __forceinline__ void drain_accumulator_narrow(const TcArgs& g, uint32
             const int64_t c1 = col0 + l16;
             if (c1 < g.N) {
               uint32_t w = stage[rl * S_EPI_PITCH + l16];
-              if (rbase) w = add_residual_word<OutT>(w, reinterpret_cast<const uint32_t*>(rrow)[c1], g.residual_mul);
+              if (chunked) {
+                const uint32_t c_old = first_chunk ? 0u : reinterpret_cast<const volatile uint32_t*>(crow)[c1];
+                w = combine_chunk_word(g, w, c_old, first_chunk, last_chunk, c1, (last_chunk && rbase) ? reinterpret_cast<const float*>(rrow) + c1 : nullptr);
+              } else if (rbase) w = add_residual_word<OutT>(w, reinterpret_cast<const uint32_t*>(rrow)[c1], g.residual_mul);
               reinterpret_cast<uint32_t*>(crow)[c1] = w;
             }
           } else {
@@ -475,6 +553,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* err = g.err_flag;
+  // only fp32 results cut the K range into chunks; for 16-bit results these fold to constants and the chunk loops vanish
+  const int NCH = sizeof(OutT) == 4 ? g.num_chunks : 1;
+  const int CHB = sizeof(OutT) == 4 ? g.chunk_blocks : g.k_blocks;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -490,8 +571,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int iters = g.k_blocks * g.segs;
-
   if (warp == 0) {
     // ------------------------------------------------------------------ producer ---
     if (lane == 0) {
@@ -503,9 +582,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         int b, m_t, n_t;
         tile_coords(g, t, &b, &m_t, &n_t);
         const int m0 = m_t * BM, n0 = n_t * BN;
+        for (int chunk = 0; chunk < NCH && ok; ++chunk) {
+        const int kb_begin = chunk * CHB;
+        const int kb_end = kb_begin + CHB < g.k_blocks ? kb_begin + CHB : g.k_blocks;
         for (int seg = 0; seg < g.segs && ok; ++seg) {
           const int pa = g.segs > 1 ? kPlaneA[seg] : 0, pb = g.segs > 1 ? kPlaneB[seg] : 0;
-          for (int kb = 0; kb < g.k_blocks; ++kb) {
+          for (int kb = kb_begin; kb < kb_end; ++kb) {
             if (!mbar_wait(&empty[s], phase ^ 1, err, 1)) { ok = false; break; }
             unsigned char* sa = tiles + s * STAGE_BYTES;
             unsigned char* sb = sa + A_STAGE_BYTES;
@@ -527,6 +609,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             }
             if (++s == STAGES) { s = 0; phase ^= 1; }
           }
+        }
         }
       }
     }
@@ -551,13 +634,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
+      // one work item = one chunk of one tile (a whole tile when the K range is not cut): items alternate between the
+      // two accumulators
       int local_tile = 0;
-      for (int64_t t = blockIdx.x; t < g.total_tiles && ok; t += gridDim.x, ++local_tile) {
+      for (int64_t t = blockIdx.x; t < g.total_tiles && ok; t += gridDim.x)
+      for (int chunk = 0; chunk < NCH && ok; ++chunk, ++local_tile) {
         const int acc = local_tile & 1;
         const uint32_t acc_phase = (local_tile >> 1) & 1;
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, err, 2)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
+        const int kb_begin = chunk * CHB;
+        const int kb_end = kb_begin + CHB < g.k_blocks ? kb_begin + CHB : g.k_blocks;
+        const int iters = (kb_end - kb_begin) * g.segs;
         for (int it = 0; it < iters; ++it) {
           if (!mbar_wait(&full[s], phase, err, 3)) { ok = false; break; }
           tc_fence_after();
@@ -576,19 +665,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const int quarter = warp & 3;              // TMEM lanes [32*quarter, 32*quarter + 32) belong to this warp
     bool ok = true;
     int local_tile = 0;
-    for (int64_t t = blockIdx.x; t < g.total_tiles && ok; t += gridDim.x, ++local_tile) {
+    for (int64_t t = blockIdx.x; t < g.total_tiles && ok; t += gridDim.x) {
       int b, m_t, n_t;
       tile_coords(g, t, &b, &m_t, &n_t);
+      for (int chunk = 0; chunk < NCH && ok; ++chunk, ++local_tile) {
       const int acc = local_tile & 1;
       const uint32_t acc_phase = (local_tile >> 1) & 1;
       const bool landed = mbar_wait(&acc_full[acc], acc_phase, err, 4);
       if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }  // the warp leaves together: tcgen05.ld is warp-collective
       tc_fence_after();
       drain_accumulator_narrow<OutT>(g, tmem_base + acc * BN, (int64_t)m_t * BM, (int64_t)n_t * BN, b, quarter, (warp - 2) >> 2, lane,
-                                     epi_stage + (warp - 2) * S_EPI_STAGE_WORDS);
+                                     epi_stage + (warp - 2) * S_EPI_STAGE_WORDS, chunk);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      }
     }
   }
 
@@ -649,6 +740,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   const bool leader = rank == 0;
   const int64_t pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
   volatile int* err = g.err_flag;
+  // only fp32 results cut the K range into chunks; for 16-bit results these fold to constants and the chunk loops vanish
+  const int NCH = sizeof(OutT) == 4 ? g.num_chunks : 1;
+  const int CHB = sizeof(OutT) == 4 ? g.chunk_blocks : g.k_blocks;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -665,8 +759,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int iters = g.k_blocks * g.segs;
-
   if (warp == 0) {
     // ------------------------------------------------------------------ producer ---
     if (lane == 0) {
@@ -677,6 +769,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         int64_t t;        // global tile index
         int b, m0, n0;    // this CTA's rows of A / columns of B in that tile
         int seg, kb;
+        int chunk, kb_end;   // the chunk of the tile's K range being loaded and its last k-block + 1
       };
       auto place = [&](Cursor& c) {
         int m_t, n_t;
@@ -684,15 +777,22 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         c.m0 = m_t * 2 * BM + (int)rank * BM;
         c.n0 = n_t * BN + (int)rank * P_BN_HALF;
       };
-      auto advance = [&](Cursor& c) {  // returns false past the last item
-        if (++c.kb == g.k_blocks) {
-          c.kb = 0;
+      auto chunk_range = [&](Cursor& c) {
+        c.kb = c.chunk * CHB;
+        c.kb_end = c.kb + CHB < g.k_blocks ? c.kb + CHB : g.k_blocks;
+      };
+      auto advance = [&](Cursor& c) {  // returns false past the last item; order: tile, chunk, segment, k-block
+        if (++c.kb == c.kb_end) {
           if (++c.seg == g.segs) {
             c.seg = 0;
-            c.t += num_pairs;
-            if (c.t >= g.total_tiles) return false;
-            place(c);
+            if (++c.chunk == NCH) {
+              c.chunk = 0;
+              c.t += num_pairs;
+              if (c.t >= g.total_tiles) return false;
+              place(c);
+            }
           }
+          chunk_range(c);
         }
         return true;
       };
@@ -714,8 +814,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         }
       };
       if (pair < g.total_tiles) {
-        Cursor ld{pair, 0, 0, 0, 0, 0};
+        Cursor ld{pair, 0, 0, 0, 0, 0, 0, 0};
         place(ld);
+        chunk_range(ld);
         // full[s] of the leader, as a cluster address: the same offset for every stage
         const uint32_t full0 = map_to_cta(smem_u32(&full[0]), 0);
         int s = 0;
@@ -747,13 +848,17 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
-      int local_tile = 0;
-      for (int64_t t = pair; t < g.total_tiles && ok; t += num_pairs, ++local_tile) {
+      int local_tile = 0;   // counts work items: one per chunk of a tile
+      for (int64_t t = pair; t < g.total_tiles && ok; t += num_pairs)
+      for (int chunk = 0; chunk < NCH && ok; ++chunk, ++local_tile) {
         const int acc = local_tile & 1;
         const uint32_t acc_phase = (local_tile >> 1) & 1;
         if (!mbar_wait_cluster(&acc_empty[acc], acc_phase ^ 1, err, 2)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
+        const int kb_begin = chunk * CHB;
+        const int kb_end = kb_begin + CHB < g.k_blocks ? kb_begin + CHB : g.k_blocks;
+        const int iters = (kb_end - kb_begin) * g.segs;
         for (int it = 0; it < iters; ++it) {
           if (!mbar_wait_cluster(&full[s], phase, err, 3)) { ok = false; break; }
           tc_fence_after();
@@ -778,19 +883,21 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
     const int quarter = warp & 3;
     bool ok = true;
     int local_tile = 0;
-    for (int64_t t = pair; t < g.total_tiles && ok; t += num_pairs, ++local_tile) {
+    for (int64_t t = pair; t < g.total_tiles && ok; t += num_pairs) {
       int b, m_t, n_t;
       pair_tile_coords(g, t, &b, &m_t, &n_t);
-      const int acc = local_tile & 1;
-      const uint32_t acc_phase = (local_tile >> 1) & 1;
-      const bool landed = mbar_wait_cluster(&acc_full[acc], acc_phase, err, 4);
-      if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }
-      tc_fence_after();
-      drain_accumulator<OutT>(g, tmem_base + acc * BN, (int64_t)m_t * 2 * BM + (int64_t)rank * BM, (int64_t)n_t * BN, b, quarter,
-                              (warp - 2) >> 2, lane, epi_stage + (warp - 2) * EPI_STAGE_FLOATS);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
+      for (int chunk = 0; chunk < NCH && ok; ++chunk, ++local_tile) {
+        const int acc = local_tile & 1;
+        const uint32_t acc_phase = (local_tile >> 1) & 1;
+        const bool landed = mbar_wait_cluster(&acc_full[acc], acc_phase, err, 4);
+        if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }
+        tc_fence_after();
+        drain_accumulator<OutT>(g, tmem_base + acc * BN, (int64_t)m_t * 2 * BM + (int64_t)rank * BM, (int64_t)n_t * BN, b, quarter,
+                                (warp - 2) >> 2, lane, epi_stage + (warp - 2) * EPI_STAGE_FLOATS, chunk);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
+      }
     }
   }
 
@@ -918,6 +1025,10 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
   g.total_tiles = (int64_t)g.tiles_m * g.tiles_n * p.batch;
   g.k_blocks = (int)((p.k + BK - 1) / BK);
   g.segs = is32 ? 6 : 1;
+  // fp32: chunks of at most 8 k-blocks (512 elements of K), balanced over the K range (see TcArgs::num_chunks)
+  static const int chunk_cap = []() { const char* v = getenv("B200MLX_GEMM_F32_CHUNK_BLOCKS"); return v ? atoi(v) : 8; }();   // 0 = never cut
+  g.num_chunks = (is32 && chunk_cap > 0) ? (g.k_blocks + chunk_cap - 1) / chunk_cap : 1;
+  g.chunk_blocks = (g.k_blocks + g.num_chunks - 1) / g.num_chunks;
   const int out_vec = is32 ? 4 : 8;
   g.vec_store = (g.ldc % out_vec == 0 && g.ldc >= (p.n + out_vec - 1) / out_vec * out_vec && aligned16(p.c) && aligned16(p.residual)) ? 1 : 0;
   if (p.num_c_extra > 0) {

@@ -1,13 +1,11 @@
 // LayerNorm and RMSNorm row kernels.
 //
-//   LayerNorm: one pass over the row: d = x - K; m = sum(d)/n; var = sum(d*d)/n - m*m (biased);
-//              y = (d - m) * rsqrt(var + eps) [* gamma] [+ beta]          -- equal to the two-pass textbook form.
-//              K is the row's first element for fp32 and f16 rows (any value near the data removes the cancellation
-//              of the one-pass formula).  bf16 rows use K = 0: with fp32 sums the cancellation error of the variance
-//              is about 1e-6 * (mean/sigma)^2 relative, and a bf16 row whose mean/sigma exceeds 100 has lost its
-//              variance to its own 8-bit quantisation already, so the error stays below the input's noise;
-//              (the formula of the reference's FusedLayerNorm lowering,
-//              mpsgraph function.go:2430-2558, which spends ~12 graph ops on it)
+//   LayerNorm: two passes over the row held in registers: m = sum(x)/n; d = x - m; var = sum(d*d)/n (biased);
+//              y = d * rsqrt(var + eps) [* gamma] [+ beta]
+//              (the formula of the reference's FusedLayerNorm lowering, mpsgraph function.go:2430-2558, which spends
+//              ~12 graph ops on it).  The one-pass forms (sum and sum of squares together, with or without a shift)
+//              cancel when a row has an outlier or a mean far from its spread; with the row in registers the second
+//              pass costs one more reduction round and no memory traffic.
 //   RMSNorm:   y = x * rsqrt(sum(x*x)/n + eps) [* gamma]   (no reference counterpart)
 //
 // Statistics are accumulated in fp32 whatever the storage type; the result is
@@ -27,11 +25,9 @@
 //     the instruction-issue limit as to the HBM limit, so every per-element
 //     instruction counts;
 //   * the next row's loads are issued before the current row is reduced;
-//   * one reduction round per row: sum and sum of squares travel together (LayerNorm's shifted one-pass variance),
-//     the per-warp partials are double-buffered in shared memory so a round costs ONE named barrier, and the
-//     cross-warp step is a few broadcast reads instead of a second shuffle tree.
-#include <type_traits>
-
+//   * one reduction round per row for RMSNorm, two for LayerNorm (mean, then centred sum of squares); the per-warp
+//     partials are double-buffered in shared memory so a round costs ONE named barrier, and the cross-warp step is
+//     a few broadcast reads instead of a second shuffle tree.
 #include "../kernels.h"
 #include "rowwise.cuh"
 
@@ -82,10 +78,10 @@ __global__ void __launch_bounds__(TPR > 256 ? TPR : 256, TPR > 512 ? 1 : (TPR > 
   constexpr int V = Cvt<T>::N;
   constexpr int BLOCK = TPR > 256 ? TPR : 256;
   constexpr int GROUPS = BLOCK / TPR;
-  __shared__ float red[2 * 2 * 32];   // per group: 2 phases x up to 2 values x warps per row
+  __shared__ float red[2 * 32];   // per group: 2 phases x warps per row
   const int group = threadIdx.x / TPR;
   const int t = threadIdx.x % TPR;
-  float* slot = red + group * (4 * (TPR / 32));
+  float* slot = red + group * (2 * (TPR / 32));
   int phase = 0;
   const int bar = 1 + group;
   const float inv_n = 1.0f / (float)a.cols;
@@ -121,21 +117,17 @@ __global__ void __launch_bounds__(TPR > 256 ? TPR : 256, TPR > 512 ? 1 : (TPR > 
   const int64_t row_stride = (int64_t)gridDim.x * GROUPS;
   int64_t row = (int64_t)blockIdx.x * GROUPS + group;
   Raw16 raw[ITERS];
-  constexpr bool SHIFT = !RMS && !std::is_same<T, __nv_bfloat16>::value;
-  float shift = 0.f;   // LayerNorm on fp32 / f16 rows: the row's first element
   if (row < a.rows) {
     const T* xr = reinterpret_cast<const T*>(a.x) + row * a.cols;
 #pragma unroll
     for (int it = 0; it < ITERS; ++it)
       if (valid[it]) raw[it] = ld_stream16(xr + c0[it]);
-    if constexpr (SHIFT) shift = Cvt<T>::load1(xr);
   }
   for (; row < a.rows; row += row_stride) {
     float f[ITERS][V];
 #pragma unroll
     for (int it = 0; it < ITERS; ++it)
       if (valid[it]) Cvt<T>::unpack(raw[it], f[it]);
-    const float K = shift;
     // prefetch the next row of this group while this one is reduced
     const int64_t next = row + row_stride;
     if (next < a.rows) {
@@ -143,37 +135,34 @@ __global__ void __launch_bounds__(TPR > 256 ? TPR : 256, TPR > 512 ? 1 : (TPR > 
 #pragma unroll
       for (int it = 0; it < ITERS; ++it)
         if (valid[it]) raw[it] = ld_stream16(xn + c0[it]);
-      if constexpr (SHIFT) shift = Cvt<T>::load1(xn);
     }
-    float rstd, offset = 0.f;   // y = f * rstd + offset
-    if constexpr (RMS) {
-      float acc[1] = {0.f};
+    float rstd;
+    float acc[1] = {0.f};
+    if constexpr (!RMS) {
 #pragma unroll
       for (int it = 0; it < ITERS; ++it)
         if (valid[it]) {
 #pragma unroll
-          for (int e = 0; e < V; ++e) acc[0] += f[it][e] * f[it][e];
+          for (int e = 0; e < V; ++e) acc[0] += f[it][e];
         }
       group_sum_n<TPR, 1>(acc, slot, bar, phase);
-      rstd = rsqrtf(acc[0] * inv_n + a.eps);
-    } else {
-      float acc[2] = {0.f, 0.f};
+      const float mean = acc[0] * inv_n;
+      acc[0] = 0.f;
 #pragma unroll
       for (int it = 0; it < ITERS; ++it)
         if (valid[it]) {
 #pragma unroll
-          for (int e = 0; e < V; ++e) {
-            if constexpr (SHIFT) f[it][e] -= K;
-            acc[0] += f[it][e];
-            acc[1] += f[it][e] * f[it][e];
-          }
+          for (int e = 0; e < V; ++e) f[it][e] -= mean;   // the output pass multiplies the centred value
         }
-      group_sum_n<TPR, 2>(acc, slot, bar, phase);
-      const float center = acc[0] * inv_n;                      // mean - K
-      const float var = fmaxf(acc[1] * inv_n - center * center, 0.f);
-      rstd = rsqrtf(var + a.eps);
-      offset = -center * rstd;
     }
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it)
+      if (valid[it]) {
+#pragma unroll
+        for (int e = 0; e < V; ++e) acc[0] += f[it][e] * f[it][e];
+      }
+    group_sum_n<TPR, 1>(acc, slot, bar, phase);
+    rstd = rsqrtf(acc[0] * inv_n + a.eps);
     T* yr = reinterpret_cast<T*>(a.y) + row * a.cols;
 #pragma unroll
     for (int it = 0; it < ITERS; ++it)
@@ -192,7 +181,7 @@ __global__ void __launch_bounds__(TPR > 256 ? TPR : 256, TPR > 512 ? 1 : (TPR > 
         }
 #pragma unroll
         for (int e = 0; e < V; ++e) {
-          float v = RMS ? f[it][e] * rstd : fmaf(f[it][e], rstd, offset);
+          float v = f[it][e] * rstd;
           if constexpr (PACKED_G) v *= gu[e];
           else if constexpr (HAS_G) v *= g[it][e];
           if constexpr (HAS_B && !RMS) v += b[e];

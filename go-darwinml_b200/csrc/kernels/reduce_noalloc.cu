@@ -14,16 +14,20 @@
 // image: kNoAllocScratchBytes bytes on every GPU that loads the library, held
 // until the process exits.  Consequences the caller must know:
 //   * n is limited to kNoAllocMaxElements; larger inputs are refused.
-//   * The FIRST call on a device looks up the array's device address and, if
-//     nothing else has used that device through this library yet, performs the
-//     library's one-time device set-up (its stream and status word).  Make that
-//     first call before starting any stream capture.
+//   * The FIRST call on a device looks up the array's device address.  If
+//     nothing else has used that device through this library yet, that call
+//     also performs the library's one-time device set-up: it creates the
+//     library's stream (cudaStreamCreateWithFlags) and looks up the address of
+//     the library's status word, which is a __device__ array like the scratch.
+//     Neither step calls cudaMalloc, but creating a stream is not free: make
+//     that first call at start-up, and before starting any stream capture.
 //   * Every call on a device uses the same array and leaves its partial sums
 //     behind.  Nothing needs clearing between calls: each launch overwrites
 //     every slot it later reads.  Calls issued through this library run one
 //     after another on the device's stream; if a caller arranges for two of
 //     them to overlap on one GPU they race on the array.
-//   * No cudaMalloc, cudaFree or other allocating routine is called here.
+//   * No cudaMalloc, cudaFree or other allocating routine is called here or
+//     in the device set-up this may trigger.
 #include <mutex>
 
 #include "../kernels.h"

@@ -608,66 +608,83 @@ class Planner {
     return true;
   }
 
+  // Drops size-1 dims and collapses neighbouring output dims that every leaf walks contiguously.  `fences` lists dims d
+  // (of the uncollapsed space) that must not be merged with dim d - 1: a reduction keeps the boundaries of its reduced
+  // run.  Returns, through remap_out, where each original dim went.
+  static void CollapseProgram(const EwBuild& b, k::EwProgram& prog, const std::vector<int>& fences, int* remap_out = nullptr) {
+    int r = 0;
+    int remap[k::kMaxDims];
+    int64_t dims[k::kMaxDims];
+    int64_t strides[k::kEwMaxLeaves][k::kMaxDims];
+    bool kept_iota[k::kMaxDims];
+    bool fence_pending = false;
+    for (int d = 0; d < prog.rank; ++d) {
+      remap[d] = r > 0 ? r - 1 : 0;
+      for (int f : fences) fence_pending |= (f == d);
+      if (prog.dims[d] == 1) continue;  // never an iota dim (BuildExpr turns those into immediates)
+      bool merge = r > 0 && !fence_pending && !b.dim_used_by_iota[d] && !kept_iota[r - 1];
+      if (merge)
+        for (int l = 0; l < prog.num_leaves; ++l) merge &= (strides[l][r - 1] == prog.leaves[l].strides[d] * prog.dims[d]);
+      if (merge) {
+        dims[r - 1] *= prog.dims[d];
+        for (int l = 0; l < prog.num_leaves; ++l) strides[l][r - 1] = prog.leaves[l].strides[d];
+        remap[d] = r - 1;
+      } else {
+        dims[r] = prog.dims[d];
+        for (int l = 0; l < prog.num_leaves; ++l) strides[l][r] = prog.leaves[l].strides[d];
+        kept_iota[r] = b.dim_used_by_iota[d];
+        remap[d] = r;
+        ++r;
+      }
+      fence_pending = false;
+    }
+    if (r == 0) {
+      dims[0] = 1;
+      for (int l = 0; l < prog.num_leaves; ++l) strides[l][0] = 0;
+      r = 1;
+    }
+    for (int i = 0; i < prog.num_instr; ++i)
+      if (prog.instr[i].kind == k::EW_IOTA) prog.instr[i].a = (uint8_t)remap[prog.instr[i].a];
+    if (remap_out)
+      for (int d = 0; d < prog.rank; ++d) remap_out[d] = remap[d];
+    prog.rank = r;
+    for (int d = 0; d < k::kMaxDims; ++d) {
+      prog.dims[d] = d < r ? dims[d] : 0;
+      for (int l = 0; l < prog.num_leaves; ++l) prog.leaves[l].strides[d] = d < r ? strides[l][d] : 0;
+    }
+  }
+
   Status FinishEwise(EwBuild& b, Node* x) {
     k::EwProgram prog = b.prog;
     prog.out_dtype = x->dtype;
     prog.wide = dtype_size(x->dtype) == 8;
     for (int i = 0; i < prog.num_instr; ++i)
       if (dtype_size(prog.instr[i].dtype) == 8 || dtype_size(prog.instr[i].sdtype) == 8) prog.wide = true;
-    // Drop size-1 dims and collapse neighbouring output dims that every leaf walks contiguously.
-    {
-      int r = 0;
-      int remap[k::kMaxDims];
-      int64_t dims[k::kMaxDims];
-      int64_t strides[k::kEwMaxLeaves][k::kMaxDims];
-      bool kept_iota[k::kMaxDims];
-      for (int d = 0; d < prog.rank; ++d) {
-        remap[d] = 0;
-        if (prog.dims[d] == 1) continue;  // never an iota dim (BuildExpr turns those into immediates)
-        bool merge = r > 0 && !b.dim_used_by_iota[d] && !kept_iota[r - 1];
-        if (merge)
-          for (int l = 0; l < prog.num_leaves; ++l) merge &= (strides[l][r - 1] == prog.leaves[l].strides[d] * prog.dims[d]);
-        if (merge) {
-          dims[r - 1] *= prog.dims[d];
-          for (int l = 0; l < prog.num_leaves; ++l) strides[l][r - 1] = prog.leaves[l].strides[d];
-          remap[d] = r - 1;
-        } else {
-          dims[r] = prog.dims[d];
-          for (int l = 0; l < prog.num_leaves; ++l) strides[l][r] = prog.leaves[l].strides[d];
-          kept_iota[r] = b.dim_used_by_iota[d];
-          remap[d] = r;
-          ++r;
-        }
-      }
-      if (r == 0) {
-        dims[0] = 1;
-        for (int l = 0; l < prog.num_leaves; ++l) strides[l][0] = 0;
-        r = 1;
-      }
-      for (int i = 0; i < prog.num_instr; ++i)
-        if (prog.instr[i].kind == k::EW_IOTA) prog.instr[i].a = (uint8_t)remap[prog.instr[i].a];
-      prog.rank = r;
-      for (int d = 0; d < k::kMaxDims; ++d) {
-        prog.dims[d] = d < r ? dims[d] : 0;
-        for (int l = 0; l < prog.num_leaves; ++l) prog.leaves[l].strides[d] = d < r ? strides[l][d] : 0;
-      }
-    }
+    CollapseProgram(b, prog, {});
     const int out_slot = NewValueSlot(x);
+    // The chain as one straight-line kernel, compiled now (NVRTC) and cached by its text; without NVRTC the interpreter
+    // kernel runs the program.  The two templated fast shapes keep priority at launch time (they depend on pointers).
+    k::EwJit* jit = nullptr;
+    if (!k::ewise_jit_prepare(ex_->dev, prog, &jit).ok()) jit = nullptr;
     Step st;
     std::ostringstream os;
     os << "ewise[" << op_name(x->op) << " instr=" << prog.num_instr << " leaves=" << prog.num_leaves << " regs=" << prog.num_regs
-       << (prog.wide ? " wide" : "") << "]";
+       << (prog.wide ? " wide" : "") << (jit ? " compiled" : " interpreted") << "]";
     st.desc = os.str();
     st.reads = b.leaf_slots;
     st.writes = {out_slot};
     std::vector<int> leaf_slots = b.leaf_slots;
     std::vector<int64_t> leaf_offsets = b.leaf_offsets;
-    st.run = [prog, leaf_slots, leaf_offsets, out_slot](Device* dev, void* const* p) -> Status {
+    st.run = [prog, leaf_slots, leaf_offsets, out_slot, jit](Device* dev, void* const* p) -> Status {
       k::EwProgram q = prog;
       for (int l = 0; l < q.num_leaves; ++l)
         q.leaves[l].ptr = (const char*)p[leaf_slots[l]] + leaf_offsets[l] * dtype_size(q.leaves[l].dtype);
       q.out = p[out_slot];
-      return k::ewise_run(dev, q);
+      if (!jit) return k::ewise_run(dev, q);
+      bool taken = false;
+      B200_TRY(k::ewise_run_fast(dev, q, &taken));
+      if (taken) return Status::OK();
+      return k::ewise_jit_run(dev, jit, q);
     };
     ex_->steps.push_back(std::move(st));
     return Status::OK();
@@ -1084,12 +1101,76 @@ class Planner {
   }
 
   // ------------------------------------------------------------ reductions ---
+  // A reduction over ONE run of neighbouring axes whose operand is an elementwise chain (or a plain tensor): the chain
+  // is evaluated inside the reduction kernel, which is compiled at plan time, so the chain's value never goes to memory
+  // and the operand is read with 128-bit loads.  Sets *done when the step was emitted; otherwise nothing has changed and
+  // the caller materialises the operand and uses the precompiled reduction kernels.
+  Status TryEmitFusedReduce(Node* x, int rt, int lo, int hi, bool* done) {
+    *done = false;
+    Node* src = x->in[0];
+    if (src->rank() > k::kMaxDims || src->rank() == 0) return Status::OK();
+    std::string why;
+    if (!k::ewise_jit_available(&why)) return Status::OK();
+    int64_t outer = 1, n = 1, inner = 1;
+    for (int d = 0; d < lo; ++d) outer *= src->dims[d];
+    for (int d = lo; d <= hi; ++d) n *= src->dims[d];
+    for (int d = hi + 1; d < src->rank(); ++d) inner *= src->dims[d];
+    if (outer * n * inner == 0 || !k::ewise_jit_reduce_fits(outer, n, inner, ex_->dev->sm_count())) return Status::OK();
+    for (int budget = 24; budget >= 1; budget /= 2) {
+      EwBuild b;
+      b.op_budget = budget;
+      b.dim_used_by_iota.assign(src->rank() + 1, false);
+      b.prog.rank = src->rank();
+      for (int d = 0; d < src->rank(); ++d) b.prog.dims[d] = src->dims[d];
+      int root = 0;
+      B200_TRY(BuildExpr(b, src, IndexMap::Identity(src->rank()), &root));
+      if (b.overflow) continue;
+      if (!AssignRegisters(b, root)) continue;
+      k::EwProgram prog = b.prog;
+      prog.out_dtype = src->dtype;
+      prog.wide = dtype_size(src->dtype) == 8;
+      for (int i = 0; i < prog.num_instr; ++i)
+        if (dtype_size(prog.instr[i].dtype) == 8 || dtype_size(prog.instr[i].sdtype) == 8) prog.wide = true;
+      CollapseProgram(b, prog, {lo, hi + 1});
+      k::EwJit* jit = nullptr;
+      if (!k::ewise_jit_reduce_prepare(ex_->dev, prog, rt, outer, n, inner, &jit).ok() || !jit) return Status::OK();
+      const int out_slot = NewValueSlot(x);
+      Step st;
+      st.desc = strfmt("reduce[type=%d outer=%lld n=%lld inner=%lld %s fused instr=%d leaves=%d compiled]", rt, (long long)outer, (long long)n,
+                       (long long)inner, dtype_name(src->dtype), prog.num_instr, prog.num_leaves);
+      st.reads = b.leaf_slots;
+      st.writes = {out_slot};
+      std::vector<int> leaf_slots = b.leaf_slots;
+      std::vector<int64_t> leaf_offsets = b.leaf_offsets;
+      st.run = [prog, leaf_slots, leaf_offsets, out_slot, jit](Device* dev, void* const* p) -> Status {
+        k::EwProgram q = prog;
+        for (int l = 0; l < q.num_leaves; ++l)
+          q.leaves[l].ptr = (const char*)p[leaf_slots[l]] + leaf_offsets[l] * dtype_size(q.leaves[l].dtype);
+        q.out = p[out_slot];
+        return k::ewise_jit_run(dev, jit, q);
+      };
+      ex_->steps.push_back(std::move(st));
+      *done = true;
+      return Status::OK();
+    }
+    return Status::OK();
+  }
+
   Status EmitReduce(Node* x) {
     Node* src = x->in[0];
-    B200_TRY(EnsureMaterialized(src));
     const int rt = (int)x->ia[0];
     std::vector<int64_t> axes(x->ia.begin() + 1, x->ia.end());
     std::sort(axes.begin(), axes.end());
+    {
+      bool one_run = !axes.empty();
+      for (size_t i = 1; i < axes.size(); ++i) one_run = one_run && axes[i] == axes[i - 1] + 1;
+      if (one_run) {
+        bool done = false;
+        B200_TRY(TryEmitFusedReduce(x, rt, (int)axes.front(), (int)axes.back(), &done));
+        if (done) return Status::OK();
+      }
+    }
+    B200_TRY(EnsureMaterialized(src));
     // Runs of neighbouring reduced axes, folded from the innermost run outwards.
     struct Run { int lo, hi; };
     std::vector<Run> runs;
@@ -1676,6 +1757,7 @@ B200Exec b200_compile(B200Context ctx, const B200Value* feeds, int num_feeds, co
     t.push_back(n);
   }
   RewriteRmsNorm(c->graph, t);
+  RewriteSoftmax(c->graph, t);
   RewriteGemmResidual(c->graph, t);
   RewriteRope(c->graph, t);
   std::unique_ptr<Exec> ex(new Exec());
@@ -1851,8 +1933,10 @@ static bool execute_impl(B200Exec exec, const B200Buffer* inputs, int num_inputs
       // meanwhile stays out of it.
       cudaGraph_t graph = nullptr;
       cudaStream_t cs = nullptr;
+      std::lock_guard<std::mutex> recording(ex->dev->capture_mutex());   // one capture stream per device
       cudaError_t ce = ex->dev->CaptureStream(&cs).ok() ? cudaSuccess : cudaErrorUnknown;
       if (ce == cudaSuccess) ce = cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal);
+      const bool began = ce == cudaSuccess;
       if (ce == cudaSuccess) {
         Status rs = Status::OK();
         {
@@ -1881,8 +1965,10 @@ static bool execute_impl(B200Exec exec, const B200Buffer* inputs, int num_inputs
       }
       if (!hit) {
         cudaGetLastError();
-        ex->capturable = false;   // this plan does not record cleanly; nothing was launched: the plain path below runs it
-                                  // now (and reports a real error if there is one) and on every later call
+        // A plan that began recording and did not finish cleanly runs step by step from now on (nothing was launched:
+        // the plain path below runs it now and reports a real error if there is one).  A capture that could not even
+        // begin says nothing about the plan: a later call tries again.
+        if (began) ex->capturable = false;
       }
     }
     if (hit) {

@@ -74,7 +74,7 @@ struct RowShapes {
   bool IsFull(const Node* n) const { return n->dims == x->dims; }
 };
 
-// value(n) = a * sum_j x[row, j]^2 + b for every row
+// value(n) = a * sum_j x[row, j]^2 + b for every row (or a * sum_j x[row, j] + b when matched with squared = false)
 struct Affine {
   Node* x = nullptr;
   double a = 1, b = 0;
@@ -115,19 +115,19 @@ bool LayoutStepOk(const Node* l, const RowShapes& rs) {
 }
 
 // Proves value(n) = a * rowsumsq(x) + b.  On the way down x is unknown, so shapes are validated on the way back up.
-bool MatchAffine(Node* n, Affine* out, RowShapes* rs, int depth = 0) {
+bool MatchAffine(Node* n, Affine* out, RowShapes* rs, int depth = 0, bool squared = true) {
   if (depth > 16) return false;
   auto shaped = [&](Node* m) { return rs->IsStat(m) || rs->IsFull(m); };
   switch (n->op) {
     case Op::Reshape:
     case Op::Identity:
     case Op::BroadcastInDim:
-      return MatchAffine(n->in[0], out, rs, depth + 1) && LayoutStepOk(n, *rs);
+      return MatchAffine(n->in[0], out, rs, depth + 1, squared) && LayoutStepOk(n, *rs);
     case Op::Reduce: {
       Node* sq = n->in[0];
       if (n->ia.size() != 2 || n->ia[0] != B200_REDUCE_SUM || sq->rank() < 1 || n->ia[1] != sq->rank() - 1) return false;
-      if (sq->op != Op::Mul || sq->in[0] != sq->in[1]) return false;
-      Node* x = sq->in[0];
+      if (squared && (sq->op != Op::Mul || sq->in[0] != sq->in[1])) return false;
+      Node* x = squared ? sq->in[0] : sq;
       if (x->dims.back() < 2) return false;
       out->x = x; out->a = 1; out->b = 0;
       rs->x = x;
@@ -145,7 +145,7 @@ bool MatchAffine(Node* n, Affine* out, RowShapes* rs, int depth = 0) {
       else if (ScalarValue(n->in[0], &c)) { u = n->in[1]; const_first = true; }
       else return false;
       if (const_first && (n->op == Op::Sub || n->op == Op::Div)) return false;
-      if (!MatchAffine(u, out, rs, depth + 1) || !shaped(n)) return false;
+      if (!MatchAffine(u, out, rs, depth + 1, squared) || !shaped(n)) return false;
       switch (n->op) {
         case Op::Add: out->b += c; break;
         case Op::Sub: out->b -= c; break;
@@ -394,11 +394,80 @@ int RewriteRmsNorm(Graph& graph, const std::vector<Node*>& targets) {
         }
       }
     }
-    root->op = Op::RmsNorm;
-    root->in = {x};
+    // LayerNorm spelled in primitives is the same pattern one level up: the normalised value is d = x0 - mean(x0), i.e.
+    // Sub(x0, M) with M = rowsum(x0) / C per row (ref mpsgraph function.go:2430-2558 is this very chain, two-pass).
+    Node* x0 = nullptr;
+    if (x->op == Op::Sub && x->in[0]->dims == x->dims && x->in[0]->dtype == x->dtype) {
+      Affine mean;
+      RowShapes mrs{};
+      const double C = (double)x->dims.back();
+      if (MatchAffine(x->in[1], &mean, &mrs, 0, /*squared=*/false) && mean.x == x->in[0] && (mrs.IsStat(x->in[1]) || mrs.IsFull(x->in[1])) &&
+          std::fabs(mean.a * C - 1.0) <= 4e-3 && mean.b == 0.0)
+        x0 = x->in[0];
+    }
+    Node* beta = nullptr;
+    if (x0 && !is_target.count(root)) {
+      // ... [* gamma] + beta: an Add of a vector broadcast over the rows
+      auto& ru = users[root];
+      if (ru.size() == 1 && ru[0]->op == Op::Add && ru[0]->dtype == root->dtype) {
+        Node* u = ru[0];
+        Node* B = u->in[0] == root ? u->in[1] : u->in[0];
+        if (B != root) {
+          if (Node* b = MatchGamma(B, x)) {
+            root = u;
+            beta = b;
+          }
+        }
+      }
+    }
+    root->op = x0 ? Op::LayerNorm : Op::RmsNorm;
+    root->in = {x0 ? x0 : x};
     if (gamma) root->in.push_back(gamma);
-    root->ia = {gamma ? 1 : 0, 0, (int64_t)x->rank() - 1};
+    if (beta) root->in.push_back(beta);
+    root->ia = {gamma ? 1 : 0, beta ? 1 : 0, (int64_t)x->rank() - 1};
     root->fa = {eps};
+    ++rewritten;
+  }
+  return rewritten;
+}
+
+// Softmax spelled in primitives (what a model emits when a backend does not list FusedSoftmax):
+//   e = Exp(Sub(x, M)),  M = ReduceMax(x, last) kept / broadcast per row;   y = Div(e, S),  S = ReduceSum(e, last) per row.
+// Op by op that is two reductions and three elementwise passes; as one Softmax node the row kernel reads x once and
+// writes y once.  The row kernel computes the same max-subtracted form in fp32 with one final rounding.
+int RewriteSoftmax(Graph& graph, const std::vector<Node*>& targets) {
+  std::unordered_set<Node*> live;
+  std::unordered_map<Node*, std::vector<Node*>> users;
+  LiveAndUsers(graph, targets, &live, &users);
+  // n = Reduce(type, last axis)(src) seen through layout ops that keep every row's value in its row
+  auto row_reduce = [](Node* n, int type, const Node* like) -> Node* {
+    std::vector<Node*> layout;
+    while (n->op == Op::Reshape || n->op == Op::BroadcastInDim || n->op == Op::Identity) { layout.push_back(n); n = n->in[0]; }
+    if (n->op != Op::Reduce || n->ia.size() != 2 || n->ia[0] != type) return nullptr;
+    Node* src = n->in[0];
+    if (src->rank() < 1 || n->ia[1] != src->rank() - 1 || src->dims != like->dims) return nullptr;
+    RowShapes rs{src, NonUnit(src->dims, src->dims.size() - 1)};
+    if (!rs.IsStat(n)) return nullptr;
+    for (Node* l : layout)
+      if (!LayoutStepOk(l, rs)) return nullptr;
+    return src;
+  };
+  int rewritten = 0;
+  for (auto& up : graph.nodes) {
+    Node* m = up.get();
+    if (!live.count(m) || m->op != Op::Div) continue;
+    if (!(m->dtype == B200_FLOAT32 || m->dtype == B200_BFLOAT16 || m->dtype == B200_FLOAT16)) continue;
+    Node* e = m->in[0];
+    if (e->op != Op::Exp || e->dims != m->dims || e->dtype != m->dtype || m->rank() < 1 || m->dims.back() < 2) continue;
+    if (row_reduce(m->in[1], B200_REDUCE_SUM, e) != e) continue;
+    Node* d = e->in[0];
+    if (d->op != Op::Sub || d->in[0]->dims != m->dims || d->in[0]->dtype != m->dtype) continue;
+    Node* x = d->in[0];
+    if (row_reduce(d->in[1], B200_REDUCE_MAX, x) != x) continue;
+    m->op = Op::Softmax;
+    m->in = {x};
+    m->ia = {(int64_t)m->rank() - 1};
+    m->fa.clear();
     ++rewritten;
   }
   return rewritten;

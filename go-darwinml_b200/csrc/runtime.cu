@@ -28,6 +28,10 @@ const char* dtype_name(int dt) {
 
 namespace {
 constexpr int kMaxDevices = 64;
+// The per-device status word that kernels with bounded waits set when a wait gives up.  It lives in the library's
+// device image (every GPU that loads the library holds these 256 bytes, zero at load), so device set-up allocates
+// nothing; in host code the name is only a stand-in, the device address comes from cudaGetSymbolAddress.
+static __device__ __align__(256) int g_status_word[64];
 std::mutex g_dev_mu;
 Device* g_devices[kMaxDevices] = {nullptr};
 
@@ -57,8 +61,7 @@ Status Device::Get(int ordinal, Device** out) {
     int sms = 0;
     B200_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ordinal));
     d->sm_count_ = sms > 0 ? sms : 148;
-    B200_CUDA_TRY(cudaMalloc((void**)&d->error_flag_, 256));
-    B200_CUDA_TRY(cudaMemset(d->error_flag_, 0, 256));
+    B200_CUDA_TRY(cudaGetSymbolAddress((void**)&d->error_flag_, g_status_word));   // with this device current
     g_devices[ordinal] = d.release();
   }
   *out = g_devices[ordinal];

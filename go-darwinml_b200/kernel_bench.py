@@ -4,6 +4,8 @@
   python go-darwinml_b200/kernel_bench.py rmsnorm  --rows 16384 --cols 4096 --dtype bf16
   python go-darwinml_b200/kernel_bench.py layernorm --rows 16384 --cols 4096 --dtype bf16
   python go-darwinml_b200/kernel_bench.py gemm --batch 8 --m 4096 --n 4096 --k 4096 --dtype bf16 [--a-km] [--b-nk] [--act gelu]
+  python go-darwinml_b200/kernel_bench.py ewise --expr chain4 --rows 65536 --cols 2048 --dtype bf16   # 4 leaves, 6 ops: the run-time compiled path
+  python go-darwinml_b200/kernel_bench.py reduce --expr sumsq --rows 16384 --cols 4096 --dtype bf16   # ReduceSum(x * x) over rows, one fused launch
   python go-darwinml_b200/kernel_bench.py copy --rows 16384 --cols 4096 --dtype bf16    # yardstick, not a kernel of this library
   python go-darwinml_b200/kernel_bench.py fill --rows 524288 --cols 1024 --dtype f32    # yardstick: write-only stream
 
@@ -33,7 +35,7 @@ DT = {"f32": (7, 4), "bf16": (6, 2), "f16": (5, 2)}
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["softmax", "rmsnorm", "layernorm", "gemm", "attention", "ewise", "copy", "fill"])
+    ap.add_argument("kernel", choices=["softmax", "rmsnorm", "layernorm", "gemm", "attention", "ewise", "reduce", "copy", "fill"])
     ap.add_argument("--rows", type=int, default=65536)
     ap.add_argument("--cols", type=int, default=1024)
     ap.add_argument("--seq-q", type=int, default=0)
@@ -46,7 +48,8 @@ def main():
     ap.add_argument("--b-nk", action="store_true", help="B stored [batch, N, K]")
     ap.add_argument("--act", default="none", choices=["none", "gelu", "relu", "silu", "tanh"],
                     help="gemm: add a bias [N] and this activation in the epilogue (a dense layer)")
-    ap.add_argument("--expr", default="add", choices=["add", "bias", "rope", "chain"], help="ewise: which fused chain to time")
+    ap.add_argument("--expr", default="add", choices=["add", "bias", "rope", "chain", "chain4", "sumsq", "sum", "colsum"],
+                    help="ewise / reduce: which fused chain to time")
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--seq", type=int, default=2048)
@@ -143,6 +146,12 @@ def main():
             cb = f.BroadcastInDim(ps[2], S(R, H, Dh), [0, 2])
             sb = f.BroadcastInDim(ps[3], S(R, H, Dh), [0, 2])
             y = f.Add(f.Mul(ps[0], cb), f.Mul(ps[1], sb))
+        elif args.expr == "chain4":
+            # 4 leaves, 6 ops, outside the two templated shapes: tanh((x * w + b) * y) - max(x, y)
+            shapes = [(R, C), (C,), (R,), (R, C)]
+            ps = [f.Parameter(f"p{i}", S(*sh)) for i, sh in enumerate(shapes)]
+            t = f.Add(f.Mul(ps[0], f.BroadcastInDim(ps[1], S(R, C), [1])), f.BroadcastInDim(ps[2], S(R, C), [0]))
+            y = f.Sub(f.Tanh(f.Mul(t, ps[3])), f.Max(ps[0], ps[3]))
         else:
             shapes = [(R, C), (C,), (C,)]
             ps = [f.Parameter(f"p{i}", S(*sh)) for i, sh in enumerate(shapes)]
@@ -155,6 +164,33 @@ def main():
             e = libmod.B200Error()
             bufs.append(b200.Buffer(L.b200_buffer_wrap(args.device, t.data_ptr(), code, (ctypes.c_int64 * len(sh))(*sh), len(sh), ctypes.byref(e))))
         work = (sum(t.numel() for t in tens) + R * C) * es
+        unit, kind = "GB/s", "hbm"
+        operand_bytes = work
+        print(exe.Describe().strip(), file=sys.stderr)
+
+        def launch():
+            for o in exe.Execute(bufs, None, args.device):
+                backend.BufferFinalize(o)
+    elif args.kernel == "reduce":
+        # a Reduce whose operand is an elementwise chain, compiled through the graph layer; bytes = input + output
+        npdt = {"f32": np.float32, "bf16": __import__("ml_dtypes").bfloat16, "f16": np.float16}[args.dtype]
+        S = lambda *d: b200.Shape(b200.dtypes.from_numpy(np.dtype(npdt)), d)
+        R, C = args.rows, args.cols
+        builder = backend.Builder("reduce")
+        f = builder.Main()
+        x = f.Parameter("x", S(R, C))
+        if args.expr == "sumsq":
+            y, out_elems = f.ReduceSum(f.Mul(x, x), 1), R
+        elif args.expr == "colsum":
+            y, out_elems = f.ReduceSum(x, 0), C
+        else:
+            y, out_elems = f.ReduceSum(x, 1), R
+        f.Return([y], None)
+        exe = builder.Compile()
+        t = rand(R, C)
+        e = libmod.B200Error()
+        bufs = [b200.Buffer(L.b200_buffer_wrap(args.device, t.data_ptr(), code, (ctypes.c_int64 * 2)(R, C), 2, ctypes.byref(e)))]
+        work = (R * C + out_elems) * es
         unit, kind = "GB/s", "hbm"
         operand_bytes = work
         print(exe.Describe().strip(), file=sys.stderr)

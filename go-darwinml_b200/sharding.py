@@ -118,6 +118,12 @@ class ColumnShardedMatmul:
 
     `exchange(obj) -> list` must return every rank's `obj` in rank order (torch.distributed.all_gather_object does);
     `barrier()` must return once all ranks have called it.  One process per GPU.
+
+    Ownership of C: every rank's kernel writes into every rank's C.  `run()` therefore opens with a synchronise and a
+    barrier of its own -- a rank enters only when ITS consumers of the previous C have finished, and no rank's kernel
+    starts before all have entered -- so a fast rank cannot overwrite a C that a slower rank is still reading.
+    `launch()` has no such guard (it exists for back-to-back timing): its caller must make sure that every rank has
+    finished reading C before any rank launches again.
     """
 
     def __init__(self, backend, device: int, rank: int, world: int, m: int, n_local: int, k: int, np_dtype,
@@ -171,6 +177,8 @@ class ColumnShardedMatmul:
         from . import _lib
         from .backend import _check
 
+        self.backend.Synchronize(self.device)   # this rank's readers of the previous C are done ...
+        self._barrier()                          # ... and so are everybody else's: C may be overwritten
         err = _lib.B200Error()
         self._L.b200_k_gemm_allgather(self.device, self._L.b200_buffer_device_ptr(a.handle), self._L.b200_buffer_device_ptr(b_local.handle),
                                       self._c_all, self.world, self.rank, self.m, self.n_local, self.k, 1, int(self.b_k_major),
@@ -201,3 +209,94 @@ class ColumnShardedMatmul:
         self._imported = []
         self._barrier()
         self.backend.BufferFinalize(self.c)
+
+
+def column_sharded_matmul_check(backend, device: int, rank: int, world: int, gm: int, gn: int, gk: int, iters: int = 10, warmup: int = 3):
+    """Runs ColumnShardedMatmul on bf16 A [gm, gk] (replicated) and W [gk, gn] split by columns over the ranks of an
+    initialised torch.distributed NCCL group (one process per GPU), compares this rank's full C bit for bit with this
+    library's single-GPU GEMM on the whole W, and times (CUDA events on the library's stream, max over ranks) the
+    fused kernel beside the two-step form -- the same GEMM into a local slab, then all_gather_into_tensor -- and the
+    GEMM alone.  Every rank returns the same dict."""
+    import ctypes
+
+    import ml_dtypes
+    import torch
+    import torch.distributed as dist
+
+    from . import _lib as libmod
+    from .backend import Buffer
+
+    L = libmod.lib()
+    if gn % (8 * world) != 0:
+        raise ValueError("gn must be a multiple of 8 * world")
+    n_local = gn // world
+    dev = f"cuda:{device}"
+    gen = torch.Generator(device=dev).manual_seed(1234)      # the same A and W on every rank
+    a = (torch.randn(gm, gk, generator=gen, device=dev) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(gk, gn, generator=gen, device=dev) * 0.05).to(torch.bfloat16)
+    w_local = w[:, rank * n_local:(rank + 1) * n_local].contiguous()
+    code = 6   # BFloat16
+
+    def wrap(t):
+        err = libmod.B200Error()
+        shape = (ctypes.c_int64 * t.dim())(*t.shape)
+        return Buffer(L.b200_buffer_wrap(device, t.data_ptr(), code, shape, t.dim(), ctypes.byref(err)))
+
+    def exchange(obj):
+        out = [None] * world
+        dist.all_gather_object(out, obj)
+        return out
+
+    def gemm(a_t, w_t, out_t, n):
+        e = libmod.B200Error()
+        if not L.b200_k_gemm(device, a_t.data_ptr(), w_t.data_ptr(), out_t.data_ptr(), 1, gm, n, gk, 1, 0, code, None, 0, ctypes.byref(e)):
+            raise RuntimeError(L.take_string(e.message))
+
+    mm = ColumnShardedMatmul(backend, device, rank, world, gm, n_local, gk, np.dtype(ml_dtypes.bfloat16), exchange, dist.barrier)
+    a_buf, w_buf = wrap(a), wrap(w_local)
+    c_buf = mm.run(a_buf, w_buf)
+    ref = torch.empty(gm, gn, device=dev, dtype=torch.bfloat16)
+    gemm(a, w, ref, gn)
+    backend.Synchronize(device)
+    got = backend.ToNumpy(c_buf).view(np.uint16)
+    match = bool(np.array_equal(got, ref.view(torch.int16).cpu().numpy().view(np.uint16)))
+    del ref
+
+    stream = torch.cuda.ExternalStream(L.b200_device_stream(device, ctypes.byref(libmod.B200Error())), device=device)
+
+    def timed(fn):
+        for _ in range(warmup):
+            fn()
+        backend.Synchronize(device)
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(iters):
+            fn()
+        e1.record(stream)
+        backend.Synchronize(device)
+        torch.cuda.synchronize()
+        dist.barrier()
+        return max_over_ranks([e0.elapsed_time(e1) / iters], device=dev)[0]
+
+    # every launch writes the same values, so back-to-back launches without the guard of run() are safe here
+    fused_ms = timed(lambda: mm.launch(a_buf, w_buf))
+    slab = torch.empty(gm, n_local, device=dev, dtype=torch.bfloat16)
+    gathered = torch.empty(world, gm, n_local, device=dev, dtype=torch.bfloat16)
+
+    def two_step():
+        gemm(a, w_local, slab, n_local)
+        with torch.cuda.stream(stream):
+            dist.all_gather_into_tensor(gathered, slab)     # leaves [world, m, n_local]: a transpose short of C
+
+    two_ms = timed(two_step)
+    gemm_only_ms = timed(lambda: gemm(a, w_local, slab, n_local))
+    matches = exchange(match)
+    mm.close()
+    flops = 2.0 * gm * n_local * gk
+    nvlink_bytes = (world - 1) * gm * n_local * 2
+    return {"what": "column-sharded matmul, all-gather fused into the GEMM epilogue (peer stores over NVLink)", "n_gpus": world,
+            "m": gm, "n": gn, "k": gk, "match_single_gpu_gemm_bitwise": all(matches), "fused_ms": fused_ms,
+            "gemm_then_nccl_all_gather_ms": two_ms, "gemm_only_ms": gemm_only_ms, "fused_TFLOP/s_per_gpu": flops / (fused_ms * 1e-3) / 1e12,
+            "nvlink_GB/s_out_per_gpu": nvlink_bytes / (fused_ms * 1e-3) / 1e9}

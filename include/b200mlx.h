@@ -407,8 +407,11 @@ bool b200_k_reduce_sum_f32(int device, const float* x, float* out, int64_t n, vo
  * allocator): the partial sums go to a 16 KiB array built into the library's
  * device image, so no scratch pointer is passed and nothing is allocated.
  * n must be <= 2^30; larger inputs are refused with B200_ERR_INVALID.  The
- * first call on a device performs one-time set-up and should precede any stream
- * capture.  All calls on a device share the array: overlapping calls would race.
+ * first call on a device looks up the array's address; on a device nothing else
+ * has used through this library it also creates the library's stream (no
+ * cudaMalloc: the library's status word is a device-image array too).  Make that
+ * first call at start-up, before any stream capture.  All calls on a device
+ * share the array: overlapping calls would race.
  * This entry point has no counterpart in the reference. */
 bool b200_k_reduce_sum_f32_noalloc(int device, const float* x, float* out, int64_t n, B200Error* err);
 

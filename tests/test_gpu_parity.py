@@ -1026,3 +1026,55 @@ def test_concurrent_executes_do_not_leak_into_each_others_graph_recording(b200, 
     for t in threads:
         t.join()
     assert not errors, errors
+
+
+# ------------------------------------------------ entry points that had no test of their own ---
+def test_buffer_copy_to_device_same_device(b200, backend):
+    # one visible GPU is enough: device 0 -> device 0 is a stream-ordered copy into a fresh buffer
+    x = np.random.default_rng(70).standard_normal((33, 129)).astype(np.float32)
+    src = backend.FromNumpy(x)
+    dst = backend.BufferCopyToDevice(src, 0)
+    assert backend.BufferDeviceNum(dst) == 0 and backend.BufferShape(dst) == backend.BufferShape(src)
+    backend.BufferFinalize(src)                      # the copy must not depend on the source staying alive
+    other = backend.FromNumpy(np.zeros_like(x))      # likely reuses the freed block
+    np.testing.assert_array_equal(backend.ToNumpy(dst), x)
+    for b in (dst, other):
+        backend.BufferFinalize(b)
+    with pytest.raises(b200.BackendError):
+        backend.BufferCopyToDevice(backend.FromNumpy(x), 99)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, BF16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("axis", [1, 3, -1])
+def test_batch_norm_for_inference(b200, backend, dtype, axis):
+    # y = (x - mean) / sqrt(var + eps) * scale + offset along the feature axis (ref mpsgraph/gomlx/function.go:1244-1261)
+    rng = np.random.default_rng(71)
+    x = rng_array(rng, (3, 5, 4, 5), dtype)
+    c = x.shape[axis]
+    scale, offset, mean = (rng_array(rng, (c,), dtype) for _ in range(3))
+    var = (np.abs(rng_array(rng, (c,), np.float32)) + 0.5).astype(dtype)
+
+    def want_fn():
+        shp = [1] * 4
+        shp[axis] = c
+        v64 = lambda t: t.astype(np.float64).reshape(shp)
+        y = (x.astype(np.float64) - v64(mean)) / np.sqrt(v64(var) + float(np.float32(1e-3))) * v64(scale) + v64(offset)
+        return y.astype(dtype)
+    (got,) = run_backend(b200, backend, lambda f, a, s, o, m, v: f.BatchNormForInference(a, s, o, m, v, 1e-3, axis), [x, scale, offset, mean, var])
+    ok, viol = compare(got, want_fn(), 1e-5 if dtype == np.float32 else 2e-2, 1.0)
+    assert ok, viol
+
+
+@pytest.mark.parametrize("op,plain", [("EqualTotalOrder", "Equal"), ("NotEqualTotalOrder", "NotEqual"), ("LessThanTotalOrder", "LessThan"),
+                                      ("LessOrEqualTotalOrder", "LessOrEqual"), ("GreaterThanTotalOrder", "GreaterThan"),
+                                      ("GreaterOrEqualTotalOrder", "GreaterOrEqual")])
+def test_total_order_compares_delegate_to_plain_compares(b200, backend, op, plain):
+    # the reference delegates every *TotalOrder compare to the plain one (ref mpsgraph/gomlx/function.go:2234-2256)
+    rng = np.random.default_rng(72)
+    a = rng.integers(-3, 4, size=(9, 31)).astype(np.float32)
+    b = rng.integers(-3, 4, size=(31,)).astype(np.float32)
+    if not hasattr(backend.Builder("probe").Main(), op):
+        pytest.fail(f"Function has no {op}")
+    (got,) = run_backend(b200, backend, lambda f, x, y: getattr(f, op)(x, y), [a, b])
+    (want,) = run_backend(b200, backend, lambda f, x, y: getattr(f, plain)(x, y), [a, b])
+    np.testing.assert_array_equal(got, want)

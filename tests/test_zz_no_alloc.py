@@ -79,3 +79,30 @@ def test_noalloc_reduce_small_input_and_limit(b200, backend):
     assert not ok and err.code == 1
     assert "outside" in L.take_string(err.message)
     backend.BufferFinalize(d)
+
+
+def test_noalloc_reduce_leaves_device_memory_untouched(b200, backend):
+    """The point of the entry: a call on an initialised device takes no device memory, neither from the driver
+    (free bytes as cudaMemGetInfo reports them) nor from this library's own pool (bytes reserved)."""
+    import torch
+    L = b200.lib()
+    rng = np.random.default_rng(41)
+    x = rng.standard_normal(2_000_000).astype(np.float32)
+    d_x = backend.FromNumpy(x)
+    d_out = backend.FromNumpy(np.zeros(1, dtype=np.float32))
+    backend.Synchronize(0)
+    free_before, _ = torch.cuda.mem_get_info(0)
+    reserved_before = L.b200_device_bytes_reserved(0)
+    for _ in range(3):
+        err = _err(b200)
+        ok = L.b200_k_reduce_sum_f32_noalloc(0, L.b200_buffer_device_ptr(d_x.handle), L.b200_buffer_device_ptr(d_out.handle), x.size,
+                                             ctypes.byref(err))
+        _check(b200, err)
+        assert ok
+    backend.Synchronize(0)
+    free_after, _ = torch.cuda.mem_get_info(0)
+    assert L.b200_device_bytes_reserved(0) == reserved_before
+    assert free_after == free_before
+    np.testing.assert_allclose(backend.ToNumpy(d_out)[0], x.astype(np.float64).sum(), rtol=1e-5, atol=1e-2)
+    for b in (d_x, d_out):
+        backend.BufferFinalize(b)
