@@ -578,7 +578,7 @@ def run_extras(b200, backend, L, libmod, torch, stream, local_rank, world, peaks
                     if not L.b200_k_gemm(local_rank, a.data_ptr(), b.data_ptr(), c.data_ptr(), 8, n, n, n, a_kmajor, 0, code, None, 0,
                                          ctypes.byref(e)):
                         raise RuntimeError(L.take_string(e.message))
-                ms = timed(launch, 3 if n == 8192 else 10)
+                ms = timed(launch, 5 if n == 8192 else 10)
                 tf = 2 * 8 * n ** 3 / (ms * 1e-3) / 1e12
                 sweep[f"{dt_name}_{form}_{n}"] = {"ms": ms, "TFLOP/s": tf, "frac_of_bf16_peak": tf / peaks["bf16_tflops"]}
             del a, b, c
@@ -609,6 +609,13 @@ def run_extras(b200, backend, L, libmod, torch, stream, local_rank, world, peaks
     out["llama_1b_fwd_bf16"] = model_tokens_per_s("llama", lc, W.llama_param_shapes(lc),
                                                  lambda f, *p: W.llama_forward(f, lc, int(b200.dtypes.BFloat16), *p),
                                                  W.llama_flops_per_token(lc), 20)
+    if world > 1:
+        # The one optional exchange of the path: a weight split by columns over the ranks, the all-gather of the result
+        # fused into the GEMM epilogue (peer stores over NVLink), checked bit for bit against the single-GPU GEMM and
+        # timed beside GEMM + NCCL all-gather.  Every rank takes part; rank 0 reports.
+        from go_darwinml_b200.sharding import column_sharded_matmul_check
+        out["column_sharded_matmul"] = column_sharded_matmul_check(backend, local_rank, int(os.environ.get("RANK", "0")), world,
+                                                                   8192, 16384, 4096, iters=10, warmup=3)
     return out
 
 

@@ -646,6 +646,61 @@ class Function:
                                                             self._h(scale, "BatchNormForInference"), self._h(offset, "BatchNormForInference"),
                                                             float(epsilon), int(feature_axis), ctypes.byref(err)), err, "BatchNormForInference")
 
+    # -- training-side ops (ref function.go:1263-1527, 1627-1692; gather.go:441-641) --
+    def BatchNormForTraining(self, operand, scale, offset, epsilon: float, feature_axis: int):
+        """Returns (normalized, batchMean, batchVariance) (ref function.go:1263-1375)."""
+        err = _lib.B200Error()
+        y, m, v = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_void_p()
+        self._L.b200_batch_norm_training(self.builder.ctx, self._h(operand, "BatchNormForTraining: operand"),
+                                         self._h(scale, "BatchNormForTraining: scale"), self._h(offset, "BatchNormForTraining: offset"),
+                                         float(epsilon), int(feature_axis), ctypes.byref(y), ctypes.byref(m), ctypes.byref(v), ctypes.byref(err))
+        _check(err, "BatchNormForTraining")
+        return Value(y.value, self), Value(m.value, self), Value(v.value, self)
+
+    def BatchNormGradient(self, operand, scale, mean, variance, grad_output, epsilon: float, feature_axis: int):
+        """Returns (gradOperand, gradScale, gradOffset) (ref function.go:1377-1527)."""
+        err = _lib.B200Error()
+        a, b, c = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_void_p()
+        self._L.b200_batch_norm_gradient(self.builder.ctx, self._h(operand, "BatchNormGradient: operand"), self._h(scale, "BatchNormGradient: scale"),
+                                         self._h(mean, "BatchNormGradient: mean"), self._h(variance, "BatchNormGradient: variance"),
+                                         self._h(grad_output, "BatchNormGradient: gradOutput"), float(epsilon), int(feature_axis),
+                                         ctypes.byref(a), ctypes.byref(b), ctypes.byref(c), ctypes.byref(err))
+        _check(err, "BatchNormGradient")
+        return Value(a.value, self), Value(b.value, self), Value(c.value, self)
+
+    def _scatter(self, what: str, mode: int, operand, scatter_indices, updates, index_vector_axis, update_window_axes, inserted_window_axes,
+                 scatter_axes_to_operand_axes, indices_are_sorted, unique_indices) -> Value:
+        err = _lib.B200Error()
+        return self._wrap(self._L.b200_scatter(self.builder.ctx, mode, self._h(operand, what + ": operand"), self._h(scatter_indices, what + ": indices"),
+                                               self._h(updates, what + ": updates"), int(index_vector_axis), _i32(update_window_axes),
+                                               len(update_window_axes), _i32(inserted_window_axes), len(inserted_window_axes),
+                                               _i32(scatter_axes_to_operand_axes), len(scatter_axes_to_operand_axes), bool(indices_are_sorted),
+                                               bool(unique_indices), ctypes.byref(err)), err, what)
+
+    def ScatterSum(self, operand, scatter_indices, updates, index_vector_axis, update_window_axes, inserted_window_axes,
+                   scatter_axes_to_operand_axes, indices_are_sorted=False, unique_indices=False) -> Value:
+        return self._scatter("ScatterSum", 0, operand, scatter_indices, updates, index_vector_axis, update_window_axes, inserted_window_axes,
+                             scatter_axes_to_operand_axes, indices_are_sorted, unique_indices)
+
+    def ScatterMax(self, operand, scatter_indices, updates, index_vector_axis, update_window_axes, inserted_window_axes,
+                   scatter_axes_to_operand_axes, indices_are_sorted=False, unique_indices=False) -> Value:
+        return self._scatter("ScatterMax", 1, operand, scatter_indices, updates, index_vector_axis, update_window_axes, inserted_window_axes,
+                             scatter_axes_to_operand_axes, indices_are_sorted, unique_indices)
+
+    def ScatterMin(self, operand, scatter_indices, updates, index_vector_axis, update_window_axes, inserted_window_axes,
+                   scatter_axes_to_operand_axes, indices_are_sorted=False, unique_indices=False) -> Value:
+        return self._scatter("ScatterMin", 2, operand, scatter_indices, updates, index_vector_axis, update_window_axes, inserted_window_axes,
+                             scatter_axes_to_operand_axes, indices_are_sorted, unique_indices)
+
+    def RNGBitGenerator(self, state, shape: Shape):
+        """Returns (newState, values) (ref function.go:1627-1692); state is (Uint64)[3]."""
+        err = _lib.B200Error()
+        ns, v = ctypes.c_void_p(), ctypes.c_void_p()
+        self._L.b200_rng_bit_generator(self.builder.ctx, self._h(state, "RNGBitGenerator: state"), int(shape.DType), _i64(shape.Dimensions),
+                                       shape.Rank(), ctypes.byref(ns), ctypes.byref(v), ctypes.byref(err))
+        _check(err, "RNGBitGenerator")
+        return Value(ns.value, self), Value(v.value, self)
+
 
 class Executable:
     """backends.Executable (ref executable.go:18-112)."""

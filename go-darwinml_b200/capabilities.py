@@ -1,10 +1,10 @@
 """backends.Capabilities of this backend (ref mpsgraph/gomlx/capabilities.go:14-167).
 
 The reference declares 96 op types and 12 dtypes.  Listed here is what this
-backend lowers; op types of the reference that are outside the forward
-(inference) path -- convolution, pooling, scatter, dynamic slice/update, RNG,
-batch-norm training/gradient, While/If/Sort/Call -- are absent, so GoMLX reports
-them as not implemented instead of failing late.
+backend lowers.  Op types of the reference that it does not lower --
+convolution, pooling and their gradients (SelectAndScatter), While / If / Sort /
+Call over sub-functions -- are absent, so GoMLX reports them as not implemented
+instead of failing late.
 """
 from __future__ import annotations
 
@@ -25,6 +25,7 @@ OPERATIONS = [
     "Reshape", "Transpose", "ConvertDType", "BroadcastInDim", "Slice", "Concatenate", "Reverse", "Pad", "DynamicSlice", "DynamicUpdateSlice", "Where", "Clamp",
     "DotGeneral", "ReduceSum", "ReduceProduct", "ReduceMax", "ReduceMin", "ReduceLogicalAnd", "ReduceLogicalOr", "ArgMinMax",
     "Gather", "BatchNormForInference",
+    "ScatterSum", "ScatterMax", "ScatterMin", "BatchNormForTraining", "BatchNormGradient", "RNGBitGenerator",
     "FusedSoftmax", "FusedGelu", "FusedLayerNorm", "FusedDense", "FusedAttentionQKVProjection",
     "FusedScaledDotProductAttention",
 ]

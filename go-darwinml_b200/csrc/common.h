@@ -179,6 +179,8 @@ enum class Op : int {
   Softmax, SoftmaxMasked, LayerNorm, RmsNorm, Attention,
   // produced only by the compile-time rewrites: x * c + swap_halves(x) * s on the last axis (rotary embedding)
   Rope,
+  // training side: XLA scatter with a combiner (sum / max / min), and random bits from a counter-based generator
+  Scatter, RngBits,
   kNumOps
 };
 const char* op_name(Op op);

@@ -26,7 +26,7 @@ const char* op_name(Op op) {
       "Where", "Clamp",
       "Cast", "Reshape", "Transpose", "BroadcastInDim", "Slice", "Concatenate", "Reverse", "Pad", "DynamicSlice", "DynamicUpdateSlice",
       "DotGeneral", "Reduce", "ArgMinMax", "Gather",
-      "Softmax", "SoftmaxMasked", "LayerNorm", "RmsNorm", "Attention", "Rope"};
+      "Softmax", "SoftmaxMasked", "LayerNorm", "RmsNorm", "Attention", "Rope", "Scatter", "RngBits"};
   static_assert(sizeof(names) / sizeof(names[0]) == (size_t)Op::kNumOps, "op_name table out of date");
   return names[(int)op];
 }
@@ -1133,6 +1133,227 @@ B200Value b200_batch_norm_inference(B200Context ctx, B200Value input, B200Value 
   if (gamma) { B200Value gg = bc(gamma); if (!gg) return nullptr; y = b200_mul(ctx, y, gg, err); if (!y) return nullptr; }
   if (beta) { B200Value bb = bc(beta); if (!bb) return nullptr; y = b200_add(ctx, y, bb, err); if (!y) return nullptr; }
   return y;
+}
+
+// ---- training-side ops ------------------------------------------------------------------------------------
+// BatchNormForTraining (ref mpsgraph function.go:1263-1375): batch statistics over every axis but the feature axis,
+// biased variance of the centred value (two-pass), rsqrt(var + eps), scale, offset; mean and variance come back as
+// [feature] vectors.  Built from graph primitives like the reference's, so the lowering fuses the elementwise parts
+// and the reductions read their operand chains in place.  scale / offset are laid along the FEATURE axis (the
+// reference relies on trailing-axis broadcasting, which coincides when the feature axis is the last one).
+bool b200_batch_norm_training(B200Context ctx, B200Value operand, B200Value scale, B200Value offset, float epsilon, int feature_axis,
+                              B200Value* out_normalized, B200Value* out_mean, B200Value* out_variance, B200Error* err) {
+  clear_error(err);
+  Node *n, *sc, *of;
+  Status s = check_node(ctx, operand, "BatchNormForTraining: operand", &n);
+  if (s.ok()) s = check_node(ctx, scale, "BatchNormForTraining: scale", &sc);
+  if (s.ok()) s = check_node(ctx, offset, "BatchNormForTraining: offset", &of);
+  int a = 0;
+  if (s.ok()) s = normalize_axis("BatchNormForTraining", feature_axis, n->rank(), &a);
+  if (s.ok() && !dtype_is_float(n->dtype)) s = Status::Invalid("BatchNormForTraining: needs a float operand");
+  if (s.ok() && (sc->num_elements() != n->dims[a] || of->num_elements() != n->dims[a]))
+    s = Status::Invalid(strfmt("BatchNormForTraining: scale and offset must hold %lld elements (the feature axis)", (long long)n->dims[a]));
+  if (!s.ok()) { set_error(err, s); return false; }
+  if (!out_normalized || !out_mean || !out_variance) { set_error(err, Status::Invalid("BatchNormForTraining: null output pointer")); return false; }
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  std::vector<int> batch_axes;
+  int64_t count = 1;
+  for (int i = 0; i < n->rank(); ++i)
+    if (i != a) { batch_axes.push_back(i); count *= n->dims[i]; }
+  const int64_t fdim[1] = {n->dims[a]};
+  auto over_batch = [&](B200Value v) -> B200Value {   // sum over the batch axes -> [feature]
+    if (batch_axes.empty()) return b200_reshape(ctx, v, fdim, 1, err);
+    return b200_reduce(ctx, v, B200_REDUCE_SUM, batch_axes.data(), (int)batch_axes.size(), err);
+  };
+  auto along_feature = [&](B200Value v) -> B200Value {   // [feature] -> operand shape
+    B200Value flat = b200_reshape(ctx, v, fdim, 1, err);
+    if (!flat) return nullptr;
+    return b200_broadcast_in_dim(ctx, flat, n->dims.data(), n->rank(), &a, 1, err);
+  };
+  B200Value cnt = reinterpret_cast<B200Value>(make_scalar_const(g, n->dtype, (double)count));
+  B200Value eps = reinterpret_cast<B200Value>(make_scalar_const(g, n->dtype, (double)epsilon));
+  B200Value sum = over_batch(operand); if (!sum) return false;
+  B200Value mean = b200_div(ctx, sum, cnt, err); if (!mean) return false;
+  B200Value mean_b = along_feature(mean); if (!mean_b) return false;
+  B200Value diff = b200_sub(ctx, operand, mean_b, err); if (!diff) return false;
+  B200Value sq = b200_mul(ctx, diff, diff, err); if (!sq) return false;
+  B200Value vsum = over_batch(sq); if (!vsum) return false;
+  B200Value var = b200_div(ctx, vsum, cnt, err); if (!var) return false;
+  B200Value ve = b200_add(ctx, var, eps, err); if (!ve) return false;
+  B200Value inv = b200_rsqrt(ctx, ve, err); if (!inv) return false;
+  B200Value inv_b = along_feature(inv); if (!inv_b) return false;
+  B200Value y = b200_mul(ctx, diff, inv_b, err); if (!y) return false;
+  B200Value sc_b = along_feature(scale); if (!sc_b) return false;
+  y = b200_mul(ctx, y, sc_b, err); if (!y) return false;
+  B200Value of_b = along_feature(offset); if (!of_b) return false;
+  y = b200_add(ctx, y, of_b, err); if (!y) return false;
+  *out_normalized = y;
+  *out_mean = mean;
+  *out_variance = var;
+  return true;
+}
+
+// BatchNormGradient (ref mpsgraph function.go:1377-1527):
+//   xhat = (x - mean) * rsqrt(var + eps);  gradOffset = sum(dy);  gradScale = sum(dy * xhat);
+//   gradOperand = (1 / N) * scale * rsqrt(var + eps) * (N * dy - gradOffset - xhat * gradScale)       sums over the batch axes
+bool b200_batch_norm_gradient(B200Context ctx, B200Value operand, B200Value scale, B200Value mean, B200Value variance, B200Value grad_output,
+                              float epsilon, int feature_axis, B200Value* out_grad_operand, B200Value* out_grad_scale,
+                              B200Value* out_grad_offset, B200Error* err) {
+  clear_error(err);
+  Node *n, *sc, *mn, *vr, *dy;
+  Status s = check_node(ctx, operand, "BatchNormGradient: operand", &n);
+  if (s.ok()) s = check_node(ctx, scale, "BatchNormGradient: scale", &sc);
+  if (s.ok()) s = check_node(ctx, mean, "BatchNormGradient: mean", &mn);
+  if (s.ok()) s = check_node(ctx, variance, "BatchNormGradient: variance", &vr);
+  if (s.ok()) s = check_node(ctx, grad_output, "BatchNormGradient: gradOutput", &dy);
+  int a = 0;
+  if (s.ok()) s = normalize_axis("BatchNormGradient", feature_axis, n->rank(), &a);
+  if (s.ok() && !dtype_is_float(n->dtype)) s = Status::Invalid("BatchNormGradient: needs a float operand");
+  if (s.ok() && dy->dims != n->dims) s = Status::Invalid("BatchNormGradient: gradOutput must have the operand's shape");
+  if (s.ok())
+    for (Node* p : {sc, mn, vr})
+      if (p->num_elements() != n->dims[a]) s = Status::Invalid(strfmt("BatchNormGradient: scale, mean and variance must hold %lld elements", (long long)n->dims[a]));
+  if (!s.ok()) { set_error(err, s); return false; }
+  if (!out_grad_operand || !out_grad_scale || !out_grad_offset) { set_error(err, Status::Invalid("BatchNormGradient: null output pointer")); return false; }
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  std::vector<int> batch_axes;
+  int64_t count = 1;
+  for (int i = 0; i < n->rank(); ++i)
+    if (i != a) { batch_axes.push_back(i); count *= n->dims[i]; }
+  const int64_t fdim[1] = {n->dims[a]};
+  auto over_batch = [&](B200Value v) -> B200Value {
+    if (batch_axes.empty()) return b200_reshape(ctx, v, fdim, 1, err);
+    return b200_reduce(ctx, v, B200_REDUCE_SUM, batch_axes.data(), (int)batch_axes.size(), err);
+  };
+  auto along_feature = [&](B200Value v) -> B200Value {
+    B200Value flat = b200_reshape(ctx, v, fdim, 1, err);
+    if (!flat) return nullptr;
+    return b200_broadcast_in_dim(ctx, flat, n->dims.data(), n->rank(), &a, 1, err);
+  };
+  B200Value eps = reinterpret_cast<B200Value>(make_scalar_const(g, n->dtype, (double)epsilon));
+  B200Value n_c = reinterpret_cast<B200Value>(make_scalar_const(g, n->dtype, (double)count));
+  B200Value inv_n = reinterpret_cast<B200Value>(make_scalar_const(g, n->dtype, 1.0 / (double)count));
+  B200Value ve = b200_add(ctx, variance, eps, err); if (!ve) return false;
+  B200Value inv = b200_rsqrt(ctx, ve, err); if (!inv) return false;
+  B200Value inv_b = along_feature(inv); if (!inv_b) return false;
+  B200Value mean_b = along_feature(mean); if (!mean_b) return false;
+  B200Value centered = b200_sub(ctx, operand, mean_b, err); if (!centered) return false;
+  B200Value xhat = b200_mul(ctx, centered, inv_b, err); if (!xhat) return false;
+  B200Value g_off = over_batch(grad_output); if (!g_off) return false;
+  B200Value dyx = b200_mul(ctx, grad_output, xhat, err); if (!dyx) return false;
+  B200Value g_sc = over_batch(dyx); if (!g_sc) return false;
+  B200Value t1 = b200_mul(ctx, n_c, grad_output, err); if (!t1) return false;
+  B200Value g_off_b = along_feature(g_off); if (!g_off_b) return false;
+  t1 = b200_sub(ctx, t1, g_off_b, err); if (!t1) return false;
+  B200Value g_sc_b = along_feature(g_sc); if (!g_sc_b) return false;
+  B200Value t3 = b200_mul(ctx, xhat, g_sc_b, err); if (!t3) return false;
+  t1 = b200_sub(ctx, t1, t3, err); if (!t1) return false;
+  B200Value go = b200_mul(ctx, inv_n, t1, err); if (!go) return false;
+  B200Value sc_b = along_feature(scale); if (!sc_b) return false;
+  go = b200_mul(ctx, sc_b, go, err); if (!go) return false;
+  go = b200_mul(ctx, inv_b, go, err); if (!go) return false;
+  *out_grad_operand = go;
+  *out_grad_scale = g_sc;
+  *out_grad_offset = g_off;
+  return true;
+}
+
+// ScatterSum / ScatterMax / ScatterMin (ref mpsgraph gather.go:441-641): XLA scatter with a combiner.  The result is the
+// operand with every element of `updates` combined into the position its scatter indices name:
+//   update index u = (scatter coordinates s, window coordinates w);  index vector i = indices[s along index_vector_axis];
+//   operand position: axis scatter_axes_to_operand_axes[k] starts at i[k]; window axis j of the update walks the j-th operand
+//   axis that is not an inserted window axis.  An element whose position falls outside the operand is dropped.
+B200Value b200_scatter(B200Context ctx, int mode, B200Value operand, B200Value scatter_indices, B200Value updates, int index_vector_axis,
+                       const int* update_window_axes, int num_update_window_axes, const int* inserted_window_axes,
+                       int num_inserted_window_axes, const int* scatter_axes_to_operand_axes, int num_scatter_axes,
+                       bool indices_are_sorted, bool unique_indices, B200Error* err) {
+  (void)indices_are_sorted;
+  clear_error(err);
+  const char* what = mode == 0 ? "ScatterSum" : mode == 1 ? "ScatterMax" : "ScatterMin";
+  if (mode < 0 || mode > 2) return ret(err, Status::Invalid("Scatter: mode must be 0 (sum), 1 (max) or 2 (min)"), nullptr);
+  Node *op, *idx, *upd;
+  Status s = check_node(ctx, operand, what, &op);
+  if (s.ok()) s = check_node(ctx, scatter_indices, what, &idx);
+  if (s.ok()) s = check_node(ctx, updates, what, &upd);
+  if (!s.ok()) return ret(err, s, nullptr);
+  if (!dtype_is_int(idx->dtype)) return ret(err, Status::Invalid(std::string(what) + ": scatter indices must be integers"), nullptr);
+  if (upd->dtype != op->dtype) return ret(err, Status::Invalid(std::string(what) + ": updates must have the operand's dtype"), nullptr);
+  if (op->dtype == B200_BOOL) return ret(err, Status::Invalid(std::string(what) + ": Bool operand"), nullptr);
+  const int orank = op->rank(), irank = idx->rank(), urank = upd->rank();
+  if (orank > 8 || urank > 8 || irank > 8) return ret(err, Status::Unsupported(std::string(what) + ": more than 8 dims"), nullptr);
+  if (index_vector_axis < 0 || index_vector_axis > irank) return ret(err, Status::Invalid(std::string(what) + ": indexVectorAxis out of range"), nullptr);
+  const int64_t ncomp = index_vector_axis == irank ? 1 : idx->dims[index_vector_axis];
+  if (ncomp != num_scatter_axes) return ret(err, Status::Invalid(std::string(what) + ": scatterAxesToOperandAxes length must equal the index vector size"), nullptr);
+  std::set<int> inserted, window_upd, mapped;
+  for (int i = 0; i < num_inserted_window_axes; ++i)
+    if (inserted_window_axes[i] < 0 || inserted_window_axes[i] >= orank || !inserted.insert(inserted_window_axes[i]).second)
+      return ret(err, Status::Invalid(std::string(what) + ": bad insertedWindowAxes"), nullptr);
+  for (int i = 0; i < num_update_window_axes; ++i) {
+    if (update_window_axes[i] < 0 || update_window_axes[i] >= urank || !window_upd.insert(update_window_axes[i]).second)
+      return ret(err, Status::Invalid(std::string(what) + ": bad updateWindowAxes"), nullptr);
+    if (i > 0 && update_window_axes[i] <= update_window_axes[i - 1]) return ret(err, Status::Invalid(std::string(what) + ": updateWindowAxes must ascend"), nullptr);
+  }
+  for (int i = 0; i < num_scatter_axes; ++i)
+    if (scatter_axes_to_operand_axes[i] < 0 || scatter_axes_to_operand_axes[i] >= orank || !mapped.insert(scatter_axes_to_operand_axes[i]).second)
+      return ret(err, Status::Invalid(std::string(what) + ": bad scatterAxesToOperandAxes"), nullptr);
+  if (num_update_window_axes != orank - num_inserted_window_axes)
+    return ret(err, Status::Invalid(std::string(what) + ": updateWindowAxes must have one entry per operand axis that is not an inserted window axis"), nullptr);
+  // window axis j of the update <-> j-th operand axis that is not inserted; its extent must fit the operand
+  std::vector<int> window_operand_axis;
+  for (int i = 0; i < orank; ++i)
+    if (!inserted.count(i)) window_operand_axis.push_back(i);
+  for (int j = 0; j < num_update_window_axes; ++j)
+    if (upd->dims[update_window_axes[j]] > op->dims[window_operand_axis[j]])
+      return ret(err, Status::Invalid(std::string(what) + ": an update window is larger than the operand"), nullptr);
+  // the update's scatter dims are the indices' batch dims, in order
+  std::vector<int64_t> batch_dims, scatter_dims;
+  for (int i = 0; i < irank; ++i)
+    if (i != index_vector_axis) batch_dims.push_back(idx->dims[i]);
+  for (int i = 0; i < urank; ++i)
+    if (!window_upd.count(i)) scatter_dims.push_back(upd->dims[i]);
+  if (batch_dims != scatter_dims) return ret(err, Status::Invalid(std::string(what) + ": the updates' scatter dims must equal the indices' batch dims"), nullptr);
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  Node* o = g.Add(Op::Scatter, op->dtype, op->dims, {op, idx, upd});
+  // ia = [mode, index_vector_axis, unique, n_uw, uw..., n_iw, iw..., n_map, map...]
+  o->ia = {mode, index_vector_axis, unique_indices ? 1 : 0, num_update_window_axes};
+  for (int i = 0; i < num_update_window_axes; ++i) o->ia.push_back(update_window_axes[i]);
+  o->ia.push_back(num_inserted_window_axes);
+  for (int i = 0; i < num_inserted_window_axes; ++i) o->ia.push_back(inserted_window_axes[i]);
+  o->ia.push_back(num_scatter_axes);
+  for (int i = 0; i < num_scatter_axes; ++i) o->ia.push_back(scatter_axes_to_operand_axes[i]);
+  return ret(err, Status::OK(), o);
+}
+
+// RNGBitGenerator (ref mpsgraph function.go:1627-1692): state is [3] Uint64; returns the advanced state (every word + 1,
+// as the reference advances it) and values of the requested dtype and shape.  The reference takes its values from
+// MPSGraph's own generator, which ignores the state; here they are a pure function of the state: Philox4x32-10 keyed by
+// state[0], counter (state[1], state[2]) + block number, four 32-bit words per block.  Integer dtypes get the raw bits
+// (64-bit types two words), float dtypes a uniform value in [0, 1) from the top bits.
+bool b200_rng_bit_generator(B200Context ctx, B200Value state, int dtype, const int64_t* shape, int rank, B200Value* out_new_state,
+                            B200Value* out_values, B200Error* err) {
+  clear_error(err);
+  Node* st;
+  Status s = check_node(ctx, state, "RNGBitGenerator: state", &st);
+  if (s.ok() && (st->dtype != B200_UINT64 || st->rank() != 1 || st->dims[0] != 3))
+    s = Status::Invalid("RNGBitGenerator: expected state shape (Uint64)[3]");
+  if (s.ok() && (!dtype_valid(dtype) || dtype == B200_BOOL)) s = Status::Invalid("RNGBitGenerator: unsupported dtype");
+  if (s.ok()) s = check_shape("RNGBitGenerator", shape, rank);
+  if (!s.ok()) { set_error(err, s); return false; }
+  if (!out_new_state || !out_values) { set_error(err, Status::Invalid("RNGBitGenerator: null output pointer")); return false; }
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  Node* v = g.Add(Op::RngBits, dtype, std::vector<int64_t>(shape, shape + rank), {st});
+  const uint64_t one_bits = 1;
+  Node* one = g.Add(Op::Constant, B200_UINT64, {}, {});
+  one->data.resize(8);
+  memcpy(one->data.data(), &one_bits, 8);
+  const int64_t three[1] = {3};
+  B200Value one_b = b200_broadcast_in_dim(ctx, reinterpret_cast<B200Value>(one), three, 1, nullptr, 0, err);
+  if (!one_b) return false;
+  B200Value ns = b200_add(ctx, state, one_b, err);
+  if (!ns) return false;
+  *out_new_state = ns;
+  *out_values = reinterpret_cast<B200Value>(v);
+  return true;
 }
 
 }  // extern "C"

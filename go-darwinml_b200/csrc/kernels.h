@@ -78,8 +78,9 @@ struct EwProgram {
   bool wide = false;  // needs 64-bit registers (any I64/U64/F64 value)
 };
 Status ewise_run(Device* dev, const EwProgram& prog);
-// The two templated fast shapes of ewise_run alone (x op y; small trees): *taken says whether one of them was launched.
-Status ewise_run_fast(Device* dev, const EwProgram& prog, bool* taken);
+// The templated fast shapes of ewise_run alone: x op y, and (with trees = true) the small expression trees.  *taken says
+// whether one of them was launched.
+Status ewise_run_fast(Device* dev, const EwProgram& prog, bool* taken, bool trees = true);
 
 // Run-time compiled form of a program (ewise_jit.cu): one straight-line kernel per distinct program text, built with
 // NVRTC at plan time and cached for the life of the process.  ewise_jit_prepare fails with B200_ERR_UNSUPPORTED when
@@ -184,6 +185,37 @@ struct GatherParams {
   int start_index_map[kMaxDims];
 };
 Status gather_general(Device* dev, const GatherParams& p);
+
+// --------------------------------------------------------------- scatter ---
+// XLA scatter with a combiner (mode 0 sum, 1 max, 2 min): y must already hold a copy of the operand; one thread per
+// element of `updates` combines it into the operand position its scatter indices name, out-of-range elements are dropped.
+struct ScatterParams {
+  void* y = nullptr;              // operand-shaped, pre-filled with the operand
+  const void* indices = nullptr;
+  const void* updates = nullptr;
+  int dtype = B200_FLOAT32;
+  int ids_dtype = B200_INT32;
+  int mode = 0;
+  int operand_rank = 0;
+  int64_t operand_dims[kMaxDims] = {0};
+  int64_t operand_strides[kMaxDims] = {0};
+  int update_rank = 0;
+  int64_t update_dims[kMaxDims] = {0};
+  int num_batch_dims = 0;                          // update axes that are scatter (batch) axes, in order
+  int batch_update_axis[kMaxDims];
+  int64_t batch_index_strides[kMaxDims] = {0};     // strides of the indices tensor for each batch coordinate
+  int64_t index_vector_stride = 0;
+  int num_index_components = 0;
+  int scatter_axes_to_operand_axes[kMaxDims];
+  int num_window_axes = 0;                         // update window axis j walks operand axis window_operand_axis[j]
+  int window_update_axis[kMaxDims];
+  int window_operand_axis[kMaxDims];
+};
+Status scatter(Device* dev, const ScatterParams& p);
+
+// ------------------------------------------------------------------- RNG ---
+// n elements of `dtype` from Philox4x32-10 keyed and positioned by the [3] Uint64 state in device memory.
+Status rng_bits(Device* dev, const void* state, void* y, int dtype, int64_t n);
 
 // ------------------------------------------------------------------ GEMM ---
 struct GemmParams {

@@ -416,7 +416,7 @@ __global__ void __launch_bounds__(256) ewise_tree_fast_kernel(const TreeArgs g) 
     }
     if (g.post != 0) {
 #pragma unroll
-      for (int e = 0; e < N; ++e) r[e] = round_like<T>(f_unary<float>(g.post, r[e]));
+      for (int e = 0; e < N; ++e) r[e] = round_like<T>(sizeof(T) == 2 ? f_unary_to16(g.post, r[e]) : f_unary<float>(g.post, r[e]));
     }
     g.out[i] = FastCvt<T>::pack(r);
   }
@@ -536,14 +536,14 @@ bool try_tree_fast(Device* dev, const EwProgram& p, int64_t n) {
 
 }  // namespace
 
-Status ewise_run_fast(Device* dev, const EwProgram& prog_in, bool* taken) {
+Status ewise_run_fast(Device* dev, const EwProgram& prog_in, bool* taken, bool trees) {
   *taken = false;
   int64_t n = 1;
   for (int d = 0; d < prog_in.rank; ++d) n *= prog_in.dims[d];
   if (n == 0) { *taken = true; return Status::OK(); }
   B200_TRY(dev->MakeCurrent());
   if (try_binary_fast(dev, prog_in, n)) { *taken = true; return dev->CheckLaunch("ewise_binary_fast"); }
-  if (try_tree_fast(dev, prog_in, n)) { *taken = true; return dev->CheckLaunch("ewise_tree_fast"); }
+  if (trees && try_tree_fast(dev, prog_in, n)) { *taken = true; return dev->CheckLaunch("ewise_tree_fast"); }
   return Status::OK();
 }
 

@@ -16,7 +16,10 @@
 //
 // NVRTC is looked up at run time (dlopen); when it is missing, or a compile fails, the caller keeps using the
 // interpreter kernel, which needs nothing but this library.
+#include <cuda_fp16.h>
 #include <dlfcn.h>
+
+#include <cstring>
 
 #include <mutex>
 #include <sstream>
@@ -130,6 +133,57 @@ template <typename R> __device__ __forceinline__ uint64_t ew_to_raw(R r, int dt)
     default: return (uint64_t)r;
   }
 }
+// Two 16-bit float results as one 32-bit word (low half first).  The registers already hold values of the 16-bit type
+// (every op rounds), so bf16 is a matter of taking the upper halves; f16 takes one packed conversion.
+template <typename R> __device__ __forceinline__ uint32_t ew_pack_pair(R a, R b, int dt) {
+  if (dt == B200_BFLOAT16) return ((uint32_t)a >> 16) | ((uint32_t)b & 0xffff0000u);
+  uint32_t p;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(p) : "f"(as_f(b)), "f"(as_f(a)));
+  return p;
+}
+// ---- packed mode: a chain whose every value is of ONE 16-bit float type keeps two elements per 32-bit register (low
+// half = the even element).  Add / Sub / Mul / Max / Min / Neg / Abs are single packed instructions with one IEEE
+// rounding of the exact result; every other op unpacks to fp32, computes as the unpacked path does, and repacks with
+// one packed conversion.  Loads and stores move the registers as they are.
+__device__ __forceinline__ float ew_p2_lo(uint32_t p, int dt) { return dt == B200_BFLOAT16 ? __uint_as_float(p << 16) : ew_f16_to_f((uint16_t)(p & 0xffffu)); }
+__device__ __forceinline__ float ew_p2_hi(uint32_t p, int dt) { return dt == B200_BFLOAT16 ? __uint_as_float(p & 0xffff0000u) : ew_f16_to_f((uint16_t)(p >> 16)); }
+__device__ __forceinline__ uint32_t ew_p2_pack(float lo, float hi, int dt) {
+  uint32_t p;
+  if (dt == B200_BFLOAT16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(p) : "f"(hi), "f"(lo));
+  else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(p) : "f"(hi), "f"(lo));
+  return p;
+}
+#define EW_P2_BIN(NAME, BF, HF)                                                                       \
+  __device__ __forceinline__ uint32_t NAME(uint32_t a, uint32_t b, int dt) {                          \
+    uint32_t r;                                                                                       \
+    if (dt == B200_BFLOAT16) asm(BF " %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));                      \
+    else asm(HF " %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));                                          \
+    return r;                                                                                         \
+  }
+EW_P2_BIN(ew_p2_add, "add.rn.bf16x2", "add.rn.f16x2")
+EW_P2_BIN(ew_p2_sub, "sub.rn.bf16x2", "sub.rn.f16x2")
+EW_P2_BIN(ew_p2_mul, "mul.rn.bf16x2", "mul.rn.f16x2")
+EW_P2_BIN(ew_p2_max, "max.NaN.bf16x2", "max.NaN.f16x2")
+EW_P2_BIN(ew_p2_min, "min.NaN.bf16x2", "min.NaN.f16x2")
+__device__ __forceinline__ uint32_t ew_p2_op(int op, int dt, uint32_t a, uint32_t b, uint32_t c) {
+  switch ((Op)op) {
+    case Op::Add: return ew_p2_add(a, b, dt);
+    case Op::Sub: return ew_p2_sub(a, b, dt);
+    case Op::Mul: return ew_p2_mul(a, b, dt);
+    case Op::Max: return ew_p2_max(a, b, dt);
+    case Op::Min: return ew_p2_min(a, b, dt);
+    case Op::Neg: return a ^ 0x80008000u;
+    case Op::Abs: return a & 0x7fff7fffu;
+    case Op::Identity: return a;
+    default: {
+      const float lo = as_f(eval_op_unrounded<uint32_t>(op, dt, from_f<uint32_t>(ew_p2_lo(a, dt)), from_f<uint32_t>(ew_p2_lo(b, dt)),
+                                                        from_f<uint32_t>(ew_p2_lo(c, dt))));
+      const float hi = as_f(eval_op_unrounded<uint32_t>(op, dt, from_f<uint32_t>(ew_p2_hi(a, dt)), from_f<uint32_t>(ew_p2_hi(b, dt)),
+                                                        from_f<uint32_t>(ew_p2_hi(c, dt))));
+      return ew_p2_pack(lo, hi, dt);
+    }
+  }
+}
 template <typename R> __device__ __forceinline__ R ew_iota(long long coord, int dt) {
   if (dt == B200_FLOAT64) return (R)from_d((double)coord);
   if (dtype_is_float(dt)) return from_f<R>(round_to(dt, (float)coord));
@@ -222,7 +276,39 @@ struct GenConfig {
   int vec = 1;        // elements per thread and vector
   int unroll = 1;     // vectors per thread
   bool wide_index = false;   // more than 2^32 - 1 elements
+  bool packed = false;       // every value is of one 16-bit float type: two elements per register
+  int packed_dtype = 0;
 };
+
+// Packed mode applies when every leaf, every instruction and the result are of the same 16-bit float type and no
+// instruction produces or consumes anything else (compares, selects, casts, integer iotas keep the unpacked form).
+bool CanPack(const EwProgram& p, int* dtype) {
+  const int dt = p.out_dtype;
+  if (dt != B200_BFLOAT16 && dt != B200_FLOAT16) return false;
+  for (int l = 0; l < p.num_leaves; ++l)
+    if (p.leaves[l].dtype != dt) return false;
+  for (int i = 0; i < p.num_instr; ++i) {
+    const EwInstr& in = p.instr[i];
+    if (in.dtype != dt || in.sdtype != dt) return false;
+    if (in.kind == EW_CAST) return false;
+    if (in.kind == EW_OP) {
+      const int op = in.op;
+      if ((op >= (int)Op::Equal && op <= (int)Op::GreaterOrEqual) || op == (int)Op::Where || op == (int)Op::IsFinite || op == (int)Op::IsNaN)
+        return false;
+    }
+  }
+  *dtype = dt;
+  return true;
+}
+uint32_t FloatBitsTo16(uint32_t float_bits, int dt) {   // host: a value already representable in the 16-bit type
+  if (dt == B200_BFLOAT16) return float_bits >> 16;
+  float f;
+  memcpy(&f, &float_bits, 4);
+  const __half h = __float2half_rn(f);
+  uint16_t b;
+  memcpy(&b, &h, 2);
+  return b;
+}
 
 int64_t NumElements(const EwProgram& p) {
   int64_t n = 1;
@@ -295,9 +381,66 @@ void EmitBody(std::ostringstream& o, const EwProgram& p, const GenConfig& cfg) {
     o << "        { const " << idx_t << " q = rem / " << p.dims[d] << sfx << "; ix[u][" << d << "] = rem - q * " << p.dims[d] << sfx << "; rem = q; }\n";
   }
   o << "        ix[u][0] = rem;\n      }\n";
-  for (int r = 0; r < p.num_regs; ++r) o << "      R r" << r << "[UNR][VEC];\n";
+  if (cfg.packed) {
+    for (int r = 0; r < p.num_regs; ++r) o << "      uint32_t r" << r << "[UNR][VEC / 2];\n";
+  } else {
+    for (int r = 0; r < p.num_regs; ++r) o << "      R r" << r << "[UNR][VEC];\n";
+  }
   for (int pc = 0; pc < p.num_instr; ++pc) {
     const EwInstr& in = p.instr[pc];
+    if (cfg.packed) {
+      const int dt = cfg.packed_dtype;
+      o << "      // " << pc << " (packed)\n";
+      o << "      _Pragma(\"unroll\") for (int u = 0; u < UNR; ++u) {\n        if (!live[u]) continue;\n";
+      if (in.kind == EW_LOAD) {
+        const EwLeaf& lf = p.leaves[in.a];
+        const LeafPlan lp = PlanLeaf(p, lf, cfg.vec);
+        const char* off_t = lp.wide_offset || cfg.wide_index ? "long long" : "int";
+        std::ostringstream off;
+        if (lp.kind == LeafPlan::kDense) {
+          off << "(" << (cfg.wide_index ? "long long" : "unsigned") << ")(vi[u] * VEC)";
+        } else {
+          off << "(";
+          bool any = false;
+          for (int d = 0; d < p.rank; ++d) {
+            if (lf.strides[d] == 0 || p.dims[d] == 1) continue;
+            off << (any ? " + " : "") << "(" << off_t << ")ix[u][" << d << "] * (" << off_t << ")" << lf.strides[d] << "ll";
+            any = true;
+          }
+          if (!any) off << "0";
+          off << ")";
+        }
+        const std::string base = "reinterpret_cast<const uint16_t*>(P.leaf[" + std::to_string(in.a) + "])";
+        if (lp.kind == LeafPlan::kDense || lp.kind == LeafPlan::kVector) {
+          o << "        const unsigned char* src = reinterpret_cast<const unsigned char*>(" << base << " + (long long)" << off.str() << ");\n";
+          EmitVectorLoad(o, "src", cfg.vec * 2, "w");
+          for (int i = 0; i < cfg.vec / 2; ++i) o << "        r" << (int)in.dst << "[u][" << i << "] = w[" << i << "];\n";
+        } else if (lp.kind == LeafPlan::kBroadcast) {
+          o << "        const uint32_t x = " << base << "[(long long)" << off.str() << "];\n";
+          o << "        _Pragma(\"unroll\") for (int i = 0; i < VEC / 2; ++i) r" << (int)in.dst << "[u][i] = x | (x << 16);\n";
+        } else {
+          o << "        const long long off = (long long)" << off.str() << ";\n";
+          o << "        _Pragma(\"unroll\") for (int i = 0; i < VEC / 2; ++i) r" << (int)in.dst << "[u][i] = (uint32_t)" << base << "[off + (2 * i) * "
+            << lp.last_stride << "ll] | ((uint32_t)" << base << "[off + (2 * i + 1) * " << lp.last_stride << "ll] << 16);\n";
+        }
+      } else if (in.kind == EW_IMM) {
+        const uint32_t h = FloatBitsTo16((uint32_t)in.imm, dt);
+        o << "        _Pragma(\"unroll\") for (int i = 0; i < VEC / 2; ++i) r" << (int)in.dst << "[u][i] = 0x" << std::hex << (h | (h << 16)) << std::dec << "u;\n";
+      } else if (in.kind == EW_IOTA) {
+        o << "        _Pragma(\"unroll\") for (int i = 0; i < VEC / 2; ++i) r" << (int)in.dst << "[u][i] = ew_p2_pack((float)((long long)ix[u][" << (int)in.a
+          << "]" << ((int)in.a == last ? " + 2 * i" : "") << "), (float)((long long)ix[u][" << (int)in.a << "]" << ((int)in.a == last ? " + 2 * i + 1" : "")
+          << "), " << dt << ");\n";
+      } else {
+        const int op = in.op;
+        const bool three = op == (int)Op::Clamp;
+        const bool two = three || IsBinOp(op);
+        o << "        _Pragma(\"unroll\") for (int i = 0; i < VEC / 2; ++i) r" << (int)in.dst << "[u][i] = ew_p2_op(" << op << ", " << dt << ", r"
+          << (int)in.a << "[u][i], " << (two ? "r" + std::to_string((int)in.b) + "[u][i]" : std::string("0u")) << ", "
+          << (three ? "r" + std::to_string((int)in.c) + "[u][i]" : std::string("0u")) << ");\n";
+      }
+      o << "      }\n";
+      continue;
+    }
     o << "      // " << pc << "\n";
     o << "      _Pragma(\"unroll\") for (int u = 0; u < UNR; ++u) {\n        if (!live[u]) continue;\n";
     switch (in.kind) {
@@ -355,10 +498,25 @@ void EmitBody(std::ostringstream& o, const EwProgram& p, const GenConfig& cfg) {
         const int op = in.op;
         const bool three = op == (int)Op::Where || op == (int)Op::Clamp;
         const bool two = three || IsBinOp(op) || IsCmpOp(op);
-        o << "        _Pragma(\"unroll\") for (int v = 0; v < VEC; ++v) r" << (int)in.dst << "[u][v] = eval_op_core<R>(" << op << ", " << (int)in.sdtype
-          << ", r" << (int)in.a << "[u][v], ";
-        if (two) o << "r" << (int)in.b << "[u][v], "; else o << "(R)0, ";
-        if (three) o << "r" << (int)in.c << "[u][v]);\n"; else o << "(R)0);\n";
+        // a 16-bit float result is rounded after the op: two elements per packed conversion
+        const bool is16 = in.dtype == B200_BFLOAT16 || in.dtype == B200_FLOAT16;
+        const bool float_result = !IsCmpOp(op) && op != (int)Op::IsFinite && op != (int)Op::IsNaN && op != (int)Op::Where;
+        const bool pair = is16 && float_result && cfg.vec % 2 == 0 && (in.sdtype == B200_BFLOAT16 || in.sdtype == B200_FLOAT16);
+        auto call = [&](const char* fn, const std::string& v) {
+          std::ostringstream c;
+          c << fn << "<R>(" << op << ", " << (int)in.sdtype << ", r" << (int)in.a << "[u][" << v << "], ";
+          if (two) c << "r" << (int)in.b << "[u][" << v << "], "; else c << "(R)0, ";
+          if (three) c << "r" << (int)in.c << "[u][" << v << "])"; else c << "(R)0)";
+          return c.str();
+        };
+        if (pair) {
+          o << "        _Pragma(\"unroll\") for (int v = 0; v < VEC; v += 2) {\n";
+          o << "          float t0 = as_f(" << call("eval_op_unrounded", "v") << "), t1 = as_f(" << call("eval_op_unrounded", "v + 1") << ");\n";
+          o << "          ew_round_pair(" << (int)in.dtype << ", t0, t1);\n";
+          o << "          r" << (int)in.dst << "[u][v] = from_f<R>(t0); r" << (int)in.dst << "[u][v + 1] = from_f<R>(t1);\n        }\n";
+        } else {
+          o << "        _Pragma(\"unroll\") for (int v = 0; v < VEC; ++v) r" << (int)in.dst << "[u][v] = " << call("eval_op_core", "v") << ";\n";
+        }
         break;
       }
     }
@@ -380,8 +538,9 @@ GenConfig ChooseConfig(const EwProgram& p, int sm_count, bool allow_vector) {
   while (vec > 1 && inner % vec != 0) vec /= 2;
   if (!allow_vector) vec = 1;
   cfg.vec = vec;
+  cfg.packed = vec >= 2 && CanPack(p, &cfg.packed_dtype);
   const int64_t nvec = n / vec;
-  cfg.unroll = (vec > 1 && p.num_regs * vec <= 48 && nvec >= (int64_t)sm_count * 256 * 8) ? 2 : 1;
+  cfg.unroll = (vec > 1 && p.num_regs * vec <= (cfg.packed ? 96 : 48) && nvec >= (int64_t)sm_count * 256 * 8) ? 2 : 1;
   return cfg;
 }
 
@@ -411,9 +570,15 @@ std::string ewise_jit_source(const EwProgram& p, int sm_count, bool allow_vector
     const int words = nbytes >= 4 ? nbytes / 4 : 1;
     o << "        uint32_t w[" << words << "];\n";
     for (int wi = 0; wi < words; ++wi) {
+      if (cfg.packed) {
+        o << "        w[" << wi << "] = r" << p.out_reg << "[u][" << wi << "];\n";
+        continue;
+      }
       o << "        w[" << wi << "] = ";
       if (elt == 8) {
         o << "(uint32_t)(ew_to_raw<R>(r" << p.out_reg << "[u][" << wi / 2 << "], " << p.out_dtype << ") >> " << 32 * (wi % 2) << ");\n";
+      } else if (elt == 2 && (p.out_dtype == B200_BFLOAT16 || p.out_dtype == B200_FLOAT16)) {
+        o << "ew_pack_pair<R>(r" << p.out_reg << "[u][" << 2 * wi << "], r" << p.out_reg << "[u][" << 2 * wi + 1 << "], " << p.out_dtype << ");\n";
       } else {
         const int per = 4 / elt;
         for (int e = 0; e < per; ++e)
@@ -579,7 +744,10 @@ ReduceGeom ChooseReduce(const EwProgram& p, int64_t outer, int64_t n, int64_t in
   if (g.rows) {
     const int64_t vecs = n / vec;
     g.tpr = vecs <= 1024 ? 32 : 256;
-    g.unroll = (vecs >= 2 * g.tpr && p.num_regs * vec <= 48) ? 2 : 1;
+    // vectors in flight per thread: a row group waits for its loads before it can fold them, so the loads of one
+    // iteration are all the memory parallelism it has
+    g.unroll = 1;
+    while (g.unroll < 4 && vecs >= 2 * g.unroll * g.tpr && p.num_regs * vec * 2 * g.unroll <= 64) g.unroll *= 2;
   }
   return g;
 }
@@ -589,8 +757,17 @@ std::string ReduceSource(const EwProgram& p, int rt, const ReduceGeom& g, int ou
   cfg.vec = g.vec;
   cfg.unroll = g.unroll;
   cfg.wide_index = NumElements(p) > 0xffffffffLL;
+  cfg.packed = g.vec >= 2 && CanPack(p, &cfg.packed_dtype);
   const char* idx_t = cfg.wide_index ? "uint64_t" : "uint32_t";
   const char* acc_t = AccType(out_dtype);
+  // the value of element v of vector u as an accumulator
+  auto elem_acc = [&](const std::string& v_even_odd_index) {
+    std::ostringstream e;
+    if (cfg.packed) e << "(A)(((" << v_even_odd_index << ") & 1) ? ew_p2_hi(r" << p.out_reg << "[u][(" << v_even_odd_index << ") >> 1], " << out_dtype
+                      << ") : ew_p2_lo(r" << p.out_reg << "[u][(" << v_even_odd_index << ") >> 1], " << out_dtype << "))";
+    else e << "RdAcc<A>::in(r" << p.out_reg << "[u][" << v_even_odd_index << "], " << out_dtype << ")";
+    return e.str();
+  };
   std::ostringstream o;
   o << Preamble() << kOpsSource << kGlue;
   o << "typedef " << (p.wide ? "uint64_t" : "uint32_t") << " R;\ntypedef " << acc_t << " A;\n";
@@ -610,8 +787,7 @@ std::string ReduceSource(const EwProgram& p, int rt, const ReduceGeom& g, int ou
     o << "      _Pragma(\"unroll\") for (int u = 0; u < UNR; ++u) { live[u] = v0 + u * TPR < vecs; vi[u] = row * vecs + v0 + u * TPR; }\n";
     EmitBody(o, p, cfg);
     o << "      _Pragma(\"unroll\") for (int u = 0; u < UNR; ++u) {\n        if (!live[u]) continue;\n";
-    o << "        _Pragma(\"unroll\") for (int v = 0; v < VEC; ++v) acc = rd_combine<A>(RT, acc, RdAcc<A>::in(r" << p.out_reg << "[u][v], " << out_dtype
-      << "));\n      }\n    }\n";
+    o << "        _Pragma(\"unroll\") for (int v = 0; v < VEC; ++v) acc = rd_combine<A>(RT, acc, " << elem_acc("v") << ");\n      }\n    }\n";
     o << "    acc = rd_warp<A>(RT, acc);\n";
     if (g.tpr == 256) {
       // one row per CTA and iteration: every thread takes part in both barriers
@@ -634,8 +810,7 @@ std::string ReduceSource(const EwProgram& p, int rt, const ReduceGeom& g, int ou
     o << "      _Pragma(\"unroll\") for (int u = 0; u < UNR; ++u) { live[u] = j + u < n; vi[u] = (ob * n + j + u) * ivecs + iv; }\n";
     EmitBody(o, p, cfg);
     o << "      _Pragma(\"unroll\") for (int u = 0; u < UNR; ++u) {\n        if (!live[u]) continue;\n";
-    o << "        _Pragma(\"unroll\") for (int v = 0; v < VEC; ++v) acc[v] = rd_combine<A>(RT, acc[v], RdAcc<A>::in(r" << p.out_reg << "[u][v], "
-      << out_dtype << "));\n      }\n    }\n";
+    o << "        _Pragma(\"unroll\") for (int v = 0; v < VEC; ++v) acc[v] = rd_combine<A>(RT, acc[v], " << elem_acc("v") << ");\n      }\n    }\n";
     o << "    _Pragma(\"unroll\") for (int v = 0; v < VEC; ++v) store_elem<R>(P.out, (long long)(c * VEC + v), " << out_dtype
       << ", RdAcc<A>::out<R>(acc[v], " << out_dtype << "));\n";
     o << "  }\n}\n";
@@ -757,7 +932,9 @@ Status ewise_jit_run(Device* dev, EwJit* jit, const EwProgram& prog) {
   ptrs.out = prog.out;
   const int64_t per_block = 256 * (int64_t)use->unroll;
   int64_t blocks = use->is_reduce ? use->grid_units : (use->nvec + per_block - 1) / per_block;
-  const int64_t cap = (int64_t)dev->sm_count() * 8;
+  // elementwise kernels run a persistent grid; row reductions get one CTA per 256 / TPR rows (short CTAs that the
+  // hardware deals out as SMs free up balance better than a static stride when there are only a few rows per row group)
+  const int64_t cap = use->is_reduce ? 0x7fffffffLL : (int64_t)dev->sm_count() * 8;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   void* args[] = {&ptrs};

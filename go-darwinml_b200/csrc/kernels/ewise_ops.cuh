@@ -128,6 +128,41 @@ template <typename F> __device__ __forceinline__ F f_unary(int op, F x) {
     default: return x;
   }
 }
+// Unary float ops whose result is rounded to a 16-bit float (8 or 11 significant bits): the hardware approximations
+// (tanh.approx, ex2.approx, rsqrt.approx: relative error about 2^-11 .. 2^-22) are then below the rounding step, and a
+// chain over 16-bit data is bound by instruction issue, not by memory (8 elements per 16-byte vector).  Ops without a
+// cheap form fall through to the exact one.
+__device__ __forceinline__ float ew_tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float f_unary_to16(int op, float x) {
+  switch ((Op)op) {
+    case Op::Tanh: return ew_tanh_approx(x);
+    case Op::Exp: return __expf(x);
+    case Op::Sigmoid: return __fdividef(1.0f, 1.0f + __expf(-x));
+    case Op::Silu: return __fdividef(x, 1.0f + __expf(-x));
+    case Op::Rsqrt: return rsqrtf(x);
+    case Op::GeluTanh: {
+      const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+      return 0.5f * x * (1.0f + ew_tanh_approx(u));
+    }
+    default: return f_unary<float>(op, x);
+  }
+}
+// max / min that return NaN when either operand is NaN (one instruction)
+__device__ __forceinline__ float ew_max_nan(float a, float b) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ float ew_min_nan(float a, float b) {
+  float r;
+  asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+
 template <typename F> __device__ __forceinline__ F f_binary(int op, F a, F b) {
   switch ((Op)op) {
     case Op::Add: return a + b;
@@ -209,7 +244,7 @@ __device__ __forceinline__ bool is_bin_op(int op) { return op >= (int)Op::Add &&
 
 // Narrow value of `dtype` held in r -> signed 32-bit view / float view are both r itself.
 template <typename R>
-__device__ __forceinline__ R eval_op_core(const int op, const int sd, R a, R b, R c) {
+__device__ __forceinline__ R eval_op_impl(const int op, const int sd, R a, R b, R c, const bool round16) {
   if (op == (int)Op::Where) return a ? b : c;  // a is a Bool register
   if (op == (int)Op::IsFinite || op == (int)Op::IsNaN) {
     if (sd == B200_FLOAT64) {
@@ -231,9 +266,12 @@ __device__ __forceinline__ R eval_op_core(const int op, const int sd, R a, R b, 
       if (is_cmp_op(op)) return (R)cmp<float>(op, x, y);
       float r;
       if (op == (int)Op::Clamp) r = fminf(fmaxf(y, x), z);  // (min=a, x=b, max=c)
+      else if (op == (int)Op::Max) r = ew_max_nan(x, y);
+      else if (op == (int)Op::Min) r = ew_min_nan(x, y);
       else if (is_bin_op(op)) r = f_binary<float>(op, x, y);
+      else if (sd != B200_FLOAT32) r = f_unary_to16(op, x);
       else r = f_unary<float>(op, x);
-      return from_f<R>(round_to(sd, r));
+      return from_f<R>(round16 ? round_to(sd, r) : r);
     }
     case B200_FLOAT64:
       if constexpr (RegTraits<R>::wide) {
@@ -290,6 +328,27 @@ __device__ __forceinline__ R eval_op_core(const int op, const int sd, R a, R b, 
       } else r = is_bin_op(op) ? i_binary<uint32_t>(op, x, y) : i_unary<uint32_t>(op, x);
       return (R)wrap_i32(sd, r);
     }
+  }
+}
+
+template <typename R>
+__device__ __forceinline__ R eval_op_core(const int op, const int sd, R a, R b, R c) { return eval_op_impl<R>(op, sd, a, b, c, true); }
+// The same without the final rounding of a 16-bit float result: the caller rounds two results at once (ew_round_pair).
+template <typename R>
+__device__ __forceinline__ R eval_op_unrounded(const int op, const int sd, R a, R b, R c) { return eval_op_impl<R>(op, sd, a, b, c, false); }
+// Rounds two fp32 values to the 16-bit float type dt (round to nearest even, as round_to does) with ONE packed
+// conversion.  The scalar conversion instruction is issued at a quarter of the arithmetic rate; a chain over 16-bit
+// data rounds after every op and was bound by exactly that.
+__device__ __forceinline__ void ew_round_pair(int dt, float& a, float& b) {
+  uint32_t p;
+  if (dt == B200_BFLOAT16) {
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(p) : "f"(b), "f"(a));   // upper half <- b, lower half <- a
+    a = __uint_as_float(p << 16);
+    b = __uint_as_float(p & 0xffff0000u);
+  } else {
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(p) : "f"(b), "f"(a));
+    a = ew_f16_to_f((uint16_t)(p & 0xffffu));
+    b = ew_f16_to_f((uint16_t)(p >> 16));
   }
 }
 

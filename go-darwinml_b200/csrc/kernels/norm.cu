@@ -73,8 +73,12 @@ __device__ __forceinline__ void group_sum_n(float (&v)[NV], float* slots, int ba
   }
 }
 
+// CTAs per SM the kernel is compiled for: short rows (few vectors per thread) need few registers, and more resident
+// rows are what hides the memory latency when a row is only a kilobyte or two.
+template <int ITERS, int TPR> struct NormOcc { static constexpr int kCtas = TPR > 256 ? 1 : (ITERS <= 2 ? 4 : (ITERS == 3 ? 3 : 2)); };
+
 template <typename T, int ITERS, int TPR, bool RMS, bool HAS_G, bool HAS_B>
-__global__ void __launch_bounds__(TPR > 256 ? TPR : 256, TPR > 512 ? 1 : (TPR > 256 ? 1 : 2)) norm_rows_kernel(const NArgs a) {
+__global__ void __launch_bounds__(TPR > 256 ? TPR : 256, NormOcc<ITERS, TPR>::kCtas) norm_rows_kernel(const NArgs a) {
   constexpr int V = Cvt<T>::N;
   constexpr int BLOCK = TPR > 256 ? TPR : 256;
   constexpr int GROUPS = BLOCK / TPR;
@@ -239,12 +243,15 @@ void launch_tpr(Device* dev, const NArgs& a, int iters, cudaStream_t s) {
   constexpr int GROUPS = BLOCK / TPR;
   const int64_t ctas_needed = (a.rows + GROUPS - 1) / GROUPS;
   // persistent: a few CTAs per SM, never more than there are row slots
-  int64_t grid = (int64_t)dev->sm_count() * (BLOCK >= 1024 ? 1 : 2);
-  if (grid > ctas_needed) grid = ctas_needed;
+  auto grid_for = [&](int ctas_per_sm) {
+    int64_t grid = (int64_t)dev->sm_count() * ctas_per_sm;
+    return (unsigned)(grid > ctas_needed ? ctas_needed : grid);
+  };
   switch (iters) {
-    case 1: launch_params<T, 1, TPR, RMS>(a, (unsigned)grid, s); break;
-    case 2: launch_params<T, 2, TPR, RMS>(a, (unsigned)grid, s); break;
-    default: launch_params<T, 4, TPR, RMS>(a, (unsigned)grid, s); break;
+    case 1: launch_params<T, 1, TPR, RMS>(a, grid_for(NormOcc<1, TPR>::kCtas), s); break;
+    case 2: launch_params<T, 2, TPR, RMS>(a, grid_for(NormOcc<2, TPR>::kCtas), s); break;
+    case 3: launch_params<T, 3, TPR, RMS>(a, grid_for(NormOcc<3, TPR>::kCtas), s); break;
+    default: launch_params<T, 4, TPR, RMS>(a, grid_for(NormOcc<4, TPR>::kCtas), s); break;
   }
 }
 
@@ -262,8 +269,7 @@ void launch_typed(Device* dev, const NArgs& a, cudaStream_t s) {
   const int64_t vecs = a.cols / V;
   int tpr = 32;
   while ((int64_t)tpr * MAX_ITERS < vecs) tpr *= 2;
-  int iters = 1;
-  while ((int64_t)iters * tpr < vecs) iters *= 2;
+  const int iters = (int)((vecs + tpr - 1) / tpr);   // 1 .. MAX_ITERS vectors per thread
   switch (tpr) {
     case 32: launch_tpr<T, 32, RMS>(dev, a, iters, s); break;
     case 64: launch_tpr<T, 64, RMS>(dev, a, iters, s); break;

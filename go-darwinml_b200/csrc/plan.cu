@@ -300,6 +300,8 @@ class Planner {
       case Op::Reduce: return EmitReduce(x);
       case Op::ArgMinMax: return EmitArgMinMax(x);
       case Op::Gather: return EmitGather(x);
+      case Op::Scatter: return EmitScatter(x);
+      case Op::RngBits: return EmitRngBits(x);
       case Op::Softmax: return EmitSoftmax(x);
       case Op::SoftmaxMasked: return EmitSoftmaxMasked(x);
       case Op::LayerNorm: case Op::RmsNorm: return EmitNorm(x);
@@ -681,8 +683,10 @@ class Planner {
         q.leaves[l].ptr = (const char*)p[leaf_slots[l]] + leaf_offsets[l] * dtype_size(q.leaves[l].dtype);
       q.out = p[out_slot];
       if (!jit) return k::ewise_run(dev, q);
+      // x op y keeps its templated kernel (0.92 - 0.97 of the copy rate); everything else, the small trees included, runs
+      // the compiled chain, which rounds 16-bit results two at a time
       bool taken = false;
-      B200_TRY(k::ewise_run_fast(dev, q, &taken));
+      B200_TRY(k::ewise_run_fast(dev, q, &taken, /*trees=*/false));
       if (taken) return Status::OK();
       return k::ewise_jit_run(dev, jit, q);
     };
@@ -1313,6 +1317,83 @@ class Planner {
       q.y = p[out_slot];
       return k::gather_general(dev, q);
     };
+    ex_->steps.push_back(std::move(st));
+    return Status::OK();
+  }
+
+  // ------------------------------------------------- scatter, random bits ---
+  Status EmitScatter(Node* x) {
+    Node* op = x->in[0];
+    Node* idx = x->in[1];
+    Node* upd = x->in[2];
+    B200_TRY(EnsureMaterialized(op));
+    B200_TRY(EnsureMaterialized(idx));
+    B200_TRY(EnsureMaterialized(upd));
+    size_t pos = 0;
+    const int mode = (int)x->ia[pos++], iva = (int)x->ia[pos++];
+    pos++;  // unique_indices: the atomics are correct either way
+    auto take = [&]() { const int n = (int)x->ia[pos++]; std::vector<int64_t> v(x->ia.begin() + pos, x->ia.begin() + pos + n); pos += n; return v; };
+    const std::vector<int64_t> uw = take(), iw = take(), map = take();
+    const int orank = op->rank(), irank = idx->rank(), urank = upd->rank();
+    const int op_slot = SlotOf(op), idx_slot = SlotOf(idx), upd_slot = SlotOf(upd), out_slot = NewValueSlot(x);
+    k::ScatterParams sp;
+    sp.dtype = op->dtype;
+    sp.ids_dtype = idx->dtype;
+    sp.mode = mode;
+    sp.operand_rank = orank;
+    sp.update_rank = urank;
+    const std::vector<int64_t> ostr = dense_strides(op->dims), istr = dense_strides(idx->dims);
+    for (int d = 0; d < orank; ++d) { sp.operand_dims[d] = op->dims[d]; sp.operand_strides[d] = ostr[d]; }
+    for (int d = 0; d < urank; ++d) sp.update_dims[d] = upd->dims[d];
+    int nb = 0;
+    for (int d = 0; d < urank; ++d)
+      if (!std::count(uw.begin(), uw.end(), (int64_t)d)) sp.batch_update_axis[nb++] = d;
+    sp.num_batch_dims = nb;
+    int bi = 0;
+    for (int d = 0; d < irank; ++d)
+      if (d != iva) sp.batch_index_strides[bi++] = istr[d];
+    sp.index_vector_stride = iva < irank ? istr[iva] : 0;
+    sp.num_index_components = (int)map.size();
+    for (size_t i = 0; i < map.size(); ++i) sp.scatter_axes_to_operand_axes[i] = (int)map[i];
+    int nw = 0;
+    for (int d = 0; d < orank; ++d)
+      if (!std::count(iw.begin(), iw.end(), (int64_t)d)) {
+        sp.window_operand_axis[nw] = d;
+        sp.window_update_axis[nw] = (int)uw[nw];
+        ++nw;
+      }
+    sp.num_window_axes = nw;
+    const int64_t nbytes = x->num_elements() * dtype_size(x->dtype);
+    Step st;
+    st.desc = strfmt("scatter[mode=%d operand=%lld updates=%lld %s]", mode, (long long)op->num_elements(), (long long)upd->num_elements(),
+                     dtype_name(op->dtype));
+    st.reads = {op_slot, idx_slot, upd_slot};
+    st.writes = {out_slot};
+    st.launches = 1;
+    st.run = [sp, op_slot, idx_slot, upd_slot, out_slot, nbytes](Device* dev, void* const* p) -> Status {
+      if (nbytes > 0 && p[out_slot] != p[op_slot])
+        B200_CUDA_TRY(cudaMemcpyAsync(p[out_slot], p[op_slot], (size_t)nbytes, cudaMemcpyDeviceToDevice, dev->stream()));
+      k::ScatterParams q = sp;
+      q.y = p[out_slot];
+      q.indices = p[idx_slot];
+      q.updates = p[upd_slot];
+      return k::scatter(dev, q);
+    };
+    ex_->steps.push_back(std::move(st));
+    return Status::OK();
+  }
+
+  Status EmitRngBits(Node* x) {
+    Node* state = x->in[0];
+    B200_TRY(EnsureMaterialized(state));
+    const int st_slot = SlotOf(state), out_slot = NewValueSlot(x);
+    const int dt = x->dtype;
+    const int64_t n = x->num_elements();
+    Step st;
+    st.desc = strfmt("rng_bits[n=%lld %s]", (long long)n, dtype_name(dt));
+    st.reads = {st_slot};
+    st.writes = {out_slot};
+    st.run = [=](Device* dev, void* const* p) -> Status { return k::rng_bits(dev, p[st_slot], p[out_slot], dt, n); };
     ex_->steps.push_back(std::move(st));
     return Status::OK();
   }

@@ -10,8 +10,9 @@
   python go-darwinml_b200/kernel_bench.py fill --rows 524288 --cols 1024 --dtype f32    # yardstick: write-only stream
 
 Inputs are seeded random tensors resident in HBM; timing is CUDA events on the
-library's stream after warm-up; between timed launches an L2-sized buffer is
-rewritten unless the operands exceed L2 anyway.  Prints one JSON line with the
+library's stream after warm-up; between timed launches a buffer twice the size
+of L2 is READ unless the operands exceed L2 anyway (a flush that writes would
+leave L2 full of dirty lines, whose write-back the timed kernel then pays for).  Prints one JSON line with the
 mean launch time, the achieved GB/s (algorithmic bytes) or TFLOP/s, and the
 fraction of the measured peak when MEASURED_PEAKS.json is present.  Small shapes
 of this tool are what the ncu captures under profiles/ were taken on.
@@ -230,7 +231,8 @@ def main():
     torch.cuda.synchronize()
     flush = None
     if not args.no_flush and operand_bytes < 512 << 20:
-        flush = torch.empty(256 << 20, dtype=torch.uint8, device=f"cuda:{args.device}")
+        flush = torch.zeros(256 << 20, dtype=torch.uint8, device=f"cuda:{args.device}")
+        flush_sink = torch.zeros((), dtype=torch.int64, device=f"cuda:{args.device}")
     for _ in range(args.warmup):
         launch()
     backend.Synchronize(args.device)
@@ -238,7 +240,7 @@ def main():
     for _ in range(args.iters):
         if flush is not None:
             with torch.cuda.stream(stream):
-                flush.fill_(1)
+                flush_sink.copy_(flush.view(torch.int64).sum(), non_blocking=True)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         launch()

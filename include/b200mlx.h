@@ -262,6 +262,31 @@ B200Value b200_batch_norm_inference(B200Context ctx, B200Value input, B200Value 
                                     B200Value gamma, B200Value beta, float epsilon, int feature_axis,
                                     B200Error* err);
 
+/* ---- training-side ops ---------------------------------------------------- */
+/* BatchNormForTraining (ref function.go:1263-1375): batch mean and biased variance over every axis but feature_axis,
+ * normalised * scale + offset; out_mean / out_variance are [feature] vectors.  false + *err on failure. */
+bool b200_batch_norm_training(B200Context ctx, B200Value operand, B200Value scale, B200Value offset, float epsilon,
+                              int feature_axis, B200Value* out_normalized, B200Value* out_mean, B200Value* out_variance,
+                              B200Error* err);
+/* BatchNormGradient (ref function.go:1377-1527): gradients w.r.t. operand, scale and offset. */
+bool b200_batch_norm_gradient(B200Context ctx, B200Value operand, B200Value scale, B200Value mean, B200Value variance,
+                              B200Value grad_output, float epsilon, int feature_axis, B200Value* out_grad_operand,
+                              B200Value* out_grad_scale, B200Value* out_grad_offset, B200Error* err);
+/* ScatterSum / ScatterMax / ScatterMin (ref gather.go:441-641; bridge.h:153-155, 233-235), the signature of
+ * backends.Function.ScatterSum with the combiner as `mode`: 0 sum, 1 max, 2 min.  Elements whose position falls
+ * outside the operand are dropped. */
+B200Value b200_scatter(B200Context ctx, int mode, B200Value operand, B200Value scatter_indices, B200Value updates,
+                       int index_vector_axis, const int* update_window_axes, int num_update_window_axes,
+                       const int* inserted_window_axes, int num_inserted_window_axes,
+                       const int* scatter_axes_to_operand_axes, int num_scatter_axes, bool indices_are_sorted,
+                       bool unique_indices, B200Error* err);
+/* RNGBitGenerator (ref function.go:1627-1692): state is (Uint64)[3]; *out_new_state is the state with every word + 1
+ * (as the reference advances it), *out_values are `dtype`[shape] values that are a pure function of the state
+ * (Philox4x32-10; the reference's values come from Apple's generator and are not reproducible): raw bits for integer
+ * dtypes, uniform [0, 1) for float dtypes. */
+bool b200_rng_bit_generator(B200Context ctx, B200Value state, int dtype, const int64_t* shape, int rank,
+                            B200Value* out_new_state, B200Value* out_values, B200Error* err);
+
 /* ---- compile (ref bridge.h:159-163; builder.go:72-109) ------------------ */
 /* feeds are placeholders in Parameter order, targets in Return order. */
 B200Exec b200_compile(B200Context ctx, const B200Value* feeds, int num_feeds, const B200Value* targets,

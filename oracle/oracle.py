@@ -532,6 +532,136 @@ class OracleFunction:
             out = np.ascontiguousarray(np.transpose(out, (0, 2, 1, 3)))
         return out
 
+    # ---- training-side ops ------------------------------------------------------
+    def BatchNormForInference(self, operand, scale, offset, mean, variance, epsilon, feature_axis):
+        # (x - mean) * rsqrt(var + eps) * scale + offset along the feature axis (ref function.go:1248-1261)
+        ax = feature_axis + operand.ndim if feature_axis < 0 else feature_axis
+        view = [1] * operand.ndim
+        view[ax] = operand.shape[ax]
+        lay = lambda p: _f64(p).reshape(view)
+        y = (_f64(operand) - lay(mean)) / np.sqrt(lay(variance) + float(np.float32(epsilon))) * lay(scale) + lay(offset)
+        return _round(y, operand.dtype)
+
+    def BatchNormForTraining(self, operand, scale, offset, epsilon, feature_axis):
+        # batch mean, biased variance of the centred value, normalise, scale, offset (ref function.go:1263-1375)
+        ax = feature_axis + operand.ndim if feature_axis < 0 else feature_axis
+        batch = tuple(i for i in range(operand.ndim) if i != ax)
+        view = [1] * operand.ndim
+        view[ax] = operand.shape[ax]
+        v = _f64(operand)
+        mean = v.mean(axis=batch, keepdims=True) if batch else v
+        d = v - mean
+        var = (d * d).mean(axis=batch, keepdims=True) if batch else d * d
+        y = d / np.sqrt(var + float(np.float32(epsilon))) * _f64(scale).reshape(view) + _f64(offset).reshape(view)
+        return _round(y, operand.dtype), _round(mean.reshape(-1), operand.dtype), _round(var.reshape(-1), operand.dtype)
+
+    def BatchNormGradient(self, operand, scale, mean, variance, grad_output, epsilon, feature_axis):
+        # ref function.go:1377-1527
+        ax = feature_axis + operand.ndim if feature_axis < 0 else feature_axis
+        batch = tuple(i for i in range(operand.ndim) if i != ax)
+        view = [1] * operand.ndim
+        view[ax] = operand.shape[ax]
+        n = 1
+        for i in batch:
+            n *= operand.shape[i]
+        lay = lambda p: _f64(p).reshape(view)
+        inv = 1.0 / np.sqrt(lay(variance) + float(np.float32(epsilon)))
+        xhat = (_f64(operand) - lay(mean)) * inv
+        dy = _f64(grad_output)
+        g_off = dy.sum(axis=batch, keepdims=True) if batch else dy
+        g_sc = (dy * xhat).sum(axis=batch, keepdims=True) if batch else dy * xhat
+        g_op = (1.0 / n) * lay(scale) * inv * (n * dy - g_off - xhat * g_sc)
+        return _round(g_op, operand.dtype), _round(g_sc.reshape(-1), operand.dtype), _round(g_off.reshape(-1), operand.dtype)
+
+    def _scatter(self, mode, operand, scatter_indices, updates, index_vector_axis, update_window_axes, inserted_window_axes,
+                 scatter_axes_to_operand_axes):
+        # XLA scatter with a combiner (ref gather.go:441-641); elements that land outside the operand are dropped (unpinned)
+        idx = np.asarray(scatter_indices).astype(np.int64)
+        if index_vector_axis == idx.ndim:
+            idx = idx[..., None]
+        idx = np.moveaxis(idx, index_vector_axis, -1)                 # [batch..., components]
+        upd = np.asarray(updates)
+        uw = list(update_window_axes)
+        scatter_axes = [d for d in range(upd.ndim) if d not in uw]
+        window_operand_axes = [d for d in range(operand.ndim) if d not in list(inserted_window_axes)]
+        grids = np.meshgrid(*[np.arange(n) for n in upd.shape], indexing="ij") if upd.ndim else []
+        coord = [np.zeros(upd.shape, dtype=np.int64) for _ in range(operand.ndim)]
+        batch_index = tuple(grids[d] for d in scatter_axes)
+        for c, ax in enumerate(scatter_axes_to_operand_axes):
+            coord[ax] = coord[ax] + (idx[batch_index + (c,)] if batch_index else idx[c])
+        for j, ax in enumerate(window_operand_axes):
+            coord[ax] = coord[ax] + grids[uw[j]]
+        inside = np.ones(upd.shape, dtype=bool)
+        for d in range(operand.ndim):
+            inside &= (coord[d] >= 0) & (coord[d] < operand.shape[d])
+        flat = np.zeros(upd.shape, dtype=np.int64)
+        for d in range(operand.ndim):
+            flat = flat * operand.shape[d] + np.where(inside, coord[d], 0)
+        isf = is_float(operand.dtype)
+        out = (_f64(operand) if isf else np.asarray(operand).astype(np.int64 if np.dtype(operand.dtype).kind == "i" else np.uint64)).reshape(-1).copy()
+        vals = (_f64(upd) if isf else upd.astype(out.dtype))[inside]
+        dst = flat[inside]
+        if mode == 0:
+            np.add.at(out, dst, vals)
+        elif mode == 1:
+            np.maximum.at(out, dst, vals)    # NaN-propagating, like the kernels
+        else:
+            np.minimum.at(out, dst, vals)
+        out = out.reshape(operand.shape)
+        return _round(out, operand.dtype) if isf else out.astype(operand.dtype)
+
+    def ScatterSum(self, operand, scatter_indices, updates, index_vector_axis, update_window_axes, inserted_window_axes,
+                   scatter_axes_to_operand_axes, indices_are_sorted=False, unique_indices=False):
+        return self._scatter(0, operand, scatter_indices, updates, index_vector_axis, update_window_axes, inserted_window_axes, scatter_axes_to_operand_axes)
+
+    def ScatterMax(self, operand, scatter_indices, updates, index_vector_axis, update_window_axes, inserted_window_axes,
+                   scatter_axes_to_operand_axes, indices_are_sorted=False, unique_indices=False):
+        return self._scatter(1, operand, scatter_indices, updates, index_vector_axis, update_window_axes, inserted_window_axes, scatter_axes_to_operand_axes)
+
+    def ScatterMin(self, operand, scatter_indices, updates, index_vector_axis, update_window_axes, inserted_window_axes,
+                   scatter_axes_to_operand_axes, indices_are_sorted=False, unique_indices=False):
+        return self._scatter(2, operand, scatter_indices, updates, index_vector_axis, update_window_axes, inserted_window_axes, scatter_axes_to_operand_axes)
+
+    def RNGBitGenerator(self, state, shape):
+        # unpinned: the reference takes its values from Apple's generator (ref function.go:1627-1692) and only adds 1 to every
+        # state word.  Defined here as Philox4x32-10 (Salmon et al., SC'11): key = state[0], counter = (state[2] : state[1]) +
+        # block number, four 32-bit words per block; integers take the raw bits, floats a uniform [0, 1) from the top bits.
+        st = np.asarray(state, dtype=np.uint64)
+        dt = np.dtype(_dtype_of(shape))
+        dims = _dims_of(shape)
+        n = int(np.prod(dims)) if len(dims) else 1
+        wide = dt.itemsize == 8
+        per = 2 if wide else 4
+        blocks = (n + per - 1) // per
+        b = np.arange(blocks, dtype=np.uint64)
+        with np.errstate(over="ignore"):
+            c_lo = st[1] + b
+            c_hi = st[2] + (c_lo < st[1]).astype(np.uint64)
+        M32 = np.uint64(0xffffffff)
+        c0, c1, c2, c3 = c_lo & M32, c_lo >> np.uint64(32), c_hi & M32, c_hi >> np.uint64(32)
+        k0, k1 = np.uint64(int(st[0]) & 0xffffffff), np.uint64(int(st[0]) >> 32)
+        for _ in range(10):
+            p0, p1 = np.uint64(0xD2511F53) * c0, np.uint64(0xCD9E8D57) * c2   # 32 x 32 -> 64 bits, exact in uint64
+            c0, c1, c2, c3 = (p1 >> np.uint64(32)) ^ c1 ^ k0, p1 & M32, (p0 >> np.uint64(32)) ^ c3 ^ k1, p0 & M32
+            k0, k1 = (k0 + np.uint64(0x9E3779B9)) & M32, (k1 + np.uint64(0xBB67AE85)) & M32
+        words = np.stack([c0, c1, c2, c3], axis=1).reshape(-1)
+        if wide:
+            v = (words[0::2] | (words[1::2] << np.uint64(32)))[:n]
+            vals = (v >> np.uint64(11)).astype(np.float64) * 2.0 ** -53 if dt == np.float64 else v.astype(dt)
+        else:
+            w = words[:n]
+            if dt == np.float32:
+                vals = ((w >> np.uint64(8)).astype(np.float64) * 2.0 ** -24).astype(np.float32)
+            elif dt == np.float16:
+                vals = ((w >> np.uint64(21)).astype(np.float64) * 2.0 ** -11).astype(np.float16)
+            elif is_float(dt):   # bfloat16
+                vals = ((w >> np.uint64(24)).astype(np.float64) * 2.0 ** -8).astype(np.float32).astype(dt)
+            else:
+                vals = (w & np.uint64((1 << (8 * dt.itemsize)) - 1)).astype(dt)
+        with np.errstate(over="ignore"):
+            new_state = st + np.uint64(1)
+        return new_state, vals.reshape(dims)
+
 
 def compare(got: np.ndarray, want: np.ndarray, rtol: float, atol_scale: float = 0.0):
     """Returns (ok, max_violation).  Float rule: |got-want| <= rtol*|want| + atol, atol = atol_scale * rtol * rms(want)

@@ -221,6 +221,19 @@ CASES = [
                           f.ConvertDType(b, C_BF16), [0], None),
              C_F32),
          _a([19, 22, 43, 50], shape=(2, 2)), tol=1.0),
+    # training-side ops
+    Case("ScatterSum embedding gradient", "mpsgraph/gomlx/mpsgraph_test.go:1192-1262",
+         [_a([0] * 8, shape=(4, 2)), _a([0, 2, 0], I32, (3, 1)), _a([1, 2, 3, 4, 5, 6], shape=(3, 2))],
+         lambda f, operand, indices, updates: f.ScatterSum(operand, indices, updates, 1, [1], [0], [0], False, False),
+         _a([6, 8, 0, 0, 3, 4, 0, 0], shape=(4, 2)), tol=1e-5),
+    Case("BatchNormForTraining basic (mean, variance)", "mpsgraph/gomlx/mpsgraph_test.go:3064-3101",
+         [_a([1, 2, 3, 4, 5, 6, 7, 8], shape=(4, 2)), _a([1, 1]), _a([0, 0])],
+         lambda f, op, sc, off: list(f.BatchNormForTraining(op, sc, off, 1e-5, 1)[1:]),
+         [_a([4, 5]), _a([5, 5])], tol=1e-3),
+    Case("BatchNormForTraining scale and offset", "mpsgraph/gomlx/mpsgraph_test.go:3103-3124",
+         [_a([0, 10, 0, 10], shape=(2, 2)), _a([2, 3]), _a([1, -1])],
+         lambda f, op, sc, off: list(f.BatchNormForTraining(op, sc, off, 1e-5, 1)[:2]),
+         [_a([1, -1, 1, -1], shape=(2, 2)), _a([0, 10])], tol=1e-3),
 ]
 
 # Shape-only expectations of the reference's tests (the test asserts a shape or finiteness, not values).

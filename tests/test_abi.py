@@ -71,3 +71,53 @@ def test_capabilities_lists_the_hot_path_ops(b200):
                "FusedAttentionQKVProjection", "Iota", "Gather", "ArgMinMax", "ReduceSum", "Where", "ConvertDType"):
         assert caps.Operations.get(op), op
     assert caps.DTypes[int(b200.dtypes.BFloat16)] and caps.DTypes[int(b200.dtypes.Float32)]
+
+
+def test_go_bridge_names_only_declared_entry_points():
+    """The Go plugin layer (go/b200) cannot be compiled where this library is built, so at least every C function its
+    cgo bridge calls must be one include/b200mlx.h declares, with the argument count the header gives it."""
+    import re
+
+    from go_darwinml_b200 import _lib
+    decls = _lib.parse_header()
+    text = open(os.path.join(ROOT, "go", "b200", "internal", "bridge", "bridge.go")).read()
+    preamble, body = text.split('import "C"', 1)
+    called = set(re.findall(r"\bC\.(b200_\w+)\(", body)) | set(re.findall(r"\b(b200_\w+)\b", preamble.split("b200go_unary_fn", 1)[1]))
+    called = {c for c in called if not c.startswith("b200go_")}
+    assert called, "no C calls found"
+    missing = sorted(c for c in called if c not in decls)
+    assert not missing, f"bridge.go calls functions the header does not declare: {missing}"
+    # argument counts of the direct calls (balanced-parenthesis scan of each call site)
+    for m in re.finditer(r"\bC\.(b200_\w+)\(", body):
+        name, i, depth, args, cur = m.group(1), m.end(), 1, 0, False
+        while depth:
+            ch = body[i]
+            if ch == "(":
+                depth += 1
+            elif ch == ")":
+                depth -= 1
+            elif ch == "," and depth == 1:
+                args += 1
+            if not ch.isspace() and depth:
+                cur = True
+            i += 1
+        nargs = args + 1 if cur else 0
+        assert nargs == len(decls[name][1]), f"{name}: bridge.go passes {nargs} arguments, the header declares {len(decls[name][1])}"
+
+
+def test_go_bridge_preamble_is_valid_c():
+    """The C block of the cgo bridge (dispatch tables over the unary / binary entry points) compiles against the header."""
+    text = open(os.path.join(ROOT, "go", "b200", "internal", "bridge", "bridge.go")).read()
+    start = text.index("/*\n#cgo") + 3
+    block = text[start:text.index("*/\nimport \"C\"")]
+    src = "\n".join(l for l in block.splitlines() if not l.startswith("#cgo")) + "\nint main(void){(void)b200go_unary; (void)b200go_binary; return 0;}\n"
+    r = subprocess.run(["gcc", "-std=c11", "-Wall", "-Werror", "-fsyntax-only", "-I", os.path.join(ROOT, "include"), "-x", "c", "-"],
+                       input=src, text=True, capture_output=True)
+    assert r.returncode == 0, r.stderr
+    # the op codes on the Go side index those tables: same lengths
+    import re
+    unary = re.search(r"b200go_unary_table\[\] = \{(.*?)\};", block, re.S).group(1).split(",")
+    binary = re.search(r"b200go_binary_table\[\] = \{(.*?)\};", block, re.S).group(1).split(",")
+    go_unary = re.search(r"const \(\n\tOpAbs = iota\n(.*?)\n\)", text, re.S).group(1).split()
+    go_binary = re.search(r"const \(\n\tOpAdd = iota\n(.*?)\n\)", text, re.S).group(1).split()
+    assert len(unary) == len(go_unary) + 1 and len(binary) == len(go_binary) + 1

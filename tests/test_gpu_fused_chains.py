@@ -236,7 +236,9 @@ def test_layer_norm_from_primitives_is_one_kernel(b200, backend, spelling, dt, w
     assert len(_lines(plan)) == 1 and "layer_norm[" in plan, plan
     assert f"gamma={int(with_gamma)} beta={int(with_beta)}" in plan, plan
     (want,) = run_oracle(build, [x, g, b])
-    ok, viol = compare(got, want, 1e-5 if dt == np.float32 else 2e-2, 0.05)   # 16-bit: the chain rounds every step to 8 bits
+    # 16-bit: the chain rounds the mean, the centred value and every later step to 8 bits, so its absolute error is a few
+    # 2^-9 of the ROW's scale even where the result is near zero: norm-relative tolerance
+    ok, viol = compare(got, want, 1e-5 if dt == np.float32 else 2e-2, 0.05 if dt == np.float32 else 1.0)
     assert ok, viol
     (fused,) = run_backend(b200, backend, lambda f, a, gg, bb: f.FusedLayerNorm(a, [-1], 1e-5, gg if with_gamma else None, bb if with_beta else None),
                            [x, g, b])
@@ -303,7 +305,8 @@ def test_softmax_from_primitives_is_one_kernel(b200, backend, dt, explicit_broad
     (got,), plan = run_backend(b200, backend, build, [x], describe=True)
     assert len(_lines(plan)) == 1 and "softmax" in plan, plan
     (want,) = run_oracle(build, [x])
-    ok, viol = compare(got, want, 1e-5 if dt == np.float32 else 2e-2, 0.01)
+    # 16-bit: the chain rounds x - max, the exponentials and their sum to 8 bits each; norm-relative tolerance
+    ok, viol = compare(got, want, 1e-5 if dt == np.float32 else 2e-2, 0.01 if dt == np.float32 else 1.0)
     assert ok, viol
     (fused,) = run_backend(b200, backend, lambda f, a: f.FusedSoftmax(a, 2), [x])
     np.testing.assert_array_equal(got, fused)
