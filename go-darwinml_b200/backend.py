@@ -322,7 +322,8 @@ class Builder:
         return self._main
 
     def NewFunction(self, name: str) -> "Function":
-        raise BackendError(3, "NewFunction: sub-functions (While/If/Call closures) are outside this backend's scope")
+        """A named sub-function, the target of Call (ref builder.go:57-60).  It is built in the builder's own context."""
+        return Function(self, name, parent=None, is_main=False)
 
     def OpShape(self, value: Value) -> Shape:
         if not isinstance(value, Value) or value.owner.builder is not self:
@@ -355,9 +356,11 @@ class Builder:
 class Function:
     """backends.Function: one method per op (ref function.go, dotgeneral.go, gather.go)."""
 
-    def __init__(self, builder: Builder, name: str):
+    def __init__(self, builder: Builder, name: str, parent: Optional["Function"] = None, is_main: bool = True):
         self.builder = builder
         self.name = name
+        self.parent = parent
+        self.is_main = is_main
         self._L = builder._L
         self.params: List[Value] = []
         self.param_names: List[str] = []
@@ -367,16 +370,27 @@ class Function:
         return self.name
 
     def Parent(self):
-        return None
+        return self.parent
+
+    def Closure(self) -> "Function":
+        """A closure of this function: the cond / body of While, a branch of If, the comparator of Sort (ref
+        function.go:120-131).  It is built in the same context as its parent and captures the parent's values by using
+        them; the reference gives each closure a context of its own and feeds captures through placeholders."""
+        return Function(self.builder, "", parent=self, is_main=False)
 
     # -- helpers --
     def _h(self, v, what: str):
-        # foreign values are refused, like resolveNode (ref function.go:179-195)
+        # a closure may use its ancestors' values; other foreign values are refused, like resolveNode (ref function.go:179-195)
         if not isinstance(v, Value):
             raise BackendError(1, f"{what}: expected a Value of this backend, got {type(v).__name__}")
-        if v.owner is not self:
-            raise BackendError(1, f"{what}: node from unrelated function scope")
-        return v.handle
+        if v.owner is self:
+            return v.handle
+        p = self.parent
+        while p is not None:
+            if v.owner is p:
+                return v.handle
+            p = p.parent
+        raise BackendError(1, f"{what}: node from unrelated function scope")
 
     def _wrap(self, handle, err, what: str) -> Value:
         _check(err, what)
@@ -393,8 +407,8 @@ class Function:
     # -- leaves (ref function.go:288-351) --
     def Parameter(self, name: str, shape: Shape, sharding=None) -> Value:
         err = _lib.B200Error()
-        v = self._wrap(self._L.b200_placeholder(self.builder.ctx, int(shape.DType), _i64(shape.Dimensions), shape.Rank(), ctypes.byref(err)),
-                       err, "Parameter")
+        make = self._L.b200_placeholder if self.is_main else self._L.b200_closure_parameter
+        v = self._wrap(make(self.builder.ctx, int(shape.DType), _i64(shape.Dimensions), shape.Rank(), ctypes.byref(err)), err, "Parameter")
         self.params.append(v)
         self.param_names.append(name)
         return v
@@ -417,6 +431,134 @@ class Function:
         for o in outputs:
             self._h(o, "Return")
         self.outputs = list(outputs)
+
+    # -- control flow over closures (ref function.go:354-652) --
+    def _closure(self, op: str, role: str, fn) -> "Function":
+        # ref validateClosure, function.go:234-246
+        if not isinstance(fn, Function):
+            raise BackendError(1, f"{op}: {role} must be a Function of this backend, got {type(fn).__name__}")
+        if fn.parent is not self:
+            raise BackendError(1, f"{op}: {role} must be a closure of the current function")
+        if fn.outputs is None:
+            raise BackendError(1, f"{op}: {role} must have Return() called")
+        return fn
+
+    @staticmethod
+    def _handles(values) -> "ctypes.Array":
+        return (ctypes.c_void_p * max(len(values), 1))(*[v if isinstance(v, int) or v is None else v.handle for v in values])
+
+    def Call(self, fn, *inputs) -> List[Value]:
+        """ref function.go:354-403.  The callee is inlined where it is called."""
+        hs = [self._h(v, "Call") for v in inputs]
+        if not isinstance(fn, Function):
+            raise BackendError(1, f"Call: target must be a Function of this backend, got {type(fn).__name__}")
+        if fn.builder is not self.builder:
+            raise BackendError(1, "Call: target function must be from the same builder")
+        if fn.outputs is None:
+            raise BackendError(1, f"Call: target function {fn.name!r} must have Return() called")
+        if len(hs) != len(fn.params):
+            raise BackendError(1, f"Call: function {fn.name!r} expects {len(fn.params)} parameters, got {len(hs)} inputs")
+        for i, (p, v) in enumerate(zip(fn.params, inputs)):
+            if p.shape != v.shape:
+                raise BackendError(1, f"Call: parameter {i} shape mismatch: expected {p.shape}, got {v.shape}")
+        n = len(fn.outputs)
+        res = (ctypes.c_void_p * n)()
+        err = _lib.B200Error()
+        self._L.b200_call(self.builder.ctx, self._handles(fn.params), len(fn.params), self._handles(fn.outputs), n,
+                          (ctypes.c_void_p * max(len(hs), 1))(*hs), res, ctypes.byref(err))
+        _check(err, "Call")
+        return [Value(res[i], self) for i in range(n)]
+
+    def While(self, cond, body, *initial_state) -> List[Value]:
+        """ref function.go:406-489: state -> cond(state) scalar bool, state -> body(state); returns the final state."""
+        if len(initial_state) == 0:
+            raise BackendError(1, "While: requires at least one initial state value")
+        hs = [self._h(v, "While") for v in initial_state]
+        c = self._closure("While", "cond", cond)
+        b = self._closure("While", "body", body)
+        n = len(hs)
+        for role, fn in (("cond", c), ("body", b)):
+            if len(fn.params) != n:
+                raise BackendError(1, f"While: {role} must have {n} parameters, got {len(fn.params)}")
+            for i, (p, v) in enumerate(zip(fn.params, initial_state)):
+                if p.shape != v.shape:
+                    raise BackendError(1, f"While: {role} parameter {i} shape {p.shape} doesn't match state shape {v.shape}")
+        if len(c.outputs) != 1:
+            raise BackendError(1, f"While: cond must return exactly one value, got {len(c.outputs)}")
+        if c.outputs[0].shape.Rank() != 0 or c.outputs[0].shape.DType != dtypes.Bool:
+            raise BackendError(1, f"While: cond must return scalar bool, got {c.outputs[0].shape}")
+        if len(b.outputs) != n:
+            raise BackendError(1, f"While: body must return {n} values, got {len(b.outputs)}")
+        for i, (o, v) in enumerate(zip(b.outputs, initial_state)):
+            if o.shape != v.shape:
+                raise BackendError(1, f"While: body output {i} shape {o.shape} must match state shape {v.shape}")
+        res = (ctypes.c_void_p * n)()
+        err = _lib.B200Error()
+        self._L.b200_while(self.builder.ctx, self._handles(c.params), c.outputs[0].handle, self._handles(b.params), self._handles(b.outputs), n,
+                           (ctypes.c_void_p * n)(*hs), res, ctypes.byref(err))
+        _check(err, "While")
+        return [Value(res[i], self) for i in range(n)]
+
+    def If(self, pred, true_branch, false_branch) -> List[Value]:
+        """ref function.go:492-560.  Both branches are evaluated (they are pure) and the outputs selected by pred."""
+        ph = self._h(pred, "If: pred")
+        if pred.shape.Rank() != 0 or pred.shape.DType != dtypes.Bool:
+            raise BackendError(1, f"If: pred must be scalar bool, got {pred.shape}")
+        t = self._closure("If", "trueBranch", true_branch)
+        f = self._closure("If", "falseBranch", false_branch)
+        if len(t.params) != 0:
+            raise BackendError(1, f"If: trueBranch must have no parameters, got {len(t.params)}")
+        if len(f.params) != 0:
+            raise BackendError(1, f"If: falseBranch must have no parameters, got {len(f.params)}")
+        if len(t.outputs) != len(f.outputs):
+            raise BackendError(1, f"If: branches must return same number of outputs (true={len(t.outputs)}, false={len(f.outputs)})")
+        for i, (a, b) in enumerate(zip(t.outputs, f.outputs)):
+            if a.shape != b.shape:
+                raise BackendError(1, f"If: output {i} shapes must match (true={a.shape}, false={b.shape})")
+        n = len(t.outputs)
+        res = (ctypes.c_void_p * n)()
+        err = _lib.B200Error()
+        self._L.b200_if(self.builder.ctx, ph, self._handles(t.outputs), self._handles(f.outputs), n, res, ctypes.byref(err))
+        _check(err, "If")
+        return [Value(res[i], self) for i in range(n)]
+
+    def Sort(self, comparator, axis: int, is_stable: bool, *inputs) -> List[Value]:
+        """ref function.go:563-652.  The comparator must order by the first input alone (LessThan / GreaterThan of its first
+        two parameters, what GoMLX's Sort builds); every input is permuted alike.  Always stable; NaN keys sort last."""
+        if len(inputs) == 0:
+            raise BackendError(1, "Sort: requires at least one input tensor")
+        hs = [self._h(v, "Sort") for v in inputs]
+        c = self._closure("Sort", "comparator", comparator)
+        first = inputs[0].shape
+        for i, v in enumerate(inputs[1:]):
+            if v.shape.Rank() != first.Rank():
+                raise BackendError(1, f"Sort: all inputs must have same rank, input 0 rank={first.Rank()}, input {i + 1} rank={v.shape.Rank()}")
+            if tuple(v.shape.Dimensions) != tuple(first.Dimensions):
+                raise BackendError(1, "Sort: all inputs must have same dimensions")
+        rank = first.Rank()
+        a = axis + rank if axis < 0 else axis
+        if a < 0 or a >= rank:
+            raise BackendError(1, f"Sort: axis {axis} out of range for rank {rank}")
+        if len(c.params) != 2 * len(inputs):
+            raise BackendError(1, f"Sort: comparator must have {2 * len(inputs)} parameters, got {len(c.params)}")
+        for i, v in enumerate(inputs):
+            for j in range(2):
+                p = c.params[2 * i + j]
+                if p.shape.Rank() != 0:
+                    raise BackendError(1, f"Sort: comparator parameter {2 * i + j} must be scalar, got {p.shape}")
+                if p.shape.DType != v.shape.DType:
+                    raise BackendError(1, f"Sort: comparator parameter {2 * i + j} dtype {p.shape.DType!r} must match input dtype {v.shape.DType!r}")
+        if len(c.outputs) != 1:
+            raise BackendError(1, f"Sort: comparator must return exactly one value, got {len(c.outputs)}")
+        if c.outputs[0].shape.Rank() != 0 or c.outputs[0].shape.DType != dtypes.Bool:
+            raise BackendError(1, f"Sort: comparator must return scalar bool, got {c.outputs[0].shape}")
+        n = len(inputs)
+        res = (ctypes.c_void_p * n)()
+        err = _lib.B200Error()
+        self._L.b200_sort(self.builder.ctx, self._handles(c.params), len(c.params), c.outputs[0].handle, a, bool(is_stable),
+                          (ctypes.c_void_p * n)(*hs), n, res, ctypes.byref(err))
+        _check(err, "Sort")
+        return [Value(res[i], self) for i in range(n)]
 
     def Iota(self, shape: Shape, iota_axis: int) -> Value:
         err = _lib.B200Error()

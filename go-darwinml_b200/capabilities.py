@@ -2,9 +2,9 @@
 
 The reference declares 96 op types and 12 dtypes.  Listed here is what this
 backend lowers.  Op types of the reference that it does not lower --
-convolution, pooling and their gradients (SelectAndScatter), While / If / Sort /
-Call over sub-functions -- are absent, so GoMLX reports them as not implemented
-instead of failing late.
+convolution, pooling and their gradients (SelectAndScatter) -- are absent, so
+GoMLX reports them as not implemented instead of failing late.  Sort is
+listed with a limit: its comparator must order by the first input.
 """
 from __future__ import annotations
 
@@ -26,6 +26,7 @@ OPERATIONS = [
     "DotGeneral", "ReduceSum", "ReduceProduct", "ReduceMax", "ReduceMin", "ReduceLogicalAnd", "ReduceLogicalOr", "ArgMinMax",
     "Gather", "BatchNormForInference",
     "ScatterSum", "ScatterMax", "ScatterMin", "BatchNormForTraining", "BatchNormGradient", "RNGBitGenerator",
+    "Call", "While", "If", "Sort",
     "FusedSoftmax", "FusedGelu", "FusedLayerNorm", "FusedDense", "FusedAttentionQKVProjection",
     "FusedScaledDotProductAttention",
 ]
@@ -33,7 +34,7 @@ OPERATIONS = [
 
 @dataclass
 class Capabilities:
-    Functions: bool = False  # no sub-functions (the reference sets true for While/If/Call closures)
+    Functions: bool = True  # closures and named sub-functions for While / If / Sort / Call (ref capabilities.go:17)
     # Weights handed over as graph constants are uploaded to the device once, at compile, and stay resident; as
     # parameters they would be passed (and shape-checked) on every Execute.  Same field as the reference's second
     # backend sets (ref coreml/gomlx/capabilities.go:18-23).
@@ -44,7 +45,7 @@ class Capabilities:
 
 def backend_capabilities() -> Capabilities:
     return Capabilities(
-        Functions=False,
+        Functions=True,
         PreferConstantsForVariables=True,
         Operations={name: True for name in OPERATIONS},
         DTypes={int(d): True for d in (dtypes.Bool, dtypes.Int8, dtypes.Int16, dtypes.Int32, dtypes.Int64, dtypes.Float16,

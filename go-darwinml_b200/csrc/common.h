@@ -181,6 +181,9 @@ enum class Op : int {
   Rope,
   // training side: XLA scatter with a combiner (sum / max / min), and random bits from a counter-based generator
   Scatter, RngBits,
+  // control flow over closures (sub-graphs of the same graph whose inputs are ClosureParam nodes): While is the loop itself
+  // (no value), WhileResult picks one of its final state values; ArgSort is the permutation a Sort applies to its inputs
+  ClosureParam, While, WhileResult, ArgSort,
   kNumOps
 };
 const char* op_name(Op op);
@@ -239,10 +242,25 @@ int RewriteGemmResidual(Graph& graph, const std::vector<Node*>& targets);
 // Rope node (inputs x, c, s): one pass over x instead of two slices, a concatenation and a three-op chain.
 int RewriteRope(Graph& graph, const std::vector<Node*>& targets);
 
+// Copies the sub-graph that computes `outputs` from the closure parameters `params` into graph `dst` (which may be the
+// graph they live in): parameter i becomes subst[i]; a node that does not depend on any parameter is shared when dst
+// is its own graph, else cloned if it is a constant / iota (or computed from those alone) and otherwise turned into a
+// fresh Parameter of dst and appended to *captures (the value the caller must feed).  Defined in graph.cpp.
+Status CloneClosure(Graph& dst, const std::vector<Node*>& params, const std::vector<Node*>& subst, const std::vector<Node*>& outputs,
+                    std::vector<Node*>* cloned_outputs, std::vector<Node*>* captures, std::vector<Node*>* capture_params);
+
 // What a B200Context handle points to: one graph under construction and its device.
+// A closure extracted into a graph of its own (the cond or the body of a While): its feeds are the closure's parameters
+// followed by the outer values it captures, in the order the While node lists them among its operands.
+struct SubGraph {
+  Graph graph;
+  std::vector<Node*> feeds, targets;
+};
+
 struct Ctx {
   Graph graph;
   Device* dev = nullptr;
+  std::vector<std::unique_ptr<SubGraph>> subgraphs;   // owned by the context; a While node names two of them by index
 };
 
 }  // namespace b200

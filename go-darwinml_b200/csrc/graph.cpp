@@ -8,7 +8,9 @@
 // call sites; GoMLX's shapeinference package itself is not part of that tree.
 #include <algorithm>
 #include <cmath>
+#include <functional>
 #include <set>
+#include <unordered_map>
 
 #include "common.h"
 
@@ -26,7 +28,8 @@ const char* op_name(Op op) {
       "Where", "Clamp",
       "Cast", "Reshape", "Transpose", "BroadcastInDim", "Slice", "Concatenate", "Reverse", "Pad", "DynamicSlice", "DynamicUpdateSlice",
       "DotGeneral", "Reduce", "ArgMinMax", "Gather",
-      "Softmax", "SoftmaxMasked", "LayerNorm", "RmsNorm", "Attention", "Rope", "Scatter", "RngBits"};
+      "Softmax", "SoftmaxMasked", "LayerNorm", "RmsNorm", "Attention", "Rope", "Scatter", "RngBits",
+      "ClosureParam", "While", "WhileResult", "ArgSort"};
   static_assert(sizeof(names) / sizeof(names[0]) == (size_t)Op::kNumOps, "op_name table out of date");
   return names[(int)op];
 }
@@ -1356,4 +1359,242 @@ bool b200_rng_bit_generator(B200Context ctx, B200Value state, int dtype, const i
   return true;
 }
 
+// ---- control flow over closures (ref mpsgraph function.go:354-652; the reference runs these on the host, one control-flow
+// op per function, executable.go:219-480) -------------------------------------------------------------------------
+// A closure is a sub-graph of the SAME graph: its parameters are ClosureParam nodes, its results ordinary values, and it
+// captures outer values simply by using them.  Call inlines the callee; If computes both branches and selects (the
+// branches are pure); While keeps cond and body as sub-graphs that the executor compiles into two sub-plans; Sort
+// recognises a comparator that orders by its first operand and becomes ArgSort + one gather per input.
+B200Value b200_closure_parameter(B200Context ctx, int dtype, const int64_t* shape, int rank, B200Error* err) {
+  clear_error(err);
+  if (!ctx) return ret(err, Status::Invalid("closure parameter: null context"), nullptr);
+  if (!dtype_valid(dtype)) return ret(err, Status::Invalid("closure parameter: bad dtype"), nullptr);
+  Status s = check_shape("closure parameter", shape, rank);
+  if (!s.ok()) return ret(err, s, nullptr);
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  return ret(err, Status::OK(), g.Add(Op::ClosureParam, dtype, std::vector<int64_t>(shape, shape + rank), {}));
+}
+
+static Status closure_nodes(B200Context ctx, const char* what, const B200Value* vals, int n, std::vector<Node*>* out) {
+  for (int i = 0; i < n; ++i) {
+    Node* x;
+    B200_TRY(check_node(ctx, vals[i], what, &x));
+    out->push_back(x);
+  }
+  return Status::OK();
+}
+
+bool b200_call(B200Context ctx, const B200Value* params, int num_params, const B200Value* outputs, int num_outputs,
+               const B200Value* inputs, B200Value* results, B200Error* err) {
+  clear_error(err);
+  std::vector<Node*> ps, outs, ins;
+  Status s = closure_nodes(ctx, "Call: parameter", params, num_params, &ps);
+  if (s.ok()) s = closure_nodes(ctx, "Call: output", outputs, num_outputs, &outs);
+  if (s.ok()) s = closure_nodes(ctx, "Call: input", inputs, num_params, &ins);
+  for (int i = 0; s.ok() && i < num_params; ++i) {
+    if (ps[i]->op != Op::ClosureParam) s = Status::Invalid("Call: parameter is not a function parameter");
+    else if (ps[i]->dtype != ins[i]->dtype || ps[i]->dims != ins[i]->dims)
+      s = Status::Invalid(strfmt("Call: parameter %d shape mismatch", i));
+  }
+  if (s.ok() && (num_outputs < 1 || !results)) s = Status::Invalid("Call: the function returns nothing");
+  if (!s.ok()) { set_error(err, s); return false; }
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  std::vector<Node*> cloned;
+  s = CloneClosure(g, ps, ins, outs, &cloned, nullptr, nullptr);
+  if (!s.ok()) { set_error(err, s); return false; }
+  for (int i = 0; i < num_outputs; ++i) results[i] = reinterpret_cast<B200Value>(cloned[i]);
+  return true;
+}
+
+bool b200_if(B200Context ctx, B200Value pred, const B200Value* true_outputs, const B200Value* false_outputs, int num_outputs,
+             B200Value* results, B200Error* err) {
+  clear_error(err);
+  Node* p;
+  std::vector<Node*> t, f;
+  Status s = check_node(ctx, pred, "If: pred", &p);
+  if (s.ok() && (p->dtype != B200_BOOL || p->num_elements() != 1 || p->rank() != 0)) s = Status::Invalid("If: pred must be scalar bool");
+  if (s.ok()) s = closure_nodes(ctx, "If: trueBranch output", true_outputs, num_outputs, &t);
+  if (s.ok()) s = closure_nodes(ctx, "If: falseBranch output", false_outputs, num_outputs, &f);
+  for (int i = 0; s.ok() && i < num_outputs; ++i)
+    if (t[i]->dtype != f[i]->dtype || t[i]->dims != f[i]->dims) s = Status::Invalid(strfmt("If: output %d shapes must match", i));
+  if (s.ok() && (num_outputs < 1 || !results)) s = Status::Invalid("If: the branches return nothing");
+  if (!s.ok()) { set_error(err, s); return false; }
+  for (int i = 0; i < num_outputs; ++i) {
+    B200Value cond = b200_broadcast_in_dim(ctx, pred, t[i]->dims.data(), t[i]->rank(), nullptr, 0, err);
+    if (!cond) return false;
+    results[i] = b200_where(ctx, cond, true_outputs[i], false_outputs[i], err);
+    if (!results[i]) return false;
+  }
+  return true;
+}
+
+bool b200_while(B200Context ctx, const B200Value* cond_params, B200Value cond_output, const B200Value* body_params,
+                const B200Value* body_outputs, int num_state, const B200Value* initial_state, B200Value* results, B200Error* err) {
+  clear_error(err);
+  std::vector<Node*> cp, bp, bo, init;
+  Node* co = nullptr;
+  Status s = num_state >= 1 ? Status::OK() : Status::Invalid("While: requires at least one initial state value");
+  if (s.ok()) s = closure_nodes(ctx, "While: cond parameter", cond_params, num_state, &cp);
+  if (s.ok()) s = closure_nodes(ctx, "While: body parameter", body_params, num_state, &bp);
+  if (s.ok()) s = closure_nodes(ctx, "While: body output", body_outputs, num_state, &bo);
+  if (s.ok()) s = closure_nodes(ctx, "While: initial state", initial_state, num_state, &init);
+  if (s.ok()) s = check_node(ctx, cond_output, "While: cond output", &co);
+  if (s.ok() && (co->dtype != B200_BOOL || co->rank() != 0)) s = Status::Invalid("While: cond must return scalar bool");
+  for (int i = 0; s.ok() && i < num_state; ++i) {
+    auto same = [&](Node* a) { return a->dtype == init[i]->dtype && a->dims == init[i]->dims; };
+    if (cp[i]->op != Op::ClosureParam || bp[i]->op != Op::ClosureParam) s = Status::Invalid("While: cond / body parameter is not a closure parameter");
+    else if (!same(cp[i])) s = Status::Invalid(strfmt("While: cond parameter %d doesn't match state shape", i));
+    else if (!same(bp[i])) s = Status::Invalid(strfmt("While: body parameter %d doesn't match state shape", i));
+    else if (!same(bo[i])) s = Status::Invalid(strfmt("While: body output %d must match state shape", i));
+  }
+  if (s.ok() && !results) s = Status::Invalid("While: null result pointer");
+  if (!s.ok()) { set_error(err, s); return false; }
+  Ctx* c = reinterpret_cast<Ctx*>(ctx);
+  Graph& g = c->graph;
+  // cond and body each become a graph of their own (compiled into a sub-plan when the parent is compiled): parameters
+  // first, then the outer values they capture, which the While node lists after its initial state so that they are
+  // live and materialised in the parent
+  auto extract = [&](const std::vector<Node*>& params, const std::vector<Node*>& outs, std::vector<Node*>* caps) -> int {
+    std::unique_ptr<SubGraph> sg(new SubGraph());
+    sg->graph.device = g.device;
+    std::vector<Node*> feeds, cap_params;
+    for (Node* p : params) feeds.push_back(sg->graph.Add(Op::Parameter, p->dtype, p->dims, {}));
+    s = CloneClosure(sg->graph, params, feeds, outs, &sg->targets, caps, &cap_params);
+    if (!s.ok()) return -1;
+    feeds.insert(feeds.end(), cap_params.begin(), cap_params.end());
+    sg->feeds = feeds;
+    c->subgraphs.push_back(std::move(sg));
+    return (int)c->subgraphs.size() - 1;
+  };
+  std::vector<Node*> cond_caps, body_caps;
+  const int cond_sg = extract(cp, {co}, &cond_caps);
+  const int body_sg = cond_sg >= 0 ? extract(bp, bo, &body_caps) : -1;
+  if (cond_sg < 0 || body_sg < 0) { set_error(err, s); return false; }
+  std::vector<Node*> operands = init;
+  operands.insert(operands.end(), cond_caps.begin(), cond_caps.end());
+  operands.insert(operands.end(), body_caps.begin(), body_caps.end());
+  Node* w = g.Add(Op::While, B200_BOOL, {}, operands);
+  // ia = [n_state, cond subgraph, body subgraph, n_cond_captures, n_body_captures]
+  w->ia = {num_state, cond_sg, body_sg, (int64_t)cond_caps.size(), (int64_t)body_caps.size()};
+  for (int i = 0; i < num_state; ++i) {
+    Node* r = g.Add(Op::WhileResult, init[i]->dtype, init[i]->dims, {w});
+    r->ia = {i};
+    results[i] = reinterpret_cast<B200Value>(r);
+  }
+  return true;
+}
+
+// The comparator must order by its FIRST operand alone: output = LessThan / LessOrEqual (ascending) or GreaterThan /
+// GreaterOrEqual (descending) of parameters 0 and 1, in either order, which is what GoMLX's Sort helper builds.
+bool b200_sort(B200Context ctx, const B200Value* comparator_params, int num_params, B200Value comparator_output, int axis, bool is_stable,
+               const B200Value* inputs, int num_inputs, B200Value* results, B200Error* err) {
+  (void)is_stable;   // the sort is always stable
+  clear_error(err);
+  std::vector<Node*> cp, ins;
+  Node* co = nullptr;
+  Status s = num_inputs >= 1 ? Status::OK() : Status::Invalid("Sort: requires at least one input tensor");
+  if (s.ok() && num_params != 2 * num_inputs) s = Status::Invalid(strfmt("Sort: comparator must have %d parameters, got %d", 2 * num_inputs, num_params));
+  if (s.ok()) s = closure_nodes(ctx, "Sort: comparator parameter", comparator_params, num_params, &cp);
+  if (s.ok()) s = closure_nodes(ctx, "Sort: input", inputs, num_inputs, &ins);
+  if (s.ok()) s = check_node(ctx, comparator_output, "Sort: comparator output", &co);
+  if (s.ok() && (co->dtype != B200_BOOL || co->rank() != 0)) s = Status::Invalid("Sort: comparator must return scalar bool");
+  for (int i = 0; s.ok() && i < num_inputs; ++i) {
+    if (ins[i]->dims != ins[0]->dims) s = Status::Invalid("Sort: all inputs must have same dimensions");
+    for (int j = 0; s.ok() && j < 2; ++j) {
+      Node* q = cp[2 * i + j];
+      if (q->op != Op::ClosureParam || q->rank() != 0) s = Status::Invalid(strfmt("Sort: comparator parameter %d must be scalar", 2 * i + j));
+      else if (q->dtype != ins[i]->dtype) s = Status::Invalid(strfmt("Sort: comparator parameter %d dtype must match input dtype", 2 * i + j));
+    }
+  }
+  int a = 0;
+  if (s.ok()) s = normalize_axis("Sort", axis, ins[0]->rank(), &a);
+  bool descending = false;
+  if (s.ok()) {
+    Node* c = co;
+    while (c->op == Op::Identity || c->op == Op::Reshape) c = c->in[0];
+    const bool lt = c->op == Op::LessThan || c->op == Op::LessOrEqual, gt = c->op == Op::GreaterThan || c->op == Op::GreaterOrEqual;
+    if ((lt || gt) && c->in[0] == cp[0] && c->in[1] == cp[1]) descending = gt;
+    else if ((lt || gt) && c->in[0] == cp[1] && c->in[1] == cp[0]) descending = lt;
+    else s = Status::Unsupported("Sort: only comparators that order by the first input (LessThan / GreaterThan of its two parameters) are supported");
+  }
+  if (s.ok() && dtype_size(ins[0]->dtype) == 8) s = Status::Unsupported("Sort: 64-bit keys are not supported");
+  if (s.ok() && !results) s = Status::Invalid("Sort: null result pointer");
+  if (!s.ok()) { set_error(err, s); return false; }
+  Graph& g = reinterpret_cast<Ctx*>(ctx)->graph;
+  Node* perm = g.Add(Op::ArgSort, B200_INT32, ins[0]->dims, {ins[0]});
+  perm->ia = {a, descending ? 1 : 0};
+  for (int i = 0; i < num_inputs; ++i) {
+    results[i] = b200_gather_along_axis(ctx, inputs[i], reinterpret_cast<B200Value>(perm), a, err);
+    if (!results[i]) return false;
+  }
+  return true;
+}
+
 }  // extern "C"
+
+namespace b200 {
+
+Status CloneClosure(Graph& dst, const std::vector<Node*>& params, const std::vector<Node*>& subst, const std::vector<Node*>& outputs,
+                    std::vector<Node*>* cloned_outputs, std::vector<Node*>* captures, std::vector<Node*>* capture_params) {
+  if (outputs.empty()) return Status::Invalid("closure: no outputs");
+  Graph* src = outputs[0]->graph;
+  const bool same_graph = src == &dst;
+  std::unordered_map<Node*, Node*> map;
+  for (size_t i = 0; i < params.size(); ++i) map[params[i]] = subst[i];
+  // does a node depend on a parameter of THIS closure?  (memoised; another closure's parameter counts as outside)
+  std::unordered_map<Node*, bool> dep;
+  std::function<bool(Node*)> depends = [&](Node* n) -> bool {
+    auto it = dep.find(n);
+    if (it != dep.end()) return it->second;
+    bool d = map.count(n) && n->op == Op::ClosureParam;
+    for (Node* i : n->in) d = depends(i) || d;
+    return dep[n] = d;
+  };
+  // computed from constants and iotas alone (cheap to copy into another graph)
+  std::function<bool(Node*)> constant_only = [&](Node* n) -> bool {
+    if (n->op == Op::Constant || n->op == Op::Iota) return true;
+    if (n->op == Op::Parameter || n->op == Op::ClosureParam || n->in.empty()) return false;
+    if (n->op == Op::While || n->op == Op::WhileResult || n->num_elements() > 4096) return false;
+    for (Node* i : n->in)
+      if (!constant_only(i)) return false;
+    return true;
+  };
+  Status failed = Status::OK();
+  std::function<Node*(Node*)> clone = [&](Node* n) -> Node* {
+    auto it = map.find(n);
+    if (it != map.end()) return it->second;
+    if (n->op == Op::While || n->op == Op::WhileResult) {
+      if (same_graph && !depends(n)) return map[n] = n;
+      failed = Status::Unsupported("a While inside a closure that is compiled or called separately is not supported");
+      return n;
+    }
+    if (n->op == Op::ClosureParam) {
+      failed = Status::Invalid("closure uses a parameter of another closure");
+      return n;
+    }
+    if (!depends(n)) {
+      if (same_graph) return map[n] = n;
+      if (!constant_only(n)) {   // an outer value: feed it
+        Node* p = dst.Add(Op::Parameter, n->dtype, n->dims, {});
+        if (captures) captures->push_back(n);
+        if (capture_params) capture_params->push_back(p);
+        return map[n] = p;
+      }
+    }
+    std::vector<Node*> in;
+    for (Node* i : n->in) in.push_back(clone(i));
+    Node* c = dst.Add(n->op, n->dtype, n->dims, in);
+    c->ia = n->ia;
+    c->fa = n->fa;
+    c->data = n->data;
+    return map[n] = c;
+  };
+  for (Node* o : outputs) {
+    Node* c = clone(o);
+    if (!failed.ok()) return failed;
+    cloned_outputs->push_back(c);
+  }
+  return Status::OK();
+}
+
+}  // namespace b200

@@ -213,6 +213,13 @@ struct ScatterParams {
 };
 Status scatter(Device* dev, const ScatterParams& p);
 
+// ------------------------------------------------------------------ sort ---
+// out (int32, x's shape) = the stable permutation that sorts x, viewed as [outer, n, inner], along n; NaN keys last.
+// Rows longer than 4096 keys need arg_sort_scratch_bytes of scratch.
+int64_t arg_sort_scratch_bytes(int64_t outer, int64_t n, int64_t inner, int sm_count);
+Status arg_sort(Device* dev, const void* x, void* out, int dtype, int64_t outer, int64_t n, int64_t inner, bool descending, void* scratch,
+                int64_t scratch_bytes);
+
 // ------------------------------------------------------------------- RNG ---
 // n elements of `dtype` from Philox4x32-10 keyed and positioned by the [3] Uint64 state in device memory.
 Status rng_bits(Device* dev, const void* state, void* y, int dtype, int64_t n);

@@ -91,6 +91,8 @@ struct Exec {
   std::vector<PlanGraph> graphs;
   std::vector<void*> last_key;
   uint64_t tick = 0;
+  // sub-plans of While loops (cond, body); run by the While step through RunSubPlan, never from outside
+  std::vector<std::unique_ptr<Exec>> children;
   ~Exec() {
     for (auto& g : graphs)
       if (g.exec) cudaGraphExecDestroy(g.exec);
@@ -131,9 +133,29 @@ struct IndexMap {
   }
 };
 
+// Rewrites + plan + arena for one graph (the context's own, or a While's cond / body sub-graph of `owner`).
+Status CompileGraph(Ctx* owner, Graph& graph, std::vector<Node*> feeds, std::vector<Node*> targets, std::unique_ptr<Exec>* out);
+
+// Runs a sub-plan's steps on the device's stream with caller-provided input and output addresses.
+Status RunSubPlan(Exec* ex, void* const* in_ptrs, void* const* out_ptrs) {
+  std::vector<void*> ptrs(ex->slots.size(), nullptr);
+  for (size_t i = 0; i < ex->inputs.size(); ++i) ptrs[ex->inputs[i].slot] = in_ptrs[i];
+  for (size_t i = 0; i < ex->outputs.size(); ++i) ptrs[ex->outputs[i].slot] = out_ptrs[i];
+  for (size_t s = 0; s < ex->slots.size(); ++s) {
+    const Slot& sl = ex->slots[s];
+    if (sl.kind == SlotKind::Arena) ptrs[s] = (char*)ex->arena + sl.offset;
+    else if (sl.kind == SlotKind::Const) ptrs[s] = ex->const_ptrs[sl.index];
+  }
+  for (auto& st : ex->steps) {
+    Status rs = st.run(ex->dev, ptrs.data());
+    if (!rs.ok()) return Status{rs.code, st.desc + ": " + rs.msg};
+  }
+  return Status::OK();
+}
+
 class Planner {
  public:
-  Planner(Ctx* ctx, Exec* exec) : ctx_(ctx), ex_(exec), g_(ctx->graph) {}
+  Planner(Ctx* ctx, Graph& graph, Exec* exec) : ctx_(ctx), ex_(exec), g_(graph) {}
 
   Status Run(const std::vector<Node*>& feeds, const std::vector<Node*>& targets) {
     const int n = (int)g_.nodes.size();
@@ -302,6 +324,12 @@ class Planner {
       case Op::Gather: return EmitGather(x);
       case Op::Scatter: return EmitScatter(x);
       case Op::RngBits: return EmitRngBits(x);
+      case Op::ArgSort: return EmitArgSort(x);
+      case Op::While: return EmitWhile(x);
+      case Op::WhileResult:
+        B200_TRY(EnsureMaterialized(x->in[0]));
+        return slot_of_[x->id] >= 0 ? Status::OK() : Status::Invalid("compile: While did not produce its result");
+      case Op::ClosureParam: return Status::Invalid("compile: a closure's parameter is used outside its closure");
       case Op::Softmax: return EmitSoftmax(x);
       case Op::SoftmaxMasked: return EmitSoftmaxMasked(x);
       case Op::LayerNorm: case Op::RmsNorm: return EmitNorm(x);
@@ -1383,6 +1411,116 @@ class Planner {
     return Status::OK();
   }
 
+  // The stable sorting permutation of in[0] along ia[0] (ia[1]: descending), int32.
+  Status EmitArgSort(Node* x) {
+    Node* a = x->in[0];
+    B200_TRY(EnsureMaterialized(a));
+    const int axis = (int)x->ia[0];
+    const bool descending = x->ia[1] != 0;
+    int64_t outer = 1, inner = 1;
+    for (int i = 0; i < axis; ++i) outer *= a->dims[i];
+    for (int i = axis + 1; i < a->rank(); ++i) inner *= a->dims[i];
+    const int64_t n = a->rank() ? a->dims[axis] : 1;
+    const int sa = SlotOf(a);
+    const int so = NewValueSlot(x);
+    const int64_t scratch_bytes = k::arg_sort_scratch_bytes(outer, n, inner, ex_->dev->sm_count());
+    const int sc = scratch_bytes > 0 ? NewTemp(scratch_bytes) : -1;
+    const int dt = a->dtype;
+    Step st;
+    st.desc = strfmt("argsort[%s rows=%lld n=%lld inner=%lld %s]", dtype_name(dt), (long long)outer, (long long)n, (long long)inner,
+                     descending ? "descending" : "ascending");
+    st.reads = {sa};
+    st.writes = {so};
+    if (sc >= 0) st.writes.push_back(sc);
+    st.run = [=](Device* dev, void* const* p) -> Status {
+      return k::arg_sort(dev, p[sa], p[so], dt, outer, n, inner, descending, sc >= 0 ? p[sc] : nullptr, scratch_bytes);
+    };
+    ex_->steps.push_back(std::move(st));
+    return Status::OK();
+  }
+
+  // While: in = initial state, then the outer values cond captures, then those body captures;
+  // ia = [n_state, cond sub-graph, body sub-graph, n cond captures, n body captures] (sub-graphs are owned by the context).
+  // cond and body compile into two sub-plans.  The step copies the initial state into the result slots, then loops on the
+  // host: run cond, read its one byte back, stop or run body into a second set of state buffers and swap.  The reference
+  // also loops on the host, re-entering a whole executable per iteration (ref mpsgraph executable.go:219-300).
+  Status EmitWhile(Node* w) {
+    if (!ctx_) return Status::Unsupported("compile: a While inside a While's cond or body is not supported");
+    const int n_state = (int)w->ia[0];
+    const int n_cc = (int)w->ia[3], n_bc = (int)w->ia[4];
+    if (w->ia[1] < 0 || w->ia[2] < 0 || (size_t)w->ia[1] >= ctx_->subgraphs.size() || (size_t)w->ia[2] >= ctx_->subgraphs.size())
+      return Status::Invalid("compile: While names a sub-graph the context does not hold");
+    for (Node* i : w->in) B200_TRY(EnsureMaterialized(i));
+    std::unique_ptr<Exec> cond, body;
+    SubGraph* csg = ctx_->subgraphs[(size_t)w->ia[1]].get();
+    SubGraph* bsg = ctx_->subgraphs[(size_t)w->ia[2]].get();
+    Status s = CompileGraph(nullptr, csg->graph, csg->feeds, csg->targets, &cond);
+    if (!s.ok()) return Status{s.code, "While cond: " + s.msg};
+    s = CompileGraph(nullptr, bsg->graph, bsg->feeds, bsg->targets, &body);
+    if (!s.ok()) return Status{s.code, "While body: " + s.msg};
+    Exec* ce = cond.get();
+    Exec* be = body.get();
+    ex_->children.push_back(std::move(cond));
+    ex_->children.push_back(std::move(body));
+
+    std::vector<int> in_slots, res_slots, tmp_slots;
+    std::vector<int64_t> nbytes;
+    for (Node* i : w->in) in_slots.push_back(SlotOf(i));
+    // the WhileResult nodes that exist for this loop claim their slots now; a state value nobody reads still needs memory
+    std::vector<Node*> result_node(n_state, nullptr);
+    for (auto& up : g_.nodes)
+      if (up->op == Op::WhileResult && up->in[0] == w && live_[up->id]) result_node[(size_t)up->ia[0]] = up.get();
+    for (int i = 0; i < n_state; ++i) {
+      const int64_t nb = w->in[i]->num_elements() * dtype_size(w->in[i]->dtype);
+      nbytes.push_back(nb);
+      res_slots.push_back(result_node[i] ? NewValueSlot(result_node[i]) : NewTemp(nb));
+      tmp_slots.push_back(NewTemp(nb));
+    }
+    const int pred_slot = NewTemp(256);
+    slot_of_[w->id] = pred_slot;
+
+    Step st;
+    st.desc = strfmt("while[state=%d cond: %d steps, %d captures; body: %d steps, %d captures]", n_state, (int)ce->steps.size(), n_cc,
+                     (int)be->steps.size(), n_bc);
+    st.reads = in_slots;
+    st.writes = res_slots;
+    st.writes.insert(st.writes.end(), tmp_slots.begin(), tmp_slots.end());
+    st.writes.push_back(pred_slot);
+    st.capturable = false;   // the trip count is read back from the device
+    st.launches = 0;         // counted per run: unknown at compile time
+    st.run = [=](Device* dev, void* const* p) -> Status {
+      B200_TRY(dev->MakeCurrent());
+      std::vector<void*> cur(n_state), nxt(n_state);
+      for (int i = 0; i < n_state; ++i) {
+        cur[i] = p[res_slots[i]];
+        nxt[i] = p[tmp_slots[i]];
+        if (nbytes[i] > 0) B200_CUDA_TRY(cudaMemcpyAsync(cur[i], p[in_slots[i]], (size_t)nbytes[i], cudaMemcpyDeviceToDevice, dev->stream()));
+      }
+      std::vector<void*> cin(n_state + n_cc), bin(n_state + n_bc);
+      for (int i = 0; i < n_cc; ++i) cin[n_state + i] = p[in_slots[n_state + i]];
+      for (int i = 0; i < n_bc; ++i) bin[n_state + i] = p[in_slots[n_state + n_cc + i]];
+      void* pred = p[pred_slot];
+      constexpr int64_t kMaxIterations = 1000000;   // the reference's limit (ref mpsgraph executable.go:241)
+      for (int64_t iter = 0;; ++iter) {
+        if (iter >= kMaxIterations) return Status::Invalid("While: exceeded maximum iterations (1000000)");
+        for (int i = 0; i < n_state; ++i) cin[i] = bin[i] = cur[i];
+        B200_TRY(RunSubPlan(ce, cin.data(), &pred));
+        unsigned char go = 0;
+        B200_CUDA_TRY(cudaMemcpyAsync(&go, pred, 1, cudaMemcpyDeviceToHost, dev->stream()));
+        B200_CUDA_TRY(cudaStreamSynchronize(dev->stream()));
+        if (!go) break;
+        B200_TRY(RunSubPlan(be, bin.data(), nxt.data()));
+        cur.swap(nxt);
+      }
+      for (int i = 0; i < n_state; ++i)
+        if (cur[i] != p[res_slots[i]] && nbytes[i] > 0)
+          B200_CUDA_TRY(cudaMemcpyAsync(p[res_slots[i]], cur[i], (size_t)nbytes[i], cudaMemcpyDeviceToDevice, dev->stream()));
+      return Status::OK();
+    };
+    ex_->steps.push_back(std::move(st));
+    return Status::OK();
+  }
+
   Status EmitRngBits(Node* x) {
     Node* state = x->in[0];
     B200_TRY(EnsureMaterialized(state));
@@ -1808,6 +1946,26 @@ class Planner {
   }
 };
 
+Status CompileGraph(Ctx* owner, Graph& graph, std::vector<Node*> feeds, std::vector<Node*> targets, std::unique_ptr<Exec>* out) {
+  Device* dev = nullptr;
+  B200_TRY(Device::Get(graph.device, &dev));
+  RewriteRmsNorm(graph, targets);
+  RewriteSoftmax(graph, targets);
+  RewriteGemmResidual(graph, targets);
+  RewriteRope(graph, targets);
+  std::unique_ptr<Exec> ex(new Exec());
+  ex->dev = dev;
+  Planner planner(owner, graph, ex.get());
+  B200_TRY(planner.Run(feeds, targets));
+  if (ex->arena_bytes > 0) B200_TRY(ex->dev->Alloc(ex->arena_bytes, &ex->arena));
+  static const bool graphs_on = []() { const char* v = getenv("B200MLX_GRAPHS"); return !(v && v[0] == '0'); }();
+  bool all = graphs_on && ex->steps.size() >= 4;
+  for (const Step& st : ex->steps) all = all && st.capturable;
+  ex->capturable = all;
+  *out = std::move(ex);
+  return Status::OK();
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -1837,21 +1995,8 @@ B200Exec b200_compile(B200Context ctx, const B200Value* feeds, int num_feeds, co
     if (!n) { set_error(err, Status::Invalid("compile: target does not belong to this context")); return nullptr; }
     t.push_back(n);
   }
-  RewriteRmsNorm(c->graph, t);
-  RewriteSoftmax(c->graph, t);
-  RewriteGemmResidual(c->graph, t);
-  RewriteRope(c->graph, t);
-  std::unique_ptr<Exec> ex(new Exec());
-  ex->dev = c->dev;
-  Planner planner(c, ex.get());
-  Status s = planner.Run(f, t);
-  if (s.ok() && ex->arena_bytes > 0) s = ex->dev->Alloc(ex->arena_bytes, &ex->arena);
-  {
-    static const bool graphs_on = []() { const char* v = getenv("B200MLX_GRAPHS"); return !(v && v[0] == '0'); }();
-    bool all = graphs_on && ex->steps.size() >= 4;
-    for (const Step& st : ex->steps) all = all && st.capturable;
-    ex->capturable = all;
-  }
+  std::unique_ptr<Exec> ex;
+  Status s = CompileGraph(c, c->graph, f, t, &ex);
   if (!s.ok()) { set_error(err, s); return nullptr; }
   return ex.release();
 }

@@ -26,9 +26,10 @@ var _ backends.Builder = (*Builder)(nil)
 func (b *Builder) Name() string            { return b.name }
 func (b *Builder) Main() backends.Function { return b.main }
 
-// NewFunction: sub-functions (closures for While / If / Sort / Call) are not lowered; Capabilities().Functions is false.
+// NewFunction creates a named sub-function, the target of Call (mpsgraph/gomlx/builder.go:57-60).  It is built in the
+// builder's own native context; Call inlines it.
 func (b *Builder) NewFunction(name string) (backends.Function, error) {
-	return nil, errors.Wrapf(notimplemented.NotImplementedError, "b200: NewFunction(%q): sub-functions are not supported", name)
+	return &Function{builder: b, name: name, sub: true}, nil
 }
 
 func (b *Builder) OpShape(op backends.Value) (shapes.Shape, error) {

@@ -36,6 +36,8 @@ type Function struct {
 
 	builder  *Builder
 	name     string
+	parent   *Function // set for closures
+	sub      bool      // a closure or a named sub-function: its parameters are closure parameters, not executable inputs
 	params   []param
 	outputs  []*node
 	returned bool
@@ -43,23 +45,50 @@ type Function struct {
 
 var _ backends.Function = (*Function)(nil)
 
-func (f *Function) Name() string                       { return f.name }
-func (f *Function) Parent() backends.Function          { return nil }
-func (f *Function) Closure() (backends.Function, error) {
-	return nil, errors.Wrap(notimplemented.NotImplementedError, "b200: closures are not supported")
+func (f *Function) Name() string { return f.name }
+
+func (f *Function) Parent() backends.Function {
+	if f.parent == nil {
+		return nil
+	}
+	return f.parent
 }
+
+// Closure creates a closure of this function: the cond / body of While, a branch of If, Sort's comparator
+// (mpsgraph/gomlx/function.go:120-131).  It shares the builder's native context and captures the values of its
+// ancestors by using them; the reference gives every closure a context of its own and feeds captures through placeholders.
+func (f *Function) Closure() (backends.Function, error) {
+	return &Function{builder: f.builder, parent: f, sub: true}, nil
+}
+
 func (f *Function) ctx() bridge.Context { return f.builder.ctx }
 
-// resolve checks that v is a live value of this function (foreign values are errors: builder.go:64-67 in the reference).
+// resolve checks that v is a live value of this function or, for a closure, of one of its ancestors; other foreign
+// values are errors (resolveNode, mpsgraph/gomlx/function.go:179-195).
 func (f *Function) resolve(op string, v backends.Value) (*node, error) {
 	n, ok := v.(*node)
 	if !ok || n == nil {
 		return nil, errors.Errorf("%s: value of type %T does not belong to the b200 backend", op, v)
 	}
-	if n.owner != f {
-		return nil, errors.Errorf("%s: value belongs to another function or builder", op)
+	for p := f; p != nil; p = p.parent {
+		if n.owner == p {
+			return n, nil
+		}
 	}
-	return n, nil
+	return nil, errors.Errorf("%s: node from unrelated function scope", op)
+}
+
+func (f *Function) resolveAll(op string, vs []backends.Value) ([]*node, []bridge.Value, error) {
+	ns := make([]*node, len(vs))
+	hs := make([]bridge.Value, len(vs))
+	for i, v := range vs {
+		n, err := f.resolve(op, v)
+		if err != nil {
+			return nil, nil, err
+		}
+		ns[i], hs[i] = n, n.value
+	}
+	return ns, hs, nil
 }
 
 // optional resolves a value that may be nil (a bias, a mask).
@@ -103,7 +132,11 @@ func (f *Function) Parameter(name string, shape shapes.Shape, sharding *backends
 	if err != nil {
 		return nil, errors.Wrap(err, "Parameter")
 	}
-	v, err := f.ctx().Placeholder(dt, dims64(shape.Dimensions))
+	newParam := f.ctx().Placeholder
+	if f.sub {
+		newParam = f.ctx().ClosureParameter
+	}
+	v, err := newParam(dt, dims64(shape.Dimensions))
 	if err != nil {
 		return nil, errors.Wrapf(err, "Parameter(%q)", name)
 	}
@@ -769,4 +802,212 @@ func (f *Function) RNGBitGenerator(state backends.Value, shape shapes.Shape) (ne
 	}
 	values, err = f.wrap("RNGBitGenerator", v, nil)
 	return newState, values, err
+}
+
+// ---- control flow over closures (mpsgraph/gomlx/function.go:354-652) ----
+// Validation and messages follow the reference; unlike it there is no limit of one control-flow op per function.
+
+func (f *Function) validateClosure(op, role string, fn backends.Function) (*Function, error) {
+	c, ok := fn.(*Function)
+	if !ok || c == nil {
+		return nil, errors.Errorf("%s: %s must be a *b200.Function, got %T", op, role, fn)
+	}
+	if c.parent != f {
+		return nil, errors.Errorf("%s: %s must be a closure of the current function", op, role)
+	}
+	if !c.returned {
+		return nil, errors.Errorf("%s: %s must have Return() called", op, role)
+	}
+	return c, nil
+}
+
+func paramValues(c *Function) []bridge.Value {
+	hs := make([]bridge.Value, len(c.params))
+	for i, p := range c.params {
+		hs[i] = p.value
+	}
+	return hs
+}
+
+func outputValues(c *Function) []bridge.Value {
+	hs := make([]bridge.Value, len(c.outputs))
+	for i, o := range c.outputs {
+		hs[i] = o.value
+	}
+	return hs
+}
+
+func (f *Function) wrapAll(op string, vs []bridge.Value, err error) ([]backends.Value, error) {
+	if err != nil {
+		return nil, errors.Wrap(err, op)
+	}
+	out := make([]backends.Value, len(vs))
+	for i, v := range vs {
+		if out[i], err = f.wrap(op, v, nil); err != nil {
+			return nil, err
+		}
+	}
+	return out, nil
+}
+
+func (f *Function) Call(fn backends.Function, inputs ...backends.Value) ([]backends.Value, error) {
+	ins, hs, err := f.resolveAll("Call", inputs)
+	if err != nil {
+		return nil, err
+	}
+	target, ok := fn.(*Function)
+	if !ok || target == nil {
+		return nil, errors.Errorf("Call: target must be *b200.Function, got %T", fn)
+	}
+	if target.builder != f.builder {
+		return nil, errors.New("Call: target function must be from the same builder")
+	}
+	if !target.returned {
+		return nil, errors.Errorf("Call: target function %q must have Return() called", target.name)
+	}
+	if len(ins) != len(target.params) {
+		return nil, errors.Errorf("Call: function %q expects %d parameters, got %d inputs", target.name, len(target.params), len(ins))
+	}
+	for i, p := range target.params {
+		if !p.shape.Equal(ins[i].shape) {
+			return nil, errors.Errorf("Call: parameter %d shape mismatch: expected %s, got %s", i, p.shape, ins[i].shape)
+		}
+	}
+	res, err := f.ctx().Call(paramValues(target), outputValues(target), hs)
+	return f.wrapAll("Call", res, err)
+}
+
+func (f *Function) While(cond, body backends.Function, initialState ...backends.Value) ([]backends.Value, error) {
+	if len(initialState) == 0 {
+		return nil, errors.New("While: requires at least one initial state value")
+	}
+	state, hs, err := f.resolveAll("While", initialState)
+	if err != nil {
+		return nil, err
+	}
+	c, err := f.validateClosure("While", "cond", cond)
+	if err != nil {
+		return nil, err
+	}
+	b, err := f.validateClosure("While", "body", body)
+	if err != nil {
+		return nil, err
+	}
+	for _, role := range []struct {
+		name string
+		fn   *Function
+	}{{"cond", c}, {"body", b}} {
+		if len(role.fn.params) != len(state) {
+			return nil, errors.Errorf("While: %s must have %d parameters, got %d", role.name, len(state), len(role.fn.params))
+		}
+		for i, p := range role.fn.params {
+			if !p.shape.Equal(state[i].shape) {
+				return nil, errors.Errorf("While: %s parameter %d shape %s doesn't match state shape %s", role.name, i, p.shape, state[i].shape)
+			}
+		}
+	}
+	if len(c.outputs) != 1 {
+		return nil, errors.Errorf("While: cond must return exactly one value, got %d", len(c.outputs))
+	}
+	if c.outputs[0].shape.Rank() != 0 || c.outputs[0].shape.DType != dtypes.Bool {
+		return nil, errors.Errorf("While: cond must return scalar bool, got %s", c.outputs[0].shape)
+	}
+	if len(b.outputs) != len(state) {
+		return nil, errors.Errorf("While: body must return %d values, got %d", len(state), len(b.outputs))
+	}
+	for i, o := range b.outputs {
+		if !o.shape.Equal(state[i].shape) {
+			return nil, errors.Errorf("While: body output %d shape %s must match state shape %s", i, o.shape, state[i].shape)
+		}
+	}
+	res, err := f.ctx().While(paramValues(c), c.outputs[0].value, paramValues(b), outputValues(b), hs)
+	return f.wrapAll("While", res, err)
+}
+
+func (f *Function) If(pred backends.Value, trueBranch, falseBranch backends.Function) ([]backends.Value, error) {
+	p, err := f.resolve("If: pred", pred)
+	if err != nil {
+		return nil, err
+	}
+	if p.shape.Rank() != 0 || p.shape.DType != dtypes.Bool {
+		return nil, errors.Errorf("If: pred must be scalar bool, got %s", p.shape)
+	}
+	t, err := f.validateClosure("If", "trueBranch", trueBranch)
+	if err != nil {
+		return nil, err
+	}
+	e, err := f.validateClosure("If", "falseBranch", falseBranch)
+	if err != nil {
+		return nil, err
+	}
+	if len(t.params) != 0 {
+		return nil, errors.Errorf("If: trueBranch must have no parameters, got %d", len(t.params))
+	}
+	if len(e.params) != 0 {
+		return nil, errors.Errorf("If: falseBranch must have no parameters, got %d", len(e.params))
+	}
+	if len(t.outputs) != len(e.outputs) {
+		return nil, errors.Errorf("If: branches must return same number of outputs (true=%d, false=%d)", len(t.outputs), len(e.outputs))
+	}
+	for i := range t.outputs {
+		if !t.outputs[i].shape.Equal(e.outputs[i].shape) {
+			return nil, errors.Errorf("If: output %d shapes must match (true=%s, false=%s)", i, t.outputs[i].shape, e.outputs[i].shape)
+		}
+	}
+	res, err := f.ctx().If(p.value, outputValues(t), outputValues(e))
+	return f.wrapAll("If", res, err)
+}
+
+func (f *Function) Sort(comparator backends.Function, axis int, isStable bool, inputs ...backends.Value) ([]backends.Value, error) {
+	if len(inputs) == 0 {
+		return nil, errors.New("Sort: requires at least one input tensor")
+	}
+	ins, hs, err := f.resolveAll("Sort", inputs)
+	if err != nil {
+		return nil, err
+	}
+	c, err := f.validateClosure("Sort", "comparator", comparator)
+	if err != nil {
+		return nil, err
+	}
+	first := ins[0].shape
+	for i, n := range ins[1:] {
+		if first.Rank() != n.shape.Rank() {
+			return nil, errors.Errorf("Sort: all inputs must have same rank, input 0 rank=%d, input %d rank=%d", first.Rank(), i+1, n.shape.Rank())
+		}
+		for j := range first.Dimensions {
+			if first.Dimensions[j] != n.shape.Dimensions[j] {
+				return nil, errors.Errorf("Sort: all inputs must have same dimensions")
+			}
+		}
+	}
+	rank := first.Rank()
+	if axis < 0 {
+		axis += rank
+	}
+	if axis < 0 || axis >= rank {
+		return nil, errors.Errorf("Sort: axis %d out of range for rank %d", axis, rank)
+	}
+	if len(c.params) != 2*len(ins) {
+		return nil, errors.Errorf("Sort: comparator must have %d parameters, got %d", 2*len(ins), len(c.params))
+	}
+	for i, n := range ins {
+		for j := 0; j < 2; j++ {
+			p := c.params[2*i+j]
+			if p.shape.Rank() != 0 {
+				return nil, errors.Errorf("Sort: comparator parameter %d must be scalar, got %s", 2*i+j, p.shape)
+			}
+			if p.shape.DType != n.shape.DType {
+				return nil, errors.Errorf("Sort: comparator parameter %d dtype %s must match input dtype %s", 2*i+j, p.shape.DType, n.shape.DType)
+			}
+		}
+	}
+	if len(c.outputs) != 1 {
+		return nil, errors.Errorf("Sort: comparator must return exactly one value, got %d", len(c.outputs))
+	}
+	if c.outputs[0].shape.Rank() != 0 || c.outputs[0].shape.DType != dtypes.Bool {
+		return nil, errors.Errorf("Sort: comparator must return scalar bool, got %s", c.outputs[0].shape)
+	}
+	res, err := f.ctx().Sort(paramValues(c), c.outputs[0].value, axis, isStable, hs)
+	return f.wrapAll("Sort", res, err)
 }

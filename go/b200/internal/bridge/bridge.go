@@ -428,6 +428,44 @@ func (c *contextImpl) RNGBitGenerator(state Value, dtype int, dims []int64) (new
 	return newState, values, takeError(&e)
 }
 
+// ---- control flow over closures ----
+
+// ClosureParameter is a parameter of a closure or of a named sub-function (built in the same context as its parent).
+func (c *contextImpl) ClosureParameter(dtype int, dims []int64) (Value, error) {
+	var e C.B200Error
+	return c.wrap(C.b200_closure_parameter(c.h, C.int(dtype), i64ptr(dims), C.int(len(dims)), &e), &e)
+}
+
+func (c *contextImpl) Call(params, outputs, inputs []Value) ([]Value, error) {
+	var e C.B200Error
+	results := make([]Value, len(outputs))
+	C.b200_call(c.h, valptr(params), C.int(len(params)), valptr(outputs), C.int(len(outputs)), valptr(inputs), valptr(results), &e)
+	return results, takeError(&e)
+}
+
+func (c *contextImpl) If(pred Value, trueOutputs, falseOutputs []Value) ([]Value, error) {
+	var e C.B200Error
+	results := make([]Value, len(trueOutputs))
+	C.b200_if(c.h, pred, valptr(trueOutputs), valptr(falseOutputs), C.int(len(trueOutputs)), valptr(results), &e)
+	return results, takeError(&e)
+}
+
+func (c *contextImpl) While(condParams []Value, condOutput Value, bodyParams, bodyOutputs, initialState []Value) ([]Value, error) {
+	var e C.B200Error
+	results := make([]Value, len(initialState))
+	C.b200_while(c.h, valptr(condParams), condOutput, valptr(bodyParams), valptr(bodyOutputs), C.int(len(initialState)),
+		valptr(initialState), valptr(results), &e)
+	return results, takeError(&e)
+}
+
+func (c *contextImpl) Sort(comparatorParams []Value, comparatorOutput Value, axis int, isStable bool, inputs []Value) ([]Value, error) {
+	var e C.B200Error
+	results := make([]Value, len(inputs))
+	C.b200_sort(c.h, valptr(comparatorParams), C.int(len(comparatorParams)), comparatorOutput, C.int(axis), C.bool(isStable),
+		valptr(inputs), C.int(len(inputs)), valptr(results), &e)
+	return results, takeError(&e)
+}
+
 // ---- compile / execute ----
 
 type execImpl struct{ h C.B200Exec }

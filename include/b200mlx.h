@@ -287,6 +287,30 @@ B200Value b200_scatter(B200Context ctx, int mode, B200Value operand, B200Value s
 bool b200_rng_bit_generator(B200Context ctx, B200Value state, int dtype, const int64_t* shape, int rank,
                             B200Value* out_new_state, B200Value* out_values, B200Error* err);
 
+/* ---- control flow over closures (ref function.go:109-131, 354-652; executable.go:219-480) ----------------
+ * A closure (GoMLX's Function.Closure() / Builder.NewFunction()) is built in the SAME context as its parent: its
+ * parameters come from b200_closure_parameter, its results are ordinary values, and it captures outer values by
+ * using them.  The reference keeps one control-flow op per function and runs it on the host; here there is no
+ * such limit. */
+B200Value b200_closure_parameter(B200Context ctx, int dtype, const int64_t* shape, int rank, B200Error* err);
+/* Call: the callee (params -> outputs) is inlined with `inputs` in place of its parameters. */
+bool b200_call(B200Context ctx, const B200Value* params, int num_params, const B200Value* outputs, int num_outputs,
+               const B200Value* inputs, B200Value* results, B200Error* err);
+/* If: pred is a scalar Bool; both branches (no parameters) are evaluated and results[i] selects between them. */
+bool b200_if(B200Context ctx, B200Value pred, const B200Value* true_outputs, const B200Value* false_outputs,
+             int num_outputs, B200Value* results, B200Error* err);
+/* While: state -> cond(state) scalar Bool; state -> body(state) of the same shapes; results = the final state.  cond and
+ * body are compiled into two sub-plans when the parent is compiled; the loop runs them on the device's stream and
+ * reads the one-byte condition back each iteration. */
+bool b200_while(B200Context ctx, const B200Value* cond_params, B200Value cond_output, const B200Value* body_params,
+                const B200Value* body_outputs, int num_state, const B200Value* initial_state, B200Value* results,
+                B200Error* err);
+/* Sort along `axis` (always stable): the comparator (2 scalar parameters per input) must order by its first input:
+ * LessThan / LessOrEqual / GreaterThan / GreaterOrEqual of its parameters 0 and 1.  Every input is permuted alike.
+ * NaN keys sort last.  64-bit keys are not supported. */
+bool b200_sort(B200Context ctx, const B200Value* comparator_params, int num_params, B200Value comparator_output, int axis,
+               bool is_stable, const B200Value* inputs, int num_inputs, B200Value* results, B200Error* err);
+
 /* ---- compile (ref bridge.h:159-163; builder.go:72-109) ------------------ */
 /* feeds are placeholders in Parameter order, targets in Return order. */
 B200Exec b200_compile(B200Context ctx, const B200Value* feeds, int num_feeds, const B200Value* targets,

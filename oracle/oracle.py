@@ -662,6 +662,81 @@ class OracleFunction:
             new_state = st + np.uint64(1)
         return new_state, vals.reshape(dims)
 
+    # ---- control flow over closures (ref function.go:354-652; executable.go:219-480) ----
+    # The oracle evaluates eagerly, so a closure here is a Python callable over arrays: MakeClosure(param_shapes, body) wraps
+    # body(f, *params) -> list of outputs and checks the arguments against the declared parameter shapes on every call.
+    def MakeClosure(self, param_shapes, body):
+        shapes = [(np.dtype(_dtype_of(s)), tuple(_dims_of(s))) for s in param_shapes]
+
+        def call(*args):
+            if len(args) != len(shapes):
+                raise OracleError(f"closure expects {len(shapes)} parameters, got {len(args)}")
+            for i, (a, (dt, dims)) in enumerate(zip(args, shapes)):
+                a = np.asarray(a)
+                if a.dtype != dt or tuple(a.shape) != dims:
+                    raise OracleError(f"closure parameter {i}: expected {dt}{list(dims)}, got {a.dtype}{list(a.shape)}")
+            return [np.asarray(o) for o in body(self, *[np.asarray(a) for a in args])]
+
+        call.num_params = len(shapes)
+        return call
+
+    def Call(self, fn, *inputs):
+        # ref function.go:354-403; executable.go:449-480: run the target on the inputs
+        return fn(*inputs)
+
+    def While(self, cond, body, *initial_state):
+        # ref function.go:406-489; executable.go:219-283: cond(state) -> scalar bool, body(state) -> state, at most 1e6 trips
+        if len(initial_state) == 0:
+            raise OracleError("While: requires at least one initial state value")
+        state = [np.asarray(v) for v in initial_state]
+        for _ in range(1000000):
+            (go,) = cond(*state)
+            if go.dtype != np.bool_ or go.ndim != 0:
+                raise OracleError("While: cond must return scalar bool")
+            if not bool(go):
+                return state
+            new = body(*state)
+            if len(new) != len(state) or any(n.dtype != o.dtype or n.shape != o.shape for n, o in zip(new, state)):
+                raise OracleError("While: body output must match state shape")
+            state = new
+        raise OracleError("While: exceeded maximum iterations (1000000)")
+
+    def If(self, pred, true_branch, false_branch):
+        # ref function.go:492-560; executable.go:286-318: the chosen branch alone runs; branches take no parameters
+        pred = np.asarray(pred)
+        if pred.dtype != np.bool_ or pred.ndim != 0:
+            raise OracleError("If: pred must be scalar bool")
+        return true_branch() if bool(pred) else false_branch()
+
+    def Sort(self, comparator, axis, is_stable, *inputs):
+        # ref function.go:563-652; executable.go:321-446: every row along `axis` is sorted on the host by a comparison sort
+        # that asks the comparator (lhs_0, rhs_0, lhs_1, rhs_1, ...) -> "lhs before rhs"; all inputs are permuted alike.
+        # Always stable here (a stable order is one of the orders an unstable sort may return).
+        import functools
+        if len(inputs) == 0:
+            raise OracleError("Sort: requires at least one input tensor")
+        ins = [np.asarray(v) for v in inputs]
+        if any(v.shape != ins[0].shape for v in ins):
+            raise OracleError("Sort: all inputs must have same dimensions")
+        rank = ins[0].ndim
+        ax = axis + rank if axis < 0 else axis
+        if ax < 0 or ax >= rank:
+            raise OracleError(f"Sort: axis {axis} out of range for rank {rank}")
+        moved = [np.moveaxis(v, ax, -1) for v in ins]
+        outs = [np.empty_like(m) for m in moved]
+        n = ins[0].shape[ax]
+        for row in np.ndindex(*moved[0].shape[:-1]):
+            def before(a, b):
+                args = []
+                for m in moved:
+                    args += [m[row][a], m[row][b]]
+                (r,) = comparator(*args)
+                return bool(r)
+            order = sorted(range(n), key=functools.cmp_to_key(lambda a, b: -1 if before(a, b) else (1 if before(b, a) else 0)))
+            for m, o in zip(moved, outs):
+                o[row] = m[row][order]
+        return [np.ascontiguousarray(np.moveaxis(o, -1, ax)) for o in outs]
+
 
 def compare(got: np.ndarray, want: np.ndarray, rtol: float, atol_scale: float = 0.0):
     """Returns (ok, max_violation).  Float rule: |got-want| <= rtol*|want| + atol, atol = atol_scale * rtol * rms(want)

@@ -72,6 +72,70 @@ def _shape(f, dtype_name, *dims):
     return _Shape(_CODE[dtype_name], dims)
 
 
+def closure(f, param_shapes, body):
+    """body(c, *params) -> outputs, as a closure of function f (the cond / body of While, a branch of If, Sort's comparator):
+    a Function.Closure() with its Parameters and Return on the backend, a callable on the oracle."""
+    if hasattr(f, "MakeClosure"):
+        return f.MakeClosure(param_shapes, body)
+    c = f.Closure()
+    params = [c.Parameter(f"p{i}", s) for i, s in enumerate(param_shapes)]
+    c.Return(list(body(c, *params)), None)
+    return c
+
+
+def named_function(f, name, param_shapes, body):
+    """The same for Builder.NewFunction(name), the target of Call."""
+    if hasattr(f, "MakeClosure"):
+        return f.MakeClosure(param_shapes, body)
+    c = f.builder.NewFunction(name)
+    params = [c.Parameter(f"p{i}", s) for i, s in enumerate(param_shapes)]
+    c.Return(list(body(c, *params)), None)
+    return c
+
+
+def _const(f, value, dtype_name):
+    return f.Constant(np.array([value], dtype=dtype_name))
+
+
+def _while_sum(f, _dummy):
+    s = _shape(f, I32)
+    cond = closure(f, [s, s], lambda c, counter, total: [c.LessOrEqual(counter, _const(c, 10, I32))])
+    body = closure(f, [s, s], lambda c, counter, total: [c.Add(counter, _const(c, 1, I32)), c.Add(total, counter)])
+    return f.While(cond, body, _const(f, 1, I32), _const(f, 0, I32))[1]
+
+
+def _while_factorial(f, _dummy):
+    s = _shape(f, I32)
+    cond = closure(f, [s, s], lambda c, n, result: [c.GreaterThan(n, _const(c, 1, I32))])
+    body = closure(f, [s, s], lambda c, n, result: [c.Sub(n, _const(c, 1, I32)), c.Mul(result, n)])
+    return f.While(cond, body, _const(f, 5, I32), _const(f, 1, I32))[1]
+
+
+def _if_const(f, x):
+    pred = f.GreaterThan(x, _const(f, 5, F32))
+    return f.If(pred, closure(f, [], lambda c: [_const(c, 1, F32)]), closure(f, [], lambda c: [_const(c, -1, F32)]))[0]
+
+
+def _if_captured(f, x):
+    factor = _const(f, 10, F32)
+    pred = f.GreaterThan(x, _const(f, 0, F32))
+    return f.If(pred, closure(f, [], lambda c: [c.Mul(x, factor)]), closure(f, [], lambda c: [c.Neg(c.Mul(x, factor))]))[0]
+
+
+def _sort(descending):
+    def build(f, x):
+        s = _shape(f, F32)
+        comparator = closure(f, [s, s], lambda c, a, b: [c.GreaterThan(a, b) if descending else c.LessThan(a, b)])
+        return f.Sort(comparator, 0, True, x)[0]
+    return build
+
+
+def _call_add(f, _dummy):
+    s = _shape(f, F32)
+    add = named_function(f, "add", [s, s], lambda c, a, b: [c.Add(a, b)])
+    return f.Call(add, _const(f, 10, F32), _const(f, 32, F32))[0]
+
+
 CASES = [
     Case("Add", "mpsgraph/gomlx/mpsgraph_test.go:223-238",
          [_a([1, 2, 3, 4, 5, 6], shape=(2, 3)), _a([10, 20, 30, 40, 50, 60], shape=(2, 3))],
@@ -234,6 +298,15 @@ CASES = [
          [_a([0, 10, 0, 10], shape=(2, 2)), _a([2, 3]), _a([1, -1])],
          lambda f, op, sc, off: list(f.BatchNormForTraining(op, sc, off, 1e-5, 1)[:2]),
          [_a([1, -1, 1, -1], shape=(2, 2)), _a([0, 10])], tol=1e-3),
+    # control flow over closures
+    Case("While sum 1..10", "mpsgraph/gomlx/mpsgraph_test.go:3379-3410", [_a(0, I32)], _while_sum, _a(55, I32), tol=0),
+    Case("While factorial 5!", "mpsgraph/gomlx/mpsgraph_test.go:3412-3442", [_a(0, I32)], _while_factorial, _a(120, I32), tol=0),
+    Case("If true branch (10 > 5)", "mpsgraph/gomlx/mpsgraph_test.go:3449-3472", [_a(10.0)], _if_const, _a(1.0), tol=0),
+    Case("If false branch (3 > 5)", "mpsgraph/gomlx/mpsgraph_test.go:3474-3497", [_a(3.0)], _if_const, _a(-1.0), tol=0),
+    Case("If with captured values (3 * 10)", "mpsgraph/gomlx/mpsgraph_test.go:3499-3523", [_a(3.0)], _if_captured, _a(30.0), tol=0),
+    Case("Sort ascending", "mpsgraph/gomlx/mpsgraph_test.go:3529-3538", [_a([5, 2, 8, 1, 9, 3])], _sort(False), _a([1, 2, 3, 5, 8, 9]), tol=0),
+    Case("Sort descending", "mpsgraph/gomlx/mpsgraph_test.go:3540-3549", [_a([5, 2, 8, 1, 9, 3])], _sort(True), _a([9, 8, 5, 3, 2, 1]), tol=0),
+    Case("Call add(10, 32)", "mpsgraph/gomlx/mpsgraph_test.go:3556-3578", [_a(0.0)], _call_add, _a(42.0), tol=0),
 ]
 
 # Shape-only expectations of the reference's tests (the test asserts a shape or finiteness, not values).
