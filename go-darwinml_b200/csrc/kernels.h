@@ -253,6 +253,9 @@ struct GemmParams {
 Status gemm(Device* dev, const GemmParams& p);
 // The tensor-core path alone: *taken is false (and nothing is launched) when the problem is outside its rules.
 Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken);
+// True when the tensor-core path writes this dense 16-bit result, whose rows are not a whole number of 16-byte vectors,
+// with aligned vector stores all the same (pointers aside: shapes, majors and what is fused decide).
+bool gemm_tcgen05_ragged_rows(const GemmParams& p, bool has_bias, bool has_residual);
 
 // ------------------------------------------------------------------ rope ---
 // y[r, j] = round(round(x[r, j] * c[r, j]) + round(x[r, j ^ half] * s[r, j])) over rows of `cols` elements made of heads of

@@ -99,8 +99,51 @@ struct TcArgs {
   // below 0.3 of the tolerance at every K (better than a plain fp32 FFMA GEMM, which is at 1.8 at K = 8192).
   int num_chunks, chunk_blocks;
   int vec_store;    // rows of C start 16-byte aligned and N is a multiple of the vector width
+  // Ragged rows (16-bit C, dense, N not a multiple of 8, M a multiple of 8): row r of C starts (r * N) mod 8 elements off
+  // the 16-byte grid, the same for every row of one residue class r mod 8.  The problem is cut into 8 classes; a class's
+  // tiles take every 8th row of A (a 4-D map) and a column window shifted left by the class's offset, so every vector of
+  // a tile is aligned in memory and only the first and last vector of a ROW are partial (written element by element).
+  // m-tile index = 8 * (tile within the class) + class.  rag_q = N mod 8.
+  int rag, rag_q;
   int* err_flag;
 };
+
+// Where a tile's rows live in C.  Plain: batch b, pitch ldc.  Ragged rows: class `kres` of batch b, pitch 8 N, base moved
+// left by the class's shift so that the tile's column j is element j of a 16-byte aligned row image.
+template <typename OutT>
+struct CView {
+  OutT* base;
+  int64_t ld, rows, col_lo, col_hi;   // valid tile columns are [col_lo, col_hi)
+};
+template <typename OutT>
+__device__ __forceinline__ CView<OutT> c_view(const TcArgs& g, int b, int kres) {
+  CView<OutT> v;
+  if (g.rag) {
+    const int64_t shift = (kres * g.rag_q) & 7;
+    v.base = reinterpret_cast<OutT*>(g.c) + ((int64_t)b * g.M + kres) * g.N - shift;
+    v.ld = 8 * g.N;
+    v.rows = g.M >> 3;
+    v.col_lo = shift;
+    v.col_hi = g.N + shift;
+  } else {
+    v.base = reinterpret_cast<OutT*>(g.c) + (int64_t)b * g.M * g.ldc;
+    v.ld = g.ldc;
+    v.rows = g.M;
+    v.col_lo = 0;
+    v.col_hi = g.N;
+  }
+  return v;
+}
+
+// The valid elements of a 16-byte vector that straddles the start or the end of a ragged row, as 2-byte stores.
+template <typename OutT>
+__device__ __forceinline__ void store_partial_vector(OutT* dst, uint4 q, int64_t col, int64_t col_lo, int64_t col_hi) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+  uint16_t* d16 = reinterpret_cast<uint16_t*>(dst);
+#pragma unroll
+  for (int e = 0; e < 8; ++e)
+    if (col + e >= col_lo && col + e < col_hi) d16[e] = (uint16_t)(w[e >> 1] >> (16 * (e & 1)));
+}
 
 // plane of A / B used by each of the six partial products of the 3-way split,
 // smallest terms first: a1*b3, a3*b1, a2*b2, a1*b2, a2*b1, a1*b1
@@ -226,16 +269,18 @@ __device__ __forceinline__ uint32_t combine_chunk_word(const TcArgs& g, uint32_t
 }
 
 template <typename OutT>
-__device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem_acc, int64_t row0, int64_t n0, int b, int quarter, int chalf,
-                                                  int lane, float* stage_f, int chunk) {
+__device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem_acc, int64_t row0, int64_t n0, int b, int kres, int quarter,
+                                                  int chalf, int lane, float* stage_f, int chunk) {
   using Tr = OutTraits<OutT>;
   constexpr int CPW = Tr::kColsPerWord;
   constexpr int STEP_COLS = 32 * CPW;          // columns per step: 32 words per row
   uint32_t* stage = reinterpret_cast<uint32_t*>(stage_f);
   const uint32_t taddr = tmem_acc + ((uint32_t)(quarter * 32) << 16);
   const int64_t row_base = row0 + quarter * 32;
-  OutT* cbase = reinterpret_cast<OutT*>(g.c) + ((int64_t)b * g.M + row_base) * g.ldc;
-  const OutT* rbase = g.residual ? reinterpret_cast<const OutT*>(g.residual) + ((int64_t)b * g.M + row_base) * g.ldc : nullptr;
+  const CView<OutT> cv = c_view<OutT>(g, b, kres);
+  const int64_t ld = cv.ld, c_rows = cv.rows, col_hi = cv.col_hi;
+  OutT* cbase = cv.base + row_base * ld;
+  const OutT* rbase = g.residual ? reinterpret_cast<const OutT*>(g.residual) + ((int64_t)b * g.M + row_base) * g.ldc : nullptr;   // never with ragged rows
   // chunked fp32 accumulation (see TcArgs::num_chunks): this drain adds its chunk to what C holds; only the last chunk
   // applies bias, activation and residual, and it does so in the write-out loop, after the sum is complete
   const bool chunked = CPW == 1 && g.num_chunks > 1;
@@ -244,7 +289,7 @@ __device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem
 #pragma unroll 1
   for (int step = chalf * (BN / 2 / STEP_COLS); step < (chalf + 1) * (BN / 2 / STEP_COLS); ++step) {
     const int64_t col0 = n0 + step * STEP_COLS;
-    if (col0 >= g.N) break;  // uniform across the warp
+    if (col0 >= col_hi) break;  // uniform across the warp
     const int64_t col = col0 + (int64_t)wg * CPW;
     // The residual block of this step is fetched first, in the write-out layout, so that its latency hides under the
     // TMEM reads and the activation arithmetic (loads issued after the stores below could not be hoisted: the
@@ -257,7 +302,7 @@ __device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem
 #pragma unroll
         for (int pass = 0; pass < 8; ++pass) {
           const int rr = pass * 4 + (lane >> 3);
-          rv[pass] = (row_base + rr < g.M && col < g.N) ? ld_c16(cbase + (int64_t)rr * g.ldc + col)
+          rv[pass] = (row_base + rr < c_rows && col < col_hi) ? ld_c16(cbase + (int64_t)rr * ld + col)
                                                          : make_uint4(0, 0, 0, 0);
         }
       }
@@ -306,7 +351,7 @@ __device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem
           const int rl = pass * 4 + (lane >> 3);
           const int rr = round * 16 + rl;
           uint4 q = *reinterpret_cast<const uint4*>(stage + rl * EPI_PITCH + wg);
-          if (row_base + rr < g.M && col < g.N) {
+          if (row_base + rr < c_rows && col < col_hi) {
             if (chunked) {
               const uint4 rq = first_chunk ? make_uint4(0, 0, 0, 0) : rv[round * 4 + pass];
               const float* re = (last_chunk && rbase) ? reinterpret_cast<const float*>(rbase) + (int64_t)rr * g.ldc + col : nullptr;
@@ -321,8 +366,9 @@ __device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem
               q.z = add_residual_word<OutT>(q.z, rq.z, g.residual_mul);
               q.w = add_residual_word<OutT>(q.w, rq.w, g.residual_mul);
             }
-            const int64_t off = (int64_t)rr * g.ldc + col;
-            *reinterpret_cast<uint4*>(cbase + off) = q;
+            const int64_t off = (int64_t)rr * ld + col;
+            if (CPW == 2 && g.rag && (col < cv.col_lo || col + 8 > col_hi)) store_partial_vector<OutT>(cbase + off, q, col, cv.col_lo, col_hi);
+            else *reinterpret_cast<uint4*>(cbase + off) = q;
             // the same vector to every other rank's copy: plain stores to peer-mapped memory (NVLink)
             for (int x = 0; x < g.num_c_extra; ++x)
               *reinterpret_cast<uint4*>(reinterpret_cast<OutT*>(g.c_extra[x]) + ((int64_t)b * g.M + row_base) * g.ldc + off) = q;
@@ -388,8 +434,8 @@ __device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem
 // Same data path as above with narrower rows: 16 rows x 16 words per staging round (20-word pitch: conflict-free 16-byte
 // accesses), written back 8 rows x 64 contiguous bytes per store instruction.
 template <typename OutT>
-__device__ __forceinline__ void drain_accumulator_narrow(const TcArgs& g, uint32_t tmem_acc, int64_t row0, int64_t n0, int b, int quarter,
-                                                         int cq, int lane, uint32_t* stage, int chunk) {
+__device__ __forceinline__ void drain_accumulator_narrow(const TcArgs& g, uint32_t tmem_acc, int64_t row0, int64_t n0, int b, int kres,
+                                                         int quarter, int cq, int lane, uint32_t* stage, int chunk) {
   using Tr = OutTraits<OutT>;
   constexpr int CPW = Tr::kColsPerWord;
   constexpr int SUB_COLS = 16 * CPW;            // columns per sub-step: 16 words per row
@@ -397,23 +443,26 @@ __device__ __forceinline__ void drain_accumulator_narrow(const TcArgs& g, uint32
   constexpr int SUBS = WARP_COLS / SUB_COLS;
   const uint32_t taddr = tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(cq * WARP_COLS);
   const int64_t row_base = row0 + quarter * 32;
-  OutT* cbase = reinterpret_cast<OutT*>(g.c) + ((int64_t)b * g.M + row_base) * g.ldc;
-  const OutT* rbase = g.residual ? reinterpret_cast<const OutT*>(g.residual) + ((int64_t)b * g.M + row_base) * g.ldc : nullptr;
+  const CView<OutT> cv = c_view<OutT>(g, b, kres);
+  const int64_t ld = cv.ld, col_hi = cv.col_hi;
+  OutT* cbase = cv.base + row_base * ld;
+  const OutT* rbase = g.residual ? reinterpret_cast<const OutT*>(g.residual) + ((int64_t)b * g.M + row_base) * g.ldc : nullptr;   // never with ragged rows
   const bool chunked = CPW == 1 && g.num_chunks > 1;   // fp32 chunked accumulation, as in drain_accumulator
   const bool first_chunk = chunk == 0, last_chunk = chunk == g.num_chunks - 1;
   const int wg = (lane & 3) * 4;                // write-out: this lane's 4 words of a 16-word row
   const int rsub = lane >> 2;                   // write-out: row within a pass of 8 rows
   // per-store work is kept to a pointer increment and a 32-bit compare: the epilogue is bound by instruction issue
-  const int rows_left = (int)((g.M - row_base) < 32 ? (g.M - row_base) : 32);
-  const int64_t pass_stride = 8 * g.ldc;
+  const int rows_left = (int)((cv.rows - row_base) < 32 ? (cv.rows - row_base) : 32);
+  const int64_t pass_stride = 8 * ld;
 #pragma unroll 1
   for (int sub = 0; sub < SUBS; ++sub) {
     const int64_t col0 = n0 + cq * WARP_COLS + sub * SUB_COLS;
-    if (col0 >= g.N) break;  // uniform across the warp
+    if (col0 >= col_hi) break;  // uniform across the warp
     const int64_t col = col0 + (int64_t)wg * CPW;
     // the residual block of this sub-step, fetched first in the write-out layout (latency hides under the TMEM read)
-    const bool col_ok = col < g.N;
-    const int64_t first = (int64_t)rsub * g.ldc + col;   // element offset of this lane's vector in pass 0
+    const bool col_ok = col < col_hi;
+    const int64_t first = (int64_t)rsub * ld + col;   // element offset of this lane's vector in pass 0
+    const bool partial = CPW == 2 && g.rag && (col < cv.col_lo || col + 8 > col_hi);   // the vector straddles an end of a ragged row
     uint4 rv[4];
     if (chunked) {
       if (!first_chunk && g.vec_store) {
@@ -477,7 +526,8 @@ __device__ __forceinline__ void drain_accumulator_narrow(const TcArgs& g, uint32
               q.w = add_residual_word<OutT>(q.w, rq.w, g.residual_mul);
             }
             const int64_t off = first + (round * 2 + pass) * pass_stride;
-            *reinterpret_cast<uint4*>(cbase + off) = q;
+            if (partial) store_partial_vector<OutT>(cbase + off, q, col, cv.col_lo, col_hi);
+            else *reinterpret_cast<uint4*>(cbase + off) = q;
             if (g.num_c_extra > 0) {
               // the same vector to every other rank's copy: plain stores to peer-mapped memory (NVLink)
               for (int x = 0; x < g.num_c_extra; ++x)
@@ -581,7 +631,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       for (int64_t t = blockIdx.x; t < g.total_tiles && ok; t += gridDim.x) {
         int b, m_t, n_t;
         tile_coords(g, t, &b, &m_t, &n_t);
-        const int m0 = m_t * BM, n0 = n_t * BN;
+        int kres = 0, shift = 0;
+        if (g.rag) { kres = m_t & 7; m_t >>= 3; shift = (kres * g.rag_q) & 7; }
+        const int m0 = m_t * BM, n0 = n_t * BN - shift;   // ragged rows: the class's column window starts `shift` columns early
+        // coordinates 3 and 4 of A: (batch, plane), or with ragged rows (row class, batch)
+        const int a3 = g.rag ? kres : b, a4_rag = b;
         for (int chunk = 0; chunk < NCH && ok; ++chunk) {
         const int kb_begin = chunk * CHB;
         const int kb_end = kb_begin + CHB < g.k_blocks ? kb_begin + CHB : g.k_blocks;
@@ -595,7 +649,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             mbar_expect_tx(&full[s], STAGE_BYTES);
             if (g.a_kmajor) {
               // box {64 k, 128 m}: 128 rows of 128 bytes
-              tma_load_4d(sa, &tm_a, &full[s], k0, m0, b, pa);
+              tma_load_4d(sa, &tm_a, &full[s], k0, m0, a3, g.rag ? a4_rag : pa);
             } else {
               // two boxes {64 m, 64 k}: 64 k-rows of 128 bytes each, one box per 64-wide block of M
               tma_load_4d(sa, &tm_a, &full[s], m0, k0, b, pa);
@@ -668,13 +722,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     for (int64_t t = blockIdx.x; t < g.total_tiles && ok; t += gridDim.x) {
       int b, m_t, n_t;
       tile_coords(g, t, &b, &m_t, &n_t);
+      int kres = 0;
+      if (g.rag) { kres = m_t & 7; m_t >>= 3; }
       for (int chunk = 0; chunk < NCH && ok; ++chunk, ++local_tile) {
       const int acc = local_tile & 1;
       const uint32_t acc_phase = (local_tile >> 1) & 1;
       const bool landed = mbar_wait(&acc_full[acc], acc_phase, err, 4);
       if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }  // the warp leaves together: tcgen05.ld is warp-collective
       tc_fence_after();
-      drain_accumulator_narrow<OutT>(g, tmem_base + acc * BN, (int64_t)m_t * BM, (int64_t)n_t * BN, b, quarter, (warp - 2) >> 2, lane,
+      drain_accumulator_narrow<OutT>(g, tmem_base + acc * BN, (int64_t)m_t * BM, (int64_t)n_t * BN, b, kres, quarter, (warp - 2) >> 2, lane,
                                      epi_stage + (warp - 2) * S_EPI_STAGE_WORDS, chunk);
       tc_fence_before();
       __syncwarp();
@@ -768,14 +824,18 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
       struct Cursor {
         int64_t t;        // global tile index
         int b, m0, n0;    // this CTA's rows of A / columns of B in that tile
+        int kres;         // ragged rows: the tile's row class
         int seg, kb;
         int chunk, kb_end;   // the chunk of the tile's K range being loaded and its last k-block + 1
       };
       auto place = [&](Cursor& c) {
         int m_t, n_t;
         pair_tile_coords(g, c.t, &c.b, &m_t, &n_t);
+        int shift = 0;
+        c.kres = 0;
+        if (g.rag) { c.kres = m_t & 7; m_t >>= 3; shift = (c.kres * g.rag_q) & 7; }
         c.m0 = m_t * 2 * BM + (int)rank * BM;
-        c.n0 = n_t * BN + (int)rank * P_BN_HALF;
+        c.n0 = n_t * BN + (int)rank * P_BN_HALF - shift;
       };
       auto chunk_range = [&](Cursor& c) {
         c.kb = c.chunk * CHB;
@@ -801,7 +861,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         const int k0 = c.kb * BK;
         unsigned char* sb = sa + A_STAGE_BYTES;
         if (g.a_kmajor) {
-          tma_load_4d_pair(sa, &tm_a, bar, k0, c.m0, c.b, pa);
+          tma_load_4d_pair(sa, &tm_a, bar, k0, c.m0, g.rag ? c.kres : c.b, g.rag ? c.b : pa);
         } else {
           tma_load_4d_pair(sa, &tm_a, bar, c.m0, k0, c.b, pa);
           tma_load_4d_pair(sa + 8192, &tm_a, bar, c.m0 + 64, k0, c.b, pa);
@@ -814,7 +874,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         }
       };
       if (pair < g.total_tiles) {
-        Cursor ld{pair, 0, 0, 0, 0, 0, 0, 0};
+        Cursor ld{pair, 0, 0, 0, 0, 0, 0, 0, 0};
         place(ld);
         chunk_range(ld);
         // full[s] of the leader, as a cluster address: the same offset for every stage
@@ -886,13 +946,15 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
     for (int64_t t = pair; t < g.total_tiles && ok; t += num_pairs) {
       int b, m_t, n_t;
       pair_tile_coords(g, t, &b, &m_t, &n_t);
+      int kres = 0;
+      if (g.rag) { kres = m_t & 7; m_t >>= 3; }
       for (int chunk = 0; chunk < NCH && ok; ++chunk, ++local_tile) {
         const int acc = local_tile & 1;
         const uint32_t acc_phase = (local_tile >> 1) & 1;
         const bool landed = mbar_wait_cluster(&acc_full[acc], acc_phase, err, 4);
         if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }
         tc_fence_after();
-        drain_accumulator<OutT>(g, tmem_base + acc * BN, (int64_t)m_t * 2 * BM + (int64_t)rank * BM, (int64_t)n_t * BN, b, quarter,
+        drain_accumulator<OutT>(g, tmem_base + acc * BN, (int64_t)m_t * 2 * BM + (int64_t)rank * BM, (int64_t)n_t * BN, b, kres, quarter,
                                 (warp - 2) >> 2, lane, epi_stage + (warp - 2) * EPI_STAGE_FLOATS, chunk);
         tc_fence_before();
         __syncwarp();
@@ -949,6 +1011,17 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 
 }  // namespace
 
+// Ragged rows (see TcArgs::rag): a dense 16-bit result whose row length is not a multiple of 8, written with aligned
+// 16-byte vectors all the same.  Needs both operands K-major (the shifted column window moves B's N coordinate, which
+// must not be the contiguous one; A's rows are taken with a stride of 8), whole classes (M a multiple of 8), classes
+// of at least one full tile, and nothing fused that is indexed by column or laid out like C.
+bool gemm_tcgen05_ragged_rows(const GemmParams& p, bool has_bias, bool has_residual) {
+  const bool is16 = p.dtype == B200_BFLOAT16 || p.dtype == B200_FLOAT16;
+  static const bool on = []() { const char* v = getenv("B200MLX_GEMM_RAGGED"); return !(v && v[0] == '0'); }();
+  return on && is16 && p.a_k_major && p.b_k_major && p.m % 8 == 0 && p.m >= 8 * BM && p.n % 8 != 0 && p.k % 8 == 0 && !has_bias &&
+         !has_residual && p.num_c_extra == 0 && (p.ldc <= 0 || p.ldc == p.n) && p.a_batch_stride < 0 && p.b_batch_stride < 0;
+}
+
 Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
   *taken = false;
   const bool is16 = p.dtype == B200_BFLOAT16 || p.dtype == B200_FLOAT16;
@@ -964,7 +1037,7 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
   // tiny problems are latency-bound either way; leave them to the SIMT kernel
   if ((double)p.batch * p.m * p.n * p.k < 64.0 * 64.0 * 64.0) return Status::OK();
   // tile coordinates are computed in 32-bit arithmetic on the device
-  if ((double)p.batch * (double)((p.m + BM - 1) / BM) * (double)((p.n + BN - 1) / BN) >= 2147483648.0) return Status::OK();
+  if ((double)p.batch * (double)((p.m + BM - 1) / BM + 8) * (double)((p.n + 7 + BN - 1) / BN) >= 2147483648.0) return Status::OK();
   *taken = true;
 
   B200_TRY(dev->MakeCurrent());
@@ -994,14 +1067,19 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
   // Pairs pay off once a tile's main loop is long enough to hide the cross-CTA hand-offs (measured: K = 512 is 8 % slower on
   // pairs, K >= 4096 is 5 - 10 % faster) and there are enough tiles to fill the GPU either way.
   const int64_t k_iters = (p.k + BK - 1) / BK * (is32 ? 6 : 1);
-  const int64_t pair_tiles = ((p.m + 2 * BM - 1) / (2 * BM)) * ((p.n + BN - 1) / BN) * p.batch;
-  const bool use_pair = pair_allowed && p.m > BM && (pair_mode == 2 || (k_iters >= 16 && pair_tiles >= 32));
+  const bool rag = gemm_tcgen05_ragged_rows(p, p.bias != nullptr, p.residual != nullptr) && aligned16(p.c);
+  const int64_t m_rows = rag ? p.m / 8 : p.m;            // rows of one tile grid (a row class, or all of M)
+  const int64_t n_cols = rag ? p.n + 7 : p.n;            // its columns (a class's window may start up to 7 columns early)
+  const int64_t grids = rag ? 8 : 1;
+  const int64_t pair_tiles = ((m_rows + 2 * BM - 1) / (2 * BM)) * ((n_cols + BN - 1) / BN) * p.batch * grids;
+  const bool use_pair = pair_allowed && m_rows > BM && (pair_mode == 2 || (k_iters >= 16 && pair_tiles >= 32));
 
   CUtensorMap tm_a, tm_b;
   Status s;
   const bool f16 = p.dtype == B200_FLOAT16;
   const int b_box = use_pair ? P_BN_HALF : BN;
-  if (p.a_k_major) s = make_operand_map(&tm_a, a, f16, p.k, p.m, p.k, p.batch, p.m * p.k, planes, planes > 1 ? a_plane_stride : p.m * p.k * p.batch, BM);
+  if (rag) s = make_operand_map(&tm_a, a, f16, p.k, p.m / 8, 8 * p.k, 8, p.k, p.batch, p.m * p.k, BM);   // {K, row in class, class, batch}
+  else if (p.a_k_major) s = make_operand_map(&tm_a, a, f16, p.k, p.m, p.k, p.batch, p.m * p.k, planes, planes > 1 ? a_plane_stride : p.m * p.k * p.batch, BM);
   else s = make_operand_map(&tm_a, a, f16, p.m, p.k, p.m, p.batch, p.m * p.k, planes, planes > 1 ? a_plane_stride : p.m * p.k * p.batch, 64);
   if (s.ok()) {
     if (p.b_k_major) s = make_operand_map(&tm_b, b, f16, p.k, p.n, p.k, p.batch, p.n * p.k, planes, planes > 1 ? b_plane_stride : p.n * p.k * p.batch, b_box);
@@ -1020,8 +1098,10 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
   g.in_f16 = f16 ? 1 : 0;
   g.out_dtype = p.dtype;
   const int tile_rows = use_pair ? 2 * BM : BM;
-  g.tiles_m = (int)((p.m + tile_rows - 1) / tile_rows);
-  g.tiles_n = (int)((p.n + BN - 1) / BN);
+  g.tiles_m = (int)((m_rows + tile_rows - 1) / tile_rows * grids);   // ragged rows: 8 * (tile within the class) + class
+  g.tiles_n = (int)((n_cols + BN - 1) / BN);
+  g.rag = rag ? 1 : 0;
+  g.rag_q = (int)(p.n & 7);
   g.total_tiles = (int64_t)g.tiles_m * g.tiles_n * p.batch;
   g.k_blocks = (int)((p.k + BK - 1) / BK);
   g.segs = is32 ? 6 : 1;
@@ -1030,7 +1110,7 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
   g.num_chunks = (is32 && chunk_cap > 0) ? (g.k_blocks + chunk_cap - 1) / chunk_cap : 1;
   g.chunk_blocks = (g.k_blocks + g.num_chunks - 1) / g.num_chunks;
   const int out_vec = is32 ? 4 : 8;
-  g.vec_store = (g.ldc % out_vec == 0 && g.ldc >= (p.n + out_vec - 1) / out_vec * out_vec && aligned16(p.c) && aligned16(p.residual)) ? 1 : 0;
+  g.vec_store = (rag || (g.ldc % out_vec == 0 && g.ldc >= (p.n + out_vec - 1) / out_vec * out_vec && aligned16(p.c) && aligned16(p.residual))) ? 1 : 0;
   if (p.num_c_extra > 0) {
     bool ok = g.vec_store != 0 && !is32;
     for (int x = 0; x < p.num_c_extra; ++x) ok = ok && aligned16(p.c_extra[x]);

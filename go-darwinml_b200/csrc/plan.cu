@@ -1085,15 +1085,18 @@ class Planner {
     const int64_t es_out = dtype_size(x->dtype);
     const int64_t vec_out = 16 / es_out;
     const bool float_out = x->dtype == B200_FLOAT32 || x->dtype == B200_BFLOAT16 || x->dtype == B200_FLOAT16;
-    const bool pad_rows = float_out && !residual && N % vec_out != 0 && B * M * N * es_out >= (int64_t)(8 << 20);
-    const int64_t ldc = pad_rows ? (N + vec_out - 1) / vec_out * vec_out : 0;
-    const int gemm_out = pad_rows ? NewTemp(B * M * ldc * es_out + 16) : out_slot;
     k::GemmParams gp;
-    gp.ldc = ldc;
     gp.batch = B; gp.m = M; gp.n = N; gp.k = K;
     gp.a_k_major = a_major == 1;
     gp.b_k_major = b_major == 1;
     gp.dtype = x->dtype;
+    // ... unless the tensor-core kernel can write the ragged rows with aligned vectors itself (row classes: both operands
+    // K-major, M a multiple of 8, nothing fused)
+    const bool ragged_direct = k::gemm_tcgen05_ragged_rows(gp, bias != nullptr, residual != nullptr);
+    const bool pad_rows = float_out && !residual && !ragged_direct && N % vec_out != 0 && B * M * N * es_out >= (int64_t)(8 << 20);
+    const int64_t ldc = pad_rows ? (N + vec_out - 1) / vec_out * vec_out : 0;
+    const int gemm_out = pad_rows ? NewTemp(B * M * ldc * es_out + 16) : out_slot;
+    gp.ldc = ldc;
     gp.activation = (int)x->fa[0];
     gp.residual_op = (has_residual && x->fa[1] == 2.0) ? 1 : 0;
     const int bias_slot = bias ? SlotOf(bias) : -1;
@@ -1102,6 +1105,7 @@ class Planner {
     st.desc = strfmt("gemm[B=%lld M=%lld N=%lld K=%lld %s a:%s b:%s%s%s act=%d]", (long long)B, (long long)M, (long long)N, (long long)K,
                      dtype_name(x->dtype), gp.a_k_major ? "MK" : "KM", gp.b_k_major ? "NK" : "KN", bias ? " bias" : "",
                      residual ? (gp.residual_op ? " *residual" : " +residual") : "", gp.activation);
+    if (ragged_direct) st.desc.insert(st.desc.size() - 1, " ragged-rows");
     st.reads = {a_slot, b_slot};
     if (bias) st.reads.push_back(bias_slot);
     if (residual) st.reads.push_back(res_slot);

@@ -132,6 +132,26 @@ def test_dot_general_config_sizes_sampled_rows(b200, backend, n, form, dtype, rt
         assert ok, (bi, viol)
 
 
+@pytest.mark.parametrize("m,n,k,batch", [(1024, 1001, 768, 1), (1024, 50257, 64, 1), (2048, 1003, 1024, 2), (1024, 254, 256, 3), (3072, 777, 128, 1),
+                                          (1032, 1006, 512, 1), (1024, 2044, 2048, 2)],
+                         ids=["single-q1", "vocab-q1", "pair-q3-batched", "q6-narrower-than-a-tile", "q1-three-tiles-per-class", "m-ragged-q6",
+                              "pair-q4"])
+@pytest.mark.parametrize("dtype", [BF16, np.float16], ids=["bf16", "f16"])
+def test_dot_general_rows_not_a_multiple_of_the_vector_width(b200, backend, m, n, k, batch, dtype):
+    # a dense 16-bit result with N % 8 != 0: the tensor-core kernel cuts the rows into 8 classes (row mod 8) and shifts each
+    # class's column window so that every store is an aligned vector; the first and last vector of a row go out by element
+    rng = np.random.default_rng(m + n)
+    a = _normal(rng, (batch, m, k), dtype)
+    w = _normal(rng, (batch, n, k), dtype)   # [B, N, K]: what x @ table^T contracts
+    (got,), plan = run_backend(b200, backend, lambda f, x, y: f.DotGeneral(x, [2], [0], y, [2], [0]), [a, w], describe=True)
+    assert "ragged-rows" in plan and "pack" not in plan, plan
+    assert got.shape == (batch, m, n)
+    for bi in range(batch):
+        want = (a[bi].astype(np.float64) @ w[bi].astype(np.float64).T).astype(dtype)
+        ok, viol = compare(got[bi], want, 2e-2, 1.0)
+        assert ok, (bi, viol)
+
+
 # -------------------------------------------------------------------------- attention ---
 @pytest.mark.parametrize("causal", [True, False], ids=["causal", "full"])
 def test_fused_attention_llama_shape_sampled_heads(b200, backend, causal):
