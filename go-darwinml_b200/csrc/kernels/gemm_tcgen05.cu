@@ -17,9 +17,10 @@
 //   warp 1     issuer: one lane issues tcgen05.mma (M=128, N=256, K=16 per instruction)
 //              from shared-memory descriptors into a TMEM accumulator; tcgen05.commit
 //              releases ring stages ("empty") and publishes finished accumulators;
-//   warps 2-   epilogue: tcgen05.ld the accumulator (a warp reaches the 32 TMEM lanes of its quarter), add bias,
-//              apply the activation, round, store 16-byte vectors.  Sixteen warps of 64 columns in this kernel
-//              (short K: the epilogue is the critical path), eight of 128 columns in the CTA-pair kernel below.
+//   warps 2-17 epilogue: tcgen05.ld the accumulator (a warp reaches the 32 TMEM lanes of its quarter), add bias,
+//              apply the activation, round, and hand the rows to a TMA tile store (16-bit results with aligned rows) or
+//              write them out through a staging transpose as 16-byte vectors.  Sixteen warps of 64 columns each, in the
+//              single-CTA kernel and in the CTA-pair kernel below: with short K the epilogue is the critical path.
 // TMEM holds two 256-column accumulators, so the epilogue of tile i overlaps the
 // main loop of tile i+1.  Tensor-core bound: flops = 2 * batch * M * N * K.
 //
@@ -57,18 +58,17 @@ constexpr int STAGES = 4;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
 constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr int EPI_PITCH = 36;                 // words per scratch row: 32 + 4, so 16-byte accesses are aligned and conflict-free
-constexpr int EPI_WARPS = 8;                  // two per TMEM lane quarter: one per half of the tile's columns
-constexpr int EPI_STAGE_FLOATS = 16 * EPI_PITCH;  // per epilogue warp: 16 rows x 32 words (a warp stages its rows in two rounds)
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + EPI_WARPS * EPI_STAGE_FLOATS * 4;
-constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;   // producer warp, issuer warp, epilogue warps
 constexpr int TMEM_COLS = 512;
-// the single-CTA kernel: sixteen epilogue warps, four per TMEM lane quarter (64 columns each)
+// sixteen epilogue warps, four per TMEM lane quarter (64 columns each)
 constexpr int S_EPI_WARPS = 16;
 constexpr int S_EPI_PITCH = 20;                      // words per scratch row: 16 + 4
-constexpr int S_EPI_STAGE_WORDS = 16 * S_EPI_PITCH;  // per warp: 16 rows x 16 words
-constexpr int S_SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + S_EPI_WARPS * S_EPI_STAGE_WORDS * 4;
-constexpr int S_NUM_THREADS = 64 + 32 * S_EPI_WARPS;
+// per warp: 32 rows x 16 words (2 KiB), the source box of a tile store {32 columns of 16 bits, 32 rows} with 64-byte
+// swizzle; the write-out through registers uses the first 16 x 20 words of it
+constexpr int S_EPI_STAGE_WORDS = 32 * 16;
+constexpr int S_BAR_BYTES = 1024;   // barriers and the TMEM slot, padded so that the staging area stays 1024-byte aligned
+constexpr int S_SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + S_BAR_BYTES + S_EPI_WARPS * S_EPI_STAGE_WORDS * 4;
+static_assert(S_SMEM_BYTES <= 232448, "single-CTA GEMM: shared memory over the per-block limit");
+constexpr int S_NUM_THREADS = 64 + 32 * S_EPI_WARPS;   // producer warp, issuer warp, epilogue warps
 
 }  // namespace
 
@@ -105,6 +105,9 @@ struct TcArgs {
   // a tile is aligned in memory and only the first and last vector of a ROW are partial (written element by element).
   // m-tile index = 8 * (tile within the class) + class.  rag_q = N mod 8.
   int rag, rag_q;
+  // single-CTA kernel, 16-bit C with aligned rows: the epilogue hands its staged rows to a tile store (tm_c) instead of
+  // reading them back and storing from registers
+  int tma_store;
   int* err_flag;
 };
 
@@ -237,14 +240,6 @@ __device__ __forceinline__ void add_bias_n(const TcArgs& g, int64_t col, float* 
 template <typename OutT>
 __device__ __forceinline__ void add_bias32(const TcArgs& g, int64_t col, float* v) { add_bias_n<OutT, 32>(g, col, v); }
 
-// One epilogue warp drains its 32 TMEM lanes x 128 columns (half `chalf`) of a finished 128 x 256 accumulator: bias,
-// activation, rounding, stores.  row0 is the first row of C held by lane 0 of this CTA's accumulator; `stage` is the
-// warp's 16 x 36 word scratch.
-// A thread holds one ROW of the accumulator, so storing from registers would scatter every store instruction over 32
-// rows (32 cache lines).  Instead the rounded values go through the scratch, 32 words per row at a time (32 fp32 or 64
-// 16-bit columns), 16 rows per round, and are written back transposed: a store instruction covers 4 rows x 128
-// contiguous bytes.  With short K (a GELU layer at K = 768) the epilogue, not the main loop, is the kernel's critical
-// path, which is why eight warps share it.
 // 16 bytes of C read back through the coherent path (never ld.global.nc: the line was written by this kernel)
 __device__ __forceinline__ uint4 ld_c16(const void* p) {
   uint4 q;
@@ -268,174 +263,19 @@ __device__ __forceinline__ uint32_t combine_chunk_word(const TcArgs& g, uint32_t
   return __float_as_uint(v);
 }
 
+// The epilogue of both kernels.  With short K a tile's main loop is no longer than its epilogue, and the epilogue is a
+// chain of dependent instructions (TMEM read, rounding, staging, write-out) that a scheduler with two warps cannot keep
+// issuing: SIXTEEN warps share a CTA's 128 x 256 accumulator, four per TMEM lane quarter, 64 columns each, in sub-steps
+// of 16 words per row (32 16-bit columns or 16 fp32 columns) so that a thread stays under 112 registers.
+// A thread holds one ROW of the accumulator, so storing from registers would scatter every store instruction over 32
+// rows (32 cache lines).  16-bit results with aligned rows go to a 32 x 64-byte staging box per warp and from there to C
+// as one TMA tile store per sub-step (measured on M = 16384, N = 3072: the epilogue alone, K = 64, 54 -> 32 us; a warp's
+// drain of a tile 7100 -> 2800 cycles).  Everything else (fp32 and its chunked accumulation, ragged rows, extra
+// destinations) is staged 16 rows x 16 words at a time (20-word pitch) and written back transposed, 8 rows x 64
+// contiguous bytes per store instruction.
 template <typename OutT>
-__device__ __forceinline__ void drain_accumulator(const TcArgs& g, uint32_t tmem_acc, int64_t row0, int64_t n0, int b, int kres, int quarter,
-                                                  int chalf, int lane, float* stage_f, int chunk) {
-  using Tr = OutTraits<OutT>;
-  constexpr int CPW = Tr::kColsPerWord;
-  constexpr int STEP_COLS = 32 * CPW;          // columns per step: 32 words per row
-  uint32_t* stage = reinterpret_cast<uint32_t*>(stage_f);
-  const uint32_t taddr = tmem_acc + ((uint32_t)(quarter * 32) << 16);
-  const int64_t row_base = row0 + quarter * 32;
-  const CView<OutT> cv = c_view<OutT>(g, b, kres);
-  const int64_t ld = cv.ld, c_rows = cv.rows, col_hi = cv.col_hi;
-  OutT* cbase = cv.base + row_base * ld;
-  const OutT* rbase = g.residual ? reinterpret_cast<const OutT*>(g.residual) + ((int64_t)b * g.M + row_base) * g.ldc : nullptr;   // never with ragged rows
-  // chunked fp32 accumulation (see TcArgs::num_chunks): this drain adds its chunk to what C holds; only the last chunk
-  // applies bias, activation and residual, and it does so in the write-out loop, after the sum is complete
-  const bool chunked = CPW == 1 && g.num_chunks > 1;
-  const bool first_chunk = chunk == 0, last_chunk = chunk == g.num_chunks - 1;
-  const int wg = (lane & 7) * 4;               // write-out: this lane's 4 words of a row
-#pragma unroll 1
-  for (int step = chalf * (BN / 2 / STEP_COLS); step < (chalf + 1) * (BN / 2 / STEP_COLS); ++step) {
-    const int64_t col0 = n0 + step * STEP_COLS;
-    if (col0 >= col_hi) break;  // uniform across the warp
-    const int64_t col = col0 + (int64_t)wg * CPW;
-    // The residual block of this step is fetched first, in the write-out layout, so that its latency hides under the
-    // TMEM reads and the activation arithmetic (loads issued after the stores below could not be hoisted: the
-    // compiler has to assume C and the residual alias).
-    uint4 rv[8];
-    if (chunked) {
-      // what C holds so far, written by this very thread while draining the previous chunk (plain loads: the
-      // non-coherent path could return what the line held before that store)
-      if (!first_chunk && g.vec_store) {
-#pragma unroll
-        for (int pass = 0; pass < 8; ++pass) {
-          const int rr = pass * 4 + (lane >> 3);
-          rv[pass] = (row_base + rr < c_rows && col < col_hi) ? ld_c16(cbase + (int64_t)rr * ld + col)
-                                                         : make_uint4(0, 0, 0, 0);
-        }
-      }
-    } else if (rbase && g.vec_store) {
-#pragma unroll
-      for (int pass = 0; pass < 8; ++pass) {
-        const int rr = pass * 4 + (lane >> 3);
-        rv[pass] = (row_base + rr < g.M && col < g.N) ? __ldg(reinterpret_cast<const uint4*>(rbase + (int64_t)rr * g.ldc + col))
-                                                       : make_uint4(0, 0, 0, 0);
-      }
-    }
-    uint32_t words[32];
-#pragma unroll
-    for (int part = 0; part < CPW; ++part) {
-      uint32_t r[32];
-      tmem_ld32(taddr + step * STEP_COLS + part * 32, r);
-      tmem_ld_wait();
-      float v[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-      if (!chunked) {
-        if (g.bias) add_bias32<OutT>(g, col0 + part * 32, v);
-        apply_activation_n<32, Tr::kFast>(g.activation, v);
-      }
-      if (CPW == 1) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) words[j] = pack_word<OutT>(v[j], 0.f);
-      } else {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) words[part * 16 + j] = pack_word<OutT>(v[2 * j], v[2 * j + 1]);
-      }
-    }
-#pragma unroll
-    for (int round = 0; round < 2; ++round) {
-      // rows [16 * round, +16) of the warp -> scratch, as 16-byte stores (row pitch 36 words: a quarter-warp covers all 32 banks)
-      if ((lane >> 4) == round) {
-#pragma unroll
-        for (int j = 0; j < 32; j += 4)
-          *reinterpret_cast<uint4*>(stage + (lane & 15) * EPI_PITCH + j) = make_uint4(words[j], words[j + 1], words[j + 2], words[j + 3]);
-      }
-      __syncwarp();
-      if (g.vec_store) {
-        // transposed write-out: lane handles 4 words (16 bytes) of row (16 * round + 4 * pass + lane / 8)
-#pragma unroll
-        for (int pass = 0; pass < 4; ++pass) {
-          const int rl = pass * 4 + (lane >> 3);
-          const int rr = round * 16 + rl;
-          uint4 q = *reinterpret_cast<const uint4*>(stage + rl * EPI_PITCH + wg);
-          if (row_base + rr < c_rows && col < col_hi) {
-            if (chunked) {
-              const uint4 rq = first_chunk ? make_uint4(0, 0, 0, 0) : rv[round * 4 + pass];
-              const float* re = (last_chunk && rbase) ? reinterpret_cast<const float*>(rbase) + (int64_t)rr * g.ldc + col : nullptr;
-              q.x = combine_chunk_word(g, q.x, rq.x, first_chunk, last_chunk, col, re);
-              q.y = combine_chunk_word(g, q.y, rq.y, first_chunk, last_chunk, col + 1, re ? re + 1 : nullptr);
-              q.z = combine_chunk_word(g, q.z, rq.z, first_chunk, last_chunk, col + 2, re ? re + 2 : nullptr);
-              q.w = combine_chunk_word(g, q.w, rq.w, first_chunk, last_chunk, col + 3, re ? re + 3 : nullptr);
-            } else if (rbase) {
-              const uint4 rq = rv[round * 4 + pass];
-              q.x = add_residual_word<OutT>(q.x, rq.x, g.residual_mul);
-              q.y = add_residual_word<OutT>(q.y, rq.y, g.residual_mul);
-              q.z = add_residual_word<OutT>(q.z, rq.z, g.residual_mul);
-              q.w = add_residual_word<OutT>(q.w, rq.w, g.residual_mul);
-            }
-            const int64_t off = (int64_t)rr * ld + col;
-            if (CPW == 2 && g.rag && (col < cv.col_lo || col + 8 > col_hi)) store_partial_vector<OutT>(cbase + off, q, col, cv.col_lo, col_hi);
-            else *reinterpret_cast<uint4*>(cbase + off) = q;
-            // the same vector to every other rank's copy: plain stores to peer-mapped memory (NVLink)
-            for (int x = 0; x < g.num_c_extra; ++x)
-              *reinterpret_cast<uint4*>(reinterpret_cast<OutT*>(g.c_extra[x]) + ((int64_t)b * g.M + row_base) * g.ldc + off) = q;
-          }
-        }
-      } else {
-        // Rows of C do not start 16-byte aligned (N is not a multiple of the vector width): a warp writes one row's 32
-        // words per store instruction, 4 bytes per lane.  A 16-bit row that starts on an odd element is 2 bytes off the
-        // word grid: its words are re-cut from neighbouring staged words (funnel shift) and the two end elements go out
-        // as 2-byte stores.  Fully unrolled and predicated: the loads of all 16 rows are independent.
-        // parity of the element index of (row, col0): col0 and ldc * 16 * round contribute nothing when they are even
-        const uint32_t n_odd = (uint32_t)(g.ldc & 1);
-        const uint32_t base_odd = (uint32_t)((((int64_t)b * g.M + row_base + round * 16) * g.ldc + col0) & 1);
-        OutT* crow = cbase + (int64_t)(round * 16) * g.ldc;
-        const OutT* rrow = rbase ? rbase + (int64_t)(round * 16) * g.ldc : nullptr;
-#pragma unroll 4
-        for (int rl = 0; rl < 16; ++rl, crow += g.ldc, rrow += (rbase ? g.ldc : 0)) {
-          if (row_base + round * 16 + rl >= g.M) break;
-          if (CPW == 1) {
-            const int64_t c1 = col0 + lane;
-            if (c1 < g.N) {
-              uint32_t w = stage[rl * EPI_PITCH + lane];
-              if (chunked) {
-                const uint32_t c_old = first_chunk ? 0u : reinterpret_cast<const volatile uint32_t*>(crow)[c1];
-                w = combine_chunk_word(g, w, c_old, first_chunk, last_chunk, c1, (last_chunk && rbase) ? reinterpret_cast<const float*>(rrow) + c1 : nullptr);
-              } else if (rbase) w = add_residual_word<OutT>(w, reinterpret_cast<const uint32_t*>(rrow)[c1], g.residual_mul);
-              reinterpret_cast<uint32_t*>(crow)[c1] = w;
-            }
-          } else {
-            const uint32_t odd = base_odd ^ ((uint32_t)rl & n_odd);
-            const uint32_t w0 = stage[rl * EPI_PITCH + lane];
-            const uint32_t w1 = stage[rl * EPI_PITCH + lane + 1];   // lane 31 reads the pad word: unused
-            uint32_t w = odd ? __funnelshift_r(w0, w1, 16) : w0;     // elements (2 lane + odd, 2 lane + odd + 1)
-            const int64_t c1 = col0 + 2 * lane + odd;
-            uint16_t* c16 = reinterpret_cast<uint16_t*>(crow);
-            const uint16_t* r16 = reinterpret_cast<const uint16_t*>(rrow);
-            const bool pair_ok = c1 + 1 < g.N && !(odd && lane == 31);
-            if (pair_ok) {
-              if (rbase) w = add_residual_word<OutT>(w, (uint32_t)r16[c1] | ((uint32_t)r16[c1 + 1] << 16), g.residual_mul);
-              *reinterpret_cast<uint32_t*>(c16 + c1) = w;     // (row start + 2 lane + odd) is even: 4-byte aligned
-            } else if (c1 < g.N) {
-              uint32_t lo = w & 0xffffu;                      // the last column of the row, or element 63 of an odd row
-              if (rbase) lo = add_residual_word<OutT>(lo, r16[c1], g.residual_mul) & 0xffffu;
-              c16[c1] = (uint16_t)lo;
-            }
-            if (odd && lane == 0 && col0 < g.N) {             // element 0 of an odd row
-              uint32_t lo = w0 & 0xffffu;
-              if (rbase) lo = add_residual_word<OutT>(lo, r16[col0], g.residual_mul) & 0xffffu;
-              c16[col0] = (uint16_t)lo;
-            }
-          }
-        }
-      }
-      __syncwarp();
-    }
-  }
-}
-
-// The single-CTA kernel's epilogue.  That kernel runs the short-K shapes, where a tile's main loop is no longer than
-// its epilogue and the epilogue is a chain of dependent instructions (TMEM read, rounding, staging, write-out) that a
-// scheduler with two warps cannot keep issuing: SIXTEEN warps share a tile, four per TMEM lane quarter, 64 columns each,
-// in sub-steps of 16 words per row (32 16-bit columns or 16 fp32 columns) so that a thread stays under 112 registers.
-// Same data path as above with narrower rows: 16 rows x 16 words per staging round (20-word pitch: conflict-free 16-byte
-// accesses), written back 8 rows x 64 contiguous bytes per store instruction.
-template <typename OutT>
-__device__ __forceinline__ void drain_accumulator_narrow(const TcArgs& g, uint32_t tmem_acc, int64_t row0, int64_t n0, int b, int kres,
-                                                         int quarter, int cq, int lane, uint32_t* stage, int chunk) {
+__device__ __forceinline__ void drain_accumulator_narrow(const TcArgs& g, const CUtensorMap* tm_c, uint32_t tmem_acc, int64_t row0, int64_t n0,
+                                                         int b, int kres, int quarter, int cq, int lane, uint32_t* stage, int chunk) {
   using Tr = OutTraits<OutT>;
   constexpr int CPW = Tr::kColsPerWord;
   constexpr int SUB_COLS = 16 * CPW;            // columns per sub-step: 16 words per row
@@ -464,7 +304,15 @@ __device__ __forceinline__ void drain_accumulator_narrow(const TcArgs& g, uint32
     const int64_t first = (int64_t)rsub * ld + col;   // element offset of this lane's vector in pass 0
     const bool partial = CPW == 2 && g.rag && (col < cv.col_lo || col + 8 > col_hi);   // the vector straddles an end of a ragged row
     uint4 rv[4];
-    if (chunked) {
+    if (CPW == 2 && g.tma_store) {
+      // the residual in the accumulator's layout (a thread owns a row): its 64 bytes of this sub-step
+      if (rbase) {
+        const OutT* rrow = rbase + (int64_t)lane * ld + col0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          rv[j] = (lane < rows_left && col0 + 8 * j < col_hi) ? __ldg(reinterpret_cast<const uint4*>(rrow) + j) : make_uint4(0, 0, 0, 0);
+      }
+    } else if (chunked) {
       if (!first_chunk && g.vec_store) {
 #pragma unroll
         for (int pass = 0; pass < 4; ++pass)
@@ -495,6 +343,35 @@ __device__ __forceinline__ void drain_accumulator_narrow(const TcArgs& g, uint32
         if constexpr (CPW == 2) words[j] = pack_word<OutT>(v[2 * j], v[2 * j + 1]);
         else words[j] = pack_word<OutT>(v[j], 0.f);
       }
+    }
+    if (CPW == 2 && g.tma_store) {
+      if (rbase) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          words[4 * j] = add_residual_word<OutT>(words[4 * j], rv[j].x, g.residual_mul);
+          words[4 * j + 1] = add_residual_word<OutT>(words[4 * j + 1], rv[j].y, g.residual_mul);
+          words[4 * j + 2] = add_residual_word<OutT>(words[4 * j + 2], rv[j].z, g.residual_mul);
+          words[4 * j + 3] = add_residual_word<OutT>(words[4 * j + 3], rv[j].w, g.residual_mul);
+        }
+      }
+      // The warp's 32 rows x 64 bytes go to its staging box and from there to C as ONE tile store, issued by lane 0:
+      // nothing is read back, no store instruction or address arithmetic per row, and rows / columns past the edge of
+      // C are clipped by the copy.  64-byte swizzle: the 16-byte chunk j of row r sits at chunk j ^ ((r >> 1) & 3), so the
+      // eight rows a store instruction's quarter-warp covers fall in eight different bank groups.
+      if (lane == 0) bulk_wait_read_all();   // the previous store has finished reading the box
+      __syncwarp();
+      uint32_t* srow = stage + lane * 16;
+      const int sw = (lane >> 1) & 3;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        *reinterpret_cast<uint4*>(srow + ((j ^ sw) << 2)) = make_uint4(words[4 * j], words[4 * j + 1], words[4 * j + 2], words[4 * j + 3]);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_4d(tm_c, stage, (int)col0, (int)row_base, b, 0);
+        bulk_commit_group();
+      }
+      continue;
     }
 #pragma unroll
     for (int round = 0; round < 2; ++round) {
@@ -589,7 +466,8 @@ __device__ __forceinline__ void drain_accumulator_narrow(const TcArgs& g, uint32
 
 template <typename OutT>
 __global__ void __launch_bounds__(S_NUM_THREADS, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const TcArgs g) {
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_c,
+                    const TcArgs g) {
   extern __shared__ unsigned char smem_raw[];
   // operand tiles need 1024-byte alignment for the 128-byte swizzle
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -599,7 +477,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   uint64_t* acc_full = bars + 2 * STAGES;   // [2]       accumulator complete
   uint64_t* acc_empty = bars + 2 * STAGES + 2;  // [2]   accumulator drained by the epilogue
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
-  uint32_t* epi_stage = reinterpret_cast<uint32_t*>(tiles + STAGES * STAGE_BYTES + 256);
+  uint32_t* epi_stage = reinterpret_cast<uint32_t*>(tiles + STAGES * STAGE_BYTES + S_BAR_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* err = g.err_flag;
@@ -730,13 +608,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const bool landed = mbar_wait(&acc_full[acc], acc_phase, err, 4);
       if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }  // the warp leaves together: tcgen05.ld is warp-collective
       tc_fence_after();
-      drain_accumulator_narrow<OutT>(g, tmem_base + acc * BN, (int64_t)m_t * BM, (int64_t)n_t * BN, b, kres, quarter, (warp - 2) >> 2, lane,
+      drain_accumulator_narrow<OutT>(g, &tm_c, tmem_base + acc * BN, (int64_t)m_t * BM, (int64_t)n_t * BN, b, kres, quarter, (warp - 2) >> 2, lane,
                                      epi_stage + (warp - 2) * S_EPI_STAGE_WORDS, chunk);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
       }
     }
+    if (g.tma_store && lane == 0) bulk_wait_all();   // this warp's tile stores are done before its staging memory goes away
   }
 
   // ---------------------------------------------------------------------- teardown ---
@@ -771,7 +650,8 @@ constexpr int P_STAGES = 6;
 constexpr int P_BN_HALF = BN / 2;                         // B columns held per CTA
 constexpr int P_B_STAGE_BYTES = P_BN_HALF * BK * 2;       // 16 KiB
 constexpr int P_STAGE_BYTES = A_STAGE_BYTES + P_B_STAGE_BYTES;  // 32 KiB
-constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256 + EPI_WARPS * EPI_STAGE_FLOATS * 4;
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + S_BAR_BYTES + S_EPI_WARPS * S_EPI_STAGE_WORDS * 4;
+static_assert(P_SMEM_BYTES <= 232448, "CTA-pair GEMM: shared memory over the per-block limit");
 
 __device__ __forceinline__ void pair_tile_coords(const TcArgs& g, int64_t t, int* b, int* m_t, int* n_t) {
   // same grouping as tile_coords over tiles of 256 rows: g.tiles_m counts 256-row tiles here
@@ -779,8 +659,9 @@ __device__ __forceinline__ void pair_tile_coords(const TcArgs& g, int64_t t, int
 }
 
 template <typename OutT>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
-gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const TcArgs g) {
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(S_NUM_THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_c,
+                         const TcArgs g) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + P_STAGES * P_STAGE_BYTES);
@@ -789,7 +670,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   uint64_t* acc_full = bars + 2 * P_STAGES;       // [2]
   uint64_t* acc_empty = bars + 2 * P_STAGES + 2;  // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * P_STAGES + 4);
-  float* epi_stage = reinterpret_cast<float*>(tiles + P_STAGES * P_STAGE_BYTES + 256);
+  uint32_t* epi_stage = reinterpret_cast<uint32_t*>(tiles + P_STAGES * P_STAGE_BYTES + S_BAR_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -802,7 +683,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 2 * EPI_WARPS); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 2 * S_EPI_WARPS); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -954,13 +835,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         const bool landed = mbar_wait_cluster(&acc_full[acc], acc_phase, err, 4);
         if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }
         tc_fence_after();
-        drain_accumulator<OutT>(g, tmem_base + acc * BN, (int64_t)m_t * 2 * BM + (int64_t)rank * BM, (int64_t)n_t * BN, b, kres, quarter,
-                                (warp - 2) >> 2, lane, epi_stage + (warp - 2) * EPI_STAGE_FLOATS, chunk);
+        drain_accumulator_narrow<OutT>(g, &tm_c, tmem_base + acc * BN, (int64_t)m_t * 2 * BM + (int64_t)rank * BM, (int64_t)n_t * BN, b, kres,
+                                       quarter, (warp - 2) >> 2, lane, epi_stage + (warp - 2) * S_EPI_STAGE_WORDS, chunk);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
       }
     }
+    if (g.tma_store && lane == 0) bulk_wait_all();   // this warp's tile stores are done before its staging memory goes away
   }
 
   // ---------------------------------------------------------------------- teardown ---
@@ -1117,6 +999,17 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
     if (!ok) { cleanup(); return Status::Unsupported("gemm: extra destinations need 16-byte aligned rows and a 16-bit type"); }
   }
   g.err_flag = dev->kernel_error_flag();
+  // C as a tile-store destination {N, M, batch}: boxes of 32 columns x 32 rows, 64-byte swizzle
+  static const bool tma_store_on = []() { const char* v = getenv("B200MLX_GEMM_TMA_STORE"); return !(v && v[0] == '0'); }();
+  g.tma_store = (tma_store_on && is16 && g.vec_store && !rag && p.num_c_extra == 0) ? 1 : 0;
+  CUtensorMap tm_c = tm_a;   // a valid map when unused
+  if (g.tma_store) {
+    const uint64_t cdims[4] = {(uint64_t)p.n, (uint64_t)p.m, (uint64_t)p.batch, 1};
+    const uint64_t cstrides[3] = {(uint64_t)g.ldc * 2, (uint64_t)p.m * (uint64_t)g.ldc * 2, (uint64_t)p.m * (uint64_t)g.ldc * 2 * (uint64_t)p.batch};
+    const uint32_t cbox[4] = {32, 32, 1, 1};
+    s = encode_tma_4d_16bit(&tm_c, p.c, f16, cdims, cstrides, cbox, 64);
+    if (!s.ok()) { cleanup(); return s; }
+  }
 
   cudaError_t e = cudaSuccess;
   // the dynamic shared memory opt-in is per function and per device; do it once
@@ -1133,7 +1026,7 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
       }                                                                                                                     \
     }                                                                                                                       \
     const int64_t grid = g.total_tiles < dev->sm_count() ? g.total_tiles : dev->sm_count();                                 \
-    if (e == cudaSuccess) gemm_tcgen05_kernel<OutT><<<(unsigned)grid, S_NUM_THREADS, S_SMEM_BYTES, stream>>>(tm_a, tm_b, g); \
+    if (e == cudaSuccess) gemm_tcgen05_kernel<OutT><<<(unsigned)grid, S_NUM_THREADS, S_SMEM_BYTES, stream>>>(tm_a, tm_b, tm_c, g); \
   } while (0)
 #define LAUNCH_TC_PAIR(OutT, SLOT)                                                                                          \
   do {                                                                                                                      \
@@ -1146,7 +1039,7 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
         int clusters = 0;                                                                                                   \
         cudaLaunchConfig_t cfg = {};                                                                                        \
         cfg.gridDim = dim3((unsigned)(dev->sm_count() & ~1));                                                               \
-        cfg.blockDim = dim3(NUM_THREADS);                                                                                   \
+        cfg.blockDim = dim3(S_NUM_THREADS);                                                                                 \
         cfg.dynamicSmemBytes = P_SMEM_BYTES;                                                                                \
         cudaLaunchAttribute attr[1];                                                                                        \
         attr[0].id = cudaLaunchAttributeClusterDimension;                                                                   \
@@ -1163,7 +1056,7 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
     const int64_t cap = max_pairs[SLOT][dev->ordinal()];                                                                    \
     const int64_t pairs = g.total_tiles < cap ? g.total_tiles : cap;                                                        \
     if (e == cudaSuccess)                                                                                                   \
-      gemm_tcgen05_pair_kernel<OutT><<<(unsigned)(2 * pairs), NUM_THREADS, P_SMEM_BYTES, stream>>>(tm_a, tm_b, g);           \
+      gemm_tcgen05_pair_kernel<OutT><<<(unsigned)(2 * pairs), S_NUM_THREADS, P_SMEM_BYTES, stream>>>(tm_a, tm_b, tm_c, g);   \
   } while (0)
   if (use_pair) {
     if (is32) LAUNCH_TC_PAIR(float, 3);

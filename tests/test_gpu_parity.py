@@ -821,13 +821,14 @@ def test_rope_reads_queries_inside_the_projection_buffer(b200, backend):
     assert ok, viol
 
 
-@pytest.mark.parametrize("dtype,M,N", [(BF16, 2048, 2051), (np.float32, 1040, 2050), (BF16, 4100, 1030)], ids=["bf16_odd", "f32_even", "bf16_even"])
+@pytest.mark.parametrize("dtype,M,N", [(BF16, 2050, 2051), (np.float32, 1040, 2050), (BF16, 4100, 1030)], ids=["bf16_odd", "f32_even", "bf16_even"])
 def test_large_ragged_result_goes_through_a_padded_pitch(b200, backend, dtype, M, N):
-    # rows that are not a whole number of 16-byte vectors: GEMM into a padded pitch, then one packing pass
+    # rows that are not a whole number of 16-byte vectors, and no way to write them in row classes (M not a multiple of 8, or
+    # fp32): GEMM into a padded pitch, then one packing pass
     rng = np.random.default_rng(99)
     a, w = rng_array(rng, (M, 64), dtype), rng_array(rng, (N, 64), dtype, 0.2)
     (got,), plan = run_backend(b200, backend, lambda f, x, y: f.DotGeneral(x, [1], [], y, [1], []), [a, w], describe=True)
-    assert "move[pack" in plan, plan
+    assert "move[pack" in plan and "ragged-rows" not in plan, plan
     (want,) = run_oracle(lambda f, x, y: f.DotGeneral(x, [1], [], y, [1], []), [a, w])
     rtol, ascale = _dot_tol(dtype)
     ok, viol = compare(got, want, rtol, ascale)
