@@ -70,7 +70,12 @@ struct AttArgs {
   int is_f16;
   float scale_log2e;          // scale * log2(e), > 0
   int* err_flag;
+  int* next_item;             // zero before the launch: work items beyond the first of each CTA are taken from here
 };
+
+// The work-item counter of a launch (one per device: the array lives in each device's copy of the module).  Launches of
+// one device are ordered on its stream, and each is preceded by a memset of the counter on that stream.
+__device__ int g_next_item[4];
 
 template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
 template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
@@ -130,16 +135,21 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   uint64_t* s_full = kv_empty + KV_STAGES;       // [QT] scores of the current block are in TMEM
   uint64_t* p_ready = s_full + QT;               // [QT] P is in tensor memory (and S has been read): 4 warp arrivals
   uint64_t* o_done = p_ready + QT;               // [QT] the PV MMAs of the current block are done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + QT);
+  uint64_t* item_ready = o_done + QT;            // [Q_BUFS] the loader has published the work item that will use this Q buffer
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(item_ready + Q_BUFS);
   int* failed = reinterpret_cast<int*>(tmem_slot + 1);
+  volatile int* s_item = reinterpret_cast<volatile int*>(tmem_slot + 2);   // [Q_BUFS] work item per Q buffer; -1: no more work
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* err = g.err_flag;
 
-  // Persistent CTAs: work items (256 query rows of one head) are dealt round-robin, heaviest (latest query block
-  // under a causal mask) first, so every CTA gets a similar mix and the fixed cost of a CTA -- launch, TMEM allocation,
-  // the first loads, the drain -- is paid once per CTA instead of once per item (it measured 7.5 us per item against
-  // 1.5 us per key block).  Barrier phases simply keep counting across items.
+  // Persistent CTAs: the fixed cost of a CTA -- launch, TMEM allocation, the first loads, the drain -- is paid once per
+  // CTA instead of once per work item (256 query rows of one head; it measured 7.5 us per item against 1.5 us per key
+  // block).  Items are ordered heaviest first (latest query block under a causal mask).  A CTA starts with item
+  // blockIdx.x and takes every further one from a global counter when it gets there, so a CTA that drew light items
+  // simply does more of them: with a fixed round-robin deal, GPT-2's shape (768 items of 4..16 key-block steps on 296
+  // CTAs) left the busiest CTA with 32 steps against a mean of 26.  The loader draws the item and publishes it to the
+  // other warps through shared memory (item_ready); barrier phases keep counting across items.
   const int nq = (g.Sq + QT * BQ - 1) / (QT * BQ);
   const int64_t heads_total = (int64_t)g.H * g.B;
   const int64_t num_items = (int64_t)nq * heads_total;
@@ -173,7 +183,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   };
 
   if (threadIdx.x == 0) {
-    for (int q = 0; q < Q_BUFS; ++q) { mbar_init(&q_full[q], 1); mbar_init(&q_empty[q], 1 + QT * 4); }
+    for (int q = 0; q < Q_BUFS; ++q) { mbar_init(&q_full[q], 1); mbar_init(&q_empty[q], 1 + QT * 4); mbar_init(&item_ready[q], 1); }
     for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
     for (int t = 0; t < QT; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_ready[t], 4); mbar_init(&o_done[t], 1); }
     *failed = 0;
@@ -198,10 +208,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       int s = 0;
       uint32_t phase = 0, n_item = 0;
       bool ok = true;
-      for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++n_item) {
-        const Item it = decode(item);
+      for (int64_t item = blockIdx.x; ok; ++n_item) {
         const int qbuf = (int)(n_item & 1);
-        if (!mbar_wait(&q_empty[qbuf], ((n_item >> 1) & 1) ^ 1, err, 1)) break;
+        if (!mbar_wait(&q_empty[qbuf], ((n_item >> 1) & 1) ^ 1, err, 1)) break;   // the slot's previous item is finished everywhere
+        const bool more = item < num_items;
+        s_item[qbuf] = more ? (int)item : -1;
+        mbar_arrive(&item_ready[qbuf]);   // release: the store above is visible to whoever sees this phase complete
+        if (!more) break;
+        const Item it = decode(item);
         mbar_expect_tx(&q_full[qbuf], QT * Q_BYTES);
 #pragma unroll
         for (int t = 0; t < QT; ++t) tma_load_4d(sQ + (qbuf * QT + t) * Q_BYTES, &tm_q, &q_full[qbuf], 0, it.q0 + t * BQ, it.h, it.b);
@@ -213,6 +227,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           tma_load_4d(dst + KV_BYTES, &tm_v, &kv_full[s], 0, j * BKV, it.hkv, it.b);
           if (++s == KV_STAGES) { s = 0; phase ^= 1; }
         }
+        item = (int64_t)gridDim.x + atomicAdd(g.next_item, 1);
       }
     }
   } else if (warp == 1) {
@@ -236,9 +251,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       uint32_t phase = 0, n_item = 0;
       uint32_t done[QT] = {0, 0};   // key blocks each tile has finished so far, over all items: the phase of its barriers
       bool ok = true;
-      for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++n_item) {
-        const Item it = decode(item);
+      for (;; ++n_item) {
         qbuf = (int)(n_item & 1);
+        if (!mbar_wait(&item_ready[qbuf], (n_item >> 1) & 1, err, 2)) break;
+        const int item = s_item[qbuf];
+        if (item < 0) break;
+        const Item it = decode(item);
         if (it.nkv_max == 0) { tc_commit(&q_empty[qbuf]); continue; }   // the loader loaded Q anyway: hand the buffer back
         ok = mbar_wait(&q_full[qbuf], (n_item >> 1) & 1, err, 2);
         if (ok) ok = mbar_wait(&kv_full[s], phase, err, 3);
@@ -279,7 +297,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           s = s_next;
           phase = phase_next;
         }
-        if (ok) tc_commit(&q_empty[qbuf]);   // every score MMA of this item has been issued: Q may be replaced when they are done
+        if (!ok) break;
+        tc_commit(&q_empty[qbuf]);   // every score MMA of this item has been issued: Q may be replaced when they are done
       }
     }
   } else {
@@ -293,7 +312,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     uint32_t done = 0;                      // key blocks this tile has finished so far, over all items: the barriers' phase
     uint32_t n_item = 0;
     bool ok = true;
-    for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++n_item) {
+    for (; ok; ++n_item) {
+    {
+      const bool published = mbar_wait(&item_ready[n_item & 1], (n_item >> 1) & 1, err, 6);
+      if (!__all_sync(0xffffffffu, published)) break;
+    }
+    const int item = s_item[n_item & 1];
+    if (item < 0) break;
     const Item it = decode(item);
     const int h = it.h, b = it.b;
     const int q_row = it.q0 + t * BQ + row;   // the row this thread's softmax works on
@@ -504,6 +529,12 @@ Status attention(Device* dev, const AttentionParams& p) {
   g.is_f16 = f16 ? 1 : 0;
   g.scale_log2e = (float)(p.scale * 1.4426950408889634);
   g.err_flag = dev->kernel_error_flag();
+  {
+    void* ctr = nullptr;
+    B200_CUDA_TRY(cudaGetSymbolAddress(&ctr, g_next_item));
+    g.next_item = reinterpret_cast<int*>(ctr);
+    B200_CUDA_TRY(cudaMemsetAsync(ctr, 0, sizeof(int), dev->stream()));
+  }
   const int64_t nq = (p.Sq + QT * BQ - 1) / (QT * BQ);
   const int64_t items = nq * p.H * p.B;
   if (items >= 2147483648LL) return Status::Unsupported("attention: more than 2^31 work items");
