@@ -333,11 +333,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const int kv0 = j * BKV;
       int limit = g.Sk - kv0;                               // columns >= limit are masked
       if (g.causal && q_row + 1 - kv0 < limit) limit = q_row + 1 - kv0;
-      // Pass 1: the row maximum.  The scores are read from TMEM here and again in pass 2 instead of being held across
-      // the rescale in between (TMEM reads are cheap; registers are what limits two CTAs per SM).
-      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;   // four chains: the reduction is latency-bound otherwise
-      {
-        uint32_t sr[64];
+      // The block's 64 scores of this row stay in registers from the maximum (pass 1) to the exponentials (pass 2): a
+      // TMEM read costs some 300 cycles of pure latency on the tile's critical path.  Only when the reference maximum
+      // moves (the first block of an item, then rarely) are they dropped across the rescale of O and read again.
+      uint32_t sr[64];
+      auto load_scores = [&]() {
         tmem_ld32(tmem_s, sr);
         tmem_ld32(tmem_s + 32, sr + 32);
         tmem_ld_wait();
@@ -346,14 +346,16 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           for (int cidx = 0; cidx < 64; ++cidx)
             if (cidx >= limit) sr[cidx] = 0xff800000u;   // -inf
         }
-        // three-input maximum (sm_100): 32 instructions for the 64 scores, in four independent chains
+      };
+      load_scores();
+      // Pass 1: the row maximum: three-input maximum (sm_100), 32 instructions in four independent chains
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-        for (int cidx = 0; cidx < 64; cidx += 8) {
-          mx0 = max3(mx0, __uint_as_float(sr[cidx]), __uint_as_float(sr[cidx + 1]));
-          mx1 = max3(mx1, __uint_as_float(sr[cidx + 2]), __uint_as_float(sr[cidx + 3]));
-          mx2 = max3(mx2, __uint_as_float(sr[cidx + 4]), __uint_as_float(sr[cidx + 5]));
-          mx3 = max3(mx3, __uint_as_float(sr[cidx + 6]), __uint_as_float(sr[cidx + 7]));
-        }
+      for (int cidx = 0; cidx < 64; cidx += 8) {
+        mx0 = max3(mx0, __uint_as_float(sr[cidx]), __uint_as_float(sr[cidx + 1]));
+        mx1 = max3(mx1, __uint_as_float(sr[cidx + 2]), __uint_as_float(sr[cidx + 3]));
+        mx2 = max3(mx2, __uint_as_float(sr[cidx + 4]), __uint_as_float(sr[cidx + 5]));
+        mx3 = max3(mx3, __uint_as_float(sr[cidx + 6]), __uint_as_float(sr[cidx + 7]));
       }
       const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       const float m_new = mx * c;                           // c > 0: the maximum commutes with the scale
@@ -378,6 +380,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             tmem_st32(tmem_o + half * 32, orow);
           }
           tmem_st_wait();
+          load_scores();   // the registers were given to the row of O
         }
         m_ref = m_next;
       }
@@ -386,15 +389,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // before the score MMAs that produced this S, and MMAs run in issue order: they are done).
       float psum0 = 0.f, psum1 = 0.f;
       {
-        uint32_t sr[64];
-        tmem_ld32(tmem_s, sr);
-        tmem_ld32(tmem_s + 32, sr + 32);
-        tmem_ld_wait();
-        if (limit < 64) {
-#pragma unroll
-          for (int cidx = 0; cidx < 64; ++cidx)
-            if (cidx >= limit) sr[cidx] = 0xff800000u;
-        }
         // One exponential per score makes the special-function unit (16 per clock per SM) the kernel's limiter at head
         // dim 64, so every third pair of scores takes its exp2 from the FMA pipe instead: round to the nearest integer n
         // with the 1.5 * 2^23 trick, a cubic for 2^r on r in [-1/2, 1/2] (relative error 7.5e-5, below half an ulp of
