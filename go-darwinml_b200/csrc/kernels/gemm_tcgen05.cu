@@ -274,8 +274,9 @@ __device__ __forceinline__ uint32_t combine_chunk_word(const TcArgs& g, uint32_t
 // destinations) is staged 16 rows x 16 words at a time (20-word pitch) and written back transposed, 8 rows x 64
 // contiguous bytes per store instruction.
 template <typename OutT>
-__device__ __forceinline__ void drain_accumulator_narrow(const TcArgs& g, const CUtensorMap* tm_c, uint32_t tmem_acc, int64_t row0, int64_t n0,
-                                                         int b, int kres, int quarter, int cq, int lane, uint32_t* stage, int chunk) {
+__device__ __forceinline__ void drain_accumulator_narrow(const TcArgs& g, const CUtensorMap* tm_c, const CUtensorMap* tm_r, uint64_t* rbar,
+                                                         uint32_t& rphase, uint32_t tmem_acc, int64_t row0, int64_t n0, int b, int kres,
+                                                         int quarter, int cq, int lane, uint32_t* stage, int chunk) {
   using Tr = OutTraits<OutT>;
   constexpr int CPW = Tr::kColsPerWord;
   constexpr int SUB_COLS = 16 * CPW;            // columns per sub-step: 16 words per row
@@ -305,12 +306,13 @@ __device__ __forceinline__ void drain_accumulator_narrow(const TcArgs& g, const 
     const bool partial = CPW == 2 && g.rag && (col < cv.col_lo || col + 8 > col_hi);   // the vector straddles an end of a ragged row
     uint4 rv[4];
     if (CPW == 2 && g.tma_store) {
-      // the residual in the accumulator's layout (a thread owns a row): its 64 bytes of this sub-step
-      if (rbase) {
-        const OutT* rrow = rbase + (int64_t)lane * ld + col0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          rv[j] = (lane < rows_left && col0 + 8 * j < col_hi) ? __ldg(reinterpret_cast<const uint4*>(rrow) + j) : make_uint4(0, 0, 0, 0);
+      // The residual's 32 x 64-byte block of this sub-step comes into the warp's staging box by a tile load (a thread
+      // owns a row, so loads from registers would touch 32 lines per instruction), under the TMEM read and the
+      // arithmetic below; the box is free once the previous tile store has read it.
+      if (rbase && lane == 0) {
+        bulk_wait_read_all();
+        mbar_expect_tx(rbar, 32 * 64);
+        tma_load_4d(stage, tm_r, rbar, (int)col0, (int)row_base, b, 0);
       }
     } else if (chunked) {
       if (!first_chunk && g.vec_store) {
@@ -345,23 +347,27 @@ __device__ __forceinline__ void drain_accumulator_narrow(const TcArgs& g, const 
       }
     }
     if (CPW == 2 && g.tma_store) {
-      if (rbase) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          words[4 * j] = add_residual_word<OutT>(words[4 * j], rv[j].x, g.residual_mul);
-          words[4 * j + 1] = add_residual_word<OutT>(words[4 * j + 1], rv[j].y, g.residual_mul);
-          words[4 * j + 2] = add_residual_word<OutT>(words[4 * j + 2], rv[j].z, g.residual_mul);
-          words[4 * j + 3] = add_residual_word<OutT>(words[4 * j + 3], rv[j].w, g.residual_mul);
-        }
-      }
       // The warp's 32 rows x 64 bytes go to its staging box and from there to C as ONE tile store, issued by lane 0:
       // nothing is read back, no store instruction or address arithmetic per row, and rows / columns past the edge of
       // C are clipped by the copy.  64-byte swizzle: the 16-byte chunk j of row r sits at chunk j ^ ((r >> 1) & 3), so the
       // eight rows a store instruction's quarter-warp covers fall in eight different bank groups.
-      if (lane == 0) bulk_wait_read_all();   // the previous store has finished reading the box
-      __syncwarp();
       uint32_t* srow = stage + lane * 16;
       const int sw = (lane >> 1) & 3;
+      if (rbase) {
+        mbar_wait(rbar, rphase, g.err_flag, 8);   // the residual block has landed (a wait that gives up raises the error word)
+        rphase ^= 1;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint4 rq = *reinterpret_cast<const uint4*>(srow + ((j ^ sw) << 2));
+          words[4 * j] = add_residual_word<OutT>(words[4 * j], rq.x, g.residual_mul);
+          words[4 * j + 1] = add_residual_word<OutT>(words[4 * j + 1], rq.y, g.residual_mul);
+          words[4 * j + 2] = add_residual_word<OutT>(words[4 * j + 2], rq.z, g.residual_mul);
+          words[4 * j + 3] = add_residual_word<OutT>(words[4 * j + 3], rq.w, g.residual_mul);
+        }
+      } else {
+        if (lane == 0) bulk_wait_read_all();   // the previous store has finished reading the box
+        __syncwarp();
+      }
 #pragma unroll
       for (int j = 0; j < 4; ++j)
         *reinterpret_cast<uint4*>(srow + ((j ^ sw) << 2)) = make_uint4(words[4 * j], words[4 * j + 1], words[4 * j + 2], words[4 * j + 3]);
@@ -467,7 +473,7 @@ __device__ __forceinline__ void drain_accumulator_narrow(const TcArgs& g, const 
 template <typename OutT>
 __global__ void __launch_bounds__(S_NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_c,
-                    const TcArgs g) {
+                    const __grid_constant__ CUtensorMap tm_r, const TcArgs g) {
   extern __shared__ unsigned char smem_raw[];
   // operand tiles need 1024-byte alignment for the 128-byte swizzle
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -477,6 +483,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   uint64_t* acc_full = bars + 2 * STAGES;   // [2]       accumulator complete
   uint64_t* acc_empty = bars + 2 * STAGES + 2;  // [2]   accumulator drained by the epilogue
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  uint64_t* res_bar = bars + 32;            // [S_EPI_WARPS] an epilogue warp's residual block has landed
   uint32_t* epi_stage = reinterpret_cast<uint32_t*>(tiles + STAGES * STAGE_BYTES + S_BAR_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -488,6 +495,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], S_EPI_WARPS); }
+    for (int w = 0; w < S_EPI_WARPS; ++w) mbar_init(&res_bar[w], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -597,6 +605,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const int quarter = warp & 3;              // TMEM lanes [32*quarter, 32*quarter + 32) belong to this warp
     bool ok = true;
     int local_tile = 0;
+    uint32_t rphase = 0;
     for (int64_t t = blockIdx.x; t < g.total_tiles && ok; t += gridDim.x) {
       int b, m_t, n_t;
       tile_coords(g, t, &b, &m_t, &n_t);
@@ -608,7 +617,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const bool landed = mbar_wait(&acc_full[acc], acc_phase, err, 4);
       if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }  // the warp leaves together: tcgen05.ld is warp-collective
       tc_fence_after();
-      drain_accumulator_narrow<OutT>(g, &tm_c, tmem_base + acc * BN, (int64_t)m_t * BM, (int64_t)n_t * BN, b, kres, quarter, (warp - 2) >> 2, lane,
+      drain_accumulator_narrow<OutT>(g, &tm_c, &tm_r, &res_bar[warp - 2], rphase, tmem_base + acc * BN, (int64_t)m_t * BM, (int64_t)n_t * BN, b, kres, quarter, (warp - 2) >> 2, lane,
                                      epi_stage + (warp - 2) * S_EPI_STAGE_WORDS, chunk);
       tc_fence_before();
       __syncwarp();
@@ -661,7 +670,7 @@ __device__ __forceinline__ void pair_tile_coords(const TcArgs& g, int64_t t, int
 template <typename OutT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(S_NUM_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_c,
-                         const TcArgs g) {
+                         const __grid_constant__ CUtensorMap tm_r, const TcArgs g) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + P_STAGES * P_STAGE_BYTES);
@@ -670,6 +679,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   uint64_t* acc_full = bars + 2 * P_STAGES;       // [2]
   uint64_t* acc_empty = bars + 2 * P_STAGES + 2;  // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * P_STAGES + 4);
+  uint64_t* res_bar = bars + 32;                  // [S_EPI_WARPS] an epilogue warp's residual block has landed
   uint32_t* epi_stage = reinterpret_cast<uint32_t*>(tiles + P_STAGES * P_STAGE_BYTES + S_BAR_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -684,6 +694,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 2 * S_EPI_WARPS); }
+    for (int w = 0; w < S_EPI_WARPS; ++w) mbar_init(&res_bar[w], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -824,6 +835,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
     const int quarter = warp & 3;
     bool ok = true;
     int local_tile = 0;
+    uint32_t rphase = 0;
     for (int64_t t = pair; t < g.total_tiles && ok; t += num_pairs) {
       int b, m_t, n_t;
       pair_tile_coords(g, t, &b, &m_t, &n_t);
@@ -835,7 +847,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         const bool landed = mbar_wait_cluster(&acc_full[acc], acc_phase, err, 4);
         if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }
         tc_fence_after();
-        drain_accumulator_narrow<OutT>(g, &tm_c, tmem_base + acc * BN, (int64_t)m_t * 2 * BM + (int64_t)rank * BM, (int64_t)n_t * BN, b, kres,
+        drain_accumulator_narrow<OutT>(g, &tm_c, &tm_r, &res_bar[warp - 2], rphase, tmem_base + acc * BN, (int64_t)m_t * 2 * BM + (int64_t)rank * BM, (int64_t)n_t * BN, b, kres,
                                        quarter, (warp - 2) >> 2, lane, epi_stage + (warp - 2) * S_EPI_STAGE_WORDS, chunk);
         tc_fence_before();
         __syncwarp();
@@ -1002,12 +1014,13 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
   // C as a tile-store destination {N, M, batch}: boxes of 32 columns x 32 rows, 64-byte swizzle
   static const bool tma_store_on = []() { const char* v = getenv("B200MLX_GEMM_TMA_STORE"); return !(v && v[0] == '0'); }();
   g.tma_store = (tma_store_on && is16 && g.vec_store && !rag && p.num_c_extra == 0) ? 1 : 0;
-  CUtensorMap tm_c = tm_a;   // a valid map when unused
+  CUtensorMap tm_c = tm_a, tm_r = tm_a;   // valid maps when unused
   if (g.tma_store) {
     const uint64_t cdims[4] = {(uint64_t)p.n, (uint64_t)p.m, (uint64_t)p.batch, 1};
     const uint64_t cstrides[3] = {(uint64_t)g.ldc * 2, (uint64_t)p.m * (uint64_t)g.ldc * 2, (uint64_t)p.m * (uint64_t)g.ldc * 2 * (uint64_t)p.batch};
     const uint32_t cbox[4] = {32, 32, 1, 1};
     s = encode_tma_4d_16bit(&tm_c, p.c, f16, cdims, cstrides, cbox, 64);
+    if (s.ok() && p.residual) s = encode_tma_4d_16bit(&tm_r, p.residual, f16, cdims, cstrides, cbox, 64);   // same shape and pitch as C
     if (!s.ok()) { cleanup(); return s; }
   }
 
@@ -1026,7 +1039,7 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
       }                                                                                                                     \
     }                                                                                                                       \
     const int64_t grid = g.total_tiles < dev->sm_count() ? g.total_tiles : dev->sm_count();                                 \
-    if (e == cudaSuccess) gemm_tcgen05_kernel<OutT><<<(unsigned)grid, S_NUM_THREADS, S_SMEM_BYTES, stream>>>(tm_a, tm_b, tm_c, g); \
+    if (e == cudaSuccess) gemm_tcgen05_kernel<OutT><<<(unsigned)grid, S_NUM_THREADS, S_SMEM_BYTES, stream>>>(tm_a, tm_b, tm_c, tm_r, g); \
   } while (0)
 #define LAUNCH_TC_PAIR(OutT, SLOT)                                                                                          \
   do {                                                                                                                      \
@@ -1056,7 +1069,7 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
     const int64_t cap = max_pairs[SLOT][dev->ordinal()];                                                                    \
     const int64_t pairs = g.total_tiles < cap ? g.total_tiles : cap;                                                        \
     if (e == cudaSuccess)                                                                                                   \
-      gemm_tcgen05_pair_kernel<OutT><<<(unsigned)(2 * pairs), S_NUM_THREADS, P_SMEM_BYTES, stream>>>(tm_a, tm_b, tm_c, g);   \
+      gemm_tcgen05_pair_kernel<OutT><<<(unsigned)(2 * pairs), S_NUM_THREADS, P_SMEM_BYTES, stream>>>(tm_a, tm_b, tm_c, tm_r, g); \
   } while (0)
   if (use_pair) {
     if (is32) LAUNCH_TC_PAIR(float, 3);
