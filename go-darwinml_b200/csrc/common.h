@@ -94,6 +94,9 @@ class Device {
   cudaStream_t stream() const;
   cudaStream_t compute_stream() const { return stream_; }
   Status CaptureStream(cudaStream_t* out);
+  // A second private stream: the body of a While loop is recorded on it into the loop's conditional graph node while
+  // the plan around the loop is being recorded on the capture stream (same holder of capture_mutex).
+  Status LoopStream(cudaStream_t* out);
   // Held from cudaStreamBeginCapture to cudaStreamEndCapture on the capture stream: the device has one such stream,
   // and two executables reaching their recording run at the same time would otherwise begin a capture on a stream
   // that is already capturing.
@@ -123,7 +126,7 @@ class Device {
   int ordinal_ = 0;
   int sm_count_ = 148;
   cudaStream_t stream_ = nullptr;
-  cudaStream_t copy_in_ = nullptr, copy_out_ = nullptr, capture_ = nullptr;
+  cudaStream_t copy_in_ = nullptr, copy_out_ = nullptr, capture_ = nullptr, loop_ = nullptr;
   int* error_flag_ = nullptr;
   std::atomic<bool> error_check_pending_{false};   // set by launching threads, read at synchronisation points
   std::mutex mu_, capture_mu_;
@@ -132,13 +135,21 @@ class Device {
   int64_t reserved_ = 0;
 };
 
+// Code a device-resident While loop writes to the device's error word when it stops at its iteration limit (codes 1..8
+// are the bounded waits of the tensor-core kernels).
+constexpr int kErrWhileLimit = 100;
+
 // While alive, Device::stream() of `dev` returns `s` on this thread only.
 class StreamOverride {
  public:
   StreamOverride(const Device* dev, cudaStream_t s);
-  ~StreamOverride();
+  ~StreamOverride();   // restores what was in force before (overrides nest)
   StreamOverride(const StreamOverride&) = delete;
   StreamOverride& operator=(const StreamOverride&) = delete;
+
+ private:
+  const Device* prev_dev_;
+  cudaStream_t prev_stream_;
 };
 
 struct Buffer {

@@ -54,6 +54,7 @@ struct Step {
   std::vector<int> reads, writes;
   int launches = 1;
   bool capturable = true;   // false when run() allocates or frees device memory (its pointers would be stale in a replay)
+  bool wants_graph = false; // a step that is much cheaper inside a replayed graph (a While loop then runs on the device)
   std::function<Status(Device*, void* const*)> run;  // ptrs indexed by slot
 };
 
@@ -150,6 +151,72 @@ Status RunSubPlan(Exec* ex, void* const* in_ptrs, void* const* out_ptrs) {
     Status rs = st.run(ex->dev, ptrs.data());
     if (!rs.ok()) return Status{rs.code, st.desc + ": " + rs.msg};
   }
+  return Status::OK();
+}
+
+constexpr int kWhileMaxIterations = 1000000;   // the reference's limit (ref mpsgraph executable.go:241)
+
+// Sets the condition of a device-resident While loop for its next trip: the cond sub-plan's byte, unless the trip limit
+// is reached (then the loop stops and the device's error word says why).  One thread.
+__global__ void while_set_cond_kernel(cudaGraphConditionalHandle handle, const unsigned char* pred, int* trips, int limit, int* err_flag) {
+  unsigned go = *pred != 0 ? 1u : 0u;
+  const int t = *trips;
+  if (go && t >= limit) {
+    atomicCAS(err_flag, 0, kErrWhileLimit);
+    go = 0;
+  }
+  *trips = t + 1;
+  cudaGraphSetConditional(handle, go);
+}
+
+// Records a While loop into the CUDA graph that `dev->stream()` is being captured into, as a conditional WHILE node:
+// cond runs once in front of the node; the node's body graph (recorded on the device's loop stream) runs body, copies the
+// new state over the current one, runs cond again and sets the node's condition, all on the device.  `run_cond` and
+// `run_body` launch the sub-plans on dev->stream(), whatever it is at the time.
+Status RecordWhileNode(Device* dev, const std::function<Status()>& run_cond, const std::function<Status()>& run_body_and_advance,
+                       const unsigned char* pred, int* trips) {
+  cudaStream_t ps = dev->stream();
+  cudaStream_t ls = nullptr;
+  B200_TRY(dev->LoopStream(&ls));
+  B200_CUDA_TRY(cudaMemsetAsync(trips, 0, sizeof(int), ps));
+  B200_TRY(run_cond());
+  cudaStreamCaptureStatus status;
+  unsigned long long id = 0;
+  cudaGraph_t parent = nullptr;
+  const cudaGraphNode_t* deps = nullptr;
+  size_t num_deps = 0;
+  B200_CUDA_TRY(cudaStreamGetCaptureInfo_v2(ps, &status, &id, &parent, &deps, &num_deps));
+  if (status != cudaStreamCaptureStatusActive || !parent) return Status::Invalid("While: the stream is not being recorded");
+  cudaGraphConditionalHandle handle;
+  B200_CUDA_TRY(cudaGraphConditionalHandleCreate(&handle, parent, 0, cudaGraphCondAssignDefault));
+  int* err_flag = dev->kernel_error_flag();
+  while_set_cond_kernel<<<1, 1, 0, ps>>>(handle, pred, trips, kWhileMaxIterations, err_flag);
+  B200_TRY(dev->CheckLaunch("while_set_cond"));
+  B200_CUDA_TRY(cudaStreamGetCaptureInfo_v2(ps, &status, &id, &parent, &deps, &num_deps));
+  cudaGraphNodeParams params = {};
+  params.type = cudaGraphNodeTypeConditional;
+  params.conditional.handle = handle;
+  params.conditional.type = cudaGraphCondTypeWhile;
+  params.conditional.size = 1;
+  cudaGraphNode_t node = nullptr;
+  B200_CUDA_TRY(cudaGraphAddNode(&node, parent, deps, num_deps, &params));
+  cudaGraph_t body = params.conditional.phGraph_out[0];
+  B200_CUDA_TRY(cudaStreamUpdateCaptureDependencies(ps, &node, 1, cudaStreamSetCaptureDependencies));
+  B200_CUDA_TRY(cudaStreamBeginCaptureToGraph(ls, body, nullptr, nullptr, 0, cudaStreamCaptureModeThreadLocal));
+  Status st = Status::OK();
+  {
+    StreamOverride in_body(dev, ls);
+    st = run_body_and_advance();
+    if (st.ok()) st = run_cond();
+    if (st.ok()) {
+      while_set_cond_kernel<<<1, 1, 0, ls>>>(handle, pred, trips, kWhileMaxIterations, err_flag);
+      st = dev->CheckLaunch("while_set_cond");
+    }
+  }
+  cudaGraph_t ended = nullptr;
+  const cudaError_t ce = cudaStreamEndCapture(ls, &ended);   // always: the loop stream must not stay in capture mode
+  B200_TRY(st);
+  if (ce != cudaSuccess) { cudaGetLastError(); return Status::Cuda(strfmt("While: recording the loop body failed: %s", cudaGetErrorString(ce))); }
   return Status::OK();
 }
 
@@ -1483,14 +1550,25 @@ class Planner {
     const int pred_slot = NewTemp(256);
     slot_of_[w->id] = pred_slot;
 
+    // The loop runs on the device (a conditional WHILE node) when the plan is replayed as a CUDA graph, which needs every
+    // step of both sub-plans to be recordable; otherwise, and on a plan's first runs, the host drives it.
+    static const bool device_loops = []() { const char* v = getenv("B200MLX_DEVICE_LOOPS"); return !(v && v[0] == '0'); }();
+    bool recordable = device_loops;
+    for (const Step& cs : ce->steps) recordable = recordable && cs.capturable;
+    for (const Step& bs : be->steps) recordable = recordable && bs.capturable;
+    if (recordable) {
+      cudaStream_t ls = nullptr;
+      B200_TRY(ex_->dev->LoopStream(&ls));   // created now: not while a recording is under way
+    }
     Step st;
-    st.desc = strfmt("while[state=%d cond: %d steps, %d captures; body: %d steps, %d captures]", n_state, (int)ce->steps.size(), n_cc,
-                     (int)be->steps.size(), n_bc);
+    st.desc = strfmt("while[state=%d cond: %d steps, %d captures; body: %d steps, %d captures%s]", n_state, (int)ce->steps.size(), n_cc,
+                     (int)be->steps.size(), n_bc, recordable ? "; on the device when replayed" : "");
     st.reads = in_slots;
     st.writes = res_slots;
     st.writes.insert(st.writes.end(), tmp_slots.begin(), tmp_slots.end());
     st.writes.push_back(pred_slot);
-    st.capturable = false;   // the trip count is read back from the device
+    st.capturable = recordable;
+    st.wants_graph = recordable;
     st.launches = 0;         // counted per run: unknown at compile time
     st.run = [=](Device* dev, void* const* p) -> Status {
       B200_TRY(dev->MakeCurrent());
@@ -1504,9 +1582,24 @@ class Planner {
       for (int i = 0; i < n_cc; ++i) cin[n_state + i] = p[in_slots[n_state + i]];
       for (int i = 0; i < n_bc; ++i) bin[n_state + i] = p[in_slots[n_state + n_cc + i]];
       void* pred = p[pred_slot];
-      constexpr int64_t kMaxIterations = 1000000;   // the reference's limit (ref mpsgraph executable.go:241)
+      cudaStreamCaptureStatus recording = cudaStreamCaptureStatusNone;
+      B200_CUDA_TRY(cudaStreamIsCapturing(dev->stream(), &recording));
+      if (recording == cudaStreamCaptureStatusActive) {
+        // fixed addresses: body writes the second set of state buffers and the new state is copied over the current one
+        for (int i = 0; i < n_state; ++i) cin[i] = bin[i] = cur[i];
+        auto run_cond = [&]() { return RunSubPlan(ce, cin.data(), &pred); };
+        auto run_body = [&]() -> Status {
+          B200_TRY(RunSubPlan(be, bin.data(), nxt.data()));
+          for (int i = 0; i < n_state; ++i)
+            if (nbytes[i] > 0) B200_CUDA_TRY(cudaMemcpyAsync(cur[i], nxt[i], (size_t)nbytes[i], cudaMemcpyDeviceToDevice, dev->stream()));
+          return Status::OK();
+        };
+        dev->kernel_error_flag();   // the loop may raise the error word: have the next synchronisation point read it
+        return RecordWhileNode(dev, run_cond, run_body, reinterpret_cast<const unsigned char*>(pred),
+                               reinterpret_cast<int*>(reinterpret_cast<char*>(pred) + 64));
+      }
       for (int64_t iter = 0;; ++iter) {
-        if (iter >= kMaxIterations) return Status::Invalid("While: exceeded maximum iterations (1000000)");
+        if (iter >= kWhileMaxIterations) return Status::Invalid("While: exceeded maximum iterations (1000000)");
         for (int i = 0; i < n_state; ++i) cin[i] = bin[i] = cur[i];
         B200_TRY(RunSubPlan(ce, cin.data(), &pred));
         unsigned char go = 0;
@@ -1963,7 +2056,9 @@ Status CompileGraph(Ctx* owner, Graph& graph, std::vector<Node*> feeds, std::vec
   B200_TRY(planner.Run(feeds, targets));
   if (ex->arena_bytes > 0) B200_TRY(ex->dev->Alloc(ex->arena_bytes, &ex->arena));
   static const bool graphs_on = []() { const char* v = getenv("B200MLX_GRAPHS"); return !(v && v[0] == '0'); }();
-  bool all = graphs_on && ex->steps.size() >= 4;
+  bool wanted = ex->steps.size() >= 4;   // short plans are not launch-bound ... unless a step asks
+  for (const Step& st : ex->steps) wanted = wanted || st.wants_graph;
+  bool all = graphs_on && wanted;
   for (const Step& st : ex->steps) all = all && st.capturable;
   ex->capturable = all;
   *out = std::move(ex);

@@ -75,13 +75,23 @@ thread_local cudaStream_t tls_override_stream = nullptr;
 
 cudaStream_t Device::stream() const { return (tls_override_dev == this && tls_override_stream) ? tls_override_stream : stream_; }
 
-StreamOverride::StreamOverride(const Device* dev, cudaStream_t s) {
+StreamOverride::StreamOverride(const Device* dev, cudaStream_t s) : prev_dev_(tls_override_dev), prev_stream_(tls_override_stream) {
   tls_override_dev = dev;
   tls_override_stream = s;
 }
 StreamOverride::~StreamOverride() {
-  tls_override_dev = nullptr;
-  tls_override_stream = nullptr;
+  tls_override_dev = prev_dev_;
+  tls_override_stream = prev_stream_;
+}
+
+Status Device::LoopStream(cudaStream_t* out) {
+  std::lock_guard<std::mutex> lock(mu_);
+  if (!loop_) {
+    B200_CUDA_TRY(cudaSetDevice(ordinal_));
+    B200_CUDA_TRY(cudaStreamCreateWithFlags(&loop_, cudaStreamNonBlocking));
+  }
+  *out = loop_;
+  return Status::OK();
 }
 
 Status Device::CaptureStream(cudaStream_t* out) {
@@ -128,9 +138,10 @@ Status Device::CheckKernelErrors() {
     static const char* who[] = {"?", "a tile loader waiting for a free stage", "an MMA issuer waiting for a drained accumulator or for Q",
                                 "an MMA issuer waiting for operand tiles", "an epilogue or MMA issuer waiting for its producer",
                                 "a kernel whose shared-memory window is not 1024-byte aligned", "a softmax warp waiting for scores",
-                                "a softmax warp waiting for the output MMAs"};
+                                "a softmax warp waiting for the output MMAs", "an epilogue warp waiting for its residual block"};
+    if (code == kErrWhileLimit) return Status::Invalid("While: exceeded maximum iterations (1000000); the loop was stopped and its results are invalid");
     return Status::Timeout(strfmt("a bounded wait inside a tensor-core kernel gave up (%s); its results are invalid",
-                                  (code >= 1 && code <= 7) ? who[code] : who[0]));
+                                  (code >= 1 && code <= 8) ? who[code] : who[0]));
   }
   return Status::OK();
 }

@@ -300,8 +300,9 @@ bool b200_call(B200Context ctx, const B200Value* params, int num_params, const B
 bool b200_if(B200Context ctx, B200Value pred, const B200Value* true_outputs, const B200Value* false_outputs,
              int num_outputs, B200Value* results, B200Error* err);
 /* While: state -> cond(state) scalar Bool; state -> body(state) of the same shapes; results = the final state.  cond and
- * body are compiled into two sub-plans when the parent is compiled; the loop runs them on the device's stream and
- * reads the one-byte condition back each iteration. */
+ * body are compiled into two sub-plans when the parent is compiled.  On the executable's first runs the host drives the
+ * loop (it reads the one-byte condition back each trip); once the plan replays as a CUDA graph the loop is a
+ * conditional node and runs entirely on the device.  At most 1 000 000 trips (ref executable.go:241). */
 bool b200_while(B200Context ctx, const B200Value* cond_params, B200Value cond_output, const B200Value* body_params,
                 const B200Value* body_outputs, int num_state, const B200Value* initial_state, B200Value* results,
                 B200Error* err);

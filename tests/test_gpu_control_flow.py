@@ -98,6 +98,48 @@ def test_while_runs_the_same_on_every_execution(b200, backend):
     builder.Finalize()
 
 
+def test_while_on_the_device_when_the_plan_is_replayed(b200, backend):
+    # the third run on the same buffers replays the plan as a CUDA graph in which the loop is a conditional node: cond,
+    # body and the trip decision all run on the device.  Same results as the host-driven runs before it, for several
+    # trip counts through ONE recorded graph (the count is data), including zero trips.
+    rng = np.random.default_rng(7)
+    x0 = rng.standard_normal((64, 96)).astype(np.float32)
+    w = rng.standard_normal((64, 96)).astype(np.float32)
+    builder = backend.Builder("device-loop")
+    f = builder.Main()
+    x = f.Parameter("x", _sh(b200, np.float32, 64, 96))
+    ww = f.Parameter("w", _sh(b200, np.float32, 64, 96))
+    n = f.Parameter("n", _sh(b200, np.int32))
+    si, sx = _sh(b200, np.int32), _sh(b200, np.float32, 64, 96)
+    cond = closure(f, [si, sx], lambda c, i, v: [c.LessThan(i, n)])
+    body = closure(f, [si, sx], lambda c, i, v: [c.Add(i, _c(c, 1, np.int32)), c.Tanh(c.Add(c.Mul(v, ww), c.Reverse(v, 1)))])
+    i_end, x_end = f.While(cond, body, _c(f, 0, np.int32), x)
+    f.Return([i_end, f.Neg(x_end)], None)
+    exe = builder.Compile()
+    assert "on the device when replayed" in exe.Describe(), exe.Describe()
+    bx, bw = backend.FromNumpy(x0), backend.FromNumpy(w)
+    bn = backend.FromNumpy(np.array(0, dtype=np.int32))
+
+    def want(trips):
+        v = x0.astype(np.float64)
+        for _ in range(trips):
+            v = np.tanh(v * w.astype(np.float64) + v[:, ::-1])
+        return -v
+
+    for trips in (3, 3, 3, 0, 7, 1, 25, 0, 3):   # runs 1-2 are driven by the host, the rest replay the graph
+        backend.BufferFinalize(bn)
+        bn = backend.FromNumpy(np.array(trips, dtype=np.int32))   # the freed block comes back: same address, new count
+        outs = exe.Execute([bx, bw, bn], None, 0)
+        got_i, got_x = (backend.ToNumpy(o) for o in outs)
+        for o in outs:
+            backend.BufferFinalize(o)
+        assert int(got_i) == trips
+        ok, viol = compare(got_x, want(trips).astype(np.float32), 2e-5, 1.0)
+        assert ok, (trips, viol)
+    exe.Finalize()
+    builder.Finalize()
+
+
 def test_while_refusals(b200, backend):
     builder = backend.Builder("bad")
     f = builder.Main()
