@@ -249,7 +249,15 @@ struct GemmParams {
   int num_c_extra = 0;
   // batch strides in elements; 0 on an operand broadcasts it over the batch
   int64_t a_batch_stride = -1, b_batch_stride = -1;  // -1 = dense (m*k, k*n)
+  // fp32 on the tensor-core path: room for the three bf16 planes of both operands (gemm_split_scratch_bytes).  Without
+  // it the launch allocates them itself, which keeps the step out of recorded plans.
+  void* split_scratch = nullptr;
+  int64_t split_scratch_bytes = 0;
 };
+inline int64_t gemm_split_scratch_bytes(int64_t batch, int64_t m, int64_t n, int64_t k) {
+  const int64_t a = (batch * m * k * 6 + 255) / 256 * 256, b = (batch * k * n * 6 + 255) / 256 * 256;
+  return a + b;
+}
 Status gemm(Device* dev, const GemmParams& p);
 // The tensor-core path alone: *taken is false (and nothing is launched) when the problem is outside its rules.
 Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken);

@@ -942,15 +942,24 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
   void* tmp_b = nullptr;
   int64_t planes = 1, a_plane_stride = 0, b_plane_stride = 0;
   const int64_t a_elems = p.batch * p.m * p.k, b_elems = p.batch * p.k * p.n;
+  void* planes_a = nullptr;
+  void* planes_b = nullptr;
   if (is32) {
-    // three bf16 planes per operand
-    Status s = dev->Alloc(a_elems * 6, &tmp_a);
-    if (s.ok()) s = dev->Alloc(b_elems * 6, &tmp_b);
-    if (!s.ok()) { dev->Free(tmp_a); return s; }
+    // three bf16 planes per operand: in the caller's scratch when it gave one, else allocated for this launch
+    if (p.split_scratch && p.split_scratch_bytes >= gemm_split_scratch_bytes(p.batch, p.m, p.n, p.k) && aligned16(p.split_scratch)) {
+      planes_a = p.split_scratch;
+      planes_b = reinterpret_cast<char*>(p.split_scratch) + (a_elems * 6 + 255) / 256 * 256;
+    } else {
+      Status s = dev->Alloc(a_elems * 6, &tmp_a);
+      if (s.ok()) s = dev->Alloc(b_elems * 6, &tmp_b);
+      if (!s.ok()) { dev->Free(tmp_a); return s; }
+      planes_a = tmp_a;
+      planes_b = tmp_b;
+    }
     auto grid_for = [&](int64_t n) { int64_t g = (n + 255) / 256, cap = (int64_t)dev->sm_count() * 16; return (unsigned)(g < cap ? g : cap); };
-    split3_kernel<<<grid_for(a_elems), 256, 0, stream>>>((const float*)p.a, (__nv_bfloat16*)tmp_a, a_elems);
-    split3_kernel<<<grid_for(b_elems), 256, 0, stream>>>((const float*)p.b, (__nv_bfloat16*)tmp_b, b_elems);
-    a = tmp_a; b = tmp_b;
+    split3_kernel<<<grid_for(a_elems), 256, 0, stream>>>((const float*)p.a, (__nv_bfloat16*)planes_a, a_elems);
+    split3_kernel<<<grid_for(b_elems), 256, 0, stream>>>((const float*)p.b, (__nv_bfloat16*)planes_b, b_elems);
+    a = planes_a; b = planes_b;
     planes = 3; a_plane_stride = a_elems; b_plane_stride = b_elems;
   }
   auto cleanup = [&]() { dev->Free(tmp_a); dev->Free(tmp_b); };

@@ -1177,9 +1177,14 @@ class Planner {
     if (bias) st.reads.push_back(bias_slot);
     if (residual) st.reads.push_back(res_slot);
     st.writes = {gemm_out};
-    st.capturable = x->dtype != B200_FLOAT32;   // the fp32 path allocates its bf16 planes per launch
-    st.run = [gp, a_slot, b_slot, bias_slot, res_slot, gemm_out](Device* dev, void* const* p) -> Status {
+    // fp32 on the tensor cores splits both operands into bf16 planes: their room comes from the plan's arena, so the step
+    // allocates nothing and can be recorded
+    const int64_t split_bytes = x->dtype == B200_FLOAT32 ? k::gemm_split_scratch_bytes(B, M, N, K) : 0;
+    const int split_slot = split_bytes > 0 ? NewTemp(split_bytes) : -1;
+    if (split_slot >= 0) st.writes.push_back(split_slot);
+    st.run = [gp, a_slot, b_slot, bias_slot, res_slot, gemm_out, split_slot, split_bytes](Device* dev, void* const* p) -> Status {
       k::GemmParams q = gp;
+      if (split_slot >= 0) { q.split_scratch = p[split_slot]; q.split_scratch_bytes = split_bytes; }
       q.a = p[a_slot];
       q.b = p[b_slot];
       q.c = p[gemm_out];

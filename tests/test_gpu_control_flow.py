@@ -140,6 +140,35 @@ def test_while_on_the_device_when_the_plan_is_replayed(b200, backend):
     builder.Finalize()
 
 
+def test_while_with_an_fp32_contraction_in_its_body_replays_on_the_device(b200, backend):
+    # the fp32 DotGeneral's split planes live in the sub-plan's arena, so the loop is recordable
+    rng = np.random.default_rng(8)
+    x0 = rng.standard_normal((128, 128)).astype(np.float32)
+    w = (0.1 * rng.standard_normal((128, 128))).astype(np.float32)
+    builder = backend.Builder("device-loop-f32")
+    f = builder.Main()
+    x = f.Parameter("x", _sh(b200, np.float32, 128, 128))
+    ww = f.Parameter("w", _sh(b200, np.float32, 128, 128))
+    si, sx = _sh(b200, np.int32), _sh(b200, np.float32, 128, 128)
+    cond = closure(f, [si, sx], lambda c, i, v: [c.LessThan(i, _c(c, 4, np.int32))])
+    body = closure(f, [si, sx], lambda c, i, v: [c.Add(i, _c(c, 1, np.int32)), c.Tanh(c.DotGeneral(v, [1], [], ww, [0], []))])
+    f.Return([f.While(cond, body, _c(f, 0, np.int32), x)[1]], None)
+    exe = builder.Compile()
+    assert "on the device when replayed" in exe.Describe(), exe.Describe()
+    v = x0.astype(np.float64)
+    for _ in range(4):
+        v = np.tanh(v @ w.astype(np.float64))
+    bx, bw = backend.FromNumpy(x0), backend.FromNumpy(w)
+    for run in range(4):
+        (out,) = exe.Execute([bx, bw], None, 0)
+        got = backend.ToNumpy(out)
+        backend.BufferFinalize(out)
+        ok, viol = compare(got, v.astype(np.float32), 1e-5, 1.0)
+        assert ok, (run, viol)
+    exe.Finalize()
+    builder.Finalize()
+
+
 def test_while_refusals(b200, backend):
     builder = backend.Builder("bad")
     f = builder.Main()
