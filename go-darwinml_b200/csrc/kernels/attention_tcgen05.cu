@@ -34,6 +34,7 @@
 #include <mutex>
 
 #include "../kernels.h"
+#include "pdl.cuh"
 #include "sm100_ptx.cuh"
 #include "tma_host.h"
 
@@ -70,11 +71,13 @@ struct AttArgs {
   int is_f16;
   float scale_log2e;          // scale * log2(e), > 0
   int* err_flag;
-  int* next_item;             // zero before the launch: work items beyond the first of each CTA are taken from here
+  int* next_item;             // [0] work items beyond the first of each CTA are taken from here; [1] CTAs that have finished
 };
 
-// The work-item counter of a launch (one per device: the array lives in each device's copy of the module).  Launches of
-// one device are ordered on its stream, and each is preceded by a memset of the counter on that stream.
+// The work-item counter of a launch and the count of its finished CTAs (one pair per device: the array lives in each
+// device's copy of the module).  Both are zero between launches: the last CTA to finish puts them back, so no memset
+// has to sit between this kernel and the one before it (which would keep it from starting under that kernel's tail).
+// Launches of one device are ordered on its stream.
 __device__ int g_next_item[4];
 
 template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
@@ -199,6 +202,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const bool misaligned = *failed != 0;
+  // everything above ran under the tail of the kernel before this one (when launched as its programmatic dependent)
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (misaligned) {
     // nothing was issued; fall through to the teardown
@@ -478,6 +484,15 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     tc_fence_after();
     tmem_dealloc(tmem_base, ATT_TMEM_COLS);
   }
+  // the last CTA out zeroes the counters for the next launch (every CTA's draws from next_item precede its arrival here)
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(g.next_item + 1, 1) == (int)gridDim.x - 1) {
+      g.next_item[0] = 0;
+      g.next_item[1] = 0;
+      __threadfence();
+    }
+  }
 }
 
 }  // namespace
@@ -527,7 +542,6 @@ Status attention(Device* dev, const AttentionParams& p) {
     void* ctr = nullptr;
     B200_CUDA_TRY(cudaGetSymbolAddress(&ctr, g_next_item));
     g.next_item = reinterpret_cast<int*>(ctr);
-    B200_CUDA_TRY(cudaMemsetAsync(ctr, 0, sizeof(int), dev->stream()));
   }
   const int64_t nq = (p.Sq + QT * BQ - 1) / (QT * BQ);
   const int64_t items = nq * p.H * p.B;
@@ -547,9 +561,10 @@ Status attention(Device* dev, const AttentionParams& p) {
     }
   }
   if (e == cudaSuccess) {
-    if (f16) attention_kernel<__half><<<(unsigned)grid, ATT_THREADS, ATT_SMEM, dev->stream()>>>(tq, tk, tv, g);
-    else attention_kernel<__nv_bfloat16><<<(unsigned)grid, ATT_THREADS, ATT_SMEM, dev->stream()>>>(tq, tk, tv, g);
-  } else {
+    e = f16 ? launch_dependent(attention_kernel<__half>, (unsigned)grid, ATT_THREADS, ATT_SMEM, dev->stream(), tq, tk, tv, g)
+            : launch_dependent(attention_kernel<__nv_bfloat16>, (unsigned)grid, ATT_THREADS, ATT_SMEM, dev->stream(), tq, tk, tv, g);
+  }
+  if (e != cudaSuccess) {
     cudaGetLastError();
     return Status::Cuda(strfmt("attention: %s", cudaGetErrorString(e)));
   }

@@ -40,6 +40,7 @@
 
 #include "../kernels.h"
 #include "gemm_common.cuh"
+#include "pdl.cuh"
 #include "sm100_ptx.cuh"
 #include "tma_host.h"
 
@@ -506,6 +507,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above ran under the tail of the kernel before this one (when launched as its programmatic dependent);
+  // from here on its results are read and its operands' memory may be overwritten
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer ---
@@ -706,6 +711,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   cluster_sync_all();  // both CTAs' barriers exist before either signals the other's
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above ran under the tail of the kernel before this one (when launched as its programmatic dependent);
+  // from here on its results are read and its operands' memory may be overwritten
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer ---
@@ -903,6 +912,7 @@ Status make_operand_map(CUtensorMap* map, const void* base, bool f16, int64_t in
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+
 }  // namespace
 
 // Ragged rows (see TcArgs::rag): a dense 16-bit result whose row length is not a multiple of 8, written with aligned
@@ -1048,7 +1058,7 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
       }                                                                                                                     \
     }                                                                                                                       \
     const int64_t grid = g.total_tiles < dev->sm_count() ? g.total_tiles : dev->sm_count();                                 \
-    if (e == cudaSuccess) gemm_tcgen05_kernel<OutT><<<(unsigned)grid, S_NUM_THREADS, S_SMEM_BYTES, stream>>>(tm_a, tm_b, tm_c, tm_r, g); \
+    if (e == cudaSuccess) e = launch_dependent(gemm_tcgen05_kernel<OutT>, (unsigned)grid, S_NUM_THREADS, S_SMEM_BYTES, stream, tm_a, tm_b, tm_c, tm_r, g); \
   } while (0)
 #define LAUNCH_TC_PAIR(OutT, SLOT)                                                                                          \
   do {                                                                                                                      \
@@ -1078,7 +1088,7 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken) {
     const int64_t cap = max_pairs[SLOT][dev->ordinal()];                                                                    \
     const int64_t pairs = g.total_tiles < cap ? g.total_tiles : cap;                                                        \
     if (e == cudaSuccess)                                                                                                   \
-      gemm_tcgen05_pair_kernel<OutT><<<(unsigned)(2 * pairs), S_NUM_THREADS, P_SMEM_BYTES, stream>>>(tm_a, tm_b, tm_c, tm_r, g); \
+      e = launch_dependent(gemm_tcgen05_pair_kernel<OutT>, (unsigned)(2 * pairs), S_NUM_THREADS, P_SMEM_BYTES, stream, tm_a, tm_b, tm_c, tm_r, g); \
   } while (0)
   if (use_pair) {
     if (is32) LAUNCH_TC_PAIR(float, 3);

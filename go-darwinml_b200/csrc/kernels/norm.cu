@@ -29,6 +29,7 @@
 //     partials are double-buffered in shared memory so a round costs ONE named barrier, and the cross-warp step is
 //     a few broadcast reads instead of a second shuffle tree.
 #include "../kernels.h"
+#include "pdl.cuh"
 #include "rowwise.cuh"
 
 namespace b200 {
@@ -82,6 +83,8 @@ __global__ void __launch_bounds__(TPR > 256 ? TPR : 256, NormOcc<ITERS, TPR>::kC
   constexpr int V = Cvt<T>::N;
   constexpr int BLOCK = TPR > 256 ? TPR : 256;
   constexpr int GROUPS = BLOCK / TPR;
+  pdl_launch_dependents();   // the next kernel may be scheduled as SMs fall free; it waits for this one in its own pdl_wait
+  pdl_wait();                // launched as a programmatic dependent: the kernel before this one has completed
   __shared__ float red[2 * 32];   // per group: 2 phases x warps per row
   const int group = threadIdx.x / TPR;
   const int t = threadIdx.x % TPR;
@@ -231,10 +234,10 @@ template <typename T, int ITERS, int TPR, bool RMS>
 void launch_params(const NArgs& a, unsigned grid, cudaStream_t s) {
   constexpr int BLOCK = TPR > 256 ? TPR : 256;
   const bool hg = a.gamma != nullptr, hb = a.beta != nullptr && !RMS;
-  if (hg && hb) norm_rows_kernel<T, ITERS, TPR, RMS, true, true><<<grid, BLOCK, 0, s>>>(a);
-  else if (hg) norm_rows_kernel<T, ITERS, TPR, RMS, true, false><<<grid, BLOCK, 0, s>>>(a);
-  else if (hb) norm_rows_kernel<T, ITERS, TPR, RMS, false, true><<<grid, BLOCK, 0, s>>>(a);
-  else norm_rows_kernel<T, ITERS, TPR, RMS, false, false><<<grid, BLOCK, 0, s>>>(a);
+  if (hg && hb) launch_dependent(norm_rows_kernel<T, ITERS, TPR, RMS, true, true>, grid, BLOCK, 0, s, a);
+  else if (hg) launch_dependent(norm_rows_kernel<T, ITERS, TPR, RMS, true, false>, grid, BLOCK, 0, s, a);
+  else if (hb) launch_dependent(norm_rows_kernel<T, ITERS, TPR, RMS, false, true>, grid, BLOCK, 0, s, a);
+  else launch_dependent(norm_rows_kernel<T, ITERS, TPR, RMS, false, false>, grid, BLOCK, 0, s, a);
 }
 
 template <typename T, int TPR, bool RMS>
