@@ -43,7 +43,7 @@ if ROOT not in sys.path:
 SM_SHAPE = (32, 16, 1024, 1024)
 NORM_SHAPE = (16384, 4096)
 EPS = 1e-6
-E2E_SLICES = 16  # leading-axis slices of the end-to-end leg (32 / 16 softmax batches, 16384 / 16 norm rows per slice)
+E2E_SLICES = int(os.environ.get("B200MLX_E2E_SLICES", "16"))  # leading-axis slices of the end-to-end leg (must divide 32 softmax batches and 16384 norm rows)
 
 
 def causal_softmax_bytes(shape, elt=4, vec_bytes=16):
