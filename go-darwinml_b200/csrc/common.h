@@ -96,7 +96,9 @@ class Device {
   Status CaptureStream(cudaStream_t* out);
   // A second private stream: the body of a While loop is recorded on it into the loop's conditional graph node while
   // the plan around the loop is being recorded on the capture stream (same holder of capture_mutex).
-  Status LoopStream(cudaStream_t* out);
+  // One such stream per nesting depth of loops (0 = outermost), at most kMaxLoopDepth.
+  static constexpr int kMaxLoopDepth = 4;
+  Status LoopStream(int depth, cudaStream_t* out);
   // Held from cudaStreamBeginCapture to cudaStreamEndCapture on the capture stream: the device has one such stream,
   // and two executables reaching their recording run at the same time would otherwise begin a capture on a stream
   // that is already capturing.
@@ -126,7 +128,7 @@ class Device {
   int ordinal_ = 0;
   int sm_count_ = 148;
   cudaStream_t stream_ = nullptr;
-  cudaStream_t copy_in_ = nullptr, copy_out_ = nullptr, capture_ = nullptr, loop_ = nullptr;
+  cudaStream_t copy_in_ = nullptr, copy_out_ = nullptr, capture_ = nullptr, loop_[kMaxLoopDepth] = {};
   int* error_flag_ = nullptr;
   std::atomic<bool> error_check_pending_{false};   // set by launching threads, read at synchronisation points
   std::mutex mu_, capture_mu_;

@@ -1554,7 +1554,7 @@ Status CloneClosure(Graph& dst, const std::vector<Node*>& params, const std::vec
   std::function<bool(Node*)> constant_only = [&](Node* n) -> bool {
     if (n->op == Op::Constant || n->op == Op::Iota) return true;
     if (n->op == Op::Parameter || n->op == Op::ClosureParam || n->in.empty()) return false;
-    if (n->op == Op::While || n->op == Op::WhileResult || n->num_elements() > 4096) return false;
+    if (n->op == Op::While || n->op == Op::WhileResult || n->num_elements() > 4096) return false;   // an outer loop's result is fed, not re-run
     for (Node* i : n->in)
       if (!constant_only(i)) return false;
     return true;
@@ -1563,15 +1563,9 @@ Status CloneClosure(Graph& dst, const std::vector<Node*>& params, const std::vec
   std::function<Node*(Node*)> clone = [&](Node* n) -> Node* {
     auto it = map.find(n);
     if (it != map.end()) return it->second;
-    if (n->op == Op::While || n->op == Op::WhileResult) {
-      if (same_graph && !depends(n)) return map[n] = n;
-      failed = Status::Unsupported("a While inside a closure that is compiled or called separately is not supported");
-      return n;
-    }
-    if (n->op == Op::ClosureParam) {
-      failed = Status::Invalid("closure uses a parameter of another closure");
-      return n;
-    }
+    // a While (and the picks of its results) is copied like any other node: its cond / body sub-graphs belong to the
+    // context and are named by index, its operands (initial state and captured values) are cloned or captured in turn
+    // (a parameter of an ENCLOSING closure is an outer value like any other: shared when inlining, fed when extracting)
     if (!depends(n)) {
       if (same_graph) return map[n] = n;
       if (!constant_only(n)) {   // an outer value: feed it

@@ -135,7 +135,7 @@ struct IndexMap {
 };
 
 // Rewrites + plan + arena for one graph (the context's own, or a While's cond / body sub-graph of `owner`).
-Status CompileGraph(Ctx* owner, Graph& graph, std::vector<Node*> feeds, std::vector<Node*> targets, std::unique_ptr<Exec>* out);
+Status CompileGraph(Ctx* owner, Graph& graph, std::vector<Node*> feeds, std::vector<Node*> targets, std::unique_ptr<Exec>* out, int loop_depth = 0);
 
 // Runs a sub-plan's steps on the device's stream with caller-provided input and output addresses.
 Status RunSubPlan(Exec* ex, void* const* in_ptrs, void* const* out_ptrs) {
@@ -173,11 +173,11 @@ __global__ void while_set_cond_kernel(cudaGraphConditionalHandle handle, const u
 // cond runs once in front of the node; the node's body graph (recorded on the device's loop stream) runs body, copies the
 // new state over the current one, runs cond again and sets the node's condition, all on the device.  `run_cond` and
 // `run_body` launch the sub-plans on dev->stream(), whatever it is at the time.
-Status RecordWhileNode(Device* dev, const std::function<Status()>& run_cond, const std::function<Status()>& run_body_and_advance,
+Status RecordWhileNode(Device* dev, int depth, const std::function<Status()>& run_cond, const std::function<Status()>& run_body_and_advance,
                        const unsigned char* pred, int* trips) {
   cudaStream_t ps = dev->stream();
   cudaStream_t ls = nullptr;
-  B200_TRY(dev->LoopStream(&ls));
+  B200_TRY(dev->LoopStream(depth, &ls));   // a loop inside this loop's body records on the next depth's stream
   B200_CUDA_TRY(cudaMemsetAsync(trips, 0, sizeof(int), ps));
   B200_TRY(run_cond());
   cudaStreamCaptureStatus status;
@@ -222,7 +222,7 @@ Status RecordWhileNode(Device* dev, const std::function<Status()>& run_cond, con
 
 class Planner {
  public:
-  Planner(Ctx* ctx, Graph& graph, Exec* exec) : ctx_(ctx), ex_(exec), g_(graph) {}
+  Planner(Ctx* ctx, Graph& graph, Exec* exec, int loop_depth = 0) : ctx_(ctx), ex_(exec), g_(graph), loop_depth_(loop_depth) {}
 
   Status Run(const std::vector<Node*>& feeds, const std::vector<Node*>& targets) {
     const int n = (int)g_.nodes.size();
@@ -312,6 +312,7 @@ class Planner {
   Ctx* ctx_;
   Exec* ex_;
   Graph& g_;
+  int loop_depth_;   // how many While loops enclose the graph being planned
   std::vector<bool> live_;
   std::vector<int> uses_;
   std::vector<int> slot_of_;  // node id -> slot (materialised nodes; views resolve through ViewBase)
@@ -1521,7 +1522,7 @@ class Planner {
   // host: run cond, read its one byte back, stop or run body into a second set of state buffers and swap.  The reference
   // also loops on the host, re-entering a whole executable per iteration (ref mpsgraph executable.go:219-300).
   Status EmitWhile(Node* w) {
-    if (!ctx_) return Status::Unsupported("compile: a While inside a While's cond or body is not supported");
+    if (loop_depth_ >= Device::kMaxLoopDepth) return Status::Unsupported("compile: While loops nested deeper than 4");
     const int n_state = (int)w->ia[0];
     const int n_cc = (int)w->ia[3], n_bc = (int)w->ia[4];
     if (w->ia[1] < 0 || w->ia[2] < 0 || (size_t)w->ia[1] >= ctx_->subgraphs.size() || (size_t)w->ia[2] >= ctx_->subgraphs.size())
@@ -1530,9 +1531,9 @@ class Planner {
     std::unique_ptr<Exec> cond, body;
     SubGraph* csg = ctx_->subgraphs[(size_t)w->ia[1]].get();
     SubGraph* bsg = ctx_->subgraphs[(size_t)w->ia[2]].get();
-    Status s = CompileGraph(nullptr, csg->graph, csg->feeds, csg->targets, &cond);
+    Status s = CompileGraph(ctx_, csg->graph, csg->feeds, csg->targets, &cond, loop_depth_ + 1);
     if (!s.ok()) return Status{s.code, "While cond: " + s.msg};
-    s = CompileGraph(nullptr, bsg->graph, bsg->feeds, bsg->targets, &body);
+    s = CompileGraph(ctx_, bsg->graph, bsg->feeds, bsg->targets, &body, loop_depth_ + 1);
     if (!s.ok()) return Status{s.code, "While body: " + s.msg};
     Exec* ce = cond.get();
     Exec* be = body.get();
@@ -1563,7 +1564,7 @@ class Planner {
     for (const Step& bs : be->steps) recordable = recordable && bs.capturable;
     if (recordable) {
       cudaStream_t ls = nullptr;
-      B200_TRY(ex_->dev->LoopStream(&ls));   // created now: not while a recording is under way
+      B200_TRY(ex_->dev->LoopStream(loop_depth_, &ls));   // created now: not while a recording is under way
     }
     Step st;
     st.desc = strfmt("while[state=%d cond: %d steps, %d captures; body: %d steps, %d captures%s]", n_state, (int)ce->steps.size(), n_cc,
@@ -1575,6 +1576,7 @@ class Planner {
     st.capturable = recordable;
     st.wants_graph = recordable;
     st.launches = 0;         // counted per run: unknown at compile time
+    const int depth = loop_depth_;
     st.run = [=](Device* dev, void* const* p) -> Status {
       B200_TRY(dev->MakeCurrent());
       std::vector<void*> cur(n_state), nxt(n_state);
@@ -1600,7 +1602,7 @@ class Planner {
           return Status::OK();
         };
         dev->kernel_error_flag();   // the loop may raise the error word: have the next synchronisation point read it
-        return RecordWhileNode(dev, run_cond, run_body, reinterpret_cast<const unsigned char*>(pred),
+        return RecordWhileNode(dev, depth, run_cond, run_body, reinterpret_cast<const unsigned char*>(pred),
                                reinterpret_cast<int*>(reinterpret_cast<char*>(pred) + 64));
       }
       for (int64_t iter = 0;; ++iter) {
@@ -2048,7 +2050,7 @@ class Planner {
   }
 };
 
-Status CompileGraph(Ctx* owner, Graph& graph, std::vector<Node*> feeds, std::vector<Node*> targets, std::unique_ptr<Exec>* out) {
+Status CompileGraph(Ctx* owner, Graph& graph, std::vector<Node*> feeds, std::vector<Node*> targets, std::unique_ptr<Exec>* out, int loop_depth) {
   Device* dev = nullptr;
   B200_TRY(Device::Get(graph.device, &dev));
   RewriteRmsNorm(graph, targets);
@@ -2057,7 +2059,7 @@ Status CompileGraph(Ctx* owner, Graph& graph, std::vector<Node*> feeds, std::vec
   RewriteRope(graph, targets);
   std::unique_ptr<Exec> ex(new Exec());
   ex->dev = dev;
-  Planner planner(owner, graph, ex.get());
+  Planner planner(owner, graph, ex.get(), loop_depth);
   B200_TRY(planner.Run(feeds, targets));
   if (ex->arena_bytes > 0) B200_TRY(ex->dev->Alloc(ex->arena_bytes, &ex->arena));
   static const bool graphs_on = []() { const char* v = getenv("B200MLX_GRAPHS"); return !(v && v[0] == '0'); }();

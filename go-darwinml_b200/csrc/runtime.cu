@@ -84,13 +84,14 @@ StreamOverride::~StreamOverride() {
   tls_override_stream = prev_stream_;
 }
 
-Status Device::LoopStream(cudaStream_t* out) {
+Status Device::LoopStream(int depth, cudaStream_t* out) {
+  if (depth < 0 || depth >= kMaxLoopDepth) return Status::Unsupported("While: loops nested deeper than 4");
   std::lock_guard<std::mutex> lock(mu_);
-  if (!loop_) {
+  if (!loop_[depth]) {
     B200_CUDA_TRY(cudaSetDevice(ordinal_));
-    B200_CUDA_TRY(cudaStreamCreateWithFlags(&loop_, cudaStreamNonBlocking));
+    B200_CUDA_TRY(cudaStreamCreateWithFlags(&loop_[depth], cudaStreamNonBlocking));
   }
-  *out = loop_;
+  *out = loop_[depth];
   return Status::OK();
 }
 

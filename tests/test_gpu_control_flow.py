@@ -169,6 +169,67 @@ def test_while_with_an_fp32_contraction_in_its_body_replays_on_the_device(b200, 
     builder.Finalize()
 
 
+def test_nested_loops(b200, backend):
+    # a loop inside a loop's body (the reference allows one control-flow op per function, ref function.go:407-409): the
+    # inner loop's trip count depends on the outer counter, its body uses the outer body's parameters and a value of main
+    rng = np.random.default_rng(9)
+    x0 = rng.standard_normal((5, 40)).astype(np.float32)
+    y = (0.1 * rng.standard_normal((5, 40))).astype(np.float32)
+
+    def build(f, x, yy):
+        si, sx = _sh(b200, np.int32), _sh(b200, np.float32, 5, 40)
+
+        def outer_body(c, i, v):
+            # inner: j from 0 to i: w = w * 0.5 + v * y   (v: the outer body's parameter, yy: a value of main)
+            icond = closure(c, [si, sx], lambda d, j, w: [d.LessThan(j, i)])
+            ibody = closure(c, [si, sx], lambda d, j, w: [d.Add(j, _c(d, 1, np.int32)),
+                                                          d.Add(d.Mul(w, d.BroadcastInDim(_c(d, 0.5, np.float32), sx, [])), d.Mul(v, yy))])
+            _, w_end = c.While(icond, ibody, _c(c, 0, np.int32), v)
+            return [c.Add(i, _c(c, 1, np.int32)), c.Tanh(w_end)]
+
+        cond = closure(f, [si, sx], lambda c, i, v: [c.LessThan(i, _c(c, 4, np.int32))])
+        body = closure(f, [si, sx], outer_body)
+        i_end, v_end = f.While(cond, body, _c(f, 0, np.int32), x)
+        return i_end, v_end
+
+    got = assert_parity(b200, backend, build, [x0, y], rtol=1e-5, atol_scale=1.0, what="nested loops")
+    assert int(got[0]) == 4
+    # and replayed: the inner loop is a conditional node inside the outer loop's body graph
+    builder = backend.Builder("nested")
+    f = builder.Main()
+    px, py = f.Parameter("x", _sh(b200, np.float32, 5, 40)), f.Parameter("y", _sh(b200, np.float32, 5, 40))
+    f.Return(list(build(f, px, py)), None)
+    exe = builder.Compile()
+    bx, by = backend.FromNumpy(x0), backend.FromNumpy(y)
+    for run in range(4):
+        outs = exe.Execute([bx, by], None, 0)
+        v = backend.ToNumpy(outs[1])
+        for o in outs:
+            backend.BufferFinalize(o)
+        np.testing.assert_array_equal(v, got[1])   # every run, host-driven or replayed, gives the same bits
+    exe.Finalize()
+    builder.Finalize()
+
+
+def test_a_loop_inside_a_function_that_is_called_twice(b200, backend):
+    def build(f, x, n):
+        si, sx = _sh(b200, np.int32), _sh(b200, np.float32, 3, 50)
+
+        def repeat(c, v, count):   # v <- tanh(v + 0.25) `count` times
+            cond = closure(c, [si, sx], lambda d, j, w: [d.LessThan(j, count)])
+            body = closure(c, [si, sx], lambda d, j, w: [d.Add(j, _c(d, 1, np.int32)),
+                                                         d.Tanh(d.Add(w, d.BroadcastInDim(_c(d, 0.25, np.float32), sx, [])))])
+            return [c.While(cond, body, _c(c, 0, np.int32), v)[1]]
+
+        fn = named_function(f, "repeat", [sx, si], repeat)
+        (a,) = f.Call(fn, x, n)
+        (b,) = f.Call(fn, f.Neg(a), f.Add(n, n))   # the same function, other values, twice the trips
+        return a, b
+
+    x = np.random.default_rng(10).standard_normal((3, 50)).astype(np.float32)
+    assert_parity(b200, backend, build, [x, np.array(3, dtype=np.int32)], rtol=1e-5, atol_scale=1.0, what="loop in a function")
+
+
 def test_while_refusals(b200, backend):
     builder = backend.Builder("bad")
     f = builder.Main()
