@@ -500,7 +500,8 @@ class Function:
         return [Value(res[i], self) for i in range(n)]
 
     def If(self, pred, true_branch, false_branch) -> List[Value]:
-        """ref function.go:492-560.  Both branches are evaluated (they are pure) and the outputs selected by pred."""
+        """ref function.go:492-560.  Light branches are both evaluated (they are pure) and the outputs selected by pred; heavy
+        ones (contractions, reductions, loops ...) become two sub-plans of which one runs."""
         ph = self._h(pred, "If: pred")
         if pred.shape.Rank() != 0 or pred.shape.DType != dtypes.Bool:
             raise BackendError(1, f"If: pred must be scalar bool, got {pred.shape}")

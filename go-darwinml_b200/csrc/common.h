@@ -197,6 +197,8 @@ enum class Op : int {
   // control flow over closures (sub-graphs of the same graph whose inputs are ClosureParam nodes): While is the loop itself
   // (no value), WhileResult picks one of its final state values; ArgSort is the permutation a Sort applies to its inputs
   ClosureParam, While, WhileResult, ArgSort,
+  // If with branches too heavy to evaluate both: runs one of two sub-plans; IfResult picks one of its outputs
+  If, IfResult,
   kNumOps
 };
 const char* op_name(Op op);

@@ -11,6 +11,7 @@
 #include <functional>
 #include <set>
 #include <unordered_map>
+#include <unordered_set>
 
 #include "common.h"
 
@@ -29,7 +30,7 @@ const char* op_name(Op op) {
       "Cast", "Reshape", "Transpose", "BroadcastInDim", "Slice", "Concatenate", "Reverse", "Pad", "DynamicSlice", "DynamicUpdateSlice",
       "DotGeneral", "Reduce", "ArgMinMax", "Gather",
       "Softmax", "SoftmaxMasked", "LayerNorm", "RmsNorm", "Attention", "Rope", "Scatter", "RngBits",
-      "ClosureParam", "While", "WhileResult", "ArgSort"};
+      "ClosureParam", "While", "WhileResult", "ArgSort", "If", "IfResult"};
   static_assert(sizeof(names) / sizeof(names[0]) == (size_t)Op::kNumOps, "op_name table out of date");
   return names[(int)op];
 }
@@ -1419,6 +1420,64 @@ bool b200_if(B200Context ctx, B200Value pred, const B200Value* true_outputs, con
     if (t[i]->dtype != f[i]->dtype || t[i]->dims != f[i]->dims) s = Status::Invalid(strfmt("If: output %d shapes must match", i));
   if (s.ok() && (num_outputs < 1 || !results)) s = Status::Invalid("If: the branches return nothing");
   if (!s.ok()) { set_error(err, s); return false; }
+  // Light branches (elementwise work on small values) are both evaluated and the outputs selected: no hand-off, and the
+  // select fuses into whatever consumes it.  A branch that holds a contraction, a reduction, a row kernel, a gather or
+  // a loop, or that produces a lot of data, is worth skipping: then each branch becomes a sub-graph and one of the two
+  // sub-plans runs (on the host's say-so on a plan's first runs, as a conditional graph node when the plan is replayed).
+  {
+    Ctx* c = reinterpret_cast<Ctx*>(ctx);
+    Graph& g = c->graph;
+    std::unordered_set<Node*> seen;
+    int64_t weight = 0;
+    bool heavy = false;
+    std::function<void(Node*)> walk = [&](Node* n) {
+      if (!seen.insert(n).second) return;
+      // what was built before the predicate exists whether or not a branch runs (the branches are built after it)
+      if (n->id <= p->id || n->op == Op::Parameter || n->op == Op::ClosureParam || n->op == Op::Constant) return;
+      switch (n->op) {
+        case Op::DotGeneral: case Op::Reduce: case Op::ArgMinMax: case Op::Gather: case Op::Scatter: case Op::Softmax: case Op::SoftmaxMasked:
+        case Op::LayerNorm: case Op::RmsNorm: case Op::Attention: case Op::While: case Op::WhileResult: case Op::ArgSort: case Op::RngBits:
+        case Op::If: case Op::IfResult:
+          heavy = true;
+          break;
+        default: break;
+      }
+      weight += n->num_elements();
+      if (seen.size() > 4096) { heavy = true; return; }
+      for (Node* i : n->in) walk(i);
+    };
+    for (Node* o : t) walk(o);
+    for (Node* o : f) walk(o);
+    static const int64_t kSelectLimit = []() { const char* v = getenv("B200MLX_IF_SELECT_ELEMENTS"); return v ? atoll(v) : (int64_t)(1 << 20); }();
+    if (heavy || weight > kSelectLimit) {
+      auto extract = [&](const std::vector<Node*>& outs, std::vector<Node*>* caps) -> int {
+        std::unique_ptr<SubGraph> sg(new SubGraph());
+        sg->graph.device = g.device;
+        std::vector<Node*> cap_params;
+        s = CloneClosure(sg->graph, {}, {}, outs, &sg->targets, caps, &cap_params);
+        if (!s.ok()) return -1;
+        sg->feeds = cap_params;
+        c->subgraphs.push_back(std::move(sg));
+        return (int)c->subgraphs.size() - 1;
+      };
+      std::vector<Node*> t_caps, f_caps;
+      const int t_sg = extract(t, &t_caps);
+      const int f_sg = t_sg >= 0 ? extract(f, &f_caps) : -1;
+      if (t_sg < 0 || f_sg < 0) { set_error(err, s); return false; }
+      std::vector<Node*> operands = {p};
+      operands.insert(operands.end(), t_caps.begin(), t_caps.end());
+      operands.insert(operands.end(), f_caps.begin(), f_caps.end());
+      Node* branch = g.Add(Op::If, B200_BOOL, {}, operands);
+      // ia = [n_outputs, true sub-graph, false sub-graph, n true captures, n false captures]
+      branch->ia = {num_outputs, t_sg, f_sg, (int64_t)t_caps.size(), (int64_t)f_caps.size()};
+      for (int i = 0; i < num_outputs; ++i) {
+        Node* r = g.Add(Op::IfResult, t[i]->dtype, t[i]->dims, {branch});
+        r->ia = {i};
+        results[i] = reinterpret_cast<B200Value>(r);
+      }
+      return true;
+    }
+  }
   for (int i = 0; i < num_outputs; ++i) {
     B200Value cond = b200_broadcast_in_dim(ctx, pred, t[i]->dims.data(), t[i]->rank(), nullptr, 0, err);
     if (!cond) return false;
@@ -1554,7 +1613,8 @@ Status CloneClosure(Graph& dst, const std::vector<Node*>& params, const std::vec
   std::function<bool(Node*)> constant_only = [&](Node* n) -> bool {
     if (n->op == Op::Constant || n->op == Op::Iota) return true;
     if (n->op == Op::Parameter || n->op == Op::ClosureParam || n->in.empty()) return false;
-    if (n->op == Op::While || n->op == Op::WhileResult || n->num_elements() > 4096) return false;   // an outer loop's result is fed, not re-run
+    if (n->op == Op::While || n->op == Op::WhileResult || n->op == Op::If || n->op == Op::IfResult || n->num_elements() > 4096)
+      return false;   // an outer loop's or branch's result is fed, not re-run
     for (Node* i : n->in)
       if (!constant_only(i)) return false;
     return true;

@@ -169,6 +169,57 @@ __global__ void while_set_cond_kernel(cudaGraphConditionalHandle handle, const u
   cudaGraphSetConditional(handle, go);
 }
 
+// Sets the conditions of the two conditional IF nodes of a branch: one runs when the predicate byte is set, the other
+// when it is not.  One thread.
+__global__ void if_set_cond_kernel(cudaGraphConditionalHandle on_true, cudaGraphConditionalHandle on_false, const unsigned char* pred) {
+  const unsigned v = *pred != 0 ? 1u : 0u;
+  cudaGraphSetConditional(on_true, v);
+  cudaGraphSetConditional(on_false, 1u - v);
+}
+
+// Records a two-way branch into the CUDA graph that `dev->stream()` is being captured into: two conditional IF nodes, one
+// per branch, whose body graphs are recorded on the loop stream of this nesting depth.
+Status RecordIfNodes(Device* dev, int depth, const unsigned char* pred, const std::function<Status()>& run_true,
+                     const std::function<Status()>& run_false) {
+  cudaStream_t ps = dev->stream();
+  cudaStream_t ls = nullptr;
+  B200_TRY(dev->LoopStream(depth, &ls));
+  cudaStreamCaptureStatus status;
+  unsigned long long id = 0;
+  cudaGraph_t parent = nullptr;
+  const cudaGraphNode_t* deps = nullptr;
+  size_t num_deps = 0;
+  B200_CUDA_TRY(cudaStreamGetCaptureInfo_v2(ps, &status, &id, &parent, &deps, &num_deps));
+  if (status != cudaStreamCaptureStatusActive || !parent) return Status::Invalid("If: the stream is not being recorded");
+  cudaGraphConditionalHandle handles[2];
+  for (int b = 0; b < 2; ++b) B200_CUDA_TRY(cudaGraphConditionalHandleCreate(&handles[b], parent, 0, cudaGraphCondAssignDefault));
+  if_set_cond_kernel<<<1, 1, 0, ps>>>(handles[0], handles[1], pred);
+  B200_TRY(dev->CheckLaunch("if_set_cond"));
+  for (int b = 0; b < 2; ++b) {
+    B200_CUDA_TRY(cudaStreamGetCaptureInfo_v2(ps, &status, &id, &parent, &deps, &num_deps));
+    cudaGraphNodeParams params = {};
+    params.type = cudaGraphNodeTypeConditional;
+    params.conditional.handle = handles[b];
+    params.conditional.type = cudaGraphCondTypeIf;
+    params.conditional.size = 1;
+    cudaGraphNode_t node = nullptr;
+    B200_CUDA_TRY(cudaGraphAddNode(&node, parent, deps, num_deps, &params));
+    cudaGraph_t body = params.conditional.phGraph_out[0];
+    B200_CUDA_TRY(cudaStreamUpdateCaptureDependencies(ps, &node, 1, cudaStreamSetCaptureDependencies));
+    B200_CUDA_TRY(cudaStreamBeginCaptureToGraph(ls, body, nullptr, nullptr, 0, cudaStreamCaptureModeThreadLocal));
+    Status st = Status::OK();
+    {
+      StreamOverride in_body(dev, ls);
+      st = b == 0 ? run_true() : run_false();
+    }
+    cudaGraph_t ended = nullptr;
+    const cudaError_t ce = cudaStreamEndCapture(ls, &ended);   // always: the loop stream must not stay in capture mode
+    B200_TRY(st);
+    if (ce != cudaSuccess) { cudaGetLastError(); return Status::Cuda(strfmt("If: recording a branch failed: %s", cudaGetErrorString(ce))); }
+  }
+  return Status::OK();
+}
+
 // Records a While loop into the CUDA graph that `dev->stream()` is being captured into, as a conditional WHILE node:
 // cond runs once in front of the node; the node's body graph (recorded on the device's loop stream) runs body, copies the
 // new state over the current one, runs cond again and sets the node's condition, all on the device.  `run_cond` and
@@ -397,6 +448,10 @@ class Planner {
       case Op::WhileResult:
         B200_TRY(EnsureMaterialized(x->in[0]));
         return slot_of_[x->id] >= 0 ? Status::OK() : Status::Invalid("compile: While did not produce its result");
+      case Op::If: return EmitIf(x);
+      case Op::IfResult:
+        B200_TRY(EnsureMaterialized(x->in[0]));
+        return slot_of_[x->id] >= 0 ? Status::OK() : Status::Invalid("compile: If did not produce its result");
       case Op::ClosureParam: return Status::Invalid("compile: a closure's parameter is used outside its closure");
       case Op::Softmax: return EmitSoftmax(x);
       case Op::SoftmaxMasked: return EmitSoftmaxMasked(x);
@@ -1511,6 +1566,78 @@ class Planner {
     if (sc >= 0) st.writes.push_back(sc);
     st.run = [=](Device* dev, void* const* p) -> Status {
       return k::arg_sort(dev, p[sa], p[so], dt, outer, n, inner, descending, sc >= 0 ? p[sc] : nullptr, scratch_bytes);
+    };
+    ex_->steps.push_back(std::move(st));
+    return Status::OK();
+  }
+
+  // If with heavy branches: in = predicate, then the outer values the true branch captures, then those of the false branch;
+  // ia = [n outputs, true sub-graph, false sub-graph, n true captures, n false captures].  Each branch compiles into a
+  // sub-plan that writes the result slots; the step runs ONE of them: on a plan's first runs the host reads the
+  // predicate byte and launches the chosen sub-plan, in a replayed plan two conditional IF graph nodes do it on the
+  // device.  The reference reads the predicate on the host and runs the chosen branch's executable
+  // (ref mpsgraph executable.go:286-318).
+  Status EmitIf(Node* w) {
+    if (loop_depth_ >= Device::kMaxLoopDepth) return Status::Unsupported("compile: control flow nested deeper than 4");
+    const int n_out = (int)w->ia[0];
+    const int n_tc = (int)w->ia[3], n_fc = (int)w->ia[4];
+    if (w->ia[1] < 0 || w->ia[2] < 0 || (size_t)w->ia[1] >= ctx_->subgraphs.size() || (size_t)w->ia[2] >= ctx_->subgraphs.size())
+      return Status::Invalid("compile: If names a sub-graph the context does not hold");
+    for (Node* i : w->in) B200_TRY(EnsureMaterialized(i));
+    std::unique_ptr<Exec> on_true, on_false;
+    SubGraph* tsg = ctx_->subgraphs[(size_t)w->ia[1]].get();
+    SubGraph* fsg = ctx_->subgraphs[(size_t)w->ia[2]].get();
+    Status s = CompileGraph(ctx_, tsg->graph, tsg->feeds, tsg->targets, &on_true, loop_depth_ + 1);
+    if (!s.ok()) return Status{s.code, "If trueBranch: " + s.msg};
+    s = CompileGraph(ctx_, fsg->graph, fsg->feeds, fsg->targets, &on_false, loop_depth_ + 1);
+    if (!s.ok()) return Status{s.code, "If falseBranch: " + s.msg};
+    Exec* te = on_true.get();
+    Exec* fe = on_false.get();
+    ex_->children.push_back(std::move(on_true));
+    ex_->children.push_back(std::move(on_false));
+    std::vector<int> in_slots, res_slots;
+    for (Node* i : w->in) in_slots.push_back(SlotOf(i));
+    std::vector<Node*> result_node(n_out, nullptr);
+    for (auto& up : g_.nodes)
+      if (up->op == Op::IfResult && up->in[0] == w && live_[up->id]) result_node[(size_t)up->ia[0]] = up.get();
+    for (int i = 0; i < n_out; ++i) {
+      const OutputDesc& od = te->outputs[(size_t)i];
+      res_slots.push_back(result_node[i] ? NewValueSlot(result_node[i]) : NewTemp(od.nbytes));
+    }
+    slot_of_[w->id] = in_slots[0];   // the branch node itself has no value of its own
+    static const bool device_loops = []() { const char* v = getenv("B200MLX_DEVICE_LOOPS"); return !(v && v[0] == '0'); }();
+    bool recordable = device_loops;
+    for (const Step& cs : te->steps) recordable = recordable && cs.capturable;
+    for (const Step& cs : fe->steps) recordable = recordable && cs.capturable;
+    if (recordable) {
+      cudaStream_t ls = nullptr;
+      B200_TRY(ex_->dev->LoopStream(loop_depth_, &ls));   // created now: not while a recording is under way
+    }
+    Step st;
+    st.desc = strfmt("if[outputs=%d true: %d steps, %d captures; false: %d steps, %d captures%s]", n_out, (int)te->steps.size(), n_tc,
+                     (int)fe->steps.size(), n_fc, recordable ? "; on the device when replayed" : "");
+    st.reads = in_slots;
+    st.writes = res_slots;
+    st.capturable = recordable;
+    st.wants_graph = recordable;
+    st.launches = 0;
+    const int depth = loop_depth_;
+    st.run = [=](Device* dev, void* const* p) -> Status {
+      B200_TRY(dev->MakeCurrent());
+      std::vector<void*> tin(n_tc), fin(n_fc), outs(n_out);
+      for (int i = 0; i < n_tc; ++i) tin[i] = p[in_slots[1 + i]];
+      for (int i = 0; i < n_fc; ++i) fin[i] = p[in_slots[1 + n_tc + i]];
+      for (int i = 0; i < n_out; ++i) outs[i] = p[res_slots[i]];
+      const unsigned char* pred = reinterpret_cast<const unsigned char*>(p[in_slots[0]]);
+      cudaStreamCaptureStatus recording = cudaStreamCaptureStatusNone;
+      B200_CUDA_TRY(cudaStreamIsCapturing(dev->stream(), &recording));
+      if (recording == cudaStreamCaptureStatusActive)
+        return RecordIfNodes(dev, depth, pred, [&]() { return RunSubPlan(te, tin.data(), outs.data()); },
+                             [&]() { return RunSubPlan(fe, fin.data(), outs.data()); });
+      unsigned char go = 0;
+      B200_CUDA_TRY(cudaMemcpyAsync(&go, pred, 1, cudaMemcpyDeviceToHost, dev->stream()));
+      B200_CUDA_TRY(cudaStreamSynchronize(dev->stream()));
+      return go ? RunSubPlan(te, tin.data(), outs.data()) : RunSubPlan(fe, fin.data(), outs.data());
     };
     ex_->steps.push_back(std::move(st));
     return Status::OK();

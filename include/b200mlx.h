@@ -296,7 +296,9 @@ B200Value b200_closure_parameter(B200Context ctx, int dtype, const int64_t* shap
 /* Call: the callee (params -> outputs) is inlined with `inputs` in place of its parameters. */
 bool b200_call(B200Context ctx, const B200Value* params, int num_params, const B200Value* outputs, int num_outputs,
                const B200Value* inputs, B200Value* results, B200Error* err);
-/* If: pred is a scalar Bool; both branches (no parameters) are evaluated and results[i] selects between them. */
+/* If: pred is a scalar Bool; the branches take no parameters.  Light (elementwise, small) branches are both evaluated
+ * and results[i] selects between them; heavy ones become two sub-plans of which one runs (chosen by the host on the
+ * executable's first runs, by conditional graph nodes on the device once the plan replays as a CUDA graph). */
 bool b200_if(B200Context ctx, B200Value pred, const B200Value* true_outputs, const B200Value* false_outputs,
              int num_outputs, B200Value* results, B200Error* err);
 /* While: state -> cond(state) scalar Bool; state -> body(state) of the same shapes; results = the final state.  cond and

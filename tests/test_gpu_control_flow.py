@@ -276,6 +276,62 @@ def test_if_with_tensor_outputs_and_captures(b200, backend, threshold):
     assert_parity(b200, backend, build, [x, w], rtol=1e-5, atol_scale=1.0, what="If")
 
 
+def test_heavy_branches_run_one_at_a_time_and_on_the_device_when_replayed(b200, backend):
+    # branches with contractions are not both evaluated: each is a sub-plan and one of them runs.  One executable, the
+    # predicate flipping between runs; runs 3+ replay the recorded plan, where two conditional graph nodes pick the branch.
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((64, 128)).astype(np.float32)
+    w = rng.standard_normal((128, 32)).astype(np.float32)
+    builder = backend.Builder("branch")
+    f = builder.Main()
+    px = f.Parameter("x", _sh(b200, np.float32, 64, 128))
+    pw = f.Parameter("w", _sh(b200, np.float32, 128, 32))
+    pt = f.Parameter("threshold", _sh(b200, np.float32))
+    pred = f.GreaterThan(f.ReduceSum(px), pt)
+    t = closure(f, [], lambda c: [c.DotGeneral(px, [1], [], pw, [0], []), c.Exp(px)])
+    e = closure(f, [], lambda c: [c.Neg(c.DotGeneral(c.Abs(px), [1], [], pw, [0], [])), c.Tanh(px)])
+    a, b = f.If(pred, t, e)
+    f.Return([f.Add(a, a), b], None)   # the branch's results feed further ops
+    exe = builder.Compile()
+    assert "if[" in exe.Describe() and "on the device when replayed" in exe.Describe(), exe.Describe()
+    x64, w64 = x.astype(np.float64), w.astype(np.float64)
+    want = {True: (2 * (x64 @ w64), np.exp(x64)), False: (-2 * (np.abs(x64) @ w64), np.tanh(x64))}
+    bx, bw = backend.FromNumpy(x), backend.FromNumpy(w)
+    bt = backend.FromNumpy(np.array(0, dtype=np.float32))
+    for thr in (-1e6, -1e6, -1e6, 1e6, -1e6, 1e6, 1e6):
+        backend.BufferFinalize(bt)
+        bt = backend.FromNumpy(np.array(thr, dtype=np.float32))   # the freed block comes back: same address, new threshold
+        outs = exe.Execute([bx, bw, bt], None, 0)
+        got = [backend.ToNumpy(o) for o in outs]
+        for o in outs:
+            backend.BufferFinalize(o)
+        taken = bool(x.sum() > thr)
+        for g, wnt in zip(got, want[taken]):
+            ok, viol = compare(g, wnt.astype(np.float32), 1e-5, 1.0)
+            assert ok, (thr, viol)
+    exe.Finalize()
+    builder.Finalize()
+
+
+def test_a_branch_inside_a_loop(b200, backend):
+    # Collatz steps on a vector's first element decide, per trip, which heavy branch transforms the vector
+    def build(f, x, n):
+        si, sx = _sh(b200, np.int32), _sh(b200, np.float32, 8, 8)
+
+        def body(c, i, v):
+            even = c.Equal(c.Rem(i, _c(c, 2, np.int32)), _c(c, 0, np.int32))
+            t = closure(c, [], lambda d: [d.Tanh(d.DotGeneral(v, [1], [], v, [0], []))])
+            e = closure(c, [], lambda d: [d.Neg(d.DotGeneral(v, [0], [], v, [0], []))])
+            (nv,) = c.If(even, t, e)
+            return [c.Add(i, _c(c, 1, np.int32)), c.Mul(nv, c.BroadcastInDim(_c(c, 0.3, np.float32), sx, []))]
+
+        cond = closure(f, [si, sx], lambda c, i, v: [c.LessThan(i, n)])
+        return f.While(cond, closure(f, [si, sx], body), _c(f, 0, np.int32), x)[1]
+
+    x = (0.5 * np.random.default_rng(12).standard_normal((8, 8))).astype(np.float32)
+    assert_parity(b200, backend, build, [x, np.array(5, dtype=np.int32)], rtol=1e-5, atol_scale=1.0, what="branch in a loop")
+
+
 def test_if_refusals(b200, backend):
     builder = backend.Builder("bad-if")
     f = builder.Main()
