@@ -605,6 +605,16 @@ def run_extras(b200, backend, L, libmod, torch, stream, local_rank, world, peaks
     out["gpt2_small_fwd_bf16"] = model_tokens_per_s("gpt2", g, W.gpt2_param_shapes(g),
                                                    lambda f, *p: W.gpt2_forward(f, g, int(b200.dtypes.BFloat16), *p),
                                                    W.gpt2_flops_per_token(g), 20)
+    # Incremental decoding of the same model: 64 greedy steps from one start token per sequence inside ONE executable (a
+    # While loop that runs on the device once the plan is replayed; KV caches of 1024 positions extended in place).
+    n_new = 64
+    dshapes = W.gpt2_decode_param_shapes(g)
+    dec = model_tokens_per_s("gpt2-decode", g, dshapes, lambda f, *p: W.gpt2_greedy_decode(f, g, int(b200.dtypes.BFloat16), n_new, *p), 0.0, 5)
+    out["gpt2_small_greedy_decode_bf16"] = {
+        "ms_per_call": dec["ms_per_forward"], "new_tokens_per_sequence": n_new, "batch_this_gpu": g.batch, "cache_positions": g.seq,
+        "ms_per_step": dec["ms_per_forward"] / n_new, "tokens_per_s_this_gpu": g.batch * n_new / (dec["ms_per_forward"] * 1e-3),
+        "launches_outside_the_loop": dec["launches_per_forward"], "arena_GiB": dec["arena_GiB"],
+        "note": "every step attends over the whole 1024-position cache under a position mask; weights (0.25 GB) are re-read from HBM each step"}
     lc = W.LlamaConfig(batch=64 // world)  # batch 64 sharded by batch across the GPUs
     out["llama_1b_fwd_bf16"] = model_tokens_per_s("llama", lc, W.llama_param_shapes(lc),
                                                  lambda f, *p: W.llama_forward(f, lc, int(b200.dtypes.BFloat16), *p),

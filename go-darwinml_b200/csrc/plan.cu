@@ -1678,7 +1678,11 @@ class Planner {
       const int64_t nb = w->in[i]->num_elements() * dtype_size(w->in[i]->dtype);
       nbytes.push_back(nb);
       res_slots.push_back(result_node[i] ? NewValueSlot(result_node[i]) : NewTemp(nb));
-      tmp_slots.push_back(NewTemp(nb));
+      // A state value that body only updates in place (its new value is DynamicUpdateSlice of its parameter, which
+      // feeds nothing else: a KV cache that gets one more entry per trip) lives in ONE buffer: body is handed the same
+      // address for the value and its successor and writes just the block.  The others alternate between two buffers.
+      const bool in_place = (size_t)i < be->donate_alias.size() && be->donate_alias[(size_t)i] == i;
+      tmp_slots.push_back(in_place ? -1 : NewTemp(nb));
     }
     const int pred_slot = NewTemp(256);
     slot_of_[w->id] = pred_slot;
@@ -1694,11 +1698,14 @@ class Planner {
       B200_TRY(ex_->dev->LoopStream(loop_depth_, &ls));   // created now: not while a recording is under way
     }
     Step st;
-    st.desc = strfmt("while[state=%d cond: %d steps, %d captures; body: %d steps, %d captures%s]", n_state, (int)ce->steps.size(), n_cc,
-                     (int)be->steps.size(), n_bc, recordable ? "; on the device when replayed" : "");
+    int n_in_place = 0;
+    for (int t : tmp_slots) n_in_place += t < 0 ? 1 : 0;
+    st.desc = strfmt("while[state=%d (%d updated in place) cond: %d steps, %d captures; body: %d steps, %d captures%s]", n_state, n_in_place,
+                     (int)ce->steps.size(), n_cc, (int)be->steps.size(), n_bc, recordable ? "; on the device when replayed" : "");
     st.reads = in_slots;
     st.writes = res_slots;
-    st.writes.insert(st.writes.end(), tmp_slots.begin(), tmp_slots.end());
+    for (int t : tmp_slots)
+      if (t >= 0) st.writes.push_back(t);
     st.writes.push_back(pred_slot);
     st.capturable = recordable;
     st.wants_graph = recordable;
@@ -1709,7 +1716,7 @@ class Planner {
       std::vector<void*> cur(n_state), nxt(n_state);
       for (int i = 0; i < n_state; ++i) {
         cur[i] = p[res_slots[i]];
-        nxt[i] = p[tmp_slots[i]];
+        nxt[i] = tmp_slots[i] >= 0 ? p[tmp_slots[i]] : cur[i];   // updated in place: one buffer
         if (nbytes[i] > 0) B200_CUDA_TRY(cudaMemcpyAsync(cur[i], p[in_slots[i]], (size_t)nbytes[i], cudaMemcpyDeviceToDevice, dev->stream()));
       }
       std::vector<void*> cin(n_state + n_cc), bin(n_state + n_bc);
@@ -1725,7 +1732,8 @@ class Planner {
         auto run_body = [&]() -> Status {
           B200_TRY(RunSubPlan(be, bin.data(), nxt.data()));
           for (int i = 0; i < n_state; ++i)
-            if (nbytes[i] > 0) B200_CUDA_TRY(cudaMemcpyAsync(cur[i], nxt[i], (size_t)nbytes[i], cudaMemcpyDeviceToDevice, dev->stream()));
+            if (nbytes[i] > 0 && cur[i] != nxt[i])
+              B200_CUDA_TRY(cudaMemcpyAsync(cur[i], nxt[i], (size_t)nbytes[i], cudaMemcpyDeviceToDevice, dev->stream()));
           return Status::OK();
         };
         dev->kernel_error_flag();   // the loop may raise the error word: have the next synchronisation point read it
@@ -2258,8 +2266,17 @@ int64_t b200_exec_arena_bytes(B200Exec exec) { return exec ? reinterpret_cast<Ex
 int64_t b200_exec_describe(B200Exec exec, char* buf, int64_t cap) {
   Exec* ex = reinterpret_cast<Exec*>(exec);
   if (!ex) return -1;
+  // one line per step; the sub-plans of loops and branches follow their step, indented, in the order the step names them
   std::string s;
-  for (auto& st : ex->steps) s += st.desc + "\n";
+  std::function<void(const Exec*, const std::string&)> list = [&](const Exec* e, const std::string& indent) {
+    size_t child = 0;
+    for (auto& st : e->steps) {
+      s += indent + st.desc + "\n";
+      const bool owns_two = st.desc.compare(0, 6, "while[") == 0 || st.desc.compare(0, 3, "if[") == 0;
+      for (int k = 0; owns_two && k < 2 && child < e->children.size(); ++k) list(e->children[child++].get(), indent + "    ");
+    }
+  };
+  list(ex, "");
   if (buf && cap > 0) {
     const int64_t n = std::min<int64_t>(cap - 1, (int64_t)s.size());
     memcpy(buf, s.data(), (size_t)n);

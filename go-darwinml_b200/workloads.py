@@ -9,6 +9,8 @@ FusedAttentionQKVProjection, FusedScaledDotProductAttention, DotGeneral and elem
   mlp_forward          configuration "MLP forward, fp32"            x[64,784] -> softmax probabilities [64,10]
   gpt2_forward         GPT-2-small-shaped decoder forward, bf16     ids[B,S] -> logits [B,S,V]
   llama_forward        Llama-style decoder forward (GQA, SwiGLU, RMSNorm, RoPE), bf16
+  gpt2_greedy_decode   incremental decoding of the GPT-2-shaped model: one While loop, a KV cache per layer updated in
+                       place (DynamicUpdateSlice), greedy next token (ArgMinMax + Gather); ids[B] -> tokens [B, n]
 """
 from __future__ import annotations
 
@@ -124,6 +126,94 @@ def gpt2_forward(f, c: GPT2Config, dtype_code, *params):
 def gpt2_flops_per_token(c: GPT2Config) -> float:
     d, S = c.d_model, c.seq
     return c.layers * (2 * d * 3 * d + 2 * d * d + 4 * d * c.d_ff + 4 * S * d) + 2 * d * c.vocab  # full S x S attention counted
+
+
+def closure(f, param_shapes, body):
+    """body(c, *params) -> outputs, as a closure of function f: a Function.Closure() with its Parameters and Return on the
+    backend; an object with MakeClosure (an eager evaluator such as the tests' CPU oracle) gets a callable instead."""
+    if hasattr(f, "MakeClosure"):
+        return f.MakeClosure(param_shapes, body)
+    c = f.Closure()
+    params = [c.Parameter(f"p{i}", s) for i, s in enumerate(param_shapes)]
+    c.Return(list(body(c, *params)), None)
+    return c
+
+
+def gpt2_decode_param_shapes(c: GPT2Config):
+    """The forward's parameters with the token ids replaced by one start token per batch entry."""
+    return [("ids", (c.batch, 1, 1))] + gpt2_param_shapes(c)[1:]
+
+
+def _const_i32(g, v):
+    return g.Constant(np.array([v], dtype=np.int32))
+
+
+def gpt2_decode_step(g, c: GPT2Config, dtype_code, weights, t, tok, out, caches):
+    """One decoding step at position t (int32 scalar): the current token [B,1,1] goes through the model against the
+    caches (per layer a key and a value cache [B, H, seq, D], extended at position t), the greedy next token is written
+    to out[:, t].  `weights` = (wte, wpe, [14 tensors per layer], lnf_g, lnf_b).
+    Returns (next token [B,1,1], out, logits [B,1,V], new caches)."""
+    wte, wpe, layers, lnf_g, lnf_b = weights
+    B, S, d, H = c.batch, c.seq, c.d_model, c.heads
+    D = d // H
+    zero = _const_i32(g, 0)
+    x = g.Gather(wte, tok, 2, [2], [0], [0], [1, d], False)                            # [B, 1, d]
+    pos = g.DynamicSlice(wpe, [t, zero], [1, d])                                       # [1, d]
+    x = g.Add(x, g.BroadcastInDim(pos, _Shape(dtype_code, (B, 1, d)), [1, 2]))
+    # keys at positions <= t are visible: [1, 1, 1, S] broadcast over batch, heads and the one query
+    visible = g.LessOrEqual(g.Iota(_Shape(C_I32, (1, 1, 1, S)), 3), g.BroadcastInDim(t, _Shape(C_I32, (1, 1, 1, S)), []))
+    new_caches = []
+    for li, (ln1_g, ln1_b, wqkv, bq, bk, bv, wo, bo, ln2_g, ln2_b, wfc, bfc, wproj, bproj) in enumerate(layers):
+        h = g.FusedLayerNorm(x, [-1], c.eps, ln1_g, ln1_b)
+        q, k, v = g.FusedAttentionQKVProjection(h, wqkv, bq, bk, bv, d, d)
+        q, k, v = (g.Reshape(u, B, H, 1, D) for u in (q, k, v))
+        kc = g.DynamicUpdateSlice(caches[2 * li], k, [zero, zero, t, zero])
+        vc = g.DynamicUpdateSlice(caches[2 * li + 1], v, [zero, zero, t, zero])
+        new_caches += [kc, vc]
+        a = g.FusedScaledDotProductAttention(q, kc, vc, visible, H, H, LAYOUT_BHSD, 1.0 / math.sqrt(D), False)
+        x = g.Add(x, g.FusedDense(g.Reshape(a, B, 1, d), wo, bo, ACT_NONE))
+        h = g.FusedLayerNorm(x, [-1], c.eps, ln2_g, ln2_b)
+        x = g.Add(x, g.FusedDense(g.FusedDense(h, wfc, bfc, ACT_GELU), wproj, bproj, ACT_NONE))
+    x = g.FusedLayerNorm(x, [-1], c.eps, lnf_g, lnf_b)
+    logits = g.DotGeneral(x, [2], None, wte, [1], None)                                # [B, 1, V]
+    nxt = g.ArgMinMax(logits, 2, C_I32, False)                                         # [B, 1]
+    out2 = g.DynamicUpdateSlice(out, nxt, [zero, t])
+    return g.Reshape(nxt, B, 1, 1), out2, logits, new_caches
+
+
+def gpt2_greedy_decode(f, c: GPT2Config, dtype_code, n_tokens: int, *params):
+    """Greedy incremental decoding: n_tokens steps from one start token per batch entry, positions 0 .. n_tokens - 1, as ONE
+    While loop.  State: step t, current token [B,1,1], the tokens produced so far [B, n_tokens], the last logits, and per
+    layer a key and a value cache [B, H, seq, D] that each step extends by one position in place (heads before
+    positions: the one query of a step then contracts with the cache where it lies, and [B,1,H,D] reshapes to
+    [B,H,1,D] for free).  Every step attends over the whole cache under a mask `key position <= t`.
+    Returns (tokens [B, n_tokens] int32, last step's logits [B, 1, V])."""
+    it = iter(params)
+    ids, wte, wpe = next(it), next(it), next(it)
+    layers = [tuple(next(it) for _ in range(14)) for _ in range(c.layers)]
+    lnf_g, lnf_b = next(it), next(it)
+    weights = (wte, wpe, layers, lnf_g, lnf_b)
+    B, S, d, H, V = c.batch, c.seq, c.d_model, c.heads, c.vocab
+    D = d // H
+    s_i, s_tok, s_out = _Shape(C_I32, ()), _Shape(C_I32, (B, 1, 1)), _Shape(C_I32, (B, n_tokens))
+    s_cache, s_logits = _Shape(dtype_code, (B, H, S, D)), _Shape(dtype_code, (B, 1, V))
+    state_shapes = [s_i, s_tok, s_out, s_logits] + [s_cache] * (2 * c.layers)
+
+    def body(g, t, tok, out, _logits, *caches):
+        nxt, out2, logits, new_caches = gpt2_decode_step(g, c, dtype_code, weights, t, tok, out, caches)
+        return [g.Add(t, _const_i32(g, 1)), nxt, out2, logits] + new_caches
+
+    cond = closure(f, state_shapes, lambda g, t, *rest: [g.LessThan(t, _const_i32(g, n_tokens))])
+    loop = closure(f, state_shapes, body)
+    float_np = {C_F32: np.float32}.get(dtype_code)
+    if float_np is None:
+        import ml_dtypes
+        float_np = ml_dtypes.bfloat16
+    # zero-filled initial values as broadcasts of a scalar: no large constants in the graph
+    zeros = lambda shape, np_dt: f.BroadcastInDim(f.Constant(np.zeros(1, dtype=np_dt)), shape, [])
+    init = [_const_i32(f, 0), ids, zeros(s_out, np.int32), zeros(s_logits, float_np)] + [zeros(s_cache, float_np) for _ in range(2 * c.layers)]
+    res = f.While(cond, loop, *init)
+    return res[2], res[3]
 
 
 # ---------------------------------------------------------------------------------- Llama ---
