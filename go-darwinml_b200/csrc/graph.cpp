@@ -1056,16 +1056,28 @@ B200Value b200_scaled_dot_product_attention(B200Context ctx, B200Value query, B2
   if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
     return ret(err, Status::Invalid(strfmt("SDPA: numHeads (%d) must be positive and divisible by numKVHeads (%d)", num_heads, num_kv_heads)), nullptr);
   const bool bshd = axes_layout == B200_LAYOUT_BSHD;
-  // Fused path: no mask tensor, head dim 64, 16-bit floats.  One kernel reads Q, K and V in the layout they come
+  // Fused path: no mask tensor (or one query position), head dim 64, 16-bit floats.  One kernel reads Q, K and V in the layout they come
   // in; neither the scores, nor a mask, nor repeated K/V heads, nor a transposed copy is ever written.
   {
     const int s_ax = bshd ? 1 : 2, h_ax = bshd ? 2 : 1;
     const bool shapes_ok = k->dims == v->dims && q->dims[0] == k->dims[0] && q->dims[3] == k->dims[3] &&
                            q->dims[h_ax] == num_heads && k->dims[h_ax] == num_kv_heads && q->dtype == k->dtype && q->dtype == v->dtype;
     if (!shapes_ok) return ret(err, Status::Invalid("SDPA: query / key / value shapes, dtypes or head counts do not agree"), nullptr);
-    if (!m && q->dims[3] == 64 && (q->dtype == B200_BFLOAT16 || q->dtype == B200_FLOAT16) && q->dims[s_ax] > 0 && k->dims[s_ax] > 0) {
+    const bool fusable = q->dims[3] == 64 && (q->dtype == B200_BFLOAT16 || q->dtype == B200_FLOAT16) && q->dims[s_ax] > 0 && k->dims[s_ax] > 0;
+    // One query position (a decoding step) takes a mask tensor too: any mask that broadcasts to [B, H, 1, Sk].
+    static const bool decode_on = []() { const char* e = getenv("B200MLX_DECODE_ATTENTION"); return !(e && e[0] == '0'); }();
+    bool mask_ok = !m;
+    if (m && decode_on && fusable && q->dims[s_ax] == 1 && !causal && scale > 0 && (m->dtype == B200_BOOL || m->dtype == q->dtype) && m->rank() <= 4) {
+      const int64_t full[4] = {q->dims[0], bshd && m->rank() == 4 ? 1 : (int64_t)num_heads, bshd && m->rank() == 4 ? (int64_t)num_heads : 1, k->dims[s_ax]};
+      mask_ok = true;
+      for (int i = 0; i < m->rank(); ++i) {
+        const int64_t want = full[4 - m->rank() + i];
+        if (m->dims[i] != 1 && m->dims[i] != want) mask_ok = false;
+      }
+    }
+    if (mask_ok && fusable) {
       Graph& gr = reinterpret_cast<Ctx*>(ctx)->graph;
-      Node* o = gr.Add(Op::Attention, q->dtype, q->dims, {q, k, v});
+      Node* o = m ? gr.Add(Op::Attention, q->dtype, q->dims, {q, k, v, m}) : gr.Add(Op::Attention, q->dtype, q->dims, {q, k, v});
       o->ia = {num_heads, num_kv_heads, bshd ? 1 : 0, causal ? 1 : 0};
       o->fa = {scale};
       return ret(err, Status::OK(), o);

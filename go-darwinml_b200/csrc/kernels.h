@@ -131,6 +131,9 @@ struct DynSliceParams {
   int64_t b_dims[kMaxDims] = {0};  // slice sizes / update dims
   const void* starts[kMaxDims] = {nullptr};
   int start_dtypes[kMaxDims] = {0};
+  // update only: element strides of the update block when it is read in place inside a larger tensor (dense otherwise)
+  bool u_strided = false;
+  int64_t u_strides[kMaxDims] = {0};
 };
 Status dynamic_slice(Device* dev, const DynSliceParams& p);
 Status dynamic_update_slice(Device* dev, const DynSliceParams& p);
@@ -251,9 +254,17 @@ struct GemmParams {
   int64_t a_batch_stride = -1, b_batch_stride = -1;  // -1 = dense (m*k, k*n)
   // fp32 on the tensor-core path: room for the three bf16 planes of both operands (gemm_split_scratch_bytes).  Without
   // it the launch allocates them itself, which keeps the step out of recorded plans.
+  // A 16-bit product of at most 16 rows (gemm_skinny): split_scratch holds the K slices' fp32 partial sums
+  // (gemm_skinny_scratch_bytes) and skinny_counters one zeroed 32-bit counter per 64 columns (gemm_skinny_counter_bytes),
+  // which the kernel leaves at zero.  Counters must not be shared by launches that may run at the same time.
   void* split_scratch = nullptr;
   int64_t split_scratch_bytes = 0;
+  void* skinny_counters = nullptr;
 };
+int64_t gemm_skinny_scratch_bytes(const GemmParams& p, int sm_count);   // 0: not a shape gemm_skinny takes
+int64_t gemm_skinny_counter_bytes(const GemmParams& p);
+// The few-rows path alone: *taken is false (and nothing is launched) when the problem is outside its rules or has no scratch.
+Status gemm_skinny(Device* dev, const GemmParams& p, bool* taken);
 inline int64_t gemm_split_scratch_bytes(int64_t batch, int64_t m, int64_t n, int64_t k) {
   const int64_t a = (batch * m * k * 6 + 255) / 256 * 256, b = (batch * k * n * 6 + 255) / 256 * 256;
   return a + b;
@@ -301,9 +312,17 @@ struct AttentionParams {
   // Optional element strides (batch, head, sequence) per input; 0 = dense in the stated layout.  Lets Q, K and V be
   // read straight out of a wider buffer, e.g. the three column blocks of a fused QKV projection.
   int64_t q_strides[3] = {0, 0, 0}, k_strides[3] = {0, 0, 0}, v_strides[3] = {0, 0, 0};
+  // One query position only (attention_decode): an optional mask over [batch, head, key], Bool (1: false = masked) or
+  // additive in the tensors' dtype (2), with its element strides (0 on a broadcast dim).
+  const void* mask = nullptr;
+  int mask_kind = 0;
+  int64_t m_b = 0, m_h = 0, m_k = 0;
 };
 bool attention_supported(const AttentionParams& p);
 Status attention(Device* dev, const AttentionParams& p);
+// One query position per (batch, head) against a key / value cache (Sq == 1, not causal): one bandwidth-bound launch.
+bool attention_decode_supported(const AttentionParams& p);
+Status attention_decode(Device* dev, const AttentionParams& p);
 
 }  // namespace k
 }  // namespace b200

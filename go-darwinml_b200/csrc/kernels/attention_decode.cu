@@ -1,0 +1,306 @@
+// Attention of ONE query position per (batch, head) over a key / value cache: the decoding step.
+//
+//   o[b, h, :] = softmax_k( scale * q[b, h, :] . K[b, h / group, k, :] + mask[b, h, k] ) V[b, h / group, k, :]     head dim 64
+//
+// The general lowering runs this as two batched matrix-vector products around a masked softmax (four launches, the
+// scores and probabilities through memory); here it is one launch that reads K and V once.  Bandwidth-bound: bytes =
+// the cache (2 * Sk * 128 B per KV head and batch entry).
+//
+// A cluster of up to 8 CTAs owns one (batch, head) and splits the keys.  A CTA walks its keys 256 at a time; eight
+// lanes share a key (16 bytes of its K row and of its V row each), so after a 3-step shuffle all eight hold the key's
+// score and P.V needs no exchange.  All of a chunk's K and V loads are issued first (64 KB in flight per CTA), and each
+// warp keeps an online softmax of its own keys, so nothing in the loop waits for another warp.  The warps', then the
+// CTAs', (maximum, sum, partial output) meet at the end, the CTAs' through distributed shared memory; CTA 0 writes the row.
+// A row with every key masked yields NaN, as the general lowering does.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "../kernels.h"
+#include "pdl.cuh"
+#include "sm100_ptx.cuh"
+
+namespace b200 {
+namespace k {
+
+namespace {
+
+constexpr int DEC_THREADS = 256;
+constexpr int DEC_CHUNK = 256;     // keys per pass
+constexpr int DEC_D = 64;
+constexpr int DEC_MAX_SPLITS = 8;
+constexpr int DEC_WARPS = DEC_THREADS / 32;
+
+struct DecArgs {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  const void* mask;
+  int mask_kind;                     // 0 none, 1 Bool (false = masked), 2 additive, of the tensors' dtype
+  int64_t m_b, m_h, m_k;             // mask element strides (0 on broadcast dims)
+  int B, H, group, Sk;
+  int64_t q_sb, q_sh, k_sb, k_sh, k_ss, v_sb, v_sh, v_ss, o_sb, o_sh;   // element strides
+  float scale_log2e;
+  int keys_per_cta;
+};
+
+template <typename T> __device__ __forceinline__ float2 dec_unpack2(uint32_t w);
+template <> __device__ __forceinline__ float2 dec_unpack2<__nv_bfloat16>(uint32_t w) {
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+template <> __device__ __forceinline__ float2 dec_unpack2<__half>(uint32_t w) { return __half22float2(*reinterpret_cast<const __half2*>(&w)); }
+template <typename T> __device__ __forceinline__ float dec_to_f(T v);
+template <> __device__ __forceinline__ float dec_to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float dec_to_f(__half v) { return __half2float(v); }
+template <typename T> __device__ __forceinline__ T dec_from_f(float v);
+template <> __device__ __forceinline__ __nv_bfloat16 dec_from_f(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half dec_from_f(float v) { return __float2half_rn(v); }
+
+__device__ __forceinline__ float dec_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float dec_ld_cluster(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+
+// 16 bytes (eight 16-bit elements) as four float pairs
+template <typename T>
+__device__ __forceinline__ void dec_unpack8(const uint4& r, float2 (&f)[4]) {
+  f[0] = dec_unpack2<T>(r.x);
+  f[1] = dec_unpack2<T>(r.y);
+  f[2] = dec_unpack2<T>(r.z);
+  f[3] = dec_unpack2<T>(r.w);
+}
+
+// CONTIG: key rows of K and V are 64 elements apart (a BHSD cache), so every load's offset is an immediate.
+template <typename T, bool CONTIG>
+__global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(const DecArgs g) {
+  __shared__ float wm[DEC_WARPS], wl[DEC_WARPS];   // each warp's running maximum (log2 units) and sum
+  __shared__ float wacc[DEC_WARPS][DEC_D];         // and unnormalised output
+  __shared__ float part[DEC_D + 2];                // this CTA's result: output (unnormalised), maximum, sum
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.x, rank = blockIdx.y, csize = gridDim.y;
+  const int b = bh / g.H, h = bh - b * g.H, hkv = h / g.group;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t kss = CONTIG ? DEC_D : g.k_ss, vss = CONTIG ? DEC_D : g.v_ss;
+  const int key_begin = rank * g.keys_per_cta;
+  const int key_end = key_begin + g.keys_per_cta < g.Sk ? key_begin + g.keys_per_cta : g.Sk;
+  // Lane (kq, part) of warp w: keys 32 it + 4 w + kq of every 256-key chunk (it = 0..7), dims [8 part, 8 part + 8) of
+  // both K and V.  The eight lanes of a key all end up with its score, so P.V needs no exchange, and a warp keeps an
+  // online softmax of its own keys: nothing in the loop waits for another warp.
+  const int kq = lane >> 3, dpart = lane & 7;
+  const int key0 = warp * 4 + kq;
+  const T* Kt = reinterpret_cast<const T*>(g.k) + (int64_t)b * g.k_sb + (int64_t)hkv * g.k_sh + (int64_t)(key_begin + key0) * kss + dpart * 8;
+  const T* Vt = reinterpret_cast<const T*>(g.v) + (int64_t)b * g.v_sb + (int64_t)hkv * g.v_sh + (int64_t)(key_begin + key0) * vss + dpart * 8;
+  const int64_t mrow = (int64_t)b * g.m_b + (int64_t)h * g.m_h;
+  float2 qf[4];   // the query's eight dims, pre-multiplied by scale * log2(e)
+  {
+    const uint4 qv = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(g.q) + (int64_t)b * g.q_sb + (int64_t)h * g.q_sh + dpart * 8);
+    dec_unpack8<T>(qv, qf);
+    const float2 sl = make_float2(g.scale_log2e, g.scale_log2e);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) qf[i] = __fmul2_rn(qf[i], sl);
+  }
+  float m_run = -INFINITY, l_run = 0.f;
+  float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+  constexpr int ITS = DEC_CHUNK / 32;
+  for (int c0 = key_begin; c0 < key_end; c0 += DEC_CHUNK, Kt += DEC_CHUNK * kss, Vt += DEC_CHUNK * vss) {
+    const bool full = c0 + DEC_CHUNK <= key_end;
+    uint4 kreg[ITS], vreg[ITS];
+    float s[ITS];
+    // every load of the chunk is issued up front (V does not depend on the scores)
+    if (full) {
+#pragma unroll
+      for (int it = 0; it < ITS; ++it) kreg[it] = __ldg(reinterpret_cast<const uint4*>(Kt + it * 32 * kss));
+#pragma unroll
+      for (int it = 0; it < ITS; ++it) vreg[it] = __ldg(reinterpret_cast<const uint4*>(Vt + it * 32 * vss));
+    } else {
+#pragma unroll
+      for (int it = 0; it < ITS; ++it) {
+        const bool in = c0 + it * 32 + key0 < key_end;
+        kreg[it] = in ? __ldg(reinterpret_cast<const uint4*>(Kt + it * 32 * kss)) : make_uint4(0, 0, 0, 0);
+        vreg[it] = in ? __ldg(reinterpret_cast<const uint4*>(Vt + it * 32 * vss)) : make_uint4(0, 0, 0, 0);
+      }
+    }
+    // the keys' mask terms, in log2 units (the eight lanes of a key read the same element)
+#pragma unroll
+    for (int it = 0; it < ITS; ++it) {
+      const int key = c0 + it * 32 + key0;
+      s[it] = key < key_end ? 0.f : -INFINITY;
+      if (g.mask_kind != 0 && key < key_end) {
+        if (g.mask_kind == 1) s[it] = reinterpret_cast<const uint8_t*>(g.mask)[mrow + (int64_t)key * g.m_k] ? 0.f : -INFINITY;
+        else s[it] = dec_to_f<T>(reinterpret_cast<const T*>(g.mask)[mrow + (int64_t)key * g.m_k]) * 1.4426950408889634f;
+      }
+    }
+    // scores
+    float cmax = -INFINITY;
+#pragma unroll
+    for (int it = 0; it < ITS; ++it) {
+      float2 kf[4];
+      dec_unpack8<T>(kreg[it], kf);
+      float2 d2 = __fmul2_rn(kf[0], qf[0]);
+#pragma unroll
+      for (int i = 1; i < 4; ++i) d2 = __ffma2_rn(kf[i], qf[i], d2);
+      float d = d2.x + d2.y;
+      d += __shfl_xor_sync(0xffffffffu, d, 1);
+      d += __shfl_xor_sync(0xffffffffu, d, 2);
+      d += __shfl_xor_sync(0xffffffffu, d, 4);
+      s[it] += d;
+      cmax = fmaxf(cmax, s[it]);
+    }
+    cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, 8));
+    cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, 16));
+    const float m_new = fmaxf(m_run, cmax);
+    const float m_safe = m_new == -INFINITY ? 0.f : m_new;   // every key so far masked: keep the arithmetic finite
+    const float alpha = dec_exp2(m_run - m_safe);            // 0 on the first chunk (m_run = -inf)
+    m_run = m_new;
+    const float2 a2 = make_float2(alpha, alpha);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] = __fmul2_rn(acc[i], a2);
+    float lsum = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITS; ++it) {
+      const float pk = dec_exp2(s[it] - m_safe);   // 0 for a masked key and past the end
+      lsum += pk;
+      float2 vf[4];
+      dec_unpack8<T>(vreg[it], vf);
+      const float2 p2 = make_float2(pk, pk);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[i] = __ffma2_rn(p2, vf[i], acc[i]);
+    }
+    l_run = fmaf(l_run, alpha, lsum);   // this lane group's keys only; the groups meet below
+  }
+  // the warp's four key groups (they share m_run), then the CTA's warps, meet in a fixed order
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 8);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 16);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    acc[i].x += __shfl_xor_sync(0xffffffffu, acc[i].x, 8);
+    acc[i].y += __shfl_xor_sync(0xffffffffu, acc[i].y, 8);
+    acc[i].x += __shfl_xor_sync(0xffffffffu, acc[i].x, 16);
+    acc[i].y += __shfl_xor_sync(0xffffffffu, acc[i].y, 16);
+  }
+  if (kq == 0) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      wacc[warp][dpart * 8 + 2 * i] = acc[i].x;
+      wacc[warp][dpart * 8 + 2 * i + 1] = acc[i].y;
+    }
+    if (dpart == 0) { wm[warp] = m_run; wl[warp] = l_run; }
+  }
+  __syncthreads();
+  if (threadIdx.x < DEC_D) {
+    float M = wm[0];
+#pragma unroll
+    for (int w = 1; w < DEC_WARPS; ++w) M = fmaxf(M, wm[w]);
+    const float Ms = M == -INFINITY ? 0.f : M;
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      const float wgt = dec_exp2(wm[w] - Ms);
+      L = fmaf(wl[w], wgt, L);
+      O = fmaf(wacc[w][threadIdx.x], wgt, O);
+    }
+    part[threadIdx.x] = O;
+    if (threadIdx.x == 0) { part[DEC_D] = M; part[DEC_D + 1] = L; }
+  }
+  __syncthreads();
+  // the CTAs' results meet through distributed shared memory; CTA 0 writes the row
+  if (csize > 1) sm100::cluster_sync_all();
+  if (rank == 0 && threadIdx.x < DEC_D) {
+    const uint32_t base = sm100::smem_u32(&part[0]);
+    float M = -INFINITY;
+    for (int r = 0; r < csize; ++r) M = fmaxf(M, csize > 1 ? dec_ld_cluster(sm100::map_to_cta(base + DEC_D * 4u, (uint32_t)r)) : part[DEC_D]);
+    const float Ms = M == -INFINITY ? 0.f : M;
+    float L = 0.f, O = 0.f;
+    for (int r = 0; r < csize; ++r) {
+      const uint32_t pb = csize > 1 ? sm100::map_to_cta(base, (uint32_t)r) : 0u;
+      const float mr = csize > 1 ? dec_ld_cluster(pb + DEC_D * 4u) : part[DEC_D];
+      const float lr = csize > 1 ? dec_ld_cluster(pb + (DEC_D + 1) * 4u) : part[DEC_D + 1];
+      const float orr = csize > 1 ? dec_ld_cluster(pb + threadIdx.x * 4u) : part[threadIdx.x];
+      const float wgt = dec_exp2(mr - Ms);
+      L = fmaf(lr, wgt, L);
+      O = fmaf(orr, wgt, O);
+    }
+    T* Op = reinterpret_cast<T*>(g.o) + (int64_t)b * g.o_sb + (int64_t)h * g.o_sh;
+    Op[threadIdx.x] = dec_from_f<T>(O / L);   // L = 0 (every key masked): NaN
+  }
+  if (csize > 1) sm100::cluster_sync_all();   // nobody leaves while its result may still be read
+}
+
+}  // namespace
+
+bool attention_decode_supported(const AttentionParams& p) {
+  static const bool on = []() { const char* v = getenv("B200MLX_DECODE_ATTENTION"); return !(v && v[0] == '0'); }();
+  const bool is16 = p.dtype == B200_BFLOAT16 || p.dtype == B200_FLOAT16;
+  if (!on || !is16 || p.head_dim != DEC_D || p.Sq != 1 || p.causal) return false;
+  if (p.B <= 0 || p.H <= 0 || p.Hkv <= 0 || p.Sk <= 0 || p.H % p.Hkv != 0 || p.B * p.H > 0x7fffffffLL || p.Sk > 0x7fffffffLL) return false;
+  return p.scale > 0 && p.scale < 1e30;
+}
+
+Status attention_decode(Device* dev, const AttentionParams& p) {
+  if (!attention_decode_supported(p)) return Status::Unsupported("attention_decode: needs one query position, head dim 64, 16-bit floats, no causal flag");
+  auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  if (!al(p.q) || !al(p.k) || !al(p.v)) return Status::Unsupported("attention_decode: operands must be 16-byte aligned");
+  B200_TRY(dev->MakeCurrent());
+  DecArgs g;
+  g.q = p.q; g.k = p.k; g.v = p.v; g.o = p.o;
+  g.mask = p.mask; g.mask_kind = p.mask ? p.mask_kind : 0;
+  g.m_b = p.m_b; g.m_h = p.m_h; g.m_k = p.m_k;
+  g.B = (int)p.B; g.H = (int)p.H; g.group = (int)(p.H / p.Hkv); g.Sk = (int)p.Sk;
+  auto strides = [&](int64_t S, int64_t Hx, const int64_t* custom, int64_t* sb, int64_t* sh, int64_t* ss) {
+    if (custom[0] | custom[1] | custom[2]) { *sb = custom[0]; *sh = custom[1]; *ss = custom[2]; return; }
+    if (p.bshd) { *ss = Hx * DEC_D; *sh = DEC_D; *sb = S * Hx * DEC_D; }
+    else { *ss = DEC_D; *sh = S * DEC_D; *sb = Hx * S * DEC_D; }
+  };
+  int64_t q_ss, o_ss;
+  const int64_t none[3] = {0, 0, 0};
+  strides(1, p.H, p.q_strides, &g.q_sb, &g.q_sh, &q_ss);
+  strides(p.Sk, p.Hkv, p.k_strides, &g.k_sb, &g.k_sh, &g.k_ss);
+  strides(p.Sk, p.Hkv, p.v_strides, &g.v_sb, &g.v_sh, &g.v_ss);
+  strides(1, p.H, none, &g.o_sb, &g.o_sh, &o_ss);
+  if ((g.q_sb | g.q_sh | g.k_sb | g.k_sh | g.k_ss | g.v_sb | g.v_sh) % 8 != 0 || g.v_ss % 8 != 0)
+    return Status::Unsupported("attention_decode: operand strides must be multiples of 8 elements");
+  g.scale_log2e = (float)(p.scale * 1.4426950408889634);
+  // CTAs per (batch, head): about four CTAs per SM in all (each keeps 64 KB of loads in flight), whole 256-key chunks, at most 8
+  const int64_t bh = p.B * p.H;
+  int64_t splits = (4 * (int64_t)dev->sm_count() + bh - 1) / bh;
+  if (splits > DEC_MAX_SPLITS) splits = DEC_MAX_SPLITS;
+  if (splits > (p.Sk + DEC_CHUNK - 1) / DEC_CHUNK) splits = (p.Sk + DEC_CHUNK - 1) / DEC_CHUNK;
+  if (splits < 1) splits = 1;
+  int64_t per = ((p.Sk + splits - 1) / splits + DEC_CHUNK - 1) / DEC_CHUNK * DEC_CHUNK;
+  splits = (p.Sk + per - 1) / per;
+  g.keys_per_cta = (int)per;
+  static const bool pdl_on = []() { const char* v = getenv("B200MLX_PDL"); return !(v && v[0] == '0'); }();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)bh, (unsigned)splits);
+  cfg.blockDim = dim3(DEC_THREADS);
+  cfg.stream = dev->stream();
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = (unsigned)splits; attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_on ? 2 : 1;
+  const bool contig = g.k_ss == DEC_D && g.v_ss == DEC_D;
+  cudaError_t e;
+  if (p.dtype == B200_FLOAT16)
+    e = contig ? cudaLaunchKernelEx(&cfg, attention_decode_kernel<__half, true>, g) : cudaLaunchKernelEx(&cfg, attention_decode_kernel<__half, false>, g);
+  else
+    e = contig ? cudaLaunchKernelEx(&cfg, attention_decode_kernel<__nv_bfloat16, true>, g)
+               : cudaLaunchKernelEx(&cfg, attention_decode_kernel<__nv_bfloat16, false>, g);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return Status::Cuda(strfmt("attention_decode: %s", cudaGetErrorString(e)));
+  }
+  return dev->CheckLaunch("attention_decode");
+}
+
+}  // namespace k
+}  // namespace b200

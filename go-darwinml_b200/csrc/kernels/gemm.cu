@@ -12,6 +12,8 @@ Status gemm_tcgen05(Device* dev, const GemmParams& p, bool* taken);
 Status gemm(Device* dev, const GemmParams& p) {
   if (p.batch < 0 || p.m < 0 || p.n < 0 || p.k < 0) return Status::Invalid("gemm: negative size");
   bool taken = false;
+  B200_TRY(gemm_skinny(dev, p, &taken));
+  if (taken) return Status::OK();
   B200_TRY(gemm_tcgen05(dev, p, &taken));
   if (taken) return Status::OK();
   return gemm_simt(dev, p);

@@ -1,0 +1,269 @@
+// C[M, N] = act(X[M, K] W[K, N] + bias) (+ / * residual) for a handful of rows (M <= 16): a decoding step's projections.
+//
+// Such a product is bound by reading W once (2 K N bytes); the 128 x 256 tensor-core tile gives it N / 256 CTAs, each
+// streaming its whole K through one SM's load path (28 us for K = 3072, N = 768).  Here about two CTAs per SM share W:
+// a CTA owns 64 columns and one slice of K, brings its whole W slice (at most 512 x 64) and X slice into shared memory
+// with one batch of 16-byte asynchronous copies -- so all of W is in flight at once --, multiplies with
+// mma.sync m16n8k16 (X as the 16-row operand, rows past M zero), and writes a 16 x 64 fp32 partial.  The CTA that
+// arrives last on its column slab's counter adds the partials in slice order (the same sum on every run), applies the
+// epilogue and writes C; it leaves the counter at zero for the next launch.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <map>
+#include <mutex>
+
+#include "../kernels.h"
+#include "gemm_common.cuh"
+#include "pdl.cuh"
+#include "sm100_ptx.cuh"
+
+namespace b200 {
+namespace k {
+
+namespace {
+
+constexpr int SK_THREADS = 128;
+constexpr int SK_BN = 64;
+constexpr int SK_ROWS = 16;
+constexpr int SK_MAX_KC = 512;
+constexpr int SK_X_PAD = 8;   // elements: the X rows' pitch is an odd number of 16-byte units, conflict-free for ldmatrix
+
+struct SkArgs {
+  const void* x;
+  const void* w;
+  void* c;
+  const void* bias;
+  const void* residual;
+  float* partial;       // [splits, 16, N]
+  unsigned* counters;   // [N / 64], zero between launches
+  int M, N, K, kc, splits, act, residual_mul;
+};
+
+__device__ __forceinline__ void sk_cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void sk_cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void sk_ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void sk_ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+template <typename T> __device__ __forceinline__ void sk_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <> __device__ __forceinline__ void sk_mma<__nv_bfloat16>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <> __device__ __forceinline__ void sk_mma<__half>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <typename T> __device__ __forceinline__ float sk_to_f(T v);
+template <> __device__ __forceinline__ float sk_to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float sk_to_f(__half v) { return __half2float(v); }
+template <typename T> __device__ __forceinline__ T sk_from_f(float v);
+template <> __device__ __forceinline__ __nv_bfloat16 sk_from_f(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half sk_from_f(float v) { return __float2half_rn(v); }
+
+template <typename T>
+__global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g) {
+  extern __shared__ __align__(128) unsigned char sk_smem[];
+  __shared__ int s_last;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int slab = blockIdx.x, split = blockIdx.y;
+  const int n0 = slab * SK_BN;
+  const int k0 = split * g.kc;
+  const int kc = g.K - k0 < g.kc ? g.K - k0 : g.kc;   // a multiple of 16
+  const int x_pitch = (g.kc + SK_X_PAD) * 2;          // bytes
+  unsigned char* wsm = sk_smem;                       // [kc][64] elements, 16-byte units XOR-swizzled by (row & 7)
+  unsigned char* xsm = sk_smem + (size_t)g.kc * SK_BN * 2;
+  const uint32_t wsm_u = sm100::smem_u32(wsm), xsm_u = sm100::smem_u32(xsm);
+  pdl_launch_dependents();
+  pdl_wait();
+  // one batch of copies: the W slice (kc rows of 128 bytes) and the X slice (M rows of kc elements; rows past M zero)
+  {
+    const T* W = reinterpret_cast<const T*>(g.w) + (int64_t)k0 * g.N + n0;
+    for (int idx = tid; idx < kc * 8; idx += SK_THREADS) {
+      const int row = idx >> 3, ch = idx & 7;
+      sk_cp_async16(wsm_u + row * 128 + ((ch ^ (row & 7)) << 4), W + (int64_t)row * g.N + ch * 8);
+    }
+    const T* X = reinterpret_cast<const T*>(g.x) + k0;
+    const int xch = kc >> 3;
+    for (int idx = tid; idx < SK_ROWS * xch; idx += SK_THREADS) {
+      const int row = idx / xch, ch = idx - row * xch;
+      if (row < g.M) sk_cp_async16(xsm_u + row * x_pitch + ch * 16, X + (int64_t)row * g.K + ch * 8);
+      else *reinterpret_cast<uint4*>(xsm + row * x_pitch + ch * 16) = make_uint4(0, 0, 0, 0);
+    }
+    sk_cp_async_wait_all();
+    __syncthreads();
+  }
+  // warp w: columns [16 w, 16 w + 16) of the slab, all of the slice's k
+  float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+  {
+    const int mi = lane >> 3, r = lane & 7;
+    const uint32_t a_addr = xsm_u + (lane & 15) * x_pitch + (lane >> 4) * 16;
+    const int b_k = (mi & 1) * 8 + r;          // k within the 16-step; (k & 7) == r
+    const int b_ch = warp * 2 + (mi >> 1);     // 16-byte unit within the 128-byte row
+    const uint32_t b_addr = wsm_u + b_k * 128 + ((b_ch ^ r) << 4);
+#pragma unroll 4
+    for (int kk = 0; kk < kc; kk += 16) {
+      uint32_t a[4], bq[4];
+      sk_ldmatrix_x4(a_addr + kk * 2, a);
+      sk_ldmatrix_x4_trans(b_addr + kk * 128, bq);
+      sk_mma<T>(acc[0], a, bq[0], bq[1]);
+      sk_mma<T>(acc[1], a, bq[2], bq[3]);
+    }
+  }
+  // the slice's partial: rows lane / 4 and lane / 4 + 8, columns 16 w + 8 t + 2 (lane % 4) + {0, 1}
+  {
+    float* P = g.partial + (int64_t)split * SK_ROWS * g.N + n0 + warp * 16 + 2 * (lane & 3);
+    const int r0 = lane >> 2;
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      if (r0 < g.M) __stcg(reinterpret_cast<float2*>(P + (int64_t)r0 * g.N + 8 * t), make_float2(acc[t][0], acc[t][1]));
+      if (r0 + 8 < g.M) __stcg(reinterpret_cast<float2*>(P + (int64_t)(r0 + 8) * g.N + 8 * t), make_float2(acc[t][2], acc[t][3]));
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned old = atomicAdd(g.counters + slab, 1u);
+    const int last = old == (unsigned)(g.splits - 1);
+    if (last) g.counters[slab] = 0;   // everybody has arrived: ready for the next launch
+    s_last = last;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // the slab's last CTA: thread t owns row t / 8, columns [8 (t % 8), 8 (t % 8) + 8)
+  const int row = tid >> 3, col = n0 + (tid & 7) * 8;
+  if (row >= g.M) return;
+  float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  const float* P = g.partial + (int64_t)row * g.N + col;
+  const int64_t pstride = (int64_t)SK_ROWS * g.N;
+  int s = 0;
+  for (; s + 4 <= g.splits; s += 4) {   // four slices' loads in flight, added in slice order
+    float4 q[8];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      q[2 * u] = __ldcg(reinterpret_cast<const float4*>(P + (s + u) * pstride));
+      q[2 * u + 1] = __ldcg(reinterpret_cast<const float4*>(P + (s + u) * pstride + 4));
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      v[0] += q[2 * u].x; v[1] += q[2 * u].y; v[2] += q[2 * u].z; v[3] += q[2 * u].w;
+      v[4] += q[2 * u + 1].x; v[5] += q[2 * u + 1].y; v[6] += q[2 * u + 1].z; v[7] += q[2 * u + 1].w;
+    }
+  }
+  for (; s < g.splits; ++s) {
+    const float4 q0 = __ldcg(reinterpret_cast<const float4*>(P + s * pstride)), q1 = __ldcg(reinterpret_cast<const float4*>(P + s * pstride + 4));
+    v[0] += q0.x; v[1] += q0.y; v[2] += q0.z; v[3] += q0.w;
+    v[4] += q1.x; v[5] += q1.y; v[6] += q1.z; v[7] += q1.w;
+  }
+  if (g.bias) {
+    const uint4 bq = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(g.bias) + col);
+    const T* bt = reinterpret_cast<const T*>(&bq);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] += sk_to_f<T>(bt[j]);
+  }
+  apply_activation_n<8, true>(g.act, v);
+  uint4 out;
+  T* ot = reinterpret_cast<T*>(&out);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) ot[j] = sk_from_f<T>(v[j]);
+  if (g.residual) {   // the rounded value combined with the residual, rounded again
+    const uint4 rq = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(g.residual) + (int64_t)row * g.N + col);
+    const T* rt = reinterpret_cast<const T*>(&rq);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float a = sk_to_f<T>(ot[j]), r = sk_to_f<T>(rt[j]);
+      ot[j] = sk_from_f<T>(g.residual_mul ? a * r : a + r);
+    }
+  }
+  *reinterpret_cast<uint4*>(reinterpret_cast<T*>(g.c) + (int64_t)row * g.N + col) = out;
+}
+
+struct SkPlan { int splits, kc; };
+
+bool sk_shape_ok(const GemmParams& p) {
+  static const bool on = []() { const char* v = getenv("B200MLX_GEMM_SKINNY"); return !(v && v[0] == '0'); }();
+  if (!on) return false;
+  if (p.dtype != B200_BFLOAT16 && p.dtype != B200_FLOAT16) return false;
+  if (p.batch != 1 || p.m < 1 || p.m > SK_ROWS || !p.a_k_major || p.b_k_major) return false;
+  if (p.n % SK_BN != 0 || p.k % 16 != 0 || p.n < SK_BN || p.k < 16 || p.n > (1 << 20) || p.k > (1 << 20)) return false;
+  if (p.ldc != 0 && p.ldc != p.n) return false;
+  return p.num_c_extra == 0;
+}
+
+SkPlan sk_plan(const GemmParams& p, int sm_count) {
+  const int64_t slabs = p.n / SK_BN;
+  int64_t splits = (2 * (int64_t)sm_count + slabs - 1) / slabs;
+  if (splits < 1) splits = 1;
+  if (splits > p.k / 16) splits = p.k / 16;
+  int64_t kc = ((p.k + splits - 1) / splits + 15) / 16 * 16;
+  if (kc > SK_MAX_KC) kc = SK_MAX_KC;
+  splits = (p.k + kc - 1) / kc;
+  return SkPlan{(int)splits, (int)kc};
+}
+
+}  // namespace
+
+int64_t gemm_skinny_scratch_bytes(const GemmParams& p, int sm_count) {
+  if (!sk_shape_ok(p)) return 0;
+  return (int64_t)sk_plan(p, sm_count).splits * SK_ROWS * p.n * 4;
+}
+int64_t gemm_skinny_counter_bytes(const GemmParams& p) { return sk_shape_ok(p) ? p.n / SK_BN * 4 : 0; }
+
+Status gemm_skinny(Device* dev, const GemmParams& p, bool* taken) {
+  *taken = false;
+  if (!sk_shape_ok(p) || !p.split_scratch || !p.skinny_counters) return Status::OK();
+  const SkPlan pl = sk_plan(p, dev->sm_count());
+  if (p.split_scratch_bytes < (int64_t)pl.splits * SK_ROWS * p.n * 4) return Status::OK();
+  auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  if (!al(p.a) || !al(p.b) || !al(p.c) || !al(p.bias) || !al(p.residual) || !al(p.split_scratch)) return Status::OK();
+  B200_TRY(dev->MakeCurrent());
+  SkArgs g;
+  g.x = p.a; g.w = p.b; g.c = p.c; g.bias = p.bias; g.residual = p.residual;
+  g.partial = reinterpret_cast<float*>(p.split_scratch);
+  g.counters = reinterpret_cast<unsigned*>(p.skinny_counters);
+  g.M = (int)p.m; g.N = (int)p.n; g.K = (int)p.k; g.kc = pl.kc; g.splits = pl.splits;
+  g.act = p.activation; g.residual_mul = p.residual_op;
+  const size_t smem = (size_t)pl.kc * SK_BN * 2 + (size_t)SK_ROWS * (pl.kc + SK_X_PAD) * 2;
+  auto kern = p.dtype == B200_FLOAT16 ? gemm_skinny_kernel<__half> : gemm_skinny_kernel<__nv_bfloat16>;
+  static std::mutex mu;
+  static std::map<std::pair<int, const void*>, bool> configured;   // per device and kernel
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    bool& done = configured[{dev->ordinal(), (const void*)kern}];
+    if (!done) {
+      B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_MAX_KC * SK_BN * 2 + SK_ROWS * (SK_MAX_KC + SK_X_PAD) * 2));
+      done = true;
+    }
+  }
+  static const bool pdl_on = []() { const char* v = getenv("B200MLX_PDL"); return !(v && v[0] == '0'); }();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(p.n / SK_BN), (unsigned)pl.splits);
+  cfg.blockDim = dim3(SK_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = dev->stream();
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_on ? 1 : 0;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, g);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return Status::Cuda(strfmt("gemm_skinny: %s", cudaGetErrorString(e)));
+  }
+  *taken = true;
+  return dev->CheckLaunch("gemm_skinny");
+}
+
+}  // namespace k
+}  // namespace b200

@@ -151,9 +151,19 @@ struct DynArgs {
   void* y;
   int rank;
   int64_t x_dims[kMaxDims], b_dims[kMaxDims];
+  int64_t u_strides[kMaxDims];   // of the update block, in elements
   const void* starts[kMaxDims];
   int start_dtypes[kMaxDims];
 };
+// The update block's strides: the caller's, or dense.
+static void fill_update_strides(const DynSliceParams& p, DynArgs* a) {
+  int64_t dense = 1;
+  for (int d = kMaxDims - 1; d >= 0; --d) {
+    if (d >= p.rank) { a->u_strides[d] = 0; continue; }
+    a->u_strides[d] = p.u_strided ? p.u_strides[d] : dense;
+    dense *= p.b_dims[d];
+  }
+}
 __device__ __forceinline__ int64_t load_index(const void* p, int dtype) {
   switch (dtype) {
     case B200_INT8: return *reinterpret_cast<const int8_t*>(p);
@@ -200,15 +210,14 @@ __global__ void __launch_bounds__(256) dynamic_update_slice_kernel(const DynArgs
   __shared__ int64_t start[kMaxDims];
   block_starts(a, start);
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    int64_t rem = i, usrc = 0, ustride = 1;
+    int64_t rem = i, usrc = 0;
     bool inside = true;
     for (int d = a.rank - 1; d >= 0; --d) {
       const int64_t c = rem % a.x_dims[d];
       rem /= a.x_dims[d];
       const int64_t r = c - start[d];
       inside = inside && r >= 0 && r < a.b_dims[d];
-      usrc += r * ustride;
-      ustride *= a.b_dims[d];
+      usrc += r * a.u_strides[d];
     }
     reinterpret_cast<E*>(a.y)[i] = inside ? reinterpret_cast<const E*>(a.u)[usrc] : reinterpret_cast<const E*>(a.x)[i];
   }
@@ -298,14 +307,15 @@ __global__ void __launch_bounds__(256) dynamic_update_inplace_kernel(const DynAr
   __shared__ int64_t start[kMaxDims];
   block_starts(a, start);
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    int64_t rem = i, dst = 0, stride = 1;
+    int64_t rem = i, dst = 0, src = 0, stride = 1;
     for (int d = a.rank - 1; d >= 0; --d) {
       const int64_t c = rem % a.b_dims[d];
       rem /= a.b_dims[d];
       dst += (c + start[d]) * stride;
+      src += c * a.u_strides[d];
       stride *= a.x_dims[d];
     }
-    reinterpret_cast<E*>(a.y)[dst] = reinterpret_cast<const E*>(a.u)[i];
+    reinterpret_cast<E*>(a.y)[dst] = reinterpret_cast<const E*>(a.u)[src];
   }
 }
 
@@ -313,6 +323,7 @@ Status dynamic_update_slice_inplace(Device* dev, const DynSliceParams& p) {
   if (p.rank < 0 || p.rank > kMaxDims) return Status::Invalid("dynamic slice: rank");
   DynArgs a;
   a.x = p.y; a.u = p.u; a.y = p.y; a.rank = p.rank;
+  fill_update_strides(p, &a);
   int64_t total = 1;
   for (int d = 0; d < kMaxDims; ++d) {
     a.x_dims[d] = d < p.rank ? p.x_dims[d] : 1;
@@ -339,6 +350,7 @@ static Status dyn_launch(Device* dev, const DynSliceParams& p, bool update) {
   if (p.rank < 0 || p.rank > kMaxDims) return Status::Invalid("dynamic slice: rank");
   DynArgs a;
   a.x = p.x; a.u = p.u; a.y = p.y; a.rank = p.rank;
+  fill_update_strides(p, &a);
   int64_t total = 1;
   for (int d = 0; d < kMaxDims; ++d) {
     a.x_dims[d] = d < p.rank ? p.x_dims[d] : 1;

@@ -472,6 +472,18 @@ class Planner {
     }
   }
 
+  // Device memory of the plan's own, zeroed once when the plan is built (counters that their kernel leaves at zero).
+  Status NewZeroedConst(int64_t nbytes, int* slot) {
+    void* p = nullptr;
+    B200_TRY(ex_->dev->Alloc(nbytes > 0 ? nbytes : 1, &p));
+    ex_->const_ptrs.push_back(p);
+    B200_TRY(ex_->dev->MakeCurrent());
+    B200_CUDA_TRY(cudaMemsetAsync(p, 0, (size_t)(nbytes > 0 ? nbytes : 1), ex_->dev->stream()));
+    B200_CUDA_TRY(cudaStreamSynchronize(ex_->dev->stream()));
+    *slot = NewSlot(SlotKind::Const, (int)ex_->const_ptrs.size() - 1, nbytes);
+    return Status::OK();
+  }
+
   Status EmitConstant(Node* x) {
     void* p = nullptr;
     const int64_t nbytes = (int64_t)x->data.size();
@@ -1010,7 +1022,13 @@ class Planner {
     Node* upd = update ? x->in[1] : nullptr;
     const size_t first = update ? 2 : 1;
     B200_TRY(EnsureMaterialized(operand));
-    if (upd) B200_TRY(EnsureMaterialized(upd));
+    // an update block that is a column range of a wider tensor (the K or V part of a fused projection) is read in place
+    Node* upd_src = nullptr;
+    int64_t upd_off = 0;
+    std::vector<int64_t> upd_strides;
+    if (upd && ColumnRangeView(upd, &upd_src, &upd_off, &upd_strides)) B200_TRY(EnsureMaterialized(upd_src));
+    else upd_src = nullptr;
+    if (upd && !upd_src) B200_TRY(EnsureMaterialized(upd));
     for (size_t i = first; i < x->in.size(); ++i) B200_TRY(EnsureMaterialized(x->in[i]));
     k::DynSliceParams dp;
     dp.elt_size = dtype_size(x->dtype);
@@ -1022,9 +1040,14 @@ class Planner {
     }
     std::vector<int> start_slots;
     for (size_t i = first; i < x->in.size(); ++i) start_slots.push_back(SlotOf(x->in[i]));
-    const int x_slot = SlotOf(operand), u_slot = upd ? SlotOf(upd) : -1, out_slot = NewValueSlot(x);
+    const int x_slot = SlotOf(operand), u_slot = upd ? SlotOf(upd_src ? upd_src : upd) : -1, out_slot = NewValueSlot(x);
+    const int64_t u_byte_off = upd_off * dtype_size(x->dtype);
+    if (upd_src) {
+      dp.u_strided = true;
+      for (int d = 0; d < dp.rank; ++d) dp.u_strides[d] = upd_strides[d];
+    }
     Step st;
-    st.desc = strfmt("move[%s rank=%d]", update ? "DynamicUpdateSlice" : "DynamicSlice", dp.rank);
+    st.desc = strfmt("move[%s rank=%d%s]", update ? "DynamicUpdateSlice" : "DynamicSlice", dp.rank, upd_src ? " update read in place" : "");
     st.reads = start_slots;
     st.reads.push_back(x_slot);
     if (upd) st.reads.push_back(u_slot);
@@ -1036,10 +1059,10 @@ class Planner {
       if (ex_->donate_alias.size() <= (size_t)ex_->slots[out_slot].index) ex_->donate_alias.resize(ex_->slots[out_slot].index + 1, -1);
       ex_->donate_alias[ex_->slots[out_slot].index] = ex_->slots[x_slot].index;
     }
-    st.run = [dp, start_slots, x_slot, u_slot, out_slot, update](Device* dev, void* const* p) -> Status {
+    st.run = [dp, start_slots, x_slot, u_slot, out_slot, update, u_byte_off](Device* dev, void* const* p) -> Status {
       k::DynSliceParams q = dp;
       q.x = p[x_slot];
-      q.u = u_slot >= 0 ? p[u_slot] : nullptr;
+      q.u = u_slot >= 0 ? (const char*)p[u_slot] + u_byte_off : nullptr;
       q.y = p[out_slot];
       for (size_t i = 0; i < start_slots.size(); ++i) q.starts[i] = p[start_slots[i]];
       if (update && q.x == q.y) return k::dynamic_update_slice_inplace(dev, q);
@@ -1235,12 +1258,21 @@ class Planner {
     st.writes = {gemm_out};
     // fp32 on the tensor cores splits both operands into bf16 planes: their room comes from the plan's arena, so the step
     // allocates nothing and can be recorded
-    const int64_t split_bytes = x->dtype == B200_FLOAT32 ? k::gemm_split_scratch_bytes(B, M, N, K) : 0;
+    // A 16-bit product of a handful of rows splits K over many CTAs: fp32 partial sums in the arena and a few counters
+    // of the step's own (zeroed once; the kernel leaves them at zero).
+    const int64_t skinny_bytes = k::gemm_skinny_scratch_bytes(gp, ex_->dev->sm_count());
+    const int64_t split_bytes = x->dtype == B200_FLOAT32 ? k::gemm_split_scratch_bytes(B, M, N, K) : skinny_bytes;
     const int split_slot = split_bytes > 0 ? NewTemp(split_bytes) : -1;
     if (split_slot >= 0) st.writes.push_back(split_slot);
-    st.run = [gp, a_slot, b_slot, bias_slot, res_slot, gemm_out, split_slot, split_bytes](Device* dev, void* const* p) -> Status {
+    int counter_slot = -1;
+    if (skinny_bytes > 0) {
+      B200_TRY(NewZeroedConst(k::gemm_skinny_counter_bytes(gp), &counter_slot));
+      st.desc.insert(st.desc.size() - 1, " few-rows");
+    }
+    st.run = [gp, a_slot, b_slot, bias_slot, res_slot, gemm_out, split_slot, split_bytes, counter_slot](Device* dev, void* const* p) -> Status {
       k::GemmParams q = gp;
       if (split_slot >= 0) { q.split_scratch = p[split_slot]; q.split_scratch_bytes = split_bytes; }
+      if (counter_slot >= 0) q.skinny_counters = p[counter_slot];
       q.a = p[a_slot];
       q.b = p[b_slot];
       q.c = p[gemm_out];
@@ -1881,6 +1913,43 @@ class Planner {
     return true;
   }
 
+  // Recognises t = Reshape*(Slice(X)) where the slice keeps every axis of X whole except a unit-stride range [lo, lo + w)
+  // of the last one, the slice has not been copied yet, and the reshapes keep the split "rows of X | columns of the
+  // range" (leading dims of t multiply to X's row count, the rest to w).  t can then be read in place inside X: fills
+  // the source node, the element offset and t's element strides.
+  bool ColumnRangeView(Node* t, Node** src, int64_t* offset, std::vector<int64_t>* strides) {
+    Node* sl = t;
+    while (sl->op == Op::Reshape) sl = sl->in[0];
+    if (sl->op != Op::Slice || sl->rank() < 1 || t->rank() < 1 || slot_of_[ViewBase(t)->id] >= 0 || slot_of_[ViewBase(sl)->id] >= 0) return false;
+    Node* X = sl->in[0];
+    const int r = sl->rank();
+    for (int d = 0; d < r; ++d) {
+      if (sl->ia[2 * d + 1] != 1) return false;
+      if (d < r - 1 && (sl->ia[2 * d] != 0 || sl->dims[d] != X->dims[d])) return false;
+    }
+    const int64_t W = X->dims[r - 1], w = sl->dims[r - 1], lo = sl->ia[2 * (r - 1)];
+    int64_t rows = 1;
+    for (int d = 0; d < r - 1; ++d) rows *= X->dims[d];
+    if (w <= 0 || rows <= 0 || w == W) return false;
+    int j = 0;
+    int64_t lead = 1;
+    while (j < t->rank() && lead < rows) lead *= t->dims[j++];
+    if (lead != rows) return false;
+    int64_t rest = 1;
+    for (int d = j; d < t->rank(); ++d) rest *= t->dims[d];
+    if (rest != w) return false;
+    Node* base = ViewBase(X);
+    if (!(base->op == Op::Parameter || slot_of_[base->id] >= 0 || MustMaterialize(base))) return false;
+    strides->assign(t->rank(), 0);
+    int64_t st = 1;
+    for (int d = t->rank() - 1; d >= j; --d) { (*strides)[d] = st; st *= t->dims[d]; }
+    st = W;
+    for (int d = j - 1; d >= 0; --d) { (*strides)[d] = st; st *= t->dims[d]; }
+    *src = X;
+    *offset = lo;
+    return true;
+  }
+
   Status EmitAttention(Node* x) {
     Node* q = x->in[0];
     Node* kk = x->in[1];
@@ -1889,14 +1958,28 @@ class Planner {
     Node* srcs[3] = {q, kk, v};
     int64_t offs[3] = {0, 0, 0};
     int64_t strd[3][3] = {{0, 0, 0}, {0, 0, 0}, {0, 0, 0}};
+    k::AttentionParams probe;
+    probe.B = q->dims[0]; probe.H = x->ia[0]; probe.Hkv = x->ia[1];
+    probe.Sq = q->dims[bshd ? 1 : 2]; probe.Sk = kk->dims[bshd ? 1 : 2];
+    probe.head_dim = q->dims[3]; probe.causal = x->ia[3] != 0; probe.scale = x->fa[0]; probe.dtype = x->dtype;
+    const bool decode_shape = k::attention_decode_supported(probe);
     if (x->dtype == B200_BFLOAT16 || x->dtype == B200_FLOAT16) {
       for (int i = 0; i < 3; ++i) {
         Node* src;
         int64_t off, st3[3];
+        std::vector<int64_t> st4;
         if (StridedProjectionView(srcs[i], bshd, &src, &off, st3)) {
           srcs[i] = src;
           offs[i] = off;
           for (int j = 0; j < 3; ++j) strd[i][j] = st3[j];
+        } else if (i == 0 && decode_shape && ColumnRangeView(q, &src, &off, &st4) &&
+                   st4[3] == 1 && off % 8 == 0 && st4[0] % 8 == 0 && st4[bshd ? 2 : 1] % 8 == 0) {
+          // one query position: the cache-reading kernel takes the query in place inside the fused projection
+          srcs[i] = src;
+          offs[i] = off;
+          strd[i][0] = st4[0];
+          strd[i][1] = st4[bshd ? 2 : 1];
+          strd[i][2] = st4[0];   // one position only: never multiplied by anything but 0
         }
       }
     }
@@ -1915,22 +1998,46 @@ class Planner {
     ap.scale = x->fa[0];
     ap.dtype = x->dtype;
     for (int j = 0; j < 3; ++j) { ap.q_strides[j] = strd[0][j]; ap.k_strides[j] = strd[1][j]; ap.v_strides[j] = strd[2][j]; }
+    // One query position: the cache-reading kernel, which also takes the mask (dims aligned to the trailing dims of
+    // [B, H, 1, Sk]; of [B, 1, H, Sk] for a rank-4 mask in the BSHD layout).
+    const bool decode = k::attention_decode_supported(ap);
+    Node* mk = x->in.size() > 3 ? x->in[3] : nullptr;
+    if (mk && !decode) return Status::Unsupported("attention with a mask tensor needs one query position");
+    int ms = -1;
+    if (mk) {
+      B200_TRY(EnsureMaterialized(mk));
+      ms = SlotOf(mk);
+      ap.mask_kind = mk->dtype == B200_BOOL ? 1 : 2;
+      const int r = mk->rank();
+      const int h_pos = bshd && r == 4 ? 2 : 1;   // position of the head dim among the four
+      int64_t stride = 1;
+      for (int i = r - 1; i >= 0; --i) {
+        const int pos = 4 - r + i;   // position among the four dims
+        const int64_t st1 = mk->dims[i] == 1 ? 0 : stride;
+        if (pos == 3) ap.m_k = st1;
+        else if (pos == h_pos) ap.m_h = st1;
+        else if (pos == 0) ap.m_b = st1;
+        stride *= mk->dims[i];
+      }
+    }
     const int qs = SlotOf(srcs[0]), ks = SlotOf(srcs[1]), vs = SlotOf(srcs[2]), os = NewValueSlot(x);
     const int64_t es = dtype_size(x->dtype);
     const int64_t qo = offs[0] * es, ko = offs[1] * es, vo = offs[2] * es;
     Step st;
-    st.desc = strfmt("attention[B=%lld H=%lld Hkv=%lld Sq=%lld Sk=%lld D=%lld %s %s causal=%d]", (long long)ap.B, (long long)ap.H,
-                     (long long)ap.Hkv, (long long)ap.Sq, (long long)ap.Sk, (long long)ap.head_dim, dtype_name(ap.dtype),
-                     bshd ? "BSHD" : "BHSD", (int)ap.causal);
+    st.desc = strfmt("%s[B=%lld H=%lld Hkv=%lld Sq=%lld Sk=%lld D=%lld %s %s causal=%d%s]", decode ? "attention_decode" : "attention",
+                     (long long)ap.B, (long long)ap.H, (long long)ap.Hkv, (long long)ap.Sq, (long long)ap.Sk, (long long)ap.head_dim,
+                     dtype_name(ap.dtype), bshd ? "BSHD" : "BHSD", (int)ap.causal, mk ? (ap.mask_kind == 1 ? " mask=Bool" : " mask=additive") : "");
     st.reads = {qs, ks, vs};
+    if (ms >= 0) st.reads.push_back(ms);
     st.writes = {os};
-    st.run = [ap, qs, ks, vs, os, qo, ko, vo](Device* dev, void* const* p) -> Status {
+    st.run = [ap, qs, ks, vs, os, ms, qo, ko, vo, decode](Device* dev, void* const* p) -> Status {
       k::AttentionParams a = ap;
       a.q = (const char*)p[qs] + qo;
       a.k = (const char*)p[ks] + ko;
       a.v = (const char*)p[vs] + vo;
       a.o = p[os];
-      return k::attention(dev, a);
+      a.mask = ms >= 0 ? p[ms] : nullptr;
+      return decode ? k::attention_decode(dev, a) : k::attention(dev, a);
     };
     ex_->steps.push_back(std::move(st));
     return Status::OK();

@@ -1,0 +1,119 @@
+"""16-bit matrix products with at most 16 rows (a decoding step's projections): the K-split kernel against the oracle.
+
+K is cut into slices that different CTAs multiply; the slices' fp32 partial sums are added in slice order by the last
+CTA to arrive, which also applies bias, activation and residual.  Checked: every row count 1..16, K that does not
+divide evenly among the slices, one slice only, epilogue combinations, that the counters are left ready for the next
+run (the same executable run many times), and that two runs give identical bits.
+"""
+import ml_dtypes
+import numpy as np
+import pytest
+
+from oracle.oracle import OracleFunction, compare
+from tests.util import rng_array, run_backend
+
+pytestmark = pytest.mark.gpu
+BF16 = ml_dtypes.bfloat16
+RTOL = 2e-2
+
+
+def _dense(f, x, w, b, act, res):
+    y = f.FusedDense(x, w, b, act)
+    return f.Add(y, res) if res is not None else y
+
+
+def _check(b200, backend, M, N, K, dtype, bias, act, residual, seed=0, lead=None):
+    rng = np.random.default_rng(seed)
+    xs = (M, K) if lead is None else lead + (K,)
+    x = rng_array(rng, xs, dtype, 1.0)
+    w = rng_array(rng, (K, N), dtype, 1.0 / np.sqrt(K))
+    inputs = [x, w]
+    bi = ri = None
+    if bias:
+        bi = len(inputs); inputs.append(rng_array(rng, (N,), dtype))
+    if residual:
+        ri = len(inputs); inputs.append(rng_array(rng, xs[:-1] + (N,), dtype))
+    build = lambda f, *p: _dense(f, p[0], p[1], p[bi] if bias else None, act, p[ri] if residual else None)
+    (got,), plan = run_backend(b200, backend, build, inputs, describe=True)
+    assert "few-rows" in plan and plan.count("\n") == 1, plan
+    # the yardstick: exact product rounded once (twice with a residual), as the fused epilogue does
+    o = OracleFunction()
+    want = o.FusedDense(x.astype(np.float32), w.astype(np.float32), inputs[bi].astype(np.float32) if bias else None, act).astype(dtype)
+    if residual:
+        want = (want.astype(np.float32) + inputs[ri].astype(np.float32)).astype(dtype)
+    ok, viol = compare(got, want, RTOL, 1.0)
+    assert ok, viol
+    return got
+
+
+@pytest.mark.parametrize("M", list(range(1, 17)))
+def test_every_row_count(b200, backend, M):
+    _check(b200, backend, M, 768, 768, BF16, True, 0, False, seed=M)
+
+
+@pytest.mark.parametrize("N,K", [(64, 16), (64, 48), (128, 8192), (768, 3072), (2304, 768), (3072, 768), (4096, 11008), (1024, 1040), (320, 80),
+                                 (32000 // 64 * 64, 512)])
+def test_shapes(b200, backend, N, K):
+    _check(b200, backend, 16, N, K, BF16, False, 0, False, seed=N + K)
+
+
+@pytest.mark.parametrize("bias", [False, True])
+@pytest.mark.parametrize("act", [0, 1, 2, 3, 4], ids=["none", "gelu", "relu", "silu", "tanh"])
+@pytest.mark.parametrize("residual", [False, True])
+def test_epilogues(b200, backend, bias, act, residual):
+    _check(b200, backend, 7, 512, 1024, BF16, bias, act, residual, seed=17)
+
+
+def test_f16_and_leading_dims(b200, backend):
+    _check(b200, backend, 12, 768, 3072, np.float16, True, 1, True, seed=3)
+    _check(b200, backend, 16, 768, 768, BF16, True, 0, True, seed=4, lead=(16, 1))
+    _check(b200, backend, 6, 256, 256, np.float16, False, 0, False, seed=5, lead=(2, 3))
+
+
+def test_repeated_runs_are_identical_and_leave_the_counters_ready(b200, backend):
+    rng = np.random.default_rng(8)
+    x, w, b = rng_array(rng, (16, 3072), BF16), rng_array(rng, (3072, 768), BF16, 0.02), rng_array(rng, (768,), BF16)
+    builder = backend.Builder("few_rows")
+    f = builder.Main()
+    params = [f.Parameter(f"p{i}", b200.Shape(b200.dtypes.from_numpy(a.dtype), a.shape)) for i, a in enumerate((x, w, b))]
+    f.Return([f.FusedDense(params[0], params[1], params[2], 1)], None)
+    exe = builder.Compile()
+    bufs = [backend.FromNumpy(a) for a in (x, w, b)]
+    first = None
+    for run in range(12):   # direct launches first, then the recorded plan
+        (r,) = exe.Execute(bufs, None, 0)
+        got = backend.ToNumpy(r)
+        backend.BufferFinalize(r)
+        if first is None:
+            first = got
+        else:
+            np.testing.assert_array_equal(got.view(np.uint16), first.view(np.uint16))
+    want = OracleFunction().FusedDense(x.astype(np.float32), w.astype(np.float32), b.astype(np.float32), 1).astype(BF16)
+    ok, viol = compare(first, want, RTOL, 1.0)
+    assert ok, viol
+    exe.Finalize()
+    builder.Finalize()
+
+
+def test_two_products_in_one_plan_have_counters_of_their_own(b200, backend):
+    rng = np.random.default_rng(9)
+    x, w1, w2 = rng_array(rng, (4, 256), BF16), rng_array(rng, (256, 1024), BF16, 0.06), rng_array(rng, (1024, 256), BF16, 0.03)
+    build = lambda f, xx, a, b: f.FusedDense(f.FusedDense(xx, a, None, 2), b, None, 0)
+    (got,), plan = run_backend(b200, backend, build, [x, w1, w2], describe=True)
+    assert plan.count("few-rows") == 2, plan
+    o = OracleFunction()
+    h = o.FusedDense(x.astype(np.float32), w1.astype(np.float32), None, 2).astype(BF16)
+    want = o.FusedDense(h.astype(np.float32), w2.astype(np.float32), None, 0).astype(BF16)
+    ok, viol = compare(got, want, RTOL, 1.0)
+    assert ok, viol
+
+
+def test_other_shapes_keep_their_kernels(b200, backend):
+    rng = np.random.default_rng(10)
+    for M, N, K in [(17, 768, 768), (16, 100, 64), (16, 64, 24)]:
+        x, w = rng_array(rng, (M, K), BF16), rng_array(rng, (K, N), BF16, 0.1)
+        (got,), plan = run_backend(b200, backend, lambda f, a, b: f.FusedDense(a, b, None, 0), [x, w], describe=True)
+        assert "few-rows" not in plan, plan
+        want = OracleFunction().FusedDense(x.astype(np.float32), w.astype(np.float32), None, 0).astype(BF16)
+        ok, viol = compare(got, want, RTOL, 1.0)
+        assert ok, viol
