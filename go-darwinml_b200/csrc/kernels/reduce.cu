@@ -19,6 +19,7 @@
 #include <type_traits>
 
 #include "../kernels.h"
+#include "sm100_ptx.cuh"
 
 namespace b200 {
 namespace k {
@@ -254,19 +255,30 @@ template <typename A> __device__ __forceinline__ bool better(bool is_min, A cv, 
   return is_min ? (cv < bv) : (cv > bv);
 }
 
-// grid = ceil(outer*inner / rows_per_cta); one warp per (outer, inner) pair when inner == 1,
-// one thread per pair otherwise.
+// One row per cluster (grid (outer, C), cluster (1, C)): a CTA scans its share of the row, four independent loads per
+// thread in flight, and the CTAs' winners meet in CTA 0 through distributed shared memory.  A long row with few rows in
+// all (an argmax over the vocabulary of a decoding step) would otherwise be one CTA's serial scan.
 template <typename T, typename A, typename O>
-__global__ void __launch_bounds__(256) argminmax_rows_kernel(const T* x, O* y, bool is_min, int64_t outer, int64_t n) {
-  __shared__ unsigned long long sv[8];
-  __shared__ long long si[8];
+__global__ void __launch_bounds__(1024) argminmax_rows_kernel(const T* x, O* y, bool is_min, int64_t outer, int64_t n) {
+  __shared__ unsigned long long sv[32];
+  __shared__ long long si[32];
+  __shared__ unsigned long long cta_v;
+  __shared__ long long cta_i;
   const int64_t row = blockIdx.x;
+  const int rank = blockIdx.y, csize = gridDim.y;
+  const int64_t chunk = (n + csize - 1) / csize;
+  const int64_t begin = rank * chunk, end = begin + chunk < n ? begin + chunk : n;
   const T* xr = x + row * n;
   A bv = (A)0;
   int64_t bi = -1;
-  for (int64_t j = threadIdx.x; j < n; j += 256) {
-    const A v = to_acc<T, A>(xr[j]);
-    if (better<A>(is_min, v, j, bv, bi)) { bv = v; bi = j; }
+  const int64_t step = blockDim.x;
+  for (int64_t j = begin + threadIdx.x; j < end; j += 4 * step) {
+    A v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = j + u * step < end ? to_acc<T, A>(xr[j + u * step]) : (A)0;
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (j + u * step < end && better<A>(is_min, v[u], j + u * step, bv, bi)) { bv = v[u]; bi = j + u * step; }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -274,20 +286,38 @@ __global__ void __launch_bounds__(256) argminmax_rows_kernel(const T* x, O* y, b
     const int64_t oi = __shfl_xor_sync(0xffffffffu, (long long)bi, o);
     if (better<A>(is_min, ov, oi, bv, bi)) { bv = ov; bi = oi; }
   }
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (lane == 0) { *reinterpret_cast<A*>(&sv[warp]) = bv; si[warp] = bi; }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  if (lane == 0) { sv[warp] = 0; *reinterpret_cast<A*>(&sv[warp]) = bv; si[warp] = bi; }
   __syncthreads();
   if (warp == 0) {
-    bv = (lane < 8) ? *reinterpret_cast<A*>(&sv[lane]) : (A)0;
-    bi = (lane < 8) ? si[lane] : -1;
+    bv = (lane < warps) ? *reinterpret_cast<A*>(&sv[lane]) : (A)0;
+    bi = (lane < warps) ? si[lane] : -1;
 #pragma unroll
-    for (int o = 4; o > 0; o >>= 1) {
+    for (int o = 16; o > 0; o >>= 1) {
       const A ov = shfl_xor_any<A>(bv, o);
       const int64_t oi = __shfl_xor_sync(0xffffffffu, (long long)bi, o);
       if (better<A>(is_min, ov, oi, bv, bi)) { bv = ov; bi = oi; }
     }
-    if (lane == 0) y[row] = (O)bi;
+    if (lane == 0) {
+      if (csize == 1) y[row] = (O)bi;
+      else { cta_v = 0; *reinterpret_cast<A*>(&cta_v) = bv; cta_i = bi; }
+    }
   }
+  if (csize == 1) return;
+  sm100::cluster_sync_all();
+  if (rank == 0 && threadIdx.x == 0) {
+    const uint32_t va = sm100::smem_u32(&cta_v), ia = sm100::smem_u32(&cta_i);
+    for (int r = 1; r < csize; ++r) {
+      unsigned long long rv;
+      long long ri;
+      asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(rv) : "r"(sm100::map_to_cta(va, (uint32_t)r)) : "memory");
+      asm volatile("ld.shared::cluster.s64 %0, [%1];" : "=l"(ri) : "r"(sm100::map_to_cta(ia, (uint32_t)r)) : "memory");
+      const A ov = *reinterpret_cast<A*>(&rv);
+      if (better<A>(is_min, ov, (int64_t)ri, bv, bi)) { bv = ov; bi = ri; }
+    }
+    y[row] = (O)bi;
+  }
+  sm100::cluster_sync_all();   // nobody leaves while its winner may still be read
 }
 
 template <typename T, typename A, typename O>
@@ -310,7 +340,27 @@ Status argminmax_typed2(Device* dev, const void* xv, void* yv, bool is_min, int6
   using A = typename AccOf<T>::type;
   cudaStream_t s = dev->stream();
   if (inner == 1) {
-    argminmax_rows_kernel<T, A, O><<<(unsigned)outer, 256, 0, s>>>((const T*)xv, (O*)yv, is_min, outer, n);
+    // CTAs per row: enough to give every SM a share when the rows are few and long; at least 4096 elements each
+    int64_t c = 1;
+    if (outer < dev->sm_count() && n >= 8192) {
+      c = (dev->sm_count() + outer - 1) / outer;
+      if (c > 8) c = 8;
+      if (c > n / 4096) c = n / 4096;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)outer, (unsigned)c);
+    cfg.blockDim = dim3(n >= 4096 ? 1024 : 256);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = (unsigned)c; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, argminmax_rows_kernel<T, A, O>, (const T*)xv, (O*)yv, is_min, outer, n);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return Status::Cuda(strfmt("argminmax_rows: %s", cudaGetErrorString(e)));
+    }
     return dev->CheckLaunch("argminmax_rows");
   }
   const int64_t count = outer * inner;

@@ -239,6 +239,23 @@ def test_argmax_ties_and_nan(b200, backend):
     np.testing.assert_array_equal(got, np.array([1, 0, 0], dtype=np.int64))  # lowest index on ties; first NaN wins
 
 
+@pytest.mark.parametrize("rows,n", [(1, 8192), (3, 8191), (16, 50257), (2, 1000003), (147, 9000), (200, 9000)])
+@pytest.mark.parametrize("dtype", [np.float32, BF16, np.int64, np.float64], ids=["f32", "bf16", "i64", "f64"])
+def test_argminmax_long_rows_split_over_a_cluster(b200, backend, rows, n, dtype):
+    # few, long rows: each row is scanned by several CTAs whose winners meet in one; ties across the CTAs' shares
+    # must still go to the lowest index, and a NaN anywhere wins
+    rng = np.random.default_rng(rows + n)
+    x = rng_array(rng, (rows, n), dtype)
+    if np.dtype(dtype).kind == "f":
+        x = np.round(x.astype(np.float32) * 2).astype(dtype)   # few distinct values: many ties
+        if rows > 2:
+            x[1, n - 5] = np.nan
+            x[2, 7] = np.nan
+            x[2, n // 2] = np.nan
+    for is_min in (False, True):
+        assert_parity(b200, backend, lambda f, a: f.ArgMinMax(a, 1, b200.dtypes.Int32, is_min), [x])
+
+
 def test_argmax_vocab_sized_rows(b200, backend):
     x = rng_array(np.random.default_rng(20), (4, 50257), np.float32)
     assert_parity(b200, backend, lambda f, a: f.ArgMinMax(a, -1 + 2, b200.dtypes.Int32, False), [x])
