@@ -260,6 +260,9 @@ struct GemmParams {
   void* split_scratch = nullptr;
   int64_t split_scratch_bytes = 0;
   void* skinny_counters = nullptr;
+  // B is not written by anything that may still be running when this launch starts (a plan input or constant): a
+  // kernel launched as a programmatic dependent may then fetch it before the previous kernel has finished.
+  bool b_static = false;
 };
 int64_t gemm_skinny_scratch_bytes(const GemmParams& p, int sm_count);   // 0: not a shape gemm_skinny takes
 int64_t gemm_skinny_counter_bytes(const GemmParams& p);

@@ -4,9 +4,11 @@
 // streaming its whole K through one SM's load path (28 us for K = 3072, N = 768).  Here about two CTAs per SM share W:
 // a CTA owns 64 columns and one slice of K, brings its whole W slice (at most 512 x 64) and X slice into shared memory
 // with one batch of 16-byte asynchronous copies -- so all of W is in flight at once --, multiplies with
-// mma.sync m16n8k16 (X as the 16-row operand, rows past M zero), and writes a 16 x 64 fp32 partial.  The CTA that
-// arrives last on its column slab's counter adds the partials in slice order (the same sum on every run), applies the
-// epilogue and writes C; it leaves the counter at zero for the next launch.
+// mma.sync m16n8k16 (X as the 16-row operand, rows past M zero), and holds a 16 x 64 fp32 partial.  With K up to 8192
+// a slab's slices are the (at most 8) CTAs of one cluster: the partials meet through distributed shared memory, added
+// in slice order (the same sum on every run), each CTA finishing a share of the outputs (bias, activation, residual).
+// A longer K goes through global memory: the CTA that arrives last on its slab's counter adds the partials, again in
+// slice order, and writes C; it leaves the counter at zero for the next launch.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -27,6 +29,7 @@ constexpr int SK_THREADS = 128;
 constexpr int SK_BN = 64;
 constexpr int SK_ROWS = 16;
 constexpr int SK_MAX_KC = 512;
+constexpr int SK_MAX_SPLITS = 16;   // the last CTA adds the slices' partial sums: two rounds of eight loads at most (longer K: more, 512 per slice)
 constexpr int SK_X_PAD = 8;   // elements: the X rows' pitch is an odd number of 16-byte units, conflict-free for ldmatrix
 
 struct SkArgs {
@@ -38,6 +41,7 @@ struct SkArgs {
   float* partial;       // [splits, 16, N]
   unsigned* counters;   // [N / 64], zero between launches
   int M, N, K, kc, splits, act, residual_mul;
+  int w_static;   // W may be fetched before the previous kernel on the stream has finished
 };
 
 __device__ __forceinline__ void sk_cp_async16(uint32_t dst, const void* src) {
@@ -70,7 +74,10 @@ template <typename T> __device__ __forceinline__ T sk_from_f(float v);
 template <> __device__ __forceinline__ __nv_bfloat16 sk_from_f(float v) { return __float2bfloat16_rn(v); }
 template <> __device__ __forceinline__ __half sk_from_f(float v) { return __float2half_rn(v); }
 
-template <typename T>
+// CLUSTER: the slab's K slices are the CTAs of one cluster (at most 8); their partial sums stay in shared memory and
+// meet through distributed shared memory, each CTA finishing an equal share of the slab's outputs.  Otherwise (K too
+// long for 8 slices of 1024) the partial sums go through global memory and the slab's last CTA finishes them.
+template <typename T, bool CLUSTER>
 __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g) {
   extern __shared__ __align__(128) unsigned char sk_smem[];
   __shared__ int s_last;
@@ -84,14 +91,16 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
   unsigned char* xsm = sk_smem + (size_t)g.kc * SK_BN * 2;
   const uint32_t wsm_u = sm100::smem_u32(wsm), xsm_u = sm100::smem_u32(xsm);
   pdl_launch_dependents();
-  pdl_wait();
-  // one batch of copies: the W slice (kc rows of 128 bytes) and the X slice (M rows of kc elements; rows past M zero)
+  if (!g.w_static) pdl_wait();
+  // one batch of copies: the W slice (kc rows of 128 bytes) and the X slice (M rows of kc elements; rows past M zero).
+  // Weights that nothing in flight can be writing are requested before the previous kernel's results are waited for.
   {
     const T* W = reinterpret_cast<const T*>(g.w) + (int64_t)k0 * g.N + n0;
     for (int idx = tid; idx < kc * 8; idx += SK_THREADS) {
       const int row = idx >> 3, ch = idx & 7;
       sk_cp_async16(wsm_u + row * 128 + ((ch ^ (row & 7)) << 4), W + (int64_t)row * g.N + ch * 8);
     }
+    if (g.w_static) pdl_wait();
     const T* X = reinterpret_cast<const T*>(g.x) + k0;
     const int xch = kc >> 3;
     for (int idx = tid; idx < SK_ROWS * xch; idx += SK_THREADS) {
@@ -120,6 +129,42 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
     }
   }
   // the slice's partial: rows lane / 4 and lane / 4 + 8, columns 16 w + 8 t + 2 (lane % 4) + {0, 1}
+  if constexpr (CLUSTER) {
+    __syncthreads();   // everybody is done with the operand tiles: the partial takes their place
+    float* psm = reinterpret_cast<float*>(sk_smem);   // [16][64]
+    const int r0 = lane >> 2, c0 = warp * 16 + 2 * (lane & 3);
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      *reinterpret_cast<float2*>(psm + r0 * SK_BN + c0 + 8 * t) = make_float2(acc[t][0], acc[t][1]);
+      *reinterpret_cast<float2*>(psm + (r0 + 8) * SK_BN + c0 + 8 * t) = make_float2(acc[t][2], acc[t][3]);
+    }
+    sm100::cluster_sync_all();
+    const int csize = g.splits;
+    const int per = SK_ROWS * SK_BN / csize;   // outputs this CTA finishes (csize is 1, 2, 4 or 8)
+    const uint32_t psm_u = sm100::smem_u32(psm);
+    for (int e = split * per + tid; e < (split + 1) * per; e += SK_THREADS) {
+      const int row = e >> 6, col = e & 63;
+      if (row < g.M) {
+        float v = 0.f;
+        for (int c = 0; c < csize; ++c) {   // slice order: the same sum on every run
+          float pv;
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pv) : "r"(sm100::map_to_cta(psm_u + e * 4u, (uint32_t)c)) : "memory");
+          v += pv;
+        }
+        if (g.bias) v += sk_to_f<T>(reinterpret_cast<const T*>(g.bias)[n0 + col]);
+        float v1[2] = {v, 0.f};
+        apply_activation_n<2, true>(g.act, v1);
+        T o = sk_from_f<T>(v1[0]);
+        if (g.residual) {
+          const float a = sk_to_f<T>(o), r = sk_to_f<T>(reinterpret_cast<const T*>(g.residual)[(int64_t)row * g.N + n0 + col]);
+          o = sk_from_f<T>(g.residual_mul ? a * r : a + r);
+        }
+        reinterpret_cast<T*>(g.c)[(int64_t)row * g.N + n0 + col] = o;
+      }
+    }
+    sm100::cluster_sync_all();   // nobody leaves while its partial may still be read
+    return;
+  }
   {
     float* P = g.partial + (int64_t)split * SK_ROWS * g.N + n0 + warp * 16 + 2 * (lane & 3);
     const int r0 = lane >> 2;
@@ -147,15 +192,15 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
   const float* P = g.partial + (int64_t)row * g.N + col;
   const int64_t pstride = (int64_t)SK_ROWS * g.N;
   int s = 0;
-  for (; s + 4 <= g.splits; s += 4) {   // four slices' loads in flight, added in slice order
-    float4 q[8];
+  for (; s + 8 <= g.splits; s += 8) {   // eight slices' loads in flight (each round costs one trip to L2), added in slice order
+    float4 q[16];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < 8; ++u) {
       q[2 * u] = __ldcg(reinterpret_cast<const float4*>(P + (s + u) * pstride));
       q[2 * u + 1] = __ldcg(reinterpret_cast<const float4*>(P + (s + u) * pstride + 4));
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < 8; ++u) {
       v[0] += q[2 * u].x; v[1] += q[2 * u].y; v[2] += q[2 * u].z; v[3] += q[2 * u].w;
       v[4] += q[2 * u + 1].x; v[5] += q[2 * u + 1].y; v[6] += q[2 * u + 1].z; v[7] += q[2 * u + 1].w;
     }
@@ -188,7 +233,8 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
   *reinterpret_cast<uint4*>(reinterpret_cast<T*>(g.c) + (int64_t)row * g.N + col) = out;
 }
 
-struct SkPlan { int splits, kc; };
+struct SkPlan { int splits, kc; bool cluster; };
+constexpr int SK_CLUSTER_MAX_KC = 1024;
 
 bool sk_shape_ok(const GemmParams& p) {
   static const bool on = []() { const char* v = getenv("B200MLX_GEMM_SKINNY"); return !(v && v[0] == '0'); }();
@@ -202,20 +248,31 @@ bool sk_shape_ok(const GemmParams& p) {
 
 SkPlan sk_plan(const GemmParams& p, int sm_count) {
   const int64_t slabs = p.n / SK_BN;
+  static const bool cluster_on = []() { const char* v = getenv("B200MLX_GEMM_SKINNY_CLUSTER"); return !(v && v[0] == '0'); }();
+  if (cluster_on && p.k <= 8 * SK_CLUSTER_MAX_KC) {
+    // a power of two of slices, at most 8, about two CTAs per SM in all, at least 64 of K each (all of it when shorter)
+    int64_t splits = 8;
+    while (splits > 1 && (slabs * splits > 4 * (int64_t)sm_count || p.k / splits < 64)) splits /= 2;
+    while (((p.k + splits - 1) / splits + 15) / 16 * 16 > SK_CLUSTER_MAX_KC) splits *= 2;
+    const int64_t kc = ((p.k + splits - 1) / splits + 15) / 16 * 16;
+    if ((splits - 1) * kc < p.k) return SkPlan{(int)splits, (int)kc, true};   // every slice has some of K
+  }
   int64_t splits = (2 * (int64_t)sm_count + slabs - 1) / slabs;
   if (splits < 1) splits = 1;
   if (splits > p.k / 16) splits = p.k / 16;
+  if (splits > SK_MAX_SPLITS) splits = SK_MAX_SPLITS;
   int64_t kc = ((p.k + splits - 1) / splits + 15) / 16 * 16;
   if (kc > SK_MAX_KC) kc = SK_MAX_KC;
   splits = (p.k + kc - 1) / kc;
-  return SkPlan{(int)splits, (int)kc};
+  return SkPlan{(int)splits, (int)kc, false};
 }
 
 }  // namespace
 
 int64_t gemm_skinny_scratch_bytes(const GemmParams& p, int sm_count) {
   if (!sk_shape_ok(p)) return 0;
-  return (int64_t)sk_plan(p, sm_count).splits * SK_ROWS * p.n * 4;
+  const SkPlan pl = sk_plan(p, sm_count);
+  return pl.cluster ? 16 : (int64_t)pl.splits * SK_ROWS * p.n * 4;   // (16: "taken", nothing goes through it)
 }
 int64_t gemm_skinny_counter_bytes(const GemmParams& p) { return sk_shape_ok(p) ? p.n / SK_BN * 4 : 0; }
 
@@ -223,7 +280,7 @@ Status gemm_skinny(Device* dev, const GemmParams& p, bool* taken) {
   *taken = false;
   if (!sk_shape_ok(p) || !p.split_scratch || !p.skinny_counters) return Status::OK();
   const SkPlan pl = sk_plan(p, dev->sm_count());
-  if (p.split_scratch_bytes < (int64_t)pl.splits * SK_ROWS * p.n * 4) return Status::OK();
+  if (!pl.cluster && p.split_scratch_bytes < (int64_t)pl.splits * SK_ROWS * p.n * 4) return Status::OK();
   auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
   if (!al(p.a) || !al(p.b) || !al(p.c) || !al(p.bias) || !al(p.residual) || !al(p.split_scratch)) return Status::OK();
   B200_TRY(dev->MakeCurrent());
@@ -233,15 +290,18 @@ Status gemm_skinny(Device* dev, const GemmParams& p, bool* taken) {
   g.counters = reinterpret_cast<unsigned*>(p.skinny_counters);
   g.M = (int)p.m; g.N = (int)p.n; g.K = (int)p.k; g.kc = pl.kc; g.splits = pl.splits;
   g.act = p.activation; g.residual_mul = p.residual_op;
-  const size_t smem = (size_t)pl.kc * SK_BN * 2 + (size_t)SK_ROWS * (pl.kc + SK_X_PAD) * 2;
-  auto kern = p.dtype == B200_FLOAT16 ? gemm_skinny_kernel<__half> : gemm_skinny_kernel<__nv_bfloat16>;
+  g.w_static = p.b_static ? 1 : 0;
+  size_t smem = (size_t)pl.kc * SK_BN * 2 + (size_t)SK_ROWS * (pl.kc + SK_X_PAD) * 2;
+  if (smem < SK_ROWS * SK_BN * 4) smem = SK_ROWS * SK_BN * 4;   // the partial takes the tiles' place
+  auto kern = p.dtype == B200_FLOAT16 ? (pl.cluster ? gemm_skinny_kernel<__half, true> : gemm_skinny_kernel<__half, false>)
+                                      : (pl.cluster ? gemm_skinny_kernel<__nv_bfloat16, true> : gemm_skinny_kernel<__nv_bfloat16, false>);
   static std::mutex mu;
   static std::map<std::pair<int, const void*>, bool> configured;   // per device and kernel
   {
     std::lock_guard<std::mutex> lk(mu);
     bool& done = configured[{dev->ordinal(), (const void*)kern}];
     if (!done) {
-      B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_MAX_KC * SK_BN * 2 + SK_ROWS * (SK_MAX_KC + SK_X_PAD) * 2));
+      B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_CLUSTER_MAX_KC * SK_BN * 2 + SK_ROWS * (SK_CLUSTER_MAX_KC + SK_X_PAD) * 2));
       done = true;
     }
   }
@@ -251,11 +311,20 @@ Status gemm_skinny(Device* dev, const GemmParams& p, bool* taken) {
   cfg.blockDim = dim3(SK_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = dev->stream();
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (pl.cluster) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1; attr[na].val.clusterDim.y = (unsigned)pl.splits; attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  if (pdl_on) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_on ? 1 : 0;
+  cfg.numAttrs = na;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, g);
   if (e != cudaSuccess) {
     cudaGetLastError();

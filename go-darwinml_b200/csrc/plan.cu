@@ -1260,6 +1260,9 @@ class Planner {
     // allocates nothing and can be recorded
     // A 16-bit product of a handful of rows splits K over many CTAs: fp32 partial sums in the arena and a few counters
     // of the step's own (zeroed once; the kernel leaves them at zero).
+    // weights that are an input or a constant of this plan: nothing this plan launches writes them (an input that a
+    // DynamicUpdateSlice updates in place feeds nothing else)
+    gp.b_static = ex_->slots[b_slot].kind == SlotKind::Input || ex_->slots[b_slot].kind == SlotKind::Const;
     const int64_t skinny_bytes = k::gemm_skinny_scratch_bytes(gp, ex_->dev->sm_count());
     const int64_t split_bytes = x->dtype == B200_FLOAT32 ? k::gemm_split_scratch_bytes(B, M, N, K) : skinny_bytes;
     const int split_slot = split_bytes > 0 ? NewTemp(split_bytes) : -1;
