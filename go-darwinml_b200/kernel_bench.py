@@ -6,6 +6,8 @@
   python go-darwinml_b200/kernel_bench.py gemm --batch 8 --m 4096 --n 4096 --k 4096 --dtype bf16 [--a-km] [--b-nk] [--act gelu]
   python go-darwinml_b200/kernel_bench.py ewise --expr chain4 --rows 65536 --cols 2048 --dtype bf16   # 4 leaves, 6 ops: the run-time compiled path
   python go-darwinml_b200/kernel_bench.py reduce --expr sumsq --rows 16384 --cols 4096 --dtype bf16   # ReduceSum(x * x) over rows, one fused launch
+  python go-darwinml_b200/kernel_bench.py decode-attention --batch 64 --heads 12 --kv-heads 12 --seq 1024 --bhsd --dtype bf16   # one query over a KV cache
+  python go-darwinml_b200/kernel_bench.py few-rows --m 16 --n 3072 --k 768 --dtype bf16 --act gelu   # a decoding step's projection
   python go-darwinml_b200/kernel_bench.py copy --rows 16384 --cols 4096 --dtype bf16    # yardstick, not a kernel of this library
   python go-darwinml_b200/kernel_bench.py fill --rows 524288 --cols 1024 --dtype f32    # yardstick: write-only stream
 
@@ -36,7 +38,7 @@ DT = {"f32": (7, 4), "bf16": (6, 2), "f16": (5, 2)}
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["softmax", "rmsnorm", "layernorm", "gemm", "attention", "ewise", "reduce", "copy", "fill"])
+    ap.add_argument("kernel", choices=["softmax", "rmsnorm", "layernorm", "gemm", "attention", "decode-attention", "few-rows", "ewise", "reduce", "copy", "fill"])
     ap.add_argument("--rows", type=int, default=65536)
     ap.add_argument("--cols", type=int, default=1024)
     ap.add_argument("--seq-q", type=int, default=0)
@@ -192,6 +194,48 @@ def main():
         e = libmod.B200Error()
         bufs = [b200.Buffer(L.b200_buffer_wrap(args.device, t.data_ptr(), code, (ctypes.c_int64 * 2)(R, C), 2, ctypes.byref(e)))]
         work = (R * C + out_elems) * es
+        unit, kind = "GB/s", "hbm"
+        operand_bytes = work
+        print(exe.Describe().strip(), file=sys.stderr)
+
+        def launch():
+            for o in exe.Execute(bufs, None, args.device):
+                backend.BufferFinalize(o)
+    elif args.kernel in ("decode-attention", "few-rows"):
+        # the decoding step's two kernels, through the graph layer (one launch each)
+        npdt = {"bf16": __import__("ml_dtypes").bfloat16, "f16": np.float16}[args.dtype]
+        S = lambda *d: b200.Shape(b200.dtypes.from_numpy(np.dtype(npdt)), d)
+        builder = backend.Builder(args.kernel)
+        f = builder.Main()
+        if args.kernel == "decode-attention":
+            # one query position per (batch, head) over a cache of --seq keys under a position mask; bytes = K and V
+            B, H, Hkv, Sk = args.batch, args.heads, args.kv_heads, args.seq
+            shp = (lambda h, s: (B, h, s, 64)) if args.bhsd else (lambda h, s: (B, s, h, 64))
+            shapes = [shp(H, 1), shp(Hkv, Sk), shp(Hkv, Sk)]
+            ps = [f.Parameter(f"p{i}", S(*sh)) for i, sh in enumerate(shapes)]
+            mask = f.Parameter("mask", b200.Shape(b200.dtypes.Bool, (1, 1, 1, Sk)))
+            mask_t = (torch.arange(Sk, device=f"cuda:{args.device}") <= Sk - 2).reshape(1, 1, 1, Sk).contiguous()
+            y = f.FusedScaledDotProductAttention(ps[0], ps[1], ps[2], mask, H, Hkv, 0 if args.bhsd else 1, 0.125, False)
+            work = 2 * B * Hkv * Sk * 64 * es
+        else:
+            # X[m <= 16, k] W[k, n] (+ bias and --act): bytes = W
+            M, N, K = args.m, args.n, args.k
+            act = ["none", "gelu", "relu", "silu", "tanh"].index(args.act)
+            shapes = [(M, K), (K, N)] + ([(N,)] if act else [])
+            ps = [f.Parameter(f"p{i}", S(*sh)) for i, sh in enumerate(shapes)]
+            y = f.FusedDense(ps[0], ps[1], ps[2] if act else None, act)
+            work = K * N * es
+        f.Return([y], None)
+        exe = builder.Compile()
+        tens = [rand(*sh, scale=0.05 if args.kernel == "few-rows" else 1.0) for sh in shapes]
+        bufs = []
+        for t, sh in zip(tens, shapes):
+            e = libmod.B200Error()
+            bufs.append(b200.Buffer(L.b200_buffer_wrap(args.device, t.data_ptr(), code, (ctypes.c_int64 * len(sh))(*sh), len(sh), ctypes.byref(e))))
+        if args.kernel == "decode-attention":
+            e = libmod.B200Error()
+            bufs.append(b200.Buffer(L.b200_buffer_wrap(args.device, mask_t.data_ptr(), int(b200.dtypes.Bool), (ctypes.c_int64 * 4)(1, 1, 1, Sk), 4,
+                                                       ctypes.byref(e))))
         unit, kind = "GB/s", "hbm"
         operand_bytes = work
         print(exe.Describe().strip(), file=sys.stderr)

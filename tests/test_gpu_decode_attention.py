@@ -34,7 +34,7 @@ def _case(b200, backend, B, H, Hkv, Sk, layout, dtype, mask, seed=0, scale=0.125
 
 
 @pytest.mark.parametrize("layout", [0, 1], ids=["BHSD", "BSHD"])
-@pytest.mark.parametrize("H,Hkv", [(2, 2), (8, 2), (12, 1)])
+@pytest.mark.parametrize("H,Hkv", [(2, 2), (4, 2), (8, 2), (8, 1), (12, 1)])   # groups of 1, 2, 4, 8 (shared K / V loads) and 12
 @pytest.mark.parametrize("Sk", [1, 7, 64, 257, 1000, 1024, 5000])
 def test_one_query_without_a_mask(b200, backend, layout, H, Hkv, Sk):
     _case(b200, backend, 2, H, Hkv, Sk, layout, BF16, None, seed=Sk)
@@ -56,6 +56,17 @@ def test_one_query_with_a_mask_of_every_broadcast_shape(b200, backend, layout, m
     else:
         mask = (rng.standard_normal(size=dims) * 2).astype(BF16)
     _case(b200, backend, B, H, Hkv, Sk, layout, BF16, mask, seed=3)
+
+
+def test_grouped_heads_with_a_mask_per_head(b200, backend):
+    # the heads of a group share K and V but not the mask
+    rng = np.random.default_rng(21)
+    B, H, Hkv, Sk = 2, 8, 2, 700
+    mask = rng.integers(0, 3, size=(B, H, 1, Sk)) > 0
+    mask[..., 5] = True
+    _case(b200, backend, B, H, Hkv, Sk, 0, BF16, mask, seed=22)
+    add = (rng.standard_normal(size=(1, 1, H, Sk)) * 2).astype(BF16)   # BSHD: [B, 1, H, Sk]
+    _case(b200, backend, B, H, Hkv, Sk, 1, BF16, add, seed=23)
 
 
 def test_f16_tensors_and_an_f16_additive_mask(b200, backend):
