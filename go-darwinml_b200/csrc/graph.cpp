@@ -1067,7 +1067,7 @@ B200Value b200_scaled_dot_product_attention(B200Context ctx, B200Value query, B2
     // One query position (a decoding step) takes a mask tensor too: any mask that broadcasts to [B, H, 1, Sk].
     static const bool decode_on = []() { const char* e = getenv("B200MLX_DECODE_ATTENTION"); return !(e && e[0] == '0'); }();
     bool mask_ok = !m;
-    if (m && decode_on && fusable && q->dims[s_ax] == 1 && !causal && scale > 0 && (m->dtype == B200_BOOL || m->dtype == q->dtype) && m->rank() <= 4) {
+    if (m && decode_on && fusable && q->dims[s_ax] == 1 && !causal && scale > 0 && scale < 1e30 && (m->dtype == B200_BOOL || m->dtype == q->dtype) && m->rank() <= 4) {
       const int64_t full[4] = {q->dims[0], bshd && m->rank() == 4 ? 1 : (int64_t)num_heads, bshd && m->rank() == 4 ? (int64_t)num_heads : 1, k->dims[s_ax]};
       mask_ok = true;
       for (int i = 0; i < m->rank(); ++i) {
