@@ -254,7 +254,7 @@ struct GemmParams {
   int64_t a_batch_stride = -1, b_batch_stride = -1;  // -1 = dense (m*k, k*n)
   // fp32 on the tensor-core path: room for the three bf16 planes of both operands (gemm_split_scratch_bytes).  Without
   // it the launch allocates them itself, which keeps the step out of recorded plans.
-  // A 16-bit product of at most 16 rows (gemm_skinny): split_scratch holds the K slices' fp32 partial sums
+  // A 16-bit product of at most 64 rows (gemm_skinny): split_scratch holds the K slices' fp32 partial sums
   // (gemm_skinny_scratch_bytes) and skinny_counters one zeroed 32-bit counter per 64 columns (gemm_skinny_counter_bytes),
   // which the kernel leaves at zero.  Counters must not be shared by launches that may run at the same time.
   void* split_scratch = nullptr;

@@ -1,10 +1,11 @@
-// C[M, N] = act(X[M, K] W[K, N] + bias) (+ / * residual) for a handful of rows (M <= 16): a decoding step's projections.
+// C[M, N] = act(X[M, K] W[K, N] + bias) (+ / * residual) for a handful of rows (M <= 64): a decoding step's projections.
 //
 // Such a product is bound by reading W once (2 K N bytes); the 128 x 256 tensor-core tile gives it N / 256 CTAs, each
 // streaming its whole K through one SM's load path (28 us for K = 3072, N = 768).  Here about two CTAs per SM share W:
 // a CTA owns 64 columns and one slice of K, brings its whole W slice (at most 512 x 64) and X slice into shared memory
 // with one batch of 16-byte asynchronous copies -- so all of W is in flight at once --, multiplies with
-// mma.sync m16n8k16 (X as the 16-row operand, rows past M zero), and holds a 16 x 64 fp32 partial.  With K up to 8192
+// mma.sync m16n8k16 (X as one, two or four 16-row operands, rows past M zero), and holds an M x 64 fp32 partial.  With K up to 8192
+// (6144 past 32 rows)
 // a slab's slices are the (at most 8) CTAs of one cluster: the partials meet through distributed shared memory, added
 // in slice order (the same sum on every run), each CTA finishing a share of the outputs (bias, activation, residual).
 // A longer K goes through global memory: the CTA that arrives last on its slab's counter adds the partials, again in
@@ -27,7 +28,7 @@ namespace {
 
 constexpr int SK_THREADS = 128;
 constexpr int SK_BN = 64;
-constexpr int SK_ROWS = 16;
+constexpr int SK_MAX_ROWS = 64;
 constexpr int SK_MAX_KC = 512;
 constexpr int SK_MAX_SPLITS = 16;   // the last CTA adds the slices' partial sums: two rounds of eight loads at most (longer K: more, 512 per slice)
 constexpr int SK_X_PAD = 8;   // elements: the X rows' pitch is an odd number of 16-byte units, conflict-free for ldmatrix
@@ -76,9 +77,11 @@ template <> __device__ __forceinline__ __half sk_from_f(float v) { return __floa
 
 // CLUSTER: the slab's K slices are the CTAs of one cluster (at most 8); their partial sums stay in shared memory and
 // meet through distributed shared memory, each CTA finishing an equal share of the slab's outputs.  Otherwise (K too
-// long for 8 slices of 1024) the partial sums go through global memory and the slab's last CTA finishes them.
-template <typename T, bool CLUSTER>
+// long for 8 slices) the partial sums go through global memory and the slab's last CTA finishes them.
+// MT: 16-row tiles of X (1, 2 or 4: up to 16, 32 or 64 rows); W's fragments are loaded once per k-step for all of them.
+template <typename T, bool CLUSTER, int MT>
 __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g) {
+  constexpr int ROWS = 16 * MT;
   extern __shared__ __align__(128) unsigned char sk_smem[];
   __shared__ int s_last;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -103,7 +106,7 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
     if (g.w_static) pdl_wait();
     const T* X = reinterpret_cast<const T*>(g.x) + k0;
     const int xch = kc >> 3;
-    for (int idx = tid; idx < SK_ROWS * xch; idx += SK_THREADS) {
+    for (int idx = tid; idx < ROWS * xch; idx += SK_THREADS) {
       const int row = idx / xch, ch = idx - row * xch;
       if (row < g.M) sk_cp_async16(xsm_u + row * x_pitch + ch * 16, X + (int64_t)row * g.K + ch * 8);
       else *reinterpret_cast<uint4*>(xsm + row * x_pitch + ch * 16) = make_uint4(0, 0, 0, 0);
@@ -111,67 +114,103 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
     sk_cp_async_wait_all();
     __syncthreads();
   }
-  // warp w: columns [16 w, 16 w + 16) of the slab, all of the slice's k
-  float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+  // warp w: columns [16 w, 16 w + 16) of the slab, all rows, all of the slice's k
+  float acc[MT][2][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int t = 0; t < 2; ++t)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[mt][t][i] = 0.f;
   {
     const int mi = lane >> 3, r = lane & 7;
     const uint32_t a_addr = xsm_u + (lane & 15) * x_pitch + (lane >> 4) * 16;
     const int b_k = (mi & 1) * 8 + r;          // k within the 16-step; (k & 7) == r
     const int b_ch = warp * 2 + (mi >> 1);     // 16-byte unit within the 128-byte row
     const uint32_t b_addr = wsm_u + b_k * 128 + ((b_ch ^ r) << 4);
-#pragma unroll 4
+#pragma unroll 2
     for (int kk = 0; kk < kc; kk += 16) {
-      uint32_t a[4], bq[4];
-      sk_ldmatrix_x4(a_addr + kk * 2, a);
+      uint32_t bq[4];
       sk_ldmatrix_x4_trans(b_addr + kk * 128, bq);
-      sk_mma<T>(acc[0], a, bq[0], bq[1]);
-      sk_mma<T>(acc[1], a, bq[2], bq[3]);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        uint32_t a[4];
+        sk_ldmatrix_x4(a_addr + mt * 16 * x_pitch + kk * 2, a);
+        sk_mma<T>(acc[mt][0], a, bq[0], bq[1]);
+        sk_mma<T>(acc[mt][1], a, bq[2], bq[3]);
+      }
     }
   }
-  // the slice's partial: rows lane / 4 and lane / 4 + 8, columns 16 w + 8 t + 2 (lane % 4) + {0, 1}
+  // the slice's partial: rows 16 mt + lane / 4 (+ 8), columns 16 w + 8 t + 2 (lane % 4) + {0, 1}
   if constexpr (CLUSTER) {
     __syncthreads();   // everybody is done with the operand tiles: the partial takes their place
-    float* psm = reinterpret_cast<float*>(sk_smem);   // [16][64]
+    float* psm = reinterpret_cast<float*>(sk_smem);   // [ROWS][64]
     const int r0 = lane >> 2, c0 = warp * 16 + 2 * (lane & 3);
 #pragma unroll
-    for (int t = 0; t < 2; ++t) {
-      *reinterpret_cast<float2*>(psm + r0 * SK_BN + c0 + 8 * t) = make_float2(acc[t][0], acc[t][1]);
-      *reinterpret_cast<float2*>(psm + (r0 + 8) * SK_BN + c0 + 8 * t) = make_float2(acc[t][2], acc[t][3]);
-    }
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        *reinterpret_cast<float2*>(psm + (16 * mt + r0) * SK_BN + c0 + 8 * t) = make_float2(acc[mt][t][0], acc[mt][t][1]);
+        *reinterpret_cast<float2*>(psm + (16 * mt + r0 + 8) * SK_BN + c0 + 8 * t) = make_float2(acc[mt][t][2], acc[mt][t][3]);
+      }
     sm100::cluster_sync_all();
     const int csize = g.splits;
-    const int per = SK_ROWS * SK_BN / csize;   // outputs this CTA finishes (csize is 1, 2, 4 or 8)
+    const int per = ROWS * SK_BN / csize;   // outputs this CTA finishes (csize is 1, 2, 4 or 8), four per thread and step
     const uint32_t psm_u = sm100::smem_u32(psm);
-    for (int e = split * per + tid; e < (split + 1) * per; e += SK_THREADS) {
+    for (int e = split * per + 4 * tid; e < (split + 1) * per; e += 4 * SK_THREADS) {
       const int row = e >> 6, col = e & 63;
       if (row < g.M) {
-        float v = 0.f;
-        for (int c = 0; c < csize; ++c) {   // slice order: the same sum on every run
-          float pv;
-          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pv) : "r"(sm100::map_to_cta(psm_u + e * 4u, (uint32_t)c)) : "memory");
-          v += pv;
+        float4 pv[8];   // every slice's four values requested before any is used
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          pv[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (c < csize)
+            asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                         : "=f"(pv[c].x), "=f"(pv[c].y), "=f"(pv[c].z), "=f"(pv[c].w)
+                         : "r"(sm100::map_to_cta(psm_u + e * 4u, (uint32_t)c))
+                         : "memory");
         }
-        if (g.bias) v += sk_to_f<T>(reinterpret_cast<const T*>(g.bias)[n0 + col]);
-        float v1[2] = {v, 0.f};
-        apply_activation_n<2, true>(g.act, v1);
-        T o = sk_from_f<T>(v1[0]);
-        if (g.residual) {
-          const float a = sk_to_f<T>(o), r = sk_to_f<T>(reinterpret_cast<const T*>(g.residual)[(int64_t)row * g.N + n0 + col]);
-          o = sk_from_f<T>(g.residual_mul ? a * r : a + r);
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {   // slice order: the same sum on every run (absent slices add +0)
+          v[0] += pv[c].x; v[1] += pv[c].y; v[2] += pv[c].z; v[3] += pv[c].w;
         }
-        reinterpret_cast<T*>(g.c)[(int64_t)row * g.N + n0 + col] = o;
+        if (g.bias) {
+          const uint2 bq = *reinterpret_cast<const uint2*>(reinterpret_cast<const T*>(g.bias) + n0 + col);
+          const T* bt = reinterpret_cast<const T*>(&bq);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) v[j] += sk_to_f<T>(bt[j]);
+        }
+        apply_activation_n<4, true>(g.act, v);
+        uint2 out;
+        T* ot = reinterpret_cast<T*>(&out);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) ot[j] = sk_from_f<T>(v[j]);
+        if (g.residual) {   // the rounded value combined with the residual, rounded again
+          const uint2 rq = *reinterpret_cast<const uint2*>(reinterpret_cast<const T*>(g.residual) + (int64_t)row * g.N + n0 + col);
+          const T* rt = reinterpret_cast<const T*>(&rq);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float a = sk_to_f<T>(ot[j]), r = sk_to_f<T>(rt[j]);
+            ot[j] = sk_from_f<T>(g.residual_mul ? a * r : a + r);
+          }
+        }
+        *reinterpret_cast<uint2*>(reinterpret_cast<T*>(g.c) + (int64_t)row * g.N + n0 + col) = out;
       }
     }
     sm100::cluster_sync_all();   // nobody leaves while its partial may still be read
     return;
   }
   {
-    float* P = g.partial + (int64_t)split * SK_ROWS * g.N + n0 + warp * 16 + 2 * (lane & 3);
-    const int r0 = lane >> 2;
+    float* P = g.partial + (int64_t)split * ROWS * g.N + n0 + warp * 16 + 2 * (lane & 3);
 #pragma unroll
-    for (int t = 0; t < 2; ++t) {
-      if (r0 < g.M) __stcg(reinterpret_cast<float2*>(P + (int64_t)r0 * g.N + 8 * t), make_float2(acc[t][0], acc[t][1]));
-      if (r0 + 8 < g.M) __stcg(reinterpret_cast<float2*>(P + (int64_t)(r0 + 8) * g.N + 8 * t), make_float2(acc[t][2], acc[t][3]));
+    for (int mt = 0; mt < MT; ++mt) {
+      const int r0 = 16 * mt + (lane >> 2);
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        if (r0 < g.M) __stcg(reinterpret_cast<float2*>(P + (int64_t)r0 * g.N + 8 * t), make_float2(acc[mt][t][0], acc[mt][t][1]));
+        if (r0 + 8 < g.M) __stcg(reinterpret_cast<float2*>(P + (int64_t)(r0 + 8) * g.N + 8 * t), make_float2(acc[mt][t][2], acc[mt][t][3]));
+      }
     }
   }
   __threadfence();
@@ -185,62 +224,75 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  // the slab's last CTA: thread t owns row t / 8, columns [8 (t % 8), 8 (t % 8) + 8)
-  const int row = tid >> 3, col = n0 + (tid & 7) * 8;
-  if (row >= g.M) return;
-  float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  const float* P = g.partial + (int64_t)row * g.N + col;
-  const int64_t pstride = (int64_t)SK_ROWS * g.N;
-  int s = 0;
-  for (; s + 8 <= g.splits; s += 8) {   // eight slices' loads in flight (each round costs one trip to L2), added in slice order
-    float4 q[16];
+  // the slab's last CTA: thread t owns rows t / 8 + 16 mt, columns [8 (t % 8), 8 (t % 8) + 8)
+  const int64_t pstride = (int64_t)ROWS * g.N;
+  for (int mt = 0; mt < MT; ++mt) {
+    const int row = 16 * mt + (tid >> 3), col = n0 + (tid & 7) * 8;
+    if (row >= g.M) break;
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    const float* P = g.partial + (int64_t)row * g.N + col;
+    int s = 0;
+    for (; s + 8 <= g.splits; s += 8) {   // eight slices' loads in flight (each round costs one trip to L2), added in slice order
+      float4 q[16];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      q[2 * u] = __ldcg(reinterpret_cast<const float4*>(P + (s + u) * pstride));
-      q[2 * u + 1] = __ldcg(reinterpret_cast<const float4*>(P + (s + u) * pstride + 4));
+      for (int u = 0; u < 8; ++u) {
+        q[2 * u] = __ldcg(reinterpret_cast<const float4*>(P + (s + u) * pstride));
+        q[2 * u + 1] = __ldcg(reinterpret_cast<const float4*>(P + (s + u) * pstride + 4));
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        v[0] += q[2 * u].x; v[1] += q[2 * u].y; v[2] += q[2 * u].z; v[3] += q[2 * u].w;
+        v[4] += q[2 * u + 1].x; v[5] += q[2 * u + 1].y; v[6] += q[2 * u + 1].z; v[7] += q[2 * u + 1].w;
+      }
     }
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      v[0] += q[2 * u].x; v[1] += q[2 * u].y; v[2] += q[2 * u].z; v[3] += q[2 * u].w;
-      v[4] += q[2 * u + 1].x; v[5] += q[2 * u + 1].y; v[6] += q[2 * u + 1].z; v[7] += q[2 * u + 1].w;
+    for (; s < g.splits; ++s) {
+      const float4 q0 = __ldcg(reinterpret_cast<const float4*>(P + s * pstride)), q1 = __ldcg(reinterpret_cast<const float4*>(P + s * pstride + 4));
+      v[0] += q0.x; v[1] += q0.y; v[2] += q0.z; v[3] += q0.w;
+      v[4] += q1.x; v[5] += q1.y; v[6] += q1.z; v[7] += q1.w;
     }
-  }
-  for (; s < g.splits; ++s) {
-    const float4 q0 = __ldcg(reinterpret_cast<const float4*>(P + s * pstride)), q1 = __ldcg(reinterpret_cast<const float4*>(P + s * pstride + 4));
-    v[0] += q0.x; v[1] += q0.y; v[2] += q0.z; v[3] += q0.w;
-    v[4] += q1.x; v[5] += q1.y; v[6] += q1.z; v[7] += q1.w;
-  }
-  if (g.bias) {
-    const uint4 bq = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(g.bias) + col);
-    const T* bt = reinterpret_cast<const T*>(&bq);
+    if (g.bias) {
+      const uint4 bq = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(g.bias) + col);
+      const T* bt = reinterpret_cast<const T*>(&bq);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] += sk_to_f<T>(bt[j]);
-  }
-  apply_activation_n<8, true>(g.act, v);
-  uint4 out;
-  T* ot = reinterpret_cast<T*>(&out);
-#pragma unroll
-  for (int j = 0; j < 8; ++j) ot[j] = sk_from_f<T>(v[j]);
-  if (g.residual) {   // the rounded value combined with the residual, rounded again
-    const uint4 rq = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(g.residual) + (int64_t)row * g.N + col);
-    const T* rt = reinterpret_cast<const T*>(&rq);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float a = sk_to_f<T>(ot[j]), r = sk_to_f<T>(rt[j]);
-      ot[j] = sk_from_f<T>(g.residual_mul ? a * r : a + r);
+      for (int j = 0; j < 8; ++j) v[j] += sk_to_f<T>(bt[j]);
     }
+    apply_activation_n<8, true>(g.act, v);
+    uint4 out;
+    T* ot = reinterpret_cast<T*>(&out);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ot[j] = sk_from_f<T>(v[j]);
+    if (g.residual) {   // the rounded value combined with the residual, rounded again
+      const uint4 rq = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(g.residual) + (int64_t)row * g.N + col);
+      const T* rt = reinterpret_cast<const T*>(&rq);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float a = sk_to_f<T>(ot[j]), r = sk_to_f<T>(rt[j]);
+        ot[j] = sk_from_f<T>(g.residual_mul ? a * r : a + r);
+      }
+    }
+    *reinterpret_cast<uint4*>(reinterpret_cast<T*>(g.c) + (int64_t)row * g.N + col) = out;
   }
-  *reinterpret_cast<uint4*>(reinterpret_cast<T*>(g.c) + (int64_t)row * g.N + col) = out;
 }
 
-struct SkPlan { int splits, kc; bool cluster; };
-constexpr int SK_CLUSTER_MAX_KC = 1024;
+struct SkPlan { int splits, kc, mt; bool cluster; };
+constexpr int SK_SMEM_BUDGET = 200 * 1024;
+
+int sk_tiles(int64_t m) { return m <= 16 ? 1 : (m <= 32 ? 2 : 4); }
+size_t sk_smem_bytes(int kc, int mt) {
+  const size_t tiles = (size_t)kc * SK_BN * 2 + (size_t)16 * mt * (kc + SK_X_PAD) * 2, partial = (size_t)16 * mt * SK_BN * 4;
+  return tiles > partial ? tiles : partial;   // the partial takes the tiles' place
+}
+// the longest K slice (a multiple of 16, at most 1024) whose tiles fit the shared-memory budget
+int sk_max_kc(int mt) {
+  int kc = (SK_SMEM_BUDGET - 16 * mt * SK_X_PAD * 2) / (SK_BN * 2 + 16 * mt * 2) / 16 * 16;
+  return kc > 1024 ? 1024 : kc;
+}
 
 bool sk_shape_ok(const GemmParams& p) {
   static const bool on = []() { const char* v = getenv("B200MLX_GEMM_SKINNY"); return !(v && v[0] == '0'); }();
   if (!on) return false;
   if (p.dtype != B200_BFLOAT16 && p.dtype != B200_FLOAT16) return false;
-  if (p.batch != 1 || p.m < 1 || p.m > SK_ROWS || !p.a_k_major || p.b_k_major) return false;
+  if (p.batch != 1 || p.m < 1 || p.m > SK_MAX_ROWS || !p.a_k_major || p.b_k_major) return false;
   if (p.n % SK_BN != 0 || p.k % 16 != 0 || p.n < SK_BN || p.k < 16 || p.n > (1 << 20) || p.k > (1 << 20)) return false;
   if (p.ldc != 0 && p.ldc != p.n) return false;
   return p.num_c_extra == 0;
@@ -248,23 +300,31 @@ bool sk_shape_ok(const GemmParams& p) {
 
 SkPlan sk_plan(const GemmParams& p, int sm_count) {
   const int64_t slabs = p.n / SK_BN;
+  const int mt = sk_tiles(p.m);
+  const int64_t max_kc = sk_max_kc(mt);
   static const bool cluster_on = []() { const char* v = getenv("B200MLX_GEMM_SKINNY_CLUSTER"); return !(v && v[0] == '0'); }();
-  if (cluster_on && p.k <= 8 * SK_CLUSTER_MAX_KC) {
+  if (cluster_on && p.k <= 8 * max_kc) {
     // a power of two of slices, at most 8, about two CTAs per SM in all, at least 64 of K each (all of it when shorter)
     int64_t splits = 8;
     while (splits > 1 && (slabs * splits > 4 * (int64_t)sm_count || p.k / splits < 64)) splits /= 2;
-    while (((p.k + splits - 1) / splits + 15) / 16 * 16 > SK_CLUSTER_MAX_KC) splits *= 2;
+    while (((p.k + splits - 1) / splits + 15) / 16 * 16 > max_kc) splits *= 2;
     const int64_t kc = ((p.k + splits - 1) / splits + 15) / 16 * 16;
-    if ((splits - 1) * kc < p.k) return SkPlan{(int)splits, (int)kc, true};   // every slice has some of K
+    if ((splits - 1) * kc < p.k) return SkPlan{(int)splits, (int)kc, mt, true};   // every slice has some of K
   }
   int64_t splits = (2 * (int64_t)sm_count + slabs - 1) / slabs;
   if (splits < 1) splits = 1;
   if (splits > p.k / 16) splits = p.k / 16;
   if (splits > SK_MAX_SPLITS) splits = SK_MAX_SPLITS;
   int64_t kc = ((p.k + splits - 1) / splits + 15) / 16 * 16;
-  if (kc > SK_MAX_KC) kc = SK_MAX_KC;
+  const int64_t cap = max_kc < SK_MAX_KC ? max_kc : SK_MAX_KC;
+  if (kc > cap) kc = cap;
   splits = (p.k + kc - 1) / kc;
-  return SkPlan{(int)splits, (int)kc, false};
+  return SkPlan{(int)splits, (int)kc, mt, false};
+}
+
+template <typename T, bool CLUSTER>
+auto sk_kernel_for(int mt) -> void (*)(const SkArgs) {
+  return mt == 1 ? gemm_skinny_kernel<T, CLUSTER, 1> : (mt == 2 ? gemm_skinny_kernel<T, CLUSTER, 2> : gemm_skinny_kernel<T, CLUSTER, 4>);
 }
 
 }  // namespace
@@ -272,7 +332,7 @@ SkPlan sk_plan(const GemmParams& p, int sm_count) {
 int64_t gemm_skinny_scratch_bytes(const GemmParams& p, int sm_count) {
   if (!sk_shape_ok(p)) return 0;
   const SkPlan pl = sk_plan(p, sm_count);
-  return pl.cluster ? 16 : (int64_t)pl.splits * SK_ROWS * p.n * 4;   // (16: "taken", nothing goes through it)
+  return pl.cluster ? 16 : (int64_t)pl.splits * 16 * pl.mt * p.n * 4;   // (16: "taken", nothing goes through it)
 }
 int64_t gemm_skinny_counter_bytes(const GemmParams& p) { return sk_shape_ok(p) ? p.n / SK_BN * 4 : 0; }
 
@@ -280,7 +340,7 @@ Status gemm_skinny(Device* dev, const GemmParams& p, bool* taken) {
   *taken = false;
   if (!sk_shape_ok(p) || !p.split_scratch || !p.skinny_counters) return Status::OK();
   const SkPlan pl = sk_plan(p, dev->sm_count());
-  if (!pl.cluster && p.split_scratch_bytes < (int64_t)pl.splits * SK_ROWS * p.n * 4) return Status::OK();
+  if (!pl.cluster && p.split_scratch_bytes < (int64_t)pl.splits * 16 * pl.mt * p.n * 4) return Status::OK();
   auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
   if (!al(p.a) || !al(p.b) || !al(p.c) || !al(p.bias) || !al(p.residual) || !al(p.split_scratch)) return Status::OK();
   B200_TRY(dev->MakeCurrent());
@@ -291,17 +351,16 @@ Status gemm_skinny(Device* dev, const GemmParams& p, bool* taken) {
   g.M = (int)p.m; g.N = (int)p.n; g.K = (int)p.k; g.kc = pl.kc; g.splits = pl.splits;
   g.act = p.activation; g.residual_mul = p.residual_op;
   g.w_static = p.b_static ? 1 : 0;
-  size_t smem = (size_t)pl.kc * SK_BN * 2 + (size_t)SK_ROWS * (pl.kc + SK_X_PAD) * 2;
-  if (smem < SK_ROWS * SK_BN * 4) smem = SK_ROWS * SK_BN * 4;   // the partial takes the tiles' place
-  auto kern = p.dtype == B200_FLOAT16 ? (pl.cluster ? gemm_skinny_kernel<__half, true> : gemm_skinny_kernel<__half, false>)
-                                      : (pl.cluster ? gemm_skinny_kernel<__nv_bfloat16, true> : gemm_skinny_kernel<__nv_bfloat16, false>);
+  const size_t smem = sk_smem_bytes(pl.kc, pl.mt);
+  auto kern = p.dtype == B200_FLOAT16 ? (pl.cluster ? sk_kernel_for<__half, true>(pl.mt) : sk_kernel_for<__half, false>(pl.mt))
+                                      : (pl.cluster ? sk_kernel_for<__nv_bfloat16, true>(pl.mt) : sk_kernel_for<__nv_bfloat16, false>(pl.mt));
   static std::mutex mu;
   static std::map<std::pair<int, const void*>, bool> configured;   // per device and kernel
   {
     std::lock_guard<std::mutex> lk(mu);
     bool& done = configured[{dev->ordinal(), (const void*)kern}];
     if (!done) {
-      B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_CLUSTER_MAX_KC * SK_BN * 2 + SK_ROWS * (SK_CLUSTER_MAX_KC + SK_X_PAD) * 2));
+      B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM_BUDGET));
       done = true;
     }
   }

@@ -1,7 +1,7 @@
-"""16-bit matrix products with at most 16 rows (a decoding step's projections): the K-split kernel against the oracle.
+"""16-bit matrix products with at most 64 rows (a decoding step's projections): the K-split kernel against the oracle.
 
 K is cut into slices that different CTAs multiply; the slices' fp32 partial sums are added in slice order by the last
-CTA to arrive, which also applies bias, activation and residual.  Checked: every row count 1..16, K that does not
+CTA to arrive (or met through a cluster's shared memory), then bias, activation and residual are applied.  Checked: every row count 1..16 and the edges of the 32- and 64-row forms, K that does not
 divide evenly among the slices, one slice only, epilogue combinations, that the counters are left ready for the next
 run (the same executable run many times), and that two runs give identical bits.
 """
@@ -46,7 +46,7 @@ def _check(b200, backend, M, N, K, dtype, bias, act, residual, seed=0, lead=None
     return got
 
 
-@pytest.mark.parametrize("M", list(range(1, 17)))
+@pytest.mark.parametrize("M", list(range(1, 17)) + [17, 24, 32, 33, 47, 64])
 def test_every_row_count(b200, backend, M):
     _check(b200, backend, M, 768, 768, BF16, True, 0, False, seed=M)
 
@@ -62,6 +62,13 @@ def test_shapes(b200, backend, N, K):
 @pytest.mark.parametrize("residual", [False, True])
 def test_epilogues(b200, backend, bias, act, residual):
     _check(b200, backend, 7, 512, 1024, BF16, bias, act, residual, seed=17)
+
+
+@pytest.mark.parametrize("M", [32, 64])
+@pytest.mark.parametrize("N,K", [(768, 3072), (3072, 768), (4096, 6144), (4096, 6400), (1024, 11008), (64, 16)])
+def test_more_rows(b200, backend, M, N, K):
+    # 6144 is the longest K whose slices fit one cluster at 64 rows; 6400 and 11008 go through global memory
+    _check(b200, backend, M, N, K, BF16, True, 1, True, seed=M + N + K)
 
 
 def test_f16_and_leading_dims(b200, backend):
@@ -110,7 +117,7 @@ def test_two_products_in_one_plan_have_counters_of_their_own(b200, backend):
 
 def test_other_shapes_keep_their_kernels(b200, backend):
     rng = np.random.default_rng(10)
-    for M, N, K in [(17, 768, 768), (16, 100, 64), (16, 64, 24)]:
+    for M, N, K in [(65, 768, 768), (16, 100, 64), (16, 64, 24)]:
         x, w = rng_array(rng, (M, K), BF16), rng_array(rng, (K, N), BF16, 0.1)
         (got,), plan = run_backend(b200, backend, lambda f, a, b: f.FusedDense(a, b, None, 0), [x, w], describe=True)
         assert "few-rows" not in plan, plan
