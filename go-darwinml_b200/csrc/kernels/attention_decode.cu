@@ -8,12 +8,16 @@
 //
 // A cluster of up to 8 CTAs owns one (batch, head) and splits the keys.  A CTA walks its keys 256 at a time; eight
 // lanes share a key (16 bytes of its K row and of its V row each), so after a 3-step shuffle all eight hold the key's
-// score and P.V needs no exchange.  All of a chunk's K and V loads are issued first (64 KB in flight per CTA), and each
-// warp keeps an online softmax of its own keys, so nothing in the loop waits for another warp.  The warps', then the
+// score and P.V needs no exchange.  All of a chunk's K and V loads are issued first, as asynchronous copies into the
+// thread's own slots of shared memory (64 KB in flight per CTA at no register cost: three CTAs per SM), and each warp
+// keeps an online softmax of its own keys, so nothing in the loop waits for another warp.  The warps', then the
 // CTAs', (maximum, sum, partial output) meet at the end, the CTAs' through distributed shared memory; CTA 0 writes the row.
 // A row with every key masked yields NaN, as the general lowering does.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+
+#include <map>
+#include <mutex>
 
 #include "../kernels.h"
 #include "pdl.cuh"
@@ -28,6 +32,7 @@ constexpr int DEC_THREADS = 256;
 constexpr int DEC_CHUNK = 256;     // keys per pass
 constexpr int DEC_D = 64;
 constexpr int DEC_MAX_SPLITS = 8;
+constexpr int DEC_SMEM_BYTES = 2 * (DEC_CHUNK / 32) * DEC_THREADS * 16;   // the chunk in flight: K and V, 16 bytes per thread and key round
 constexpr int DEC_WARPS = DEC_THREADS / 32;
 
 struct DecArgs {
@@ -78,7 +83,8 @@ __device__ __forceinline__ void dec_unpack8(const uint4& r, float2 (&f)[4]) {
 
 // CONTIG: key rows of K and V are 64 elements apart (a BHSD cache), so every load's offset is an immediate.
 template <typename T, bool CONTIG>
-__global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(const DecArgs g) {
+__global__ void __launch_bounds__(DEC_THREADS, 3) attention_decode_kernel(const DecArgs g) {
+  extern __shared__ __align__(128) unsigned char dec_smem[];   // the chunk in flight: 2 x [8][256] x 16 bytes
   __shared__ float wm[DEC_WARPS], wl[DEC_WARPS];   // each warp's running maximum (log2 units) and sum
   __shared__ float wacc[DEC_WARPS][DEC_D];         // and unnormalised output
   __shared__ float part[DEC_D + 2];                // this CTA's result: output (unnormalised), maximum, sum
@@ -111,22 +117,26 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(const 
   constexpr int ITS = DEC_CHUNK / 32;
   for (int c0 = key_begin; c0 < key_end; c0 += DEC_CHUNK, Kt += DEC_CHUNK * kss, Vt += DEC_CHUNK * vss) {
     const bool full = c0 + DEC_CHUNK <= key_end;
-    uint4 kreg[ITS], vreg[ITS];
-    float s[ITS];
-    // every load of the chunk is issued up front (V does not depend on the scores)
-    if (full) {
-#pragma unroll
-      for (int it = 0; it < ITS; ++it) kreg[it] = __ldg(reinterpret_cast<const uint4*>(Kt + it * 32 * kss));
-#pragma unroll
-      for (int it = 0; it < ITS; ++it) vreg[it] = __ldg(reinterpret_cast<const uint4*>(Vt + it * 32 * vss));
-    } else {
+    // Every load of the chunk is issued up front (V does not depend on the scores), as asynchronous copies into the
+    // thread's own 16-byte slots of shared memory: the chunk in flight costs no registers, which is what lets three
+    // CTAs share an SM.  A thread reads back only what it copied itself, so its own wait is all the ordering needed.
+    uint4* kslot = reinterpret_cast<uint4*>(dec_smem) + threadIdx.x;   // [ITS][256] for K, then the same for V
+    uint4* vslot = kslot + ITS * DEC_THREADS;
+    {
+      const uint32_t ks = sm100::smem_u32(kslot), vs = sm100::smem_u32(vslot);
 #pragma unroll
       for (int it = 0; it < ITS; ++it) {
-        const bool in = c0 + it * 32 + key0 < key_end;
-        kreg[it] = in ? __ldg(reinterpret_cast<const uint4*>(Kt + it * 32 * kss)) : make_uint4(0, 0, 0, 0);
-        vreg[it] = in ? __ldg(reinterpret_cast<const uint4*>(Vt + it * 32 * vss)) : make_uint4(0, 0, 0, 0);
+        const bool in = full || c0 + it * 32 + key0 < key_end;
+        if (in) {
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ks + it * DEC_THREADS * 16), "l"(Kt + it * 32 * kss) : "memory");
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vs + it * DEC_THREADS * 16), "l"(Vt + it * 32 * vss) : "memory");
+        } else {
+          kslot[it * DEC_THREADS] = make_uint4(0, 0, 0, 0);
+          vslot[it * DEC_THREADS] = make_uint4(0, 0, 0, 0);
+        }
       }
     }
+    float s[ITS];
     // the keys' mask terms, in log2 units (the eight lanes of a key read the same element)
 #pragma unroll
     for (int it = 0; it < ITS; ++it) {
@@ -137,12 +147,13 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(const 
         else s[it] = dec_to_f<T>(reinterpret_cast<const T*>(g.mask)[mrow + (int64_t)key * g.m_k]) * 1.4426950408889634f;
       }
     }
+    asm volatile("cp.async.wait_all;" ::: "memory");
     // scores
     float cmax = -INFINITY;
 #pragma unroll
     for (int it = 0; it < ITS; ++it) {
       float2 kf[4];
-      dec_unpack8<T>(kreg[it], kf);
+      dec_unpack8<T>(kslot[it * DEC_THREADS], kf);
       float2 d2 = __fmul2_rn(kf[0], qf[0]);
 #pragma unroll
       for (int i = 1; i < 4; ++i) d2 = __ffma2_rn(kf[i], qf[i], d2);
@@ -168,7 +179,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(const 
       const float pk = dec_exp2(s[it] - m_safe);   // 0 for a masked key and past the end
       lsum += pk;
       float2 vf[4];
-      dec_unpack8<T>(vreg[it], vf);
+      dec_unpack8<T>(vslot[it * DEC_THREADS], vf);
       const float2 p2 = make_float2(pk, pk);
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[i] = __ffma2_rn(p2, vf[i], acc[i]);
@@ -267,9 +278,11 @@ Status attention_decode(Device* dev, const AttentionParams& p) {
   if ((g.q_sb | g.q_sh | g.k_sb | g.k_sh | g.k_ss | g.v_sb | g.v_sh) % 8 != 0 || g.v_ss % 8 != 0)
     return Status::Unsupported("attention_decode: operand strides must be multiples of 8 elements");
   g.scale_log2e = (float)(p.scale * 1.4426950408889634);
-  // CTAs per (batch, head): about four CTAs per SM in all (each keeps 64 KB of loads in flight), whole 256-key chunks, at most 8
+  // CTAs per (batch, head): as many as keep the whole grid resident at once (three CTAs of 64 KB per SM) -- a second
+  // wave of short CTAs costs more than longer CTAs do --, whole 256-key chunks, at most 8
   const int64_t bh = p.B * p.H;
-  int64_t splits = (4 * (int64_t)dev->sm_count() + bh - 1) / bh;
+  int64_t splits = 3 * (int64_t)dev->sm_count() / bh;
+  if (splits < 1) splits = 1;
   if (splits > DEC_MAX_SPLITS) splits = DEC_MAX_SPLITS;
   if (splits > (p.Sk + DEC_CHUNK - 1) / DEC_CHUNK) splits = (p.Sk + DEC_CHUNK - 1) / DEC_CHUNK;
   if (splits < 1) splits = 1;
@@ -280,6 +293,7 @@ Status attention_decode(Device* dev, const AttentionParams& p) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)bh, (unsigned)splits);
   cfg.blockDim = dim3(DEC_THREADS);
+  cfg.dynamicSmemBytes = DEC_SMEM_BYTES;
   cfg.stream = dev->stream();
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -289,12 +303,19 @@ Status attention_decode(Device* dev, const AttentionParams& p) {
   cfg.attrs = attr;
   cfg.numAttrs = pdl_on ? 2 : 1;
   const bool contig = g.k_ss == DEC_D && g.v_ss == DEC_D;
-  cudaError_t e;
-  if (p.dtype == B200_FLOAT16)
-    e = contig ? cudaLaunchKernelEx(&cfg, attention_decode_kernel<__half, true>, g) : cudaLaunchKernelEx(&cfg, attention_decode_kernel<__half, false>, g);
-  else
-    e = contig ? cudaLaunchKernelEx(&cfg, attention_decode_kernel<__nv_bfloat16, true>, g)
-               : cudaLaunchKernelEx(&cfg, attention_decode_kernel<__nv_bfloat16, false>, g);
+  void (*kern)(const DecArgs) = p.dtype == B200_FLOAT16 ? (contig ? attention_decode_kernel<__half, true> : attention_decode_kernel<__half, false>)
+                                                        : (contig ? attention_decode_kernel<__nv_bfloat16, true> : attention_decode_kernel<__nv_bfloat16, false>);
+  {
+    static std::mutex mu;
+    static std::map<std::pair<int, const void*>, bool> configured;   // the shared-memory opt-in is per device and kernel
+    std::lock_guard<std::mutex> lk(mu);
+    bool& done = configured[{dev->ordinal(), (const void*)kern}];
+    if (!done) {
+      B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM_BYTES));
+      done = true;
+    }
+  }
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, g);
   if (e != cudaSuccess) {
     cudaGetLastError();
     return Status::Cuda(strfmt("attention_decode: %s", cudaGetErrorString(e)));
