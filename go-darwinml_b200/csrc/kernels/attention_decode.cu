@@ -13,6 +13,7 @@
 // keeps an online softmax of its own keys, so nothing in the loop waits for another warp.  The warps', then the
 // CTAs', (maximum, sum, partial output) meet at the end, the CTAs' through distributed shared memory; CTA 0 writes the row.
 // A row with every key masked yields NaN, as the general lowering does.
+// When 2 to 16 query heads share a KV head, attention_decode_mma_kernel (below) takes the launch instead.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -244,6 +245,250 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) attention_decode_kernel(const 
   if (csize > 1) sm100::cluster_sync_all();   // nobody leaves while its result may still be read
 }
 
+// ---- the group's heads as the rows of a tensor-core product ----------------------------------------------------
+// One cluster per (batch, KV head); the group's query heads (up to 16) are the 16 rows of mma.sync m16n8k16 products:
+// S = Q K^T with K's rows as the column operand, O += P V with V through ldmatrix.trans and P taken from the score
+// accumulators in registers.  The FMA kernel above spends about 20 instructions per head and key, which binds grouped-
+// query attention on instruction issue rather than on the cache's bytes; here a warp's 32 keys cost 32 MMAs and a
+// two-row softmax whatever the group size.  A chunk of 256 keys (K and V, 64 KB) is brought into XOR-swizzled shared
+// memory by asynchronous copies; warp w owns keys [32 w, 32 w + 32) of it and an online softmax of its own.
+template <typename T> __device__ __forceinline__ uint32_t dec_pack2(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t dec_pack2<__nv_bfloat16>(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t dec_pack2<__half>(float lo, float hi) {
+  const __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+template <typename T> __device__ __forceinline__ void dec_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <> __device__ __forceinline__ void dec_mma<__nv_bfloat16>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <> __device__ __forceinline__ void dec_mma<__half>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void dec_ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void dec_ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+constexpr int DEC_GROUP_ROWS = 16;
+constexpr int DEC_MMA_SMEM_BYTES = 2 * DEC_CHUNK * DEC_D * 2;   // K and V of one chunk
+
+template <typename T>
+__global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_mma_kernel(const DecArgs g) {
+  extern __shared__ __align__(128) unsigned char dec_smem[];   // K chunk [256][128 B], V chunk [256][128 B]; 16-byte units XOR (row & 7)
+  __shared__ __align__(128) unsigned char qsm[DEC_GROUP_ROWS * DEC_D * 2];   // the group's queries (rows past the group zero), same swizzle
+  __shared__ float wm[DEC_WARPS][DEC_GROUP_ROWS], wl[DEC_WARPS][DEC_GROUP_ROWS];
+  __shared__ float part[DEC_GROUP_ROWS][DEC_D + 2];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int rank = blockIdx.y, csize = gridDim.y;
+  const int G = g.group;
+  const int hkv_count = g.H / G;
+  const int b = blockIdx.x / hkv_count, hkv = blockIdx.x - b * hkv_count;
+  const int h0 = hkv * G;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int key_begin = rank * g.keys_per_cta;
+  const int key_end = key_begin + g.keys_per_cta < g.Sk ? key_begin + g.keys_per_cta : g.Sk;
+  const T* Kb = reinterpret_cast<const T*>(g.k) + (int64_t)b * g.k_sb + (int64_t)hkv * g.k_sh;
+  const T* Vb = reinterpret_cast<const T*>(g.v) + (int64_t)b * g.v_sb + (int64_t)hkv * g.v_sh;
+  unsigned char* kbuf = dec_smem;
+  unsigned char* vbuf = dec_smem + DEC_CHUNK * DEC_D * 2;
+  const uint32_t kbuf_u = sm100::smem_u32(kbuf), vbuf_u = sm100::smem_u32(vbuf), qsm_u = sm100::smem_u32(qsm);
+  // the queries: 16 rows x 8 units of 16 bytes
+  if (tid < DEC_GROUP_ROWS * 8) {
+    const int row = tid >> 3, c = tid & 7;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < G) v = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(g.q) + (int64_t)b * g.q_sb + (int64_t)(h0 + row) * g.q_sh + c * 8);
+    *reinterpret_cast<uint4*>(qsm + row * 128 + ((c ^ (row & 7)) << 4)) = v;
+  }
+  __syncthreads();
+  uint32_t qa[4][4];   // Q as the row operand, four k-steps of 16 dims
+  {
+    const int mi = lane >> 3, row = (mi & 1) * 8 + (lane & 7);
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) dec_ldmatrix_x4(qsm_u + row * 128 + (((2 * kk + (mi >> 1)) ^ (row & 7)) << 4), qa[kk]);
+  }
+  // this thread's rows (heads) hr0 = lane / 4 and hr0 + 8; its columns within an 8-key tile 2 (lane % 4) + {0, 1}
+  const int hr0 = lane >> 2, hr1 = hr0 + 8, kc2 = 2 * (lane & 3);
+  const int64_t mrow0 = (int64_t)b * g.m_b + (int64_t)(h0 + hr0) * g.m_h, mrow1 = (int64_t)b * g.m_b + (int64_t)(h0 + hr1) * g.m_h;
+  const bool row0_real = hr0 < G, row1_real = hr1 < G;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  float o[8][4];
+#pragma unroll
+  for (int n = 0; n < 8; ++n)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
+  for (int c0 = key_begin; c0 < key_end; c0 += DEC_CHUNK) {
+    __syncthreads();   // everybody is done with the previous chunk
+#pragma unroll
+    for (int it = 0; it < DEC_CHUNK * 8 / DEC_THREADS; ++it) {
+      const int idx = it * DEC_THREADS + tid, key = idx >> 3, c = idx & 7;
+      const uint32_t off = key * 128 + ((c ^ (key & 7)) << 4);
+      if (c0 + key < key_end) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kbuf_u + off), "l"(Kb + (int64_t)(c0 + key) * g.k_ss + c * 8) : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vbuf_u + off), "l"(Vb + (int64_t)(c0 + key) * g.v_ss + c * 8) : "memory");
+      } else {
+        *reinterpret_cast<uint4*>(kbuf + off) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(vbuf + off) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    // the mask terms of this thread's 2 rows x 8 keys, in log2 units, requested while the copies fly
+    const int wkey = c0 + warp * 32;   // the warp's first key
+    float mk[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int key = wkey + 8 * j + kc2 + (i & 1);
+        const bool real = (i < 2 ? row0_real : row1_real);
+        float t = key < key_end ? 0.f : -INFINITY;
+        if (g.mask_kind != 0 && key < key_end && real) {
+          const int64_t at = (i < 2 ? mrow0 : mrow1) + (int64_t)key * g.m_k;
+          if (g.mask_kind == 1) t = reinterpret_cast<const uint8_t*>(g.mask)[at] ? 0.f : -INFINITY;
+          else t = dec_to_f<T>(reinterpret_cast<const T*>(g.mask)[at]) * 1.4426950408889634f;
+        }
+        mk[j][i] = t;
+      }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    __syncthreads();
+    if (wkey >= key_end) continue;   // nothing of this chunk is this warp's (warp-uniform; the barriers are above)
+    // S = Q K^T for the warp's 32 keys: four 8-key tiles x four k-steps
+    float sc[4][4];
+    {
+      const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sc[j][i] = 0.f;
+        const uint32_t rowaddr = kbuf_u + (warp * 32 + 8 * j + r) * 128;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t kb[4];
+          dec_ldmatrix_x4(rowaddr + (((4 * hh + mi) ^ r) << 4), kb);
+          dec_mma<T>(sc[j], qa[2 * hh], kb[0], kb[1]);
+          dec_mma<T>(sc[j], qa[2 * hh + 1], kb[2], kb[3]);
+        }
+      }
+    }
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sc[j][i] = fmaf(sc[j][i], g.scale_log2e, mk[j][i]);
+      mx0 = fmaxf(mx0, fmaxf(sc[j][0], sc[j][1]));
+      mx1 = fmaxf(mx1, fmaxf(sc[j][2], sc[j][3]));
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;   // every key so far masked: stay finite
+    const float al0 = dec_exp2(m0 - ms0), al1 = dec_exp2(m1 - ms1);
+    m0 = mn0;
+    m1 = mn1;
+    float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      sc[j][0] = dec_exp2(sc[j][0] - ms0);
+      sc[j][1] = dec_exp2(sc[j][1] - ms0);
+      sc[j][2] = dec_exp2(sc[j][2] - ms1);
+      sc[j][3] = dec_exp2(sc[j][3] - ms1);
+      ps0 += sc[j][0] + sc[j][1];
+      ps1 += sc[j][2] + sc[j][3];
+    }
+    l0 = fmaf(l0, al0, ps0);   // this thread's keys only; the quad meets at the end
+    l1 = fmaf(l1, al1, ps1);
+#pragma unroll
+    for (int n = 0; n < 8; ++n) { o[n][0] *= al0; o[n][1] *= al0; o[n][2] *= al1; o[n][3] *= al1; }
+    // O += P V: two k-steps of 16 keys; P from the score registers, V through ldmatrix.trans
+    {
+      const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        uint32_t pa[4];
+        pa[0] = dec_pack2<T>(sc[2 * t][0], sc[2 * t][1]);
+        pa[1] = dec_pack2<T>(sc[2 * t][2], sc[2 * t][3]);
+        pa[2] = dec_pack2<T>(sc[2 * t + 1][0], sc[2 * t + 1][1]);
+        pa[3] = dec_pack2<T>(sc[2 * t + 1][2], sc[2 * t + 1][3]);
+        const uint32_t rowaddr = vbuf_u + (warp * 32 + 16 * t + (mi & 1) * 8 + r) * 128;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          uint32_t vb[4];
+          dec_ldmatrix_x4_trans(rowaddr + (((2 * u + (mi >> 1)) ^ r) << 4), vb);
+          dec_mma<T>(o[2 * u], pa, vb[0], vb[1]);
+          dec_mma<T>(o[2 * u + 1], pa, vb[2], vb[3]);
+        }
+      }
+    }
+  }
+  // the quad's sums, then the warps' (maximum, sum, output) through shared memory (the outputs take the chunk's place)
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  __syncthreads();
+  float (*wo)[DEC_GROUP_ROWS][DEC_D] = reinterpret_cast<float (*)[DEC_GROUP_ROWS][DEC_D]>(dec_smem);   // [8][16][64] floats = 32 KB
+#pragma unroll
+  for (int n = 0; n < 8; ++n) {
+    *reinterpret_cast<float2*>(&wo[warp][hr0][8 * n + kc2]) = make_float2(o[n][0], o[n][1]);
+    *reinterpret_cast<float2*>(&wo[warp][hr1][8 * n + kc2]) = make_float2(o[n][2], o[n][3]);
+  }
+  if ((lane & 3) == 0) { wm[warp][hr0] = m0; wm[warp][hr1] = m1; wl[warp][hr0] = l0; wl[warp][hr1] = l1; }
+  __syncthreads();
+  for (int e = tid; e < G * DEC_D; e += DEC_THREADS) {
+    const int gi = e >> 6, d = e & 63;
+    float M = wm[0][gi];
+#pragma unroll
+    for (int w = 1; w < DEC_WARPS; ++w) M = fmaxf(M, wm[w][gi]);
+    const float Ms = M == -INFINITY ? 0.f : M;
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      const float wgt = dec_exp2(wm[w][gi] - Ms);
+      L = fmaf(wl[w][gi], wgt, L);
+      O = fmaf(wo[w][gi][d], wgt, O);
+    }
+    part[gi][d] = O;
+    if (d == 0) { part[gi][DEC_D] = M; part[gi][DEC_D + 1] = L; }
+  }
+  __syncthreads();
+  if (csize > 1) sm100::cluster_sync_all();
+  if (rank == 0) {
+    for (int e = tid; e < G * DEC_D; e += DEC_THREADS) {
+      const int gi = e >> 6, d = e & 63;
+      const uint32_t base = sm100::smem_u32(&part[gi][0]);
+      float M = -INFINITY;
+      for (int r = 0; r < csize; ++r) M = fmaxf(M, csize > 1 ? dec_ld_cluster(sm100::map_to_cta(base + DEC_D * 4u, (uint32_t)r)) : part[gi][DEC_D]);
+      const float Ms = M == -INFINITY ? 0.f : M;
+      float L = 0.f, O = 0.f;
+      for (int r = 0; r < csize; ++r) {
+        const uint32_t pb = csize > 1 ? sm100::map_to_cta(base, (uint32_t)r) : 0u;
+        const float mr = csize > 1 ? dec_ld_cluster(pb + DEC_D * 4u) : part[gi][DEC_D];
+        const float lr = csize > 1 ? dec_ld_cluster(pb + (DEC_D + 1) * 4u) : part[gi][DEC_D + 1];
+        const float orr = csize > 1 ? dec_ld_cluster(pb + d * 4u) : part[gi][d];
+        const float wgt = dec_exp2(mr - Ms);
+        L = fmaf(lr, wgt, L);
+        O = fmaf(orr, wgt, O);
+      }
+      T* Op = reinterpret_cast<T*>(g.o) + (int64_t)b * g.o_sb + (int64_t)(h0 + gi) * g.o_sh;
+      Op[d] = dec_from_f<T>(O / L);   // L = 0 (every key masked): NaN
+    }
+  }
+  if (csize > 1) sm100::cluster_sync_all();   // nobody leaves while its result may still be read
+}
+
 }  // namespace
 
 bool attention_decode_supported(const AttentionParams& p) {
@@ -278,10 +523,14 @@ Status attention_decode(Device* dev, const AttentionParams& p) {
   if ((g.q_sb | g.q_sh | g.k_sb | g.k_sh | g.k_ss | g.v_sb | g.v_sh) % 8 != 0 || g.v_ss % 8 != 0)
     return Status::Unsupported("attention_decode: operand strides must be multiples of 8 elements");
   g.scale_log2e = (float)(p.scale * 1.4426950408889634);
-  // CTAs per (batch, head): as many as keep the whole grid resident at once (three CTAs of 64 KB per SM) -- a second
-  // wave of short CTAs costs more than longer CTAs do --, whole 256-key chunks, at most 8
-  const int64_t bh = p.B * p.H;
-  int64_t splits = 3 * (int64_t)dev->sm_count() / bh;
+  // Which kernel: the group's heads as the rows of tensor-core products (one cluster per KV head) from B200MLX_DECODE_ATTENTION_MMA
+  // heads per group on (default 2; 1 = always, 0 = never), else one cluster per head on the FMA pipe.
+  static const int mma_from = []() { const char* v = getenv("B200MLX_DECODE_ATTENTION_MMA"); return v ? atoi(v) : 2; }();
+  const bool use_mma = mma_from > 0 && g.group >= mma_from && g.group <= DEC_GROUP_ROWS;
+  // CTAs per cluster: as many as keep the whole grid resident at once (three CTAs of 64 KB per SM; two of the tensor-
+  // core kernel) -- a second wave of short CTAs costs more than longer CTAs do --, whole 256-key chunks, at most 8
+  const int64_t bh = use_mma ? p.B * p.Hkv : p.B * p.H;
+  int64_t splits = (use_mma ? 2 : 3) * (int64_t)dev->sm_count() / bh;
   if (splits < 1) splits = 1;
   if (splits > DEC_MAX_SPLITS) splits = DEC_MAX_SPLITS;
   if (splits > (p.Sk + DEC_CHUNK - 1) / DEC_CHUNK) splits = (p.Sk + DEC_CHUNK - 1) / DEC_CHUNK;
@@ -293,7 +542,7 @@ Status attention_decode(Device* dev, const AttentionParams& p) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)bh, (unsigned)splits);
   cfg.blockDim = dim3(DEC_THREADS);
-  cfg.dynamicSmemBytes = DEC_SMEM_BYTES;
+  cfg.dynamicSmemBytes = use_mma ? DEC_MMA_SMEM_BYTES : DEC_SMEM_BYTES;
   cfg.stream = dev->stream();
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -305,13 +554,14 @@ Status attention_decode(Device* dev, const AttentionParams& p) {
   const bool contig = g.k_ss == DEC_D && g.v_ss == DEC_D;
   void (*kern)(const DecArgs) = p.dtype == B200_FLOAT16 ? (contig ? attention_decode_kernel<__half, true> : attention_decode_kernel<__half, false>)
                                                         : (contig ? attention_decode_kernel<__nv_bfloat16, true> : attention_decode_kernel<__nv_bfloat16, false>);
+  if (use_mma) kern = p.dtype == B200_FLOAT16 ? attention_decode_mma_kernel<__half> : attention_decode_mma_kernel<__nv_bfloat16>;
   {
     static std::mutex mu;
     static std::map<std::pair<int, const void*>, bool> configured;   // the shared-memory opt-in is per device and kernel
     std::lock_guard<std::mutex> lk(mu);
     bool& done = configured[{dev->ordinal(), (const void*)kern}];
     if (!done) {
-      B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM_BYTES));
+      B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, use_mma ? DEC_MMA_SMEM_BYTES : DEC_SMEM_BYTES));
       done = true;
     }
   }
