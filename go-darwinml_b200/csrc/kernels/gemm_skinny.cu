@@ -1,14 +1,14 @@
 // C[M, N] = act(X[M, K] W[K, N] + bias) (+ / * residual) for a handful of rows (M <= 64): a decoding step's projections.
 //
 // Such a product is bound by reading W once (2 K N bytes); the 128 x 256 tensor-core tile gives it N / 256 CTAs, each
-// streaming its whole K through one SM's load path (28 us for K = 3072, N = 768).  Here about two CTAs per SM share W:
-// a CTA owns 64 columns and one slice of K, brings its whole W slice (at most 512 x 64) and X slice into shared memory
-// with one batch of 16-byte asynchronous copies -- so all of W is in flight at once --, multiplies with
-// mma.sync m16n8k16 (X as one, two or four 16-row operands, rows past M zero), and holds an M x 64 fp32 partial.  With K up to 8192
-// (6144 past 32 rows)
-// a slab's slices are the (at most 8) CTAs of one cluster: the partials meet through distributed shared memory, added
-// in slice order (the same sum on every run), each CTA finishing a share of the outputs (bias, activation, residual).
-// A longer K goes through global memory: the CTA that arrives last on its slab's counter adds the partials, again in
+// streaming its whole K through one SM's load path (28 us for K = 3072, N = 768).  Here many CTAs share W: a CTA owns
+// 64 columns and one slice of K and streams the slice through a four-stage ring of 64-row chunks in shared memory
+// (16-byte asynchronous copies, always three chunks ahead of the arithmetic; a slice of up to 256 rows is simply in
+// flight at once), multiplies with mma.sync m16n8k16 (X as one, two or four 16-row operands, rows past M zero), and
+// holds an M x 64 fp32 partial.  A slab's (at most 8) slices are the CTAs of one cluster: the partials meet through
+// distributed shared memory, added in slice order (the same sum on every run), each CTA finishing a share of the
+// outputs (bias, activation, residual).  The other reduction (B200MLX_GEMM_SKINNY_CLUSTER=0: up to 16 slices, no
+// cluster) goes through global memory: the CTA that arrives last on its slab's counter adds the partials, again in
 // slice order, and writes C; it leaves the counter at zero for the next launch.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -29,8 +29,8 @@ namespace {
 constexpr int SK_THREADS = 128;
 constexpr int SK_BN = 64;
 constexpr int SK_MAX_ROWS = 64;
-constexpr int SK_MAX_KC = 512;
 constexpr int SK_MAX_SPLITS = 16;   // the last CTA adds the slices' partial sums: two rounds of eight loads at most (longer K: more, 512 per slice)
+constexpr int SK_STAGES = 4;
 constexpr int SK_X_PAD = 8;   // elements: the X rows' pitch is an odd number of 16-byte units, conflict-free for ldmatrix
 
 struct SkArgs {
@@ -41,7 +41,7 @@ struct SkArgs {
   const void* residual;
   float* partial;       // [splits, 16, N]
   unsigned* counters;   // [N / 64], zero between launches
-  int M, N, K, kc, splits, act, residual_mul;
+  int M, N, K, kc, kch, splits, act, residual_mul;   // kc: K per slice; kch: rows of K per ring stage
   int w_static;   // W may be fetched before the previous kernel on the stream has finished
 };
 
@@ -49,6 +49,8 @@ __device__ __forceinline__ void sk_cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void sk_cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void sk_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void sk_cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void sk_ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
@@ -88,31 +90,52 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
   const int slab = blockIdx.x, split = blockIdx.y;
   const int n0 = slab * SK_BN;
   const int k0 = split * g.kc;
-  const int kc = g.K - k0 < g.kc ? g.K - k0 : g.kc;   // a multiple of 16
-  const int x_pitch = (g.kc + SK_X_PAD) * 2;          // bytes
-  unsigned char* wsm = sk_smem;                       // [kc][64] elements, 16-byte units XOR-swizzled by (row & 7)
-  unsigned char* xsm = sk_smem + (size_t)g.kc * SK_BN * 2;
-  const uint32_t wsm_u = sm100::smem_u32(wsm), xsm_u = sm100::smem_u32(xsm);
-  pdl_launch_dependents();
-  if (!g.w_static) pdl_wait();
-  // one batch of copies: the W slice (kc rows of 128 bytes) and the X slice (M rows of kc elements; rows past M zero).
-  // Weights that nothing in flight can be writing are requested before the previous kernel's results are waited for.
-  {
-    const T* W = reinterpret_cast<const T*>(g.w) + (int64_t)k0 * g.N + n0;
-    for (int idx = tid; idx < kc * 8; idx += SK_THREADS) {
+  const int kc = g.K - k0 < g.kc ? g.K - k0 : g.kc;   // this slice's length, a multiple of 16
+  // The slice streams through a ring of SK_STAGES stages of g.kch rows of K: W rows [kch][64] with 16-byte units
+  // XOR-swizzled by (row & 7), then X [ROWS][kch + 8].  Chunk c + SK_STAGES is requested as soon as chunk c has been
+  // multiplied, so loads stay SK_STAGES - 1 chunks ahead of the arithmetic; a slice that fits the ring is in flight at once.
+  const int kch = g.kch;
+  const int x_pitch = (kch + SK_X_PAD) * 2;           // bytes
+  const int stage_bytes = kch * SK_BN * 2 + ROWS * x_pitch;
+  const uint32_t ring_u = sm100::smem_u32(sk_smem);
+  const int nch = (kc + kch - 1) / kch;
+  const T* Wg = reinterpret_cast<const T*>(g.w) + (int64_t)k0 * g.N + n0;
+  const T* Xg = reinterpret_cast<const T*>(g.x) + k0;
+  auto issue_w = [&](int c) {
+    if (c >= nch) return;
+    const int rows = kc - c * kch < kch ? kc - c * kch : kch;
+    const uint32_t wst = ring_u + (c % SK_STAGES) * stage_bytes;
+    const T* W = Wg + (int64_t)c * kch * g.N;
+    for (int idx = tid; idx < rows * 8; idx += SK_THREADS) {
       const int row = idx >> 3, ch = idx & 7;
-      sk_cp_async16(wsm_u + row * 128 + ((ch ^ (row & 7)) << 4), W + (int64_t)row * g.N + ch * 8);
+      sk_cp_async16(wst + row * 128 + ((ch ^ (row & 7)) << 4), W + (int64_t)row * g.N + ch * 8);
     }
-    if (g.w_static) pdl_wait();
-    const T* X = reinterpret_cast<const T*>(g.x) + k0;
-    const int xch = kc >> 3;
+  };
+  auto issue_x = [&](int c) {
+    if (c >= nch) return;
+    const int rows = kc - c * kch < kch ? kc - c * kch : kch;
+    unsigned char* xst = sk_smem + (c % SK_STAGES) * stage_bytes + kch * SK_BN * 2;
+    const uint32_t xst_u = sm100::smem_u32(xst);
+    const T* X = Xg + c * kch;
+    const int xch = rows >> 3;
     for (int idx = tid; idx < ROWS * xch; idx += SK_THREADS) {
       const int row = idx / xch, ch = idx - row * xch;
-      if (row < g.M) sk_cp_async16(xsm_u + row * x_pitch + ch * 16, X + (int64_t)row * g.K + ch * 8);
-      else *reinterpret_cast<uint4*>(xsm + row * x_pitch + ch * 16) = make_uint4(0, 0, 0, 0);
+      if (row < g.M) sk_cp_async16(xst_u + row * x_pitch + ch * 16, X + (int64_t)row * g.K + ch * 8);
+      else *reinterpret_cast<uint4*>(xst + row * x_pitch + ch * 16) = make_uint4(0, 0, 0, 0);
     }
-    sk_cp_async_wait_all();
-    __syncthreads();
+  };
+  pdl_launch_dependents();
+  // Weights that nothing in flight can be writing are requested before the previous kernel's results are waited for.
+  if (g.w_static) {
+#pragma unroll 1
+    for (int c = 0; c < SK_STAGES; ++c) issue_w(c);
+    pdl_wait();
+#pragma unroll 1
+    for (int c = 0; c < SK_STAGES; ++c) { issue_x(c); sk_cp_async_commit(); }   // (group 0 also holds every W chunk of the prologue)
+  } else {
+    pdl_wait();
+#pragma unroll 1
+    for (int c = 0; c < SK_STAGES; ++c) { issue_w(c); issue_x(c); sk_cp_async_commit(); }
   }
   // warp w: columns [16 w, 16 w + 16) of the slab, all rows, all of the slice's k
   float acc[MT][2][4];
@@ -124,22 +147,34 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
       for (int i = 0; i < 4; ++i) acc[mt][t][i] = 0.f;
   {
     const int mi = lane >> 3, r = lane & 7;
-    const uint32_t a_addr = xsm_u + (lane & 15) * x_pitch + (lane >> 4) * 16;
+    const uint32_t a_off = kch * SK_BN * 2 + (lane & 15) * x_pitch + (lane >> 4) * 16;
     const int b_k = (mi & 1) * 8 + r;          // k within the 16-step; (k & 7) == r
     const int b_ch = warp * 2 + (mi >> 1);     // 16-byte unit within the 128-byte row
-    const uint32_t b_addr = wsm_u + b_k * 128 + ((b_ch ^ r) << 4);
+    const uint32_t b_off = b_k * 128 + ((b_ch ^ r) << 4);
+#pragma unroll 1
+    for (int c = 0; c < nch; ++c) {
+      sk_cp_async_wait_group<SK_STAGES - 1>();   // chunk c has landed (one group per chunk, complete in order)
+      __syncthreads();
+      const uint32_t st = ring_u + (c % SK_STAGES) * stage_bytes;
+      const int rows = kc - c * kch < kch ? kc - c * kch : kch;
 #pragma unroll 2
-    for (int kk = 0; kk < kc; kk += 16) {
-      uint32_t bq[4];
-      sk_ldmatrix_x4_trans(b_addr + kk * 128, bq);
+      for (int kk = 0; kk < rows; kk += 16) {
+        uint32_t bq[4];
+        sk_ldmatrix_x4_trans(st + b_off + kk * 128, bq);
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-        uint32_t a[4];
-        sk_ldmatrix_x4(a_addr + mt * 16 * x_pitch + kk * 2, a);
-        sk_mma<T>(acc[mt][0], a, bq[0], bq[1]);
-        sk_mma<T>(acc[mt][1], a, bq[2], bq[3]);
+        for (int mt = 0; mt < MT; ++mt) {
+          uint32_t a[4];
+          sk_ldmatrix_x4(st + a_off + mt * 16 * x_pitch + kk * 2, a);
+          sk_mma<T>(acc[mt][0], a, bq[0], bq[1]);
+          sk_mma<T>(acc[mt][1], a, bq[2], bq[3]);
+        }
       }
+      __syncthreads();   // everybody is done with the stage: it takes chunk c + SK_STAGES
+      issue_w(c + SK_STAGES);
+      issue_x(c + SK_STAGES);
+      sk_cp_async_commit();
     }
+    sk_cp_async_wait_all();
   }
   // the slice's partial: rows 16 mt + lane / 4 (+ 8), columns 16 w + 8 t + 2 (lane % 4) + {0, 1}
   if constexpr (CLUSTER) {
@@ -274,18 +309,12 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
   }
 }
 
-struct SkPlan { int splits, kc, mt; bool cluster; };
-constexpr int SK_SMEM_BUDGET = 200 * 1024;
+struct SkPlan { int splits, kc, kch, mt; bool cluster; };
 
 int sk_tiles(int64_t m) { return m <= 16 ? 1 : (m <= 32 ? 2 : 4); }
-size_t sk_smem_bytes(int kc, int mt) {
-  const size_t tiles = (size_t)kc * SK_BN * 2 + (size_t)16 * mt * (kc + SK_X_PAD) * 2, partial = (size_t)16 * mt * SK_BN * 4;
-  return tiles > partial ? tiles : partial;   // the partial takes the tiles' place
-}
-// the longest K slice (a multiple of 16, at most 1024) whose tiles fit the shared-memory budget
-int sk_max_kc(int mt) {
-  int kc = (SK_SMEM_BUDGET - 16 * mt * SK_X_PAD * 2) / (SK_BN * 2 + 16 * mt * 2) / 16 * 16;
-  return kc > 1024 ? 1024 : kc;
+size_t sk_smem_bytes(int kch, int mt) {
+  const size_t ring = (size_t)SK_STAGES * ((size_t)kch * SK_BN * 2 + (size_t)16 * mt * (kch + SK_X_PAD) * 2), partial = (size_t)16 * mt * SK_BN * 4;
+  return ring > partial ? ring : partial;   // the partial takes the ring's place
 }
 
 bool sk_shape_ok(const GemmParams& p) {
@@ -301,25 +330,31 @@ bool sk_shape_ok(const GemmParams& p) {
 SkPlan sk_plan(const GemmParams& p, int sm_count) {
   const int64_t slabs = p.n / SK_BN;
   const int mt = sk_tiles(p.m);
-  const int64_t max_kc = sk_max_kc(mt);
   static const bool cluster_on = []() { const char* v = getenv("B200MLX_GEMM_SKINNY_CLUSTER"); return !(v && v[0] == '0'); }();
-  if (cluster_on && p.k <= 8 * max_kc) {
-    // a power of two of slices, at most 8, about two CTAs per SM in all, at least 64 of K each (all of it when shorter)
-    int64_t splits = 8;
-    while (splits > 1 && (slabs * splits > 4 * (int64_t)sm_count || p.k / splits < 64)) splits /= 2;
-    while (((p.k + splits - 1) / splits + 15) / 16 * 16 > max_kc) splits *= 2;
-    const int64_t kc = ((p.k + splits - 1) / splits + 15) / 16 * 16;
-    if ((splits - 1) * kc < p.k) return SkPlan{(int)splits, (int)kc, mt, true};   // every slice has some of K
+  int64_t splits, kc;
+  if (cluster_on) {
+    // a power of two of slices, at most 8 (one cluster), up to four CTAs per SM in all -- eight from 32 M weights on (measured:
+    // 4096 x 11008 takes 21.6 us so and 29.5 at four per SM, while 3072 x 768 takes 5.4 against 4.6) --, at least 64 of K
+    // each (all of it when shorter)
+    splits = 8;
+    const int64_t per_sm = p.k * p.n >= (32LL << 20) ? 8 : 4;
+    while (splits > 1 && (slabs * splits > per_sm * (int64_t)sm_count || p.k / splits < 64)) splits /= 2;
+    kc = ((p.k + splits - 1) / splits + 15) / 16 * 16;
+    while (splits > 1 && (splits - 1) * kc >= p.k) { splits /= 2; kc = ((p.k + splits - 1) / splits + 15) / 16 * 16; }   // every slice has some of K
+  } else {
+    splits = (2 * (int64_t)sm_count + slabs - 1) / slabs;
+    if (splits < 1) splits = 1;
+    if (splits > p.k / 16) splits = p.k / 16;
+    if (splits > SK_MAX_SPLITS) splits = SK_MAX_SPLITS;
+    kc = ((p.k + splits - 1) / splits + 15) / 16 * 16;
+    splits = (p.k + kc - 1) / kc;
   }
-  int64_t splits = (2 * (int64_t)sm_count + slabs - 1) / slabs;
-  if (splits < 1) splits = 1;
-  if (splits > p.k / 16) splits = p.k / 16;
-  if (splits > SK_MAX_SPLITS) splits = SK_MAX_SPLITS;
-  int64_t kc = ((p.k + splits - 1) / splits + 15) / 16 * 16;
-  const int64_t cap = max_kc < SK_MAX_KC ? max_kc : SK_MAX_KC;
-  if (kc > cap) kc = cap;
-  splits = (p.k + kc - 1) / kc;
-  return SkPlan{(int)splits, (int)kc, mt, false};
+  // rows of K per ring stage: 64 (a 10 KB stage at 16 rows of X: five CTAs per SM; 32 measured 30 - 70 % slower), 128 when
+  // the CTAs are fewer than two per SM (fewer, longer steps per CTA: 768 x 3072 takes 4.7 us so and 5.3 with 64); never
+  // more than the slice
+  int64_t kch = slabs * splits < 2 * (int64_t)sm_count ? 128 : 64;
+  if (kch > kc) kch = kc;
+  return SkPlan{(int)splits, (int)kc, (int)kch, mt, cluster_on};
 }
 
 template <typename T, bool CLUSTER>
@@ -348,10 +383,10 @@ Status gemm_skinny(Device* dev, const GemmParams& p, bool* taken) {
   g.x = p.a; g.w = p.b; g.c = p.c; g.bias = p.bias; g.residual = p.residual;
   g.partial = reinterpret_cast<float*>(p.split_scratch);
   g.counters = reinterpret_cast<unsigned*>(p.skinny_counters);
-  g.M = (int)p.m; g.N = (int)p.n; g.K = (int)p.k; g.kc = pl.kc; g.splits = pl.splits;
+  g.M = (int)p.m; g.N = (int)p.n; g.K = (int)p.k; g.kc = pl.kc; g.kch = pl.kch; g.splits = pl.splits;
   g.act = p.activation; g.residual_mul = p.residual_op;
   g.w_static = p.b_static ? 1 : 0;
-  const size_t smem = sk_smem_bytes(pl.kc, pl.mt);
+  const size_t smem = sk_smem_bytes(pl.kch, pl.mt);
   auto kern = p.dtype == B200_FLOAT16 ? (pl.cluster ? sk_kernel_for<__half, true>(pl.mt) : sk_kernel_for<__half, false>(pl.mt))
                                       : (pl.cluster ? sk_kernel_for<__nv_bfloat16, true>(pl.mt) : sk_kernel_for<__nv_bfloat16, false>(pl.mt));
   static std::mutex mu;
@@ -360,7 +395,7 @@ Status gemm_skinny(Device* dev, const GemmParams& p, bool* taken) {
     std::lock_guard<std::mutex> lk(mu);
     bool& done = configured[{dev->ordinal(), (const void*)kern}];
     if (!done) {
-      B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM_BUDGET));
+      B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sk_smem_bytes(128, 4)));
       done = true;
     }
   }
