@@ -619,6 +619,20 @@ def run_extras(b200, backend, L, libmod, torch, stream, local_rank, world, peaks
     out["llama_1b_fwd_bf16"] = model_tokens_per_s("llama", lc, W.llama_param_shapes(lc),
                                                  lambda f, *p: W.llama_forward(f, lc, int(b200.dtypes.BFloat16), *p),
                                                  W.llama_flops_per_token(lc), 20)
+    # Incremental decoding of the Llama-shaped model: batch 16 per GPU, 32 greedy steps in one executable, grouped-query
+    # attention (32 heads on 8 KV heads) over 2048-position caches, rotary embedding at the loop-carried position.
+    ld = W.LlamaConfig(batch=16)
+    n_new_l = 32
+    ldec = model_tokens_per_s("llama-decode", ld, W.llama_decode_param_shapes(ld),
+                              lambda f, *p: W.llama_greedy_decode(f, ld, int(b200.dtypes.BFloat16), n_new_l, *p), 0.0, 5)
+    weight_bytes = 2 * (sum(int(np.prod(sh)) for nm, sh in W.llama_param_shapes(ld) if nm not in ("ids", "embed", "rope_cos", "rope_sin")))
+    out["llama_1b_greedy_decode_bf16"] = {
+        "ms_per_call": ldec["ms_per_forward"], "new_tokens_per_sequence": n_new_l, "batch_this_gpu": ld.batch, "cache_positions": ld.seq,
+        "ms_per_step": ldec["ms_per_forward"] / n_new_l, "tokens_per_s_this_gpu": ld.batch * n_new_l / (ldec["ms_per_forward"] * 1e-3),
+        "launches_outside_the_loop": ldec["launches_per_forward"], "arena_GiB": ldec["arena_GiB"],
+        "weight_GB_read_per_step": weight_bytes / 1e9,
+        "weights_GB/s": weight_bytes / 1e9 / (ldec["ms_per_forward"] / n_new_l * 1e-3),
+        "note": "every step reads all the weights once (the step's floor at the copy rate) and attends over the whole cache under a position mask"}
     if world > 1:
         # The one optional exchange of the path: a weight split by columns over the ranks, the all-gather of the result
         # fused into the GEMM epilogue (peer stores over NVLink), checked bit for bit against the single-GPU GEMM and

@@ -2095,11 +2095,19 @@ class Planner {
     rp.head_dim = x->dims.back();
     Node* base = src;
     int64_t offset = 0, st3[3];
+    bool in_place_range = false;
     const int64_t vec = 16 / dtype_size(x->dtype);
     if (src->rank() == 4 && StridedProjectionView(src, true, &base, &offset, st3) && offset % vec == 0 && st3[2] % vec == 0) {
       rp.rows = src->dims[0] * src->dims[1];
       rp.cols = src->dims[2] * src->dims[3];
       rp.x_pitch = st3[2];
+    } else if (std::vector<int64_t> vs; ColumnRangeView(src, &base, &offset, &vs) && vs.back() == 1 && offset % vec == 0 &&
+               base->dims.back() % vec == 0 && (src->num_elements() / (base->num_elements() / base->dims.back())) % rp.head_dim == 0) {
+      // a column range of a wider tensor (the Q or K part of a decoding step's fused projection): its rows in place
+      rp.x_pitch = base->dims.back();
+      rp.rows = base->num_elements() / rp.x_pitch;
+      rp.cols = src->num_elements() / rp.rows;
+      in_place_range = true;
     } else {
       base = src;
       offset = 0;
@@ -2112,7 +2120,7 @@ class Planner {
     int c_slot, s_slot;
     // a per-head table needs x's rows to be (batch.., position) and its columns (head, head_dim): rank >= 3 with the
     // position on axis rank - 3
-    const bool rows_are_positions = src->rank() >= 3 && rp.cols == src->dims[src->rank() - 2] * src->dims[src->rank() - 1];
+    const bool rows_are_positions = !in_place_range && src->rank() >= 3 && rp.cols == src->dims[src->rank() - 2] * src->dims[src->rank() - 1];
     B200_TRY(PeriodicOperand(x->in[1], &c_slot, &rp.c_period, rows_are_positions ? rp.head_dim : 0, &rp.c_per_head));
     B200_TRY(PeriodicOperand(x->in[2], &s_slot, &rp.s_period, rows_are_positions ? rp.head_dim : 0, &rp.s_per_head));
     const int x_slot = SlotOf(base), out_slot = NewValueSlot(x);

@@ -308,6 +308,80 @@ def llama_forward(f, c: LlamaConfig, dtype_code, *params):
     return f.FusedDense(x, lm_head, None, ACT_NONE)
 
 
+def llama_decode_param_shapes(c: LlamaConfig):
+    """The forward's parameters with the token ids replaced by one start token per batch entry."""
+    return [("ids", (c.batch, 1, 1))] + llama_param_shapes(c)[1:]
+
+
+def llama_decode_step(g, c: LlamaConfig, dtype_code, weights, t, tok, out, caches):
+    """One decoding step at position t (int32 scalar) of the Llama-shaped model: RMSNorm, fused QKV projection, rotary
+    embedding of the one query and key at position t (the tables' row t, read with DynamicSlice), grouped-query attention
+    of the query over the caches (per layer a key and a value cache [B, Hkv, seq, D], extended at position t) under a
+    position mask, gated MLP.  `weights` = (embed, cos, sin, [7 tensors per layer], normf_g, lm_head).
+    Returns (next token [B,1,1], out with the greedy token at [:, t], logits [B,1,V], new caches)."""
+    embed, cos, sin, layers, normf_g, lm_head = weights
+    B, S, d, H, Hkv = c.batch, c.seq, c.d_model, c.heads, c.kv_heads
+    D = d // H
+    kv = Hkv * D
+    zero = _const_i32(g, 0)
+    x = g.Gather(embed, tok, 2, [2], [0], [0], [1, d], False)                          # [B, 1, d]
+    cos_t = g.DynamicSlice(cos, [t, zero], [1, D])                                     # [1, D]
+    sin_t = g.DynamicSlice(sin, [t, zero], [1, D])
+    table = lambda tb, hx: g.BroadcastInDim(tb, _Shape(dtype_code, (B, hx, 1, D)), [2, 3])
+    cos_q, sin_q, cos_k, sin_k = table(cos_t, H), table(sin_t, H), table(cos_t, Hkv), table(sin_t, Hkv)
+    visible = g.LessOrEqual(g.Iota(_Shape(C_I32, (1, 1, 1, S)), 3), g.BroadcastInDim(t, _Shape(C_I32, (1, 1, 1, S)), []))
+    new_caches = []
+    for li, (norm1_g, wqkv, wo, norm2_g, wgate, wup, wdown) in enumerate(layers):
+        h = g.FusedRMSNorm(x, [-1], c.eps, norm1_g)
+        q, k, v = g.FusedAttentionQKVProjection(h, wqkv, None, None, None, d, kv)
+        q = _rope(g, g.Reshape(q, B, H, 1, D), cos_q, sin_q, [B, H, 1, D], D // 2)
+        k = _rope(g, g.Reshape(k, B, Hkv, 1, D), cos_k, sin_k, [B, Hkv, 1, D], D // 2)
+        kc = g.DynamicUpdateSlice(caches[2 * li], k, [zero, zero, t, zero])
+        vc = g.DynamicUpdateSlice(caches[2 * li + 1], g.Reshape(v, B, Hkv, 1, D), [zero, zero, t, zero])
+        new_caches += [kc, vc]
+        a = g.FusedScaledDotProductAttention(q, kc, vc, visible, H, Hkv, LAYOUT_BHSD, 1.0 / math.sqrt(D), False)
+        x = g.Add(x, g.FusedDense(g.Reshape(a, B, 1, d), wo, None, ACT_NONE))
+        h = g.FusedRMSNorm(x, [-1], c.eps, norm2_g)
+        gate = g.FusedDense(h, wgate, None, ACT_SILU)
+        up = g.FusedDense(h, wup, None, ACT_NONE)
+        x = g.Add(x, g.FusedDense(g.Mul(gate, up), wdown, None, ACT_NONE))
+    x = g.FusedRMSNorm(x, [-1], c.eps, normf_g)
+    logits = g.FusedDense(x, lm_head, None, ACT_NONE)                                  # [B, 1, V]
+    nxt = g.ArgMinMax(logits, 2, C_I32, False)                                         # [B, 1]
+    out2 = g.DynamicUpdateSlice(out, nxt, [zero, t])
+    return g.Reshape(nxt, B, 1, 1), out2, logits, new_caches
+
+
+def llama_greedy_decode(f, c: LlamaConfig, dtype_code, n_tokens: int, *params):
+    """Greedy incremental decoding of the Llama-shaped model, n_tokens steps from one start token per batch entry, as ONE
+    While loop (see gpt2_greedy_decode).  Returns (tokens [B, n_tokens] int32, last step's logits [B, 1, V])."""
+    it = iter(params)
+    ids, embed, cos, sin = next(it), next(it), next(it), next(it)
+    layers = [tuple(next(it) for _ in range(7)) for _ in range(c.layers)]
+    normf_g, lm_head = next(it), next(it)
+    weights = (embed, cos, sin, layers, normf_g, lm_head)
+    B, S, d, H, Hkv, V = c.batch, c.seq, c.d_model, c.heads, c.kv_heads, c.vocab
+    D = d // H
+    s_i, s_tok, s_out = _Shape(C_I32, ()), _Shape(C_I32, (B, 1, 1)), _Shape(C_I32, (B, n_tokens))
+    s_cache, s_logits = _Shape(dtype_code, (B, Hkv, S, D)), _Shape(dtype_code, (B, 1, V))
+    state_shapes = [s_i, s_tok, s_out, s_logits] + [s_cache] * (2 * c.layers)
+
+    def body(g, t, tok, out, _logits, *caches):
+        nxt, out2, logits, new_caches = llama_decode_step(g, c, dtype_code, weights, t, tok, out, caches)
+        return [g.Add(t, _const_i32(g, 1)), nxt, out2, logits] + new_caches
+
+    cond = closure(f, state_shapes, lambda g, t, *rest: [g.LessThan(t, _const_i32(g, n_tokens))])
+    loop = closure(f, state_shapes, body)
+    float_np = {C_F32: np.float32}.get(dtype_code)
+    if float_np is None:
+        import ml_dtypes
+        float_np = ml_dtypes.bfloat16
+    zeros = lambda shape, np_dt: f.BroadcastInDim(f.Constant(np.zeros(1, dtype=np_dt)), shape, [])
+    init = [_const_i32(f, 0), ids, zeros(s_out, np.int32), zeros(s_logits, float_np)] + [zeros(s_cache, float_np) for _ in range(2 * c.layers)]
+    res = f.While(cond, loop, *init)
+    return res[2], res[3]
+
+
 def llama_flops_per_token(c: LlamaConfig) -> float:
     d, S = c.d_model, c.seq
     kv = c.kv_heads * (d // c.heads)

@@ -54,3 +54,79 @@ def test_greedy_decode_matches_the_oracle_token_for_token(b200, backend):
         assert ok, (run, viol)
     exe.Finalize()
     builder.Finalize()
+
+
+def _llama_decode_inputs(c, seed, dtype):
+    shapes = w.llama_decode_param_shapes(c)
+    arrays = w._init_params(shapes, seed, np.float32, c.vocab)
+    cos, sin = w.rope_tables(c)
+    scale = {"embed": 20.0, "wqkv": 30.0, "wo": 30.0, "wgate": 30.0, "wup": 30.0, "wdown": 30.0, "lm_head": 30.0}
+    for i, (name, _) in enumerate(shapes):
+        if name == "rope_cos":
+            arrays[i] = cos
+        elif name == "rope_sin":
+            arrays[i] = sin
+        k = scale.get(name.split(".")[-1])
+        if k:
+            arrays[i] = arrays[i] * k
+        if arrays[i].dtype != np.int32:
+            arrays[i] = arrays[i].astype(dtype)
+    return shapes, arrays
+
+
+def _compile_llama_decode(b200, backend, c, code, n_tokens, shapes, arrays):
+    builder = backend.Builder("llama_decode")
+    f = builder.Main()
+    params = [f.Parameter(name, b200.Shape(b200.dtypes.from_numpy(a.dtype), a.shape)) for (name, _), a in zip(shapes, arrays)]
+    tokens, logits = w.llama_greedy_decode(f, c, code, n_tokens, *params)
+    f.Return([tokens, logits], None)
+    return builder, builder.Compile()
+
+
+def test_llama_shaped_greedy_decode_matches_the_oracle_token_for_token(b200, backend):
+    # rotary embedding at a loop-carried position, grouped-query attention over the caches (4 heads on 2 KV heads),
+    # gated MLP; fp32, so tokens must agree exactly
+    c = w.LlamaConfig(layers=2, d_model=256, heads=4, kv_heads=2, d_ff=512, seq=24, vocab=211, batch=3)
+    n_tokens = 12
+    shapes, arrays = _llama_decode_inputs(c, 7, np.float32)
+    code = int(b200.dtypes.Float32)
+    builder, exe = _compile_llama_decode(b200, backend, c, code, n_tokens, shapes, arrays)
+    plan = exe.Describe()
+    assert "while[" in plan and "on the device when replayed" in plan, plan
+    want_tokens, want_logits = w.llama_greedy_decode(OracleFunction(), c, code, n_tokens, *arrays)
+    assert len(np.unique(np.asarray(want_tokens))) > 3
+    bufs = [backend.FromNumpy(a) for a in arrays]
+    for run in range(4):
+        outs = exe.Execute(bufs, None, 0)
+        got_tokens, got_logits = (backend.ToNumpy(o) for o in outs)
+        for o in outs:
+            backend.BufferFinalize(o)
+        np.testing.assert_array_equal(got_tokens, np.asarray(want_tokens))
+        ok, viol = compare(got_logits, np.asarray(want_logits), 1e-4, 1.0)
+        assert ok, (run, viol)
+    exe.Finalize()
+    builder.Finalize()
+
+
+def test_llama_shaped_decode_in_bf16_takes_the_decoding_kernels(b200, backend):
+    # the same model in bf16: the step runs on the one-query tensor-core attention and the few-rows products; its first
+    # step's logits agree with the oracle's bf16 evaluation to bf16 accuracy on the logits' scale
+    import ml_dtypes
+    bf16 = ml_dtypes.bfloat16
+    c = w.LlamaConfig(layers=2, d_model=256, heads=4, kv_heads=2, d_ff=512, seq=32, vocab=256, batch=3)
+    shapes, arrays = _llama_decode_inputs(c, 8, bf16)
+    code = int(b200.dtypes.BFloat16)
+    builder, exe = _compile_llama_decode(b200, backend, c, code, 1, shapes, arrays)
+    plan = exe.Describe()
+    assert "attention_decode[" in plan and "Hkv=2" in plan and plan.count("few-rows") >= 2 * 4 + 1, plan
+    _, want_logits = w.llama_greedy_decode(OracleFunction(), c, code, 1, *arrays)
+    bufs = [backend.FromNumpy(a) for a in arrays]
+    outs = exe.Execute(bufs, None, 0)
+    got_logits = backend.ToNumpy(outs[1]).astype(np.float32)
+    for o in outs:
+        backend.BufferFinalize(o)
+    want = np.asarray(want_logits).astype(np.float32)
+    assert np.isfinite(got_logits).all()
+    assert np.abs(got_logits - want).max() <= 0.04 * np.abs(want).max(), (np.abs(got_logits - want).max(), np.abs(want).max())
+    exe.Finalize()
+    builder.Finalize()
