@@ -250,8 +250,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) attention_decode_kernel(const 
 // S = Q K^T with K's rows as the column operand, O += P V with V through ldmatrix.trans and P taken from the score
 // accumulators in registers.  The FMA kernel above spends about 20 instructions per head and key, which binds grouped-
 // query attention on instruction issue rather than on the cache's bytes; here a warp's 32 keys cost 32 MMAs and a
-// two-row softmax whatever the group size.  A chunk of 256 keys (K and V, 64 KB) is brought into XOR-swizzled shared
-// memory by asynchronous copies; warp w owns keys [32 w, 32 w + 32) of it and an online softmax of its own.
+// two-row softmax whatever the group size.  Chunks of 128 keys (K and V, 32 KB) stream through a ring of three
+// XOR-swizzled buffers in shared memory, two chunks always in flight under the arithmetic; warp w owns keys
+// [16 w, 16 w + 16) of a chunk and an online softmax of its own.
 template <typename T> __device__ __forceinline__ uint32_t dec_pack2(float lo, float hi);
 template <> __device__ __forceinline__ uint32_t dec_pack2<__nv_bfloat16>(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -282,11 +283,14 @@ __device__ __forceinline__ void dec_ldmatrix_x4_trans(uint32_t addr, uint32_t (&
 }
 
 constexpr int DEC_GROUP_ROWS = 16;
-constexpr int DEC_MMA_SMEM_BYTES = 2 * DEC_CHUNK * DEC_D * 2;   // K and V of one chunk
+constexpr int DEC_MMA_CHUNK = 128;                                   // keys per ring buffer: 16 per warp
+constexpr int DEC_MMA_BUFS = 3;
+constexpr int DEC_MMA_BUF_BYTES = 2 * DEC_MMA_CHUNK * DEC_D * 2;      // K and V of one chunk
+constexpr int DEC_MMA_SMEM_BYTES = DEC_MMA_BUFS * DEC_MMA_BUF_BYTES;  // 96 KB: two CTAs per SM
 
 template <typename T>
 __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_mma_kernel(const DecArgs g) {
-  extern __shared__ __align__(128) unsigned char dec_smem[];   // K chunk [256][128 B], V chunk [256][128 B]; 16-byte units XOR (row & 7)
+  extern __shared__ __align__(128) unsigned char dec_smem[];   // three buffers of K [128][128 B] + V [128][128 B]; 16-byte units XOR (row & 7)
   __shared__ __align__(128) unsigned char qsm[DEC_GROUP_ROWS * DEC_D * 2];   // the group's queries (rows past the group zero), same swizzle
   __shared__ float wm[DEC_WARPS][DEC_GROUP_ROWS], wl[DEC_WARPS][DEC_GROUP_ROWS];
   __shared__ float part[DEC_GROUP_ROWS][DEC_D + 2];
@@ -302,9 +306,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_mma_kernel(co
   const int key_end = key_begin + g.keys_per_cta < g.Sk ? key_begin + g.keys_per_cta : g.Sk;
   const T* Kb = reinterpret_cast<const T*>(g.k) + (int64_t)b * g.k_sb + (int64_t)hkv * g.k_sh;
   const T* Vb = reinterpret_cast<const T*>(g.v) + (int64_t)b * g.v_sb + (int64_t)hkv * g.v_sh;
-  unsigned char* kbuf = dec_smem;
-  unsigned char* vbuf = dec_smem + DEC_CHUNK * DEC_D * 2;
-  const uint32_t kbuf_u = sm100::smem_u32(kbuf), vbuf_u = sm100::smem_u32(vbuf), qsm_u = sm100::smem_u32(qsm);
+  const uint32_t ring_u = sm100::smem_u32(dec_smem), qsm_u = sm100::smem_u32(qsm);
   // the queries: 16 rows x 8 units of 16 bytes
   if (tid < DEC_GROUP_ROWS * 8) {
     const int row = tid >> 3, c = tid & 7;
@@ -329,25 +331,39 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_mma_kernel(co
   for (int n = 0; n < 8; ++n)
 #pragma unroll
     for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
-  for (int c0 = key_begin; c0 < key_end; c0 += DEC_CHUNK) {
-    __syncthreads();   // everybody is done with the previous chunk
+  // A ring of three buffers of 128 keys (K 16 KB + V 16 KB each): chunk c + 2 is requested before chunk c is multiplied,
+  // so two chunks are always in flight under the arithmetic and one barrier per chunk is all the ordering needed (the
+  // buffer that takes chunk c + 2 held chunk c - 1, which every warp finished before this iteration's barrier).
+  const int nchunks = (key_end - key_begin + DEC_MMA_CHUNK - 1) / DEC_MMA_CHUNK;
+  auto issue = [&](int c) {
+    if (c < nchunks) {
+      const int c0 = key_begin + c * DEC_MMA_CHUNK;
+      const uint32_t kb_u = ring_u + (c % DEC_MMA_BUFS) * DEC_MMA_BUF_BYTES, vb_u = kb_u + DEC_MMA_CHUNK * DEC_D * 2;
 #pragma unroll
-    for (int it = 0; it < DEC_CHUNK * 8 / DEC_THREADS; ++it) {
-      const int idx = it * DEC_THREADS + tid, key = idx >> 3, c = idx & 7;
-      const uint32_t off = key * 128 + ((c ^ (key & 7)) << 4);
-      if (c0 + key < key_end) {
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kbuf_u + off), "l"(Kb + (int64_t)(c0 + key) * g.k_ss + c * 8) : "memory");
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vbuf_u + off), "l"(Vb + (int64_t)(c0 + key) * g.v_ss + c * 8) : "memory");
-      } else {
-        *reinterpret_cast<uint4*>(kbuf + off) = make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4*>(vbuf + off) = make_uint4(0, 0, 0, 0);
+      for (int it = 0; it < DEC_MMA_CHUNK * 8 / DEC_THREADS; ++it) {
+        const int idx = it * DEC_THREADS + tid, key = idx >> 3, ch = idx & 7;
+        const uint32_t off = key * 128 + ((ch ^ (key & 7)) << 4);
+        if (c0 + key < key_end) {
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kb_u + off), "l"(Kb + (int64_t)(c0 + key) * g.k_ss + ch * 8) : "memory");
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vb_u + off), "l"(Vb + (int64_t)(c0 + key) * g.v_ss + ch * 8) : "memory");
+        } else {
+          const uint32_t z = 0;
+          asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(kb_u + off), "r"(z) : "memory");
+          asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(vb_u + off), "r"(z) : "memory");
+        }
       }
     }
-    // the mask terms of this thread's 2 rows x 8 keys, in log2 units, requested while the copies fly
-    const int wkey = c0 + warp * 32;   // the warp's first key
-    float mk[4][4];
+    asm volatile("cp.async.commit_group;" ::: "memory");   // one group per chunk index, empty past the end
+  };
+  issue(0);
+  issue(1);
+  for (int c = 0; c < nchunks; ++c) {
+    const int c0 = key_begin + c * DEC_MMA_CHUNK;
+    // the mask terms of this thread's 2 rows x 4 keys, in log2 units, requested before the wait
+    const int wkey = c0 + warp * 16;   // the warp's first key
+    float mk[2][4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+    for (int j = 0; j < 2; ++j)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int key = wkey + 8 * j + kc2 + (i & 1);
@@ -360,18 +376,20 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_mma_kernel(co
         }
         mk[j][i] = t;
       }
-    asm volatile("cp.async.wait_all;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");   // chunk c has landed (groups complete in order)
     __syncthreads();
-    if (wkey >= key_end) continue;   // nothing of this chunk is this warp's (warp-uniform; the barriers are above)
-    // S = Q K^T for the warp's 32 keys: four 8-key tiles x four k-steps
-    float sc[4][4];
+    issue(c + 2);
+    if (wkey >= key_end) continue;   // nothing of this chunk is this warp's (warp-uniform; the barrier is above)
+    const uint32_t kbuf_u = ring_u + (c % DEC_MMA_BUFS) * DEC_MMA_BUF_BYTES, vbuf_u = kbuf_u + DEC_MMA_CHUNK * DEC_D * 2;
+    // S = Q K^T for the warp's 16 keys: two 8-key tiles x four k-steps
+    float sc[2][4];
     {
       const int mi = lane >> 3, r = lane & 7;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < 2; ++j) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) sc[j][i] = 0.f;
-        const uint32_t rowaddr = kbuf_u + (warp * 32 + 8 * j + r) * 128;
+        const uint32_t rowaddr = kbuf_u + (warp * 16 + 8 * j + r) * 128;
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
           uint32_t kb[4];
@@ -383,7 +401,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_mma_kernel(co
     }
     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < 2; ++j) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) sc[j][i] = fmaf(sc[j][i], g.scale_log2e, mk[j][i]);
       mx0 = fmaxf(mx0, fmaxf(sc[j][0], sc[j][1]));
@@ -400,7 +418,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_mma_kernel(co
     m1 = mn1;
     float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < 2; ++j) {
       sc[j][0] = dec_exp2(sc[j][0] - ms0);
       sc[j][1] = dec_exp2(sc[j][1] - ms0);
       sc[j][2] = dec_exp2(sc[j][2] - ms1);
@@ -412,27 +430,25 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_mma_kernel(co
     l1 = fmaf(l1, al1, ps1);
 #pragma unroll
     for (int n = 0; n < 8; ++n) { o[n][0] *= al0; o[n][1] *= al0; o[n][2] *= al1; o[n][3] *= al1; }
-    // O += P V: two k-steps of 16 keys; P from the score registers, V through ldmatrix.trans
+    // O += P V: one k-step of 16 keys; P from the score registers, V through ldmatrix.trans
     {
       const int mi = lane >> 3, r = lane & 7;
+      uint32_t pa[4];
+      pa[0] = dec_pack2<T>(sc[0][0], sc[0][1]);
+      pa[1] = dec_pack2<T>(sc[0][2], sc[0][3]);
+      pa[2] = dec_pack2<T>(sc[1][0], sc[1][1]);
+      pa[3] = dec_pack2<T>(sc[1][2], sc[1][3]);
+      const uint32_t rowaddr = vbuf_u + (warp * 16 + (mi & 1) * 8 + r) * 128;
 #pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        uint32_t pa[4];
-        pa[0] = dec_pack2<T>(sc[2 * t][0], sc[2 * t][1]);
-        pa[1] = dec_pack2<T>(sc[2 * t][2], sc[2 * t][3]);
-        pa[2] = dec_pack2<T>(sc[2 * t + 1][0], sc[2 * t + 1][1]);
-        pa[3] = dec_pack2<T>(sc[2 * t + 1][2], sc[2 * t + 1][3]);
-        const uint32_t rowaddr = vbuf_u + (warp * 32 + 16 * t + (mi & 1) * 8 + r) * 128;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          uint32_t vb[4];
-          dec_ldmatrix_x4_trans(rowaddr + (((2 * u + (mi >> 1)) ^ r) << 4), vb);
-          dec_mma<T>(o[2 * u], pa, vb[0], vb[1]);
-          dec_mma<T>(o[2 * u + 1], pa, vb[2], vb[3]);
-        }
+      for (int u = 0; u < 4; ++u) {
+        uint32_t vb[4];
+        dec_ldmatrix_x4_trans(rowaddr + (((2 * u + (mi >> 1)) ^ r) << 4), vb);
+        dec_mma<T>(o[2 * u], pa, vb[0], vb[1]);
+        dec_mma<T>(o[2 * u + 1], pa, vb[2], vb[3]);
       }
     }
   }
+  asm volatile("cp.async.wait_all;" ::: "memory");
   // the quad's sums, then the warps' (maximum, sum, output) through shared memory (the outputs take the chunk's place)
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
