@@ -30,7 +30,7 @@ constexpr int SK_THREADS = 128;
 constexpr int SK_BN = 64;
 constexpr int SK_MAX_ROWS = 64;
 constexpr int SK_MAX_SPLITS = 16;   // the last CTA adds the slices' partial sums: two rounds of eight loads at most (longer K: more, 512 per slice)
-constexpr int SK_STAGES = 4;
+constexpr int SK_STAGES = 4;   // at most; three when that lets the whole grid be resident at once
 constexpr int SK_X_PAD = 8;   // elements: the X rows' pitch is an odd number of 16-byte units, conflict-free for ldmatrix
 
 struct SkArgs {
@@ -41,7 +41,7 @@ struct SkArgs {
   const void* residual;
   float* partial;       // [splits, 16, N]
   unsigned* counters;   // [N / 64], zero between launches
-  int M, N, K, kc, kch, splits, act, residual_mul;   // kc: K per slice; kch: rows of K per ring stage
+  int M, N, K, kc, kch, stages, splits, act, residual_mul;   // kc: K per slice; kch: rows of K per ring stage; stages: 3 or 4
   int w_static;   // W may be fetched before the previous kernel on the stream has finished
 };
 
@@ -81,7 +81,10 @@ template <> __device__ __forceinline__ __half sk_from_f(float v) { return __floa
 // meet through distributed shared memory, each CTA finishing an equal share of the slab's outputs.  Otherwise (K too
 // long for 8 slices) the partial sums go through global memory and the slab's last CTA finishes them.
 // MT: 16-row tiles of X (1, 2 or 4: up to 16, 32 or 64 rows); W's fragments are loaded once per k-step for all of them.
-template <typename T, bool CLUSTER, int MT>
+// NK: W is stored [N, K] (an LM head tied to the embedding table): a stage holds [64 columns][kch] instead of [kch][64], its
+// fragments come from ldmatrix without .trans, and N need not be a multiple of 64 (columns past N are zero in shared
+// memory and never stored).
+template <typename T, bool CLUSTER, int MT, bool NK, int S>
 __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g) {
   constexpr int ROWS = 16 * MT;
   extern __shared__ __align__(128) unsigned char sk_smem[];
@@ -96,25 +99,39 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
   // multiplied, so loads stay SK_STAGES - 1 chunks ahead of the arithmetic; a slice that fits the ring is in flight at once.
   const int kch = g.kch;
   const int x_pitch = (kch + SK_X_PAD) * 2;           // bytes
-  const int stage_bytes = kch * SK_BN * 2 + ROWS * x_pitch;
+  const int w_bytes = (NK ? (kch + 63) / 64 * 64 : kch) * SK_BN * 2;   // a stage's W part (NK: whole 128-byte groups per column, it swizzles within them)
+  const int stage_bytes = w_bytes + ROWS * x_pitch;
   const uint32_t ring_u = sm100::smem_u32(sk_smem);
   const int nch = (kc + kch - 1) / kch;
-  const T* Wg = reinterpret_cast<const T*>(g.w) + (int64_t)k0 * g.N + n0;
+  const T* Wg = NK ? reinterpret_cast<const T*>(g.w) + (int64_t)n0 * g.K + k0 : reinterpret_cast<const T*>(g.w) + (int64_t)k0 * g.N + n0;
   const T* Xg = reinterpret_cast<const T*>(g.x) + k0;
+  const int w_pitch = (kch + 63) / 64 * 128;   // NK: bytes per column's row of a stage, whole 128-byte groups
   auto issue_w = [&](int c) {
     if (c >= nch) return;
     const int rows = kc - c * kch < kch ? kc - c * kch : kch;
-    const uint32_t wst = ring_u + (c % SK_STAGES) * stage_bytes;
-    const T* W = Wg + (int64_t)c * kch * g.N;
-    for (int idx = tid; idx < rows * 8; idx += SK_THREADS) {
-      const int row = idx >> 3, ch = idx & 7;
-      sk_cp_async16(wst + row * 128 + ((ch ^ (row & 7)) << 4), W + (int64_t)row * g.N + ch * 8);
+    const uint32_t wst = ring_u + (c % S) * stage_bytes;
+    if constexpr (NK) {
+      // 64 columns x (rows / 8) units of 16 bytes; the unit's low 3 bits XOR (column & 7)
+      const int upr = rows >> 3;
+      const T* W = Wg + c * kch;
+      for (int idx = tid; idx < SK_BN * upr; idx += SK_THREADS) {
+        const int n = idx / upr, u = idx - n * upr;
+        const uint32_t dst = wst + n * w_pitch + (((u & ~7) | ((u ^ n) & 7)) << 4);
+        if (n0 + n < g.N) sk_cp_async16(dst, W + (int64_t)n * g.K + u * 8);
+        else asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0u) : "memory");
+      }
+    } else {
+      const T* W = Wg + (int64_t)c * kch * g.N;
+      for (int idx = tid; idx < rows * 8; idx += SK_THREADS) {
+        const int row = idx >> 3, ch = idx & 7;
+        sk_cp_async16(wst + row * 128 + ((ch ^ (row & 7)) << 4), W + (int64_t)row * g.N + ch * 8);
+      }
     }
   };
   auto issue_x = [&](int c) {
     if (c >= nch) return;
     const int rows = kc - c * kch < kch ? kc - c * kch : kch;
-    unsigned char* xst = sk_smem + (c % SK_STAGES) * stage_bytes + kch * SK_BN * 2;
+    unsigned char* xst = sk_smem + (c % S) * stage_bytes + w_bytes;
     const uint32_t xst_u = sm100::smem_u32(xst);
     const T* X = Xg + c * kch;
     const int xch = rows >> 3;
@@ -128,14 +145,14 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
   // Weights that nothing in flight can be writing are requested before the previous kernel's results are waited for.
   if (g.w_static) {
 #pragma unroll 1
-    for (int c = 0; c < SK_STAGES; ++c) issue_w(c);
+    for (int c = 0; c < S; ++c) issue_w(c);
     pdl_wait();
 #pragma unroll 1
-    for (int c = 0; c < SK_STAGES; ++c) { issue_x(c); sk_cp_async_commit(); }   // (group 0 also holds every W chunk of the prologue)
+    for (int c = 0; c < S; ++c) { issue_x(c); sk_cp_async_commit(); }   // (group 0 also holds every W chunk of the prologue)
   } else {
     pdl_wait();
 #pragma unroll 1
-    for (int c = 0; c < SK_STAGES; ++c) { issue_w(c); issue_x(c); sk_cp_async_commit(); }
+    for (int c = 0; c < S; ++c) { issue_w(c); issue_x(c); sk_cp_async_commit(); }
   }
   // warp w: columns [16 w, 16 w + 16) of the slab, all rows, all of the slice's k
   float acc[MT][2][4];
@@ -147,20 +164,27 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
       for (int i = 0; i < 4; ++i) acc[mt][t][i] = 0.f;
   {
     const int mi = lane >> 3, r = lane & 7;
-    const uint32_t a_off = kch * SK_BN * 2 + (lane & 15) * x_pitch + (lane >> 4) * 16;
+    const uint32_t a_off = w_bytes + (lane & 15) * x_pitch + (lane >> 4) * 16;
     const int b_k = (mi & 1) * 8 + r;          // k within the 16-step; (k & 7) == r
     const int b_ch = warp * 2 + (mi >> 1);     // 16-byte unit within the 128-byte row
     const uint32_t b_off = b_k * 128 + ((b_ch ^ r) << 4);
+    // NK: matrix mi covers column tile mi / 2 and k half mi % 2; lane r of it reads column 16 w + 8 (mi / 2) + r
+    const uint32_t nk_row = (warp * 16 + (mi >> 1) * 8 + r) * w_pitch;
 #pragma unroll 1
     for (int c = 0; c < nch; ++c) {
-      sk_cp_async_wait_group<SK_STAGES - 1>();   // chunk c has landed (one group per chunk, complete in order)
+      sk_cp_async_wait_group<S - 1>();   // chunk c has landed (one group per chunk, complete in order)
       __syncthreads();
-      const uint32_t st = ring_u + (c % SK_STAGES) * stage_bytes;
+      const uint32_t st = ring_u + (c % S) * stage_bytes;
       const int rows = kc - c * kch < kch ? kc - c * kch : kch;
 #pragma unroll 2
       for (int kk = 0; kk < rows; kk += 16) {
         uint32_t bq[4];
-        sk_ldmatrix_x4_trans(st + b_off + kk * 128, bq);
+        if constexpr (NK) {
+          const int u = (kk >> 3) + (mi & 1);   // the 16-byte unit of this k half within the column's row
+          sk_ldmatrix_x4(st + nk_row + (((u & ~7) | ((u ^ r) & 7)) << 4), bq);
+        } else {
+          sk_ldmatrix_x4_trans(st + b_off + kk * 128, bq);
+        }
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
           uint32_t a[4];
@@ -170,8 +194,8 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
         }
       }
       __syncthreads();   // everybody is done with the stage: it takes chunk c + SK_STAGES
-      issue_w(c + SK_STAGES);
-      issue_x(c + SK_STAGES);
+      issue_w(c + S);
+      issue_x(c + S);
       sk_cp_async_commit();
     }
     sk_cp_async_wait_all();
@@ -194,7 +218,7 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
     const uint32_t psm_u = sm100::smem_u32(psm);
     for (int e = split * per + 4 * tid; e < (split + 1) * per; e += 4 * SK_THREADS) {
       const int row = e >> 6, col = e & 63;
-      if (row < g.M) {
+      if (row < g.M && (!NK || n0 + col < g.N)) {
         float4 pv[8];   // every slice's four values requested before any is used
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
@@ -210,9 +234,18 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
         for (int c = 0; c < 8; ++c) {   // slice order: the same sum on every run (absent slices add +0)
           v[0] += pv[c].x; v[1] += pv[c].y; v[2] += pv[c].z; v[3] += pv[c].w;
         }
+        const bool whole = !NK || (g.N & 3) == 0;   // rows of C (bias, residual) are 8-byte aligned at every fourth column (always so for W as [K, N])
+        const int64_t at = (int64_t)row * g.N + n0 + col;
+        const int valid = g.N - (n0 + col) < 4 ? g.N - (n0 + col) : 4;
         if (g.bias) {
-          const uint2 bq = *reinterpret_cast<const uint2*>(reinterpret_cast<const T*>(g.bias) + n0 + col);
-          const T* bt = reinterpret_cast<const T*>(&bq);
+          uint2 bq = make_uint2(0, 0);
+          T* bt = reinterpret_cast<T*>(&bq);
+          if (whole) bq = *reinterpret_cast<const uint2*>(reinterpret_cast<const T*>(g.bias) + n0 + col);
+          else if constexpr (NK) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (j < valid) bt[j] = reinterpret_cast<const T*>(g.bias)[n0 + col + j];
+          }
 #pragma unroll
           for (int j = 0; j < 4; ++j) v[j] += sk_to_f<T>(bt[j]);
         }
@@ -222,15 +255,26 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
 #pragma unroll
         for (int j = 0; j < 4; ++j) ot[j] = sk_from_f<T>(v[j]);
         if (g.residual) {   // the rounded value combined with the residual, rounded again
-          const uint2 rq = *reinterpret_cast<const uint2*>(reinterpret_cast<const T*>(g.residual) + (int64_t)row * g.N + n0 + col);
-          const T* rt = reinterpret_cast<const T*>(&rq);
+          uint2 rq = make_uint2(0, 0);
+          T* rt = reinterpret_cast<T*>(&rq);
+          if (whole) rq = *reinterpret_cast<const uint2*>(reinterpret_cast<const T*>(g.residual) + at);
+          else if constexpr (NK) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (j < valid) rt[j] = reinterpret_cast<const T*>(g.residual)[at + j];
+          }
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const float a = sk_to_f<T>(ot[j]), r = sk_to_f<T>(rt[j]);
             ot[j] = sk_from_f<T>(g.residual_mul ? a * r : a + r);
           }
         }
-        *reinterpret_cast<uint2*>(reinterpret_cast<T*>(g.c) + (int64_t)row * g.N + n0 + col) = out;
+        if (whole) *reinterpret_cast<uint2*>(reinterpret_cast<T*>(g.c) + at) = out;
+        else if constexpr (NK) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (j < valid) reinterpret_cast<T*>(g.c)[at + j] = ot[j];
+        }
       }
     }
     sm100::cluster_sync_all();   // nobody leaves while its partial may still be read
@@ -309,28 +353,37 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
   }
 }
 
-struct SkPlan { int splits, kc, kch, mt; bool cluster; };
+struct SkPlan { int splits, kc, kch, stages, mt; bool cluster; };
 
 int sk_tiles(int64_t m) { return m <= 16 ? 1 : (m <= 32 ? 2 : 4); }
-size_t sk_smem_bytes(int kch, int mt) {
-  const size_t ring = (size_t)SK_STAGES * ((size_t)kch * SK_BN * 2 + (size_t)16 * mt * (kch + SK_X_PAD) * 2), partial = (size_t)16 * mt * SK_BN * 4;
+size_t sk_smem_bytes(int kch, int mt, int stages, bool nk) {
+  const size_t ring = (size_t)stages * ((size_t)(nk ? (kch + 63) / 64 * 64 : kch) * SK_BN * 2 + (size_t)16 * mt * (kch + SK_X_PAD) * 2), partial = (size_t)16 * mt * SK_BN * 4;
   return ring > partial ? ring : partial;   // the partial takes the ring's place
+}
+
+bool sk_cluster_on() {
+  static const bool on = []() { const char* v = getenv("B200MLX_GEMM_SKINNY_CLUSTER"); return !(v && v[0] == '0'); }();
+  return on;
 }
 
 bool sk_shape_ok(const GemmParams& p) {
   static const bool on = []() { const char* v = getenv("B200MLX_GEMM_SKINNY"); return !(v && v[0] == '0'); }();
   if (!on) return false;
   if (p.dtype != B200_BFLOAT16 && p.dtype != B200_FLOAT16) return false;
-  if (p.batch != 1 || p.m < 1 || p.m > SK_MAX_ROWS || !p.a_k_major || p.b_k_major) return false;
-  if (p.n % SK_BN != 0 || p.k % 16 != 0 || p.n < SK_BN || p.k < 16 || p.n > (1 << 20) || p.k > (1 << 20)) return false;
+  if (p.batch != 1 || p.m < 1 || p.m > SK_MAX_ROWS || !p.a_k_major) return false;
+  // W as [K, N]: whole 64-column slabs; as [N, K]: any N, through the cluster reduction only (its epilogue handles a ragged N)
+  // (and only up to 32768 columns: beyond that the 128 x 256 tensor-core tile has a CTA for every SM and measured faster --
+  // GPT-2's 50257 x 768 LM head 34 us there, 47 us here, where a column's K is visited 128 bytes at a time)
+  if (p.b_k_major ? (!sk_cluster_on() || p.n > 32768) : p.n % SK_BN != 0) return false;
+  if (p.k % 16 != 0 || p.n < SK_BN || p.k < 16 || p.n > (1 << 20) || p.k > (1 << 20)) return false;
   if (p.ldc != 0 && p.ldc != p.n) return false;
   return p.num_c_extra == 0;
 }
 
 SkPlan sk_plan(const GemmParams& p, int sm_count) {
-  const int64_t slabs = p.n / SK_BN;
+  const int64_t slabs = (p.n + SK_BN - 1) / SK_BN;
   const int mt = sk_tiles(p.m);
-  static const bool cluster_on = []() { const char* v = getenv("B200MLX_GEMM_SKINNY_CLUSTER"); return !(v && v[0] == '0'); }();
+  const bool cluster_on = sk_cluster_on();
   int64_t splits, kc;
   if (cluster_on) {
     // a power of two of slices, at most 8 (one cluster), up to four CTAs per SM in all -- eight from 32 M weights on (measured:
@@ -354,12 +407,26 @@ SkPlan sk_plan(const GemmParams& p, int sm_count) {
   // more than the slice
   int64_t kch = slabs * splits < 2 * (int64_t)sm_count ? 128 : 64;
   if (kch > kc) kch = kc;
-  return SkPlan{(int)splits, (int)kc, (int)kch, mt, cluster_on};
+  // Four stages, or three when the grid fits the SMs at once with three and not with four (a second, nearly empty wave
+  // costs a whole CTA's time: 786 slabs of a 50257-column LM head against 740 places)
+  auto places = [&](int stages) { return (int64_t)sm_count * (int64_t)((227 * 1024) / (sk_smem_bytes((int)kch, mt, stages, p.b_k_major) + 1024)); };
+  const int64_t ctas = slabs * splits;
+  const int stages = (p.b_k_major && ctas > places(SK_STAGES) && ctas <= places(3)) ? 3 : SK_STAGES;
+  return SkPlan{(int)splits, (int)kc, (int)kch, stages, mt, cluster_on};
 }
 
+template <typename T, bool CLUSTER, bool NK, int S>
+auto sk_kernel_for2(int mt) -> void (*)(const SkArgs) {
+  return mt == 1 ? gemm_skinny_kernel<T, CLUSTER, 1, NK, S> : (mt == 2 ? gemm_skinny_kernel<T, CLUSTER, 2, NK, S> : gemm_skinny_kernel<T, CLUSTER, 4, NK, S>);
+}
 template <typename T, bool CLUSTER>
-auto sk_kernel_for(int mt) -> void (*)(const SkArgs) {
-  return mt == 1 ? gemm_skinny_kernel<T, CLUSTER, 1> : (mt == 2 ? gemm_skinny_kernel<T, CLUSTER, 2> : gemm_skinny_kernel<T, CLUSTER, 4>);
+auto sk_kernel_for(int mt, bool nk, int stages) -> void (*)(const SkArgs) {
+  if constexpr (CLUSTER) {
+    if (nk) return stages == 3 ? sk_kernel_for2<T, true, true, 3>(mt) : sk_kernel_for2<T, true, true, SK_STAGES>(mt);   // three stages: W as [N, K] only
+    return sk_kernel_for2<T, true, false, SK_STAGES>(mt);
+  } else {
+    return sk_kernel_for2<T, false, false, SK_STAGES>(mt);   // W as [N, K] always takes the cluster reduction
+  }
 }
 
 }  // namespace
@@ -369,7 +436,7 @@ int64_t gemm_skinny_scratch_bytes(const GemmParams& p, int sm_count) {
   const SkPlan pl = sk_plan(p, sm_count);
   return pl.cluster ? 16 : (int64_t)pl.splits * 16 * pl.mt * p.n * 4;   // (16: "taken", nothing goes through it)
 }
-int64_t gemm_skinny_counter_bytes(const GemmParams& p) { return sk_shape_ok(p) ? p.n / SK_BN * 4 : 0; }
+int64_t gemm_skinny_counter_bytes(const GemmParams& p) { return sk_shape_ok(p) ? (p.n + SK_BN - 1) / SK_BN * 4 : 0; }
 
 Status gemm_skinny(Device* dev, const GemmParams& p, bool* taken) {
   *taken = false;
@@ -383,25 +450,25 @@ Status gemm_skinny(Device* dev, const GemmParams& p, bool* taken) {
   g.x = p.a; g.w = p.b; g.c = p.c; g.bias = p.bias; g.residual = p.residual;
   g.partial = reinterpret_cast<float*>(p.split_scratch);
   g.counters = reinterpret_cast<unsigned*>(p.skinny_counters);
-  g.M = (int)p.m; g.N = (int)p.n; g.K = (int)p.k; g.kc = pl.kc; g.kch = pl.kch; g.splits = pl.splits;
+  g.M = (int)p.m; g.N = (int)p.n; g.K = (int)p.k; g.kc = pl.kc; g.kch = pl.kch; g.stages = pl.stages; g.splits = pl.splits;
   g.act = p.activation; g.residual_mul = p.residual_op;
   g.w_static = p.b_static ? 1 : 0;
-  const size_t smem = sk_smem_bytes(pl.kch, pl.mt);
-  auto kern = p.dtype == B200_FLOAT16 ? (pl.cluster ? sk_kernel_for<__half, true>(pl.mt) : sk_kernel_for<__half, false>(pl.mt))
-                                      : (pl.cluster ? sk_kernel_for<__nv_bfloat16, true>(pl.mt) : sk_kernel_for<__nv_bfloat16, false>(pl.mt));
+  const size_t smem = sk_smem_bytes(pl.kch, pl.mt, pl.stages, p.b_k_major);
+  auto kern = p.dtype == B200_FLOAT16 ? (pl.cluster ? sk_kernel_for<__half, true>(pl.mt, p.b_k_major, pl.stages) : sk_kernel_for<__half, false>(pl.mt, false, SK_STAGES))
+                                      : (pl.cluster ? sk_kernel_for<__nv_bfloat16, true>(pl.mt, p.b_k_major, pl.stages) : sk_kernel_for<__nv_bfloat16, false>(pl.mt, false, SK_STAGES));
   static std::mutex mu;
   static std::map<std::pair<int, const void*>, bool> configured;   // per device and kernel
   {
     std::lock_guard<std::mutex> lk(mu);
     bool& done = configured[{dev->ordinal(), (const void*)kern}];
     if (!done) {
-      B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sk_smem_bytes(128, 4)));
+      B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sk_smem_bytes(128, 4, SK_STAGES, true)));
       done = true;
     }
   }
   static const bool pdl_on = []() { const char* v = getenv("B200MLX_PDL"); return !(v && v[0] == '0'); }();
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(p.n / SK_BN), (unsigned)pl.splits);
+  cfg.gridDim = dim3((unsigned)((p.n + SK_BN - 1) / SK_BN), (unsigned)pl.splits);
   cfg.blockDim = dim3(SK_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = dev->stream();

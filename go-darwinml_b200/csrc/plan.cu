@@ -1251,7 +1251,7 @@ class Planner {
     st.desc = strfmt("gemm[B=%lld M=%lld N=%lld K=%lld %s a:%s b:%s%s%s act=%d]", (long long)B, (long long)M, (long long)N, (long long)K,
                      dtype_name(x->dtype), gp.a_k_major ? "MK" : "KM", gp.b_k_major ? "NK" : "KN", bias ? " bias" : "",
                      residual ? (gp.residual_op ? " *residual" : " +residual") : "", gp.activation);
-    if (ragged_direct) st.desc.insert(st.desc.size() - 1, " ragged-rows");
+    if (ragged_direct && k::gemm_skinny_scratch_bytes(gp, ex_->dev->sm_count()) == 0) st.desc.insert(st.desc.size() - 1, " ragged-rows");
     st.reads = {a_slot, b_slot};
     if (bias) st.reads.push_back(bias_slot);
     if (residual) st.reads.push_back(res_slot);

@@ -124,3 +124,28 @@ def test_other_shapes_keep_their_kernels(b200, backend):
         want = OracleFunction().FusedDense(x.astype(np.float32), w.astype(np.float32), None, 0).astype(BF16)
         ok, viol = compare(got, want, RTOL, 1.0)
         assert ok, viol
+
+
+@pytest.mark.parametrize("M", [1, 16, 40])
+@pytest.mark.parametrize("N,K", [(64, 64), (100, 64), (777, 768), (4096, 2048), (50257, 768), (32768, 256), (1000, 16), (130, 8192)])
+def test_weights_stored_n_major_and_a_ragged_n(b200, backend, M, N, K):
+    # an LM head tied to the embedding table: W is [N, K] and N is whatever the vocabulary is
+    rng = np.random.default_rng(M + N + K)
+    x = rng_array(rng, (M, K), BF16)
+    w = rng_array(rng, (N, K), BF16, 1.0 / np.sqrt(K))
+    (got,), plan = run_backend(b200, backend, lambda f, a, b: f.DotGeneral(a, [1], [], b, [1], []), [x, w], describe=True)
+    # (beyond 32768 columns the tensor-core tile fills the GPU and keeps the product)
+    assert ("few-rows" in plan) == (N <= 32768) and "b:NK" in plan and plan.count("\n") == 1, plan
+    want = (x.astype(np.float64) @ w.astype(np.float64).T).astype(np.float32).astype(BF16)
+    ok, viol = compare(got, want, RTOL, 1.0)
+    assert ok, viol
+
+
+def test_n_major_weights_in_f16(b200, backend):
+    rng = np.random.default_rng(77)
+    x, w = rng_array(rng, (9, 512), np.float16), rng_array(rng, (333, 512), np.float16, 0.05)
+    (got,), plan = run_backend(b200, backend, lambda f, a, b: f.DotGeneral(a, [1], [], b, [1], []), [x, w], describe=True)
+    assert "few-rows" in plan, plan
+    want = (x.astype(np.float64) @ w.astype(np.float64).T).astype(np.float16)
+    ok, viol = compare(got, want, RTOL, 1.0)
+    assert ok, viol
