@@ -260,12 +260,16 @@ struct GemmParams {
   void* split_scratch = nullptr;
   int64_t split_scratch_bytes = 0;
   void* skinny_counters = nullptr;
+  // gemm_skinny only: a second weight of B's shape and layout; C = round(act(A B + bias)) * round(A B2), rounded again
+  // (a gated MLP in one launch).  Set only where gemm_skinny_dual_ok() holds; without a residual.
+  const void* b2 = nullptr;
   // B is not written by anything that may still be running when this launch starts (a plan input or constant): a
   // kernel launched as a programmatic dependent may then fetch it before the previous kernel has finished.
   bool b_static = false;
 };
 int64_t gemm_skinny_scratch_bytes(const GemmParams& p, int sm_count);   // 0: not a shape gemm_skinny takes
 int64_t gemm_skinny_counter_bytes(const GemmParams& p);
+bool gemm_skinny_dual_ok(const GemmParams& p);
 // The few-rows path alone: *taken is false (and nothing is launched) when the problem is outside its rules or has no scratch.
 Status gemm_skinny(Device* dev, const GemmParams& p, bool* taken);
 inline int64_t gemm_split_scratch_bytes(int64_t batch, int64_t m, int64_t n, int64_t k) {

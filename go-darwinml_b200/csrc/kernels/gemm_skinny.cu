@@ -36,6 +36,7 @@ constexpr int SK_X_PAD = 8;   // elements: the X rows' pitch is an odd number of
 struct SkArgs {
   const void* x;
   const void* w;
+  const void* w2;   // DUAL: the second weight
   void* c;
   const void* bias;
   const void* residual;
@@ -84,7 +85,10 @@ template <> __device__ __forceinline__ __half sk_from_f(float v) { return __floa
 // NK: W is stored [N, K] (an LM head tied to the embedding table): a stage holds [64 columns][kch] instead of [kch][64], its
 // fragments come from ldmatrix without .trans, and N need not be a multiple of 64 (columns past N are zero in shared
 // memory and never stored).
-template <typename T, bool CLUSTER, int MT, bool NK, int S>
+// DUAL (cluster reduction, W as [K, N] only): a second weight W2 of the same shape streams beside W and the result is
+// round(act(X W + bias)) * round(X W2), rounded again -- a gated MLP's act(x W1) * (x W2) in one launch, bit for bit what
+// the two launches (X W2 first, then act(X W) with a multiplying residual) produce.
+template <typename T, bool CLUSTER, int MT, bool NK, int S, bool DUAL>
 __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g) {
   constexpr int ROWS = 16 * MT;
   extern __shared__ __align__(128) unsigned char sk_smem[];
@@ -100,7 +104,8 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
   const int kch = g.kch;
   const int x_pitch = (kch + SK_X_PAD) * 2;           // bytes
   const int w_bytes = (NK ? (kch + 63) / 64 * 64 : kch) * SK_BN * 2;   // a stage's W part (NK: whole 128-byte groups per column, it swizzles within them)
-  const int stage_bytes = w_bytes + ROWS * x_pitch;
+  const int x_off = (DUAL ? 2 : 1) * w_bytes;   // DUAL: W2's part follows W's
+  const int stage_bytes = x_off + ROWS * x_pitch;
   const uint32_t ring_u = sm100::smem_u32(sk_smem);
   const int nch = (kc + kch - 1) / kch;
   const T* Wg = NK ? reinterpret_cast<const T*>(g.w) + (int64_t)n0 * g.K + k0 : reinterpret_cast<const T*>(g.w) + (int64_t)k0 * g.N + n0;
@@ -126,12 +131,19 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
         const int row = idx >> 3, ch = idx & 7;
         sk_cp_async16(wst + row * 128 + ((ch ^ (row & 7)) << 4), W + (int64_t)row * g.N + ch * 8);
       }
+      if constexpr (DUAL) {
+        const T* W2 = reinterpret_cast<const T*>(g.w2) + (int64_t)(k0 + c * kch) * g.N + n0;
+        for (int idx = tid; idx < rows * 8; idx += SK_THREADS) {
+          const int row = idx >> 3, ch = idx & 7;
+          sk_cp_async16(wst + w_bytes + row * 128 + ((ch ^ (row & 7)) << 4), W2 + (int64_t)row * g.N + ch * 8);
+        }
+      }
     }
   };
   auto issue_x = [&](int c) {
     if (c >= nch) return;
     const int rows = kc - c * kch < kch ? kc - c * kch : kch;
-    unsigned char* xst = sk_smem + (c % S) * stage_bytes + w_bytes;
+    unsigned char* xst = sk_smem + (c % S) * stage_bytes + x_off;
     const uint32_t xst_u = sm100::smem_u32(xst);
     const T* X = Xg + c * kch;
     const int xch = rows >> 3;
@@ -156,15 +168,19 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
   }
   // warp w: columns [16 w, 16 w + 16) of the slab, all rows, all of the slice's k
   float acc[MT][2][4];
+  float acc2[DUAL ? MT : 1][2][4];   // DUAL: X W2
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
     for (int t = 0; t < 2; ++t)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) acc[mt][t][i] = 0.f;
+      for (int i = 0; i < 4; ++i) {
+        acc[mt][t][i] = 0.f;
+        if (DUAL) acc2[DUAL ? mt : 0][t][i] = 0.f;
+      }
   {
     const int mi = lane >> 3, r = lane & 7;
-    const uint32_t a_off = w_bytes + (lane & 15) * x_pitch + (lane >> 4) * 16;
+    const uint32_t a_off = x_off + (lane & 15) * x_pitch + (lane >> 4) * 16;
     const int b_k = (mi & 1) * 8 + r;          // k within the 16-step; (k & 7) == r
     const int b_ch = warp * 2 + (mi >> 1);     // 16-byte unit within the 128-byte row
     const uint32_t b_off = b_k * 128 + ((b_ch ^ r) << 4);
@@ -178,7 +194,8 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
       const int rows = kc - c * kch < kch ? kc - c * kch : kch;
 #pragma unroll 2
       for (int kk = 0; kk < rows; kk += 16) {
-        uint32_t bq[4];
+        uint32_t bq[4], bq2[4];
+        if constexpr (DUAL) sk_ldmatrix_x4_trans(st + w_bytes + b_off + kk * 128, bq2);
         if constexpr (NK) {
           const int u = (kk >> 3) + (mi & 1);   // the 16-byte unit of this k half within the column's row
           sk_ldmatrix_x4(st + nk_row + (((u & ~7) | ((u ^ r) & 7)) << 4), bq);
@@ -191,6 +208,10 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
           sk_ldmatrix_x4(st + a_off + mt * 16 * x_pitch + kk * 2, a);
           sk_mma<T>(acc[mt][0], a, bq[0], bq[1]);
           sk_mma<T>(acc[mt][1], a, bq[2], bq[3]);
+          if constexpr (DUAL) {
+            sk_mma<T>(acc2[DUAL ? mt : 0][0], a, bq2[0], bq2[1]);
+            sk_mma<T>(acc2[DUAL ? mt : 0][1], a, bq2[2], bq2[3]);
+          }
         }
       }
       __syncthreads();   // everybody is done with the stage: it takes chunk c + SK_STAGES
@@ -211,6 +232,11 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
       for (int t = 0; t < 2; ++t) {
         *reinterpret_cast<float2*>(psm + (16 * mt + r0) * SK_BN + c0 + 8 * t) = make_float2(acc[mt][t][0], acc[mt][t][1]);
         *reinterpret_cast<float2*>(psm + (16 * mt + r0 + 8) * SK_BN + c0 + 8 * t) = make_float2(acc[mt][t][2], acc[mt][t][3]);
+        if constexpr (DUAL) {   // the second product's partial follows the first's
+          float* psm2 = psm + ROWS * SK_BN;
+          *reinterpret_cast<float2*>(psm2 + (16 * mt + r0) * SK_BN + c0 + 8 * t) = make_float2(acc2[DUAL ? mt : 0][t][0], acc2[DUAL ? mt : 0][t][1]);
+          *reinterpret_cast<float2*>(psm2 + (16 * mt + r0 + 8) * SK_BN + c0 + 8 * t) = make_float2(acc2[DUAL ? mt : 0][t][2], acc2[DUAL ? mt : 0][t][3]);
+        }
       }
     sm100::cluster_sync_all();
     const int csize = g.splits;
@@ -234,6 +260,22 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
         for (int c = 0; c < 8; ++c) {   // slice order: the same sum on every run (absent slices add +0)
           v[0] += pv[c].x; v[1] += pv[c].y; v[2] += pv[c].z; v[3] += pv[c].w;
         }
+        float v2[4] = {0.f, 0.f, 0.f, 0.f};
+        if constexpr (DUAL) {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            pv[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c < csize)
+              asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                           : "=f"(pv[c].x), "=f"(pv[c].y), "=f"(pv[c].z), "=f"(pv[c].w)
+                           : "r"(sm100::map_to_cta(psm_u + (ROWS * SK_BN + e) * 4u, (uint32_t)c))
+                           : "memory");
+          }
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            v2[0] += pv[c].x; v2[1] += pv[c].y; v2[2] += pv[c].z; v2[3] += pv[c].w;
+          }
+        }
         const bool whole = !NK || (g.N & 3) == 0;   // rows of C (bias, residual) are 8-byte aligned at every fourth column (always so for W as [K, N])
         const int64_t at = (int64_t)row * g.N + n0 + col;
         const int valid = g.N - (n0 + col) < 4 ? g.N - (n0 + col) : 4;
@@ -254,6 +296,10 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
         T* ot = reinterpret_cast<T*>(&out);
 #pragma unroll
         for (int j = 0; j < 4; ++j) ot[j] = sk_from_f<T>(v[j]);
+        if constexpr (DUAL) {   // both products rounded, multiplied, rounded again
+#pragma unroll
+          for (int j = 0; j < 4; ++j) ot[j] = sk_from_f<T>(sk_to_f<T>(ot[j]) * sk_to_f<T>(sk_from_f<T>(v2[j])));
+        }
         if (g.residual) {   // the rounded value combined with the residual, rounded again
           uint2 rq = make_uint2(0, 0);
           T* rt = reinterpret_cast<T*>(&rq);
@@ -356,8 +402,9 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
 struct SkPlan { int splits, kc, kch, stages, mt; bool cluster; };
 
 int sk_tiles(int64_t m) { return m <= 16 ? 1 : (m <= 32 ? 2 : 4); }
-size_t sk_smem_bytes(int kch, int mt, int stages, bool nk) {
-  const size_t ring = (size_t)stages * ((size_t)(nk ? (kch + 63) / 64 * 64 : kch) * SK_BN * 2 + (size_t)16 * mt * (kch + SK_X_PAD) * 2), partial = (size_t)16 * mt * SK_BN * 4;
+size_t sk_smem_bytes(int kch, int mt, int stages, bool nk, bool dual = false) {
+  const size_t ring = (size_t)stages * ((size_t)(nk ? (kch + 63) / 64 * 64 : kch) * SK_BN * 2 * (dual ? 2 : 1) + (size_t)16 * mt * (kch + SK_X_PAD) * 2),
+               partial = (size_t)16 * mt * SK_BN * 4 * (dual ? 2 : 1);
   return ring > partial ? ring : partial;   // the partial takes the ring's place
 }
 
@@ -409,19 +456,22 @@ SkPlan sk_plan(const GemmParams& p, int sm_count) {
   if (kch > kc) kch = kc;
   // Four stages, or three when the grid fits the SMs at once with three and not with four (a second, nearly empty wave
   // costs a whole CTA's time: 786 slabs of a 50257-column LM head against 740 places)
-  auto places = [&](int stages) { return (int64_t)sm_count * (int64_t)((227 * 1024) / (sk_smem_bytes((int)kch, mt, stages, p.b_k_major) + 1024)); };
+  auto places = [&](int stages) { return (int64_t)sm_count * (int64_t)((227 * 1024) / (sk_smem_bytes((int)kch, mt, stages, p.b_k_major, p.b2 != nullptr) + 1024)); };
   const int64_t ctas = slabs * splits;
-  const int stages = (p.b_k_major && ctas > places(SK_STAGES) && ctas <= places(3)) ? 3 : SK_STAGES;
+  const bool dual = p.b2 != nullptr;
+  const int stages = ((p.b_k_major || dual) && ctas > places(SK_STAGES) && ctas <= places(3)) ? 3 : SK_STAGES;
   return SkPlan{(int)splits, (int)kc, (int)kch, stages, mt, cluster_on};
 }
 
-template <typename T, bool CLUSTER, bool NK, int S>
+template <typename T, bool CLUSTER, bool NK, int S, bool DUAL = false>
 auto sk_kernel_for2(int mt) -> void (*)(const SkArgs) {
-  return mt == 1 ? gemm_skinny_kernel<T, CLUSTER, 1, NK, S> : (mt == 2 ? gemm_skinny_kernel<T, CLUSTER, 2, NK, S> : gemm_skinny_kernel<T, CLUSTER, 4, NK, S>);
+  return mt == 1 ? gemm_skinny_kernel<T, CLUSTER, 1, NK, S, DUAL>
+                 : (mt == 2 ? gemm_skinny_kernel<T, CLUSTER, 2, NK, S, DUAL> : gemm_skinny_kernel<T, CLUSTER, 4, NK, S, DUAL>);
 }
 template <typename T, bool CLUSTER>
-auto sk_kernel_for(int mt, bool nk, int stages) -> void (*)(const SkArgs) {
+auto sk_kernel_for(int mt, bool nk, int stages, bool dual) -> void (*)(const SkArgs) {
   if constexpr (CLUSTER) {
+    if (dual) return stages == 3 ? sk_kernel_for2<T, true, false, 3, true>(mt) : sk_kernel_for2<T, true, false, SK_STAGES, true>(mt);
     if (nk) return stages == 3 ? sk_kernel_for2<T, true, true, 3>(mt) : sk_kernel_for2<T, true, true, SK_STAGES>(mt);   // three stages: W as [N, K] only
     return sk_kernel_for2<T, true, false, SK_STAGES>(mt);
   } else {
@@ -436,6 +486,8 @@ int64_t gemm_skinny_scratch_bytes(const GemmParams& p, int sm_count) {
   const SkPlan pl = sk_plan(p, sm_count);
   return pl.cluster ? 16 : (int64_t)pl.splits * 16 * pl.mt * p.n * 4;   // (16: "taken", nothing goes through it)
 }
+// Whether act(A B + bias) * (A B2) can be one launch for this shape (B2 of B's shape and layout).
+bool gemm_skinny_dual_ok(const GemmParams& p) { return sk_shape_ok(p) && sk_cluster_on() && !p.b_k_major && p.m <= 32; }
 int64_t gemm_skinny_counter_bytes(const GemmParams& p) { return sk_shape_ok(p) ? (p.n + SK_BN - 1) / SK_BN * 4 : 0; }
 
 Status gemm_skinny(Device* dev, const GemmParams& p, bool* taken) {
@@ -447,22 +499,24 @@ Status gemm_skinny(Device* dev, const GemmParams& p, bool* taken) {
   if (!al(p.a) || !al(p.b) || !al(p.c) || !al(p.bias) || !al(p.residual) || !al(p.split_scratch)) return Status::OK();
   B200_TRY(dev->MakeCurrent());
   SkArgs g;
-  g.x = p.a; g.w = p.b; g.c = p.c; g.bias = p.bias; g.residual = p.residual;
+  const bool dual = p.b2 != nullptr;
+  if (dual && (!pl.cluster || p.b_k_major || p.residual || !al(p.b2))) return Status::OK();   // (gemm_skinny_dual_ok said otherwise: the caller falls back)
+  g.x = p.a; g.w = p.b; g.w2 = p.b2; g.c = p.c; g.bias = p.bias; g.residual = p.residual;
   g.partial = reinterpret_cast<float*>(p.split_scratch);
   g.counters = reinterpret_cast<unsigned*>(p.skinny_counters);
   g.M = (int)p.m; g.N = (int)p.n; g.K = (int)p.k; g.kc = pl.kc; g.kch = pl.kch; g.stages = pl.stages; g.splits = pl.splits;
   g.act = p.activation; g.residual_mul = p.residual_op;
   g.w_static = p.b_static ? 1 : 0;
-  const size_t smem = sk_smem_bytes(pl.kch, pl.mt, pl.stages, p.b_k_major);
-  auto kern = p.dtype == B200_FLOAT16 ? (pl.cluster ? sk_kernel_for<__half, true>(pl.mt, p.b_k_major, pl.stages) : sk_kernel_for<__half, false>(pl.mt, false, SK_STAGES))
-                                      : (pl.cluster ? sk_kernel_for<__nv_bfloat16, true>(pl.mt, p.b_k_major, pl.stages) : sk_kernel_for<__nv_bfloat16, false>(pl.mt, false, SK_STAGES));
+  const size_t smem = sk_smem_bytes(pl.kch, pl.mt, pl.stages, p.b_k_major, dual);
+  auto kern = p.dtype == B200_FLOAT16 ? (pl.cluster ? sk_kernel_for<__half, true>(pl.mt, p.b_k_major, pl.stages, dual) : sk_kernel_for<__half, false>(pl.mt, false, SK_STAGES, false))
+                                      : (pl.cluster ? sk_kernel_for<__nv_bfloat16, true>(pl.mt, p.b_k_major, pl.stages, dual) : sk_kernel_for<__nv_bfloat16, false>(pl.mt, false, SK_STAGES, false));
   static std::mutex mu;
   static std::map<std::pair<int, const void*>, bool> configured;   // per device and kernel
   {
     std::lock_guard<std::mutex> lk(mu);
     bool& done = configured[{dev->ordinal(), (const void*)kern}];
     if (!done) {
-      B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sk_smem_bytes(128, 4, SK_STAGES, true)));
+      B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sk_smem_bytes(128, 2, SK_STAGES, true, true)));
       done = true;
     }
   }

@@ -323,10 +323,18 @@ class Planner {
     }
     // Emit in creation order (operands always precede users), materialising
     // what must exist in memory; fused producers are pulled in on demand.
+    // ... except the second product of a gated pair act(a W1) * (a W2): it waits for its consumer, which either takes both
+    // weights in one launch or asks for it then.
+    std::vector<bool> deferred(n, false);
     for (int i = 0; i < n; ++i) {
       if (!live_[i]) continue;
       Node* x = g_.nodes[i].get();
-      if (MustMaterialize(x)) B200_TRY(EnsureMaterialized(x));
+      if (Node* second = GatedSecondProduct(x)) deferred[second->id] = true;
+    }
+    for (int i = 0; i < n; ++i) {
+      if (!live_[i]) continue;
+      Node* x = g_.nodes[i].get();
+      if (MustMaterialize(x) && !deferred[i]) B200_TRY(EnsureMaterialized(x));
     }
     // Outputs.
     for (size_t t = 0; t < targets.size(); ++t) {
@@ -423,6 +431,19 @@ class Planner {
     if (target_of_base_.count(x->id)) return true;
     if (uses_[x->id] > 1 && !Cheap(x)) return true;
     return false;                                   // inlined into its consumer, or pulled in on demand
+  }
+
+  // x = DotGeneral(a, W1)[+ bias][activation] multiplied (the compile-time rewrite's fa[1] == 2) by a plain
+  // DotGeneral(a, W2) of the same shapes that feeds nothing else and is no output: returns that second product.
+  Node* GatedSecondProduct(Node* x) const {
+    if (x->op != Op::DotGeneral || x->fa.size() < 2 || x->fa[1] != 2.0 || x->in.size() < 3) return nullptr;
+    Node* r = x->in.back();
+    if (r->op != Op::DotGeneral || uses_[r->id] != 1 || target_of_base_.count(r->id) || r->in.size() != 2 || r->in[0] != x->in[0] ||
+        r->ia != x->ia || r->in[1]->dims != x->in[1]->dims || r->in[1]->dtype != x->in[1]->dtype || r->dtype != x->dtype)
+      return nullptr;
+    if ((!r->fa.empty() && r->fa[0] != 0) || (r->fa.size() > 1 && r->fa[1] != 0)) return nullptr;
+    if (x->dtype != B200_BFLOAT16 && x->dtype != B200_FLOAT16) return nullptr;
+    return r;
   }
 
   Status EnsureMaterialized(Node* x) {
@@ -1179,7 +1200,10 @@ class Planner {
     B200_TRY(EnsureMaterialized(a));
     B200_TRY(EnsureMaterialized(b));
     if (bias) B200_TRY(EnsureMaterialized(bias));
-    if (residual) B200_TRY(EnsureMaterialized(residual));
+    // act(a W1) * (a W2), the second product a plain DotGeneral of the same operand that feeds nothing else (a gated MLP):
+    // candidate for ONE launch with two weights when the shape is the few-rows kernel's (decided below)
+    Node* dual_w2 = nullptr;
+    if (residual && GatedSecondProduct(x) == residual && slot_of_[residual->id] < 0) dual_w2 = residual->in[1];
     const int nc = (int)x->ia[0], nb = (int)x->ia[1];
     std::vector<int64_t> lc(x->ia.begin() + 2, x->ia.begin() + 2 + nc);
     std::vector<int64_t> lb(x->ia.begin() + 2 + nc, x->ia.begin() + 2 + nc + nb);
@@ -1192,6 +1216,18 @@ class Planner {
     const int64_t N = (B * K) ? b->num_elements() / (B * K) : 0;
     int a_major = OperandMajor(a, lb, lc);
     int b_major = OperandMajor(b, rb, rc);  // 1: [B,N,K]; 0: [B,K,N]
+    if (dual_w2) {
+      k::GemmParams probe;
+      probe.batch = B; probe.m = M; probe.n = N; probe.k = K;
+      probe.a_k_major = a_major == 1; probe.b_k_major = b_major != 0; probe.dtype = x->dtype;
+      if (a_major != 1 || b_major != 0 || OperandMajor(dual_w2, rb, rc) != 0 || !k::gemm_skinny_dual_ok(probe)) dual_w2 = nullptr;
+    }
+    if (dual_w2) {
+      B200_TRY(EnsureMaterialized(dual_w2));
+      residual = nullptr;   // never computed on its own
+    } else if (residual) {
+      B200_TRY(EnsureMaterialized(residual));
+    }
     // With several contracting (or batch) axes both sides must walk them in the same order.
     auto same_order = [](Node* t1, const std::vector<int64_t>& ax1, Node* t2, const std::vector<int64_t>& ax2) {
       std::vector<size_t> idx;
@@ -1244,18 +1280,23 @@ class Planner {
     const int gemm_out = pad_rows ? NewTemp(B * M * ldc * es_out + 16) : out_slot;
     gp.ldc = ldc;
     gp.activation = (int)x->fa[0];
-    gp.residual_op = (has_residual && x->fa[1] == 2.0) ? 1 : 0;
+    gp.residual_op = (has_residual && x->fa[1] == 2.0 && !dual_w2) ? 1 : 0;
     const int bias_slot = bias ? SlotOf(bias) : -1;
     const int res_slot = residual ? SlotOf(residual) : -1;
     Step st;
     st.desc = strfmt("gemm[B=%lld M=%lld N=%lld K=%lld %s a:%s b:%s%s%s act=%d]", (long long)B, (long long)M, (long long)N, (long long)K,
                      dtype_name(x->dtype), gp.a_k_major ? "MK" : "KM", gp.b_k_major ? "NK" : "KN", bias ? " bias" : "",
-                     residual ? (gp.residual_op ? " *residual" : " +residual") : "", gp.activation);
+                     dual_w2 ? " *second-product" : (residual ? (gp.residual_op ? " *residual" : " +residual") : ""), gp.activation);
     if (ragged_direct && k::gemm_skinny_scratch_bytes(gp, ex_->dev->sm_count()) == 0) st.desc.insert(st.desc.size() - 1, " ragged-rows");
     st.reads = {a_slot, b_slot};
     if (bias) st.reads.push_back(bias_slot);
     if (residual) st.reads.push_back(res_slot);
-    st.writes = {gemm_out};
+    // two weights in one launch; should the kernel decline at run time (an unaligned buffer), the two products run one
+    // after the other through a small temporary
+    const int w2_slot = dual_w2 ? SlotOf(dual_w2) : -1;
+    const int dual_tmp = dual_w2 ? NewTemp(B * M * N * es_out + 16) : -1;
+    if (dual_w2) { st.reads.push_back(w2_slot); st.writes.push_back(dual_tmp); }
+    st.writes.insert(st.writes.begin(), gemm_out);
     // fp32 on the tensor cores splits both operands into bf16 planes: their room comes from the plan's arena, so the step
     // allocates nothing and can be recorded
     // A 16-bit product of a handful of rows splits K over many CTAs: fp32 partial sums in the arena and a few counters
@@ -1272,7 +1313,7 @@ class Planner {
       B200_TRY(NewZeroedConst(k::gemm_skinny_counter_bytes(gp), &counter_slot));
       st.desc.insert(st.desc.size() - 1, " few-rows");
     }
-    st.run = [gp, a_slot, b_slot, bias_slot, res_slot, gemm_out, split_slot, split_bytes, counter_slot](Device* dev, void* const* p) -> Status {
+    st.run = [gp, a_slot, b_slot, bias_slot, res_slot, gemm_out, split_slot, split_bytes, counter_slot, w2_slot, dual_tmp](Device* dev, void* const* p) -> Status {
       k::GemmParams q = gp;
       if (split_slot >= 0) { q.split_scratch = p[split_slot]; q.split_scratch_bytes = split_bytes; }
       if (counter_slot >= 0) q.skinny_counters = p[counter_slot];
@@ -1281,6 +1322,18 @@ class Planner {
       q.c = p[gemm_out];
       q.bias = bias_slot >= 0 ? p[bias_slot] : nullptr;
       q.residual = res_slot >= 0 ? p[res_slot] : nullptr;
+      if (w2_slot >= 0) {
+        q.b2 = p[w2_slot];
+        bool taken = false;
+        B200_TRY(k::gemm_skinny(dev, q, &taken));
+        if (taken) return Status::OK();
+        k::GemmParams second = q;   // X W2 on its own ...
+        second.b = p[w2_slot]; second.b2 = nullptr; second.c = p[dual_tmp]; second.bias = nullptr; second.activation = B200_ACT_NONE;
+        B200_TRY(k::gemm(dev, second));
+        q.b2 = nullptr;             // ... then act(X W + bias) times it
+        q.residual = p[dual_tmp];
+        q.residual_op = 1;
+      }
       return k::gemm(dev, q);
     };
     ex_->steps.push_back(std::move(st));

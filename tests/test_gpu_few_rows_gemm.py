@@ -149,3 +149,40 @@ def test_n_major_weights_in_f16(b200, backend):
     want = (x.astype(np.float64) @ w.astype(np.float64).T).astype(np.float16)
     ok, viol = compare(got, want, RTOL, 1.0)
     assert ok, viol
+
+
+@pytest.mark.parametrize("M", [1, 16, 17, 32])
+@pytest.mark.parametrize("N,K,act", [(512, 256, 3), (8192, 2048, 3), (1024, 4096, 1), (64, 16, 0)])
+def test_gated_pair_of_products_in_one_launch(b200, backend, M, N, K, act):
+    # act(x W1) * (x W2): one launch with two weights, bit for bit the two-launch result (both products rounded, multiplied,
+    # rounded again)
+    rng = np.random.default_rng(M + N + K)
+    x = rng_array(rng, (M, K), BF16)
+    w1, w2 = rng_array(rng, (K, N), BF16, 1.0 / np.sqrt(K)), rng_array(rng, (K, N), BF16, 1.0 / np.sqrt(K))
+    build = lambda f, a, b, c: f.Mul(f.FusedDense(a, b, None, act), f.FusedDense(a, c, None, 0))
+    (got,), plan = run_backend(b200, backend, build, [x, w1, w2], describe=True)
+    assert "*second-product" in plan and "few-rows" in plan and plan.count("\n") == 1, plan
+    o = OracleFunction()
+    g = o.FusedDense(x.astype(np.float32), w1.astype(np.float32), None, act).astype(BF16)
+    u = o.FusedDense(x.astype(np.float32), w2.astype(np.float32), None, 0).astype(BF16)
+    want = (g.astype(np.float32) * u.astype(np.float32)).astype(BF16)
+    ok, viol = compare(got, want, RTOL, 1.0)
+    assert ok, viol
+
+
+def test_gated_pair_is_left_alone_when_the_second_product_is_used_elsewhere(b200, backend):
+    rng = np.random.default_rng(31)
+    x, w1, w2 = rng_array(rng, (8, 256), BF16), rng_array(rng, (256, 512), BF16, 0.06), rng_array(rng, (256, 512), BF16, 0.06)
+
+    def build(f, a, b, c):
+        up = f.FusedDense(a, c, None, 0)
+        return [f.Mul(f.FusedDense(a, b, None, 3), up), up]
+    got, plan = run_backend(b200, backend, build, [x, w1, w2], describe=True)
+    assert "*second-product" not in plan, plan
+    o = OracleFunction()
+    g = o.FusedDense(x.astype(np.float32), w1.astype(np.float32), None, 3).astype(BF16)
+    u = o.FusedDense(x.astype(np.float32), w2.astype(np.float32), None, 0).astype(BF16)
+    ok, viol = compare(got[0], (g.astype(np.float32) * u.astype(np.float32)).astype(BF16), RTOL, 1.0)
+    assert ok, viol
+    ok, viol = compare(got[1], u, RTOL, 1.0)
+    assert ok, viol
