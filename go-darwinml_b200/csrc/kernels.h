@@ -139,6 +139,8 @@ Status dynamic_slice(Device* dev, const DynSliceParams& p);
 Status dynamic_update_slice(Device* dev, const DynSliceParams& p);
 // The same when y already holds x (y == x): only the block is written.
 Status dynamic_update_slice_inplace(Device* dev, const DynSliceParams& p);
+// Two of them with the same block geometry and element size (a layer's key and value caches) in ONE launch.
+Status dynamic_update_slice_inplace2(Device* dev, const DynSliceParams& p0, const DynSliceParams& p1);
 
 // Up to 8 contiguous arrays laid end to end into y with ONE launch (small concatenations are launch-bound: a fused QKV
 // projection joins three bias vectors per layer).  counts are in elements.

@@ -319,19 +319,62 @@ __global__ void __launch_bounds__(256) dynamic_update_inplace_kernel(const DynAr
   }
 }
 
+// Two in-place updates of the same geometry (a layer's key and value caches) in one launch: blockIdx.y picks the pair.
+template <typename E>
+__global__ void __launch_bounds__(256) dynamic_update_inplace2_kernel(const DynArgs a0, const DynArgs a1, int64_t total) {
+  __shared__ int64_t start[kMaxDims];
+  const DynArgs& a = blockIdx.y ? a1 : a0;
+  block_starts(a, start);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t rem = i, dst = 0, src = 0, stride = 1;
+    for (int d = a.rank - 1; d >= 0; --d) {
+      const int64_t c = rem % a.b_dims[d];
+      rem /= a.b_dims[d];
+      dst += (c + start[d]) * stride;
+      src += c * a.u_strides[d];
+      stride *= a.x_dims[d];
+    }
+    reinterpret_cast<E*>(a.y)[dst] = reinterpret_cast<const E*>(a.u)[src];
+  }
+}
+
+static int64_t fill_inplace_args(const DynSliceParams& p, DynArgs* a) {
+  a->x = p.y; a->u = p.u; a->y = p.y; a->rank = p.rank;
+  fill_update_strides(p, a);
+  int64_t total = 1;
+  for (int d = 0; d < kMaxDims; ++d) {
+    a->x_dims[d] = d < p.rank ? p.x_dims[d] : 1;
+    a->b_dims[d] = d < p.rank ? p.b_dims[d] : 1;
+    a->starts[d] = d < p.rank ? p.starts[d] : nullptr;
+    a->start_dtypes[d] = d < p.rank ? p.start_dtypes[d] : B200_INT32;
+    if (d < p.rank) total *= p.b_dims[d];
+  }
+  return total;
+}
+
+Status dynamic_update_slice_inplace2(Device* dev, const DynSliceParams& p0, const DynSliceParams& p1) {
+  if (p0.rank < 0 || p0.rank > kMaxDims || p1.rank != p0.rank || p1.elt_size != p0.elt_size) return Status::Invalid("dynamic slice: rank");
+  DynArgs a0, a1;
+  const int64_t total = fill_inplace_args(p0, &a0);
+  if (fill_inplace_args(p1, &a1) != total) return Status::Invalid("dynamic slice: the two updates differ in size");
+  if (total == 0) return Status::OK();
+  B200_TRY(dev->MakeCurrent());
+  const dim3 grid(grid_for(dev, total), 2);
+  cudaStream_t s = dev->stream();
+  switch (p0.elt_size) {
+    case 1: dynamic_update_inplace2_kernel<uint8_t><<<grid, 256, 0, s>>>(a0, a1, total); break;
+    case 2: dynamic_update_inplace2_kernel<uint16_t><<<grid, 256, 0, s>>>(a0, a1, total); break;
+    case 4: dynamic_update_inplace2_kernel<uint32_t><<<grid, 256, 0, s>>>(a0, a1, total); break;
+    case 8: dynamic_update_inplace2_kernel<uint64_t><<<grid, 256, 0, s>>>(a0, a1, total); break;
+    default: return Status::Invalid("dynamic slice: element size");
+  }
+  return dev->CheckLaunch("dynamic_update_slice_inplace2");
+}
+
 Status dynamic_update_slice_inplace(Device* dev, const DynSliceParams& p) {
   if (p.rank < 0 || p.rank > kMaxDims) return Status::Invalid("dynamic slice: rank");
   DynArgs a;
-  a.x = p.y; a.u = p.u; a.y = p.y; a.rank = p.rank;
-  fill_update_strides(p, &a);
-  int64_t total = 1;
-  for (int d = 0; d < kMaxDims; ++d) {
-    a.x_dims[d] = d < p.rank ? p.x_dims[d] : 1;
-    a.b_dims[d] = d < p.rank ? p.b_dims[d] : 1;
-    a.starts[d] = d < p.rank ? p.starts[d] : nullptr;
-    a.start_dtypes[d] = d < p.rank ? p.start_dtypes[d] : B200_INT32;
-    if (d < p.rank) total *= p.b_dims[d];
-  }
+  const int64_t total = fill_inplace_args(p, &a);
   if (total == 0) return Status::OK();
   B200_TRY(dev->MakeCurrent());
   const unsigned grid = grid_for(dev, total);

@@ -1035,6 +1035,15 @@ class Planner {
     return Status::OK();
   }
 
+  // The most recent DynamicUpdateSlice step, kept so that a twin that follows it directly can join it.
+  struct LastDus {
+    int step = -1;
+    std::vector<int> start_slots;
+    int rank = 0, elt_size = 0;
+    int64_t x_dims[k::kMaxDims] = {0}, b_dims[k::kMaxDims] = {0};
+    std::function<k::DynSliceParams(void* const*)> bind;
+  } last_dus_;
+
   // DynamicSlice (inputs: operand, starts...) and DynamicUpdateSlice (operand, update, starts...): the start scalars are
   // read on the device, so the launch plan stays static.
   Status EmitDynamicSlice(Node* x) {
@@ -1080,16 +1089,48 @@ class Planner {
       if (ex_->donate_alias.size() <= (size_t)ex_->slots[out_slot].index) ex_->donate_alias.resize(ex_->slots[out_slot].index + 1, -1);
       ex_->donate_alias[ex_->slots[out_slot].index] = ex_->slots[x_slot].index;
     }
-    st.run = [dp, start_slots, x_slot, u_slot, out_slot, update, u_byte_off](Device* dev, void* const* p) -> Status {
+    auto bind = [dp, start_slots, x_slot, u_slot, out_slot, u_byte_off](void* const* p) {
       k::DynSliceParams q = dp;
       q.x = p[x_slot];
       q.u = u_slot >= 0 ? (const char*)p[u_slot] + u_byte_off : nullptr;
       q.y = p[out_slot];
       for (size_t i = 0; i < start_slots.size(); ++i) q.starts[i] = p[start_slots[i]];
+      return q;
+    };
+    auto run_one = [update](Device* dev, const k::DynSliceParams& q) -> Status {
       if (update && q.x == q.y) return k::dynamic_update_slice_inplace(dev, q);
       return update ? k::dynamic_update_slice(dev, q) : k::dynamic_slice(dev, q);
     };
+    // A second update with the same start indices and block geometry right after the first (a layer's key cache, then its
+    // value cache): one step, and one launch when both turn out to be in place.
+    if (update && last_dus_.step == (int)ex_->steps.size() - 1 && last_dus_.step >= 0 && last_dus_.start_slots == start_slots &&
+        last_dus_.rank == dp.rank && last_dus_.elt_size == dp.elt_size &&
+        std::equal(dp.x_dims, dp.x_dims + dp.rank, last_dus_.x_dims) && std::equal(dp.b_dims, dp.b_dims + dp.rank, last_dus_.b_dims)) {
+      Step& prev = ex_->steps.back();
+      prev.desc.insert(prev.desc.size() - 1, upd_src ? " + a second one, read in place" : " + a second one");
+      prev.reads.insert(prev.reads.end(), st.reads.begin(), st.reads.end());
+      prev.writes.push_back(out_slot);
+      auto first = last_dus_.bind;
+      prev.run = [first, bind, run_one](Device* dev, void* const* p) -> Status {
+        const k::DynSliceParams q0 = first(p), q1 = bind(p);
+        if (q0.x == q0.y && q1.x == q1.y) return k::dynamic_update_slice_inplace2(dev, q0, q1);
+        B200_TRY(run_one(dev, q0));
+        return run_one(dev, q1);
+      };
+      last_dus_.step = -1;   // pairs only
+      return Status::OK();
+    }
+    st.run = [bind, run_one](Device* dev, void* const* p) -> Status { return run_one(dev, bind(p)); };
     ex_->steps.push_back(std::move(st));
+    if (update) {
+      last_dus_.step = (int)ex_->steps.size() - 1;
+      last_dus_.start_slots = start_slots;
+      last_dus_.rank = dp.rank;
+      last_dus_.elt_size = dp.elt_size;
+      std::copy(dp.x_dims, dp.x_dims + k::kMaxDims, last_dus_.x_dims);
+      std::copy(dp.b_dims, dp.b_dims + k::kMaxDims, last_dus_.b_dims);
+      last_dus_.bind = bind;
+    }
     return Status::OK();
   }
 

@@ -166,7 +166,8 @@ def test_query_and_cache_updates_are_read_in_place_inside_the_fused_projection(b
 
     inputs = [x, wqkv, kc, vc, mask, pos]
     got, plan = run_backend(b200, backend, build, inputs, describe=True)
-    assert "move[Slice" not in plan and plan.count("update read in place") == 2 and "attention_decode[" in plan, plan
+    # (the key and the value cache are updated by one step: the second update joins the first)
+    assert "move[Slice" not in plan and "update read in place + a second one, read in place" in plan and "attention_decode[" in plan, plan
     from tests.util import run_oracle
     want = run_oracle(build, inputs)
     np.testing.assert_array_equal(got[1].view(np.uint16), want[1].view(np.uint16))

@@ -74,8 +74,15 @@ def test_scatter_sum_large_embedding_gradient(b200, backend):
     build = lambda f, o, i, u: f.ScatterSum(o, i, u, 1, [1], [0], [0], False, False)
     (got,) = run_backend(b200, backend, build, [operand, ids, upd])
     (want,) = run_oracle(build, [operand, ids, upd])
-    ok, viol = compare(got, want, 1e-5, 1.0)
+    # The hot row is a sum of 64 + terms added by atomics in whatever order they arrive: its error bound is the sum's, a
+    # few ulps of the largest partial sum per term, not 1e-5 of a result that may have cancelled to nearly nothing.
+    hot = np.zeros(V, dtype=bool)
+    hot[7] = True
+    ok, viol = compare(got[~hot], want[~hot], 1e-5, 1.0)
     assert ok, viol
+    terms = upd[(ids[:, 0] == 7)]
+    bound = 2.0 * terms.shape[0] * np.finfo(np.float32).eps * np.abs(terms).sum(axis=0)
+    assert (np.abs(got[7].astype(np.float64) - want[7].astype(np.float64)) <= bound).all()
 
 
 def test_scatter_errors(b200, backend):
