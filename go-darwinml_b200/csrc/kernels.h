@@ -265,6 +265,10 @@ struct GemmParams {
   // gemm_skinny only: a second weight of B's shape and layout; C = round(act(A B + bias)) * round(A B2), rounded again
   // (a gated MLP in one launch).  Set only where gemm_skinny_dual_ok() holds; without a residual.
   const void* b2 = nullptr;
+  // gemm_skinny only (where gemm_skinny_dual_ok() holds): A is the INPUT of an RMSNorm over K with this gain [K] and
+  // epsilon, and the product is taken of the norm's output -- the norm costs no launch of its own.
+  const void* rms_gamma = nullptr;
+  double rms_eps = 0;
   // B is not written by anything that may still be running when this launch starts (a plan input or constant): a
   // kernel launched as a programmatic dependent may then fetch it before the previous kernel has finished.
   bool b_static = false;

@@ -37,6 +37,8 @@ struct SkArgs {
   const void* x;
   const void* w;
   const void* w2;   // DUAL: the second weight
+  const void* gamma;   // RMS: the norm's gain [K]
+  float rms_eps;
   void* c;
   const void* bias;
   const void* residual;
@@ -71,6 +73,18 @@ template <> __device__ __forceinline__ void sk_mma<__half>(float (&d)[4], const 
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+template <typename T> __device__ __forceinline__ float2 sk_unpack2(uint32_t w);
+template <> __device__ __forceinline__ float2 sk_unpack2<__nv_bfloat16>(uint32_t w) { return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u)); }
+template <> __device__ __forceinline__ float2 sk_unpack2<__half>(uint32_t w) { return __half22float2(*reinterpret_cast<const __half2*>(&w)); }
+template <typename T> __device__ __forceinline__ uint32_t sk_mul2(uint32_t a, uint32_t b);   // two 16-bit products, each rounded
+template <> __device__ __forceinline__ uint32_t sk_mul2<__nv_bfloat16>(uint32_t a, uint32_t b) {
+  const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+template <> __device__ __forceinline__ uint32_t sk_mul2<__half>(uint32_t a, uint32_t b) {
+  const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
 template <typename T> __device__ __forceinline__ float sk_to_f(T v);
 template <> __device__ __forceinline__ float sk_to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <> __device__ __forceinline__ float sk_to_f(__half v) { return __half2float(v); }
@@ -88,7 +102,13 @@ template <> __device__ __forceinline__ __half sk_from_f(float v) { return __floa
 // DUAL (cluster reduction, W as [K, N] only): a second weight W2 of the same shape streams beside W and the result is
 // round(act(X W + bias)) * round(X W2), rounded again -- a gated MLP's act(x W1) * (x W2) in one launch, bit for bit what
 // the two launches (X W2 first, then act(X W) with a multiplying residual) produce.
-template <typename T, bool CLUSTER, int MT, bool NK, int S, bool DUAL>
+// RMS (cluster reduction, W as [K, N] only): X is the INPUT of an RMSNorm with gain gamma whose output the product takes:
+// rms_norm(x)[m, :] W = rstd[m] * ((x[m, :] * gamma) W), so the gain is applied to X's fragments on their way into the MMAs,
+// the rows' sums of squares are collected from the same fragments (each K slice its share; the slices' shares meet
+// through distributed shared memory with the partial sums), and rstd scales the finished sums.  One launch and one pass
+// over X fewer than norm + product; the product of x and gamma is rounded to the 16-bit type, the scaling by rstd is not
+// (the two-launch form rounds x * rstd * gamma once).
+template <typename T, bool CLUSTER, int MT, bool NK, int S, bool DUAL, bool RMS>
 __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g) {
   constexpr int ROWS = 16 * MT;
   extern __shared__ __align__(128) unsigned char sk_smem[];
@@ -105,7 +125,8 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
   const int x_pitch = (kch + SK_X_PAD) * 2;           // bytes
   const int w_bytes = (NK ? (kch + 63) / 64 * 64 : kch) * SK_BN * 2;   // a stage's W part (NK: whole 128-byte groups per column, it swizzles within them)
   const int x_off = (DUAL ? 2 : 1) * w_bytes;   // DUAL: W2's part follows W's
-  const int stage_bytes = x_off + ROWS * x_pitch;
+  const int g_off = x_off + ROWS * x_pitch;           // RMS: the chunk of gamma follows X
+  const int stage_bytes = g_off + (RMS ? kch * 2 : 0);
   const uint32_t ring_u = sm100::smem_u32(sk_smem);
   const int nch = (kc + kch - 1) / kch;
   const T* Wg = NK ? reinterpret_cast<const T*>(g.w) + (int64_t)n0 * g.K + k0 : reinterpret_cast<const T*>(g.w) + (int64_t)k0 * g.N + n0;
@@ -147,6 +168,9 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
     const uint32_t xst_u = sm100::smem_u32(xst);
     const T* X = Xg + c * kch;
     const int xch = rows >> 3;
+    if constexpr (RMS) {
+      if (tid < xch) sk_cp_async16(ring_u + (c % S) * stage_bytes + g_off + tid * 16, reinterpret_cast<const T*>(g.gamma) + k0 + c * kch + tid * 8);
+    }
     for (int idx = tid; idx < ROWS * xch; idx += SK_THREADS) {
       const int row = idx / xch, ch = idx - row * xch;
       if (row < g.M) sk_cp_async16(xst_u + row * x_pitch + ch * 16, X + (int64_t)row * g.K + ch * 8);
@@ -178,6 +202,9 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
         acc[mt][t][i] = 0.f;
         if (DUAL) acc2[DUAL ? mt : 0][t][i] = 0.f;
       }
+  float ss[RMS ? MT : 1][2];   // RMS: this slice's sums of squares of rows 16 mt + lane / 4 (+ 8), this thread's columns only
+#pragma unroll
+  for (int mt = 0; mt < (RMS ? MT : 1); ++mt) ss[mt][0] = ss[mt][1] = 0.f;
   {
     const int mi = lane >> 3, r = lane & 7;
     const uint32_t a_off = x_off + (lane & 15) * x_pitch + (lane >> 4) * 16;
@@ -202,10 +229,26 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
         } else {
           sk_ldmatrix_x4_trans(st + b_off + kk * 128, bq);
         }
+        uint32_t gk0 = 0, gk1 = 0;   // RMS: gamma at this thread's fragment columns kk + 2 (lane % 4) + {0, 1} and + 8
+        if constexpr (RMS) {
+          asm volatile("ld.shared.u32 %0, [%1];" : "=r"(gk0) : "r"(st + g_off + (kk + 2 * (lane & 3)) * 2));
+          asm volatile("ld.shared.u32 %0, [%1];" : "=r"(gk1) : "r"(st + g_off + (kk + 8 + 2 * (lane & 3)) * 2));
+        }
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
           uint32_t a[4];
           sk_ldmatrix_x4(st + a_off + mt * 16 * x_pitch + kk * 2, a);
+          if constexpr (RMS) {
+            if (((kk >> 4) & 3) == warp) {   // every warp holds the same X fragments: they take turns counting
+              const float2 x0 = sk_unpack2<T>(a[0]), x1 = sk_unpack2<T>(a[1]), x2 = sk_unpack2<T>(a[2]), x3 = sk_unpack2<T>(a[3]);
+              ss[mt][0] += x0.x * x0.x + x0.y * x0.y + x2.x * x2.x + x2.y * x2.y;
+              ss[mt][1] += x1.x * x1.x + x1.y * x1.y + x3.x * x3.x + x3.y * x3.y;
+            }
+            a[0] = sk_mul2<T>(a[0], gk0);
+            a[1] = sk_mul2<T>(a[1], gk0);
+            a[2] = sk_mul2<T>(a[2], gk1);
+            a[3] = sk_mul2<T>(a[3], gk1);
+          }
           sk_mma<T>(acc[mt][0], a, bq[0], bq[1]);
           sk_mma<T>(acc[mt][1], a, bq[2], bq[3]);
           if constexpr (DUAL) {
@@ -238,6 +281,21 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
           *reinterpret_cast<float2*>(psm2 + (16 * mt + r0 + 8) * SK_BN + c0 + 8 * t) = make_float2(acc2[DUAL ? mt : 0][t][2], acc2[DUAL ? mt : 0][t][3]);
         }
       }
+    float* ssq = psm + (DUAL ? 2 : 1) * ROWS * SK_BN;   // RMS: [ROWS] sums of squares of this slice, then the warps' [4][ROWS]
+    if constexpr (RMS) {
+      float* ssw = ssq + ROWS + warp * ROWS;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        float s0 = ss[mt][0], s1 = ss[mt][1];
+        s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
+        s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+        if ((lane & 3) == 0) { ssw[16 * mt + r0] = s0; ssw[16 * mt + r0 + 8] = s1; }
+      }
+      __syncthreads();
+      if (tid < ROWS) ssq[tid] = (ssq[ROWS + tid] + ssq[2 * ROWS + tid]) + (ssq[3 * ROWS + tid] + ssq[4 * ROWS + tid]);
+    }
     sm100::cluster_sync_all();
     const int csize = g.splits;
     const int per = ROWS * SK_BN / csize;   // outputs this CTA finishes (csize is 1, 2, 4 or 8), four per thread and step
@@ -279,6 +337,20 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
         const bool whole = !NK || (g.N & 3) == 0;   // rows of C (bias, residual) are 8-byte aligned at every fourth column (always so for W as [K, N])
         const int64_t at = (int64_t)row * g.N + n0 + col;
         const int valid = g.N - (n0 + col) < 4 ? g.N - (n0 + col) : 4;
+        if constexpr (RMS) {   // the row's mean square over all of K: the slices' shares in slice order
+          const uint32_t sq_u = sm100::smem_u32(ssq + row);
+          float tot = 0.f, part[8];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            part[c] = 0.f;
+            if (c < csize) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part[c]) : "r"(sm100::map_to_cta(sq_u, (uint32_t)c)) : "memory");
+          }
+#pragma unroll
+          for (int c = 0; c < 8; ++c) tot += part[c];
+          const float rstd = rsqrtf(tot / (float)g.K + g.rms_eps);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { v[j] *= rstd; v2[j] *= rstd; }
+        }
         if (g.bias) {
           uint2 bq = make_uint2(0, 0);
           T* bt = reinterpret_cast<T*>(&bq);
@@ -402,9 +474,10 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
 struct SkPlan { int splits, kc, kch, stages, mt; bool cluster; };
 
 int sk_tiles(int64_t m) { return m <= 16 ? 1 : (m <= 32 ? 2 : 4); }
-size_t sk_smem_bytes(int kch, int mt, int stages, bool nk, bool dual = false) {
-  const size_t ring = (size_t)stages * ((size_t)(nk ? (kch + 63) / 64 * 64 : kch) * SK_BN * 2 * (dual ? 2 : 1) + (size_t)16 * mt * (kch + SK_X_PAD) * 2),
-               partial = (size_t)16 * mt * SK_BN * 4 * (dual ? 2 : 1);
+size_t sk_smem_bytes(int kch, int mt, int stages, bool nk, bool dual = false, bool rms = false) {
+  const size_t ring = (size_t)stages * ((size_t)(nk ? (kch + 63) / 64 * 64 : kch) * SK_BN * 2 * (dual ? 2 : 1) + (size_t)16 * mt * (kch + SK_X_PAD) * 2 +
+                                        (rms ? (size_t)kch * 2 : 0)),
+               partial = (size_t)16 * mt * SK_BN * 4 * (dual ? 2 : 1) + (rms ? (size_t)16 * mt * 4 * 5 : 0);
   return ring > partial ? ring : partial;   // the partial takes the ring's place
 }
 
@@ -456,21 +529,25 @@ SkPlan sk_plan(const GemmParams& p, int sm_count) {
   if (kch > kc) kch = kc;
   // Four stages, or three when the grid fits the SMs at once with three and not with four (a second, nearly empty wave
   // costs a whole CTA's time: 786 slabs of a 50257-column LM head against 740 places)
-  auto places = [&](int stages) { return (int64_t)sm_count * (int64_t)((227 * 1024) / (sk_smem_bytes((int)kch, mt, stages, p.b_k_major, p.b2 != nullptr) + 1024)); };
+  auto places = [&](int stages) { return (int64_t)sm_count * (int64_t)((227 * 1024) / (sk_smem_bytes((int)kch, mt, stages, p.b_k_major, p.b2 != nullptr, p.rms_gamma != nullptr) + 1024)); };
   const int64_t ctas = slabs * splits;
   const bool dual = p.b2 != nullptr;
   const int stages = ((p.b_k_major || dual) && ctas > places(SK_STAGES) && ctas <= places(3)) ? 3 : SK_STAGES;
   return SkPlan{(int)splits, (int)kc, (int)kch, stages, mt, cluster_on};
 }
 
-template <typename T, bool CLUSTER, bool NK, int S, bool DUAL = false>
+template <typename T, bool CLUSTER, bool NK, int S, bool DUAL = false, bool RMS = false>
 auto sk_kernel_for2(int mt) -> void (*)(const SkArgs) {
-  return mt == 1 ? gemm_skinny_kernel<T, CLUSTER, 1, NK, S, DUAL>
-                 : (mt == 2 ? gemm_skinny_kernel<T, CLUSTER, 2, NK, S, DUAL> : gemm_skinny_kernel<T, CLUSTER, 4, NK, S, DUAL>);
+  return mt == 1 ? gemm_skinny_kernel<T, CLUSTER, 1, NK, S, DUAL, RMS>
+                 : (mt == 2 ? gemm_skinny_kernel<T, CLUSTER, 2, NK, S, DUAL, RMS> : gemm_skinny_kernel<T, CLUSTER, 4, NK, S, DUAL, RMS>);
 }
 template <typename T, bool CLUSTER>
-auto sk_kernel_for(int mt, bool nk, int stages, bool dual) -> void (*)(const SkArgs) {
+auto sk_kernel_for(int mt, bool nk, int stages, bool dual, bool rms) -> void (*)(const SkArgs) {
   if constexpr (CLUSTER) {
+    if (rms) {   // (at most 32 rows, like the gated pair)
+      if (dual) return stages == 3 ? sk_kernel_for2<T, true, false, 3, true, true>(mt) : sk_kernel_for2<T, true, false, SK_STAGES, true, true>(mt);
+      return sk_kernel_for2<T, true, false, SK_STAGES, false, true>(mt);
+    }
     if (dual) return stages == 3 ? sk_kernel_for2<T, true, false, 3, true>(mt) : sk_kernel_for2<T, true, false, SK_STAGES, true>(mt);
     if (nk) return stages == 3 ? sk_kernel_for2<T, true, true, 3>(mt) : sk_kernel_for2<T, true, true, SK_STAGES>(mt);   // three stages: W as [N, K] only
     return sk_kernel_for2<T, true, false, SK_STAGES>(mt);
@@ -499,24 +576,26 @@ Status gemm_skinny(Device* dev, const GemmParams& p, bool* taken) {
   if (!al(p.a) || !al(p.b) || !al(p.c) || !al(p.bias) || !al(p.residual) || !al(p.split_scratch)) return Status::OK();
   B200_TRY(dev->MakeCurrent());
   SkArgs g;
-  const bool dual = p.b2 != nullptr;
-  if (dual && (!pl.cluster || p.b_k_major || p.residual || !al(p.b2))) return Status::OK();   // (gemm_skinny_dual_ok said otherwise: the caller falls back)
+  const bool dual = p.b2 != nullptr, rms = p.rms_gamma != nullptr;
+  if (dual && (!pl.cluster || p.b_k_major || p.residual || !al(p.b2))) return Status::OK();
+  if (rms && (!pl.cluster || p.b_k_major || p.m > 32 || !al(p.rms_gamma))) return Status::OK();   // (likewise: the caller falls back)   // (gemm_skinny_dual_ok said otherwise: the caller falls back)
+  g.gamma = p.rms_gamma; g.rms_eps = (float)p.rms_eps;
   g.x = p.a; g.w = p.b; g.w2 = p.b2; g.c = p.c; g.bias = p.bias; g.residual = p.residual;
   g.partial = reinterpret_cast<float*>(p.split_scratch);
   g.counters = reinterpret_cast<unsigned*>(p.skinny_counters);
   g.M = (int)p.m; g.N = (int)p.n; g.K = (int)p.k; g.kc = pl.kc; g.kch = pl.kch; g.stages = pl.stages; g.splits = pl.splits;
   g.act = p.activation; g.residual_mul = p.residual_op;
   g.w_static = p.b_static ? 1 : 0;
-  const size_t smem = sk_smem_bytes(pl.kch, pl.mt, pl.stages, p.b_k_major, dual);
-  auto kern = p.dtype == B200_FLOAT16 ? (pl.cluster ? sk_kernel_for<__half, true>(pl.mt, p.b_k_major, pl.stages, dual) : sk_kernel_for<__half, false>(pl.mt, false, SK_STAGES, false))
-                                      : (pl.cluster ? sk_kernel_for<__nv_bfloat16, true>(pl.mt, p.b_k_major, pl.stages, dual) : sk_kernel_for<__nv_bfloat16, false>(pl.mt, false, SK_STAGES, false));
+  const size_t smem = sk_smem_bytes(pl.kch, pl.mt, pl.stages, p.b_k_major, dual, rms);
+  auto kern = p.dtype == B200_FLOAT16 ? (pl.cluster ? sk_kernel_for<__half, true>(pl.mt, p.b_k_major, pl.stages, dual, rms) : sk_kernel_for<__half, false>(pl.mt, false, SK_STAGES, false, false))
+                                      : (pl.cluster ? sk_kernel_for<__nv_bfloat16, true>(pl.mt, p.b_k_major, pl.stages, dual, rms) : sk_kernel_for<__nv_bfloat16, false>(pl.mt, false, SK_STAGES, false, false));
   static std::mutex mu;
   static std::map<std::pair<int, const void*>, bool> configured;   // per device and kernel
   {
     std::lock_guard<std::mutex> lk(mu);
     bool& done = configured[{dev->ordinal(), (const void*)kern}];
     if (!done) {
-      B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sk_smem_bytes(128, 2, SK_STAGES, true, true)));
+      B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sk_smem_bytes(128, 2, SK_STAGES, true, true, true)));
       done = true;
     }
   }

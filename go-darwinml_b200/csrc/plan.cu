@@ -331,6 +331,33 @@ class Planner {
       Node* x = g_.nodes[i].get();
       if (Node* second = GatedSecondProduct(x)) deferred[second->id] = true;
     }
+    // ... and an RMSNorm over the last axis whose every user is a DotGeneral taking it as the left operand: a product
+    // of a few rows applies the norm itself (EmitDotGeneral); any user that does not asks for the norm then.
+    rms_deferred_.assign(n, false);
+    {
+      std::vector<int> bad(n, 0), users(n, 0);
+      for (int i = 0; i < n; ++i) {
+        if (!live_[i]) continue;
+        Node* u = g_.nodes[i].get();
+        for (size_t j = 0; j < u->in.size(); ++j) {
+          Node* b = ViewBase(u->in[j]);
+          if (b->op != Op::RmsNorm || IsView(u)) continue;   // (a view's own users are seen through it)
+          ++users[b->id];
+          if (u->op != Op::DotGeneral || j != 0) ++bad[b->id];
+        }
+      }
+      for (int i = 0; i < n; ++i) {
+        if (!live_[i]) continue;
+        Node* r = g_.nodes[i].get();
+        static const bool rms_on = []() { const char* v = getenv("B200MLX_GEMM_SKINNY_RMS"); return !(v && v[0] == '0'); }();
+        if (!rms_on || r->op != Op::RmsNorm || bad[i] || users[i] == 0 || target_of_base_.count(i)) continue;
+        if (r->dtype != B200_BFLOAT16 && r->dtype != B200_FLOAT16) continue;
+        const bool one_last_axis = r->ia.size() == 3 && r->ia[0] != 0 && r->ia[1] == 0 && r->ia[2] == r->rank() - 1;
+        if (!one_last_axis || r->in.size() < 2 || r->in[1]->num_elements() != r->dims.back() || r->in[1]->dtype != r->dtype) continue;
+        rms_deferred_[i] = true;
+        deferred[i] = true;
+      }
+    }
     for (int i = 0; i < n; ++i) {
       if (!live_[i]) continue;
       Node* x = g_.nodes[i].get();
@@ -1231,14 +1258,19 @@ class Planner {
     return -1;
   }
 
+  std::vector<bool> rms_deferred_;   // RMSNorm nodes left to their consumers (see the emission loop)
+
   Status EmitDotGeneral(Node* x) {
     Node* a = x->in[0];
     Node* b = x->in[1];
+    // the left operand is an RMSNorm that nobody has asked for yet: candidate for the norm applied inside the product
+    Node* rms = nullptr;
+    if (Node* ab = ViewBase(a); ab->op == Op::RmsNorm && (size_t)ab->id < rms_deferred_.size() && rms_deferred_[ab->id] && slot_of_[ab->id] < 0) rms = ab;
     // inputs: lhs, rhs, [bias], [residual]; fa = {activation, has_residual (set by the compile-time rewrite)}
     const bool has_residual = x->fa.size() > 1 && x->fa[1] != 0;
     Node* residual = has_residual ? x->in.back() : nullptr;
     Node* bias = (int)x->in.size() - (has_residual ? 1 : 0) > 2 ? x->in[2] : nullptr;
-    B200_TRY(EnsureMaterialized(a));
+    if (!rms) B200_TRY(EnsureMaterialized(a));
     B200_TRY(EnsureMaterialized(b));
     if (bias) B200_TRY(EnsureMaterialized(bias));
     // act(a W1) * (a W2), the second product a plain DotGeneral of the same operand that feeds nothing else (a gated MLP):
@@ -1257,6 +1289,21 @@ class Planner {
     const int64_t N = (B * K) ? b->num_elements() / (B * K) : 0;
     int a_major = OperandMajor(a, lb, lc);
     int b_major = OperandMajor(b, rb, rc);  // 1: [B,N,K]; 0: [B,K,N]
+    if (rms) {
+      k::GemmParams probe;
+      probe.batch = B; probe.m = M; probe.n = N; probe.k = K;
+      probe.a_k_major = a_major == 1; probe.b_k_major = b_major != 0; probe.dtype = x->dtype;
+      const bool last_axis_only = lc.size() == 1 && lc[0] == a->rank() - 1 && K == rms->dims.back() && lb.empty();
+      // (not into a product that streams a large weight through every CTA's whole K, such as an LM head: the norm's extra
+      // work per k-step sits on that kernel's critical path -- 128256 x 2048: 128 us against 107 -- and saves one launch)
+      if (!last_axis_only || a_major != 1 || b_major != 0 || !k::gemm_skinny_dual_ok(probe) || N * K > (64LL << 20)) {
+        rms = nullptr;
+        B200_TRY(EnsureMaterialized(a));   // the norm on its own after all
+      } else {
+        B200_TRY(EnsureMaterialized(rms->in[0]));
+        B200_TRY(EnsureMaterialized(rms->in[1]));
+      }
+    }
     if (dual_w2) {
       k::GemmParams probe;
       probe.batch = B; probe.m = M; probe.n = N; probe.k = K;
@@ -1279,7 +1326,7 @@ class Planner {
       return true;
     };
     if (!same_order(a, lc, b, rc) || !same_order(a, lb, b, rb)) b_major = -1;
-    int a_slot = SlotOf(a), b_slot = SlotOf(b);
+    int a_slot = rms ? SlotOf(rms->in[0]) : SlotOf(a), b_slot = SlotOf(b);
     auto canonical = [&](Node* t, const std::vector<int64_t>& batch, const std::vector<int64_t>& contract) {
       std::vector<int> perm;
       std::vector<bool> used(t->rank(), false);
@@ -1334,6 +1381,14 @@ class Planner {
     if (residual) st.reads.push_back(res_slot);
     // two weights in one launch; should the kernel decline at run time (an unaligned buffer), the two products run one
     // after the other through a small temporary
+    const int gamma_slot = rms ? SlotOf(rms->in[1]) : -1;
+    const int rms_tmp = rms ? NewTemp(M * K * es_out + 16) : -1;
+    const double rms_eps = rms ? rms->fa[0] : 0.0;
+    if (rms) {
+      st.reads.push_back(gamma_slot);
+      st.writes.push_back(rms_tmp);
+      st.desc.insert(st.desc.size() - 1, " of-rms-norm");
+    }
     const int w2_slot = dual_w2 ? SlotOf(dual_w2) : -1;
     const int dual_tmp = dual_w2 ? NewTemp(B * M * N * es_out + 16) : -1;
     if (dual_w2) { st.reads.push_back(w2_slot); st.writes.push_back(dual_tmp); }
@@ -1354,7 +1409,8 @@ class Planner {
       B200_TRY(NewZeroedConst(k::gemm_skinny_counter_bytes(gp), &counter_slot));
       st.desc.insert(st.desc.size() - 1, " few-rows");
     }
-    st.run = [gp, a_slot, b_slot, bias_slot, res_slot, gemm_out, split_slot, split_bytes, counter_slot, w2_slot, dual_tmp](Device* dev, void* const* p) -> Status {
+    st.run = [gp, a_slot, b_slot, bias_slot, res_slot, gemm_out, split_slot, split_bytes, counter_slot, w2_slot, dual_tmp, gamma_slot, rms_tmp,
+              rms_eps](Device* dev, void* const* p) -> Status {
       k::GemmParams q = gp;
       if (split_slot >= 0) { q.split_scratch = p[split_slot]; q.split_scratch_bytes = split_bytes; }
       if (counter_slot >= 0) q.skinny_counters = p[counter_slot];
@@ -1363,11 +1419,21 @@ class Planner {
       q.c = p[gemm_out];
       q.bias = bias_slot >= 0 ? p[bias_slot] : nullptr;
       q.residual = res_slot >= 0 ? p[res_slot] : nullptr;
-      if (w2_slot >= 0) {
-        q.b2 = p[w2_slot];
+      if (w2_slot >= 0 || gamma_slot >= 0) {
+        if (w2_slot >= 0) q.b2 = p[w2_slot];
+        if (gamma_slot >= 0) { q.rms_gamma = p[gamma_slot]; q.rms_eps = rms_eps; }
         bool taken = false;
         B200_TRY(k::gemm_skinny(dev, q, &taken));
         if (taken) return Status::OK();
+        if (gamma_slot >= 0) {   // the norm on its own into the temporary, then the product of that
+          k::NormParams np;
+          np.x = p[a_slot]; np.gamma = p[gamma_slot]; np.y = p[rms_tmp];
+          np.rows = gp.m; np.cols = gp.k; np.dtype = gp.dtype; np.epsilon = rms_eps; np.rms = true;
+          B200_TRY(k::norm_rows(dev, np));
+          q.a = p[rms_tmp];
+          q.rms_gamma = nullptr;
+        }
+        if (w2_slot < 0) return k::gemm(dev, q);
         k::GemmParams second = q;   // X W2 on its own ...
         second.b = p[w2_slot]; second.b2 = nullptr; second.c = p[dual_tmp]; second.bias = nullptr; second.activation = B200_ACT_NONE;
         B200_TRY(k::gemm(dev, second));

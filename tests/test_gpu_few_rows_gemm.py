@@ -186,3 +186,63 @@ def test_gated_pair_is_left_alone_when_the_second_product_is_used_elsewhere(b200
     assert ok, viol
     ok, viol = compare(got[1], u, RTOL, 1.0)
     assert ok, viol
+
+
+def _rms(x, gamma, eps):
+    v = x.astype(np.float64)
+    return (v / np.sqrt((v * v).mean(axis=-1, keepdims=True) + eps) * gamma.astype(np.float64))
+
+
+@pytest.mark.parametrize("M", [1, 7, 16, 32])
+@pytest.mark.parametrize("N,K", [(512, 256), (3072, 2048), (64, 16), (768, 1040)])
+def test_rms_norm_applied_inside_the_product(b200, backend, M, N, K):
+    # RMSNorm(x) W as one launch: gamma on X's fragments, the rows' sums of squares from the same fragments, rstd on the sums
+    rng = np.random.default_rng(M * 7 + N + K)
+    x = (rng_array(rng, (M, K), BF16).astype(np.float32) * 3 + 0.5).astype(BF16)
+    gamma = (1.0 + 0.3 * rng.standard_normal(K)).astype(np.float32).astype(BF16)
+    w, bias = rng_array(rng, (K, N), BF16, 1.0 / np.sqrt(K)), rng_array(rng, (N,), BF16)
+    build = lambda f, a, gm, b, c: f.FusedDense(f.FusedRMSNorm(a, [-1], 1e-5, gm), b, c, 1)
+    (got,), plan = run_backend(b200, backend, build, [x, gamma, w, bias], describe=True)
+    assert "of-rms-norm" in plan and "few-rows" in plan and "rms_norm[" not in plan and plan.count("\n") == 1, plan
+    h = _rms(x, gamma, 1e-5)
+    want = OracleFunction().FusedDense(h.astype(np.float32), w.astype(np.float32), bias.astype(np.float32), 1).astype(BF16)
+    ok, viol = compare(got, want, RTOL, 1.0)
+    assert ok, viol
+
+
+def test_rms_norm_inside_a_gated_pair_and_f16(b200, backend):
+    rng = np.random.default_rng(91)
+    for dt in (BF16, np.float16):
+        x = rng_array(rng, (5, 512), dt)
+        gamma = (1.0 + 0.2 * rng.standard_normal(512)).astype(np.float32).astype(dt)
+        w1, w2 = rng_array(rng, (512, 1024), dt, 0.05), rng_array(rng, (512, 1024), dt, 0.05)
+
+        def build(f, a, gm, b, c):
+            h = f.FusedRMSNorm(a, [-1], 1e-6, gm)
+            return f.Mul(f.FusedDense(h, b, None, 3), f.FusedDense(h, c, None, 0))
+        (got,), plan = run_backend(b200, backend, build, [x, gamma, w1, w2], describe=True)
+        assert "of-rms-norm" in plan and "*second-product" in plan and plan.count("\n") == 1, plan
+        h = _rms(x, gamma, 1e-6).astype(np.float32)
+        o = OracleFunction()
+        g = o.FusedDense(h, w1.astype(np.float32), None, 3).astype(dt)
+        u = o.FusedDense(h, w2.astype(np.float32), None, 0).astype(dt)
+        want = (g.astype(np.float32) * u.astype(np.float32)).astype(dt)
+        ok, viol = compare(got, want, RTOL, 1.0)
+        assert ok, viol
+
+
+def test_rms_norm_with_another_user_keeps_its_own_launch(b200, backend):
+    rng = np.random.default_rng(92)
+    x, gamma, w = rng_array(rng, (8, 256), BF16), np.ones(256, np.float32).astype(BF16), rng_array(rng, (256, 512), BF16, 0.06)
+
+    def build(f, a, gm, b):
+        h = f.FusedRMSNorm(a, [-1], 1e-5, gm)
+        return [f.FusedDense(h, b, None, 0), h]
+    got, plan = run_backend(b200, backend, build, [x, gamma, w], describe=True)
+    assert "of-rms-norm" not in plan and "rms_norm[" in plan, plan
+    h = _rms(x, gamma, 1e-5).astype(np.float32).astype(BF16)
+    ok, viol = compare(got[1], h, RTOL, 1.0)
+    assert ok, viol
+    want = OracleFunction().FusedDense(h.astype(np.float32), w.astype(np.float32), None, 0).astype(BF16)
+    ok, viol = compare(got[0], want, RTOL, 1.0)
+    assert ok, viol
