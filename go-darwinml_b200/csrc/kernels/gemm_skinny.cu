@@ -132,6 +132,14 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
   const T* Wg = NK ? reinterpret_cast<const T*>(g.w) + (int64_t)n0 * g.K + k0 : reinterpret_cast<const T*>(g.w) + (int64_t)k0 * g.N + n0;
   const T* Xg = reinterpret_cast<const T*>(g.x) + k0;
   const int w_pitch = (kch + 63) / 64 * 128;   // NK: bytes per column's row of a stage, whole 128-byte groups
+  // W as [K, N]: this thread's unit of the chunk's first 16 rows, in memory and (swizzled) in a stage; 16 rows further: w_step
+  const T* w_thread = Wg + (int64_t)(tid >> 3) * g.N + (tid & 7) * 8;
+  const T* w2_thread = DUAL ? reinterpret_cast<const T*>(g.w2) + (int64_t)k0 * g.N + n0 + (int64_t)(tid >> 3) * g.N + (tid & 7) * 8 : nullptr;
+  const int64_t w_step = 16 * (int64_t)g.N;
+  const uint32_t w_dst0 = (tid >> 3) * 128 + (((tid & 7) ^ ((tid >> 3) & 7)) << 4);
+  // X: with 64 or 128 rows of K per stage a row of the chunk is 8 or 16 units, so (row, unit) of a thread are shifts
+  const bool x_fast = kch == 64 || kch == 128;
+  const int x_shift = kch == 64 ? 3 : 4;
   auto issue_w = [&](int c) {
     if (c >= nch) return;
     const int rows = kc - c * kch < kch ? kc - c * kch : kch;
@@ -147,17 +155,15 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
         else asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0u) : "memory");
       }
     } else {
-      const T* W = Wg + (int64_t)c * kch * g.N;
-      for (int idx = tid; idx < rows * 8; idx += SK_THREADS) {
-        const int row = idx >> 3, ch = idx & 7;
-        sk_cp_async16(wst + row * 128 + ((ch ^ (row & 7)) << 4), W + (int64_t)row * g.N + ch * 8);
-      }
+      // thread (wr, wc) copies unit wc of rows wr, wr + 16, ...: its source and destination advance by constants
+      const int64_t chunk_off = (int64_t)c * kch * g.N;
+      const T* src = w_thread + chunk_off;
+      uint32_t dst = wst + w_dst0;
+      for (int row = tid >> 3; row < rows; row += 16, src += w_step, dst += 16 * 128) sk_cp_async16(dst, src);
       if constexpr (DUAL) {
-        const T* W2 = reinterpret_cast<const T*>(g.w2) + (int64_t)(k0 + c * kch) * g.N + n0;
-        for (int idx = tid; idx < rows * 8; idx += SK_THREADS) {
-          const int row = idx >> 3, ch = idx & 7;
-          sk_cp_async16(wst + w_bytes + row * 128 + ((ch ^ (row & 7)) << 4), W2 + (int64_t)row * g.N + ch * 8);
-        }
+        const T* src2 = w2_thread + chunk_off;
+        dst = wst + w_bytes + w_dst0;
+        for (int row = tid >> 3; row < rows; row += 16, src2 += w_step, dst += 16 * 128) sk_cp_async16(dst, src2);
       }
     }
   };
@@ -171,10 +177,20 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const SkArgs g)
     if constexpr (RMS) {
       if (tid < xch) sk_cp_async16(ring_u + (c % S) * stage_bytes + g_off + tid * 16, reinterpret_cast<const T*>(g.gamma) + k0 + c * kch + tid * 8);
     }
-    for (int idx = tid; idx < ROWS * xch; idx += SK_THREADS) {
-      const int row = idx / xch, ch = idx - row * xch;
-      if (row < g.M) sk_cp_async16(xst_u + row * x_pitch + ch * 16, X + (int64_t)row * g.K + ch * 8);
-      else *reinterpret_cast<uint4*>(xst + row * x_pitch + ch * 16) = make_uint4(0, 0, 0, 0);
+    if (x_fast) {
+      const int ch = tid & ((1 << x_shift) - 1), rstep = SK_THREADS >> x_shift;
+      if (ch < xch) {
+        for (int row = tid >> x_shift; row < ROWS; row += rstep) {
+          if (row < g.M) sk_cp_async16(xst_u + row * x_pitch + ch * 16, X + (int64_t)row * g.K + ch * 8);
+          else *reinterpret_cast<uint4*>(xst + row * x_pitch + ch * 16) = make_uint4(0, 0, 0, 0);
+        }
+      }
+    } else {
+      for (int idx = tid; idx < ROWS * xch; idx += SK_THREADS) {
+        const int row = idx / xch, ch = idx - row * xch;
+        if (row < g.M) sk_cp_async16(xst_u + row * x_pitch + ch * 16, X + (int64_t)row * g.K + ch * 8);
+        else *reinterpret_cast<uint4*>(xst + row * x_pitch + ch * 16) = make_uint4(0, 0, 0, 0);
+      }
     }
   };
   pdl_launch_dependents();
