@@ -335,21 +335,36 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_mma_kernel(co
   // so two chunks are always in flight under the arithmetic and one barrier per chunk is all the ordering needed (the
   // buffer that takes chunk c + 2 held chunk c - 1, which every warp finished before this iteration's barrier).
   const int nchunks = (key_end - key_begin + DEC_MMA_CHUNK - 1) / DEC_MMA_CHUNK;
+  // Thread (lk, lc) copies 16-byte unit lc of keys lk, lk + 32, lk + 64, lk + 96 of a chunk: its offset in a buffer
+  // (the swizzle depends on lk & 7 only) and its sources advance by constants.
+  const int lk = tid >> 3, lc = tid & 7;
+  const uint32_t l_off = lk * 128 + ((lc ^ (lk & 7)) << 4);
+  const T* k_thread = Kb + (int64_t)(key_begin + lk) * g.k_ss + lc * 8;
+  const T* v_thread = Vb + (int64_t)(key_begin + lk) * g.v_ss + lc * 8;
+  const int64_t k_step = 32 * g.k_ss, v_step = 32 * g.v_ss;
   auto issue = [&](int c) {
     if (c < nchunks) {
       const int c0 = key_begin + c * DEC_MMA_CHUNK;
-      const uint32_t kb_u = ring_u + (c % DEC_MMA_BUFS) * DEC_MMA_BUF_BYTES, vb_u = kb_u + DEC_MMA_CHUNK * DEC_D * 2;
+      const uint32_t kb_u = ring_u + (c % DEC_MMA_BUFS) * DEC_MMA_BUF_BYTES + l_off, vb_u = kb_u + DEC_MMA_CHUNK * DEC_D * 2;
+      const T* ks = k_thread + (int64_t)c * DEC_MMA_CHUNK * g.k_ss;
+      const T* vs = v_thread + (int64_t)c * DEC_MMA_CHUNK * g.v_ss;
+      if (c0 + DEC_MMA_CHUNK <= key_end) {   // a whole chunk: no guards
 #pragma unroll
-      for (int it = 0; it < DEC_MMA_CHUNK * 8 / DEC_THREADS; ++it) {
-        const int idx = it * DEC_THREADS + tid, key = idx >> 3, ch = idx & 7;
-        const uint32_t off = key * 128 + ((ch ^ (key & 7)) << 4);
-        if (c0 + key < key_end) {
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kb_u + off), "l"(Kb + (int64_t)(c0 + key) * g.k_ss + ch * 8) : "memory");
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vb_u + off), "l"(Vb + (int64_t)(c0 + key) * g.v_ss + ch * 8) : "memory");
-        } else {
-          const uint32_t z = 0;
-          asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(kb_u + off), "r"(z) : "memory");
-          asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(vb_u + off), "r"(z) : "memory");
+        for (int it = 0; it < 4; ++it) {
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kb_u + it * 32 * 128), "l"(ks + it * k_step) : "memory");
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vb_u + it * 32 * 128), "l"(vs + it * v_step) : "memory");
+        }
+      } else {
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          if (c0 + lk + 32 * it < key_end) {
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kb_u + it * 32 * 128), "l"(ks + it * k_step) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vb_u + it * 32 * 128), "l"(vs + it * v_step) : "memory");
+          } else {
+            const uint32_t z = 0;
+            asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(kb_u + it * 32 * 128), "r"(z) : "memory");
+            asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(vb_u + it * 32 * 128), "r"(z) : "memory");
+          }
         }
       }
     }
@@ -362,6 +377,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_mma_kernel(co
     // the mask terms of this thread's 2 rows x 4 keys, in log2 units, requested before the wait
     const int wkey = c0 + warp * 16;   // the warp's first key
     float mk[2][4];
+    const int64_t mkey = (int64_t)(wkey + kc2) * g.m_k;   // the thread's first key of the chunk in the mask
 #pragma unroll
     for (int j = 0; j < 2; ++j)
 #pragma unroll
@@ -370,7 +386,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_mma_kernel(co
         const bool real = (i < 2 ? row0_real : row1_real);
         float t = key < key_end ? 0.f : -INFINITY;
         if (g.mask_kind != 0 && key < key_end && real) {
-          const int64_t at = (i < 2 ? mrow0 : mrow1) + (int64_t)key * g.m_k;
+          const int64_t at = (i < 2 ? mrow0 : mrow1) + mkey + (8 * j + (i & 1)) * g.m_k;
           if (g.mask_kind == 1) t = reinterpret_cast<const uint8_t*>(g.mask)[at] ? 0.f : -INFINITY;
           else t = dec_to_f<T>(reinterpret_cast<const T*>(g.mask)[at]) * 1.4426950408889634f;
         }
