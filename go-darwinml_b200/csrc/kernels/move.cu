@@ -10,6 +10,7 @@
 #include <cuda_fp16.h>
 
 #include "../kernels.h"
+#include "pdl.cuh"
 
 namespace b200 {
 namespace k {
@@ -323,6 +324,8 @@ __global__ void __launch_bounds__(256) dynamic_update_inplace_kernel(const DynAr
 template <typename E>
 __global__ void __launch_bounds__(256) dynamic_update_inplace2_kernel(const DynArgs a0, const DynArgs a1, int64_t total) {
   __shared__ int64_t start[kMaxDims];
+  pdl_launch_dependents();
+  pdl_wait();
   const DynArgs& a = blockIdx.y ? a1 : a0;
   block_starts(a, start);
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -361,12 +364,17 @@ Status dynamic_update_slice_inplace2(Device* dev, const DynSliceParams& p0, cons
   B200_TRY(dev->MakeCurrent());
   const dim3 grid(grid_for(dev, total), 2);
   cudaStream_t s = dev->stream();
+  cudaError_t e;   // launched as a programmatic dependent (a decoding step is a chain of such small kernels)
   switch (p0.elt_size) {
-    case 1: dynamic_update_inplace2_kernel<uint8_t><<<grid, 256, 0, s>>>(a0, a1, total); break;
-    case 2: dynamic_update_inplace2_kernel<uint16_t><<<grid, 256, 0, s>>>(a0, a1, total); break;
-    case 4: dynamic_update_inplace2_kernel<uint32_t><<<grid, 256, 0, s>>>(a0, a1, total); break;
-    case 8: dynamic_update_inplace2_kernel<uint64_t><<<grid, 256, 0, s>>>(a0, a1, total); break;
+    case 1: e = launch_dependent_dims(dynamic_update_inplace2_kernel<uint8_t>, grid, dim3(256), 0, s, a0, a1, total); break;
+    case 2: e = launch_dependent_dims(dynamic_update_inplace2_kernel<uint16_t>, grid, dim3(256), 0, s, a0, a1, total); break;
+    case 4: e = launch_dependent_dims(dynamic_update_inplace2_kernel<uint32_t>, grid, dim3(256), 0, s, a0, a1, total); break;
+    case 8: e = launch_dependent_dims(dynamic_update_inplace2_kernel<uint64_t>, grid, dim3(256), 0, s, a0, a1, total); break;
     default: return Status::Invalid("dynamic slice: element size");
+  }
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return Status::Cuda(strfmt("dynamic_update_slice_inplace2: %s", cudaGetErrorString(e)));
   }
   return dev->CheckLaunch("dynamic_update_slice_inplace2");
 }

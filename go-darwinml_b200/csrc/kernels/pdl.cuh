@@ -36,5 +36,22 @@ cudaError_t launch_dependent(void (*kernel)(KArgs...), unsigned grid, unsigned b
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
+// The same with a grid and a block of up to three dimensions.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent_dims(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  static const bool on = []() { const char* v = getenv("B200MLX_PDL"); return !(v && v[0] == '0'); }();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = on ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 }  // namespace k
 }  // namespace b200

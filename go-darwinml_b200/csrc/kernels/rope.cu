@@ -11,6 +11,7 @@
 #include <cuda_fp16.h>
 
 #include "../kernels.h"
+#include "pdl.cuh"
 
 namespace b200 {
 namespace k {
@@ -124,6 +125,8 @@ struct RopeArgs {
 template <typename T>
 __global__ void __launch_bounds__(256) rope_kernel(const RopeArgs a) {
   using C = RopeCvt<T>;
+  pdl_launch_dependents();
+  pdl_wait();
   const uint32_t half = a.head_vecs >> 1;
   const uint32_t row_stride = gridDim.x * blockDim.y;
   const uint32_t rows = (uint32_t)a.rows;
@@ -200,9 +203,15 @@ Status rope(Device* dev, const RopeParams& p) {
   int64_t blocks = (p.rows + 2 * block.y - 1) / (2 * block.y);   // two rows per thread and iteration
   const int64_t cap = (int64_t)dev->sm_count() * 16;
   if (blocks > cap) blocks = cap;
-  if (p.dtype == B200_FLOAT32) rope_kernel<float><<<(unsigned)blocks, block, 0, dev->stream()>>>(a);
-  else if (p.dtype == B200_BFLOAT16) rope_kernel<__nv_bfloat16><<<(unsigned)blocks, block, 0, dev->stream()>>>(a);
-  else rope_kernel<__half><<<(unsigned)blocks, block, 0, dev->stream()>>>(a);
+  // launched as a programmatic dependent: the launch itself runs under the previous kernel's tail
+  cudaError_t e;
+  if (p.dtype == B200_FLOAT32) e = launch_dependent_dims(rope_kernel<float>, dim3((unsigned)blocks), block, 0, dev->stream(), a);
+  else if (p.dtype == B200_BFLOAT16) e = launch_dependent_dims(rope_kernel<__nv_bfloat16>, dim3((unsigned)blocks), block, 0, dev->stream(), a);
+  else e = launch_dependent_dims(rope_kernel<__half>, dim3((unsigned)blocks), block, 0, dev->stream(), a);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return Status::Cuda(strfmt("rope: %s", cudaGetErrorString(e)));
+  }
   return dev->CheckLaunch("rope");
 }
 
