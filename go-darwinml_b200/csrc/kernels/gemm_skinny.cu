@@ -3,8 +3,8 @@
 // Such a product is bound by reading W once (2 K N bytes); the 128 x 256 tensor-core tile gives it N / 256 CTAs, each
 // streaming its whole K through one SM's load path (28 us for K = 3072, N = 768).  Here many CTAs share W: a CTA owns
 // 64 columns and one slice of K and streams the slice through a four-stage ring of 64-row chunks in shared memory
-// (16-byte asynchronous copies, always three chunks ahead of the arithmetic; a slice of up to 256 rows is simply in
-// flight at once), multiplies with mma.sync m16n8k16 (X as one, two or four 16-row operands, rows past M zero), and
+// (128-row chunks when the CTAs are few; 16-byte asynchronous copies, always three chunks ahead of the arithmetic; a
+// slice that fits the ring is simply in flight at once), multiplies with mma.sync m16n8k16 (X as one, two or four 16-row operands, rows past M zero), and
 // holds an M x 64 fp32 partial.  A slab's (at most 8) slices are the CTAs of one cluster: the partials meet through
 // distributed shared memory, added in slice order (the same sum on every run), each CTA finishing a share of the
 // outputs (bias, activation, residual).  The other reduction (B200MLX_GEMM_SKINNY_CLUSTER=0: up to 16 slices, no
@@ -29,7 +29,7 @@ namespace {
 constexpr int SK_THREADS = 128;
 constexpr int SK_BN = 64;
 constexpr int SK_MAX_ROWS = 64;
-constexpr int SK_MAX_SPLITS = 16;   // the last CTA adds the slices' partial sums: two rounds of eight loads at most (longer K: more, 512 per slice)
+constexpr int SK_MAX_SPLITS = 16;   // reduction through global memory: the last CTA adds the slices' partial sums in two rounds of eight loads at most
 constexpr int SK_STAGES = 4;   // at most; three when that lets the whole grid be resident at once
 constexpr int SK_X_PAD = 8;   // elements: the X rows' pitch is an odd number of 16-byte units, conflict-free for ldmatrix
 
@@ -42,9 +42,9 @@ struct SkArgs {
   void* c;
   const void* bias;
   const void* residual;
-  float* partial;       // [splits, 16, N]
+  float* partial;       // [splits, 16 / 32 / 64 rows, N] (reduction through global memory only)
   unsigned* counters;   // [N / 64], zero between launches
-  int M, N, K, kc, kch, stages, splits, act, residual_mul;   // kc: K per slice; kch: rows of K per ring stage; stages: 3 or 4
+  int M, N, K, kc, kch, stages, splits, act, residual_mul;   // kc: K per slice; kch: rows of K per ring stage; stages: 3 or 4 (the kernel's S)
   int w_static;   // W may be fetched before the previous kernel on the stream has finished
 };
 
