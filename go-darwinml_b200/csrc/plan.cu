@@ -1066,7 +1066,7 @@ class Planner {
   struct LastDus {
     int step = -1;
     std::vector<int> start_slots;
-    int rank = 0, elt_size = 0;
+    int rank = 0, elt_size = 0, out_slot = -1, x_slot = -1;
     int64_t x_dims[k::kMaxDims] = {0}, b_dims[k::kMaxDims] = {0};
     std::function<k::DynSliceParams(void* const*)> bind;
   } last_dus_;
@@ -1130,8 +1130,10 @@ class Planner {
     };
     // A second update with the same start indices and block geometry right after the first (a layer's key cache, then its
     // value cache): one step, and one launch when both turn out to be in place.
+    // (never an update OF the first one's result or FROM it: the two run side by side)
     if (update && last_dus_.step == (int)ex_->steps.size() - 1 && last_dus_.step >= 0 && last_dus_.start_slots == start_slots &&
-        last_dus_.rank == dp.rank && last_dus_.elt_size == dp.elt_size &&
+        last_dus_.rank == dp.rank && last_dus_.elt_size == dp.elt_size && x_slot != last_dus_.out_slot && u_slot != last_dus_.out_slot &&
+        out_slot != last_dus_.out_slot && x_slot != last_dus_.x_slot &&
         std::equal(dp.x_dims, dp.x_dims + dp.rank, last_dus_.x_dims) && std::equal(dp.b_dims, dp.b_dims + dp.rank, last_dus_.b_dims)) {
       Step& prev = ex_->steps.back();
       prev.desc.insert(prev.desc.size() - 1, upd_src ? " + a second one, read in place" : " + a second one");
@@ -1154,6 +1156,8 @@ class Planner {
       last_dus_.start_slots = start_slots;
       last_dus_.rank = dp.rank;
       last_dus_.elt_size = dp.elt_size;
+      last_dus_.out_slot = out_slot;
+      last_dus_.x_slot = x_slot;
       std::copy(dp.x_dims, dp.x_dims + k::kMaxDims, last_dus_.x_dims);
       std::copy(dp.b_dims, dp.b_dims + k::kMaxDims, last_dus_.b_dims);
       last_dus_.bind = bind;

@@ -130,3 +130,23 @@ def test_llama_shaped_decode_in_bf16_takes_the_decoding_kernels(b200, backend):
     assert np.abs(got_logits - want).max() <= 0.04 * np.abs(want).max(), (np.abs(got_logits - want).max(), np.abs(want).max())
     exe.Finalize()
     builder.Finalize()
+
+
+def test_an_update_of_an_updated_tensor_keeps_its_order(b200, backend):
+    # two DynamicUpdateSlices with the same start and geometry, the second applied to the first's result: they must not
+    # be joined into one side-by-side launch -- the second's block wins
+    from tests.util import run_backend, run_oracle
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((4, 6, 8)).astype(np.float32)
+    a, b = rng.standard_normal((4, 1, 8)).astype(np.float32), rng.standard_normal((4, 1, 8)).astype(np.float32)
+    t = np.array(3, dtype=np.int32)
+
+    def build(f, xx, aa, bb, tt):
+        zero = f.Constant(np.array([0], dtype=np.int32))
+        first = f.DynamicUpdateSlice(xx, aa, [zero, tt, zero])
+        return f.DynamicUpdateSlice(first, bb, [zero, tt, zero])
+    (got,), plan = run_backend(b200, backend, build, [x, a, b, t], describe=True)
+    (want,) = run_oracle(build, [x, a, b, t])
+    assert "a second one" not in plan, plan
+    np.testing.assert_array_equal(got, want)
+    np.testing.assert_array_equal(got[:, 3, :], b[:, 0, :])
