@@ -1395,7 +1395,10 @@ class Planner {
     }
     const int w2_slot = dual_w2 ? SlotOf(dual_w2) : -1;
     const int dual_tmp = dual_w2 ? NewTemp(B * M * N * es_out + 16) : -1;
-    if (dual_w2) { st.reads.push_back(w2_slot); st.writes.push_back(dual_tmp); }
+    if (dual_w2) {
+      st.reads.push_back(w2_slot);
+      st.writes.push_back(dual_tmp);
+    }
     st.writes.insert(st.writes.begin(), gemm_out);
     // fp32 on the tensor cores splits both operands into bf16 planes: their room comes from the plan's arena, so the step
     // allocates nothing and can be recorded
@@ -1403,7 +1406,8 @@ class Planner {
     // of the step's own (zeroed once; the kernel leaves them at zero).
     // weights that are an input or a constant of this plan: nothing this plan launches writes them (an input that a
     // DynamicUpdateSlice updates in place feeds nothing else)
-    gp.b_static = ex_->slots[b_slot].kind == SlotKind::Input || ex_->slots[b_slot].kind == SlotKind::Const;
+    auto never_written = [&](int slot) { return ex_->slots[slot].kind == SlotKind::Input || ex_->slots[slot].kind == SlotKind::Const; };
+    gp.b_static = never_written(b_slot) && (w2_slot < 0 || never_written(w2_slot));   // (a gated pair: both weights)
     const int64_t skinny_bytes = k::gemm_skinny_scratch_bytes(gp, ex_->dev->sm_count());
     const int64_t split_bytes = x->dtype == B200_FLOAT32 ? k::gemm_split_scratch_bytes(B, M, N, K) : skinny_bytes;
     const int split_slot = split_bytes > 0 ? NewTemp(split_bytes) : -1;
