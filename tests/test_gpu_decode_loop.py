@@ -11,6 +11,7 @@ import pytest
 
 import go_darwinml_b200.workloads as w
 from oracle.oracle import OracleFunction, compare
+from tests.util import default_switches
 
 pytestmark = pytest.mark.gpu
 
@@ -40,7 +41,7 @@ def test_greedy_decode_matches_the_oracle_token_for_token(b200, backend):
     f.Return([tokens, logits], None)
     exe = builder.Compile()
     plan = exe.Describe()
-    assert "while[" in plan and "(5 updated in place)" in plan and "on the device when replayed" in plan, plan
+    assert ("while[" in plan and "(5 updated in place)" in plan and "on the device when replayed" in plan) or not default_switches(), plan
     want_tokens, want_logits = w.gpt2_greedy_decode(OracleFunction(), c, code, n_tokens, *arrays)
     assert len(np.unique(np.asarray(want_tokens))) > 3   # the model does produce different tokens
     bufs = [backend.FromNumpy(a) for a in arrays]
@@ -92,7 +93,7 @@ def test_llama_shaped_greedy_decode_matches_the_oracle_token_for_token(b200, bac
     code = int(b200.dtypes.Float32)
     builder, exe = _compile_llama_decode(b200, backend, c, code, n_tokens, shapes, arrays)
     plan = exe.Describe()
-    assert "while[" in plan and "on the device when replayed" in plan, plan
+    assert ("while[" in plan and "on the device when replayed" in plan) or not default_switches(), plan
     want_tokens, want_logits = w.llama_greedy_decode(OracleFunction(), c, code, n_tokens, *arrays)
     assert len(np.unique(np.asarray(want_tokens))) > 3
     bufs = [backend.FromNumpy(a) for a in arrays]
@@ -118,7 +119,7 @@ def test_llama_shaped_decode_in_bf16_takes_the_decoding_kernels(b200, backend):
     code = int(b200.dtypes.BFloat16)
     builder, exe = _compile_llama_decode(b200, backend, c, code, 1, shapes, arrays)
     plan = exe.Describe()
-    assert "attention_decode[" in plan and "Hkv=2" in plan and plan.count("few-rows") >= 2 * 4 + 1, plan
+    assert ("attention_decode[" in plan and "Hkv=2" in plan and plan.count("few-rows") >= 2 * 4 + 1) or not default_switches(), plan
     _, want_logits = w.llama_greedy_decode(OracleFunction(), c, code, 1, *arrays)
     bufs = [backend.FromNumpy(a) for a in arrays]
     outs = exe.Execute(bufs, None, 0)
@@ -147,6 +148,6 @@ def test_an_update_of_an_updated_tensor_keeps_its_order(b200, backend):
         return f.DynamicUpdateSlice(first, bb, [zero, tt, zero])
     (got,), plan = run_backend(b200, backend, build, [x, a, b, t], describe=True)
     (want,) = run_oracle(build, [x, a, b, t])
-    assert "a second one" not in plan, plan
+    assert ("a second one" not in plan) or not default_switches(), plan
     np.testing.assert_array_equal(got, want)
     np.testing.assert_array_equal(got[:, 3, :], b[:, 0, :])

@@ -10,7 +10,7 @@ import numpy as np
 import pytest
 
 from oracle.oracle import OracleFunction, compare
-from tests.util import rng_array, run_backend
+from tests.util import default_switches, rng_array, run_backend
 
 pytestmark = pytest.mark.gpu
 BF16 = ml_dtypes.bfloat16
@@ -35,7 +35,7 @@ def _check(b200, backend, M, N, K, dtype, bias, act, residual, seed=0, lead=None
         ri = len(inputs); inputs.append(rng_array(rng, xs[:-1] + (N,), dtype))
     build = lambda f, *p: _dense(f, p[0], p[1], p[bi] if bias else None, act, p[ri] if residual else None)
     (got,), plan = run_backend(b200, backend, build, inputs, describe=True)
-    assert "few-rows" in plan and plan.count("\n") == 1, plan
+    assert ("few-rows" in plan and plan.count("\n") == 1) or not default_switches(), plan
     # the yardstick: exact product rounded once (twice with a residual), as the fused epilogue does
     o = OracleFunction()
     want = o.FusedDense(x.astype(np.float32), w.astype(np.float32), inputs[bi].astype(np.float32) if bias else None, act).astype(dtype)
@@ -107,7 +107,7 @@ def test_two_products_in_one_plan_have_counters_of_their_own(b200, backend):
     x, w1, w2 = rng_array(rng, (4, 256), BF16), rng_array(rng, (256, 1024), BF16, 0.06), rng_array(rng, (1024, 256), BF16, 0.03)
     build = lambda f, xx, a, b: f.FusedDense(f.FusedDense(xx, a, None, 2), b, None, 0)
     (got,), plan = run_backend(b200, backend, build, [x, w1, w2], describe=True)
-    assert plan.count("few-rows") == 2, plan
+    assert (plan.count("few-rows") == 2) or not default_switches(), plan
     o = OracleFunction()
     h = o.FusedDense(x.astype(np.float32), w1.astype(np.float32), None, 2).astype(BF16)
     want = o.FusedDense(h.astype(np.float32), w2.astype(np.float32), None, 0).astype(BF16)
@@ -120,7 +120,7 @@ def test_other_shapes_keep_their_kernels(b200, backend):
     for M, N, K in [(65, 768, 768), (16, 100, 64), (16, 64, 24)]:
         x, w = rng_array(rng, (M, K), BF16), rng_array(rng, (K, N), BF16, 0.1)
         (got,), plan = run_backend(b200, backend, lambda f, a, b: f.FusedDense(a, b, None, 0), [x, w], describe=True)
-        assert "few-rows" not in plan, plan
+        assert ("few-rows" not in plan) or not default_switches(), plan
         want = OracleFunction().FusedDense(x.astype(np.float32), w.astype(np.float32), None, 0).astype(BF16)
         ok, viol = compare(got, want, RTOL, 1.0)
         assert ok, viol
@@ -135,7 +135,7 @@ def test_weights_stored_n_major_and_a_ragged_n(b200, backend, M, N, K):
     w = rng_array(rng, (N, K), BF16, 1.0 / np.sqrt(K))
     (got,), plan = run_backend(b200, backend, lambda f, a, b: f.DotGeneral(a, [1], [], b, [1], []), [x, w], describe=True)
     # (beyond 32768 columns the tensor-core tile fills the GPU and keeps the product)
-    assert ("few-rows" in plan) == (N <= 32768) and "b:NK" in plan and plan.count("\n") == 1, plan
+    assert (("few-rows" in plan) == (N <= 32768) and "b:NK" in plan and plan.count("\n") == 1) or not default_switches(), plan
     want = (x.astype(np.float64) @ w.astype(np.float64).T).astype(np.float32).astype(BF16)
     ok, viol = compare(got, want, RTOL, 1.0)
     assert ok, viol
@@ -145,7 +145,7 @@ def test_n_major_weights_in_f16(b200, backend):
     rng = np.random.default_rng(77)
     x, w = rng_array(rng, (9, 512), np.float16), rng_array(rng, (333, 512), np.float16, 0.05)
     (got,), plan = run_backend(b200, backend, lambda f, a, b: f.DotGeneral(a, [1], [], b, [1], []), [x, w], describe=True)
-    assert "few-rows" in plan, plan
+    assert ("few-rows" in plan) or not default_switches(), plan
     want = (x.astype(np.float64) @ w.astype(np.float64).T).astype(np.float16)
     ok, viol = compare(got, want, RTOL, 1.0)
     assert ok, viol
@@ -161,7 +161,7 @@ def test_gated_pair_of_products_in_one_launch(b200, backend, M, N, K, act):
     w1, w2 = rng_array(rng, (K, N), BF16, 1.0 / np.sqrt(K)), rng_array(rng, (K, N), BF16, 1.0 / np.sqrt(K))
     build = lambda f, a, b, c: f.Mul(f.FusedDense(a, b, None, act), f.FusedDense(a, c, None, 0))
     (got,), plan = run_backend(b200, backend, build, [x, w1, w2], describe=True)
-    assert "*second-product" in plan and "few-rows" in plan and plan.count("\n") == 1, plan
+    assert ("*second-product" in plan and "few-rows" in plan and plan.count("\n") == 1) or not default_switches(), plan
     o = OracleFunction()
     g = o.FusedDense(x.astype(np.float32), w1.astype(np.float32), None, act).astype(BF16)
     u = o.FusedDense(x.astype(np.float32), w2.astype(np.float32), None, 0).astype(BF16)
@@ -178,7 +178,7 @@ def test_gated_pair_is_left_alone_when_the_second_product_is_used_elsewhere(b200
         up = f.FusedDense(a, c, None, 0)
         return [f.Mul(f.FusedDense(a, b, None, 3), up), up]
     got, plan = run_backend(b200, backend, build, [x, w1, w2], describe=True)
-    assert "*second-product" not in plan, plan
+    assert ("*second-product" not in plan) or not default_switches(), plan
     o = OracleFunction()
     g = o.FusedDense(x.astype(np.float32), w1.astype(np.float32), None, 3).astype(BF16)
     u = o.FusedDense(x.astype(np.float32), w2.astype(np.float32), None, 0).astype(BF16)
@@ -203,7 +203,7 @@ def test_rms_norm_applied_inside_the_product(b200, backend, M, N, K):
     w, bias = rng_array(rng, (K, N), BF16, 1.0 / np.sqrt(K)), rng_array(rng, (N,), BF16)
     build = lambda f, a, gm, b, c: f.FusedDense(f.FusedRMSNorm(a, [-1], 1e-5, gm), b, c, 1)
     (got,), plan = run_backend(b200, backend, build, [x, gamma, w, bias], describe=True)
-    assert "of-rms-norm" in plan and "few-rows" in plan and "rms_norm[" not in plan and plan.count("\n") == 1, plan
+    assert ("of-rms-norm" in plan and "few-rows" in plan and "rms_norm[" not in plan and plan.count("\n") == 1) or not default_switches(), plan
     h = _rms(x, gamma, 1e-5)
     want = OracleFunction().FusedDense(h.astype(np.float32), w.astype(np.float32), bias.astype(np.float32), 1).astype(BF16)
     ok, viol = compare(got, want, RTOL, 1.0)
@@ -221,7 +221,7 @@ def test_rms_norm_inside_a_gated_pair_and_f16(b200, backend):
             h = f.FusedRMSNorm(a, [-1], 1e-6, gm)
             return f.Mul(f.FusedDense(h, b, None, 3), f.FusedDense(h, c, None, 0))
         (got,), plan = run_backend(b200, backend, build, [x, gamma, w1, w2], describe=True)
-        assert "of-rms-norm" in plan and "*second-product" in plan and plan.count("\n") == 1, plan
+        assert ("of-rms-norm" in plan and "*second-product" in plan and plan.count("\n") == 1) or not default_switches(), plan
         h = _rms(x, gamma, 1e-6).astype(np.float32)
         o = OracleFunction()
         g = o.FusedDense(h, w1.astype(np.float32), None, 3).astype(dt)
@@ -239,7 +239,7 @@ def test_rms_norm_with_another_user_keeps_its_own_launch(b200, backend):
         h = f.FusedRMSNorm(a, [-1], 1e-5, gm)
         return [f.FusedDense(h, b, None, 0), h]
     got, plan = run_backend(b200, backend, build, [x, gamma, w], describe=True)
-    assert "of-rms-norm" not in plan and "rms_norm[" in plan, plan
+    assert ("of-rms-norm" not in plan and "rms_norm[" in plan) or not default_switches(), plan
     h = _rms(x, gamma, 1e-5).astype(np.float32).astype(BF16)
     ok, viol = compare(got[1], h, RTOL, 1.0)
     assert ok, viol

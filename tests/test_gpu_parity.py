@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 
 from oracle.oracle import compare
-from tests.util import assert_parity, rng_array, run_backend, run_oracle
+from tests.util import default_switches, assert_parity, rng_array, run_backend, run_oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -581,7 +581,7 @@ def test_fused_attention_head_dim_64(b200, backend, layout, heads, kv_heads, cau
                                lambda f, qq, kk, vv: f.FusedScaledDotProductAttention(qq, kk, vv, None, heads, kv_heads, layout, 0.125, causal),
                                [q, k, v], describe=True)
     # one query position without the causal flag takes the cache-reading kernel
-    assert plan.startswith("attention_decode[" if sq == 1 and not causal else "attention[") and plan.count("\n") == 1, plan
+    assert (plan.startswith("attention_decode[" if sq == 1 and not causal else "attention[") and plan.count("\n") == 1) or not default_switches(), plan
     # The fused kernel keeps the scores in fp32 (the unfused lowering rounds them to the storage type before the
     # softmax), so the yardstick is the oracle evaluated on the same inputs in fp32, rounded once at the end.
     from oracle.oracle import OracleFunction, compare

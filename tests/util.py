@@ -6,6 +6,13 @@ import numpy as np
 from oracle.oracle import OracleFunction, compare
 
 
+def default_switches():
+    """True unless an environment switch (B200MLX_...=0) selects a non-default code path: the plan-shape assertions of the
+    GPU tests hold for the default paths only, the numerical ones for every path."""
+    import os
+    return not any(k.startswith("B200MLX_") and v[:1] == "0" for k, v in os.environ.items())
+
+
 def run_backend(pkg, backend, build, inputs, describe=False):
     builder = backend.Builder("test")
     f = builder.Main()
